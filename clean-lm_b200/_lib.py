@@ -1,0 +1,109 @@
+"""ctypes binding of libcleandl_b200.so.  There is no fallback: a missing library is an error."""
+from __future__ import annotations
+
+import ctypes
+from pathlib import Path
+
+LIB_PATH = Path(__file__).resolve().parent / "libcleandl_b200.so"
+
+CDL_BF16, CDL_F32, CDL_I32 = 0, 1, 2
+
+
+class CdlError(RuntimeError):
+    """A C-ABI call returned a negative status; `.status` holds it."""
+
+    def __init__(self, status: int, message: str):
+        super().__init__(f"cleandl_b200 error {status}: {message}")
+        self.status = status
+        self.message = message
+
+
+class CdlTensor(ctypes.Structure):
+    _fields_ = [
+        ("ptr", ctypes.c_void_p),
+        ("dtype", ctypes.c_int32),
+        ("rank", ctypes.c_int32),
+        ("shape", ctypes.c_int64 * 4),
+        ("stride", ctypes.c_int64 * 4),
+    ]
+
+
+class CdlAttnDesc(ctypes.Structure):
+    _fields_ = [("softmax_scale", ctypes.c_float), ("causal", ctypes.c_int32)]
+
+
+if not LIB_PATH.exists():
+    raise ImportError(
+        f"{LIB_PATH} is missing: build it with `python clean-lm_b200/build.py` "
+        "(needs nvcc; the library holds sm_100a code only and has no CPU fallback)"
+    )
+
+lib = ctypes.CDLL(str(LIB_PATH))
+
+_T = ctypes.POINTER(CdlTensor)
+_vp = ctypes.c_void_p
+_sz = ctypes.c_size_t
+
+# name -> argtypes; every entry point declared in include/cleandl_b200.h
+SIGNATURES = {
+    "cdl_b200_last_error": ([], ctypes.c_char_p),
+    "cdl_b200_device_ok": ([ctypes.c_int32], ctypes.c_int32),
+    "cdl_b200_device_status": ([ctypes.POINTER(ctypes.c_int32)], ctypes.c_int32),
+    "cdl_b200_matmul": ([_T, _T, _T, _T, ctypes.c_float, ctypes.c_float, _vp, _sz, _vp],
+                        ctypes.c_int32),
+    "cdl_b200_matmul_scratch_bytes": ([_T, _T, _T, ctypes.POINTER(_sz)], ctypes.c_int32),
+    "cdl_b200_rmsnorm_fwd": ([_T, _T, _T, ctypes.c_float, _T, _T, _vp], ctypes.c_int32),
+    "cdl_b200_rmsnorm_bwd": ([_T, _T, _T, _T, _T, _T, _T, _vp, _sz, _vp], ctypes.c_int32),
+    "cdl_b200_rmsnorm_bwd_scratch_bytes": ([ctypes.c_int64, ctypes.c_int64, ctypes.POINTER(_sz)],
+                                           ctypes.c_int32),
+    "cdl_b200_attn_fwd": ([ctypes.POINTER(CdlAttnDesc), _T, _T, _T, _T, _T, _vp], ctypes.c_int32),
+    "cdl_b200_attn_bwd": ([ctypes.POINTER(CdlAttnDesc), _T, _T, _T, _T, _T, _T, _T, _T, _T, _vp,
+                           _sz, _vp], ctypes.c_int32),
+    "cdl_b200_attn_bwd_scratch_bytes": ([_T, _T, ctypes.POINTER(_sz)], ctypes.c_int32),
+}
+
+for _name, (_args, _res) in SIGNATURES.items():
+    _fn = getattr(lib, _name)
+    _fn.argtypes = _args
+    _fn.restype = _res
+
+
+def last_error() -> str:
+    return lib.cdl_b200_last_error().decode()
+
+
+def check(status: int) -> None:
+    if status != 0:
+        raise CdlError(status, last_error())
+
+
+def tensor_arg(t):
+    """Wraps a torch tensor (any strides) as a cdl_tensor; None stays None (a NULL pointer)."""
+    if t is None:
+        return None
+    import torch
+
+    dt = {torch.bfloat16: CDL_BF16, torch.float32: CDL_F32, torch.int32: CDL_I32}.get(t.dtype)
+    if dt is None:
+        raise CdlError(-1, f"unsupported element type {t.dtype}: f32 or bf16 expected")
+    if t.dim() > 4:
+        raise CdlError(-1, f"rank {t.dim()} exceeds 4")
+    ct = CdlTensor()
+    ct.ptr = t.data_ptr()
+    ct.dtype = dt
+    ct.rank = t.dim()
+    for i in range(t.dim()):
+        ct.shape[i] = t.shape[i]
+        ct.stride[i] = t.stride(i)
+    return ct
+
+
+def ref(ct):
+    return None if ct is None else ctypes.byref(ct)
+
+
+def device_status() -> int:
+    """Synchronises the device; returns (and clears) the kernel status word."""
+    out = ctypes.c_int32(0)
+    check(lib.cdl_b200_device_status(ctypes.byref(out)))
+    return out.value

@@ -1,0 +1,142 @@
+// Library state: thread-local error message, the per-device kernel status word, device
+// queries, TMA tensor-map encoding (through the driver entry point, so the library does not
+// link libcuda directly).
+#include "host.h"
+
+#include <mutex>
+
+namespace cdl {
+
+std::string& last_error() {
+  static thread_local std::string msg;
+  return msg;
+}
+
+int32_t fail(int32_t code, const char* fmt, ...) {
+  char buf[1024];
+  va_list ap;
+  va_start(ap, fmt);
+  vsnprintf(buf, sizeof buf, fmt, ap);
+  va_end(ap);
+  last_error() = buf;
+  return code;
+}
+
+// One word per device (each device that loads the module gets its own copy).
+__device__ int g_kernel_status = 0;
+
+static constexpr int kMaxDevices = 64;
+
+int* device_status_ptr() {
+  static int* ptrs[kMaxDevices] = {};
+  static std::mutex mu;
+  int dev = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= kMaxDevices) return nullptr;
+  std::lock_guard<std::mutex> lock(mu);
+  if (!ptrs[dev]) {
+    void* p = nullptr;
+    if (cudaGetSymbolAddress(&p, g_kernel_status) != cudaSuccess) return nullptr;
+    ptrs[dev] = static_cast<int*>(p);
+  }
+  return ptrs[dev];
+}
+
+int sm_count() {
+  static int counts[kMaxDevices] = {};
+  int dev = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= kMaxDevices) return 148;
+  if (!counts[dev]) {
+    int n = 0;
+    if (cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || n <= 0)
+      n = 148;
+    counts[dev] = n;
+  }
+  return counts[dev];
+}
+
+using EncodeTiledFn = CUresult (*)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*,
+                                   const cuuint64_t*, const cuuint64_t*, const cuuint32_t*,
+                                   const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
+                                   CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+static EncodeTiledFn encode_fn() {
+  static EncodeTiledFn fn = [] {
+    void* p = nullptr;
+    cudaDriverEntryPointQueryResult q;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &q) !=
+            cudaSuccess ||
+        q != cudaDriverEntryPointSuccess)
+      p = nullptr;
+    return reinterpret_cast<EncodeTiledFn>(p);
+  }();
+  return fn;
+}
+
+int32_t encode_tmap(CUtensorMap* out, const void* base, int32_t dtype, int rank,
+                    const uint64_t* dims, const uint64_t* strides_bytes, const uint32_t* box,
+                    bool swizzle128) {
+  EncodeTiledFn fn = encode_fn();
+  if (!fn) return fail(CDL_ERR_CUDA, "cuTensorMapEncodeTiled is not available from the driver");
+  cuuint64_t gdim[5];
+  cuuint64_t gstr[5];
+  cuuint32_t bx[5];
+  cuuint32_t estr[5];
+  for (int i = 0; i < rank; ++i) {
+    gdim[i] = dims[i];
+    bx[i] = box[i];
+    estr[i] = 1;
+    if (i > 0) gstr[i - 1] = strides_bytes[i];
+  }
+  CUtensorMapDataType dt =
+      dtype == CDL_BF16 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT32;
+  CUresult r = fn(out, dt, static_cast<cuuint32_t>(rank), const_cast<void*>(base), gdim, gstr, bx,
+                  estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                  swizzle128 ? CU_TENSOR_MAP_SWIZZLE_128B : CU_TENSOR_MAP_SWIZZLE_NONE,
+                  CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  if (r != CUDA_SUCCESS)
+    return fail(CDL_ERR_INVALID,
+                "tensor map encode failed (CUresult %d): base %p rank %d dims [%llu,%llu,%llu,%llu] "
+                "stride bytes [%llu,%llu,%llu] box [%u,%u,%u,%u]",
+                static_cast<int>(r), base, rank, (unsigned long long)gdim[0],
+                (unsigned long long)(rank > 1 ? gdim[1] : 0),
+                (unsigned long long)(rank > 2 ? gdim[2] : 0),
+                (unsigned long long)(rank > 3 ? gdim[3] : 0),
+                (unsigned long long)(rank > 1 ? gstr[0] : 0),
+                (unsigned long long)(rank > 2 ? gstr[1] : 0),
+                (unsigned long long)(rank > 3 ? gstr[2] : 0), bx[0], rank > 1 ? bx[1] : 0,
+                rank > 2 ? bx[2] : 0, rank > 3 ? bx[3] : 0);
+  return CDL_OK;
+}
+
+}  // namespace cdl
+
+extern "C" {
+
+const char* cdl_b200_last_error(void) { return cdl::last_error().c_str(); }
+
+int32_t cdl_b200_device_ok(int32_t device) {
+  int major = 0, minor = 0;
+  CDL_CUDA(cudaDeviceGetAttribute(&major, cudaDevAttrComputeCapabilityMajor, device));
+  CDL_CUDA(cudaDeviceGetAttribute(&minor, cudaDevAttrComputeCapabilityMinor, device));
+  if (major != 10)
+    return cdl::fail(CDL_ERR_UNSUPPORTED,
+                     "device %d has compute capability %d.%d; this library only holds sm_100a code",
+                     device, major, minor);
+  return CDL_OK;
+}
+
+int32_t cdl_b200_device_status(int32_t* status_out) {
+  int* p = cdl::device_status_ptr();
+  if (!p) return cdl::fail(CDL_ERR_CUDA, "cannot resolve the device status word");
+  CDL_CUDA(cudaDeviceSynchronize());
+  int v = 0;
+  CDL_CUDA(cudaMemcpy(&v, p, sizeof v, cudaMemcpyDeviceToHost));
+  if (v != 0) {
+    int zero = 0;
+    CDL_CUDA(cudaMemcpy(p, &zero, sizeof zero, cudaMemcpyHostToDevice));
+  }
+  if (status_out) *status_out = v;
+  return CDL_OK;
+}
+
+}  // extern "C"

@@ -1,0 +1,51 @@
+// Host-side helpers shared by the operator implementations: error reporting, operand
+// validation and TMA tensor-map encoding.
+#pragma once
+#include <cuda.h>
+#include <cuda_runtime.h>
+#include <stdarg.h>
+#include <stdint.h>
+#include <stdio.h>
+
+#include <string>
+
+#include "../../include/cleandl_b200.h"
+
+namespace cdl {
+
+// Thread-local message of the last failure; returned by cdl_b200_last_error().
+std::string& last_error();
+// Records a formatted message and returns `code`.
+int32_t fail(int32_t code, const char* fmt, ...) __attribute__((format(printf, 2, 3)));
+
+#define CDL_CUDA(expr)                                                                     \
+  do {                                                                                     \
+    cudaError_t _e = (expr);                                                               \
+    if (_e != cudaSuccess)                                                                 \
+      return ::cdl::fail(CDL_ERR_CUDA, "%s failed: %s", #expr, cudaGetErrorString(_e));    \
+  } while (0)
+
+#define CDL_CHECK(expr)           \
+  do {                            \
+    int32_t _s = (expr);          \
+    if (_s != CDL_OK) return _s;  \
+  } while (0)
+
+inline size_t dtype_size(int32_t dt) { return dt == CDL_BF16 ? 2 : 4; }
+inline const char* dtype_name(int32_t dt) {
+  return dt == CDL_BF16 ? "bf16" : dt == CDL_F32 ? "f32" : dt == CDL_I32 ? "i32" : "?";
+}
+
+// Device-global status word written by kernels whose bounded waits ran out (see ptx.cuh).
+int* device_status_ptr();  // device address for the current device; nullptr on failure
+
+// The number of SMs of the current device (cached per device).
+int sm_count();
+
+// Encodes a tiled tensor map over bf16/f32 data.  dims/strides are innermost-first; strides are
+// in BYTES for dims 1.. (the innermost is contiguous).  box is innermost-first.
+int32_t encode_tmap(CUtensorMap* out, const void* base, int32_t dtype, int rank,
+                    const uint64_t* dims, const uint64_t* strides_bytes, const uint32_t* box,
+                    bool swizzle128);
+
+}  // namespace cdl

@@ -1,0 +1,409 @@
+// RMSNorm forward and backward: HBM-bound streaming kernels.
+//
+// Forward follows NormFwd / SpecializedExecutor of the reference
+// (crates/cleandl/src/execgraph/ops/norm/mod.rs:72-85, ops/norm/specialized.rs:116-200; kernel
+// crates/cleandl-specialized-kernels/src/kernels/norm/forward.rs:569-657):
+//     r_i = rsqrt(mean_j x_ij^2 + eps);   y_ij = bf16((f32(x_ij) * r_i) * scale_j + bias_j)
+// Backward has no implementation in the reference tree, only call sites
+// (crates/sky-1/src/training/model/decoder.rs:599-607, 684-692); the math is the derivative of
+// the forward above.
+//
+// Design: one warp owns one row at a time.  A lane holds 8 consecutive bf16 (one 128-bit
+// access) of every 256-column stripe, so a warp's access is a fully coalesced 512 B; the whole
+// row stays in registers between the reduction and the scaling pass, which makes both kernels
+// single-pass over HBM.  Row reductions are five shuffle steps; no shared memory or block
+// barrier is on the critical path.
+#include "host.h"
+#include "ptx.cuh"
+
+namespace cdl {
+namespace norm {
+
+constexpr int FWD_THREADS = 256;
+constexpr int BWD_THREADS = 128;
+constexpr int BWD_BLOCKS_PER_SM = 3;
+constexpr int MAX_PARTIALS = 1024;  // upper bound on backward grid size (scratch sizing)
+
+__device__ __forceinline__ float warp_sum(float v) {
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+  return v;
+}
+
+__device__ __forceinline__ void unpack8(const uint4& q, float (&f)[8]) {
+  f[0] = bf16_lo(q.x); f[1] = bf16_hi(q.x); f[2] = bf16_lo(q.y); f[3] = bf16_hi(q.y);
+  f[4] = bf16_lo(q.z); f[5] = bf16_hi(q.z); f[6] = bf16_lo(q.w); f[7] = bf16_hi(q.w);
+}
+__device__ __forceinline__ uint4 pack8(const float (&f)[8]) {
+  uint4 q;
+  q.x = pack_bf16x2(f[0], f[1]); q.y = pack_bf16x2(f[2], f[3]);
+  q.z = pack_bf16x2(f[4], f[5]); q.w = pack_bf16x2(f[6], f[7]);
+  return q;
+}
+
+// NCH = number of 256-column stripes a row spans (cols <= 256 * NCH).
+template <int NCH>
+__global__ void __launch_bounds__(FWD_THREADS)
+    rmsnorm_fwd_kernel(const __nv_bfloat16* __restrict__ x, long long ldx,
+                       const __nv_bfloat16* __restrict__ scale,
+                       const __nv_bfloat16* __restrict__ bias, __nv_bfloat16* __restrict__ y,
+                       long long ldy, float* __restrict__ r_inv, long long r_inv_stride, int rows,
+                       int cols, float eps) {
+  const int lane = threadIdx.x & 31;
+  const int warps_per_block = FWD_THREADS / 32;
+  const long long warp_global = static_cast<long long>(blockIdx.x) * warps_per_block + (threadIdx.x >> 5);
+  const long long warp_stride = static_cast<long long>(gridDim.x) * warps_per_block;
+  const float inv_cols = 1.0f / static_cast<float>(cols);
+
+  for (long long row = warp_global; row < rows; row += warp_stride) {
+    const __nv_bfloat16* xr = x + row * ldx;
+    uint4 v[NCH];
+#pragma unroll
+    for (int c = 0; c < NCH; ++c) {
+      const int col = c * 256 + lane * 8;
+      v[c] = col < cols ? ld_nc_v4(xr + col) : make_uint4(0, 0, 0, 0);
+    }
+    float ss = 0.f;
+#pragma unroll
+    for (int c = 0; c < NCH; ++c) {
+      float f[8];
+      unpack8(v[c], f);
+#pragma unroll
+      for (int j = 0; j < 8; ++j) ss = fmaf(f[j], f[j], ss);
+    }
+    ss = warp_sum(ss);
+    const float r = rsqrtf(ss * inv_cols + eps);
+    if (r_inv != nullptr && lane == 0) r_inv[row * r_inv_stride] = r;
+    __nv_bfloat16* yr = y + row * ldy;
+#pragma unroll
+    for (int c = 0; c < NCH; ++c) {
+      const int col = c * 256 + lane * 8;
+      if (col < cols) {
+        float f[8];
+        unpack8(v[c], f);
+#pragma unroll
+        for (int j = 0; j < 8; ++j) f[j] *= r;
+        if (scale != nullptr) {
+          float s[8];
+          unpack8(__ldg(reinterpret_cast<const uint4*>(scale + col)), s);
+#pragma unroll
+          for (int j = 0; j < 8; ++j) f[j] *= s[j];
+        }
+        if (bias != nullptr) {
+          float b[8];
+          unpack8(__ldg(reinterpret_cast<const uint4*>(bias + col)), b);
+#pragma unroll
+          for (int j = 0; j < 8; ++j) f[j] += b[j];
+        }
+        st_cs_v4(yr + col, pack8(f));
+      }
+    }
+  }
+}
+
+// Backward.  Every warp walks rows (grid-stride), keeps per-lane partial sums of
+// dscale for its columns in registers when DSCALE is set, and at the end the block folds its
+// warps' partials through shared memory into one row of `partials` [gridDim.x, cols].
+template <int NCH, bool DSCALE>
+__global__ void __launch_bounds__(BWD_THREADS, BWD_BLOCKS_PER_SM)
+    rmsnorm_bwd_kernel(const __nv_bfloat16* __restrict__ x, long long ldx,
+                       const __nv_bfloat16* __restrict__ dy, long long lddy,
+                       const __nv_bfloat16* __restrict__ res, long long ldres,
+                       const __nv_bfloat16* __restrict__ scale, const float* __restrict__ r_inv,
+                       long long r_inv_stride, __nv_bfloat16* __restrict__ dx, long long lddx,
+                       float* __restrict__ partials, int rows, int cols) {
+  extern __shared__ float s_part[];  // [cols] when DSCALE
+  const int lane = threadIdx.x & 31;
+  const int warp = threadIdx.x >> 5;
+  const int warps_per_block = BWD_THREADS / 32;
+  const long long warp_global = static_cast<long long>(blockIdx.x) * warps_per_block + warp;
+  const long long warp_stride = static_cast<long long>(gridDim.x) * warps_per_block;
+  const float inv_cols = 1.0f / static_cast<float>(cols);
+
+  float acc[DSCALE ? NCH * 8 : 1];
+#pragma unroll
+  for (int i = 0; i < (DSCALE ? NCH * 8 : 1); ++i) acc[i] = 0.f;
+
+  for (long long row = warp_global; row < rows; row += warp_stride) {
+    const __nv_bfloat16* xr = x + row * ldx;
+    const __nv_bfloat16* dyr = dy + row * lddy;
+    uint4 vx[NCH], vd[NCH];
+#pragma unroll
+    for (int c = 0; c < NCH; ++c) {
+      const int col = c * 256 + lane * 8;
+      const bool in = col < cols;
+      vx[c] = in ? ld_nc_v4(xr + col) : make_uint4(0, 0, 0, 0);
+      vd[c] = in ? ld_nc_v4(dyr + col) : make_uint4(0, 0, 0, 0);
+    }
+    const float r = r_inv[row * r_inv_stride];
+    // g = dy * scale (kept in vd's place as f32 is too large: recompute in the second pass).
+    float dot = 0.f;
+#pragma unroll
+    for (int c = 0; c < NCH; ++c) {
+      const int col = c * 256 + lane * 8;
+      if (col < cols) {
+        float fx[8], fd[8], fs[8];
+        unpack8(vx[c], fx);
+        unpack8(vd[c], fd);
+        unpack8(__ldg(reinterpret_cast<const uint4*>(scale + col)), fs);
+#pragma unroll
+        for (int j = 0; j < 8; ++j) {
+          dot = fmaf(fd[j] * fs[j], fx[j], dot);
+          if (DSCALE) acc[c * 8 + j] = fmaf(fd[j] * fx[j], r, acc[c * 8 + j]);
+        }
+      }
+    }
+    dot = warp_sum(dot);
+    const float k = r * r * (dot * inv_cols);  // dx = r * (g - x * k)
+    __nv_bfloat16* dxr = dx + row * lddx;
+#pragma unroll
+    for (int c = 0; c < NCH; ++c) {
+      const int col = c * 256 + lane * 8;
+      if (col < cols) {
+        float fx[8], fd[8], fs[8], o[8];
+        unpack8(vx[c], fx);
+        unpack8(vd[c], fd);
+        unpack8(__ldg(reinterpret_cast<const uint4*>(scale + col)), fs);
+#pragma unroll
+        for (int j = 0; j < 8; ++j) o[j] = r * (fd[j] * fs[j] - fx[j] * k);
+        if (res != nullptr) {
+          float fr[8];
+          unpack8(ld_nc_v4(res + row * ldres + col), fr);
+#pragma unroll
+          for (int j = 0; j < 8; ++j) o[j] += fr[j];
+        }
+        st_cs_v4(dxr + col, pack8(o));
+      }
+    }
+  }
+
+  if (DSCALE) {
+    // Fold the block's warps one after another (fixed order: deterministic).
+    for (int w = 0; w < warps_per_block; ++w) {
+      if (warp == w) {
+#pragma unroll
+        for (int c = 0; c < NCH; ++c) {
+          const int col = c * 256 + lane * 8;
+          if (col < cols) {
+#pragma unroll
+            for (int j = 0; j < 8; ++j) {
+              if (w == 0) s_part[col + j] = acc[c * 8 + j];
+              else s_part[col + j] += acc[c * 8 + j];
+            }
+          }
+        }
+      }
+      __syncthreads();
+    }
+    float* out = partials + static_cast<long long>(blockIdx.x) * cols;
+    for (int i = threadIdx.x; i < cols; i += BWD_THREADS) out[i] = s_part[i];
+  }
+}
+
+// dscale partials for rows too wide for register accumulators: block (bx, by) sums rows
+// by, by + gridDim.y, ... for 128 columns.
+__global__ void __launch_bounds__(128)
+    dscale_cols_kernel(const __nv_bfloat16* __restrict__ x, long long ldx,
+                       const __nv_bfloat16* __restrict__ dy, long long lddy,
+                       const float* __restrict__ r_inv, long long r_inv_stride,
+                       float* __restrict__ partials, int rows, int cols) {
+  const int col = blockIdx.x * 128 + threadIdx.x;
+  if (col >= cols) return;
+  float acc = 0.f;
+  for (long long row = blockIdx.y; row < rows; row += gridDim.y)
+    acc = fmaf(__bfloat162float(dy[row * lddy + col]) * __bfloat162float(x[row * ldx + col]),
+               r_inv[row * r_inv_stride], acc);
+  partials[static_cast<long long>(blockIdx.y) * cols + col] = acc;
+}
+
+// dscale[j] += sum_b partials[b][j], summed in a fixed order.
+__global__ void __launch_bounds__(256)
+    dscale_finalize_kernel(const float* __restrict__ partials, int num_partials, int cols,
+                           float* __restrict__ dscale, long long dscale_stride) {
+  const int col = blockIdx.x * 256 + threadIdx.x;
+  if (col >= cols) return;
+  float s0 = 0.f, s1 = 0.f, s2 = 0.f, s3 = 0.f;
+  int b = 0;
+  for (; b + 4 <= num_partials; b += 4) {
+    s0 += partials[static_cast<long long>(b) * cols + col];
+    s1 += partials[static_cast<long long>(b + 1) * cols + col];
+    s2 += partials[static_cast<long long>(b + 2) * cols + col];
+    s3 += partials[static_cast<long long>(b + 3) * cols + col];
+  }
+  for (; b < num_partials; ++b) s0 += partials[static_cast<long long>(b) * cols + col];
+  dscale[col * dscale_stride] += (s0 + s1) + (s2 + s3);
+}
+
+static int32_t check_rows(const char* op, const char* name, const cdl_tensor* t, long long rows,
+                          long long cols) {
+  if (t->rank != 2 || t->shape[0] != rows || t->shape[1] != cols)
+    return fail(CDL_ERR_INVALID, "%s: %s must be a 2D tensor of shape [%lld, %lld]", op, name, rows,
+                cols);
+  if (t->dtype != CDL_BF16) return fail(CDL_ERR_UNSUPPORTED, "%s: %s must be bf16", op, name);
+  if (cols > 1 && t->stride[1] != 1)
+    return fail(CDL_ERR_UNSUPPORTED, "%s: %s must have packed rows (contiguous columns)", op, name);
+  if ((reinterpret_cast<uintptr_t>(t->ptr) & 15) != 0 || (rows > 1 && t->stride[0] % 8 != 0))
+    return fail(CDL_ERR_UNSUPPORTED, "%s: %s must be 16-byte aligned (pointer and row stride)", op,
+                name);
+  return CDL_OK;
+}
+
+static int32_t check_vec(const char* op, const char* name, const cdl_tensor* t, long long n,
+                         int32_t dtype, bool need_contig) {
+  if (t->rank != 1 || t->shape[0] != n)
+    return fail(CDL_ERR_INVALID, "%s: %s must have shape [%lld]", op, name, n);
+  if (t->dtype != dtype)
+    return fail(CDL_ERR_UNSUPPORTED, "%s: %s must be %s", op, name, dtype_name(dtype));
+  if (need_contig && (t->stride[0] != 1 || (reinterpret_cast<uintptr_t>(t->ptr) & 15) != 0))
+    return fail(CDL_ERR_UNSUPPORTED, "%s: %s must be contiguous and 16-byte aligned", op, name);
+  return CDL_OK;
+}
+
+template <int NCH>
+static void launch_fwd(const cdl_tensor* x, const cdl_tensor* scale, const cdl_tensor* bias,
+                       float eps, const cdl_tensor* y, const cdl_tensor* r_inv, int rows, int cols,
+                       cudaStream_t stream) {
+  const int warps = FWD_THREADS / 32;
+  const long long want = (static_cast<long long>(rows) + warps - 1) / warps;
+  const int grid = static_cast<int>(want < 1 ? 1 : (want > (1 << 24) ? (1 << 24) : want));
+  rmsnorm_fwd_kernel<NCH><<<grid, FWD_THREADS, 0, stream>>>(
+      static_cast<const __nv_bfloat16*>(x->ptr), x->stride[0],
+      scale ? static_cast<const __nv_bfloat16*>(scale->ptr) : nullptr,
+      bias ? static_cast<const __nv_bfloat16*>(bias->ptr) : nullptr,
+      static_cast<__nv_bfloat16*>(y->ptr), y->stride[0],
+      r_inv ? static_cast<float*>(r_inv->ptr) : nullptr, r_inv ? r_inv->stride[0] : 0, rows, cols,
+      eps);
+}
+
+template <int NCH, bool DSCALE>
+static void launch_bwd(const cdl_tensor* x, const cdl_tensor* dy, const cdl_tensor* res,
+                       const cdl_tensor* scale, const cdl_tensor* r_inv, const cdl_tensor* dx,
+                       float* partials, int grid, int rows, int cols, cudaStream_t stream) {
+  const size_t smem = DSCALE ? static_cast<size_t>(cols) * sizeof(float) : 0;
+  rmsnorm_bwd_kernel<NCH, DSCALE><<<grid, BWD_THREADS, smem, stream>>>(
+      static_cast<const __nv_bfloat16*>(x->ptr), x->stride[0],
+      static_cast<const __nv_bfloat16*>(dy->ptr), dy->stride[0],
+      res ? static_cast<const __nv_bfloat16*>(res->ptr) : nullptr, res ? res->stride[0] : 0,
+      static_cast<const __nv_bfloat16*>(scale->ptr), static_cast<const float*>(r_inv->ptr),
+      r_inv->stride[0], static_cast<__nv_bfloat16*>(dx->ptr), dx->stride[0], partials, rows, cols);
+}
+
+}  // namespace norm
+
+int32_t rmsnorm_fwd_execute(const cdl_tensor* x, const cdl_tensor* scale, const cdl_tensor* bias,
+                            float eps, const cdl_tensor* y, const cdl_tensor* r_inv,
+                            cudaStream_t stream) {
+  using namespace norm;
+  const char* op = "norm_fwd";
+  if (!x || !y) return fail(CDL_ERR_INVALID, "%s: x and y are required", op);
+  if (x->rank != 2) return fail(CDL_ERR_INVALID, "%s: x must be a 2D tensor", op);
+  const long long rows = x->shape[0], cols = x->shape[1];
+  CDL_CHECK(check_rows(op, "x", x, rows, cols));
+  CDL_CHECK(check_rows(op, "y", y, rows, cols));
+  if (scale) CDL_CHECK(check_vec(op, "scale", scale, cols, CDL_BF16, true));
+  if (bias) CDL_CHECK(check_vec(op, "bias", bias, cols, CDL_BF16, true));
+  if (r_inv) CDL_CHECK(check_vec(op, "r_inv", r_inv, rows, CDL_F32, false));
+  if (rows == 0 || cols == 0) return CDL_OK;
+  if (cols % 8 != 0 || cols > 8192)
+    return fail(CDL_ERR_UNSUPPORTED,
+                "%s: cols must be a multiple of 8 and at most 8192 (got %lld)", op, cols);
+  if (rows > INT32_MAX) return fail(CDL_ERR_UNSUPPORTED, "%s: too many rows", op);
+  const int r = static_cast<int>(rows), c = static_cast<int>(cols);
+  if (c <= 256) launch_fwd<1>(x, scale, bias, eps, y, r_inv, r, c, stream);
+  else if (c <= 512) launch_fwd<2>(x, scale, bias, eps, y, r_inv, r, c, stream);
+  else if (c <= 1024) launch_fwd<4>(x, scale, bias, eps, y, r_inv, r, c, stream);
+  else if (c <= 2048) launch_fwd<8>(x, scale, bias, eps, y, r_inv, r, c, stream);
+  else if (c <= 4096) launch_fwd<16>(x, scale, bias, eps, y, r_inv, r, c, stream);
+  else launch_fwd<32>(x, scale, bias, eps, y, r_inv, r, c, stream);
+  CDL_CUDA(cudaGetLastError());
+  return CDL_OK;
+}
+
+size_t rmsnorm_bwd_scratch_bytes(long long rows, long long cols) {
+  (void)rows;
+  return static_cast<size_t>(norm::MAX_PARTIALS) * static_cast<size_t>(cols) * sizeof(float);
+}
+
+int32_t rmsnorm_bwd_execute(const cdl_tensor* x, const cdl_tensor* dy, const cdl_tensor* res,
+                            const cdl_tensor* scale, const cdl_tensor* r_inv, const cdl_tensor* dx,
+                            const cdl_tensor* dscale, void* scratch, size_t scratch_bytes,
+                            cudaStream_t stream) {
+  using namespace norm;
+  const char* op = "norm_bwd";
+  if (!x || !dy || !scale || !r_inv || !dx || !dscale)
+    return fail(CDL_ERR_INVALID, "%s: x, dy, scale, r_inv, dx and dscale are required", op);
+  if (x->rank != 2) return fail(CDL_ERR_INVALID, "%s: x must be a 2D tensor", op);
+  const long long rows = x->shape[0], cols = x->shape[1];
+  CDL_CHECK(check_rows(op, "x", x, rows, cols));
+  CDL_CHECK(check_rows(op, "dy", dy, rows, cols));
+  CDL_CHECK(check_rows(op, "dx", dx, rows, cols));
+  if (res) CDL_CHECK(check_rows(op, "residual_dy", res, rows, cols));
+  CDL_CHECK(check_vec(op, "scale", scale, cols, CDL_BF16, true));
+  CDL_CHECK(check_vec(op, "r_inv", r_inv, rows, CDL_F32, false));
+  CDL_CHECK(check_vec(op, "dscale", dscale, cols, CDL_F32, false));
+  if (cols == 0) return CDL_OK;
+  if (cols % 8 != 0 || cols > 8192)
+    return fail(CDL_ERR_UNSUPPORTED,
+                "%s: cols must be a multiple of 8 and at most 8192 (got %lld)", op, cols);
+  if (rows == 0) return CDL_OK;
+  if (rows > INT32_MAX) return fail(CDL_ERR_UNSUPPORTED, "%s: too many rows", op);
+  if (scratch == nullptr || scratch_bytes < rmsnorm_bwd_scratch_bytes(rows, cols) ||
+      (reinterpret_cast<uintptr_t>(scratch) & 15) != 0)
+    return fail(CDL_ERR_INVALID, "%s: scratch must be 16-byte aligned and hold %zu bytes (got %zu)",
+                op, rmsnorm_bwd_scratch_bytes(rows, cols), scratch_bytes);
+  const int r = static_cast<int>(rows), c = static_cast<int>(cols);
+  float* partials = static_cast<float*>(scratch);
+  const int warps = BWD_THREADS / 32;
+  int grid = sm_count() * BWD_BLOCKS_PER_SM;
+  if (grid > MAX_PARTIALS) grid = MAX_PARTIALS;
+  const int need = (r + warps - 1) / warps;
+  if (grid > need) grid = need;
+  int num_partials = grid;
+  if (c <= 256) launch_bwd<1, true>(x, dy, res, scale, r_inv, dx, partials, grid, r, c, stream);
+  else if (c <= 512) launch_bwd<2, true>(x, dy, res, scale, r_inv, dx, partials, grid, r, c, stream);
+  else if (c <= 1024) launch_bwd<4, true>(x, dy, res, scale, r_inv, dx, partials, grid, r, c, stream);
+  else if (c <= 2048) launch_bwd<8, true>(x, dy, res, scale, r_inv, dx, partials, grid, r, c, stream);
+  else {
+    if (c <= 4096) launch_bwd<16, false>(x, dy, res, scale, r_inv, dx, nullptr, grid, r, c, stream);
+    else launch_bwd<32, false>(x, dy, res, scale, r_inv, dx, nullptr, grid, r, c, stream);
+    num_partials = r < 256 ? r : 256;
+    dim3 g((c + 127) / 128, num_partials);
+    dscale_cols_kernel<<<g, 128, 0, stream>>>(
+        static_cast<const __nv_bfloat16*>(x->ptr), x->stride[0],
+        static_cast<const __nv_bfloat16*>(dy->ptr), dy->stride[0],
+        static_cast<const float*>(r_inv->ptr), r_inv->stride[0], partials, r, c);
+  }
+  CDL_CUDA(cudaGetLastError());
+  dscale_finalize_kernel<<<(c + 255) / 256, 256, 0, stream>>>(
+      partials, num_partials, c, static_cast<float*>(dscale->ptr), dscale->stride[0]);
+  CDL_CUDA(cudaGetLastError());
+  return CDL_OK;
+}
+
+}  // namespace cdl
+
+extern "C" {
+
+int32_t cdl_b200_rmsnorm_fwd(const cdl_tensor* x, const cdl_tensor* scale, const cdl_tensor* bias,
+                             float eps, const cdl_tensor* y, const cdl_tensor* r_inv,
+                             cdl_stream stream) {
+  return cdl::rmsnorm_fwd_execute(x, scale, bias, eps, y, r_inv,
+                                  static_cast<cudaStream_t>(stream));
+}
+
+int32_t cdl_b200_rmsnorm_bwd(const cdl_tensor* x, const cdl_tensor* dy,
+                             const cdl_tensor* residual_dy, const cdl_tensor* scale,
+                             const cdl_tensor* r_inv, const cdl_tensor* dx,
+                             const cdl_tensor* dscale, void* scratch, size_t scratch_bytes,
+                             cdl_stream stream) {
+  return cdl::rmsnorm_bwd_execute(x, dy, residual_dy, scale, r_inv, dx, dscale, scratch,
+                                  scratch_bytes, static_cast<cudaStream_t>(stream));
+}
+
+int32_t cdl_b200_rmsnorm_bwd_scratch_bytes(int64_t rows, int64_t cols, size_t* bytes_out) {
+  if (rows < 0 || cols < 0) return cdl::fail(CDL_ERR_INVALID, "norm_bwd: negative shape");
+  if (bytes_out) *bytes_out = cdl::rmsnorm_bwd_scratch_bytes(rows, cols);
+  return CDL_OK;
+}
+
+}  // extern "C"

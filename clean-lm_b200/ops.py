@@ -1,0 +1,176 @@
+"""Operator front ends mirroring the reference's graph nodes, executing eagerly on torch tensors.
+
+Names, options and error behaviour follow the reference's DSL entry points:
+  `SymTensor::matmul`         crates/cleandl/src/execgraph/ops/matmul.rs:90-108   -> matmul
+  `SymTensor::norm_fwd`       crates/cleandl/src/execgraph/ops/norm/mod.rs:126-160 -> norm_fwd
+  `SymTensor::attention_fwd`  crates/cleandl/src/execgraph/ops/attention/mod.rs:276-350
+  `SymTensor::attention_bwd`  (same file)                                          -> attention_*
+`norm_bwd` follows the legacy call site crates/sky-1/src/training/model/decoder.rs:599-607.
+
+This layer plays the engine's part (plan.rs:397-451): it allocates outputs and scratch with torch,
+then calls the C ABI on the current CUDA stream.  All arithmetic happens in the CUDA library.
+"""
+from __future__ import annotations
+
+import ctypes
+from dataclasses import dataclass
+from typing import Optional
+
+import torch
+
+from . import _lib
+from ._lib import CdlAttnDesc, check, lib, ref, tensor_arg
+
+
+def _stream() -> ctypes.c_void_p:
+    return ctypes.c_void_p(torch.cuda.current_stream().cuda_stream)
+
+
+def _require_cuda(*tensors):
+    for t in tensors:
+        if t is not None and not t.is_cuda:
+            raise _lib.CdlError(-1, "operands must live in device memory (there is no CPU path)")
+
+
+# --------------------------------------------------------------------------- matmul
+@dataclass
+class MatmulOpts:
+    """`MatmulOpts` of the reference (ops/matmul.rs:71-88)."""
+
+    out: torch.dtype = torch.bfloat16
+    c: Optional[torch.Tensor] = None  # needs a nonzero beta to have an effect
+    alpha: float = 1.0
+    beta: float = 0.0
+
+
+def matmul(a: torch.Tensor, b: torch.Tensor, opts: MatmulOpts | None = None,
+           out: torch.Tensor | None = None) -> torch.Tensor:
+    """D = alpha * A . B + beta * C.  `a`/`b` may be transposed views (`.mT`); `out` may be
+    given to write in place (e.g. out = c for accumulating wgrads)."""
+    opts = opts or MatmulOpts()
+    _require_cuda(a, b, opts.c, out)
+    if a.dim() != b.dim() or a.dim() not in (2, 3):
+        raise _lib.CdlError(-1, f"matmul operands must both have rank 2 or rank 3 "
+                                f"(got rank {a.dim()} and {b.dim()})")
+    if a.shape[-1] != b.shape[-2]:
+        raise _lib.CdlError(-1, f"matmul contraction dimensions differ: {tuple(a.shape)} x "
+                                f"{tuple(b.shape)}")
+    if out is None:
+        out = torch.empty(*a.shape[:-1], b.shape[-1], dtype=opts.out, device=a.device)
+    ta, tb, tc, td = tensor_arg(a), tensor_arg(b), tensor_arg(opts.c), tensor_arg(out)
+    check(lib.cdl_b200_matmul(ref(ta), ref(tb), ref(tc), ref(td), opts.alpha, opts.beta, None, 0,
+                              _stream()))
+    return out
+
+
+# --------------------------------------------------------------------------- norm
+@dataclass
+class NormFwdOpts:
+    """`NormFwdOpts` of the reference (ops/norm/mod.rs:87-111); RMSNorm with bf16 output only."""
+
+    scale: Optional[torch.Tensor] = None
+    bias: Optional[torch.Tensor] = None
+    eps: float = 1e-6
+    save_stats: bool = False
+
+
+@dataclass
+class NormFwdOutputs:
+    y: torch.Tensor
+    r_inv: Optional[torch.Tensor]  # per-row reciprocal RMS (f32), with save_stats
+
+
+def norm_fwd(x: torch.Tensor, opts: NormFwdOpts | None = None) -> NormFwdOutputs:
+    opts = opts or NormFwdOpts()
+    _require_cuda(x, opts.scale, opts.bias)
+    if x.dim() != 2:
+        raise _lib.CdlError(-1, "norm_fwd: x must be a 2D tensor")
+    y = torch.empty(x.shape, dtype=torch.bfloat16, device=x.device)
+    r_inv = torch.empty(x.shape[0], dtype=torch.float32, device=x.device) if opts.save_stats else None
+    tx, ts, tb, ty, tr = (tensor_arg(t) for t in (x, opts.scale, opts.bias, y, r_inv))
+    check(lib.cdl_b200_rmsnorm_fwd(ref(tx), ref(ts), ref(tb), opts.eps, ref(ty), ref(tr), _stream()))
+    return NormFwdOutputs(y, r_inv)
+
+
+def norm_bwd_scratch_bytes(rows: int, cols: int) -> int:
+    n = ctypes.c_size_t(0)
+    check(lib.cdl_b200_rmsnorm_bwd_scratch_bytes(rows, cols, ctypes.byref(n)))
+    return n.value
+
+
+def norm_bwd(x, dy, scale, r_inv, dscale, residual_dy=None, scratch=None) -> torch.Tensor:
+    """dx of RMSNorm; `dscale` (f32 [cols]) is accumulated in place."""
+    _require_cuda(x, dy, scale, r_inv, dscale, residual_dy)
+    if x.dim() != 2:
+        raise _lib.CdlError(-1, "norm_bwd: x must be a 2D tensor")
+    dx = torch.empty(x.shape, dtype=torch.bfloat16, device=x.device)
+    need = norm_bwd_scratch_bytes(x.shape[0], x.shape[1])
+    if scratch is None:
+        scratch = torch.empty(max(need, 16), dtype=torch.uint8, device=x.device)
+    args = [tensor_arg(t) for t in (x, dy, residual_dy, scale, r_inv, dx, dscale)]
+    check(lib.cdl_b200_rmsnorm_bwd(*(ref(a) for a in args), ctypes.c_void_p(scratch.data_ptr()),
+                                   scratch.numel() * scratch.element_size(), _stream()))
+    return dx
+
+
+# --------------------------------------------------------------------------- attention
+@dataclass
+class AttentionOpts:
+    """The subset of `AttentionOpts` (ops/attention/mod.rs:94-112) this library implements:
+    dense layouts, mask None or Causal, no softcap."""
+
+    softmax_scale: Optional[float] = None  # None is 1 / sqrt(head_dim)
+    causal: bool = True
+
+
+@dataclass
+class AttentionFwdOutputs:
+    out: torch.Tensor
+    lse: Optional[torch.Tensor]  # f32 [batch, heads, seqlen_q], natural log
+
+
+def _attn_desc(opts: AttentionOpts) -> CdlAttnDesc:
+    d = CdlAttnDesc()
+    d.softmax_scale = float(opts.softmax_scale) if opts.softmax_scale is not None else 0.0
+    d.causal = 1 if opts.causal else 0
+    return d
+
+
+def attention_fwd(q, k, v, opts: AttentionOpts | None = None, lse: bool = True) -> AttentionFwdOutputs:
+    opts = opts or AttentionOpts()
+    _require_cuda(q, k, v)
+    if q.dim() != 4:
+        raise _lib.CdlError(-1, "attention: q must be [batch, seqlen, heads, head_dim]")
+    out = torch.empty(q.shape, dtype=q.dtype, device=q.device)
+    lse_t = (torch.empty(q.shape[0], q.shape[2], q.shape[1], dtype=torch.float32, device=q.device)
+             if lse else None)
+    desc = _attn_desc(opts)
+    args = [tensor_arg(t) for t in (q, k, v, out, lse_t)]
+    check(lib.cdl_b200_attn_fwd(ctypes.byref(desc), *(ref(a) for a in args), _stream()))
+    return AttentionFwdOutputs(out, lse_t)
+
+
+def attention_bwd_scratch_bytes(q, k) -> int:
+    n = ctypes.c_size_t(0)
+    tq, tk = tensor_arg(q), tensor_arg(k)
+    check(lib.cdl_b200_attn_bwd_scratch_bytes(ref(tq), ref(tk), ctypes.byref(n)))
+    return n.value
+
+
+def attention_bwd(q, k, v, out, d_out, lse, opts: AttentionOpts | None = None, scratch=None,
+                  dq=None, dk=None, dv=None):
+    """Returns (dq, dk, dv) in the input dtype (ops/attention/mod.rs:915-919)."""
+    opts = opts or AttentionOpts()
+    _require_cuda(q, k, v, out, d_out, lse)
+    dq = torch.empty(q.shape, dtype=q.dtype, device=q.device) if dq is None else dq
+    dk = torch.empty(k.shape, dtype=k.dtype, device=k.device) if dk is None else dk
+    dv = torch.empty(v.shape, dtype=v.dtype, device=v.device) if dv is None else dv
+    need = attention_bwd_scratch_bytes(q, k)
+    if scratch is None:
+        scratch = torch.empty(max(need, 16), dtype=torch.uint8, device=q.device)
+    desc = _attn_desc(opts)
+    args = [tensor_arg(t) for t in (q, k, v, out, d_out, lse, dq, dk, dv)]
+    check(lib.cdl_b200_attn_bwd(ctypes.byref(desc), *(ref(a) for a in args),
+                                ctypes.c_void_p(scratch.data_ptr()),
+                                scratch.numel() * scratch.element_size(), _stream()))
+    return dq, dk, dv

@@ -1,0 +1,130 @@
+/* cleandl_b200 — C ABI of the B200 (sm_100a) kernels behind clean-lm's exec-graph operators.
+ *
+ * Each entry point is what an `Executor::execute` of crates/cleandl would call for that
+ * operator (crates/cleandl/src/execgraph/op.rs:130-142).  The conventions follow that trait:
+ *   - nothing here allocates or frees device memory, and nothing synchronises the device or the
+ *     stream (the two `*_status` helpers are the only exception and say so);
+ *   - all work is enqueued on the caller's stream;
+ *   - outputs and scratch have undefined contents on entry and are fully written;
+ *   - every function returns 0 on success and a negative cdl_status otherwise, with a message
+ *     available from cdl_b200_last_error() (thread-local); none throws or aborts;
+ *   - empty shapes are a silent success (ops/matmul.rs:1095-1097, ops/norm/specialized.rs:133-135);
+ *   - the library is re-entrant: execute may be called from any thread for any stream.
+ * Only sm_100 devices are accepted; there is no CPU path and no other GPU architecture.
+ */
+#ifndef CLEANDL_B200_H
+#define CLEANDL_B200_H
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+typedef enum {
+  CDL_OK = 0,
+  CDL_ERR_INVALID = -1,     /* operand validation failed (shape, type, layout, alignment) */
+  CDL_ERR_UNSUPPORTED = -2, /* valid for the reference operator, not implemented here */
+  CDL_ERR_CUDA = -3,        /* a CUDA runtime / driver call failed */
+  CDL_ERR_DEVICE = -4       /* a kernel recorded an error (bounded wait ran out) */
+} cdl_status;
+
+typedef enum { CDL_BF16 = 0, CDL_F32 = 1, CDL_I32 = 2 } cdl_dtype;
+
+/* A strided view of device memory.  Strides are in ELEMENTS, like TensorView's layout
+ * (crates/cleandl/src/tensor.rs:20-856).  rank <= 4. */
+typedef struct {
+  void* ptr;
+  int32_t dtype; /* cdl_dtype */
+  int32_t rank;
+  int64_t shape[4];
+  int64_t stride[4];
+} cdl_tensor;
+
+/* CUDA stream handle (cudaStream_t / CUstream) passed as an opaque pointer. */
+typedef void* cdl_stream;
+
+/* ---- library state ------------------------------------------------------------------- */
+
+/* Message of the last failing call on this thread ("" if none). */
+const char* cdl_b200_last_error(void);
+
+/* 0 if `device` has compute capability 10.x, CDL_ERR_UNSUPPORTED otherwise.  Mirrors the exact
+ * architecture gate of kernel-build-util (crates/kernel-build-util/src/lib.rs:96-107). */
+int32_t cdl_b200_device_ok(int32_t device);
+
+/* Reads and clears the current device's kernel status word: 0 = no kernel gave up on a wait.
+ * SYNCHRONISES the device.  Test / debugging aid, not part of the hot path. */
+int32_t cdl_b200_device_status(int32_t* status_out);
+
+/* ---- Matmul: D = alpha * A . B + beta * C ----------------------------------------------
+ * Replaces MatmulExecutor::execute (crates/cleandl/src/execgraph/ops/matmul.rs:1092-1183),
+ * which forwards to cuBLASLt.  A is [M,K] or [batch,M,K]; B is [K,N] or [batch,K,N]; C
+ * (nullable; needs beta != 0 to matter) and D are [M,N] / [batch,M,N].  A and B are bf16
+ * views with one contiguous dimension (a transposed view is free, matmul.rs:128-157); D and C
+ * are bf16 or f32; accumulation is f32.  forward = (A row-major, B row-major), dgrad =
+ * (A row-major, B transposed view), wgrad = (A transposed view, B row-major, D = C f32, beta 1).
+ * Unlike cuBLASLt, A's and B's base address and non-unit strides must be 16-byte aligned (TMA);
+ * other layouts return CDL_ERR_UNSUPPORTED.  K == 0 is an error ("K is zero", matmul.rs tests
+ * :825-843).  D may alias C. */
+int32_t cdl_b200_matmul(const cdl_tensor* a, const cdl_tensor* b, const cdl_tensor* c,
+                        const cdl_tensor* d, float alpha, float beta, void* scratch,
+                        size_t scratch_bytes, cdl_stream stream);
+/* Scratch the call above needs for these operands (Executor::scratch_bytes, op.rs:132-135). */
+int32_t cdl_b200_matmul_scratch_bytes(const cdl_tensor* a, const cdl_tensor* b,
+                                      const cdl_tensor* d, size_t* bytes_out);
+
+/* ---- RMSNorm forward -------------------------------------------------------------------
+ * Replaces SpecializedExecutor::execute (crates/cleandl/src/execgraph/ops/norm/specialized.rs:
+ * 116-200) and the kernel it launches (crates/cleandl-specialized-kernels/src/kernels/norm/
+ * forward.rs:509-785):  r_i = rsqrt(mean_j x_ij^2 + eps);  y_ij = bf16(x_ij * r_i * scale_j + bias_j).
+ * x, y: bf16 [rows, cols], packed rows; scale, bias: bf16 [cols], nullable; r_inv: f32 [rows],
+ * nullable (the op's save_stats).  cols % 8 == 0. */
+int32_t cdl_b200_rmsnorm_fwd(const cdl_tensor* x, const cdl_tensor* scale, const cdl_tensor* bias,
+                             float eps, const cdl_tensor* y, const cdl_tensor* r_inv,
+                             cdl_stream stream);
+
+/* ---- RMSNorm backward ------------------------------------------------------------------
+ * The reference tree holds only the call sites (crates/sky-1/src/training/model/decoder.rs:
+ * 599-607, 684-692): dx = rmsnorm_backward(x, dy, residual_dy, scale, r_inv; dscale +=).
+ *   g_ij = dy_ij * scale_j;  c_i = mean_j(g_ij * x_ij);
+ *   dx_ij = r_i * g_ij - r_i^3 * x_ij * c_i (+ residual_dy_ij);   dscale_j += sum_i dy_ij x_ij r_i.
+ * x, dy, residual_dy (nullable), dx: bf16 [rows, cols]; scale bf16 [cols]; r_inv f32 [rows];
+ * dscale f32 [cols], ACCUMULATED in place.  Scratch: see *_scratch_bytes. */
+int32_t cdl_b200_rmsnorm_bwd(const cdl_tensor* x, const cdl_tensor* dy,
+                             const cdl_tensor* residual_dy, const cdl_tensor* scale,
+                             const cdl_tensor* r_inv, const cdl_tensor* dx,
+                             const cdl_tensor* dscale, void* scratch, size_t scratch_bytes,
+                             cdl_stream stream);
+int32_t cdl_b200_rmsnorm_bwd_scratch_bytes(int64_t rows, int64_t cols, size_t* bytes_out);
+
+/* ---- Flash attention -------------------------------------------------------------------
+ * Replaces AttentionExecutor::execute (crates/cleandl/src/execgraph/ops/attention/exec.rs:
+ * 358-416), which forwards to flash-attention-rs.  Dense layout only: q [B,Sq,H,D], k and v
+ * [B,Sk,Hkv,D] bf16, last dimension contiguous, other strides 16-byte aligned (views into a
+ * fused QKV buffer are fine); o like q; lse f32 [B,H,Sq] (natural log; -inf for rows with no
+ * visible key).  The causal mask is aligned to the bottom right: query i sees keys
+ * j <= i + Sk - Sq (attention/mod.rs:24-31).  D = 128, H % Hkv == 0. */
+typedef struct {
+  float softmax_scale; /* <= 0 selects 1/sqrt(D) (exec.rs:198-200) */
+  int32_t causal;      /* 0 = AttentionMask::None, 1 = AttentionMask::Causal */
+} cdl_attn_desc;
+
+int32_t cdl_b200_attn_fwd(const cdl_attn_desc* desc, const cdl_tensor* q, const cdl_tensor* k,
+                          const cdl_tensor* v, const cdl_tensor* o, const cdl_tensor* lse,
+                          cdl_stream stream);
+/* Operand order of the reference backward: q, k, v, out, d_out, lse (attention/mod.rs:899-905);
+ * outputs dq, dk, dv in the input dtype (:915-919). */
+int32_t cdl_b200_attn_bwd(const cdl_attn_desc* desc, const cdl_tensor* q, const cdl_tensor* k,
+                          const cdl_tensor* v, const cdl_tensor* o, const cdl_tensor* d_out,
+                          const cdl_tensor* lse, const cdl_tensor* dq, const cdl_tensor* dk,
+                          const cdl_tensor* dv, void* scratch, size_t scratch_bytes,
+                          cdl_stream stream);
+int32_t cdl_b200_attn_bwd_scratch_bytes(const cdl_tensor* q, const cdl_tensor* k,
+                                        size_t* bytes_out);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* CLEANDL_B200_H */

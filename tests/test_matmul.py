@@ -1,0 +1,160 @@
+"""GPU parity of the tcgen05 GEMM against the f64 oracle, through the C ABI.
+
+Cases follow crates/cleandl/tests/matmul.rs: shapes and output types (:212-240), transposed views
+(:268-310), sliced views (:313-339), batched (:666-687), batched + transposed + C with alpha/beta
+(:632-663), accumulate into C (:690-725), K = 0 (:825-843), rejection messages (:355-468), with the
+tolerance of :199-202.  BASELINE's acceptance bound (max relative error 2e-2 against an
+f32-accumulated reference) is checked as well.
+"""
+import numpy as np
+import pytest
+import torch
+
+from helpers import assert_all_close, to_f32
+from oracle import cpu_oracle as oracle
+
+pytestmark = pytest.mark.gpu
+
+
+def rand_bf16(gen, *shape):
+    # Uniform(-1, 1) rounded to bf16, like random_bf16 of the reference tests (:120-148).
+    return (torch.rand(*shape, generator=gen) * 2 - 1).to(torch.bfloat16)
+
+
+def run_case(cdl, a, b, out_dtype, c=None, alpha=1.0, beta=0.0, in_place=False):
+    """a, b, c: CPU tensors (possibly views). Runs on the GPU and compares with the oracle."""
+    dev = "cuda"
+
+    def to_dev(t):
+        # Preserve the view's strides: move the base storage and re-view.
+        base = torch.empty(0, dtype=t.dtype).set_(t.untyped_storage())
+        return base.to(dev).as_strided(t.shape, t.stride(), t.storage_offset())
+
+    da, db = to_dev(a), to_dev(b)
+    dc = to_dev(c) if c is not None else None
+    opts = cdl.ops.MatmulOpts(out=out_dtype, c=dc, alpha=alpha, beta=beta)
+    d = cdl.ops.matmul(da, db, opts, out=dc if in_place else None)
+    expected, bound = oracle.matmul(to_f32(a), to_f32(b), None if c is None else to_f32(c), alpha, beta)
+    tol = oracle.matmul_tolerance(expected, bound, out_dtype == torch.bfloat16)
+    assert_all_close("matmul", to_f32(d), expected, tol)
+    # BASELINE bound: max relative error 2e-2 (relative to the largest magnitude of the output).
+    scale = max(float(np.abs(expected).max()), 1e-6)
+    assert float(np.abs(to_f32(d) - expected).max()) / scale <= 2e-2
+    return d
+
+
+@pytest.mark.parametrize("shape", [(64, 64, 64), (129, 264, 72), (1, 8, 8), (300, 520, 136),
+                                   (512, 512, 512), (256, 1024, 4096 + 8)])
+@pytest.mark.parametrize("out_dtype", [torch.bfloat16, torch.float32])
+def test_shapes_and_outputs(cdl, gpu_ok, shape, out_dtype):
+    m, k, n = shape
+    gen = torch.Generator().manual_seed(0)
+    run_case(cdl, rand_bf16(gen, m, k), rand_bf16(gen, k, n), out_dtype)
+
+
+@pytest.mark.parametrize("ta,tb", [(True, False), (False, True), (True, True)])
+def test_transposed_views(cdl, gpu_ok, ta, tb):
+    m, k, n = 136, 200, 264
+    gen = torch.Generator().manual_seed(1)
+    a = rand_bf16(gen, k, m).T if ta else rand_bf16(gen, m, k)
+    b = rand_bf16(gen, n, k).T if tb else rand_bf16(gen, k, n)
+    run_case(cdl, a, b, torch.bfloat16)
+
+
+def test_sliced_views(cdl, gpu_ok):
+    gen = torch.Generator().manual_seed(2)
+    a = rand_bf16(gen, 200, 320)[8:136, 64:64 + 128]
+    b = rand_bf16(gen, 256, 400)[16:16 + 128, 8:8 + 200]
+    run_case(cdl, a, b, torch.float32)
+
+
+def test_batched(cdl, gpu_ok):
+    gen = torch.Generator().manual_seed(3)
+    run_case(cdl, rand_bf16(gen, 3, 130, 72), rand_bf16(gen, 3, 72, 264), torch.bfloat16)
+
+
+def test_batched_transposed_with_c(cdl, gpu_ok):
+    gen = torch.Generator().manual_seed(4)
+    a = rand_bf16(gen, 2, 72, 136).transpose(1, 2)
+    b = rand_bf16(gen, 2, 200, 72).transpose(1, 2)
+    c = rand_bf16(gen, 2, 136, 200)
+    run_case(cdl, a, b, torch.bfloat16, c=c, alpha=2.0, beta=0.5)
+
+
+@pytest.mark.parametrize("c_dtype", [torch.bfloat16, torch.float32])
+def test_accumulate_c(cdl, gpu_ok, c_dtype):
+    gen = torch.Generator().manual_seed(5)
+    a, b = rand_bf16(gen, 150, 264), rand_bf16(gen, 264, 96)
+    c = rand_bf16(gen, 150, 96).to(c_dtype)
+    run_case(cdl, a, b, c_dtype, c=c, alpha=0.5, beta=-2.0)
+
+
+def test_wgrad_shape_in_place_f32(cdl, gpu_ok):
+    """dW[K_in, N_out] (f32) += X^T . dY with the reduction over tokens, written into C."""
+    gen = torch.Generator().manual_seed(6)
+    x, dy = rand_bf16(gen, 1000, 256), rand_bf16(gen, 1000, 520)
+    w = torch.randn(256, 520, generator=gen)
+    run_case(cdl, x.T, dy, torch.float32, c=w, alpha=1.0, beta=1.0, in_place=True)
+
+
+def test_unaligned_output_rows(cdl, gpu_ok):
+    """N not a multiple of 8: output rows are not 16-byte aligned, scalar stores take over."""
+    gen = torch.Generator().manual_seed(7)
+    a = rand_bf16(gen, 70, 64)
+    b = rand_bf16(gen, 64, 72)[:, :65]
+    run_case(cdl, a, b, torch.bfloat16)
+    run_case(cdl, a, b, torch.float32)
+
+
+def test_deterministic(cdl, gpu_ok):
+    gen = torch.Generator().manual_seed(8)
+    a, b = rand_bf16(gen, 1024, 2048).cuda(), rand_bf16(gen, 2048, 1536).cuda()
+    d1 = cdl.ops.matmul(a, b)
+    d2 = cdl.ops.matmul(a, b)
+    assert torch.equal(d1, d2)
+
+
+def test_large_vs_f32_accumulated(cdl, gpu_ok):
+    """A block-sized forward GEMM against a float32-accumulated torch product on the same GPU
+    (the f64 oracle would take minutes at this size)."""
+    gen = torch.Generator().manual_seed(9)
+    a = (torch.randn(4096, 2048, generator=gen)).to(torch.bfloat16).cuda()
+    b = (torch.randn(2048, 5632, generator=gen) * 0.02).to(torch.bfloat16).cuda()
+    d = cdl.ops.matmul(a, b).float()
+    ref = a.float() @ b.float()
+    rel = (d - ref).abs().max() / ref.abs().max()
+    assert rel.item() <= 2e-2
+    # dgrad (B transposed view) and wgrad (A transposed view) of the same layer
+    dy = torch.randn(4096, 5632, generator=gen).to(torch.bfloat16).cuda()
+    dx = cdl.ops.matmul(dy, b.T).float()
+    ref = dy.float() @ b.float().T
+    assert ((dx - ref).abs().max() / ref.abs().max()).item() <= 2e-2
+    dw = cdl.ops.matmul(a.T, dy, cdl.ops.MatmulOpts(out=torch.float32))
+    ref = a.float().T @ dy.float()
+    assert ((dw - ref).abs().max() / ref.abs().max()).item() <= 2e-2
+
+
+def test_empty_and_errors(cdl, gpu_ok):
+    dev = "cuda"
+    a = torch.zeros(0, 64, dtype=torch.bfloat16, device=dev)
+    b = torch.zeros(64, 32, dtype=torch.bfloat16, device=dev)
+    assert cdl.ops.matmul(a, b).shape == (0, 32)  # empty output: silent success
+    with pytest.raises(cdl._lib.CdlError, match="K is zero"):
+        cdl.ops.matmul(torch.zeros(8, 0, dtype=torch.bfloat16, device=dev),
+                       torch.zeros(0, 8, dtype=torch.bfloat16, device=dev))
+    with pytest.raises(cdl._lib.CdlError, match="contraction"):
+        cdl.ops.matmul(torch.zeros(8, 16, dtype=torch.bfloat16, device=dev),
+                       torch.zeros(24, 8, dtype=torch.bfloat16, device=dev))
+    with pytest.raises(cdl._lib.CdlError, match="rank"):
+        cdl.ops.matmul(torch.zeros(8, 16, dtype=torch.bfloat16, device=dev),
+                       torch.zeros(2, 16, 8, dtype=torch.bfloat16, device=dev))
+    with pytest.raises(cdl._lib.CdlError, match="f32 or bf16"):
+        cdl.ops.matmul(torch.zeros(8, 16, dtype=torch.bfloat16, device=dev),
+                       torch.zeros(16, 8, dtype=torch.float32, device=dev))
+    with pytest.raises(cdl._lib.CdlError, match="contiguous"):
+        cdl.ops.matmul(torch.zeros(16, 32, dtype=torch.bfloat16, device=dev)[::2, ::2],
+                       torch.zeros(16, 8, dtype=torch.bfloat16, device=dev))
+    # A leading dimension TMA cannot describe (65 elements): rejected, not mis-computed.
+    with pytest.raises(cdl._lib.CdlError, match="16-byte"):
+        cdl.ops.matmul(torch.zeros(37, 65, dtype=torch.bfloat16, device=dev)[:, :64],
+                       torch.zeros(64, 8, dtype=torch.bfloat16, device=dev))

@@ -1,0 +1,124 @@
+"""GPU parity of RMSNorm forward / backward against the f64 oracle, through the C ABI.
+
+Forward cases and tolerances follow crates/cleandl/tests/norm.rs: inputs x ~ N(0.5, 2.0),
+scale ~ U(0.5, 1.5), bias ~ N(0, 1) (:220-228); specialized cases (:322-380); bf16 output within
+1e-5 + 2^-7 |e| (:261-268), r_inv within 1e-6 + 1e-4 |e| (:309-315); strided rows (:586-621).
+The backward has no reference test; it is held to BASELINE's 1e-2 bound and to the bf16 rounding
+bound of the forward.
+"""
+import numpy as np
+import pytest
+import torch
+
+from helpers import assert_all_close, to_f32
+from oracle import cpu_oracle as oracle
+
+pytestmark = pytest.mark.gpu
+
+CASES = [(1, 128), (37, 4096), (300, 2048), (128, 8192), (100, 7168), (5, 1024), (96, 512),
+         (333, 1536), (64, 136)]
+
+
+def make_inputs(rows, cols, seed):
+    gen = torch.Generator().manual_seed(seed)
+    x = (torch.randn(rows, cols, generator=gen) * 2.0 + 0.5).to(torch.bfloat16)
+    scale = (torch.rand(cols, generator=gen) + 0.5).to(torch.bfloat16)
+    bias = torch.randn(cols, generator=gen).to(torch.bfloat16)
+    return x, scale, bias
+
+
+@pytest.mark.parametrize("rows,cols", CASES)
+@pytest.mark.parametrize("affine", ["none", "scale", "scale_bias"])
+def test_fwd_cases(cdl, gpu_ok, rows, cols, affine):
+    x, scale, bias = make_inputs(rows, cols, 1)
+    s = scale if affine != "none" else None
+    b = bias if affine == "scale_bias" else None
+    eps = 1e-2 if (rows, cols) == (333, 1536) else 1e-6
+    out = cdl.ops.norm_fwd(x.cuda(), cdl.ops.NormFwdOpts(
+        scale=None if s is None else s.cuda(), bias=None if b is None else b.cuda(), eps=eps,
+        save_stats=True))
+    y_ref, r_ref = oracle.rmsnorm_fwd(to_f32(x), None if s is None else to_f32(s),
+                                      None if b is None else to_f32(b), eps)
+    assert_all_close("y", to_f32(out.y), y_ref, oracle.abs_rel_tolerance(y_ref, 1e-5, 2.0 ** -7))
+    assert_all_close("r_inv", to_f32(out.r_inv), r_ref, oracle.abs_rel_tolerance(r_ref, 1e-6, 1e-4))
+
+
+def test_fwd_strided_rows_no_stats(cdl, gpu_ok):
+    x, scale, _ = make_inputs(64, 1024, 2)
+    big = torch.zeros(64, 2048, dtype=torch.bfloat16)
+    big[:, 512:1536] = x
+    xd = big.cuda()[:, 512:1536]
+    out = cdl.ops.norm_fwd(xd, cdl.ops.NormFwdOpts(scale=scale.cuda()))
+    assert out.r_inv is None
+    y_ref, _ = oracle.rmsnorm_fwd(to_f32(x), to_f32(scale), None, 1e-6)
+    assert_all_close("y", to_f32(out.y), y_ref, oracle.abs_rel_tolerance(y_ref, 1e-5, 2.0 ** -7))
+
+
+def test_fwd_config2_and_determinism(cdl, gpu_ok):
+    """BASELINE config 2: x[16384, 2048] ~ N(0,1), weight 1 + N(0, 0.02), eps 1e-6, seed 1."""
+    gen = torch.Generator().manual_seed(1)
+    x = torch.randn(16384, 2048, generator=gen).to(torch.bfloat16)
+    w = (1 + 0.02 * torch.randn(2048, generator=gen)).to(torch.bfloat16)
+    opts = cdl.ops.NormFwdOpts(scale=w.cuda(), save_stats=True)
+    o1 = cdl.ops.norm_fwd(x.cuda(), opts)
+    o2 = cdl.ops.norm_fwd(x.cuda(), opts)
+    assert torch.equal(o1.y, o2.y) and torch.equal(o1.r_inv, o2.r_inv)
+    y_ref, r_ref = oracle.rmsnorm_fwd(to_f32(x), to_f32(w), None, 1e-6)
+    assert_all_close("y", to_f32(o1.y), y_ref, oracle.abs_rel_tolerance(y_ref, 1e-5, 2.0 ** -7))
+    assert_all_close("r_inv", to_f32(o1.r_inv), r_ref, oracle.abs_rel_tolerance(r_ref, 1e-6, 1e-4))
+    rel = np.abs(to_f32(o1.y) - y_ref).max() / np.abs(y_ref).max()
+    assert rel <= 1e-2
+
+
+def test_fwd_empty_and_errors(cdl, gpu_ok):
+    dev = "cuda"
+    out = cdl.ops.norm_fwd(torch.zeros(0, 128, dtype=torch.bfloat16, device=dev))
+    assert out.y.shape == (0, 128)
+    with pytest.raises(cdl._lib.CdlError, match="2D"):
+        cdl.ops.norm_fwd(torch.zeros(2, 4, 128, dtype=torch.bfloat16, device=dev))
+    with pytest.raises(cdl._lib.CdlError, match="multiple of 8"):
+        cdl.ops.norm_fwd(torch.zeros(4, 16, dtype=torch.bfloat16, device=dev)[:, :12].contiguous())
+    with pytest.raises(cdl._lib.CdlError, match=r"shape \[128\]"):
+        cdl.ops.norm_fwd(torch.zeros(4, 128, dtype=torch.bfloat16, device=dev),
+                         cdl.ops.NormFwdOpts(scale=torch.zeros(64, dtype=torch.bfloat16, device=dev)))
+    with pytest.raises(cdl._lib.CdlError, match="bf16"):
+        cdl.ops.norm_fwd(torch.zeros(4, 128, dtype=torch.float32, device=dev))
+
+
+@pytest.mark.parametrize("rows,cols", [(1, 128), (37, 2048), (300, 1536), (1000, 2048), (64, 136),
+                                       (50, 4096), (33, 8192)])
+@pytest.mark.parametrize("residual", [False, True])
+def test_bwd_cases(cdl, gpu_ok, rows, cols, residual):
+    gen = torch.Generator().manual_seed(3)
+    x = torch.randn(rows, cols, generator=gen).to(torch.bfloat16)
+    dy = torch.randn(rows, cols, generator=gen).to(torch.bfloat16)
+    w = (1 + 0.02 * torch.randn(cols, generator=gen)).to(torch.bfloat16)
+    res = torch.randn(rows, cols, generator=gen).to(torch.bfloat16) if residual else None
+    dscale0 = torch.randn(cols, generator=gen)
+    fwd = cdl.ops.norm_fwd(x.cuda(), cdl.ops.NormFwdOpts(scale=w.cuda(), save_stats=True))
+    dscale = dscale0.cuda().clone()
+    dx = cdl.ops.norm_bwd(x.cuda(), dy.cuda(), w.cuda(), fwd.r_inv, dscale,
+                          residual_dy=None if res is None else res.cuda())
+    dx_ref, ds_ref = oracle.rmsnorm_bwd(to_f32(x), to_f32(dy), to_f32(w),
+                                        None if res is None else to_f32(res), 1e-6,
+                                        dscale_init=to_f32(dscale0))
+    assert_all_close("dx", to_f32(dx), dx_ref, oracle.abs_rel_tolerance(dx_ref, 1e-4, 2.0 ** -7))
+    # dscale is an f32 sum over rows of products of bf16 values.
+    bound = np.abs(to_f32(dy) * to_f32(x)).sum(axis=0) * 3.0 + np.abs(to_f32(dscale0))
+    assert_all_close("dscale", to_f32(dscale), ds_ref, 1e-5 + 1e-5 * bound + 1e-4 * np.abs(ds_ref))
+
+
+def test_bwd_config2_determinism(cdl, gpu_ok):
+    gen = torch.Generator().manual_seed(1)
+    x = torch.randn(16384, 2048, generator=gen).to(torch.bfloat16).cuda()
+    w = (1 + 0.02 * torch.randn(2048, generator=gen)).to(torch.bfloat16).cuda()
+    dy = torch.randn(16384, 2048, generator=gen).to(torch.bfloat16).cuda()
+    fwd = cdl.ops.norm_fwd(x, cdl.ops.NormFwdOpts(scale=w, save_stats=True))
+    ds1 = torch.zeros(2048, device="cuda")
+    ds2 = torch.zeros(2048, device="cuda")
+    dx1 = cdl.ops.norm_bwd(x, dy, w, fwd.r_inv, ds1)
+    dx2 = cdl.ops.norm_bwd(x, dy, w, fwd.r_inv, ds2)
+    assert torch.equal(dx1, dx2) and torch.equal(ds1, ds2)
+    dx_ref, ds_ref = oracle.rmsnorm_bwd(to_f32(x), to_f32(dy), to_f32(w), None, 1e-6)
+    assert np.abs(to_f32(dx1) - dx_ref).max() / np.abs(dx_ref).max() <= 1e-2
+    assert np.abs(to_f32(ds1) - ds_ref).max() / np.abs(ds_ref).max() <= 1e-2
