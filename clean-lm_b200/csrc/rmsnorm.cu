@@ -298,15 +298,15 @@ int32_t rmsnorm_fwd_execute(const cdl_tensor* x, const cdl_tensor* scale, const 
   if (!x || !y) return fail(CDL_ERR_INVALID, "%s: x and y are required", op);
   if (x->rank != 2) return fail(CDL_ERR_INVALID, "%s: x must be a 2D tensor", op);
   const long long rows = x->shape[0], cols = x->shape[1];
+  if (cols % 8 != 0 || cols > 8192)
+    return fail(CDL_ERR_UNSUPPORTED,
+                "%s: cols must be a multiple of 8 and at most 8192 (got %lld)", op, cols);
   CDL_CHECK(check_rows(op, "x", x, rows, cols));
   CDL_CHECK(check_rows(op, "y", y, rows, cols));
   if (scale) CDL_CHECK(check_vec(op, "scale", scale, cols, CDL_BF16, true));
   if (bias) CDL_CHECK(check_vec(op, "bias", bias, cols, CDL_BF16, true));
   if (r_inv) CDL_CHECK(check_vec(op, "r_inv", r_inv, rows, CDL_F32, false));
   if (rows == 0 || cols == 0) return CDL_OK;
-  if (cols % 8 != 0 || cols > 8192)
-    return fail(CDL_ERR_UNSUPPORTED,
-                "%s: cols must be a multiple of 8 and at most 8192 (got %lld)", op, cols);
   if (rows > INT32_MAX) return fail(CDL_ERR_UNSUPPORTED, "%s: too many rows", op);
   const int r = static_cast<int>(rows), c = static_cast<int>(cols);
   if (c <= 256) launch_fwd<1>(x, scale, bias, eps, y, r_inv, r, c, stream);
@@ -334,6 +334,9 @@ int32_t rmsnorm_bwd_execute(const cdl_tensor* x, const cdl_tensor* dy, const cdl
     return fail(CDL_ERR_INVALID, "%s: x, dy, scale, r_inv, dx and dscale are required", op);
   if (x->rank != 2) return fail(CDL_ERR_INVALID, "%s: x must be a 2D tensor", op);
   const long long rows = x->shape[0], cols = x->shape[1];
+  if (cols % 8 != 0 || cols > 8192)
+    return fail(CDL_ERR_UNSUPPORTED,
+                "%s: cols must be a multiple of 8 and at most 8192 (got %lld)", op, cols);
   CDL_CHECK(check_rows(op, "x", x, rows, cols));
   CDL_CHECK(check_rows(op, "dy", dy, rows, cols));
   CDL_CHECK(check_rows(op, "dx", dx, rows, cols));
@@ -341,11 +344,7 @@ int32_t rmsnorm_bwd_execute(const cdl_tensor* x, const cdl_tensor* dy, const cdl
   CDL_CHECK(check_vec(op, "scale", scale, cols, CDL_BF16, true));
   CDL_CHECK(check_vec(op, "r_inv", r_inv, rows, CDL_F32, false));
   CDL_CHECK(check_vec(op, "dscale", dscale, cols, CDL_F32, false));
-  if (cols == 0) return CDL_OK;
-  if (cols % 8 != 0 || cols > 8192)
-    return fail(CDL_ERR_UNSUPPORTED,
-                "%s: cols must be a multiple of 8 and at most 8192 (got %lld)", op, cols);
-  if (rows == 0) return CDL_OK;
+  if (cols == 0 || rows == 0) return CDL_OK;
   if (rows > INT32_MAX) return fail(CDL_ERR_UNSUPPORTED, "%s: too many rows", op);
   if (scratch == nullptr || scratch_bytes < rmsnorm_bwd_scratch_bytes(rows, cols) ||
       (reinterpret_cast<uintptr_t>(scratch) & 15) != 0)
