@@ -1,0 +1,111 @@
+"""GPU parity of flash attention forward / backward against the f64 oracle, through the C ABI.
+
+Follows crates/cleandl/tests/attention.rs: inputs N(0,1) rounded to bf16 (:251-259); tolerance
+atol * max|expected| + rtol * |expected| (:541-556) with (1e-2, 1e-2) for the bf16 output,
+(1e-4, 1e-3) for LSE and (2e-2, 2e-2) for bf16 gradients (:781-804); cases over masks, GQA and
+Sq != Sk (:836-866), fused-QKV slicing (:589-613), backward (:984-1032), rejections (:1035-1105).
+"""
+import numpy as np
+import pytest
+import torch
+
+from helpers import assert_all_close, to_f32
+from oracle import cpu_oracle as oracle
+
+pytestmark = pytest.mark.gpu
+
+
+def make(b, sq, sk, hq, hk, seed=7, d=128):
+    gen = torch.Generator().manual_seed(seed)
+    q = torch.randn(b, sq, hq, d, generator=gen).to(torch.bfloat16)
+    k = torch.randn(b, sk, hk, d, generator=gen).to(torch.bfloat16)
+    v = torch.randn(b, sk, hk, d, generator=gen).to(torch.bfloat16)
+    do = torch.randn(b, sq, hq, d, generator=gen).to(torch.bfloat16)
+    return q, k, v, do
+
+
+def check_fwd(out, q, k, v, causal, scale=None):
+    ref = oracle.attention(to_f32(q), to_f32(k), to_f32(v), None, scale=scale, causal=causal)
+    assert_all_close("out", to_f32(out.out), ref["out"],
+                     oracle.attention_tolerance(ref["out"], 1e-2, 1e-2))
+    got_lse = np.where(np.isneginf(to_f32(out.lse)), -1e30, to_f32(out.lse))
+    exp_lse = np.where(np.isneginf(ref["lse"]), -1e30, ref["lse"])
+    assert_all_close("lse", got_lse, exp_lse, oracle.attention_tolerance(ref["lse"], 1e-4, 1e-3))
+    return ref
+
+
+FWD_CASES = [
+    # b, sq, sk, hq, hk, causal
+    (1, 128, 128, 1, 1, True),
+    (1, 256, 256, 2, 2, True),
+    (2, 384, 384, 2, 1, True),     # GQA, odd number of 128-row tiles
+    (1, 200, 200, 2, 2, True),     # ragged tail
+    (1, 77, 333, 2, 2, True),      # sq < sk: mask aligned to the bottom right
+    (1, 300, 100, 1, 1, True),     # sq > sk: the first rows see no key
+    (2, 256, 320, 4, 2, False),    # dense (no mask), GQA
+    (1, 1, 1, 1, 1, True),
+    (1, 640, 640, 1, 1, True),
+]
+
+
+@pytest.mark.parametrize("b,sq,sk,hq,hk,causal", FWD_CASES)
+def test_fwd_cases(cdl, gpu_ok, b, sq, sk, hq, hk, causal):
+    q, k, v, _ = make(b, sq, sk, hq, hk)
+    out = cdl.ops.attention_fwd(q.cuda(), k.cuda(), v.cuda(), cdl.ops.AttentionOpts(causal=causal))
+    check_fwd(out, q, k, v, causal)
+
+
+def test_fwd_fused_qkv_views_and_scale(cdl, gpu_ok):
+    """q, k, v as slices of one fused [B, S, 3H, D] buffer, custom softmax scale."""
+    b, s, h = 2, 256, 2
+    gen = torch.Generator().manual_seed(11)
+    qkv = torch.randn(b, s, 3 * h, 128, generator=gen).to(torch.bfloat16)
+    dq = qkv.cuda()
+    q, k, v = dq[:, :, :h], dq[:, :, h:2 * h], dq[:, :, 2 * h:]
+    out = cdl.ops.attention_fwd(q, k, v, cdl.ops.AttentionOpts(softmax_scale=0.05, causal=True))
+    check_fwd(out, qkv[:, :, :h], qkv[:, :, h:2 * h], qkv[:, :, 2 * h:], True, scale=0.05)
+
+
+def test_fwd_large_logits_rescale(cdl, gpu_ok):
+    """Scores that grow along the sequence force the running max to move repeatedly."""
+    q, k, v, _ = make(1, 512, 512, 1, 1, seed=5)
+    ramp = torch.linspace(0.2, 6.0, 512).view(1, 512, 1, 1)
+    k = (k.float() * ramp).to(torch.bfloat16)
+    out = cdl.ops.attention_fwd(q.cuda(), k.cuda(), v.cuda(), cdl.ops.AttentionOpts(causal=True))
+    check_fwd(out, q, k, v, True)
+
+
+def test_fwd_deterministic_and_sdpa_at_config3_shape(cdl, gpu_ok):
+    """BASELINE config 3 shape (B=8, H=16, S=2048, D=128, seed 2): the f64 oracle would need
+    minutes, so the full size is compared with torch's fp32 attention on the GPU and one
+    (batch, head) slice with the oracle."""
+    gen = torch.Generator().manual_seed(2)
+    q, k, v = (torch.randn(8, 2048, 16, 128, generator=gen).to(torch.bfloat16).cuda() for _ in range(3))
+    o1 = cdl.ops.attention_fwd(q, k, v)
+    o2 = cdl.ops.attention_fwd(q, k, v)
+    assert torch.equal(o1.out, o2.out) and torch.equal(o1.lse, o2.lse)
+    ref = torch.nn.functional.scaled_dot_product_attention(
+        q[:2].float().transpose(1, 2), k[:2].float().transpose(1, 2), v[:2].float().transpose(1, 2),
+        is_causal=True).transpose(1, 2)
+    err = (o1.out[:2].float() - ref).abs().max().item() / ref.abs().max().item()
+    assert err <= 1e-2
+    sl = (slice(7, 8), slice(None), slice(15, 16))
+    r = oracle.attention(to_f32(q[sl]), to_f32(k[sl]), to_f32(v[sl]), None, causal=True)
+    assert_all_close("out", to_f32(o1.out[sl]), r["out"], oracle.attention_tolerance(r["out"], 1e-2, 1e-2))
+    assert_all_close("lse", to_f32(o1.lse[7:8, 15:16]), r["lse"],
+                     oracle.attention_tolerance(r["lse"], 1e-4, 1e-3))
+
+
+def test_fwd_rejections(cdl, gpu_ok):
+    dev = "cuda"
+    z = lambda *s: torch.zeros(*s, dtype=torch.bfloat16, device=dev)
+    with pytest.raises(cdl._lib.CdlError, match="head dimension"):
+        cdl.ops.attention_fwd(z(1, 8, 1, 64), z(1, 8, 1, 64), z(1, 8, 1, 64))
+    with pytest.raises(cdl._lib.CdlError, match="multiple of kv heads"):
+        cdl.ops.attention_fwd(z(1, 8, 3, 128), z(1, 8, 2, 128), z(1, 8, 2, 128))
+    with pytest.raises(cdl._lib.CdlError, match="shape"):
+        cdl.ops.attention_fwd(z(1, 8, 2, 128), z(1, 8, 2, 128), z(1, 9, 2, 128))
+    with pytest.raises(cdl._lib.CdlError, match="contiguous"):
+        cdl.ops.attention_fwd(z(1, 8, 2, 256)[..., ::2], z(1, 8, 2, 128), z(1, 8, 2, 128))
+    out = cdl.ops.attention_fwd(z(0, 8, 2, 128), z(0, 8, 2, 128), z(0, 8, 2, 128))
+    assert out.out.shape == (0, 8, 2, 128)
