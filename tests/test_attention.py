@@ -109,3 +109,80 @@ def test_fwd_rejections(cdl, gpu_ok):
         cdl.ops.attention_fwd(z(1, 8, 2, 256)[..., ::2], z(1, 8, 2, 128), z(1, 8, 2, 128))
     out = cdl.ops.attention_fwd(z(0, 8, 2, 128), z(0, 8, 2, 128), z(0, 8, 2, 128))
     assert out.out.shape == (0, 8, 2, 128)
+
+
+def check_bwd(cdl, q, k, v, do, causal, scale=None):
+    dq_, dk_, dv_, ddo = q.cuda(), k.cuda(), v.cuda(), do.cuda()
+    opts = cdl.ops.AttentionOpts(softmax_scale=scale, causal=causal)
+    fwd = cdl.ops.attention_fwd(dq_, dk_, dv_, opts)
+    dq, dk, dv = cdl.ops.attention_bwd(dq_, dk_, dv_, fwd.out, ddo, fwd.lse, opts)
+    ref = oracle.attention(to_f32(q), to_f32(k), to_f32(v), to_f32(do), scale=scale, causal=causal)
+    for name, got in (("dq", dq), ("dk", dk), ("dv", dv)):
+        assert_all_close(name, to_f32(got), ref[name], oracle.attention_tolerance(ref[name], 2e-2, 2e-2))
+
+
+BWD_CASES = [
+    (1, 128, 128, 1, 1, True),
+    (1, 256, 256, 2, 2, True),
+    (2, 384, 384, 2, 1, True),     # GQA: dk/dv accumulate over the query heads of a group
+    (1, 200, 200, 2, 2, True),     # ragged tail
+    (1, 77, 333, 2, 2, True),      # sq < sk
+    (1, 300, 100, 1, 1, True),     # sq > sk: rows without keys, key blocks without queries
+    (2, 256, 320, 4, 2, False),    # dense, GQA
+    (1, 1, 1, 1, 1, True),
+    (1, 640, 512, 1, 1, True),
+]
+
+
+@pytest.mark.parametrize("b,sq,sk,hq,hk,causal", BWD_CASES)
+def test_bwd_cases(cdl, gpu_ok, b, sq, sk, hq, hk, causal):
+    q, k, v, do = make(b, sq, sk, hq, hk)
+    check_bwd(cdl, q, k, v, do, causal)
+
+
+def test_bwd_fused_qkv_views(cdl, gpu_ok):
+    """Inputs and gradients as slices of fused [B, S, 3H, D] buffers (the sky-1 block's layout)."""
+    b, s, h = 1, 256, 2
+    gen = torch.Generator().manual_seed(13)
+    qkv = torch.randn(b, s, 3 * h, 128, generator=gen).to(torch.bfloat16)
+    do = torch.randn(b, s, h, 128, generator=gen).to(torch.bfloat16)
+    dev = qkv.cuda()
+    q, k, v = dev[:, :, :h], dev[:, :, h:2 * h], dev[:, :, 2 * h:]
+    fwd = cdl.ops.attention_fwd(q, k, v)
+    dqkv = torch.zeros_like(dev)
+    cdl.ops.attention_bwd(q, k, v, fwd.out, do.cuda(), fwd.lse, dq=dqkv[:, :, :h],
+                          dk=dqkv[:, :, h:2 * h], dv=dqkv[:, :, 2 * h:])
+    ref = oracle.attention(to_f32(qkv[:, :, :h]), to_f32(qkv[:, :, h:2 * h]), to_f32(qkv[:, :, 2 * h:]),
+                           to_f32(do), causal=True)
+    for i, name in enumerate(("dq", "dk", "dv")):
+        assert_all_close(name, to_f32(dqkv[:, :, i * h:(i + 1) * h]), ref[name],
+                         oracle.attention_tolerance(ref[name], 2e-2, 2e-2))
+
+
+def test_bwd_config3_shape_vs_torch_autograd(cdl, gpu_ok):
+    """BASELINE config 3 (B=8, H=16, S=2048, D=128, seed 2) against fp32 autograd through
+    torch's attention on the same GPU for two batches, and one (batch, head) against the oracle."""
+    gen = torch.Generator().manual_seed(2)
+    q, k, v, do = (torch.randn(8, 2048, 16, 128, generator=gen).to(torch.bfloat16).cuda()
+                   for _ in range(4))
+    fwd = cdl.ops.attention_fwd(q, k, v)
+    dq, dk, dv = cdl.ops.attention_bwd(q, k, v, fwd.out, do, fwd.lse)
+    qf, kf, vf = (t[:2].float().transpose(1, 2).detach().requires_grad_(True) for t in (q, k, v))
+    out = torch.nn.functional.scaled_dot_product_attention(qf, kf, vf, is_causal=True)
+    out.backward(do[:2].float().transpose(1, 2))
+    for name, got, ref in (("dq", dq, qf.grad), ("dk", dk, kf.grad), ("dv", dv, vf.grad)):
+        ref = ref.transpose(1, 2)
+        err = (got[:2].float() - ref).abs().max().item() / ref.abs().max().item()
+        assert err <= 2e-2, (name, err)
+    sl = (slice(5, 6), slice(None), slice(3, 4))
+    r = oracle.attention(to_f32(q[sl]), to_f32(k[sl]), to_f32(v[sl]), to_f32(do[sl]), causal=True)
+    for name, got in (("dq", dq), ("dk", dk), ("dv", dv)):
+        assert_all_close(name, to_f32(got[sl]), r[name], oracle.attention_tolerance(r[name], 2e-2, 2e-2))
+
+
+def test_bwd_scratch_is_checked(cdl, gpu_ok):
+    q, k, v, do = (t.cuda() for t in make(1, 128, 128, 1, 1))
+    fwd = cdl.ops.attention_fwd(q, k, v)
+    small = torch.empty(64, dtype=torch.uint8, device="cuda")
+    with pytest.raises(cdl._lib.CdlError, match="scratch"):
+        cdl.ops.attention_bwd(q, k, v, fwd.out, do, fwd.lse, scratch=small)
