@@ -1,0 +1,340 @@
+#!/usr/bin/env python
+"""Benchmark of the hot path: sky-1 decoder block forward + backward, tokens/s.
+
+Workload (BASELINE config 4): hidden 2048, 16 heads x 128, RoPE, pre-RMSNorm, SwiGLU FFN 5632,
+batch 8 x seq 2048 per GPU, weights ~ N(0, 0.02) bf16, tokens uniform over a 32768-token vocabulary,
+seed 3.  One step = token embedding lookup -> block forward -> block backward (weight gradients
+accumulated in f32) for one batch; at N > 1 every rank runs its own batch (weak scaling, data
+parallel) and the weight gradients are all-reduced with NCCL, the FFN bucket overlapping the
+attention half of the backward.
+
+Printed line (rank 0): `value` = tokens/s with inputs resident in HBM, timed with CUDA events over
+exactly K steps, max over ranks; `e2e` = the same through the public API with the step's token ids
+copied from pinned host memory and the step's result (the gradient of the first norm gain, 8 KiB)
+read back every step; `roofline` = the GEMM kernel (the dominant one) timed per launch by the
+library's event profiler inside the timed region; `cpu_baseline` = the CPU oracle of the same block
+on a bounded sample.  `--impl reference` times only that CPU path (the reference has no other host
+implementation of these operators and cannot be built here).
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import statistics
+import subprocess
+import sys
+import threading
+import time
+from pathlib import Path
+
+ROOT = Path(__file__).resolve().parent
+sys.path.insert(0, str(ROOT))
+
+VOCAB = 32768
+SEED = 3
+METRIC = "sky1_block_fwd_bwd_tokens_per_s"
+
+
+def measured_peaks() -> dict:
+    p = ROOT / "MEASURED_PEAKS.json"
+    if p.exists():
+        d = json.loads(p.read_text())
+        return {"bf16": float(d["bf16_tflops_sustained"]), "bf16_burst": float(d["bf16_tflops"]),
+                "hbm": float(d["hbm_gbs"]), "source": "measured"}
+    return {"bf16": 1400.0, "bf16_burst": 1590.0, "hbm": 6650.0, "source": "fallback"}
+
+
+# ------------------------------------------------------------------ CPU baseline (oracle)
+def cpu_block_tokens_per_s(seqlen: int, repeats: int = 1):
+    """Times the float64 CPU restatement of the block (oracle/block_ref.py), forward + backward,
+    on batch 1 x `seqlen` tokens at the full model dimensions. Returns (tokens/s, threads)."""
+    import torch
+
+    from oracle import block_ref
+
+    cfg = dict(heads=16, kv_heads=16, head_dim=128, eps=1e-6)
+    gen = torch.Generator().manual_seed(SEED)
+    shapes = {"norm1": (2048,), "wqkv": (2048, 6144), "wo": (2048, 2048), "norm2": (2048,),
+              "wup": (2048, 5632), "wgate": (2048, 5632), "wdown": (5632, 2048)}
+    w = {n: (torch.ones(s) if n.startswith("norm") else torch.randn(s, generator=gen) * 0.02)
+         .to(torch.bfloat16) for n, s in shapes.items()}
+    x = torch.randn(1, seqlen, 2048, generator=gen).to(torch.bfloat16)
+    dy = torch.randn(1, seqlen, 2048, generator=gen).to(torch.bfloat16)
+    table = block_ref.rope_table(seqlen, 128)
+    best = None
+    for _ in range(repeats):
+        t0 = time.perf_counter()
+        block_ref.block_forward_backward(x, w, dy, cfg, table)
+        dt = time.perf_counter() - t0
+        best = dt if best is None else min(best, dt)
+    return seqlen / best, torch.get_num_threads()
+
+
+def run_reference(args) -> None:
+    rank = int(os.environ.get("RANK", "0"))
+    if rank != 0:
+        return
+    seqlen = 512
+    for _ in range(args.warmup):
+        cpu_block_tokens_per_s(seqlen)
+    t0 = time.perf_counter()
+    threads = 1
+    for _ in range(args.steps):
+        _, threads = cpu_block_tokens_per_s(seqlen)
+    dt = time.perf_counter() - t0
+    value = args.steps * seqlen / dt
+    sample = f"batch 1 x seq {seqlen} of the block at full width, float64, per step"
+    print(json.dumps({
+        "impl": "reference", "metric": METRIC, "value": value, "unit": "tokens/s",
+        "n_gpus": args.gpus, "steps": args.steps, "warmup": args.warmup,
+        "ms_per_step": 1e3 * dt / args.steps, "higher_is_better": True, "scaling": "weak",
+        "vs_baseline": None, "dtype": "f64", "data": "synthetic",
+        "config": {"workload": "sky-1 block fwd+bwd, hidden 2048, 16x128 heads, ffn 5632 (config 4)",
+                   "sample": sample},
+        "cpu_baseline": {"value": value, "unit": "tokens/s", "cores": threads, "kind": "port",
+                         "sample": sample},
+        "e2e": {"value": value, "unit": "tokens/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+        "gpu_launches": 0,
+    }))
+
+
+# ------------------------------------------------------------------ clocks sampler
+class ClockSampler:
+    FIELDS = ("clocks.sm,clocks.max.sm,clocks_event_reasons.hw_slowdown,"
+              "clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,"
+              "clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, index: int):
+        self.samples = []
+        self.proc = None
+        try:
+            self.proc = subprocess.Popen(
+                ["nvidia-smi", f"--query-gpu={self.FIELDS}", "--format=csv,noheader,nounits",
+                 "-lms", "100", "-i", str(index)], stdout=subprocess.PIPE, stderr=subprocess.DEVNULL,
+                text=True)
+            self.thread = threading.Thread(target=self._read, daemon=True)
+            self.thread.start()
+        except OSError:
+            self.proc = None
+
+    def _read(self):
+        for line in self.proc.stdout:
+            parts = [p.strip() for p in line.split(",")]
+            if len(parts) == 6 and parts[0].isdigit():
+                self.samples.append(parts)
+
+    def stop(self) -> dict:
+        if self.proc is None:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
+        self.proc.terminate()
+        try:
+            self.proc.wait(timeout=5)
+        except subprocess.TimeoutExpired:
+            self.proc.kill()
+        if not self.samples:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["no samples"]}
+        sm = [int(s[0]) for s in self.samples]
+        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+        reasons = [n for i, n in enumerate(names) if any(s[2 + i] == "Active" for s in self.samples)]
+        return {"sm_mhz": statistics.median(sm), "sm_max_mhz": int(self.samples[0][1]),
+                "reasons": reasons, "samples": len(sm)}
+
+
+# ------------------------------------------------------------------ our arm
+def run_ours(args) -> None:
+    import torch
+    import torch.distributed as dist
+
+    import cleanlm_b200 as cdl
+
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    rank = int(os.environ.get("RANK", "0"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    torch.cuda.set_device(local)
+    dev = torch.device("cuda", local)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=dev)
+    L = cdl._lib
+    L.check(L.lib.cdl_b200_device_ok(local))
+
+    cfg = cdl.sky1.Sky1Config()  # config 4
+    T = cfg.tokens
+    params = cdl.sky1.init_params(cfg, seed=SEED)
+    # One flat f32 gradient bucket, FFN gradients first (they are final first in the backward).
+    order = ("wdown", "wup", "wgate", "norm2", "wo", "wqkv", "norm1")
+    shapes = cfg.param_shapes()
+    sizes = {n: int(torch.Size(shapes[n]).numel()) for n in order}
+    bucket = torch.zeros(sum(sizes.values()), dtype=torch.float32, device=dev)
+    grads, off = {}, 0
+    for n in order:
+        grads[n] = bucket[off:off + sizes[n]].view(shapes[n])
+        off += sizes[n]
+    ffn_elems = sum(sizes[n] for n in order[:4])
+    blk = cdl.sky1.Sky1Block(cfg, params, device=dev, grads=grads)
+
+    gen = torch.Generator().manual_seed(SEED + 1000 * rank)
+    emb = (torch.randn(VOCAB, cfg.hidden, generator=gen) * 0.02).to(torch.bfloat16).to(dev)
+    dy = torch.randn(T, cfg.hidden, generator=gen).to(torch.bfloat16).to(dev)
+    n_host = args.warmup + args.steps
+    tokens_host = torch.randint(0, VOCAB, (n_host, T), generator=gen, dtype=torch.int32).pin_memory()
+    tokens_dev = torch.empty(T, dtype=torch.int32, device=dev)
+    x = torch.empty(T, cfg.hidden, dtype=torch.bfloat16, device=dev)
+    out = torch.empty_like(x)
+    dx = torch.empty_like(x)
+    result_host = torch.empty(cfg.hidden, dtype=torch.float32).pin_memory()
+
+    main = torch.cuda.Stream(device=dev)
+    comm = torch.cuda.Stream(device=dev)
+    ffn_ready = torch.cuda.Event()
+    all_ready = torch.cuda.Event()
+    reduced = torch.cuda.Event()
+
+    def embed():
+        tt, te, tx = L.tensor_arg(tokens_dev), L.tensor_arg(emb), L.tensor_arg(x)
+        L.check(L.lib.cdl_b200_embedding_fwd(L.ref(tt), L.ref(te), L.ref(tx),
+                                             torch.cuda.current_stream().cuda_stream))
+
+    def fwd_bwd():
+        blk.forward(x, out)
+        if world == 1:
+            bucket.zero_()
+            blk.backward(dy, dx)
+            return
+        # The previous step's all-reduce must have drained before gradients are touched again.
+        torch.cuda.current_stream().wait_event(reduced)
+        bucket.zero_()
+        blk.backward(dy, dx, phase=1)
+        ffn_ready.record()
+        with torch.cuda.stream(comm):
+            comm.wait_event(ffn_ready)
+            dist.all_reduce(bucket[:ffn_elems])
+        blk.backward(dy, dx, phase=2)
+        all_ready.record()
+        with torch.cuda.stream(comm):
+            comm.wait_event(all_ready)
+            dist.all_reduce(bucket[ffn_elems:])
+            reduced.record()
+
+    def step_resident():
+        embed()
+        fwd_bwd()
+
+    def step_e2e(i: int):
+        tokens_dev.copy_(tokens_host[i], non_blocking=True)
+        embed()
+        fwd_bwd()
+        if world > 1:
+            torch.cuda.current_stream().wait_event(reduced)
+        result_host.copy_(grads["norm1"], non_blocking=True)
+        torch.cuda.current_stream().synchronize()
+
+    def barrier():
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize(dev)
+
+    def max_over_ranks(ms: float) -> float:
+        if world == 1:
+            return ms
+        t = torch.tensor([ms], dtype=torch.float64, device=dev)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        return float(t.item())
+
+    with torch.cuda.stream(main):
+        reduced.record()
+        tokens_dev.copy_(tokens_host[0])
+        # ---- device-resident number
+        for _ in range(args.warmup):
+            step_resident()
+        barrier()
+        sampler = ClockSampler(local) if rank == 0 else None
+        L.profile_start(64 * args.steps + 64)
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        for _ in range(args.steps):
+            step_resident()
+        if world > 1:
+            torch.cuda.current_stream().wait_event(reduced)
+        e1.record()
+        barrier()
+        records = L.profile_stop(64 * args.steps + 64)
+        clocks = sampler.stop() if sampler else None
+        ms_resident = max_over_ranks(e0.elapsed_time(e1))
+
+        # ---- end to end: host token ids in, result read back, every step
+        for i in range(args.warmup):
+            step_e2e(i)
+        barrier()
+        t0, t1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        t0.record()
+        for i in range(args.steps):
+            step_e2e(args.warmup + i)
+        t1.record()
+        barrier()
+        ms_e2e = max_over_ranks(t0.elapsed_time(t1))
+    status = L.device_status()
+    if status != 0:
+        raise RuntimeError(f"a kernel reported status {status} (bounded wait ran out)")
+
+    if rank == 0:
+        peaks = measured_peaks()
+        by_kind = {}
+        for kind, ms, work in records:
+            k = by_kind.setdefault(kind, [0, 0.0, 0.0])
+            k[0] += 1
+            k[1] += ms
+            k[2] += work
+        gemm = by_kind.get("gemm", [0, 0.0, 0.0])
+        achieved = gemm[2] / (gemm[1] * 1e-3) / 1e12 if gemm[1] > 0 else None
+        kernel_ms = {k: round(v[1] / args.steps, 4) for k, v in by_kind.items()}
+        # kernels launched per step: 15 GEMM, 4 norm fwd, 2 x 2 norm bwd, 1 attn fwd,
+        # 3 attn bwd (+ memset), 2 rope, 2 swiglu, 1 embedding
+        launches_per_step = 15 + 4 + 4 + 1 + 3 + 2 + 2 + 1
+        cpu_value, cpu_threads = cpu_block_tokens_per_s(512)
+        line = {
+            "metric": METRIC, "value": args.steps * T * world / (ms_resident * 1e-3),
+            "unit": "tokens/s", "n_gpus": world, "steps": args.steps, "warmup": args.warmup,
+            "ms_per_step": ms_resident / args.steps, "higher_is_better": True, "scaling": "weak",
+            "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
+            "config": {"workload": "sky-1 block fwd+bwd (config 4): hidden 2048, 16x128 heads, RoPE, "
+                                   "pre-RMSNorm, SwiGLU 5632, batch 8 x seq 2048 per GPU, seed 3",
+                       "parallelism": f"dp{world}",
+                       "l2": "per-step working set (~1 GB of activations) exceeds the 126 MB L2",
+                       "tflops_per_gpu": cfg.flops_fwd_bwd() * args.steps / (ms_resident * 1e-3) / 1e12,
+                       "kernel_ms_per_step": kernel_ms},
+            "e2e": {"value": args.steps * T * world / (ms_e2e * 1e-3), "unit": "tokens/s",
+                    "h2d_bytes_per_step": T * 4, "d2h_bytes_per_step": cfg.hidden * 4,
+                    "ms_per_step": ms_e2e / args.steps},
+            "gpu_launches": launches_per_step * args.steps * 2,
+            "clocks": clocks,
+            "roofline": {"bound": "tensor", "achieved": achieved, "peak": peaks["bf16"],
+                         "unit": "TFLOP/s", "frac": (achieved / peaks["bf16"]) if achieved else None,
+                         "traffic": None, "kernel": "gemm_bf16_kernel",
+                         "launches": gemm[0], "peak_source": peaks["source"] + " (sustained cuBLAS bf16)"},
+            "cpu_baseline": {"value": cpu_value, "unit": "tokens/s", "cores": cpu_threads,
+                             "kind": "port",
+                             "sample": "batch 1 x seq 512 of the same block, float64 oracle, one pass"},
+        }
+        print(json.dumps(line))
+    if world > 1:
+        dist.destroy_process_group()
+
+
+def main() -> None:
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=20)
+    ap.add_argument("--warmup", type=int, default=3)
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    args = ap.parse_args()
+    if args.warmup < 3 and args.impl == "ours":
+        args.warmup = 3
+    if args.impl == "reference":
+        run_reference(args)
+    else:
+        run_ours(args)
+
+
+if __name__ == "__main__":
+    main()

@@ -8,5 +8,6 @@ PyTorch is used for device memory, streams and torch.distributed only.
 """
 from . import _lib  # noqa: F401  (raises if the CUDA library has not been built)
 from . import ops  # noqa: F401
+from . import sky1  # noqa: F401
 
-__all__ = ["_lib", "ops"]
+__all__ = ["_lib", "ops", "sky1"]

@@ -32,6 +32,31 @@ class CdlAttnDesc(ctypes.Structure):
     _fields_ = [("softmax_scale", ctypes.c_float), ("causal", ctypes.c_int32)]
 
 
+class CdlProfileRecord(ctypes.Structure):
+    _fields_ = [("kind", ctypes.c_int32), ("ms", ctypes.c_float), ("work", ctypes.c_double)]
+
+
+class CdlSky1Config(ctypes.Structure):
+    _fields_ = [(n, ctypes.c_int32) for n in
+                ("batch", "seqlen", "hidden", "heads", "kv_heads", "head_dim", "ffn")] + [
+                    ("eps", ctypes.c_float)]
+
+
+_BLOCK_PARAMS = ("norm1", "wqkv", "wo", "norm2", "wup", "wgate", "wdown")
+
+
+class CdlSky1Weights(ctypes.Structure):
+    _fields_ = [(n, ctypes.c_void_p) for n in _BLOCK_PARAMS]
+
+
+class CdlSky1Grads(ctypes.Structure):
+    _fields_ = [(n, ctypes.c_void_p) for n in _BLOCK_PARAMS]
+
+
+class CdlSky1Saved(ctypes.Structure):
+    _fields_ = [(n, ctypes.c_void_p) for n in ("qkv", "attn", "lse", "o", "up", "gate", "act")]
+
+
 if not LIB_PATH.exists():
     raise ImportError(
         f"{LIB_PATH} is missing: build it with `python clean-lm_b200/build.py` "
@@ -49,6 +74,10 @@ SIGNATURES = {
     "cdl_b200_last_error": ([], ctypes.c_char_p),
     "cdl_b200_device_ok": ([ctypes.c_int32], ctypes.c_int32),
     "cdl_b200_device_status": ([ctypes.POINTER(ctypes.c_int32)], ctypes.c_int32),
+    "cdl_b200_profile_start": ([ctypes.c_int32], ctypes.c_int32),
+    "cdl_b200_profile_stop": ([ctypes.POINTER(CdlProfileRecord), ctypes.c_int32,
+                               ctypes.POINTER(ctypes.c_int32)], ctypes.c_int32),
+    "cdl_b200_embedding_fwd": ([_T, _T, _T, _vp], ctypes.c_int32),
     "cdl_b200_matmul": ([_T, _T, _T, _T, ctypes.c_float, ctypes.c_float, _vp, _sz, _vp],
                         ctypes.c_int32),
     "cdl_b200_matmul_scratch_bytes": ([_T, _T, _T, ctypes.POINTER(_sz)], ctypes.c_int32),
@@ -60,6 +89,18 @@ SIGNATURES = {
     "cdl_b200_attn_bwd": ([ctypes.POINTER(CdlAttnDesc), _T, _T, _T, _T, _T, _T, _T, _T, _T, _vp,
                            _sz, _vp], ctypes.c_int32),
     "cdl_b200_attn_bwd_scratch_bytes": ([_T, _T, ctypes.POINTER(_sz)], ctypes.c_int32),
+    "cdl_b200_rope": ([_T, _T, ctypes.c_int32, ctypes.c_int32, ctypes.c_int32, _vp], ctypes.c_int32),
+    "cdl_b200_swiglu_fwd": ([_T, _T, _T, _vp], ctypes.c_int32),
+    "cdl_b200_swiglu_bwd": ([_T, _T, _T, _T, _T, _vp], ctypes.c_int32),
+    "cdl_b200_sky1_block_workspace_bytes": ([ctypes.POINTER(CdlSky1Config), ctypes.POINTER(_sz),
+                                             ctypes.POINTER(_sz)], ctypes.c_int32),
+    "cdl_b200_sky1_block_fwd": ([ctypes.POINTER(CdlSky1Config), ctypes.POINTER(CdlSky1Weights), _vp,
+                                 _vp, ctypes.POINTER(CdlSky1Saved), _vp, _vp, _sz, _vp],
+                                ctypes.c_int32),
+    "cdl_b200_sky1_block_bwd": ([ctypes.POINTER(CdlSky1Config), ctypes.POINTER(CdlSky1Weights), _vp,
+                                 _vp, ctypes.POINTER(CdlSky1Saved), _vp,
+                                 ctypes.POINTER(CdlSky1Grads), _vp, _vp, _sz, ctypes.c_int32, _vp],
+                                ctypes.c_int32),
 }
 
 for _name, (_args, _res) in SIGNATURES.items():
@@ -107,3 +148,19 @@ def device_status() -> int:
     out = ctypes.c_int32(0)
     check(lib.cdl_b200_device_status(ctypes.byref(out)))
     return out.value
+
+
+PROFILE_KINDS = {1: "gemm", 2: "norm_fwd", 3: "norm_bwd", 4: "attn_fwd", 5: "attn_bwd",
+                 6: "elementwise"}
+
+
+def profile_start(max_records: int = 4096) -> None:
+    check(lib.cdl_b200_profile_start(max_records))
+
+
+def profile_stop(max_records: int = 4096):
+    """Synchronises the device; returns [(kind name, ms, work), ...] in launch order."""
+    buf = (CdlProfileRecord * max_records)()
+    n = ctypes.c_int32(0)
+    check(lib.cdl_b200_profile_stop(buf, max_records, ctypes.byref(n)))
+    return [(PROFILE_KINDS.get(buf[i].kind, "?"), buf[i].ms, buf[i].work) for i in range(n.value)]

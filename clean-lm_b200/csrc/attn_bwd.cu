@@ -525,6 +525,7 @@ int32_t attn_bwd_execute(const cdl_attn_desc* desc, const cdl_tensor* q, const c
   p.status = device_status_ptr();
   if (!p.status) return fail(CDL_ERR_CUDA, "cannot resolve the device status word");
 
+  ProfileScope ps(PROF_ATTN_BWD, 10.0 * B * H * Sq * Sk * D * (p.causal ? 0.5 : 1.0), stream);
   if (Sq > 0) {
     CDL_CUDA(cudaMemsetAsync(dq_acc, 0, static_cast<size_t>(B) * Sq * H * D * sizeof(float), stream));
     const long long warps = B * H * Sq_pad;

@@ -456,6 +456,8 @@ int32_t attn_fwd_execute(const cdl_attn_desc* desc, const cdl_tensor* q, const c
 
   dim3 grid(static_cast<unsigned>((Sq + 2 * BQ - 1) / (2 * BQ)), static_cast<unsigned>(H),
             static_cast<unsigned>(B));
+  // FLOP by the flash-attention convention: 4 B H Sq Sk D, halved for the causal mask.
+  ProfileScope ps(PROF_ATTN_FWD, 4.0 * B * H * Sq * Sk * D * (p.causal ? 0.5 : 1.0), stream);
   attn_fwd_kernel<<<grid, THREADS, SMEM_BYTES, stream>>>(tq, tk, tv, p);
   CDL_CUDA(cudaGetLastError());
   return CDL_OK;

@@ -458,6 +458,7 @@ int32_t matmul_execute(const cdl_tensor* a, const cdl_tensor* b, const cdl_tenso
     return fail(CDL_ERR_CUDA, "cudaFuncSetAttribute failed: %s", cudaGetErrorString(attr_err));
 
   const int grid = p.num_tiles < sm_count() ? p.num_tiles : sm_count();
+  ProfileScope ps(PROF_GEMM, 2.0 * static_cast<double>(batch) * M * N * K, stream);
   gemm_bf16_kernel<<<grid, THREADS, SMEM_BYTES, stream>>>(tm_a, tm_b, p);
   CDL_CUDA(cudaGetLastError());
   return CDL_OK;

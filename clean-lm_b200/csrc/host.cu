@@ -3,7 +3,9 @@
 // link libcuda directly).
 #include "host.h"
 
+#include <atomic>
 #include <mutex>
+#include <vector>
 
 namespace cdl {
 
@@ -108,9 +110,78 @@ int32_t encode_tmap(CUtensorMap* out, const void* base, int32_t dtype, int rank,
   return CDL_OK;
 }
 
+// ---------------------------------------------------------------- per-launch profiler
+struct ProfileState {
+  std::mutex mu;
+  std::vector<cudaEvent_t> start, stop;
+  std::vector<int> kind;
+  std::vector<double> work;
+  std::atomic<int> next{0};
+  std::atomic<bool> enabled{false};
+};
+static ProfileState& prof() {
+  static ProfileState s;
+  return s;
+}
+
+ProfileScope::ProfileScope(int kind, double work, cudaStream_t stream) : index_(-1), stream_(stream) {
+  ProfileState& p = prof();
+  if (!p.enabled.load(std::memory_order_relaxed)) return;
+  const int i = p.next.fetch_add(1);
+  if (i >= static_cast<int>(p.start.size())) return;
+  index_ = i;
+  p.kind[i] = kind;
+  p.work[i] = work;
+  cudaEventRecord(p.start[i], stream);
+}
+ProfileScope::~ProfileScope() {
+  if (index_ >= 0) cudaEventRecord(prof().stop[index_], stream_);
+}
+
 }  // namespace cdl
 
 extern "C" {
+
+int32_t cdl_b200_profile_start(int32_t max_records) {
+  cdl::ProfileState& p = cdl::prof();
+  std::lock_guard<std::mutex> lock(p.mu);
+  if (max_records <= 0) return cdl::fail(CDL_ERR_INVALID, "profile_start: max_records must be positive");
+  p.enabled.store(false);
+  while (static_cast<int>(p.start.size()) < max_records) {
+    cudaEvent_t a, b;
+    CDL_CUDA(cudaEventCreate(&a));
+    CDL_CUDA(cudaEventCreate(&b));
+    p.start.push_back(a);
+    p.stop.push_back(b);
+  }
+  p.kind.assign(p.start.size(), 0);
+  p.work.assign(p.start.size(), 0.0);
+  p.next.store(0);
+  p.enabled.store(true);
+  return CDL_OK;
+}
+
+int32_t cdl_b200_profile_stop(cdl_profile_record* out, int32_t capacity, int32_t* count) {
+  cdl::ProfileState& p = cdl::prof();
+  std::lock_guard<std::mutex> lock(p.mu);
+  p.enabled.store(false);
+  CDL_CUDA(cudaDeviceSynchronize());
+  int n = p.next.load();
+  if (n > static_cast<int>(p.start.size())) n = static_cast<int>(p.start.size());
+  int written = 0;
+  for (int i = 0; i < n && written < capacity; ++i) {
+    float ms = 0.f;
+    if (cudaEventElapsedTime(&ms, p.start[i], p.stop[i]) != cudaSuccess) continue;
+    if (out) {
+      out[written].kind = p.kind[i];
+      out[written].ms = ms;
+      out[written].work = p.work[i];
+    }
+    ++written;
+  }
+  if (count) *count = written;
+  return CDL_OK;
+}
 
 const char* cdl_b200_last_error(void) { return cdl::last_error().c_str(); }
 

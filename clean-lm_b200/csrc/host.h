@@ -48,4 +48,18 @@ int32_t encode_tmap(CUtensorMap* out, const void* base, int32_t dtype, int rank,
                     const uint64_t* dims, const uint64_t* strides_bytes, const uint32_t* box,
                     bool swizzle128);
 
+// Opt-in per-launch timing (cdl_b200_profile_start / _stop).  When enabled, a launcher brackets
+// its kernel with two pre-created CUDA events on the launching stream; when disabled the scope
+// costs one relaxed atomic load.
+enum ProfileKind { PROF_GEMM = 1, PROF_NORM_FWD = 2, PROF_NORM_BWD = 3, PROF_ATTN_FWD = 4,
+                   PROF_ATTN_BWD = 5, PROF_ELEMENTWISE = 6 };
+class ProfileScope {
+ public:
+  ProfileScope(int kind, double work, cudaStream_t stream);
+  ~ProfileScope();
+ private:
+  int index_;
+  cudaStream_t stream_;
+};
+
 }  // namespace cdl

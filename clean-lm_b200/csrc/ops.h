@@ -1,0 +1,60 @@
+// Internal C++ entry points of the operators (one per exec-graph node of the reference); the
+// extern "C" functions and the sky-1 block are thin layers over these.
+#pragma once
+#include "host.h"
+
+namespace cdl {
+
+int32_t matmul_execute(const cdl_tensor* a, const cdl_tensor* b, const cdl_tensor* c,
+                       const cdl_tensor* d, float alpha, float beta, cudaStream_t stream);
+int32_t rmsnorm_fwd_execute(const cdl_tensor* x, const cdl_tensor* scale, const cdl_tensor* bias,
+                            float eps, const cdl_tensor* y, const cdl_tensor* r_inv,
+                            cudaStream_t stream);
+size_t rmsnorm_bwd_scratch_bytes(long long rows, long long cols);
+int32_t rmsnorm_bwd_execute(const cdl_tensor* x, const cdl_tensor* dy, const cdl_tensor* res,
+                            const cdl_tensor* scale, const cdl_tensor* r_inv, const cdl_tensor* dx,
+                            const cdl_tensor* dscale, void* scratch, size_t scratch_bytes,
+                            cudaStream_t stream);
+int32_t attn_fwd_execute(const cdl_attn_desc* desc, const cdl_tensor* q, const cdl_tensor* k,
+                         const cdl_tensor* v, const cdl_tensor* o, const cdl_tensor* lse,
+                         cudaStream_t stream);
+size_t attn_bwd_scratch_bytes(long long B, long long Sq, long long H);
+int32_t attn_bwd_execute(const cdl_attn_desc* desc, const cdl_tensor* q, const cdl_tensor* k,
+                         const cdl_tensor* v, const cdl_tensor* o, const cdl_tensor* d_o,
+                         const cdl_tensor* lse, const cdl_tensor* dq, const cdl_tensor* dk,
+                         const cdl_tensor* dv, void* scratch, size_t scratch_bytes,
+                         cudaStream_t stream);
+int32_t rope_execute(const cdl_tensor* x, const cdl_tensor* cos_sin, int32_t rot_heads,
+                     int32_t seqlen, int32_t backward, cudaStream_t stream);
+int32_t swiglu_fwd_execute(const cdl_tensor* gate, const cdl_tensor* up, const cdl_tensor* act,
+                           cudaStream_t stream);
+int32_t swiglu_bwd_execute(const cdl_tensor* d_act, const cdl_tensor* gate, const cdl_tensor* up,
+                           const cdl_tensor* d_gate, const cdl_tensor* d_up, cudaStream_t stream);
+
+// Packed row-major views.
+inline cdl_tensor view2(const void* p, int32_t dt, long long r, long long c) {
+  cdl_tensor t{};
+  t.ptr = const_cast<void*>(p);
+  t.dtype = dt;
+  t.rank = 2;
+  t.shape[0] = r; t.shape[1] = c;
+  t.stride[0] = c; t.stride[1] = 1;
+  return t;
+}
+inline cdl_tensor view1(const void* p, int32_t dt, long long n) {
+  cdl_tensor t{};
+  t.ptr = const_cast<void*>(p);
+  t.dtype = dt;
+  t.rank = 1;
+  t.shape[0] = n;
+  t.stride[0] = 1;
+  return t;
+}
+inline cdl_tensor transposed(const cdl_tensor& t) {
+  cdl_tensor o = t;
+  o.shape[0] = t.shape[1]; o.shape[1] = t.shape[0];
+  o.stride[0] = t.stride[1]; o.stride[1] = t.stride[0];
+  return o;
+}
+
+}  // namespace cdl

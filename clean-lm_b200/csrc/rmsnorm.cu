@@ -309,6 +309,7 @@ int32_t rmsnorm_fwd_execute(const cdl_tensor* x, const cdl_tensor* scale, const 
   if (rows == 0 || cols == 0) return CDL_OK;
   if (rows > INT32_MAX) return fail(CDL_ERR_UNSUPPORTED, "%s: too many rows", op);
   const int r = static_cast<int>(rows), c = static_cast<int>(cols);
+  ProfileScope ps(PROF_NORM_FWD, 4.0 * rows * cols + 2.0 * cols + (r_inv ? 4.0 * rows : 0.0), stream);
   if (c <= 256) launch_fwd<1>(x, scale, bias, eps, y, r_inv, r, c, stream);
   else if (c <= 512) launch_fwd<2>(x, scale, bias, eps, y, r_inv, r, c, stream);
   else if (c <= 1024) launch_fwd<4>(x, scale, bias, eps, y, r_inv, r, c, stream);
@@ -358,6 +359,7 @@ int32_t rmsnorm_bwd_execute(const cdl_tensor* x, const cdl_tensor* dy, const cdl
   const int need = (r + warps - 1) / warps;
   if (grid > need) grid = need;
   int num_partials = grid;
+  ProfileScope ps(PROF_NORM_BWD, (res ? 8.0 : 6.0) * rows * cols + 6.0 * cols + 4.0 * rows, stream);
   if (c <= 256) launch_bwd<1, true>(x, dy, res, scale, r_inv, dx, partials, grid, r, c, stream);
   else if (c <= 512) launch_bwd<2, true>(x, dy, res, scale, r_inv, dx, partials, grid, r, c, stream);
   else if (c <= 1024) launch_bwd<4, true>(x, dy, res, scale, r_inv, dx, partials, grid, r, c, stream);

@@ -58,6 +58,20 @@ int32_t cdl_b200_device_ok(int32_t device);
  * SYNCHRONISES the device.  Test / debugging aid, not part of the hot path. */
 int32_t cdl_b200_device_status(int32_t* status_out);
 
+/* Opt-in per-launch timing, the counterpart of the CUDA-event timing inside the reference's tuner
+ * (crates/cleandl/src/execgraph/tune.rs:219-255).  After _start, every kernel launch of the
+ * operators below is bracketed by two CUDA events on its stream (events are created inside _start,
+ * never on the hot path).  _stop SYNCHRONISES the device and returns one record per launch in
+ * launch order: kind 1 = GEMM, 2 / 3 = RMSNorm fwd / bwd, 4 / 5 = attention fwd / bwd,
+ * 6 = elementwise; work = algorithmic FLOP (kinds 1, 4, 5) or bytes (others). */
+typedef struct {
+  int32_t kind;
+  float ms;
+  double work;
+} cdl_profile_record;
+int32_t cdl_b200_profile_start(int32_t max_records);
+int32_t cdl_b200_profile_stop(cdl_profile_record* out, int32_t capacity, int32_t* count);
+
 /* ---- Matmul: D = alpha * A . B + beta * C ----------------------------------------------
  * Replaces MatmulExecutor::execute (crates/cleandl/src/execgraph/ops/matmul.rs:1092-1183),
  * which forwards to cuBLASLt.  A is [M,K] or [batch,M,K]; B is [K,N] or [batch,K,N]; C
@@ -123,6 +137,81 @@ int32_t cdl_b200_attn_bwd(const cdl_attn_desc* desc, const cdl_tensor* q, const 
                           cdl_stream stream);
 int32_t cdl_b200_attn_bwd_scratch_bytes(const cdl_tensor* q, const cdl_tensor* k,
                                         size_t* bytes_out);
+
+/* ---- Elementwise glue of the sky-1 block -----------------------------------------------
+ * The reference's kernels for these lived in its legacy `cleandl::operators` module, which is
+ * absent from its tree; the call sites are crates/sky-1/src/training/model/decoder.rs:363-378
+ * and :645-655 (RoPE forward / backward on the q and k heads of the fused qkv tensor) and
+ * :487-496, :548-558 (SwiGLU).  The SiLU / dSiLU formulas are those of the reference's fused
+ * GEMM epilogues (crates/cleandl/rust-kernels/src/sky_matmul/tcgen05_bf16.rs:851-877). */
+
+/* Rotate-half RoPE in place on heads [0, rot_heads) of x bf16 [tokens, heads, head_dim];
+ * cos_sin f32 [>= seqlen, head_dim] holds cos | sin per position; position = token % seqlen;
+ * backward != 0 applies the inverse rotation (the gradient). */
+int32_t cdl_b200_rope(const cdl_tensor* x, const cdl_tensor* cos_sin, int32_t rot_heads,
+                      int32_t seqlen, int32_t backward, cdl_stream stream);
+/* act = SiLU(gate) * up, packed bf16 tensors of equal size. */
+int32_t cdl_b200_swiglu_fwd(const cdl_tensor* gate, const cdl_tensor* up, const cdl_tensor* act,
+                            cdl_stream stream);
+/* d_up = d_act * SiLU(gate);  d_gate = d_act * up * dSiLU(gate).  d_up may alias d_act. */
+int32_t cdl_b200_swiglu_bwd(const cdl_tensor* d_act, const cdl_tensor* gate, const cdl_tensor* up,
+                            const cdl_tensor* d_gate, const cdl_tensor* d_up, cdl_stream stream);
+
+/* out[t, :] = table[tokens[t], :]; tokens i32 [T], table bf16 [vocab, hidden], out bf16 [T, hidden].
+ * Call site: crates/sky-1/src/training/model/mod.rs:221-226 (embedding lookup). */
+int32_t cdl_b200_embedding_fwd(const cdl_tensor* tokens, const cdl_tensor* table,
+                               const cdl_tensor* out, cdl_stream stream);
+
+/* ---- sky-1 decoder block ---------------------------------------------------------------
+ * One call per direction for the dataflow of DecoderExecutor::train_forward / train_backward
+ * (crates/sky-1/src/training/model/decoder.rs:332-520, 523-695): pre-RMSNorm, fused QKV
+ * projection, RoPE, causal attention, output projection with fused residual, pre-RMSNorm,
+ * SwiGLU FFN with fused residual.  All tensors are packed row-major device buffers; tokens
+ * T = batch * seqlen.  Weights are bf16 stored [in, out] (decoder.rs:166-173); gradients are
+ * f32 and ACCUMULATED (parameter.rs:69-74).  head_dim must be 128. */
+typedef struct {
+  int32_t batch, seqlen, hidden, heads, kv_heads, head_dim, ffn;
+  float eps;
+} cdl_sky1_config;
+typedef struct { /* bf16 */
+  const void* norm1; /* [hidden] */
+  const void* wqkv;  /* [hidden, (heads + 2 kv_heads) head_dim] */
+  const void* wo;    /* [heads head_dim, hidden] */
+  const void* norm2; /* [hidden] */
+  const void* wup;   /* [hidden, ffn] */
+  const void* wgate; /* [hidden, ffn] */
+  const void* wdown; /* [ffn, hidden] */
+} cdl_sky1_weights;
+typedef struct { /* f32, same shapes as the weights */
+  float *norm1, *wqkv, *wo, *norm2, *wup, *wgate, *wdown;
+} cdl_sky1_grads;
+typedef struct { /* activations the forward saves for the backward (decoder.rs:506-519) */
+  void* qkv;  /* bf16 [T, (heads + 2 kv_heads) head_dim], after RoPE */
+  void* attn; /* bf16 [T, heads head_dim] */
+  float* lse; /* f32 [batch, heads, seqlen] */
+  void* o;    /* bf16 [T, hidden]: attention output projection + residual */
+  void* up;   /* bf16 [T, ffn] */
+  void* gate; /* bf16 [T, ffn] */
+  void* act;  /* bf16 [T, ffn] */
+} cdl_sky1_saved;
+
+int32_t cdl_b200_sky1_block_workspace_bytes(const cdl_sky1_config* cfg, size_t* fwd_bytes,
+                                            size_t* bwd_bytes);
+/* x, out: bf16 [T, hidden]; rope_cos_sin: f32 [seqlen, head_dim]; workspace 256-byte aligned. */
+int32_t cdl_b200_sky1_block_fwd(const cdl_sky1_config* cfg, const cdl_sky1_weights* weights,
+                                const void* x, const float* rope_cos_sin,
+                                const cdl_sky1_saved* saved, void* out, void* workspace,
+                                size_t workspace_bytes, cdl_stream stream);
+/* dy: gradient of out; dx: gradient of x (both bf16 [T, hidden]).  `phase` lets a data-parallel
+ * caller start reducing the FFN gradients while the attention half still runs: 0 = whole
+ * backward; 1 = FFN half only (after it, grads wdown / wup / wgate / norm2 are final and the
+ * workspace holds the intermediate gradient); 2 = attention half (must follow phase 1 with the
+ * same workspace, untouched in between). */
+int32_t cdl_b200_sky1_block_bwd(const cdl_sky1_config* cfg, const cdl_sky1_weights* weights,
+                                const void* x, const float* rope_cos_sin,
+                                const cdl_sky1_saved* saved, const void* dy,
+                                const cdl_sky1_grads* grads, void* dx, void* workspace,
+                                size_t workspace_bytes, int32_t phase, cdl_stream stream);
 
 #ifdef __cplusplus
 }

@@ -1,0 +1,103 @@
+"""GPU parity of the sky-1 decoder block (forward + backward) against the float64 restatement of
+the reference's dataflow (oracle/block_ref.py), on reduced dimensions the CPU finishes in seconds,
+and of the elementwise kernels it uses.  Bound: BASELINE's 2e-2 of the largest magnitude for bf16
+tensors produced by chains of bf16 GEMMs; gradients likewise."""
+import numpy as np
+import pytest
+import torch
+
+from helpers import to_f32
+from oracle import block_ref
+
+pytestmark = pytest.mark.gpu
+
+
+def rel_err(got, ref):
+    ref = ref.double().cpu()
+    return ((got.double().cpu() - ref).abs().max() / ref.abs().max().clamp_min(1e-12)).item()
+
+
+def test_rope_forward_backward(cdl, gpu_ok):
+    L = cdl._lib
+    gen = torch.Generator().manual_seed(0)
+    b, s, heads, d = 2, 96, 6, 128
+    x = torch.randn(b * s, heads, d, generator=gen).to(torch.bfloat16)
+    table = block_ref.rope_table(s, d)
+    for backward in (0, 1):
+        dev = x.cuda().clone()
+        tx, tt = L.tensor_arg(dev), L.tensor_arg(table.cuda())
+        L.check(L.lib.cdl_b200_rope(L.ref(tx), L.ref(tt), 4, s, backward, None))
+        torch.cuda.synchronize()
+        t = table.double() if backward == 0 else torch.cat([table[:, :64], -table[:, 64:]], 1).double()
+        ref = block_ref.rope(x.double().view(b, s, heads, d)[:, :, :4], t).reshape(b * s, 4, d)
+        assert rel_err(dev[:, :4], ref) <= 2.0 ** -7
+        assert torch.equal(dev[:, 4:].cpu(), x[:, 4:])  # heads beyond rot_heads are untouched
+
+
+def test_swiglu_forward_backward(cdl, gpu_ok):
+    L = cdl._lib
+    gen = torch.Generator().manual_seed(1)
+    n = (257, 264)
+    gate, up, dact = (torch.randn(n, generator=gen).to(torch.bfloat16) for _ in range(3))
+    g, u, da = gate.cuda(), up.cuda(), dact.cuda()
+    act = torch.empty_like(g)
+    args = [L.tensor_arg(t) for t in (g, u, act)]
+    L.check(L.lib.cdl_b200_swiglu_fwd(*(L.ref(a) for a in args), None))
+    gd, ud = gate.double().requires_grad_(True), up.double().requires_grad_(True)
+    ref = torch.nn.functional.silu(gd) * ud
+    ref.backward(dact.double())
+    torch.cuda.synchronize()
+    assert rel_err(act, ref.detach()) <= 2.0 ** -7
+    dg, du = torch.empty_like(g), torch.empty_like(g)
+    args = [L.tensor_arg(t) for t in (da, g, u, dg, du)]
+    L.check(L.lib.cdl_b200_swiglu_bwd(*(L.ref(a) for a in args), None))
+    torch.cuda.synchronize()
+    assert rel_err(dg, gd.grad) <= 2.0 ** -7 and rel_err(du, ud.grad) <= 2.0 ** -7
+
+
+@pytest.mark.parametrize("dims", [
+    dict(batch=2, seqlen=256, hidden=256, heads=2, kv_heads=2, head_dim=128, ffn=512),
+    dict(batch=1, seqlen=200, hidden=384, heads=4, kv_heads=2, head_dim=128, ffn=264),
+])
+def test_block_forward_backward_vs_oracle(cdl, gpu_ok, dims):
+    sky1 = cdl.sky1
+    cfg = sky1.Sky1Config(**dims)
+    params = sky1.init_params(cfg, seed=3, std=0.05)
+    gen = torch.Generator().manual_seed(3)
+    params["norm1"] = (1 + 0.1 * torch.randn(cfg.hidden, generator=gen)).to(torch.bfloat16)
+    params["norm2"] = (1 + 0.1 * torch.randn(cfg.hidden, generator=gen)).to(torch.bfloat16)
+    x = torch.randn(cfg.tokens, cfg.hidden, generator=gen).to(torch.bfloat16)
+    dy = torch.randn(cfg.tokens, cfg.hidden, generator=gen).to(torch.bfloat16)
+    blk = sky1.Sky1Block(cfg, params)
+    g0 = {n: torch.randn(g.shape, generator=gen) * 0.5 for n, g in blk.grads.items()}
+    for n, g in blk.grads.items():
+        g.copy_(g0[n])
+    out = blk.forward(x.cuda())
+    dx = blk.backward(dy.cuda())
+    torch.cuda.synchronize()
+
+    c = dict(heads=cfg.heads, kv_heads=cfg.kv_heads, head_dim=cfg.head_dim, eps=cfg.eps)
+    table = block_ref.rope_table(cfg.seqlen, cfg.head_dim)
+    shape3 = (cfg.batch, cfg.seqlen, cfg.hidden)
+    out_ref, dx_ref, g_ref = block_ref.block_forward_backward(
+        x.view(shape3), params, dy.view(shape3), c, table)
+    assert rel_err(out, out_ref.reshape(cfg.tokens, -1)) <= 2e-2
+    assert rel_err(dx, dx_ref.reshape(cfg.tokens, -1)) <= 2e-2
+    for n in sky1.PARAM_NAMES:
+        # gradients are accumulated on top of the buffers' previous contents
+        got = blk.grads[n].double().cpu() - g0[n].double()
+        err = ((got - g_ref[n]).abs().max() / g_ref[n].abs().max()).item()
+        assert err <= 2e-2, (n, err)
+
+
+def test_block_rejects_bad_arguments(cdl, gpu_ok):
+    sky1 = cdl.sky1
+    cfg = sky1.Sky1Config(batch=1, seqlen=128, hidden=256, heads=2, kv_heads=2, head_dim=64, ffn=256)
+    with pytest.raises(cdl._lib.CdlError, match="head_dim"):
+        sky1.Sky1Block(cfg, sky1.init_params(cfg, 0))
+    cfg = sky1.Sky1Config(batch=1, seqlen=128, hidden=256, heads=2, kv_heads=2, head_dim=128, ffn=256)
+    blk = sky1.Sky1Block(cfg, sky1.init_params(cfg, 0))
+    with pytest.raises(cdl._lib.CdlError, match="contiguous bf16"):
+        blk.forward(torch.zeros(cfg.tokens, cfg.hidden, device="cuda"))
+    with pytest.raises(cdl._lib.CdlError, match="before forward"):
+        blk.backward(torch.zeros(cfg.tokens, cfg.hidden, device="cuda", dtype=torch.bfloat16))
