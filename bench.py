@@ -108,10 +108,11 @@ class ClockSampler:
     def __init__(self, index: int):
         self.samples = []
         self.proc = None
+        self.t_begin = None  # samples read before mark() are dropped
         try:
             self.proc = subprocess.Popen(
                 ["nvidia-smi", f"--query-gpu={self.FIELDS}", "--format=csv,noheader,nounits",
-                 "-lms", "100", "-i", str(index)], stdout=subprocess.PIPE, stderr=subprocess.DEVNULL,
+                 "-lms", "20", "-i", str(index)], stdout=subprocess.PIPE, stderr=subprocess.DEVNULL,
                 text=True)
             self.thread = threading.Thread(target=self._read, daemon=True)
             self.thread.start()
@@ -121,8 +122,12 @@ class ClockSampler:
     def _read(self):
         for line in self.proc.stdout:
             parts = [p.strip() for p in line.split(",")]
-            if len(parts) == 6 and parts[0].isdigit():
+            if len(parts) == 6 and parts[0].isdigit() and self.t_begin is not None:
                 self.samples.append(parts)
+
+    def mark(self):
+        """Start of the timed region: keep samples from here on."""
+        self.t_begin = time.time()
 
     def stop(self) -> dict:
         if self.proc is None:
@@ -245,10 +250,12 @@ def run_ours(args) -> None:
         reduced.record()
         tokens_dev.copy_(tokens_host[0])
         # ---- device-resident number
+        sampler = ClockSampler(local) if rank == 0 else None
         for _ in range(args.warmup):
             step_resident()
         barrier()
-        sampler = ClockSampler(local) if rank == 0 else None
+        if sampler:
+            sampler.mark()
         L.profile_start(64 * args.steps + 64)
         e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
         e0.record()
@@ -321,13 +328,111 @@ def run_ours(args) -> None:
         dist.destroy_process_group()
 
 
+# ------------------------------------------------------------------ single-kernel mode
+def run_kernel(args) -> None:
+    """Times one operator alone (CUDA events, warm-up, buffers rotated so that every iteration
+    reads data that is not in L2) and prints its achieved rate against the measured roofline.
+    Also the small case the Nsight Compute captures under profiles/ are taken on."""
+    import torch
+
+    import cleanlm_b200 as cdl
+
+    torch.cuda.set_device(0)
+    dev = "cuda"
+    L = cdl._lib
+    peaks = measured_peaks()
+    gen = torch.Generator(device=dev).manual_seed(0)
+    rnd = lambda *shape: torch.randn(*shape, device=dev, generator=gen).to(torch.bfloat16)
+    k = args.kernel
+    if k == "gemm":
+        m, n, kk = args.m, args.n, args.k
+        a = rnd(kk, m).T if args.layout[0] == "t" else rnd(m, kk)
+        b = rnd(n, kk).T if args.layout[1] == "t" else rnd(kk, n)
+        out_dtype = torch.float32 if args.accumulate else torch.bfloat16
+        d = torch.zeros(m, n, device=dev, dtype=out_dtype)
+        opts = cdl.ops.MatmulOpts(out=out_dtype, c=d if args.accumulate else None,
+                                  beta=1.0 if args.accumulate else 0.0)
+        fns = [lambda: cdl.ops.matmul(a, b, opts, out=d)]
+        work, unit, peak = 2.0 * m * n * kk, "TFLOP/s", peaks["bf16_burst"]
+        desc = f"gemm {m}x{n}x{kk} layout {args.layout}" + (" f32 accumulate" if args.accumulate else "")
+    elif k in ("norm_fwd", "norm_bwd"):
+        rows, cols = args.rows, args.cols
+        nbuf = max(2, int(300e6 // (rows * cols * 2)) + 1)
+        xs = [rnd(rows, cols) for _ in range(nbuf)]
+        w = (1 + 0.02 * torch.randn(cols, device=dev, generator=gen)).to(torch.bfloat16)
+        if k == "norm_fwd":
+            o = cdl.ops.NormFwdOpts(scale=w, save_stats=True)
+            fns = [(lambda x=x: cdl.ops.norm_fwd(x, o)) for x in xs]
+            work = 4.0 * rows * cols + 2 * cols + 4 * rows
+        else:
+            dys = [rnd(rows, cols) for _ in range(nbuf)]
+            r_inv = cdl.ops.norm_fwd(xs[0], cdl.ops.NormFwdOpts(scale=w, save_stats=True)).r_inv
+            ds = torch.zeros(cols, device=dev)
+            scr = torch.empty(cdl.ops.norm_bwd_scratch_bytes(rows, cols), dtype=torch.uint8, device=dev)
+            fns = [(lambda x=x, dy=dy: cdl.ops.norm_bwd(x, dy, w, r_inv, ds, scratch=scr))
+                   for x, dy in zip(xs, dys)]
+            work = 6.0 * rows * cols + 6 * cols + 4 * rows
+        unit, peak = "GB/s", peaks["hbm"]
+        desc = f"{k} x[{rows},{cols}] bf16"
+    else:
+        bsz, s_, h = args.batch, args.seq, args.heads
+        q, kx, v, do = (rnd(bsz, s_, h, 128) for _ in range(4))
+        fwd = cdl.ops.attention_fwd(q, kx, v)
+        if k == "attn_fwd":
+            fns = [lambda: cdl.ops.attention_fwd(q, kx, v)]
+            work = 4.0 * bsz * h * s_ * s_ * 128 / 2
+        else:
+            scr = torch.empty(cdl.ops.attention_bwd_scratch_bytes(q, kx), dtype=torch.uint8, device=dev)
+            dq, dk, dv = (torch.empty_like(q) for _ in range(3))
+            fns = [lambda: cdl.ops.attention_bwd(q, kx, v, fwd.out, do, fwd.lse, scratch=scr,
+                                                 dq=dq, dk=dk, dv=dv)]
+            work = 10.0 * bsz * h * s_ * s_ * 128 / 2
+        unit, peak = "TFLOP/s", peaks["bf16_burst"]
+        desc = f"{k} causal B={bsz} H={h} S={s_} D=128"
+    for i in range(args.warmup):
+        fns[i % len(fns)]()
+    torch.cuda.synchronize()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for i in range(args.steps):
+        fns[i % len(fns)]()
+    e1.record()
+    torch.cuda.synchronize()
+    ms = e0.elapsed_time(e1) / args.steps
+    assert L.device_status() == 0
+    achieved = work / (ms * 1e-3) / (1e12 if unit == "TFLOP/s" else 1e9)
+    print(json.dumps({"kernel": k, "case": desc, "ms": ms, "achieved": achieved, "unit": unit,
+                      "peak": peak, "frac": achieved / peak,
+                      "peak_source": peaks["source"] + (" burst cuBLAS bf16" if unit == "TFLOP/s"
+                                                        else " copy bandwidth"),
+                      "steps": args.steps, "warmup": args.warmup}))
+
+
 def main() -> None:
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
     ap.add_argument("--steps", type=int, default=20)
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--kernel", default=None,
+                    choices=["gemm", "norm_fwd", "norm_bwd", "attn_fwd", "attn_bwd"],
+                    help="time one operator alone instead of the block")
+    ap.add_argument("--m", type=int, default=8192)
+    ap.add_argument("--n", type=int, default=8192)
+    ap.add_argument("--k", type=int, default=8192)
+    ap.add_argument("--layout", default="nn", choices=["nn", "nt", "tn", "tt"],
+                    help="gemm: n = row-major operand, t = transposed view (A then B)")
+    ap.add_argument("--accumulate", action="store_true", help="gemm: D (f32) += A.B, the wgrad form")
+    ap.add_argument("--rows", type=int, default=16384)
+    ap.add_argument("--cols", type=int, default=2048)
+    ap.add_argument("--batch", type=int, default=8)
+    ap.add_argument("--seq", type=int, default=2048)
+    ap.add_argument("--heads", type=int, default=16)
     args = ap.parse_args()
+    if args.kernel:
+        args.warmup = max(args.warmup, 3)
+        run_kernel(args)
+        return
     if args.warmup < 3 and args.impl == "ours":
         args.warmup = 3
     if args.impl == "reference":
