@@ -16,6 +16,8 @@
 #include "host.h"
 #include "ptx.cuh"
 
+#include <mutex>
+
 namespace cdl {
 namespace norm {
 
@@ -381,6 +383,57 @@ int32_t rmsnorm_bwd_execute(const cdl_tensor* x, const cdl_tensor* dy, const cdl
   return CDL_OK;
 }
 
+
+// ---------------------------------------------------------------- allocation-free backward
+// Scratch for cdl_b200_rmsnorm_bwd_static: one fixed array in the module's global memory, so a
+// caller that is not allowed to allocate (or to be handed) device scratch can still run the
+// backward.  8 MiB = 1024 partial rows x 2048 columns of f32; held by every device that loads
+// the library until the process exits.
+namespace norm {
+constexpr long long STATIC_MAX_COLS = 2048;
+constexpr size_t STATIC_SCRATCH_FLOATS = static_cast<size_t>(MAX_PARTIALS) * STATIC_MAX_COLS;
+static __device__ __align__(256) float g_static_partials[STATIC_SCRATCH_FLOATS];
+}  // namespace norm
+
+int32_t rmsnorm_bwd_static_execute(const cdl_tensor* x, const cdl_tensor* dy, const cdl_tensor* res,
+                                   const cdl_tensor* scale, const cdl_tensor* r_inv,
+                                   const cdl_tensor* dx, const cdl_tensor* dscale,
+                                   cudaStream_t stream) {
+  const char* op = "norm_bwd_static";
+  if (!x || x->rank != 2) return fail(CDL_ERR_INVALID, "%s: x must be a 2D tensor", op);
+  if (x->shape[1] > norm::STATIC_MAX_COLS)
+    return fail(CDL_ERR_UNSUPPORTED,
+                "%s: cols = %lld exceeds the built-in scratch (at most %lld columns); use "
+                "cdl_b200_rmsnorm_bwd with caller-provided scratch instead",
+                op, (long long)x->shape[1], norm::STATIC_MAX_COLS);
+  // In host code the array's name is only a handle; the kernels need its device address, which
+  // differs per device.  Resolve it once per device, with that device current.
+  static float* addr[64] = {};
+  static std::mutex mu;
+  int dev = 0;
+  CDL_CUDA(cudaGetDevice(&dev));
+  if (dev < 0 || dev >= 64) return fail(CDL_ERR_UNSUPPORTED, "%s: device index %d out of range", op, dev);
+  float* scratch = nullptr;
+  {
+    std::lock_guard<std::mutex> lock(mu);
+    if (!addr[dev]) {
+      void* p = nullptr;
+      cudaError_t e = cudaGetSymbolAddress(&p, norm::g_static_partials);
+      if (e != cudaSuccess || p == nullptr)
+        return fail(CDL_ERR_CUDA, "%s: cudaGetSymbolAddress failed: %s", op, cudaGetErrorString(e));
+      addr[dev] = static_cast<float*>(p);
+    }
+    scratch = addr[dev];
+  }
+  const size_t bytes = norm::STATIC_SCRATCH_FLOATS * sizeof(float);
+  if (rmsnorm_bwd_scratch_bytes(x->shape[0], x->shape[1]) > bytes)
+    return fail(CDL_ERR_UNSUPPORTED, "%s: problem needs more than the built-in %zu bytes of scratch",
+                op, bytes);
+  // Every partial row that is read is written first by the same call, so the array needs no
+  // clearing between calls.
+  return rmsnorm_bwd_execute(x, dy, res, scale, r_inv, dx, dscale, scratch, bytes, stream);
+}
+
 }  // namespace cdl
 
 extern "C" {
@@ -399,6 +452,14 @@ int32_t cdl_b200_rmsnorm_bwd(const cdl_tensor* x, const cdl_tensor* dy,
                              cdl_stream stream) {
   return cdl::rmsnorm_bwd_execute(x, dy, residual_dy, scale, r_inv, dx, dscale, scratch,
                                   scratch_bytes, static_cast<cudaStream_t>(stream));
+}
+
+int32_t cdl_b200_rmsnorm_bwd_static(const cdl_tensor* x, const cdl_tensor* dy,
+                                    const cdl_tensor* residual_dy, const cdl_tensor* scale,
+                                    const cdl_tensor* r_inv, const cdl_tensor* dx,
+                                    const cdl_tensor* dscale, cdl_stream stream) {
+  return cdl::rmsnorm_bwd_static_execute(x, dy, residual_dy, scale, r_inv, dx, dscale,
+                                         static_cast<cudaStream_t>(stream));
 }
 
 int32_t cdl_b200_rmsnorm_bwd_scratch_bytes(int64_t rows, int64_t cols, size_t* bytes_out) {

@@ -113,6 +113,27 @@ int32_t cdl_b200_rmsnorm_bwd(const cdl_tensor* x, const cdl_tensor* dy,
                              cdl_stream stream);
 int32_t cdl_b200_rmsnorm_bwd_scratch_bytes(int64_t rows, int64_t cols, size_t* bytes_out);
 
+/* RMSNorm backward for callers that cannot supply scratch.  (No counterpart in the reference: its
+ * engine always hands an executor a scratch slice.)  Some hosts of this library may not allocate
+ * device memory at the point where they need the backward — code running inside a memory-pool
+ * callback, a real-time loop with a fixed memory budget, a plugin whose host owns every
+ * allocation — and have no scratch slice to lend either.  This variant takes the same operands as
+ * cdl_b200_rmsnorm_bwd minus the scratch and uses an 8 MiB array that lives inside the library's
+ * device image instead (every GPU that loads the library holds those 8 MiB until exit).  Limits
+ * and rules:
+ *   - cols <= 2048 (what the built-in array can hold); larger problems return
+ *     CDL_ERR_UNSUPPORTED and should use cdl_b200_rmsnorm_bwd;
+ *   - it calls no cudaMalloc / cudaFree or any other allocating routine;
+ *   - the first call on each device looks up the array's device address (once, under a lock);
+ *     make that first call before starting any stream capture;
+ *   - all calls on a device share the one array: calls that may overlap on the GPU (different
+ *     streams) race on it and must be serialised by the caller.  Nothing needs clearing between
+ *     calls, each call overwrites what it later reads. */
+int32_t cdl_b200_rmsnorm_bwd_static(const cdl_tensor* x, const cdl_tensor* dy,
+                                    const cdl_tensor* residual_dy, const cdl_tensor* scale,
+                                    const cdl_tensor* r_inv, const cdl_tensor* dx,
+                                    const cdl_tensor* dscale, cdl_stream stream);
+
 /* ---- Flash attention -------------------------------------------------------------------
  * Replaces AttentionExecutor::execute (crates/cleandl/src/execgraph/ops/attention/exec.rs:
  * 358-416), which forwards to flash-attention-rs.  Dense layout only: q [B,Sq,H,D], k and v
