@@ -36,6 +36,12 @@ class CdlProfileRecord(ctypes.Structure):
     _fields_ = [("kind", ctypes.c_int32), ("ms", ctypes.c_float), ("work", ctypes.c_double)]
 
 
+class CdlAdamwParams(ctypes.Structure):
+    _fields_ = [("lr", ctypes.c_float), ("beta1", ctypes.c_float), ("beta2", ctypes.c_float),
+                ("eps", ctypes.c_float), ("weight_decay", ctypes.c_float), ("step", ctypes.c_int32),
+                ("grad_scale", ctypes.c_float), ("max_grad_norm", ctypes.c_float)]
+
+
 class CdlSky1Config(ctypes.Structure):
     _fields_ = [(n, ctypes.c_int32) for n in
                 ("batch", "seqlen", "hidden", "heads", "kv_heads", "head_dim", "ffn")] + [
@@ -93,6 +99,12 @@ SIGNATURES = {
     "cdl_b200_rope": ([_T, _T, ctypes.c_int32, ctypes.c_int32, ctypes.c_int32, _vp], ctypes.c_int32),
     "cdl_b200_swiglu_fwd": ([_T, _T, _T, _vp], ctypes.c_int32),
     "cdl_b200_swiglu_bwd": ([_T, _T, _T, _T, _T, _vp], ctypes.c_int32),
+    "cdl_b200_cross_entropy": ([_T, _T, _T, ctypes.c_float, _vp], ctypes.c_int32),
+    "cdl_b200_embedding_bwd": ([_T, _T, _T, _vp], ctypes.c_int32),
+    "cdl_b200_sum": ([_vp, ctypes.c_int64, _vp, ctypes.c_float, ctypes.c_int32, ctypes.c_int32, _vp,
+                      _sz, _vp], ctypes.c_int32),
+    "cdl_b200_adamw": ([_vp, _vp, _vp, _vp, _vp, ctypes.c_int64, _vp,
+                        ctypes.POINTER(CdlAdamwParams), _vp], ctypes.c_int32),
     "cdl_b200_sky1_block_workspace_bytes": ([ctypes.POINTER(CdlSky1Config), ctypes.POINTER(_sz),
                                              ctypes.POINTER(_sz)], ctypes.c_int32),
     "cdl_b200_sky1_block_fwd": ([ctypes.POINTER(CdlSky1Config), ctypes.POINTER(CdlSky1Weights), _vp,

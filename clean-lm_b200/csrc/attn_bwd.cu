@@ -85,7 +85,8 @@ __device__ __forceinline__ void compute_bar_sync() {
 }
 
 // ---------------------------------------------------------------- preprocess
-// One warp per (b, h, padded row): delta = sum_d dO * O, lse2 = lse * log2(e).
+// Half a warp per (b, h, padded row): 16 lanes x 8 bf16 = one 256-byte row of O and of dO.
+// delta = sum_d dO * O, lse2 = lse * log2(e).
 __global__ void __launch_bounds__(256)
     attn_bwd_preprocess_kernel(const __nv_bfloat16* __restrict__ o, long long o_sb, long long o_ss,
                                long long o_sh, const __nv_bfloat16* __restrict__ d_o,
@@ -93,27 +94,33 @@ __global__ void __launch_bounds__(256)
                                const float* __restrict__ lse, long long lse_sb, long long lse_sh,
                                long long lse_ss, float* __restrict__ lse2,
                                float* __restrict__ delta, int B, int H, int Sq, int Sq_pad) {
-  const long long warp_global = (static_cast<long long>(blockIdx.x) * 256 + threadIdx.x) >> 5;
-  const int lane = threadIdx.x & 31;
+  const long long item = (static_cast<long long>(blockIdx.x) * 256 + threadIdx.x) >> 4;
+  const int sub = threadIdx.x & 15;
   const long long total = static_cast<long long>(B) * H * Sq_pad;
-  if (warp_global >= total) return;
-  const int row = static_cast<int>(warp_global % Sq_pad);
-  const int h = static_cast<int>((warp_global / Sq_pad) % H);
-  const int b = static_cast<int>(warp_global / (static_cast<long long>(Sq_pad) * H));
+  const bool live = item < total;
+  const long long it = live ? item : 0;
+  const int row = static_cast<int>(it % Sq_pad);
+  const int h = static_cast<int>((it / Sq_pad) % H);
+  const int b = static_cast<int>(it / (static_cast<long long>(Sq_pad) * H));
   float dl = 0.f, l2 = INFINITY;
-  if (row < Sq) {
-    const uint2 vo = *reinterpret_cast<const uint2*>(o + b * o_sb + row * o_ss + h * o_sh + lane * 4);
-    const uint2 vd = *reinterpret_cast<const uint2*>(d_o + b * do_sb + row * do_ss + h * do_sh + lane * 4);
+  const bool in = live && row < Sq;
+  if (in) {
+    const uint4 vo = ld_nc_v4(o + b * o_sb + row * o_ss + h * o_sh + sub * 8);
+    const uint4 vd = ld_nc_v4(d_o + b * do_sb + row * do_ss + h * do_sh + sub * 8);
     dl = bf16_lo(vo.x) * bf16_lo(vd.x) + bf16_hi(vo.x) * bf16_hi(vd.x) +
-         bf16_lo(vo.y) * bf16_lo(vd.y) + bf16_hi(vo.y) * bf16_hi(vd.y);
+         bf16_lo(vo.y) * bf16_lo(vd.y) + bf16_hi(vo.y) * bf16_hi(vd.y) +
+         bf16_lo(vo.z) * bf16_lo(vd.z) + bf16_hi(vo.z) * bf16_hi(vd.z) +
+         bf16_lo(vo.w) * bf16_lo(vd.w) + bf16_hi(vo.w) * bf16_hi(vd.w);
+  }
 #pragma unroll
-    for (int s = 16; s > 0; s >>= 1) dl += __shfl_xor_sync(0xffffffffu, dl, s);
+  for (int s = 8; s > 0; s >>= 1) dl += __shfl_xor_sync(0xffffffffu, dl, s);
+  if (in && sub == 0) {
     const float l = lse[b * lse_sb + h * lse_sh + row * lse_ss];
     l2 = l == -INFINITY ? INFINITY : l * 1.4426950408889634f;
   }
-  if (lane == 0) {
-    lse2[warp_global] = l2;
-    delta[warp_global] = dl;
+  if (live && sub == 0) {
+    lse2[item] = l2;
+    delta[item] = dl;
   }
 }
 
@@ -528,8 +535,8 @@ int32_t attn_bwd_execute(const cdl_attn_desc* desc, const cdl_tensor* q, const c
   ProfileScope ps(PROF_ATTN_BWD, 10.0 * B * H * Sq * Sk * D * (p.causal ? 0.5 : 1.0), stream);
   if (Sq > 0) {
     CDL_CUDA(cudaMemsetAsync(dq_acc, 0, static_cast<size_t>(B) * Sq * H * D * sizeof(float), stream));
-    const long long warps = B * H * Sq_pad;
-    const unsigned blocks = static_cast<unsigned>((warps * 32 + 255) / 256);
+    const long long items = B * H * Sq_pad;
+    const unsigned blocks = static_cast<unsigned>((items * 16 + 255) / 256);
     attn_bwd_preprocess_kernel<<<blocks, 256, 0, stream>>>(
         static_cast<const __nv_bfloat16*>(o->ptr), o->stride[0], o->stride[1], o->stride[2],
         static_cast<const __nv_bfloat16*>(d_o->ptr), d_o->stride[0], d_o->stride[1], d_o->stride[2],

@@ -218,22 +218,32 @@ __global__ void __launch_bounds__(128)
   partials[static_cast<long long>(blockIdx.y) * cols + col] = acc;
 }
 
-// dscale[j] += sum_b partials[b][j], summed in a fixed order.
+// dscale[j] += sum_b partials[b][j], summed in a fixed order.  A CTA owns 32 columns; its 8
+// warps each sum every 8th partial row (coalesced 128-byte reads), then the 8 sums are folded
+// through shared memory in warp order.
 __global__ void __launch_bounds__(256)
     dscale_finalize_kernel(const float* __restrict__ partials, int num_partials, int cols,
                            float* __restrict__ dscale, long long dscale_stride) {
-  const int col = blockIdx.x * 256 + threadIdx.x;
-  if (col >= cols) return;
-  float s0 = 0.f, s1 = 0.f, s2 = 0.f, s3 = 0.f;
-  int b = 0;
-  for (; b + 4 <= num_partials; b += 4) {
-    s0 += partials[static_cast<long long>(b) * cols + col];
-    s1 += partials[static_cast<long long>(b + 1) * cols + col];
-    s2 += partials[static_cast<long long>(b + 2) * cols + col];
-    s3 += partials[static_cast<long long>(b + 3) * cols + col];
+  __shared__ float s_sum[8][32];
+  const int cx = threadIdx.x & 31, rg = threadIdx.x >> 5;
+  const int col = blockIdx.x * 32 + cx;
+  float s0 = 0.f, s1 = 0.f;
+  if (col < cols) {
+    int b = rg;
+    for (; b + 8 < num_partials; b += 16) {
+      s0 += partials[static_cast<long long>(b) * cols + col];
+      s1 += partials[static_cast<long long>(b + 8) * cols + col];
+    }
+    if (b < num_partials) s0 += partials[static_cast<long long>(b) * cols + col];
   }
-  for (; b < num_partials; ++b) s0 += partials[static_cast<long long>(b) * cols + col];
-  dscale[col * dscale_stride] += (s0 + s1) + (s2 + s3);
+  s_sum[rg][cx] = s0 + s1;
+  __syncthreads();
+  if (rg == 0 && col < cols) {
+    float t = 0.f;
+#pragma unroll
+    for (int w = 0; w < 8; ++w) t += s_sum[w][cx];
+    dscale[col * dscale_stride] += t;
+  }
 }
 
 static int32_t check_rows(const char* op, const char* name, const cdl_tensor* t, long long rows,
@@ -377,7 +387,7 @@ int32_t rmsnorm_bwd_execute(const cdl_tensor* x, const cdl_tensor* dy, const cdl
         static_cast<const float*>(r_inv->ptr), r_inv->stride[0], partials, r, c);
   }
   CDL_CUDA(cudaGetLastError());
-  dscale_finalize_kernel<<<(c + 255) / 256, 256, 0, stream>>>(
+  dscale_finalize_kernel<<<(c + 31) / 32, 256, 0, stream>>>(
       partials, num_partials, c, static_cast<float*>(dscale->ptr), dscale->stride[0]);
   CDL_CUDA(cudaGetLastError());
   return CDL_OK;

@@ -88,8 +88,12 @@ class Sky1Block:
                  workspace: torch.Tensor | None = None, table: torch.Tensor | None = None):
         self.cfg = cfg
         self.device = device
-        self.params = {n: params[n].to(device=device, dtype=torch.bfloat16).contiguous()
-                       for n in PARAM_NAMES}
+        def on_device(p):  # views of a caller-owned flat buffer are used in place, not copied
+            if p.is_cuda and p.dtype == torch.bfloat16 and p.is_contiguous():
+                return p
+            return p.to(device=device, dtype=torch.bfloat16).contiguous()
+
+        self.params = {n: on_device(params[n]) for n in PARAM_NAMES}
         for n, shape in cfg.param_shapes().items():
             if tuple(self.params[n].shape) != tuple(shape):
                 raise _lib.CdlError(-1, f"parameter {n} must have shape {shape}")
@@ -157,3 +161,206 @@ class Sky1Block:
     def zero_grads(self):
         for g in self.grads.values():
             g.zero_()
+
+
+# ======================================================================= full LM training step
+@dataclass
+class Sky1LMConfig:
+    """24-layer sky-1-style LM of BASELINE config 5 by default."""
+
+    block: Sky1Config
+    layers: int = 24
+    vocab: int = 32768
+    lr: float = 3e-4
+    beta1: float = 0.9
+    beta2: float = 0.95
+    adam_eps: float = 1e-8
+    weight_decay: float = 0.1
+    max_grad_norm: float = 0.0  # 0 = no clipping
+
+    def param_count(self) -> int:
+        return self.layers * self.block.param_count() + 2 * self.vocab * self.block.hidden + self.block.hidden
+
+
+_BLOCK_ORDER = ("wdown", "wup", "wgate", "wo", "wqkv", "norm2", "norm1")  # decayed first, gains last
+
+
+class Sky1LM:
+    """Embedding -> blocks -> final RMSNorm -> LM head -> cross-entropy, with the optimizer state.
+
+    Follows the reference's Sky1Executor (crates/sky-1/src/training/model/mod.rs:209-420): f32
+    master weights with bf16 replicas, f32 gradients accumulated over microbatches
+    (crates/sky-1/src/skyred/training.rs:263-317), AdamW without weight decay on norm gains.
+    All parameters live in flat buffers laid out in BACKWARD order (LM head first, embedding
+    last) so a data-parallel run can all-reduce a layer's gradient slice as soon as that layer's
+    backward has been enqueued.
+    """
+
+    def __init__(self, cfg: Sky1LMConfig, seed: int = 4, device="cuda", std: float = 0.02,
+                 process_group=None):
+        import torch.distributed as dist
+
+        self.cfg, self.device = cfg, torch.device(device)
+        b = cfg.block
+        self.world = dist.get_world_size(process_group) if (dist.is_available() and dist.is_initialized()) else 1
+        self.group = process_group
+        layout = [("lm_head", (b.hidden, cfg.vocab), True), ("final_norm", (b.hidden,), False)]
+        for layer in reversed(range(cfg.layers)):
+            for n in _BLOCK_ORDER:
+                layout.append((f"blocks.{layer}.{n}", b.param_shapes()[n], not n.startswith("norm")))
+        layout.append(("embedding", (cfg.vocab, b.hidden), True))
+        self.layout, self.offsets, off = layout, {}, 0
+        for name, shape, _ in layout:
+            self.offsets[name] = (off, math.prod(shape))
+            off += math.prod(shape)
+        self.numel = off
+        f32 = dict(dtype=torch.float32, device=self.device)
+        self.master = torch.empty(off, **f32)
+        self.m = torch.zeros(off, **f32)
+        self.v = torch.zeros(off, **f32)
+        self.grads = torch.zeros(off, **f32)
+        self.replica = torch.empty(off, dtype=torch.bfloat16, device=self.device)
+        gen = torch.Generator().manual_seed(seed)
+        init = {}  # drawn in name order, so the values do not depend on the flat layout
+        for name, shape, _ in sorted(layout, key=lambda t: t[0]):
+            init[name] = (torch.ones(shape) if "norm" in name else torch.randn(shape, generator=gen) * std)
+        for name, shape, _ in layout:
+            o, n = self.offsets[name]
+            self.master[o:o + n].copy_(init[name].reshape(-1))
+        self.replica.copy_(self.master)
+        # contiguous runs with one weight-decay setting -> one AdamW launch each
+        self.segments = []
+        for name, shape, decay in layout:
+            o, n = self.offsets[name]
+            if self.segments and self.segments[-1][2] == decay and self.segments[-1][0] + self.segments[-1][1] == o:
+                self.segments[-1][1] += n
+            else:
+                self.segments.append([o, n, decay])
+        t = b.tokens
+        self.table = rope_table(b.seqlen, b.head_dim, b.rope_base, self.device)
+        self.blocks = []
+        workspace = None
+        for layer in range(cfg.layers):
+            params = {n: self.view("replica", f"blocks.{layer}.{n}") for n in PARAM_NAMES}
+            grads = {n: self.view("grads", f"blocks.{layer}.{n}") for n in PARAM_NAMES}
+            blk = Sky1Block(b, params, device=self.device, grads=grads, workspace=workspace, table=self.table)
+            workspace = blk.workspace
+            self.blocks.append(blk)
+        bf = dict(dtype=torch.bfloat16, device=self.device)
+        self.acts = [torch.empty(t, b.hidden, **bf) for _ in range(cfg.layers + 1)]
+        self.hf = torch.empty(t, b.hidden, **bf)
+        self.r_inv = torch.empty(t, **f32)
+        self.logits = torch.empty(t, cfg.vocab, **bf)
+        self.loss_tok = torch.empty(t, **f32)
+        self.loss = torch.zeros(1, **f32)
+        self.sumsq = torch.zeros(1, **f32)
+        self.dx = [torch.empty(t, b.hidden, **bf) for _ in range(2)]
+        self.red_scratch = torch.empty(4096, dtype=torch.uint8, device=self.device)
+        self.norm_scratch = torch.empty(ops_norm_bwd_scratch(t, b.hidden), dtype=torch.uint8, device=self.device)
+        self.step_count = 0
+        self.comm = torch.cuda.Stream(device=self.device) if self.world > 1 else None
+        self._tokens = None
+
+    def view(self, which: str, name: str) -> torch.Tensor:
+        o, n = self.offsets[name]
+        shape = next(s for nm, s, _ in self.layout if nm == name)
+        return getattr(self, which)[o:o + n].view(shape)
+
+    # ---- one microbatch
+    def forward_backward(self, tokens: torch.Tensor, targets: torch.Tensor, loss_scale: float,
+                         reduce_grads: bool = True) -> None:
+        """tokens, targets: i32 [tokens] on the device.  Adds loss_scale * sum of token losses to
+        self.loss and accumulates gradients of that quantity.  With reduce_grads (the last
+        microbatch of a step) every layer's gradient slice is all-reduced as soon as its backward
+        is enqueued."""
+        from . import ops
+
+        L, c = _lib, self.cfg
+        st = ctypes.c_void_p(torch.cuda.current_stream().cuda_stream)
+        ta = L.tensor_arg
+        tok, tgt = ta(tokens), ta(targets)
+        emb = ta(self.view("replica", "embedding"))
+        x0 = ta(self.acts[0])
+        check(lib.cdl_b200_embedding_fwd(L.ref(tok), L.ref(emb), L.ref(x0), st))
+        for i, blk in enumerate(self.blocks):
+            blk.forward(self.acts[i], self.acts[i + 1])
+        xl, hf, gam, rinv = ta(self.acts[-1]), ta(self.hf), ta(self.view("replica", "final_norm")), ta(self.r_inv)
+        check(lib.cdl_b200_rmsnorm_fwd(L.ref(xl), L.ref(gam), None, c.block.eps, L.ref(hf), L.ref(rinv), st))
+        ops.matmul(self.hf, self.view("replica", "lm_head"), out=self.logits)
+        lg, lt = ta(self.logits), ta(self.loss_tok)
+        check(lib.cdl_b200_cross_entropy(L.ref(lg), L.ref(tgt), L.ref(lt), loss_scale, st))
+        check(lib.cdl_b200_sum(self.loss_tok.data_ptr(), self.loss_tok.numel(), self.loss.data_ptr(),
+                               loss_scale, 0, 1, self.red_scratch.data_ptr(), 4096, st))
+        # backward
+        g_head = self.view("grads", "lm_head")
+        ops.matmul(self.hf.T, self.logits, ops.MatmulOpts(out=torch.float32, c=g_head, beta=1.0), out=g_head)
+        ops.matmul(self.logits, self.view("replica", "lm_head").T, out=self.hf)  # d_hf, in place of hf
+        dgam, dxl = ta(self.view("grads", "final_norm")), ta(self.dx[0])
+        check(lib.cdl_b200_rmsnorm_bwd(L.ref(xl), L.ref(hf), None, L.ref(gam), L.ref(rinv), L.ref(dxl),
+                                       L.ref(dgam), self.norm_scratch.data_ptr(),
+                                       self.norm_scratch.numel(), st))
+        if reduce_grads:
+            self._reduce("lm_head", "final_norm")
+        cur = 0
+        for i in reversed(range(c.layers)):
+            self.blocks[i]._x = self.acts[i]
+            self.blocks[i].backward(self.dx[cur], self.dx[cur ^ 1])
+            cur ^= 1
+            if reduce_grads:
+                self._reduce(f"blocks.{i}.{_BLOCK_ORDER[0]}", f"blocks.{i}.{_BLOCK_ORDER[-1]}")
+        d0, ge = ta(self.dx[cur]), ta(self.view("grads", "embedding"))
+        check(lib.cdl_b200_embedding_bwd(L.ref(tok), L.ref(d0), L.ref(ge), st))
+        if reduce_grads:
+            self._reduce("embedding", "embedding")
+
+    def _reduce(self, first: str, last: str) -> None:
+        if self.world == 1:
+            return
+        import torch.distributed as dist
+
+        lo = self.offsets[first][0]
+        hi = self.offsets[last][0] + self.offsets[last][1]
+        ev = torch.cuda.Event()
+        ev.record()
+        with torch.cuda.stream(self.comm):
+            self.comm.wait_event(ev)
+            dist.all_reduce(self.grads[lo:hi], group=self.group)
+
+    # ---- optimizer
+    def optimizer_step(self, lr: float | None = None) -> None:
+        c = self.cfg
+        if self.comm is not None:
+            torch.cuda.current_stream().wait_stream(self.comm)
+        st = ctypes.c_void_p(torch.cuda.current_stream().cuda_stream)
+        self.step_count += 1
+        sumsq_ptr = None
+        if c.max_grad_norm > 0:
+            check(lib.cdl_b200_sum(self.grads.data_ptr(), self.numel, self.sumsq.data_ptr(), 1.0, 1, 0,
+                                   self.red_scratch.data_ptr(), 4096, st))
+            sumsq_ptr = self.sumsq.data_ptr()
+        for o, n, decay in self.segments:
+            hp = _lib.CdlAdamwParams(lr if lr is not None else c.lr, c.beta1, c.beta2, c.adam_eps,
+                                     c.weight_decay if decay else 0.0, self.step_count, 1.0,
+                                     c.max_grad_norm)
+            check(lib.cdl_b200_adamw(self.master.data_ptr() + 4 * o, self.replica.data_ptr() + 2 * o,
+                                     self.grads.data_ptr() + 4 * o, self.m.data_ptr() + 4 * o,
+                                     self.v.data_ptr() + 4 * o, n, sumsq_ptr, ctypes.byref(hp), st))
+
+    def train_step(self, tokens: torch.Tensor, targets: torch.Tensor, global_tokens: int | None = None,
+                   lr: float | None = None) -> torch.Tensor:
+        """tokens, targets: i32 [microbatches, tokens_per_microbatch].  One optimizer step over all
+        microbatches (gradient accumulation); returns the device scalar with the mean loss of this
+        rank's share (sum over ranks = global mean)."""
+        mb = tokens.shape[0]
+        total = global_tokens if global_tokens is not None else tokens.numel() * self.world
+        self.loss.zero_()
+        for i in range(mb):
+            self.forward_backward(tokens[i], targets[i], 1.0 / total, reduce_grads=(i == mb - 1))
+        self.optimizer_step(lr)
+        return self.loss
+
+
+def ops_norm_bwd_scratch(rows: int, cols: int) -> int:
+    n = ctypes.c_size_t(0)
+    check(lib.cdl_b200_rmsnorm_bwd_scratch_bytes(rows, cols, ctypes.byref(n)))
+    return max(n.value, 16)

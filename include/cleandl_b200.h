@@ -183,6 +183,36 @@ int32_t cdl_b200_swiglu_bwd(const cdl_tensor* d_act, const cdl_tensor* gate, con
 int32_t cdl_b200_embedding_fwd(const cdl_tensor* tokens, const cdl_tensor* table,
                                const cdl_tensor* out, cdl_stream stream);
 
+/* ---- Loss and optimizer step of the LM ---------------------------------------------------
+ * Call sites in the reference (the kernels themselves are not in its tree):
+ * crates/sky-1/src/training/model/mod.rs:262-271 (cross-entropy that leaves the logits' gradient
+ * in place of the logits), :351-356 (embedding scatter-add), :361-420 and decoder.rs:716-752
+ * (gradient sum of squares, AdamW with global-norm clipping writing the f32 master weight and its
+ * bf16 replica, then zero-filled gradients; no weight decay on norm gains, decoder.rs:724-731). */
+
+/* loss[t] = logsumexp(logits[t, :]) - logits[t, targets[t]];  logits[t, :] is OVERWRITTEN with
+ * (softmax - onehot) * grad_scale.  targets[t] < 0 marks an ignored row (loss 0, gradient 0).
+ * logits bf16 [T, vocab], vocab % 8 == 0; targets i32 [T]; loss f32 [T]. */
+int32_t cdl_b200_cross_entropy(const cdl_tensor* logits, const cdl_tensor* targets,
+                               const cdl_tensor* loss, float grad_scale, cdl_stream stream);
+/* d_table[tokens[t], :] += dx[t, :];  d_table f32 [vocab, hidden], dx bf16 [T, hidden]. */
+int32_t cdl_b200_embedding_bwd(const cdl_tensor* tokens, const cdl_tensor* dx,
+                               const cdl_tensor* d_table, cdl_stream stream);
+/* out[0] = (accumulate ? out[0] : 0) + scale * sum_i (square ? x_i^2 : x_i), summed in a fixed
+ * order (deterministic).  scratch: 4096 bytes. */
+int32_t cdl_b200_sum(const float* x, int64_t n, float* out, float scale, int32_t square,
+                     int32_t accumulate, void* scratch, size_t scratch_bytes, cdl_stream stream);
+typedef struct {
+  float lr, beta1, beta2, eps, weight_decay;
+  int32_t step;        /* 1-based, for the bias correction */
+  float grad_scale;    /* multiplies the raw gradient (e.g. 1 / data-parallel ranks) */
+  float max_grad_norm; /* <= 0: no clipping; else clip by sqrt(*grad_sumsq) * grad_scale */
+} cdl_adamw_params;
+/* AdamW over n contiguous elements: updates master (f32), replica (bf16), m, v, zeroes grad.
+ * grad_sumsq: device scalar with the sum of squares of ALL raw gradients of the model (nullable). */
+int32_t cdl_b200_adamw(float* master, void* replica_bf16, float* grad, float* m, float* v, int64_t n,
+                       const float* grad_sumsq, const cdl_adamw_params* hp, cdl_stream stream);
+
 /* ---- sky-1 decoder block ---------------------------------------------------------------
  * One call per direction for the dataflow of DecoderExecutor::train_forward / train_backward
  * (crates/sky-1/src/training/model/decoder.rs:332-520, 523-695): pre-RMSNorm, fused QKV
