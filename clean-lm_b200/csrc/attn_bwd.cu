@@ -15,10 +15,10 @@
 //        dP^T = V dO^T         (SS)  -> TMEM [128,256)
 //        dV  += P^T dO         (A = P^T from TMEM)        -> TMEM [256,384)
 //        dK  += dS^T Q         (A = dS^T from shared)     -> TMEM [384,512)
-//        dQ^T = K^T dS^T       (SS)  -> TMEM [128,256), reduced into an f32 dQ accumulator in
-//                                      global memory with red.global.add (coalesced along d).
+//        dQ   = dS K           (SS)  -> TMEM [128,256), reduced into an f32 dQ accumulator in
+//                                      global memory with 128-bit red.global.add.v4.f32.
 //      dS^T is written once to shared memory in the 128-byte-swizzled layout that serves both as
-//      the K-major A operand of the dK product and as the MN-major B operand of the dQ^T product.
+//      the K-major A operand of the dK product and as the MN-major A operand of the dQ product.
 //   3. postprocess: dQ accumulator f32 -> bf16.
 // Scratch: dQ accumulator [B, Sq, H, D] f32, then LSE2 and delta [B, H, Sq_pad] f32.
 #include "host.h"
@@ -76,8 +76,10 @@ __device__ __forceinline__ float ex2(float x) {
   return y;
 }
 
-__device__ __forceinline__ void red_add_f32(float* addr, float v) {
-  asm volatile("red.global.add.f32 [%0], %1;" ::"l"(addr), "f"(v) : "memory");
+__device__ __forceinline__ void red_add_v4_f32(float* addr, float a, float b, float c, float d) {
+  asm volatile("red.global.add.v4.f32 [%0], {%1, %2, %3, %4};" ::"l"(addr), "f"(a), "f"(b), "f"(c),
+               "f"(d)
+               : "memory");
 }
 
 __device__ __forceinline__ void compute_bar_sync() {
@@ -239,6 +241,9 @@ __global__ void __launch_bounds__(THREADS, 1)
     }
   } else if (warp == 1) {
     // ------------------------------------------------------------ MMA issuer
+    // Issue order per iteration: dP^T(it), dV(it), S^T(it+1), dK(it), dQ(it).  S^T of the next
+    // query block is issued before this block's dK / dQ so the compute warps can turn it into
+    // P^T while those two products run.
     if (elect_one() && iters > 0) {
       const uint32_t idesc_kk = make_idesc_bf16(128, 128, 0, 0);  // both operands K-major
       const uint32_t idesc_kmn = make_idesc_bf16(128, 128, 0, 1); // A K-major / TMEM, B MN-major
@@ -246,21 +251,25 @@ __global__ void __launch_bounds__(THREADS, 1)
       const uint32_t k_addr = smem_u32(s_k), v_addr = smem_u32(s_v), q_addr = smem_u32(s_q);
       const uint32_t do_addr = smem_u32(s_do), ds_addr = smem_u32(s_ds);
       auto koff = [](int k) { return static_cast<uint32_t>((k >> 2) * PANEL_BYTES + (k & 3) * 32); };
-      bool ok = mbar_wait(&bars->kv_full, 0, abort_word, 221);
-      for (int it = 0; it < iters && ok; ++it) {
-        const int s = it & 1;
-        const uint32_t ph = it & 1;
-        const uint32_t qa = q_addr + s * TILE_BYTES;
-        // S^T = K Q^T
-        ok = mbar_wait(&bars->q_full[s], (it >> 1) & 1, abort_word, 222);
-        if (!ok) break;
-        tc_fence_after();
+      auto issue_s = [&](int it) {  // S^T = K Q^T
+        const uint32_t qa = q_addr + (it & 1) * TILE_BYTES;
 #pragma unroll
         for (int k = 0; k < 8; ++k)
           umma_ss(tmem_base + COL_S, smem_desc_sw128(k_addr + koff(k), 16, 1024),
                   smem_desc_sw128(qa + koff(k), 16, 1024), idesc_kk, k != 0);
         umma_commit(&bars->s_full);
-        // dP^T = V dO^T  (its TMEM columns held dQ^T of the previous iteration)
+      };
+      bool ok = mbar_wait(&bars->kv_full, 0, abort_word, 221) &&
+                mbar_wait(&bars->q_full[0], 0, abort_word, 222);
+      if (ok) {
+        tc_fence_after();
+        issue_s(0);
+      }
+      for (int it = 0; it < iters && ok; ++it) {
+        const int s = it & 1;
+        const uint32_t ph = it & 1;
+        const uint32_t qa = q_addr + s * TILE_BYTES;
+        // dP^T = V dO^T  (its TMEM columns held dQ of the previous iteration)
         ok = mbar_wait(&bars->do_full, ph, abort_word, 223);
         if (ok && it > 0) ok = mbar_wait(&bars->dq_read, (it - 1) & 1, abort_word, 224);
         if (!ok) break;
@@ -281,7 +290,14 @@ __global__ void __launch_bounds__(THREADS, 1)
                   (it > 0 || k != 0) ? 1u : 0u);
         // dO is free once dP^T and dV have read it: this commit covers both.
         umma_commit(&bars->do_empty);
-        // dK += dS^T Q ;  dQ^T = K^T dS^T
+        // S^T of the next query block; it overwrites P^T, which dV (issued above) reads first.
+        if (it + 1 < iters) {
+          ok = mbar_wait(&bars->q_full[s ^ 1], ((it + 1) >> 1) & 1, abort_word, 227);
+          if (!ok) break;
+          tc_fence_after();
+          issue_s(it + 1);
+        }
+        // dK += dS^T Q ;  dQ = dS K   (dS^T tile: K-major A for dK, MN-major A for dQ)
         ok = mbar_wait(&bars->ds_ready, ph, abort_word, 226);
         if (!ok) break;
         tc_fence_after();
@@ -293,60 +309,62 @@ __global__ void __launch_bounds__(THREADS, 1)
         umma_commit(&bars->q_empty[s]);
 #pragma unroll
         for (int k = 0; k < 8; ++k)
-          umma_ss(tmem_base + COL_DP, smem_desc_sw128(k_addr + k * 2048, PANEL_BYTES, 1024),
-                  smem_desc_sw128(ds_addr + k * 2048, PANEL_BYTES, 1024), idesc_mnmn, k != 0);
+          umma_ss(tmem_base + COL_DP, smem_desc_sw128(ds_addr + k * 2048, PANEL_BYTES, 1024),
+                  smem_desc_sw128(k_addr + k * 2048, PANEL_BYTES, 1024), idesc_mnmn, k != 0);
         umma_commit(&bars->dq_full);
       }
     }
   } else {
     // ------------------------------------------------------------ compute warps (2..9)
+    // Software pipeline per iteration: dS(it), P(it+1), reduce dQ(it); P(it+1) runs while the
+    // tensor core computes dK(it) and dQ(it).
     const int ct = threadIdx.x - 64;   // 0..255
     const int wg = (warp - 2) >> 2;    // column half this thread works on
     const int quad = warp & 3;
-    const int r = quad * 32 + lane;    // key row inside the block == TMEM lane
+    const int r = quad * 32 + lane;    // row inside the block == TMEM lane
     const uint32_t lane_addr = static_cast<uint32_t>(quad * 32) << 16;
     const int key = key0 + r;
     bool ok = true;
 
-    auto load_stats = [&](int it, int stage) {
-      const int h = kvh * group + it / m_count;
-      const int q0 = (m_start + it % m_count) * BQ;
-      const long long base = (static_cast<long long>(b) * p.H + h) * p.Sq_pad + q0;
-      if (ct < 128) s_lse[stage * 128 + ct] = p.lse2[base + ct];
-      else s_delta[stage * 128 + ct - 128] = p.delta[base + ct - 128];
+    auto it_head = [&](int it) { return kvh * group + it / m_count; };
+    auto it_q0 = [&](int it) { return (m_start + it % m_count) * BQ; };
+    // Row statistics of iteration `it`: threads 0..127 fetch LSE2, 128..255 fetch delta.
+    auto fetch_stat = [&](int it) -> float {
+      const long long base = (static_cast<long long>(b) * p.H + it_head(it)) * p.Sq_pad + it_q0(it);
+      return ct < 128 ? p.lse2[base + ct] : p.delta[base + ct - 128];
     };
-    if (iters > 0) load_stats(0, 0);
-    compute_bar_sync();
+    auto store_stat = [&](int stage, float v) {
+      if (ct < 128) s_lse[stage * 128 + ct] = v;
+      else s_delta[stage * 128 + ct - 128] = v;
+    };
+    float pr[64];
 
-    for (int it = 0; it < iters && ok; ++it) {
-      const int st = it & 1;
-      const uint32_t ph = it & 1;
-      const int h = kvh * group + it / m_count;
-      const int q0 = (m_start + it % m_count) * BQ;
-      // Prefetch the next iteration's row statistics (the other stage is idle by now).
-      if (it + 1 < iters) load_stats(it + 1, st ^ 1);
-      const float* lse_s = s_lse + st * 128 + wg * 64;
-      const float* delta_s = s_delta + st * 128 + wg * 64;
-      // Is any (key, query) pair of this block masked?
+    // P^T(it) = exp2(S^T * scale_log2 - lse2) -> registers and (bf16) TMEM
+    auto p_phase = [&](int it) -> bool {
+      const int q0 = it_q0(it);
+      const float4* lse_s = reinterpret_cast<const float4*>(s_lse + (it & 1) * 128 + wg * 64);
       const bool need_mask = (p.causal && key0 + BKV - 1 > q0 + shift) || key0 + BKV > p.Sk;
-
-      // ---- P^T = exp2(S^T * scale_log2 - lse2)
-      if (!mbar_wait(&bars->s_full, ph, abort_word, 321)) { ok = false; break; }
+      if (!mbar_wait(&bars->s_full, it & 1, abort_word, 321)) return false;
       tc_fence_after();
-      float pr[64];
       {
         uint32_t sr[2][32];
         tmem_ld32(tmem_base + lane_addr + COL_S + wg * 64, sr[0]);
         tmem_ld32(tmem_base + lane_addr + COL_S + wg * 64 + 32, sr[1]);
         tmem_wait_ld();
 #pragma unroll
-        for (int c = 0; c < 64; ++c) {
-          float v = ex2(fmaf(__uint_as_float(sr[c >> 5][c & 31]), p.scale_log2, -lse_s[c]));
-          if (need_mask) {
-            const int qrow = q0 + wg * 64 + c;
-            if (key >= p.Sk || (p.causal && key > qrow + shift)) v = 0.f;
+        for (int c4 = 0; c4 < 16; ++c4) {
+          const float4 l4 = lse_s[c4];
+          const float l[4] = {l4.x, l4.y, l4.z, l4.w};
+#pragma unroll
+          for (int j = 0; j < 4; ++j) {
+            const int c = c4 * 4 + j;
+            float v = ex2(fmaf(__uint_as_float(sr[c >> 5][c & 31]), p.scale_log2, -l[j]));
+            if (need_mask) {
+              const int qrow = q0 + wg * 64 + c;
+              if (key >= p.Sk || (p.causal && key > qrow + shift)) v = 0.f;
+            }
+            pr[c] = v;
           }
-          pr[c] = v;
         }
       }
       compute_bar_sync();  // both halves have read S^T before P^T overwrites its columns
@@ -359,11 +377,28 @@ __global__ void __launch_bounds__(THREADS, 1)
       }
       tc_fence_before();
       mbar_arrive(&bars->p_ready);
+      return true;
+    };
+
+    float stat_next = 0.f;
+    if (iters > 0) store_stat(0, fetch_stat(0));
+    if (iters > 1) stat_next = fetch_stat(1);
+    compute_bar_sync();
+    if (iters > 0) ok = p_phase(0);
+    if (iters > 1) store_stat(1, stat_next);
+    compute_bar_sync();
+
+    for (int it = 0; it < iters && ok; ++it) {
+      const uint32_t ph = it & 1;
+      const int h = it_head(it);
+      const int q0 = it_q0(it);
+      if (it + 2 < iters) stat_next = fetch_stat(it + 2);  // lands while this iteration computes
 
       // ---- dS^T = P^T o (dP^T - delta) * scale  -> shared memory (128-byte swizzle)
       if (!mbar_wait(&bars->dp_full, ph, abort_word, 322)) { ok = false; break; }
       tc_fence_after();
       {
+        const float4* delta_s = reinterpret_cast<const float4*>(s_delta + (it & 1) * 128 + wg * 64);
         uint32_t dr[2][32];
         tmem_ld32(tmem_base + lane_addr + COL_DP + wg * 64, dr[0]);
         tmem_ld32(tmem_base + lane_addr + COL_DP + wg * 64 + 32, dr[1]);
@@ -371,11 +406,13 @@ __global__ void __launch_bounds__(THREADS, 1)
         uint8_t* row_ptr = s_ds + wg * PANEL_BYTES + r * 128;
 #pragma unroll
         for (int ch = 0; ch < 8; ++ch) {
+          const float4 d0 = delta_s[ch * 2], d1 = delta_s[ch * 2 + 1];
+          const float dl[8] = {d0.x, d0.y, d0.z, d0.w, d1.x, d1.y, d1.z, d1.w};
           float d[8];
 #pragma unroll
           for (int j = 0; j < 8; ++j) {
             const int c = ch * 8 + j;
-            d[j] = pr[c] * (__uint_as_float(dr[c >> 5][c & 31]) - delta_s[c]) * p.scale;
+            d[j] = pr[c] * (__uint_as_float(dr[c >> 5][c & 31]) - dl[j]) * p.scale;
           }
           uint4 q;
           q.x = pack_bf16x2(d[0], d[1]);
@@ -389,7 +426,10 @@ __global__ void __launch_bounds__(THREADS, 1)
       fence_proxy_async_smem();
       mbar_arrive(&bars->ds_ready);
 
-      // ---- dQ^T tile -> global f32 accumulator
+      // ---- P^T of the next query block (overlaps the dK / dQ products of this one)
+      if (it + 1 < iters && !p_phase(it + 1)) { ok = false; break; }
+
+      // ---- dQ tile (rows = queries, columns = head dimension) -> global f32 accumulator
       if (!mbar_wait(&bars->dq_full, ph, abort_word, 323)) { ok = false; break; }
       tc_fence_after();
       {
@@ -399,14 +439,22 @@ __global__ void __launch_bounds__(THREADS, 1)
         tmem_wait_ld();
         tc_fence_before();
         mbar_arrive(&bars->dq_read);
-        // lane row r is the head-dimension index d; column c is the query row.
-        float* base = p.dq_acc + ((static_cast<long long>(b) * p.Sq + q0 + wg * 64) * p.H + h) * D + r;
-        const int valid = min(64, p.Sq - (q0 + wg * 64));
+        const int qrow = q0 + r;
+        if (qrow < p.Sq) {
+          float* dst = p.dq_acc + ((static_cast<long long>(b) * p.Sq + qrow) * p.H + h) * D + wg * 64;
 #pragma unroll
-        for (int c = 0; c < 64; ++c)
-          if (c < valid) red_add_f32(base + static_cast<long long>(c) * p.H * D, __uint_as_float(qr[c >> 5][c & 31]));
+          for (int c = 0; c < 64; c += 4)
+            red_add_v4_f32(dst + c, __uint_as_float(qr[c >> 5][c & 31]),
+                           __uint_as_float(qr[c >> 5][(c & 31) + 1]),
+                           __uint_as_float(qr[c >> 5][(c & 31) + 2]),
+                           __uint_as_float(qr[c >> 5][(c & 31) + 3]));
+        }
       }
-      compute_bar_sync();  // next iteration's statistics are in place, this one's are done with
+      // Statistics of iteration it + 2 replace those of iteration it (all reads of them are
+      // behind the barrier inside p_phase above or, for the last iterations, behind this one).
+      compute_bar_sync();
+      if (it + 2 < iters) store_stat(it & 1, stat_next);
+      compute_bar_sync();
     }
 
     // ---- epilogue: dV and dK rows of this key block

@@ -6,10 +6,11 @@
 //   LSE = max + ln(sum exp) (natural log, f32, [B, H, Sq]); rows without a visible key give
 //   O = 0 and LSE = -inf (attention/mod.rs:104-105).
 //
-// One CTA computes 256 query rows (two 128-row tiles) of one (batch, head); 320 threads:
+// One CTA computes 256 query rows (two 128-row tiles) of one (batch, head); 384 threads (warps 2, 3
+// idle: they only exist so that register re-allocation works on whole warp groups):
 //   warp 0       TMA producer: Q once, then K and V blocks of 128 keys through two 2-stage rings.
 //   warp 1       MMA issuer: S_t = Q_t K^T (SS form) into TMEM, O_t += P_t V (A = P from TMEM).
-//   warps 2-5    softmax for tile 0, warps 6-9 for tile 1: one thread per query row.  A thread
+//   warps 4-7    softmax for tile 0, warps 8-11 for tile 1: one thread per query row.  A thread
 //                reads its S row from TMEM, keeps the running max / sum in registers, writes
 //                P (bf16) back into the TMEM columns S occupied, and only rescales the O
 //                accumulator in TMEM when the running max grew by more than 2^8.
@@ -32,7 +33,7 @@ constexpr int BQ = 128;       // query rows per tile
 constexpr int BKV = 128;      // keys per block
 constexpr int TILE_BYTES = 128 * 128 * 2;  // 32 KiB: a 128 x 128 bf16 tile as two 64-wide panels
 constexpr int PANEL_BYTES = TILE_BYTES / 2;
-constexpr int THREADS = 320;
+constexpr int THREADS = 384;  // warp group 0: TMA, MMA, 2 idle; groups 1, 2: softmax
 constexpr int TMEM_COLS = 512;
 constexpr float RESCALE_THRESHOLD = 8.0f;  // log2 units
 constexpr size_t SMEM_BYTES = 1024 + 6 * TILE_BYTES + 256;
@@ -125,9 +126,12 @@ __global__ void __launch_bounds__(THREADS, 1)
   __syncthreads();
   tc_fence_after();
   const uint32_t tmem_base = bars->tmem_base;
+  // The control warps need few registers; hand theirs to the softmax warp groups, which hold a
+  // whole 128-column row of scores per thread.
 
   if (warp == 0) {
     // ------------------------------------------------------------ TMA producer
+    setmaxnreg_dec<56>();
     if (elect_one() && n_max > 0) {
       mbar_arrive_expect_tx(&bars->q_full, 2 * TILE_BYTES);
 #pragma unroll
@@ -155,6 +159,7 @@ __global__ void __launch_bounds__(THREADS, 1)
     }
   } else if (warp == 1) {
     // ------------------------------------------------------------ MMA issuer
+    setmaxnreg_dec<56>();
     if (elect_one() && n_max > 0) {
       const uint32_t idesc_qk = make_idesc_bf16(BQ, BKV, 0, 0);
       const uint32_t idesc_pv = make_idesc_bf16(BQ, D, 0, 1);
@@ -215,9 +220,12 @@ __global__ void __launch_bounds__(THREADS, 1)
         if (j + 1 < n_max) umma_commit(&bars->k_empty[sn]);
       }
     }
+  } else if (warp < 4) {
+    setmaxnreg_dec<56>();
   } else {
     // ------------------------------------------------------------ softmax + epilogue
-    const int t = (warp - 2) >> 2;  // query tile of this warp group
+    setmaxnreg_inc<224>();
+    const int t = (warp - 4) >> 2;  // query tile of this warp group
     const int quad = warp & 3;      // TMEM lane quadrant
     const int row_in_tile = quad * 32 + lane;
     const int row = m0 + t * BQ + row_in_tile;
@@ -247,16 +255,25 @@ __global__ void __launch_bounds__(THREADS, 1)
       const int warp_first_row = m0 + t * BQ + quad * 32;
       const int warp_limit = p.causal ? warp_first_row + p.Sk - p.Sq : p.Sk - 1;
       const bool need_mask = key0 + BKV - 1 > min(warp_limit, p.Sk - 1);
-      float mx = -INFINITY;
+      // Row max over the raw scores (four independent chains), scaled afterwards: scale > 0.
+      if (need_mask) {
+#pragma unroll
+        for (int c = 0; c < 4; ++c)
+#pragma unroll
+          for (int i = 0; i < 32; ++i)
+            if (key0 + c * 32 + i > key_limit) sr[c][i] = 0xff800000u;  // -inf
+      }
+      float mxa[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
 #pragma unroll
       for (int c = 0; c < 4; ++c)
 #pragma unroll
-        for (int i = 0; i < 32; ++i) {
-          float x = __uint_as_float(sr[c][i]) * p.scale_log2;
-          if (need_mask && key0 + c * 32 + i > key_limit) x = -INFINITY;
-          sr[c][i] = __float_as_uint(x);
-          mx = fmaxf(mx, x);
+        for (int i = 0; i < 32; i += 4) {
+          mxa[0] = fmaxf(mxa[0], __uint_as_float(sr[c][i]));
+          mxa[1] = fmaxf(mxa[1], __uint_as_float(sr[c][i + 1]));
+          mxa[2] = fmaxf(mxa[2], __uint_as_float(sr[c][i + 2]));
+          mxa[3] = fmaxf(mxa[3], __uint_as_float(sr[c][i + 3]));
         }
+      const float mx = fmaxf(fmaxf(mxa[0], mxa[1]), fmaxf(mxa[2], mxa[3])) * p.scale_log2;
       // Lazy rescale: move the reference max only when it grew by more than the threshold.
       const bool grow = mx > m_used + RESCALE_THRESHOLD || (m_used == -INFINITY && mx > -INFINITY);
       if (j > 0 && __any_sync(0xffffffffu, grow)) {
@@ -279,19 +296,21 @@ __global__ void __launch_bounds__(THREADS, 1)
       }
       if (grow) m_used = mx;
       const float m_eff = m_used == -INFINITY ? 0.f : m_used;
-      float sum = 0.f;
+      float suma[4] = {0.f, 0.f, 0.f, 0.f};
 #pragma unroll
       for (int c = 0; c < 4; ++c) {
         uint32_t pk[16];
 #pragma unroll
         for (int i = 0; i < 16; ++i) {
-          const float p0 = ex2(__uint_as_float(sr[c][2 * i]) - m_eff);
-          const float p1 = ex2(__uint_as_float(sr[c][2 * i + 1]) - m_eff);
-          sum += p0 + p1;
+          const float p0 = ex2(fmaf(__uint_as_float(sr[c][2 * i]), p.scale_log2, -m_eff));
+          const float p1 = ex2(fmaf(__uint_as_float(sr[c][2 * i + 1]), p.scale_log2, -m_eff));
+          suma[(i & 1) * 2] += p0;
+          suma[(i & 1) * 2 + 1] += p1;
           pk[i] = pack_bf16x2(p0, p1);
         }
         tmem_st16(t_s + c * 16, pk);
       }
+      const float sum = (suma[0] + suma[1]) + (suma[2] + suma[3]);
       l += sum;
       tmem_wait_st();
       tc_fence_before();
