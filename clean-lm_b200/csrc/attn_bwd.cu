@@ -15,8 +15,9 @@
 //        dP^T = V dO^T         (SS)  -> TMEM [128,256)
 //        dV  += P^T dO         (A = P^T from TMEM)        -> TMEM [256,384)
 //        dK  += dS^T Q         (A = dS^T from shared)     -> TMEM [384,512)
-//        dQ   = dS K           (SS)  -> TMEM [128,256), reduced into an f32 dQ accumulator in
-//                                      global memory with 128-bit red.global.add.v4.f32.
+//        dQ   = dS K           (SS)  -> TMEM [128,256), added to an f32 dQ accumulator in global
+//                                      memory by TMA reduce operations issued by a dedicated
+//                                      warp group (staged through shared memory).
 //      dS^T is written once to shared memory in the 128-byte-swizzled layout that serves both as
 //      the K-major A operand of the dK product and as the MN-major A operand of the dQ product.
 //   3. postprocess: dQ accumulator f32 -> bf16.
@@ -42,11 +43,14 @@ constexpr int BQ = 128;
 constexpr int BKV = 128;
 constexpr int TILE_BYTES = 128 * 128 * 2;
 constexpr int PANEL_BYTES = TILE_BYTES / 2;
-constexpr int THREADS = 320;  // warp 0 TMA, warp 1 MMA, warps 2-9 compute
+constexpr int THREADS = 512;  // warps 0-3 control (TMA, MMA, 2 idle), 4-11 compute, 12-15 dQ reduce
+constexpr int DQ_CHUNK_BYTES = 128 * 32 * 4;  // 128 query rows x 32 head-dim columns of f32
 constexpr int TMEM_COLS = 512;
 constexpr int COL_S = 0, COL_DP = 128, COL_DV = 256, COL_DK = 384;
-// K, V, Q x 2 stages, dO, dS^T
-constexpr size_t SMEM_BYTES = 1024 + 6 * TILE_BYTES + 2 * 2 * 128 * sizeof(float) + 256;
+// K, V, Q x 2 stages, dO, dS^T, 2 dQ staging chunks
+constexpr size_t SMEM_BYTES =
+    6 * TILE_BYTES + 2 * DQ_CHUNK_BYTES + 2 * 2 * 128 * sizeof(float) + 256;
+static_assert(SMEM_BYTES <= 232448, "exceeds the 227 KiB of shared memory a CTA can opt in to");
 
 struct Params {
   int B, H, Hkv, Sq, Sk, Sq_pad;
@@ -54,7 +58,6 @@ struct Params {
   float scale, scale_log2;
   const float* lse2;   // [B, H, Sq_pad]  LSE * log2(e), +inf for rows that contribute nothing
   const float* delta;  // [B, H, Sq_pad]
-  float* dq_acc;       // [B, Sq, H, D] f32, packed
   __nv_bfloat16* dk;
   __nv_bfloat16* dv;
   long long dk_sb, dk_ss, dk_sh, dv_sb, dv_ss, dv_sh;
@@ -76,14 +79,11 @@ __device__ __forceinline__ float ex2(float x) {
   return y;
 }
 
-__device__ __forceinline__ void red_add_v4_f32(float* addr, float a, float b, float c, float d) {
-  asm volatile("red.global.add.v4.f32 [%0], {%1, %2, %3, %4};" ::"l"(addr), "f"(a), "f"(b), "f"(c),
-               "f"(d)
-               : "memory");
-}
-
 __device__ __forceinline__ void compute_bar_sync() {
   asm volatile("bar.sync 1, 256;" ::: "memory");
+}
+__device__ __forceinline__ void reduce_bar_sync() {
+  asm volatile("bar.sync 2, 128;" ::: "memory");
 }
 
 // ---------------------------------------------------------------- preprocess
@@ -154,16 +154,22 @@ __global__ void __launch_bounds__(THREADS, 1)
     attn_bwd_kernel(const __grid_constant__ CUtensorMap tmap_q,
                     const __grid_constant__ CUtensorMap tmap_k,
                     const __grid_constant__ CUtensorMap tmap_v,
-                    const __grid_constant__ CUtensorMap tmap_do, const Params p) {
-  extern __shared__ uint8_t smem_raw[];
-  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) &
-                                             ~static_cast<uintptr_t>(1023));
+                    const __grid_constant__ CUtensorMap tmap_do,
+                    const __grid_constant__ CUtensorMap tmap_dq, const Params p) {
+  // 227 KiB are used to the last kilobyte, so there is no room for manual alignment slack: the
+  // 1024-byte alignment the swizzled tiles need is requested from the compiler and verified.
+  extern __shared__ __align__(1024) uint8_t smem[];
+  if ((smem_u32(smem) & 1023u) != 0) {
+    if (threadIdx.x == 0) atomicExch(p.status, 901);
+    return;
+  }
   uint8_t* s_k = smem;
   uint8_t* s_v = smem + TILE_BYTES;
   uint8_t* s_q = smem + 2 * TILE_BYTES;  // 2 stages
   uint8_t* s_do = smem + 4 * TILE_BYTES;
   uint8_t* s_ds = smem + 5 * TILE_BYTES;
-  float* s_lse = reinterpret_cast<float*>(smem + 6 * TILE_BYTES);  // [2][128]
+  uint8_t* s_dq = smem + 6 * TILE_BYTES;  // 2 staging chunks for the dQ reduction
+  float* s_lse = reinterpret_cast<float*>(smem + 6 * TILE_BYTES + 2 * DQ_CHUNK_BYTES);  // [2][128]
   float* s_delta = s_lse + 2 * 128;                                // [2][128]
   Barriers* bars = reinterpret_cast<Barriers*>(s_delta + 2 * 128);
   volatile int* abort_word = &bars->abort_word;
@@ -194,7 +200,7 @@ __global__ void __launch_bounds__(THREADS, 1)
     mbar_init(&bars->p_ready, 256);
     mbar_init(&bars->ds_ready, 256);
     mbar_init(&bars->dq_full, 1);
-    mbar_init(&bars->dq_read, 256);
+    mbar_init(&bars->dq_read, 128);
     bars->abort_word = 0;
     fence_mbar_init();
   }
@@ -207,6 +213,7 @@ __global__ void __launch_bounds__(THREADS, 1)
     tma_prefetch_desc(&tmap_k);
     tma_prefetch_desc(&tmap_v);
     tma_prefetch_desc(&tmap_do);
+    tma_prefetch_desc(&tmap_dq);
   }
   tc_fence_before();
   __syncthreads();
@@ -215,6 +222,7 @@ __global__ void __launch_bounds__(THREADS, 1)
 
   if (warp == 0) {
     // ------------------------------------------------------------ TMA producer
+    setmaxnreg_dec<40>();
     if (elect_one() && iters > 0) {
       mbar_arrive_expect_tx(&bars->kv_full, 2 * TILE_BYTES);
 #pragma unroll
@@ -244,6 +252,7 @@ __global__ void __launch_bounds__(THREADS, 1)
     // Issue order per iteration: dP^T(it), dV(it), S^T(it+1), dK(it), dQ(it).  S^T of the next
     // query block is issued before this block's dK / dQ so the compute warps can turn it into
     // P^T while those two products run.
+    setmaxnreg_dec<40>();
     if (elect_one() && iters > 0) {
       const uint32_t idesc_kk = make_idesc_bf16(128, 128, 0, 0);  // both operands K-major
       const uint32_t idesc_kmn = make_idesc_bf16(128, 128, 0, 1); // A K-major / TMEM, B MN-major
@@ -314,12 +323,58 @@ __global__ void __launch_bounds__(THREADS, 1)
         umma_commit(&bars->dq_full);
       }
     }
+  } else if (warp < 4) {
+    setmaxnreg_dec<40>();
+  } else if (warp >= 12) {
+    // ------------------------------------------------------------ dQ reduction warps (12..15)
+    // One thread per query row.  The dQ tile is moved TMEM -> registers -> swizzled shared
+    // memory in four 32-column chunks (two staging buffers) and added to the f32 accumulator in
+    // global memory by TMA reduce operations, so no atomic instruction goes through the LSU.
+    setmaxnreg_dec<72>();
+    const int quad = warp & 3;
+    const int r = quad * 32 + lane;
+    const uint32_t lane_addr = static_cast<uint32_t>(quad * 32) << 16;
+    const bool leader = threadIdx.x == 12 * 32;
+    bool ok = true;
+    for (int it = 0; it < iters && ok; ++it) {
+      const int h = kvh * group + it / m_count;
+      const int q0 = (m_start + it % m_count) * BQ;
+      if (!mbar_wait(&bars->dq_full, it & 1, abort_word, 421)) { ok = false; break; }
+      tc_fence_after();
+#pragma unroll 1
+      for (int c = 0; c < 4; ++c) {
+        uint8_t* stage = s_dq + (c & 1) * DQ_CHUNK_BYTES;
+        // The reduce issued from this staging buffer two chunks ago must have read it.
+        if (leader) tma_store_wait_read<1>();
+        reduce_bar_sync();
+        uint32_t v[32];
+        tmem_ld32(tmem_base + lane_addr + COL_DP + c * 32, v);
+        tmem_wait_ld();
+        if (c == 3) {
+          tc_fence_before();
+          mbar_arrive(&bars->dq_read);  // the tile is out of TMEM: dP^T of the next block may land
+        }
+        uint8_t* row_ptr = stage + r * 128;
+#pragma unroll
+        for (int ch = 0; ch < 8; ++ch)
+          *reinterpret_cast<uint4*>(row_ptr + ((ch ^ (r & 7)) << 4)) =
+              make_uint4(v[ch * 4], v[ch * 4 + 1], v[ch * 4 + 2], v[ch * 4 + 3]);
+        fence_proxy_async_smem();
+        reduce_bar_sync();
+        if (leader) {
+          tma_reduce_add_4d(&tmap_dq, stage, c * 32, h, q0, b);
+          tma_store_commit();
+        }
+      }
+    }
+    if (leader) tma_store_wait<0>();
   } else {
-    // ------------------------------------------------------------ compute warps (2..9)
-    // Software pipeline per iteration: dS(it), P(it+1), reduce dQ(it); P(it+1) runs while the
-    // tensor core computes dK(it) and dQ(it).
-    const int ct = threadIdx.x - 64;   // 0..255
-    const int wg = (warp - 2) >> 2;    // column half this thread works on
+    // ------------------------------------------------------------ compute warps (4..11)
+    // Software pipeline per iteration: dS(it), then P(it+1), which runs while the tensor core
+    // computes dK(it) and dQ(it).
+    setmaxnreg_inc<200>();
+    const int ct = threadIdx.x - 128;  // 0..255
+    const int wg = (warp - 4) >> 2;    // column half this thread works on
     const int quad = warp & 3;
     const int r = quad * 32 + lane;    // row inside the block == TMEM lane
     const uint32_t lane_addr = static_cast<uint32_t>(quad * 32) << 16;
@@ -390,8 +445,6 @@ __global__ void __launch_bounds__(THREADS, 1)
 
     for (int it = 0; it < iters && ok; ++it) {
       const uint32_t ph = it & 1;
-      const int h = it_head(it);
-      const int q0 = it_q0(it);
       if (it + 2 < iters) stat_next = fetch_stat(it + 2);  // lands while this iteration computes
 
       // ---- dS^T = P^T o (dP^T - delta) * scale  -> shared memory (128-byte swizzle)
@@ -429,27 +482,6 @@ __global__ void __launch_bounds__(THREADS, 1)
       // ---- P^T of the next query block (overlaps the dK / dQ products of this one)
       if (it + 1 < iters && !p_phase(it + 1)) { ok = false; break; }
 
-      // ---- dQ tile (rows = queries, columns = head dimension) -> global f32 accumulator
-      if (!mbar_wait(&bars->dq_full, ph, abort_word, 323)) { ok = false; break; }
-      tc_fence_after();
-      {
-        uint32_t qr[2][32];
-        tmem_ld32(tmem_base + lane_addr + COL_DP + wg * 64, qr[0]);
-        tmem_ld32(tmem_base + lane_addr + COL_DP + wg * 64 + 32, qr[1]);
-        tmem_wait_ld();
-        tc_fence_before();
-        mbar_arrive(&bars->dq_read);
-        const int qrow = q0 + r;
-        if (qrow < p.Sq) {
-          float* dst = p.dq_acc + ((static_cast<long long>(b) * p.Sq + qrow) * p.H + h) * D + wg * 64;
-#pragma unroll
-          for (int c = 0; c < 64; c += 4)
-            red_add_v4_f32(dst + c, __uint_as_float(qr[c >> 5][c & 31]),
-                           __uint_as_float(qr[c >> 5][(c & 31) + 1]),
-                           __uint_as_float(qr[c >> 5][(c & 31) + 2]),
-                           __uint_as_float(qr[c >> 5][(c & 31) + 3]));
-        }
-      }
       // Statistics of iteration it + 2 replace those of iteration it (all reads of them are
       // behind the barrier inside p_phase above or, for the last iterations, behind this one).
       compute_bar_sync();
@@ -457,7 +489,12 @@ __global__ void __launch_bounds__(THREADS, 1)
       compute_bar_sync();
     }
 
-    // ---- epilogue: dV and dK rows of this key block
+    // ---- epilogue: dV and dK rows of this key block (every product has finished once the last
+    // dQ commit has arrived)
+    if (ok && iters > 0) {
+      ok = mbar_wait(&bars->dq_full, (iters - 1) & 1, abort_word, 324);
+      tc_fence_after();
+    }
     if (ok) {
       const bool row_ok = key < p.Sk;
       __nv_bfloat16* dv_row = p.dv + b * p.dv_sb + static_cast<long long>(key) * p.dv_ss + kvh * p.dv_sh + wg * 64;
@@ -572,7 +609,6 @@ int32_t attn_bwd_execute(const cdl_attn_desc* desc, const cdl_tensor* q, const c
   p.scale_log2 = p.scale * 1.4426950408889634f;
   p.lse2 = lse2;
   p.delta = delta;
-  p.dq_acc = dq_acc;
   p.dk = static_cast<__nv_bfloat16*>(dk->ptr);
   p.dv = static_cast<__nv_bfloat16*>(dv->ptr);
   p.dk_sb = dk->stride[0]; p.dk_ss = dk->stride[1]; p.dk_sh = dk->stride[2];
@@ -604,6 +640,19 @@ int32_t attn_bwd_execute(const cdl_attn_desc* desc, const cdl_tensor* q, const c
     }
     CDL_CHECK(attn_encode_tmap(&tk, k));
     CDL_CHECK(attn_encode_tmap(&tv, v));
+    CUtensorMap tdq;
+    if (Sq > 0) {
+      // f32 accumulator [B, Sq, H, D] seen innermost-first as (D, H, Sq, B); one reduce moves a
+      // 32-column x 128-row chunk of one head.
+      const uint64_t dims[4] = {static_cast<uint64_t>(D), static_cast<uint64_t>(H),
+                                static_cast<uint64_t>(Sq), static_cast<uint64_t>(B)};
+      const uint64_t strides[4] = {0, static_cast<uint64_t>(D) * 4, static_cast<uint64_t>(H) * D * 4,
+                                   static_cast<uint64_t>(Sq) * H * D * 4};
+      const uint32_t box[4] = {32, 1, 128, 1};
+      CDL_CHECK(encode_tmap(&tdq, dq_acc, CDL_F32, 4, dims, strides, box, true));
+    } else {
+      memset(&tdq, 0, sizeof tdq);
+    }
 
     static std::once_flag attr_once[64];
     int dev = 0;
@@ -618,7 +667,7 @@ int32_t attn_bwd_execute(const cdl_attn_desc* desc, const cdl_tensor* q, const c
 
     dim3 grid(static_cast<unsigned>((Sk + BKV - 1) / BKV), static_cast<unsigned>(Hkv),
               static_cast<unsigned>(B));
-    attn_bwd_kernel<<<grid, THREADS, SMEM_BYTES, stream>>>(tq, tk, tv, tdo, p);
+    attn_bwd_kernel<<<grid, THREADS, SMEM_BYTES, stream>>>(tq, tk, tv, tdo, tdq, p);
     CDL_CUDA(cudaGetLastError());
   }
 
