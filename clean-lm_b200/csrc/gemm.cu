@@ -20,6 +20,9 @@
 #include "host.h"
 #include "ptx.cuh"
 
+#include <stdlib.h>
+#include <string.h>
+
 #include <mutex>
 
 namespace cdl {
@@ -47,6 +50,8 @@ struct Params {
   long long ldd, ldc, d_batch, c_batch;  // in elements
   int d_vec, c_vec;                      // 1 = rows are 16-byte aligned, vector access allowed
   float alpha, beta;
+  int split_k;     // K slices per tile (pair kernel, accumulate-in-place form only); 1 = none
+  int atomic_out;  // 1 = add alpha * partial into D with red.global.add (D already holds C)
   int* status;
 };
 
@@ -70,6 +75,115 @@ __device__ __forceinline__ void tile_coords(const Params& p, int tile, int& b, i
   r -= panel * panel_tiles;
   m = r / width;
   n = first_n + (r - m * width);
+}
+
+// Epilogue of one accumulator for the calling warp: thread `lane` owns output row `row`
+// (TMEM lane = its lane inside the warp's quadrant); t_row addresses column 0 of the accumulator
+// at the warp's first lane.  Applies alpha / beta * C, converts and stores 256 columns.
+__device__ __forceinline__ void store_tile_rows(const Params& p, uint32_t t_row, int b, int row,
+                                                int col_base) {
+  const bool row_ok = row < p.M;
+#pragma unroll 1
+  for (int ch = 0; ch < BN / 32; ++ch) {
+    const int col0 = col_base + ch * 32;
+    if (col0 >= p.N) break;  // warp-uniform
+    uint32_t r[32];
+    tmem_ld32(t_row + ch * 32, r);
+    tmem_wait_ld();
+    if (row_ok) {
+      float v[32];
+#pragma unroll
+      for (int j = 0; j < 32; ++j) v[j] = p.alpha * __uint_as_float(r[j]);
+      if (p.c_mode == 1) {
+        const __nv_bfloat16* cp = static_cast<const __nv_bfloat16*>(p.c) +
+                                  b * p.c_batch + static_cast<long long>(row) * p.ldc + col0;
+#pragma unroll
+        for (int g = 0; g < 4; ++g) {
+          if (p.c_vec && col0 + g * 8 + 8 <= p.N) {
+            const uint4 q = *reinterpret_cast<const uint4*>(cp + g * 8);
+            const uint32_t w[4] = {q.x, q.y, q.z, q.w};
+#pragma unroll
+            for (int j = 0; j < 4; ++j) {
+              v[g * 8 + 2 * j] += p.beta * bf16_lo(w[j]);
+              v[g * 8 + 2 * j + 1] += p.beta * bf16_hi(w[j]);
+            }
+          } else {
+#pragma unroll
+            for (int j = 0; j < 8; ++j)
+              if (col0 + g * 8 + j < p.N)
+                v[g * 8 + j] += p.beta * __bfloat162float(cp[g * 8 + j]);
+          }
+        }
+      } else if (p.c_mode == 2) {
+        const float* cp = static_cast<const float*>(p.c) + b * p.c_batch +
+                          static_cast<long long>(row) * p.ldc + col0;
+#pragma unroll
+        for (int g = 0; g < 8; ++g) {
+          if (p.c_vec && col0 + g * 4 + 4 <= p.N) {
+            const float4 q = *reinterpret_cast<const float4*>(cp + g * 4);
+            v[g * 4 + 0] += p.beta * q.x;
+            v[g * 4 + 1] += p.beta * q.y;
+            v[g * 4 + 2] += p.beta * q.z;
+            v[g * 4 + 3] += p.beta * q.w;
+          } else {
+#pragma unroll
+            for (int j = 0; j < 4; ++j)
+              if (col0 + g * 4 + j < p.N) v[g * 4 + j] += p.beta * cp[g * 4 + j];
+          }
+        }
+      }
+      if (p.atomic_out) {
+        // K-sliced accumulation: D (f32, already holding C) += alpha * partial.  Several slices
+        // of a tile add concurrently, so the order of the f32 additions is not fixed.
+        float* dp = static_cast<float*>(p.d) + b * p.d_batch +
+                    static_cast<long long>(row) * p.ldd + col0;
+#pragma unroll
+        for (int g = 0; g < 8; ++g) {
+          if (p.d_vec && col0 + g * 4 + 4 <= p.N) {
+            asm volatile("red.global.add.v4.f32 [%0], {%1, %2, %3, %4};" ::"l"(dp + g * 4),
+                         "f"(v[g * 4]), "f"(v[g * 4 + 1]), "f"(v[g * 4 + 2]), "f"(v[g * 4 + 3])
+                         : "memory");
+          } else {
+#pragma unroll
+            for (int j = 0; j < 4; ++j)
+              if (col0 + g * 4 + j < p.N) atomicAdd(dp + g * 4 + j, v[g * 4 + j]);
+          }
+        }
+      } else if (p.out_f32) {
+        float* dp = static_cast<float*>(p.d) + b * p.d_batch +
+                    static_cast<long long>(row) * p.ldd + col0;
+#pragma unroll
+        for (int g = 0; g < 8; ++g) {
+          if (p.d_vec && col0 + g * 4 + 4 <= p.N) {
+            *reinterpret_cast<float4*>(dp + g * 4) =
+                make_float4(v[g * 4], v[g * 4 + 1], v[g * 4 + 2], v[g * 4 + 3]);
+          } else {
+#pragma unroll
+            for (int j = 0; j < 4; ++j)
+              if (col0 + g * 4 + j < p.N) dp[g * 4 + j] = v[g * 4 + j];
+          }
+        }
+      } else {
+        __nv_bfloat16* dp = static_cast<__nv_bfloat16*>(p.d) + b * p.d_batch +
+                            static_cast<long long>(row) * p.ldd + col0;
+#pragma unroll
+        for (int g = 0; g < 4; ++g) {
+          if (p.d_vec && col0 + g * 8 + 8 <= p.N) {
+            uint4 q;
+            q.x = pack_bf16x2(v[g * 8 + 0], v[g * 8 + 1]);
+            q.y = pack_bf16x2(v[g * 8 + 2], v[g * 8 + 3]);
+            q.z = pack_bf16x2(v[g * 8 + 4], v[g * 8 + 5]);
+            q.w = pack_bf16x2(v[g * 8 + 6], v[g * 8 + 7]);
+            *reinterpret_cast<uint4*>(dp + g * 8) = q;
+          } else {
+#pragma unroll
+            for (int j = 0; j < 8; ++j)
+              if (col0 + g * 8 + j < p.N) dp[g * 8 + j] = __float2bfloat16_rn(v[g * 8 + j]);
+          }
+        }
+      }
+    }
+  }
 }
 
 __global__ void __launch_bounds__(THREADS, 1)
@@ -193,93 +307,8 @@ __global__ void __launch_bounds__(THREADS, 1)
       const uint32_t acc_ph = (t >> 1) & 1;
       if (!mbar_wait(&bars->acc_full[acc], acc_ph, abort_word, 301)) break;
       tc_fence_after();
-      const int row = tm * BM + quad * 32 + lane;
-      const bool row_ok = row < p.M;
-      const uint32_t t_row = tmem_base + (static_cast<uint32_t>(quad * 32) << 16) + acc * BN;
-#pragma unroll 1
-      for (int ch = 0; ch < BN / 32; ++ch) {
-        const int col0 = tn * BN + ch * 32;
-        if (col0 >= p.N) break;  // warp-uniform
-        uint32_t r[32];
-        tmem_ld32(t_row + ch * 32, r);
-        tmem_wait_ld();
-        if (row_ok) {
-          float v[32];
-#pragma unroll
-          for (int j = 0; j < 32; ++j) v[j] = p.alpha * __uint_as_float(r[j]);
-          if (p.c_mode == 1) {
-            const __nv_bfloat16* cp = static_cast<const __nv_bfloat16*>(p.c) +
-                                      b * p.c_batch + static_cast<long long>(row) * p.ldc + col0;
-#pragma unroll
-            for (int g = 0; g < 4; ++g) {
-              if (p.c_vec && col0 + g * 8 + 8 <= p.N) {
-                const uint4 q = *reinterpret_cast<const uint4*>(cp + g * 8);
-                const uint32_t w[4] = {q.x, q.y, q.z, q.w};
-#pragma unroll
-                for (int j = 0; j < 4; ++j) {
-                  v[g * 8 + 2 * j] += p.beta * bf16_lo(w[j]);
-                  v[g * 8 + 2 * j + 1] += p.beta * bf16_hi(w[j]);
-                }
-              } else {
-#pragma unroll
-                for (int j = 0; j < 8; ++j)
-                  if (col0 + g * 8 + j < p.N)
-                    v[g * 8 + j] += p.beta * __bfloat162float(cp[g * 8 + j]);
-              }
-            }
-          } else if (p.c_mode == 2) {
-            const float* cp = static_cast<const float*>(p.c) + b * p.c_batch +
-                              static_cast<long long>(row) * p.ldc + col0;
-#pragma unroll
-            for (int g = 0; g < 8; ++g) {
-              if (p.c_vec && col0 + g * 4 + 4 <= p.N) {
-                const float4 q = *reinterpret_cast<const float4*>(cp + g * 4);
-                v[g * 4 + 0] += p.beta * q.x;
-                v[g * 4 + 1] += p.beta * q.y;
-                v[g * 4 + 2] += p.beta * q.z;
-                v[g * 4 + 3] += p.beta * q.w;
-              } else {
-#pragma unroll
-                for (int j = 0; j < 4; ++j)
-                  if (col0 + g * 4 + j < p.N) v[g * 4 + j] += p.beta * cp[g * 4 + j];
-              }
-            }
-          }
-          if (p.out_f32) {
-            float* dp = static_cast<float*>(p.d) + b * p.d_batch +
-                        static_cast<long long>(row) * p.ldd + col0;
-#pragma unroll
-            for (int g = 0; g < 8; ++g) {
-              if (p.d_vec && col0 + g * 4 + 4 <= p.N) {
-                *reinterpret_cast<float4*>(dp + g * 4) =
-                    make_float4(v[g * 4], v[g * 4 + 1], v[g * 4 + 2], v[g * 4 + 3]);
-              } else {
-#pragma unroll
-                for (int j = 0; j < 4; ++j)
-                  if (col0 + g * 4 + j < p.N) dp[g * 4 + j] = v[g * 4 + j];
-              }
-            }
-          } else {
-            __nv_bfloat16* dp = static_cast<__nv_bfloat16*>(p.d) + b * p.d_batch +
-                                static_cast<long long>(row) * p.ldd + col0;
-#pragma unroll
-            for (int g = 0; g < 4; ++g) {
-              if (p.d_vec && col0 + g * 8 + 8 <= p.N) {
-                uint4 q;
-                q.x = pack_bf16x2(v[g * 8 + 0], v[g * 8 + 1]);
-                q.y = pack_bf16x2(v[g * 8 + 2], v[g * 8 + 3]);
-                q.z = pack_bf16x2(v[g * 8 + 4], v[g * 8 + 5]);
-                q.w = pack_bf16x2(v[g * 8 + 6], v[g * 8 + 7]);
-                *reinterpret_cast<uint4*>(dp + g * 8) = q;
-              } else {
-#pragma unroll
-                for (int j = 0; j < 8; ++j)
-                  if (col0 + g * 8 + j < p.N) dp[g * 8 + j] = __float2bfloat16_rn(v[g * 8 + j]);
-              }
-            }
-          }
-        }
-      }
+      store_tile_rows(p, tmem_base + (static_cast<uint32_t>(quad * 32) << 16) + acc * BN, b,
+                      tm * BM + quad * 32 + lane, tn * BN);
       tc_fence_before();
       __syncwarp();
       if (lane == 0) mbar_arrive(&bars->acc_empty[acc]);
@@ -298,6 +327,199 @@ __global__ void __launch_bounds__(THREADS, 1)
   if (warp == 1) {
     tc_fence_after();
     tmem_dealloc(tmem_base, TMEM_COLS);
+  }
+  if (threadIdx.x == 0 && *abort_word != 0) atomicExch(p.status, *abort_word);
+}
+
+// ------------------------------------------------------------------------------------------
+// CTA-pair variant: a cluster of two CTAs computes a 256 x 256 tile with tcgen05.mma.cta_group::2.
+// Each CTA loads its own 128 rows of A and its own 128-column half of B (32 KiB per stage, so the
+// ring is 6 deep), which halves the B traffic per SM; the pair's leader (cluster rank 0) issues
+// every MMA for both CTAs and each CTA drains its own 128 accumulator rows from its own TMEM.
+// Cross-CTA signalling: the peer's TMA loads complete on the leader's `full` barrier
+// (cta_group::2 form of the load, barrier given as a cluster address); the leader releases
+// stages and publishes accumulators with one tcgen05.commit per CTA (local and peer address); the
+// peer's epilogue warps arrive on the leader's `acc_empty` barrier with a remote mbarrier.arrive.
+constexpr int PAIR_STAGES = 6;
+constexpr int PAIR_STAGE_BYTES = 2 * A_BYTES;  // A 128 x 64 and half of B 128 x 64
+constexpr int PAIR_M = 2 * BM;
+constexpr size_t PAIR_SMEM_BYTES = 1024 + PAIR_STAGES * PAIR_STAGE_BYTES + 256;
+
+struct PairBarriers {
+  uint64_t full[PAIR_STAGES];
+  uint64_t empty[PAIR_STAGES];
+  uint64_t acc_full[2];
+  uint64_t acc_empty[2];
+  uint32_t tmem_base;
+  int abort_word;
+};
+
+__global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(THREADS, 1)
+    gemm_bf16_pair_kernel(const __grid_constant__ CUtensorMap tmap_a,
+                          const __grid_constant__ CUtensorMap tmap_b, const Params p) {
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) &
+                                             ~static_cast<uintptr_t>(1023));
+  PairBarriers* bars = reinterpret_cast<PairBarriers*>(smem + PAIR_STAGES * PAIR_STAGE_BYTES);
+  volatile int* abort_word = &bars->abort_word;
+
+  const int warp = threadIdx.x >> 5;
+  const int lane = threadIdx.x & 31;
+  const uint32_t rank = cluster_ctarank();
+  const int cluster_id = blockIdx.x >> 1;
+  const int num_clusters = gridDim.x >> 1;
+  // Work unit = (tile, K slice); slices exist only in the accumulate-in-place form.
+  const int num_units = p.num_tiles * p.split_k;
+  auto unit_range = [&](int unit, int& tile, int& kb0, int& kb1) {
+    tile = unit / p.split_k;
+    const int slice = unit - tile * p.split_k;
+    kb0 = static_cast<int>(static_cast<long long>(slice) * p.k_blocks / p.split_k);
+    kb1 = static_cast<int>(static_cast<long long>(slice + 1) * p.k_blocks / p.split_k);
+  };
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < PAIR_STAGES; ++s) {
+      mbar_init(&bars->full[s], 1);
+      mbar_init(&bars->empty[s], 1);
+    }
+    for (int i = 0; i < 2; ++i) {
+      mbar_init(&bars->acc_full[i], 1);
+      mbar_init(&bars->acc_empty[i], 8);  // 4 epilogue warps of each CTA (leader's copy is used)
+    }
+    bars->abort_word = 0;
+    fence_mbar_init();
+  }
+  if (warp == 1) {
+    tmem_alloc_pair(&bars->tmem_base, TMEM_COLS);
+    tmem_relinquish_pair();
+  }
+  if (warp == 0 && lane == 0) {
+    tma_prefetch_desc(&tmap_a);
+    tma_prefetch_desc(&tmap_b);
+  }
+  tc_fence_before();
+  __syncthreads();
+  cluster_sync_all();  // both CTAs' barriers exist before anything signals across the pair
+  tc_fence_after();
+  const uint32_t tmem_base = bars->tmem_base;
+
+  if (warp == 0) {
+    // ------------------------------------------------------------ TMA producer (both CTAs)
+    if (elect_one()) {
+      uint32_t it = 0;
+      bool ok = true;
+      for (int unit = cluster_id; unit < num_units && ok; unit += num_clusters) {
+        int tile, kb0, kb1, b, tm, tn;
+        unit_range(unit, tile, kb0, kb1);
+        tile_coords(p, tile, b, tm, tn);
+        const int m0 = tm * PAIR_M + static_cast<int>(rank) * BM;
+        const int n0 = tn * BN + static_cast<int>(rank) * (BN / 2);
+        for (int kb = kb0; kb < kb1; ++kb, ++it) {
+          const int s = it % PAIR_STAGES;
+          const uint32_t ph = (it / PAIR_STAGES) & 1;
+          if (!mbar_wait(&bars->empty[s], ph ^ 1, abort_word, 111)) {
+            ok = false;
+            break;
+          }
+          uint8_t* sa = smem + s * PAIR_STAGE_BYTES;
+          uint8_t* sb = sa + A_BYTES;
+          // Bytes of both CTAs land on the leader's barrier.
+          if (rank == 0) mbar_arrive_expect_tx(&bars->full[s], 2 * PAIR_STAGE_BYTES);
+          const uint32_t full_leader = mapa_shared(smem_u32(&bars->full[s]), 0);
+          const int k0 = kb * BK;
+          if (p.a_mn) {
+#pragma unroll
+            for (int i = 0; i < BM / 64; ++i)
+              tma_load_3d_pair(sa + i * 8192, &tmap_a, full_leader, m0 + i * 64, k0, b);
+          } else {
+            tma_load_3d_pair(sa, &tmap_a, full_leader, k0, m0, b);
+          }
+          if (p.b_mn) {
+#pragma unroll
+            for (int i = 0; i < BN / 128; ++i)
+              tma_load_3d_pair(sb + i * 8192, &tmap_b, full_leader, n0 + i * 64, k0, b);
+          } else {
+            tma_load_3d_pair(sb, &tmap_b, full_leader, k0, n0, b);
+          }
+        }
+      }
+    }
+  } else if (warp == 1) {
+    // ------------------------------------------------------------ MMA issuer (leader CTA only)
+    if (rank == 0 && elect_one()) {
+      const uint32_t idesc = make_idesc_bf16(PAIR_M, BN, p.a_mn, p.b_mn);
+      const uint32_t a_lbo = p.a_mn ? 8192u : 16u, b_lbo = p.b_mn ? 8192u : 16u;
+      const uint32_t a_kstep = p.a_mn ? 2048u : 32u, b_kstep = p.b_mn ? 2048u : 32u;
+      uint32_t it = 0;
+      int t = 0;
+      bool ok = true;
+      for (int unit = cluster_id; unit < num_units && ok; unit += num_clusters, ++t) {
+        int tile, kb0, kb1;
+        unit_range(unit, tile, kb0, kb1);
+        const int acc = t & 1;
+        const uint32_t acc_ph = (t >> 1) & 1;
+        if (!mbar_wait(&bars->acc_empty[acc], acc_ph ^ 1, abort_word, 211)) break;
+        tc_fence_after();
+        const uint32_t d_tmem = tmem_base + acc * BN;
+        for (int kb = kb0; kb < kb1; ++kb, ++it) {
+          const int s = it % PAIR_STAGES;
+          const uint32_t ph = (it / PAIR_STAGES) & 1;
+          if (!mbar_wait(&bars->full[s], ph, abort_word, 212)) {
+            ok = false;
+            break;
+          }
+          tc_fence_after();
+          const uint32_t sa = smem_u32(smem + s * PAIR_STAGE_BYTES);
+          const uint32_t sb = sa + A_BYTES;
+#pragma unroll
+          for (int k = 0; k < BK / 16; ++k) {
+            const uint64_t da = smem_desc_sw128(sa + k * a_kstep, a_lbo, 1024);
+            const uint64_t db = smem_desc_sw128(sb + k * b_kstep, b_lbo, 1024);
+            umma_ss_pair(d_tmem, da, db, idesc, (kb != kb0 || k != 0) ? 1u : 0u);
+          }
+          const uint32_t e = smem_u32(&bars->empty[s]);
+          umma_commit_pair(e);                  // own producer
+          umma_commit_pair(mapa_shared(e, 1));  // the peer's producer
+        }
+        if (ok) {
+          const uint32_t f = smem_u32(&bars->acc_full[acc]);
+          umma_commit_pair(f);
+          umma_commit_pair(mapa_shared(f, 1));
+        }
+      }
+    }
+  } else {
+    // ------------------------------------------------------------ epilogue (warps 2..5, both CTAs)
+    const int quad = warp & 3;
+    int t = 0;
+    for (int unit = cluster_id; unit < num_units; unit += num_clusters, ++t) {
+      int tile, kb0, kb1, b, tm, tn;
+      unit_range(unit, tile, kb0, kb1);
+      tile_coords(p, tile, b, tm, tn);
+      const int acc = t & 1;
+      const uint32_t acc_ph = (t >> 1) & 1;
+      if (!mbar_wait(&bars->acc_full[acc], acc_ph, abort_word, 311)) break;
+      tc_fence_after();
+      store_tile_rows(p, tmem_base + (static_cast<uint32_t>(quad * 32) << 16) + acc * BN, b,
+                      tm * PAIR_M + static_cast<int>(rank) * BM + quad * 32 + lane, tn * BN);
+      tc_fence_before();
+      __syncwarp();
+      if (lane == 0) mbar_arrive_cluster(mapa_shared(smem_u32(&bars->acc_empty[acc]), 0));
+    }
+  }
+
+  // ------------------------------------------------------------ tear-down
+  __syncwarp();
+  if (*abort_word != 0) {
+    const unsigned long long t0 = globaltimer_ns();
+    while (globaltimer_ns() - t0 < 200000ull) __nanosleep(1000);
+  }
+  tc_fence_before();
+  __syncthreads();
+  cluster_sync_all();  // the peer may still signal into this CTA's shared memory until here
+  if (warp == 1) {
+    tc_fence_after();
+    tmem_dealloc_pair(tmem_base, TMEM_COLS);
   }
   if (threadIdx.x == 0 && *abort_word != 0) atomicExch(p.status, *abort_word);
 }
@@ -391,6 +613,16 @@ int32_t matmul_execute(const cdl_tensor* a, const cdl_tensor* b, const cdl_tenso
   CDL_CHECK(analyze_operand("a", a, true, &la));
   CDL_CHECK(analyze_operand("b", b, false, &lb));
 
+  // Kernel choice: CTA pairs (256 x 256 tiles) whenever the problem has more than one 128-row
+  // slab; CDL_B200_GEMM=1cta / 2cta overrides it (benchmarking aid).
+  bool use_pair = M > BM;
+  if (const char* env = getenv("CDL_B200_GEMM")) {
+    if (strcmp(env, "1cta") == 0) use_pair = false;
+    else if (strcmp(env, "2cta") == 0) use_pair = true;
+  }
+  const int tile_m = use_pair ? PAIR_M : BM;
+  const uint32_t b_box_rows = use_pair ? BN / 2 : BN;
+
   CUtensorMap tm_a, tm_b;
   {
     // Innermost-first dims: K-major operand = [K, M|N, batch]; MN-major = [M|N, K, batch].
@@ -407,7 +639,7 @@ int32_t matmul_execute(const cdl_tensor* a, const cdl_tensor* b, const cdl_tenso
     if (lb.mn_major) {
       db[0] = N; db[1] = K; bb[0] = 64; bb[1] = 64;
     } else {
-      db[0] = K; db[1] = N; bb[0] = 64; bb[1] = BN;
+      db[0] = K; db[1] = N; bb[0] = 64; bb[1] = b_box_rows;
     }
     db[2] = batch; bb[2] = 1; sb[0] = 0; sb[1] = lb.ld * 2; sb[2] = bs_b;
     CDL_CHECK(encode_tmap(&tm_a, a->ptr, CDL_BF16, 3, da, sa, ba, true));
@@ -419,7 +651,7 @@ int32_t matmul_execute(const cdl_tensor* a, const cdl_tensor* b, const cdl_tenso
   p.N = static_cast<int>(N);
   p.K = static_cast<int>(K);
   p.batch = static_cast<int>(batch);
-  p.num_m_tiles = static_cast<int>((M + BM - 1) / BM);
+  p.num_m_tiles = static_cast<int>((M + tile_m - 1) / tile_m);
   p.num_n_tiles = static_cast<int>((N + BN - 1) / BN);
   const long long tiles = batch * p.num_m_tiles * p.num_n_tiles;
   if (tiles > INT32_MAX) return fail(CDL_ERR_UNSUPPORTED, "matmul: too many tiles");
@@ -443,23 +675,77 @@ int32_t matmul_execute(const cdl_tensor* a, const cdl_tensor* b, const cdl_tenso
   p.c_vec = use_c ? vec_ok(p.c, p.ldc, p.c_batch, dtype_size(c->dtype)) : 0;
   p.alpha = alpha;
   p.beta = use_c ? beta : 0.0f;
+  p.split_k = 1;
+  p.atomic_out = 0;
   p.status = device_status_ptr();
   if (!p.status) return fail(CDL_ERR_CUDA, "cannot resolve the device status word");
 
   static std::once_flag attr_once[64];
+  static int max_clusters[64] = {};
   int dev = 0;
   CDL_CUDA(cudaGetDevice(&dev));
   cudaError_t attr_err = cudaSuccess;
   std::call_once(attr_once[dev & 63], [&] {
     attr_err = cudaFuncSetAttribute(gemm_bf16_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                     static_cast<int>(SMEM_BYTES));
+    if (attr_err == cudaSuccess)
+      attr_err = cudaFuncSetAttribute(gemm_bf16_pair_kernel,
+                                      cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                      static_cast<int>(PAIR_SMEM_BYTES));
+    // How many CTA pairs the device can hold at once (GPCs with an odd SM count lose one SM).
+    int n = 0;
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3(static_cast<unsigned>(sm_count() & ~1));
+    cfg.blockDim = dim3(THREADS);
+    cfg.dynamicSmemBytes = PAIR_SMEM_BYTES;
+    if (attr_err == cudaSuccess &&
+        cudaOccupancyMaxActiveClusters(&n, gemm_bf16_pair_kernel, &cfg) == cudaSuccess && n > 0)
+      max_clusters[dev & 63] = n;
+    else
+      max_clusters[dev & 63] = sm_count() / 2;
+    (void)cudaGetLastError();
   });
   if (attr_err != cudaSuccess)
     return fail(CDL_ERR_CUDA, "cudaFuncSetAttribute failed: %s", cudaGetErrorString(attr_err));
 
-  const int grid = p.num_tiles < sm_count() ? p.num_tiles : sm_count();
+  // K slicing for the accumulate-in-place form (D = C, f32, beta = 1: the weight-gradient GEMM,
+  // whose output is small and whose K is long).  Slices add into D with atomics, which removes
+  // the tile-count quantisation (e.g. 192 tiles on 74 CTA pairs = 2.6 waves) at the price of an
+  // unordered f32 sum; CDL_B200_DETERMINISTIC=1 turns it off.
+  if (use_pair && use_c && p.out_f32 && c->dtype == CDL_F32 && c->ptr == d->ptr && beta == 1.0f &&
+      p.ldc == p.ldd && p.c_batch == p.d_batch) {
+    const char* det = getenv("CDL_B200_DETERMINISTIC");
+    if (!(det && det[0] == '1')) {
+      const int nc = max_clusters[dev & 63];
+      int best_s = 1;
+      double best_cost = 1e30;
+      for (int sp = 1; sp <= 8 && sp * 8 <= p.k_blocks; ++sp) {
+        const long long units = static_cast<long long>(p.num_tiles) * sp;
+        const long long waves = (units + nc - 1) / nc;
+        // time ~ waves * (K slice + a fixed per-unit cost worth ~6 K blocks of epilogue / ramp)
+        const double cost = static_cast<double>(waves) * (static_cast<double>(p.k_blocks) / sp + 6.0);
+        if (cost < best_cost * 0.97) {
+          best_cost = cost;
+          best_s = sp;
+        }
+      }
+      if (best_s > 1) {
+        p.split_k = best_s;
+        p.atomic_out = 1;
+        p.c_mode = 0;  // D already holds C; the slices only add
+      }
+    }
+  }
+
   ProfileScope ps(PROF_GEMM, 2.0 * static_cast<double>(batch) * M * N * K, stream);
-  gemm_bf16_kernel<<<grid, THREADS, SMEM_BYTES, stream>>>(tm_a, tm_b, p);
+  if (use_pair) {
+    const long long units = static_cast<long long>(p.num_tiles) * p.split_k;
+    const int clusters = units < max_clusters[dev & 63] ? static_cast<int>(units) : max_clusters[dev & 63];
+    gemm_bf16_pair_kernel<<<2 * clusters, THREADS, PAIR_SMEM_BYTES, stream>>>(tm_a, tm_b, p);
+  } else {
+    const int grid = p.num_tiles < sm_count() ? p.num_tiles : sm_count();
+    gemm_bf16_kernel<<<grid, THREADS, SMEM_BYTES, stream>>>(tm_a, tm_b, p);
+  }
   CDL_CUDA(cudaGetLastError());
   return CDL_OK;
 }
