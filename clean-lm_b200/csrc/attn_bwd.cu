@@ -7,21 +7,23 @@
 //   delta_i = sum_d dO_id O_id;  P = exp(S - LSE);  dV = P^T dO;  dP = dO V^T;
 //   dS = P o (dP - delta) * scale;  dQ = dS K;  dK = dS^T Q.
 //
-// Three kernels:
+// Three kernels, none of which uses atomics (the result is bit-reproducible):
 //   1. preprocess: delta and LSE * log2(e) per query row into scratch (rows padded to 128).
-//   2. main: one CTA per (128-key block, kv head, batch) walks the query blocks that see it.
+//   2. dK/dV: one CTA per (128-key block, kv head, batch) walks the query blocks that see it.
 //      Everything is computed TRANSPOSED so that a thread owns one key row:
-//        S^T  = K Q^T          (SS)  -> TMEM [0,128)     P^T (bf16) overwrites it in place
-//        dP^T = V dO^T         (SS)  -> TMEM [128,256)
-//        dV  += P^T dO         (A = P^T from TMEM)        -> TMEM [256,384)
-//        dK  += dS^T Q         (A = dS^T from shared)     -> TMEM [384,512)
-//        dQ   = dS K           (SS)  -> TMEM [128,256), added to an f32 dQ accumulator in global
-//                                      memory by TMA reduce operations issued by a dedicated
-//                                      warp group (staged through shared memory).
-//      dS^T is written once to shared memory in the 128-byte-swizzled layout that serves both as
-//      the K-major A operand of the dK product and as the MN-major A operand of the dQ product.
-//   3. postprocess: dQ accumulator f32 -> bf16.
-// Scratch: dQ accumulator [B, Sq, H, D] f32, then LSE2 and delta [B, H, Sq_pad] f32.
+//        S^T  = K Q^T   (SS) -> TMEM [0,128)     P^T (bf16) overwrites it in place
+//        dP^T = V dO^T  (SS) -> TMEM [128,256)
+//        dV  += P^T dO  (A = P^T from TMEM)      -> TMEM [256,384)
+//        dK  += dS^T Q  (A = dS^T from shared)   -> TMEM [384,512)
+//   3. dQ: one CTA per (128-query block, head, batch) walks the key blocks it sees and recomputes
+//      S and dP (two extra products per block pair) so that dQ accumulates in TMEM instead of
+//      being reduced through global memory from the dK/dV kernel -- measured on B200, the L2
+//      reduction traffic of that single-kernel form (64 KiB per block pair) took longer than the
+//      two recomputed products:
+//        S  = Q K^T   (SS) -> TMEM S[j & 1]      dS (bf16) overwrites it in place
+//        dP = dO V^T  (SS) -> TMEM [256,384)
+//        dQ += dS K   (A = dS from TMEM)          -> TMEM [384,512)
+// Scratch: LSE2 and delta, f32 [B, H, Sq_pad] each.
 #include "host.h"
 #include "ptx.cuh"
 
@@ -43,14 +45,16 @@ constexpr int BQ = 128;
 constexpr int BKV = 128;
 constexpr int TILE_BYTES = 128 * 128 * 2;
 constexpr int PANEL_BYTES = TILE_BYTES / 2;
-constexpr int THREADS = 512;  // warps 0-3 control (TMA, MMA, 2 idle), 4-11 compute, 12-15 dQ reduce
-constexpr int DQ_CHUNK_BYTES = 128 * 32 * 4;  // 128 query rows x 32 head-dim columns of f32
+constexpr int THREADS = 384;  // warps 0-3 control (TMA, MMA, 2 idle), warps 4-11 compute
 constexpr int TMEM_COLS = 512;
-constexpr int COL_S = 0, COL_DP = 128, COL_DV = 256, COL_DK = 384;
-// K, V, Q x 2 stages, dO, dS^T, 2 dQ staging chunks
-constexpr size_t SMEM_BYTES =
-    6 * TILE_BYTES + 2 * DQ_CHUNK_BYTES + 2 * 2 * 128 * sizeof(float) + 256;
-static_assert(SMEM_BYTES <= 232448, "exceeds the 227 KiB of shared memory a CTA can opt in to");
+// dK/dV kernel: K, V, Q x 2 stages, dO x 2 stages, dS^T, row statistics, barriers
+constexpr int KV_COL_S = 0, KV_COL_DP = 128, KV_COL_DV = 256, KV_COL_DK = 384;
+constexpr size_t KV_SMEM_BYTES = 7 * TILE_BYTES + 2 * 2 * 128 * sizeof(float) + 256;
+// dQ kernel: Q, dO, K x 2 stages, V x 2 stages, barriers
+constexpr int Q_COL_S = 0, Q_COL_DP = 256, Q_COL_DQ = 384;  // S is double-buffered: [0,128) [128,256)
+constexpr size_t Q_SMEM_BYTES = 6 * TILE_BYTES + 256;
+static_assert(KV_SMEM_BYTES <= 232448 && Q_SMEM_BYTES <= 232448,
+              "exceeds the 227 KiB of shared memory a CTA can opt in to");
 
 struct Params {
   int B, H, Hkv, Sq, Sk, Sq_pad;
@@ -58,17 +62,25 @@ struct Params {
   float scale, scale_log2;
   const float* lse2;   // [B, H, Sq_pad]  LSE * log2(e), +inf for rows that contribute nothing
   const float* delta;  // [B, H, Sq_pad]
+  __nv_bfloat16* dq;
   __nv_bfloat16* dk;
   __nv_bfloat16* dv;
-  long long dk_sb, dk_ss, dk_sh, dv_sb, dv_ss, dv_sh;
+  long long dq_sb, dq_ss, dq_sh, dk_sb, dk_ss, dk_sh, dv_sb, dv_ss, dv_sh;
   int* status;
 };
 
-struct Barriers {
+struct KvBarriers {
   uint64_t kv_full;
-  uint64_t q_full[2], q_empty[2];
-  uint64_t do_full, do_empty;
-  uint64_t s_full, dp_full, p_ready, ds_ready, dq_full, dq_read;
+  uint64_t q_full[2], q_empty[2], do_full[2], do_empty[2];
+  uint64_t s_full, dp_full, p_ready, ds_ready, dk_done;
+  uint32_t tmem_base;
+  int abort_word;
+};
+
+struct QBarriers {
+  uint64_t qdo_full;
+  uint64_t k_full[2], k_empty[2], v_full[2], v_empty[2];
+  uint64_t s_full[2], dp_full, ds_ready, dq_done;
   uint32_t tmem_base;
   int abort_word;
 };
@@ -82,8 +94,16 @@ __device__ __forceinline__ float ex2(float x) {
 __device__ __forceinline__ void compute_bar_sync() {
   asm volatile("bar.sync 1, 256;" ::: "memory");
 }
-__device__ __forceinline__ void reduce_bar_sync() {
-  asm volatile("bar.sync 2, 128;" ::: "memory");
+
+// Descriptors of one kernel differ only in the start address: the constant part is built once
+// and the 16-byte-granular address goes into the low word.
+__device__ __forceinline__ uint64_t desc_kmajor(uint64_t base, uint32_t addr, int k) {
+  // 128 x 128 bf16 tile as two 64-wide K panels; one MMA covers 16 elements of K (32 bytes)
+  return base | static_cast<uint64_t>(((addr + (k >> 2) * PANEL_BYTES + (k & 3) * 32) & 0x3FFFFu) >> 4);
+}
+__device__ __forceinline__ uint64_t desc_mnmajor(uint64_t base, uint32_t addr, int k) {
+  // rows are the K index (128 bytes each); one MMA covers 16 rows
+  return base | static_cast<uint64_t>(((addr + k * 2048) & 0x3FFFFu) >> 4);
 }
 
 // ---------------------------------------------------------------- preprocess
@@ -126,38 +146,15 @@ __global__ void __launch_bounds__(256)
   }
 }
 
-// ---------------------------------------------------------------- postprocess
-__global__ void __launch_bounds__(256)
-    attn_bwd_convert_dq_kernel(const float* __restrict__ acc, __nv_bfloat16* __restrict__ dq,
-                               long long dq_sb, long long dq_ss, long long dq_sh, int B, int Sq,
-                               int H) {
-  // one thread per 8 consecutive d
-  const long long idx = static_cast<long long>(blockIdx.x) * 256 + threadIdx.x;
-  const long long total = static_cast<long long>(B) * Sq * H * (D / 8);
-  if (idx >= total) return;
-  const int d8 = static_cast<int>(idx % (D / 8));
-  const int h = static_cast<int>((idx / (D / 8)) % H);
-  const int s = static_cast<int>((idx / (D / 8) / H) % Sq);
-  const int b = static_cast<int>(idx / (D / 8) / H / Sq);
-  const float4 a0 = *reinterpret_cast<const float4*>(acc + idx * 8);
-  const float4 a1 = *reinterpret_cast<const float4*>(acc + idx * 8 + 4);
-  uint4 q;
-  q.x = pack_bf16x2(a0.x, a0.y);
-  q.y = pack_bf16x2(a0.z, a0.w);
-  q.z = pack_bf16x2(a1.x, a1.y);
-  q.w = pack_bf16x2(a1.z, a1.w);
-  *reinterpret_cast<uint4*>(dq + b * dq_sb + s * dq_ss + h * dq_sh + d8 * 8) = q;
-}
 
-// ---------------------------------------------------------------- main kernel
+// ---------------------------------------------------------------- dK / dV kernel
 __global__ void __launch_bounds__(THREADS, 1)
-    attn_bwd_kernel(const __grid_constant__ CUtensorMap tmap_q,
-                    const __grid_constant__ CUtensorMap tmap_k,
-                    const __grid_constant__ CUtensorMap tmap_v,
-                    const __grid_constant__ CUtensorMap tmap_do,
-                    const __grid_constant__ CUtensorMap tmap_dq, const Params p) {
-  // 227 KiB are used to the last kilobyte, so there is no room for manual alignment slack: the
-  // 1024-byte alignment the swizzled tiles need is requested from the compiler and verified.
+    attn_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap tmap_q,
+                         const __grid_constant__ CUtensorMap tmap_k,
+                         const __grid_constant__ CUtensorMap tmap_v,
+                         const __grid_constant__ CUtensorMap tmap_do, const Params p) {
+  // Shared memory is used to the last kilobytes, so there is no room for manual alignment slack:
+  // the 1024-byte alignment the swizzled tiles need is requested from the compiler and verified.
   extern __shared__ __align__(1024) uint8_t smem[];
   if ((smem_u32(smem) & 1023u) != 0) {
     if (threadIdx.x == 0) atomicExch(p.status, 901);
@@ -165,13 +162,12 @@ __global__ void __launch_bounds__(THREADS, 1)
   }
   uint8_t* s_k = smem;
   uint8_t* s_v = smem + TILE_BYTES;
-  uint8_t* s_q = smem + 2 * TILE_BYTES;  // 2 stages
-  uint8_t* s_do = smem + 4 * TILE_BYTES;
-  uint8_t* s_ds = smem + 5 * TILE_BYTES;
-  uint8_t* s_dq = smem + 6 * TILE_BYTES;  // 2 staging chunks for the dQ reduction
-  float* s_lse = reinterpret_cast<float*>(smem + 6 * TILE_BYTES + 2 * DQ_CHUNK_BYTES);  // [2][128]
+  uint8_t* s_q = smem + 2 * TILE_BYTES;   // 2 stages
+  uint8_t* s_do = smem + 4 * TILE_BYTES;  // 2 stages
+  uint8_t* s_ds = smem + 6 * TILE_BYTES;
+  float* s_lse = reinterpret_cast<float*>(smem + 7 * TILE_BYTES);  // [2][128]
   float* s_delta = s_lse + 2 * 128;                                // [2][128]
-  Barriers* bars = reinterpret_cast<Barriers*>(s_delta + 2 * 128);
+  KvBarriers* bars = reinterpret_cast<KvBarriers*>(s_delta + 2 * 128);
   volatile int* abort_word = &bars->abort_word;
 
   const int warp = threadIdx.x >> 5;
@@ -185,22 +181,22 @@ __global__ void __launch_bounds__(THREADS, 1)
   const int num_q_blocks = (p.Sq + BQ - 1) / BQ;
   const int m_start = p.causal ? max(0, key0 - shift) / BQ : 0;
   const int m_count = max(0, num_q_blocks - m_start);
-  const int iters = m_count * group;  // iteration it -> head kvh*group + it / m_count, block m_start + it % m_count
+  // iteration it -> head kvh * group + it / m_count, query block m_start + it % m_count
+  const int iters = m_count * group;
 
   if (threadIdx.x == 0) {
     mbar_init(&bars->kv_full, 1);
     for (int i = 0; i < 2; ++i) {
       mbar_init(&bars->q_full[i], 1);
       mbar_init(&bars->q_empty[i], 1);
+      mbar_init(&bars->do_full[i], 1);
+      mbar_init(&bars->do_empty[i], 1);
     }
-    mbar_init(&bars->do_full, 1);
-    mbar_init(&bars->do_empty, 1);
     mbar_init(&bars->s_full, 1);
     mbar_init(&bars->dp_full, 1);
     mbar_init(&bars->p_ready, 256);
     mbar_init(&bars->ds_ready, 256);
-    mbar_init(&bars->dq_full, 1);
-    mbar_init(&bars->dq_read, 128);
+    mbar_init(&bars->dk_done, 1);
     bars->abort_word = 0;
     fence_mbar_init();
   }
@@ -213,7 +209,6 @@ __global__ void __launch_bounds__(THREADS, 1)
     tma_prefetch_desc(&tmap_k);
     tma_prefetch_desc(&tmap_v);
     tma_prefetch_desc(&tmap_do);
-    tma_prefetch_desc(&tmap_dq);
   }
   tc_fence_before();
   __syncthreads();
@@ -222,7 +217,7 @@ __global__ void __launch_bounds__(THREADS, 1)
 
   if (warp == 0) {
     // ------------------------------------------------------------ TMA producer
-    setmaxnreg_dec<40>();
+    setmaxnreg_dec<56>();
     if (elect_one() && iters > 0) {
       mbar_arrive_expect_tx(&bars->kv_full, 2 * TILE_BYTES);
 #pragma unroll
@@ -234,149 +229,112 @@ __global__ void __launch_bounds__(THREADS, 1)
         const int h = kvh * group + it / m_count;
         const int q0 = (m_start + it % m_count) * BQ;
         const int s = it & 1;
-        if (!mbar_wait(&bars->q_empty[s], ((it >> 1) & 1) ^ 1, abort_word, 121)) break;
+        const uint32_t ph = ((it >> 1) & 1) ^ 1;
+        if (!mbar_wait(&bars->q_empty[s], ph, abort_word, 121)) break;
         mbar_arrive_expect_tx(&bars->q_full[s], TILE_BYTES);
 #pragma unroll
         for (int dh = 0; dh < 2; ++dh)
           tma_load_4d(s_q + s * TILE_BYTES + dh * PANEL_BYTES, &tmap_q, &bars->q_full[s], dh * 64,
                       q0, h, b);
-        if (!mbar_wait(&bars->do_empty, (it & 1) ^ 1, abort_word, 122)) break;
-        mbar_arrive_expect_tx(&bars->do_full, TILE_BYTES);
+        if (!mbar_wait(&bars->do_empty[s], ph, abort_word, 122)) break;
+        mbar_arrive_expect_tx(&bars->do_full[s], TILE_BYTES);
 #pragma unroll
         for (int dh = 0; dh < 2; ++dh)
-          tma_load_4d(s_do + dh * PANEL_BYTES, &tmap_do, &bars->do_full, dh * 64, q0, h, b);
+          tma_load_4d(s_do + s * TILE_BYTES + dh * PANEL_BYTES, &tmap_do, &bars->do_full[s],
+                      dh * 64, q0, h, b);
       }
     }
   } else if (warp == 1) {
     // ------------------------------------------------------------ MMA issuer
-    // Issue order per iteration: dP^T(it), dV(it), S^T(it+1), dK(it), dQ(it).  S^T of the next
-    // query block is issued before this block's dK / dQ so the compute warps can turn it into
-    // P^T while those two products run.
-    setmaxnreg_dec<40>();
+    // Issue order: dV(it), S^T(it+1), dK(it), dP^T(it+1): the products of the next query block
+    // that do not depend on this block's dS^T are issued before the one that does, so the
+    // compute warps always find their next input ready.
+    setmaxnreg_dec<56>();
     if (elect_one() && iters > 0) {
       const uint32_t idesc_kk = make_idesc_bf16(128, 128, 0, 0);  // both operands K-major
       const uint32_t idesc_kmn = make_idesc_bf16(128, 128, 0, 1); // A K-major / TMEM, B MN-major
-      const uint32_t idesc_mnmn = make_idesc_bf16(128, 128, 1, 1);
+      const uint64_t dk_base = smem_desc_sw128(0, 16, 1024);
+      const uint64_t dmn_base = smem_desc_sw128(0, PANEL_BYTES, 1024);
       const uint32_t k_addr = smem_u32(s_k), v_addr = smem_u32(s_v), q_addr = smem_u32(s_q);
       const uint32_t do_addr = smem_u32(s_do), ds_addr = smem_u32(s_ds);
-      auto koff = [](int k) { return static_cast<uint32_t>((k >> 2) * PANEL_BYTES + (k & 3) * 32); };
       auto issue_s = [&](int it) {  // S^T = K Q^T
         const uint32_t qa = q_addr + (it & 1) * TILE_BYTES;
 #pragma unroll
         for (int k = 0; k < 8; ++k)
-          umma_ss(tmem_base + COL_S, smem_desc_sw128(k_addr + koff(k), 16, 1024),
-                  smem_desc_sw128(qa + koff(k), 16, 1024), idesc_kk, k != 0);
+          umma_ss(tmem_base + KV_COL_S, desc_kmajor(dk_base, k_addr, k), desc_kmajor(dk_base, qa, k),
+                  idesc_kk, k != 0);
         umma_commit(&bars->s_full);
+      };
+      auto issue_dp = [&](int it) {  // dP^T = V dO^T
+        const uint32_t da = do_addr + (it & 1) * TILE_BYTES;
+#pragma unroll
+        for (int k = 0; k < 8; ++k)
+          umma_ss(tmem_base + KV_COL_DP, desc_kmajor(dk_base, v_addr, k), desc_kmajor(dk_base, da, k),
+                  idesc_kk, k != 0);
+        umma_commit(&bars->dp_full);
       };
       bool ok = mbar_wait(&bars->kv_full, 0, abort_word, 221) &&
                 mbar_wait(&bars->q_full[0], 0, abort_word, 222);
       if (ok) {
         tc_fence_after();
         issue_s(0);
+        ok = mbar_wait(&bars->do_full[0], 0, abort_word, 223);
+      }
+      if (ok) {
+        tc_fence_after();
+        issue_dp(0);
       }
       for (int it = 0; it < iters && ok; ++it) {
         const int s = it & 1;
         const uint32_t ph = it & 1;
-        const uint32_t qa = q_addr + s * TILE_BYTES;
-        // dP^T = V dO^T  (its TMEM columns held dQ of the previous iteration)
-        ok = mbar_wait(&bars->do_full, ph, abort_word, 223);
-        if (ok && it > 0) ok = mbar_wait(&bars->dq_read, (it - 1) & 1, abort_word, 224);
-        if (!ok) break;
-        tc_fence_after();
-#pragma unroll
-        for (int k = 0; k < 8; ++k)
-          umma_ss(tmem_base + COL_DP, smem_desc_sw128(v_addr + koff(k), 16, 1024),
-                  smem_desc_sw128(do_addr + koff(k), 16, 1024), idesc_kk, k != 0);
-        umma_commit(&bars->dp_full);
+        const uint32_t ph_next = ((it + 1) >> 1) & 1;
+        const uint32_t qa = q_addr + s * TILE_BYTES, da = do_addr + s * TILE_BYTES;
         // dV += P^T dO
         ok = mbar_wait(&bars->p_ready, ph, abort_word, 225);
         if (!ok) break;
         tc_fence_after();
 #pragma unroll
         for (int k = 0; k < 8; ++k)
-          umma_ts(tmem_base + COL_DV, tmem_base + COL_S + k * 8,
-                  smem_desc_sw128(do_addr + k * 2048, PANEL_BYTES, 1024), idesc_kmn,
-                  (it > 0 || k != 0) ? 1u : 0u);
-        // dO is free once dP^T and dV have read it: this commit covers both.
-        umma_commit(&bars->do_empty);
+          umma_ts(tmem_base + KV_COL_DV, tmem_base + KV_COL_S + k * 8, desc_mnmajor(dmn_base, da, k),
+                  idesc_kmn, (it > 0 || k != 0) ? 1u : 0u);
+        umma_commit(&bars->do_empty[s]);  // dP^T(it) and dV(it) were the readers of this dO stage
         // S^T of the next query block; it overwrites P^T, which dV (issued above) reads first.
         if (it + 1 < iters) {
-          ok = mbar_wait(&bars->q_full[s ^ 1], ((it + 1) >> 1) & 1, abort_word, 227);
+          ok = mbar_wait(&bars->q_full[s ^ 1], ph_next, abort_word, 227);
           if (!ok) break;
           tc_fence_after();
           issue_s(it + 1);
         }
-        // dK += dS^T Q ;  dQ = dS K   (dS^T tile: K-major A for dK, MN-major A for dQ)
+        // dK += dS^T Q
         ok = mbar_wait(&bars->ds_ready, ph, abort_word, 226);
         if (!ok) break;
         tc_fence_after();
 #pragma unroll
         for (int k = 0; k < 8; ++k)
-          umma_ss(tmem_base + COL_DK, smem_desc_sw128(ds_addr + koff(k), 16, 1024),
-                  smem_desc_sw128(qa + k * 2048, PANEL_BYTES, 1024), idesc_kmn,
-                  (it > 0 || k != 0) ? 1u : 0u);
+          umma_ss(tmem_base + KV_COL_DK, desc_kmajor(dk_base, ds_addr, k), desc_mnmajor(dmn_base, qa, k),
+                  idesc_kmn, (it > 0 || k != 0) ? 1u : 0u);
         umma_commit(&bars->q_empty[s]);
-#pragma unroll
-        for (int k = 0; k < 8; ++k)
-          umma_ss(tmem_base + COL_DP, smem_desc_sw128(ds_addr + k * 2048, PANEL_BYTES, 1024),
-                  smem_desc_sw128(k_addr + k * 2048, PANEL_BYTES, 1024), idesc_mnmn, k != 0);
-        umma_commit(&bars->dq_full);
+        // dP^T of the next block: its TMEM columns were read by the dS^T phase that just arrived.
+        if (it + 1 < iters) {
+          ok = mbar_wait(&bars->do_full[s ^ 1], ph_next, abort_word, 228);
+          if (!ok) break;
+          tc_fence_after();
+          issue_dp(it + 1);
+        }
       }
+      if (ok) umma_commit(&bars->dk_done);
     }
   } else if (warp < 4) {
-    setmaxnreg_dec<40>();
-  } else if (warp >= 12) {
-    // ------------------------------------------------------------ dQ reduction warps (12..15)
-    // One thread per query row.  The dQ tile is moved TMEM -> registers -> swizzled shared
-    // memory in four 32-column chunks (two staging buffers) and added to the f32 accumulator in
-    // global memory by TMA reduce operations, so no atomic instruction goes through the LSU.
-    setmaxnreg_dec<72>();
-    const int quad = warp & 3;
-    const int r = quad * 32 + lane;
-    const uint32_t lane_addr = static_cast<uint32_t>(quad * 32) << 16;
-    const bool leader = threadIdx.x == 12 * 32;
-    bool ok = true;
-    for (int it = 0; it < iters && ok; ++it) {
-      const int h = kvh * group + it / m_count;
-      const int q0 = (m_start + it % m_count) * BQ;
-      if (!mbar_wait(&bars->dq_full, it & 1, abort_word, 421)) { ok = false; break; }
-      tc_fence_after();
-#pragma unroll 1
-      for (int c = 0; c < 4; ++c) {
-        uint8_t* stage = s_dq + (c & 1) * DQ_CHUNK_BYTES;
-        // The reduce issued from this staging buffer two chunks ago must have read it.
-        if (leader) tma_store_wait_read<1>();
-        reduce_bar_sync();
-        uint32_t v[32];
-        tmem_ld32(tmem_base + lane_addr + COL_DP + c * 32, v);
-        tmem_wait_ld();
-        if (c == 3) {
-          tc_fence_before();
-          mbar_arrive(&bars->dq_read);  // the tile is out of TMEM: dP^T of the next block may land
-        }
-        uint8_t* row_ptr = stage + r * 128;
-#pragma unroll
-        for (int ch = 0; ch < 8; ++ch)
-          *reinterpret_cast<uint4*>(row_ptr + ((ch ^ (r & 7)) << 4)) =
-              make_uint4(v[ch * 4], v[ch * 4 + 1], v[ch * 4 + 2], v[ch * 4 + 3]);
-        fence_proxy_async_smem();
-        reduce_bar_sync();
-        if (leader) {
-          tma_reduce_add_4d(&tmap_dq, stage, c * 32, h, q0, b);
-          tma_store_commit();
-        }
-      }
-    }
-    if (leader) tma_store_wait<0>();
+    setmaxnreg_dec<56>();
   } else {
     // ------------------------------------------------------------ compute warps (4..11)
-    // Software pipeline per iteration: dS(it), then P(it+1), which runs while the tensor core
-    // computes dK(it) and dQ(it).
-    setmaxnreg_inc<200>();
+    // Per iteration: dS^T(it) from dP^T(it) and the P^T kept in registers, then P^T(it+1), which
+    // overlaps the dK product of this block.
+    setmaxnreg_inc<224>();
     const int ct = threadIdx.x - 128;  // 0..255
-    const int wg = (warp - 4) >> 2;    // column half this thread works on
+    const int wg = (warp - 4) >> 2;    // column (query) half this thread works on
     const int quad = warp & 3;
-    const int r = quad * 32 + lane;    // row inside the block == TMEM lane
+    const int r = quad * 32 + lane;    // key row inside the block == TMEM lane
     const uint32_t lane_addr = static_cast<uint32_t>(quad * 32) << 16;
     const int key = key0 + r;
     bool ok = true;
@@ -394,7 +352,7 @@ __global__ void __launch_bounds__(THREADS, 1)
     };
     float pr[64];
 
-    // P^T(it) = exp2(S^T * scale_log2 - lse2) -> registers and (bf16) TMEM
+    // P^T(it) = exp2(S^T * scale_log2 - lse2) -> registers (f32) and TMEM (bf16)
     auto p_phase = [&](int it) -> bool {
       const int q0 = it_q0(it);
       const float4* lse_s = reinterpret_cast<const float4*>(s_lse + (it & 1) * 128 + wg * 64);
@@ -403,8 +361,8 @@ __global__ void __launch_bounds__(THREADS, 1)
       tc_fence_after();
       {
         uint32_t sr[2][32];
-        tmem_ld32(tmem_base + lane_addr + COL_S + wg * 64, sr[0]);
-        tmem_ld32(tmem_base + lane_addr + COL_S + wg * 64 + 32, sr[1]);
+        tmem_ld32(tmem_base + lane_addr + KV_COL_S + wg * 64, sr[0]);
+        tmem_ld32(tmem_base + lane_addr + KV_COL_S + wg * 64 + 32, sr[1]);
         tmem_wait_ld();
 #pragma unroll
         for (int c4 = 0; c4 < 16; ++c4) {
@@ -427,7 +385,7 @@ __global__ void __launch_bounds__(THREADS, 1)
         uint32_t pk[32];
 #pragma unroll
         for (int c = 0; c < 32; ++c) pk[c] = pack_bf16x2(pr[2 * c], pr[2 * c + 1]);
-        tmem_st32(tmem_base + lane_addr + COL_S + wg * 32, pk);
+        tmem_st32(tmem_base + lane_addr + KV_COL_S + wg * 32, pk);
         tmem_wait_st();
       }
       tc_fence_before();
@@ -453,8 +411,8 @@ __global__ void __launch_bounds__(THREADS, 1)
       {
         const float4* delta_s = reinterpret_cast<const float4*>(s_delta + (it & 1) * 128 + wg * 64);
         uint32_t dr[2][32];
-        tmem_ld32(tmem_base + lane_addr + COL_DP + wg * 64, dr[0]);
-        tmem_ld32(tmem_base + lane_addr + COL_DP + wg * 64 + 32, dr[1]);
+        tmem_ld32(tmem_base + lane_addr + KV_COL_DP + wg * 64, dr[0]);
+        tmem_ld32(tmem_base + lane_addr + KV_COL_DP + wg * 64 + 32, dr[1]);
         tmem_wait_ld();
         uint8_t* row_ptr = s_ds + wg * PANEL_BYTES + r * 128;
 #pragma unroll
@@ -479,7 +437,7 @@ __global__ void __launch_bounds__(THREADS, 1)
       fence_proxy_async_smem();
       mbar_arrive(&bars->ds_ready);
 
-      // ---- P^T of the next query block (overlaps the dK / dQ products of this one)
+      // ---- P^T of the next query block (overlaps the dK product of this one)
       if (it + 1 < iters && !p_phase(it + 1)) { ok = false; break; }
 
       // Statistics of iteration it + 2 replace those of iteration it (all reads of them are
@@ -489,10 +447,9 @@ __global__ void __launch_bounds__(THREADS, 1)
       compute_bar_sync();
     }
 
-    // ---- epilogue: dV and dK rows of this key block (every product has finished once the last
-    // dQ commit has arrived)
+    // ---- epilogue: dV and dK rows of this key block
     if (ok && iters > 0) {
-      ok = mbar_wait(&bars->dq_full, (iters - 1) & 1, abort_word, 324);
+      ok = mbar_wait(&bars->dk_done, 0, abort_word, 324);
       tc_fence_after();
     }
     if (ok) {
@@ -502,7 +459,7 @@ __global__ void __launch_bounds__(THREADS, 1)
 #pragma unroll
       for (int which = 0; which < 2; ++which) {
         __nv_bfloat16* dst = which == 0 ? dv_row : dk_row;
-        const uint32_t col = (which == 0 ? COL_DV : COL_DK) + wg * 64;
+        const uint32_t col = (which == 0 ? KV_COL_DV : KV_COL_DK) + wg * 64;
 #pragma unroll
         for (int half = 0; half < 2; ++half) {
           uint32_t a[32];
@@ -544,14 +501,277 @@ __global__ void __launch_bounds__(THREADS, 1)
   if (threadIdx.x == 0 && *abort_word != 0) atomicExch(p.status, *abort_word);
 }
 
+// ---------------------------------------------------------------- dQ kernel
+// Number of 128-key blocks the query rows [q0, q0 + 128) see.
+__device__ __forceinline__ int dq_kv_blocks(const Params& p, int q0) {
+  if (q0 >= p.Sq) return 0;
+  int max_key = p.Sk - 1;
+  if (p.causal) max_key = min(max_key, min(q0 + BQ - 1, p.Sq - 1) + p.Sk - p.Sq);
+  return max_key < 0 ? 0 : max_key / BKV + 1;
+}
+
+__global__ void __launch_bounds__(THREADS, 1)
+    attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmap_q,
+                       const __grid_constant__ CUtensorMap tmap_k,
+                       const __grid_constant__ CUtensorMap tmap_v,
+                       const __grid_constant__ CUtensorMap tmap_do, const Params p) {
+  extern __shared__ __align__(1024) uint8_t smem[];
+  if ((smem_u32(smem) & 1023u) != 0) {
+    if (threadIdx.x == 0) atomicExch(p.status, 902);
+    return;
+  }
+  uint8_t* s_q = smem;
+  uint8_t* s_do = smem + TILE_BYTES;
+  uint8_t* s_k = smem + 2 * TILE_BYTES;  // 2 stages
+  uint8_t* s_v = smem + 4 * TILE_BYTES;  // 2 stages
+  QBarriers* bars = reinterpret_cast<QBarriers*>(smem + 6 * TILE_BYTES);
+  volatile int* abort_word = &bars->abort_word;
+
+  const int warp = threadIdx.x >> 5;
+  const int lane = threadIdx.x & 31;
+  const int q_block = gridDim.x - 1 - blockIdx.x;  // most keys first
+  const int h = blockIdx.y;
+  const int b = blockIdx.z;
+  const int kvh = h / (p.H / p.Hkv);
+  const int q0 = q_block * BQ;
+  const int n_kv = dq_kv_blocks(p, q0);
+
+  if (threadIdx.x == 0) {
+    mbar_init(&bars->qdo_full, 1);
+    for (int i = 0; i < 2; ++i) {
+      mbar_init(&bars->k_full[i], 1);
+      mbar_init(&bars->k_empty[i], 1);
+      mbar_init(&bars->v_full[i], 1);
+      mbar_init(&bars->v_empty[i], 1);
+      mbar_init(&bars->s_full[i], 1);
+    }
+    mbar_init(&bars->dp_full, 1);
+    mbar_init(&bars->ds_ready, 256);
+    mbar_init(&bars->dq_done, 1);
+    bars->abort_word = 0;
+    fence_mbar_init();
+  }
+  if (warp == 1) {
+    tmem_alloc(&bars->tmem_base, TMEM_COLS);
+    tmem_relinquish();
+  }
+  if (warp == 0 && lane == 0) {
+    tma_prefetch_desc(&tmap_q);
+    tma_prefetch_desc(&tmap_k);
+    tma_prefetch_desc(&tmap_v);
+    tma_prefetch_desc(&tmap_do);
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = bars->tmem_base;
+
+  if (warp == 0) {
+    // ------------------------------------------------------------ TMA producer
+    setmaxnreg_dec<56>();
+    if (elect_one() && n_kv > 0) {
+      mbar_arrive_expect_tx(&bars->qdo_full, 2 * TILE_BYTES);
+#pragma unroll
+      for (int dh = 0; dh < 2; ++dh) {
+        tma_load_4d(s_q + dh * PANEL_BYTES, &tmap_q, &bars->qdo_full, dh * 64, q0, h, b);
+        tma_load_4d(s_do + dh * PANEL_BYTES, &tmap_do, &bars->qdo_full, dh * 64, q0, h, b);
+      }
+      for (int j = 0; j < n_kv; ++j) {
+        const int s = j & 1;
+        const uint32_t ph = ((j >> 1) & 1) ^ 1;
+        if (!mbar_wait(&bars->k_empty[s], ph, abort_word, 131)) break;
+        mbar_arrive_expect_tx(&bars->k_full[s], TILE_BYTES);
+#pragma unroll
+        for (int dh = 0; dh < 2; ++dh)
+          tma_load_4d(s_k + s * TILE_BYTES + dh * PANEL_BYTES, &tmap_k, &bars->k_full[s], dh * 64,
+                      j * BKV, kvh, b);
+        if (!mbar_wait(&bars->v_empty[s], ph, abort_word, 132)) break;
+        mbar_arrive_expect_tx(&bars->v_full[s], TILE_BYTES);
+#pragma unroll
+        for (int dh = 0; dh < 2; ++dh)
+          tma_load_4d(s_v + s * TILE_BYTES + dh * PANEL_BYTES, &tmap_v, &bars->v_full[s], dh * 64,
+                      j * BKV, kvh, b);
+      }
+    }
+  } else if (warp == 1) {
+    // ------------------------------------------------------------ MMA issuer
+    // Issue order: S(j+1) [other S buffer], then after dS(j) has arrived dP(j+1) and dQ(j).
+    setmaxnreg_dec<56>();
+    if (elect_one() && n_kv > 0) {
+      const uint32_t idesc_kk = make_idesc_bf16(128, 128, 0, 0);
+      const uint32_t idesc_kmn = make_idesc_bf16(128, 128, 0, 1);
+      const uint64_t dk_base = smem_desc_sw128(0, 16, 1024);
+      const uint64_t dmn_base = smem_desc_sw128(0, PANEL_BYTES, 1024);
+      const uint32_t q_addr = smem_u32(s_q), do_addr = smem_u32(s_do);
+      const uint32_t k_addr = smem_u32(s_k), v_addr = smem_u32(s_v);
+      auto issue_s = [&](int j) {  // S = Q K_j^T
+        const uint32_t ka = k_addr + (j & 1) * TILE_BYTES;
+#pragma unroll
+        for (int k = 0; k < 8; ++k)
+          umma_ss(tmem_base + Q_COL_S + (j & 1) * 128, desc_kmajor(dk_base, q_addr, k),
+                  desc_kmajor(dk_base, ka, k), idesc_kk, k != 0);
+        umma_commit(&bars->s_full[j & 1]);
+      };
+      auto issue_dp = [&](int j) {  // dP = dO V_j^T
+        const uint32_t va = v_addr + (j & 1) * TILE_BYTES;
+#pragma unroll
+        for (int k = 0; k < 8; ++k)
+          umma_ss(tmem_base + Q_COL_DP, desc_kmajor(dk_base, do_addr, k), desc_kmajor(dk_base, va, k),
+                  idesc_kk, k != 0);
+        umma_commit(&bars->dp_full);
+        umma_commit(&bars->v_empty[j & 1]);
+      };
+      bool ok = mbar_wait(&bars->qdo_full, 0, abort_word, 231) &&
+                mbar_wait(&bars->k_full[0], 0, abort_word, 232);
+      if (ok) {
+        tc_fence_after();
+        issue_s(0);
+        ok = mbar_wait(&bars->v_full[0], 0, abort_word, 233);
+      }
+      if (ok) {
+        tc_fence_after();
+        issue_dp(0);
+      }
+      for (int j = 0; j < n_kv && ok; ++j) {
+        const int s = j & 1;
+        const uint32_t ph_next = ((j + 1) >> 1) & 1;
+        if (j + 1 < n_kv) {
+          // S buffer s ^ 1 held dS(j-1), whose reader dQ(j-1) was issued before this point.
+          ok = mbar_wait(&bars->k_full[s ^ 1], ph_next, abort_word, 234);
+          if (!ok) break;
+          tc_fence_after();
+          issue_s(j + 1);
+        }
+        ok = mbar_wait(&bars->ds_ready, j & 1, abort_word, 235);
+        if (!ok) break;
+        tc_fence_after();
+        if (j + 1 < n_kv) {
+          ok = mbar_wait(&bars->v_full[s ^ 1], ph_next, abort_word, 236);
+          if (!ok) break;
+          tc_fence_after();
+          issue_dp(j + 1);
+        }
+        // dQ += dS K_j : A = dS (bf16 pairs in the S buffer's first 64 columns), B = K_j MN-major
+        const uint32_t ka = k_addr + s * TILE_BYTES;
+#pragma unroll
+        for (int k = 0; k < 8; ++k)
+          umma_ts(tmem_base + Q_COL_DQ, tmem_base + Q_COL_S + s * 128 + k * 8,
+                  desc_mnmajor(dmn_base, ka, k), idesc_kmn, (j > 0 || k != 0) ? 1u : 0u);
+        umma_commit(&bars->k_empty[s]);
+      }
+      if (ok) umma_commit(&bars->dq_done);
+    }
+  } else if (warp < 4) {
+    setmaxnreg_dec<56>();
+  } else {
+    // ------------------------------------------------------------ compute warps (4..11)
+    setmaxnreg_inc<224>();
+    const int wg = (warp - 4) >> 2;  // key-column half this thread works on
+    const int quad = warp & 3;
+    const int r = quad * 32 + lane;  // query row inside the block == TMEM lane
+    const uint32_t lane_addr = static_cast<uint32_t>(quad * 32) << 16;
+    const int row = q0 + r;
+    const int shift = p.Sk - p.Sq;
+    const long long stat_idx = (static_cast<long long>(b) * p.H + h) * p.Sq_pad + row;
+    const float lse2 = p.lse2[stat_idx];   // +inf for rows that contribute nothing (and padding)
+    const float delta = p.delta[stat_idx];
+    const int key_limit = p.causal ? min(p.Sk - 1, row + shift) : p.Sk - 1;
+    const int warp_limit = p.causal ? min(p.Sk - 1, q0 + quad * 32 + shift) : p.Sk - 1;
+    bool ok = true;
+    for (int j = 0; j < n_kv; ++j) {
+      const int s = j & 1;
+      const int key0 = j * BKV + wg * 64;
+      const bool need_mask = key0 + 63 > warp_limit;  // warp-uniform
+      if (!mbar_wait(&bars->s_full[s], (j >> 1) & 1, abort_word, 331)) { ok = false; break; }
+      tc_fence_after();
+      float pr[64];
+      {
+        uint32_t sr[2][32];
+        tmem_ld32(tmem_base + lane_addr + Q_COL_S + s * 128 + wg * 64, sr[0]);
+        tmem_ld32(tmem_base + lane_addr + Q_COL_S + s * 128 + wg * 64 + 32, sr[1]);
+        tmem_wait_ld();
+#pragma unroll
+        for (int c = 0; c < 64; ++c) {
+          float v = ex2(fmaf(__uint_as_float(sr[c >> 5][c & 31]), p.scale_log2, -lse2));
+          if (need_mask && key0 + c > key_limit) v = 0.f;
+          pr[c] = v;
+        }
+      }
+      if (!mbar_wait(&bars->dp_full, j & 1, abort_word, 332)) { ok = false; break; }
+      tc_fence_after();
+      uint32_t pk[32];
+      {
+        uint32_t dr[2][32];
+        tmem_ld32(tmem_base + lane_addr + Q_COL_DP + wg * 64, dr[0]);
+        tmem_ld32(tmem_base + lane_addr + Q_COL_DP + wg * 64 + 32, dr[1]);
+        tmem_wait_ld();
+#pragma unroll
+        for (int c = 0; c < 32; ++c) {
+          const float d0 = pr[2 * c] * (__uint_as_float(dr[(2 * c) >> 5][(2 * c) & 31]) - delta) * p.scale;
+          const float d1 = pr[2 * c + 1] * (__uint_as_float(dr[(2 * c + 1) >> 5][(2 * c + 1) & 31]) - delta) * p.scale;
+          pk[c] = pack_bf16x2(d0, d1);
+        }
+      }
+      compute_bar_sync();  // both halves have read S before dS overwrites its first 64 columns
+      tmem_st32(tmem_base + lane_addr + Q_COL_S + s * 128 + wg * 32, pk);
+      tmem_wait_st();
+      tc_fence_before();
+      mbar_arrive(&bars->ds_ready);
+    }
+
+    // ---- epilogue: this thread's 64 columns of its dQ row
+    if (ok && n_kv > 0) {
+      ok = mbar_wait(&bars->dq_done, 0, abort_word, 333);
+      tc_fence_after();
+    }
+    if (ok && q0 < p.Sq) {
+      __nv_bfloat16* dst = p.dq + b * p.dq_sb + static_cast<long long>(row) * p.dq_ss + h * p.dq_sh + wg * 64;
+#pragma unroll
+      for (int half = 0; half < 2; ++half) {
+        uint32_t a[32];
+        if (n_kv > 0) {
+          tmem_ld32(tmem_base + lane_addr + Q_COL_DQ + wg * 64 + half * 32, a);
+          tmem_wait_ld();
+        } else {
+#pragma unroll
+          for (int i = 0; i < 32; ++i) a[i] = 0u;
+        }
+        if (row < p.Sq) {
+#pragma unroll
+          for (int g = 0; g < 4; ++g) {
+            uint4 q;
+            q.x = pack_bf16x2(__uint_as_float(a[g * 8 + 0]), __uint_as_float(a[g * 8 + 1]));
+            q.y = pack_bf16x2(__uint_as_float(a[g * 8 + 2]), __uint_as_float(a[g * 8 + 3]));
+            q.z = pack_bf16x2(__uint_as_float(a[g * 8 + 4]), __uint_as_float(a[g * 8 + 5]));
+            q.w = pack_bf16x2(__uint_as_float(a[g * 8 + 6]), __uint_as_float(a[g * 8 + 7]));
+            *reinterpret_cast<uint4*>(dst + half * 32 + g * 8) = q;
+          }
+        }
+      }
+    }
+  }
+
+  // ------------------------------------------------------------ tear-down
+  __syncwarp();
+  if (*abort_word != 0) {
+    const unsigned long long t0 = globaltimer_ns();
+    while (globaltimer_ns() - t0 < 200000ull) __nanosleep(1000);
+  }
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 1) {
+    tc_fence_after();
+    tmem_dealloc(tmem_base, TMEM_COLS);
+  }
+  if (threadIdx.x == 0 && *abort_word != 0) atomicExch(p.status, *abort_word);
+}
+
 static long long pad128(long long v) { return (v + 127) / 128 * 128; }
 
 }  // namespace attn_bwd
 
 size_t attn_bwd_scratch_bytes(long long B, long long Sq, long long H) {
-  using namespace attn_bwd;
-  return static_cast<size_t>(B) * Sq * H * D * sizeof(float) +
-         2 * static_cast<size_t>(B) * H * pad128(Sq) * sizeof(float);
+  return 2 * static_cast<size_t>(B) * H * attn_bwd::pad128(Sq) * sizeof(float);
 }
 
 int32_t attn_bwd_execute(const cdl_attn_desc* desc, const cdl_tensor* q, const cdl_tensor* k,
@@ -584,7 +804,7 @@ int32_t attn_bwd_execute(const cdl_attn_desc* desc, const cdl_tensor* q, const c
       lse->dtype != CDL_F32)
     return fail(CDL_ERR_INVALID, "%s: lse must be f32 [batch, heads, seqlen_q]", op);
   if (B == 0 || H == 0 || (Sq == 0 && Sk == 0)) return CDL_OK;
-  if (B > 65535 || Hkv > 65535 || Sq > (1 << 30) || Sk > (1 << 30))
+  if (B > 65535 || H > 65535 || Sq > (1 << 30) || Sk > (1 << 30))
     return fail(CDL_ERR_UNSUPPORTED, "%s: dimension too large", op);
   const size_t need = attn_bwd_scratch_bytes(B, Sq, H);
   if (need > 0 && (scratch == nullptr || scratch_bytes < need ||
@@ -593,8 +813,7 @@ int32_t attn_bwd_execute(const cdl_attn_desc* desc, const cdl_tensor* q, const c
                 op, need, scratch_bytes);
 
   const long long Sq_pad = pad128(Sq);
-  float* dq_acc = static_cast<float*>(scratch);
-  float* lse2 = dq_acc + B * Sq * H * D;
+  float* lse2 = static_cast<float*>(scratch);
   float* delta = lse2 + B * H * Sq_pad;
 
   Params p;
@@ -609,16 +828,33 @@ int32_t attn_bwd_execute(const cdl_attn_desc* desc, const cdl_tensor* q, const c
   p.scale_log2 = p.scale * 1.4426950408889634f;
   p.lse2 = lse2;
   p.delta = delta;
+  p.dq = static_cast<__nv_bfloat16*>(dq->ptr);
   p.dk = static_cast<__nv_bfloat16*>(dk->ptr);
   p.dv = static_cast<__nv_bfloat16*>(dv->ptr);
+  p.dq_sb = dq->stride[0]; p.dq_ss = dq->stride[1]; p.dq_sh = dq->stride[2];
   p.dk_sb = dk->stride[0]; p.dk_ss = dk->stride[1]; p.dk_sh = dk->stride[2];
   p.dv_sb = dv->stride[0]; p.dv_ss = dv->stride[1]; p.dv_sh = dv->stride[2];
   p.status = device_status_ptr();
   if (!p.status) return fail(CDL_ERR_CUDA, "cannot resolve the device status word");
 
+  static std::once_flag attr_once[64];
+  int dev = 0;
+  CDL_CUDA(cudaGetDevice(&dev));
+  cudaError_t attr_err = cudaSuccess;
+  std::call_once(attr_once[dev & 63], [&] {
+    attr_err = cudaFuncSetAttribute(attn_bwd_dkdv_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                    static_cast<int>(KV_SMEM_BYTES));
+    if (attr_err == cudaSuccess)
+      attr_err = cudaFuncSetAttribute(attn_bwd_dq_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                      static_cast<int>(Q_SMEM_BYTES));
+  });
+  if (attr_err != cudaSuccess)
+    return fail(CDL_ERR_CUDA, "cudaFuncSetAttribute failed: %s", cudaGetErrorString(attr_err));
+
+  // 14 B H Sq Sk D with the recomputed S and dP of the dQ kernel; reported as the conventional
+  // 10 B H Sq Sk D (2.5 x forward), halved for the causal mask.
   ProfileScope ps(PROF_ATTN_BWD, 10.0 * B * H * Sq * Sk * D * (p.causal ? 0.5 : 1.0), stream);
   if (Sq > 0) {
-    CDL_CUDA(cudaMemsetAsync(dq_acc, 0, static_cast<size_t>(B) * Sq * H * D * sizeof(float), stream));
     const long long items = B * H * Sq_pad;
     const unsigned blocks = static_cast<unsigned>((items * 16 + 255) / 256);
     attn_bwd_preprocess_kernel<<<blocks, 256, 0, stream>>>(
@@ -629,53 +865,31 @@ int32_t attn_bwd_execute(const cdl_attn_desc* desc, const cdl_tensor* q, const c
     CDL_CUDA(cudaGetLastError());
   }
 
+  CUtensorMap tq, tk, tv, tdo;
+  if (Sq > 0) {
+    CDL_CHECK(attn_encode_tmap(&tq, q));
+    CDL_CHECK(attn_encode_tmap(&tdo, d_o));
+  } else {
+    memset(&tq, 0, sizeof tq);
+    tdo = tq;
+  }
   if (Sk > 0) {
-    CUtensorMap tq, tk, tv, tdo;
-    if (Sq > 0) {
-      CDL_CHECK(attn_encode_tmap(&tq, q));
-      CDL_CHECK(attn_encode_tmap(&tdo, d_o));
-    } else {
-      memset(&tq, 0, sizeof tq);
-      tdo = tq;
-    }
     CDL_CHECK(attn_encode_tmap(&tk, k));
     CDL_CHECK(attn_encode_tmap(&tv, v));
-    CUtensorMap tdq;
-    if (Sq > 0) {
-      // f32 accumulator [B, Sq, H, D] seen innermost-first as (D, H, Sq, B); one reduce moves a
-      // 32-column x 128-row chunk of one head.
-      const uint64_t dims[4] = {static_cast<uint64_t>(D), static_cast<uint64_t>(H),
-                                static_cast<uint64_t>(Sq), static_cast<uint64_t>(B)};
-      const uint64_t strides[4] = {0, static_cast<uint64_t>(D) * 4, static_cast<uint64_t>(H) * D * 4,
-                                   static_cast<uint64_t>(Sq) * H * D * 4};
-      const uint32_t box[4] = {32, 1, 128, 1};
-      CDL_CHECK(encode_tmap(&tdq, dq_acc, CDL_F32, 4, dims, strides, box, true));
-    } else {
-      memset(&tdq, 0, sizeof tdq);
-    }
-
-    static std::once_flag attr_once[64];
-    int dev = 0;
-    CDL_CUDA(cudaGetDevice(&dev));
-    cudaError_t attr_err = cudaSuccess;
-    std::call_once(attr_once[dev & 63], [&] {
-      attr_err = cudaFuncSetAttribute(attn_bwd_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                      static_cast<int>(SMEM_BYTES));
-    });
-    if (attr_err != cudaSuccess)
-      return fail(CDL_ERR_CUDA, "cudaFuncSetAttribute failed: %s", cudaGetErrorString(attr_err));
-
+  } else {
+    memset(&tk, 0, sizeof tk);
+    tv = tk;
+  }
+  if (Sk > 0) {
     dim3 grid(static_cast<unsigned>((Sk + BKV - 1) / BKV), static_cast<unsigned>(Hkv),
               static_cast<unsigned>(B));
-    attn_bwd_kernel<<<grid, THREADS, SMEM_BYTES, stream>>>(tq, tk, tv, tdo, tdq, p);
+    attn_bwd_dkdv_kernel<<<grid, THREADS, KV_SMEM_BYTES, stream>>>(tq, tk, tv, tdo, p);
     CDL_CUDA(cudaGetLastError());
   }
-
   if (Sq > 0) {
-    const long long total = B * Sq * H * (D / 8);
-    attn_bwd_convert_dq_kernel<<<static_cast<unsigned>((total + 255) / 256), 256, 0, stream>>>(
-        dq_acc, static_cast<__nv_bfloat16*>(dq->ptr), dq->stride[0], dq->stride[1], dq->stride[2],
-        p.B, p.Sq, p.H);
+    dim3 grid(static_cast<unsigned>((Sq + BQ - 1) / BQ), static_cast<unsigned>(H),
+              static_cast<unsigned>(B));
+    attn_bwd_dq_kernel<<<grid, THREADS, Q_SMEM_BYTES, stream>>>(tq, tk, tv, tdo, p);
     CDL_CUDA(cudaGetLastError());
   }
   return CDL_OK;

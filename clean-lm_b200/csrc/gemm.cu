@@ -5,13 +5,13 @@
 // cuBLASLt; the kernel itself is written for sm_100a from scratch.  (The reference's own, disabled,
 // tcgen05 kernel is crates/cleandl/rust-kernels/src/sky_matmul/tcgen05_bf16.rs.)
 //
-// Kernel structure (one persistent CTA per SM, 192 threads):
+// Kernel structure (one persistent CTA per SM, 320 threads):
 //   warp 0      TMA producer: loads a 128 x 64 A tile and a 256 x 64 B tile per stage into
 //               128-byte-swizzled shared memory (4-stage ring, 48 KiB per stage).
 //   warp 1      MMA issuer: one elected thread issues 4 tcgen05.mma (M128 N256 K16) per stage into
 //               one of two 256-column f32 accumulators in TMEM; tcgen05.commit releases the stage
 //               and, after the last K block, publishes the accumulator.
-//   warps 2-5   epilogue: tcgen05.ld the accumulator (one row per thread, 32 columns at a time),
+//   warps 2-9   epilogue: tcgen05.ld the accumulator (one row per thread, 32 columns at a time),
 //               apply alpha / beta*C, convert and store straight to global memory.  The second
 //               accumulator lets the epilogue of tile i overlap the main loop of tile i+1.
 // Both operands may be K-major (K contiguous) or MN-major (M or N contiguous); that covers
@@ -35,7 +35,8 @@ constexpr int STAGES = 4;
 constexpr int A_BYTES = BM * BK * 2;  // 16 KiB
 constexpr int B_BYTES = BN * BK * 2;  // 32 KiB
 constexpr int STAGE_BYTES = A_BYTES + B_BYTES;
-constexpr int THREADS = 192;
+constexpr int THREADS = 320;  // warp 0 TMA, warp 1 MMA, warps 2-9 epilogue (two per TMEM lane quadrant)
+constexpr int EPI_WARPS = 8;
 constexpr int TMEM_COLS = 512;
 constexpr int RASTER_W = 8;  // N tiles per raster panel
 constexpr size_t SMEM_BYTES = 1024 + STAGES * STAGE_BYTES + 256;
@@ -52,6 +53,15 @@ struct Params {
   float alpha, beta;
   int split_k;     // K slices per tile (pair kernel, accumulate-in-place form only); 1 = none
   int atomic_out;  // 1 = add alpha * partial into D with red.global.add (D already holds C)
+  // Fused SwiGLU epilogues (bf16 [M, N] operands, 16-byte aligned rows):
+  //   1: D = G (the product),           out2 = SiLU(G) * aux0           (aux0 = up projection)
+  //   2: D = SiLU(aux0) * R,            out2 = R * aux1 * dSiLU(aux0)   (R = product, aux0 = gate, aux1 = up)
+  int wide;  // 1 = D, C and the fused operands all have 32-byte aligned rows: 256-bit accesses
+  int epi_mode;
+  const __nv_bfloat16* aux0;
+  const __nv_bfloat16* aux1;
+  __nv_bfloat16* out2;
+  long long ld_aux0, ld_aux1, ld_out2;
   int* status;
 };
 
@@ -77,14 +87,104 @@ __device__ __forceinline__ void tile_coords(const Params& p, int tile, int& b, i
   n = first_n + (r - m * width);
 }
 
+// sigmoid(x) = rcp.approx(1 + ex2.approx(-x log2 e)), as in the reference's fused epilogues
+// (crates/cleandl/rust-kernels/src/sky_matmul/tcgen05_bf16.rs:851-854).
+__device__ __forceinline__ float fast_sigmoid(float x) {
+  float e, r;
+  asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(e) : "f"(-x * 1.4426950408889634f));
+  asm("rcp.approx.ftz.f32 %0, %1;" : "=f"(r) : "f"(1.0f + e));
+  return r;
+}
+
+// 32 consecutive columns of one output row, all operands 32-byte aligned: C read, fused
+// SwiGLU or plain conversion, 256-bit stores.
+__device__ __forceinline__ void store_chunk_wide(const Params& p, float (&v)[32], int b, int row,
+                                                 int col0) {
+  const long long r64 = row;
+  if (p.c_mode == 1) {
+    const __nv_bfloat16* cp = static_cast<const __nv_bfloat16*>(p.c) + b * p.c_batch + r64 * p.ldc + col0;
+#pragma unroll
+    for (int g = 0; g < 2; ++g) {
+      uint32_t w[8];
+      ld_global_v8(cp + g * 16, w);
+#pragma unroll
+      for (int j = 0; j < 8; ++j) {
+        v[g * 16 + 2 * j] += p.beta * bf16_lo(w[j]);
+        v[g * 16 + 2 * j + 1] += p.beta * bf16_hi(w[j]);
+      }
+    }
+  } else if (p.c_mode == 2) {
+    const float* cp = static_cast<const float*>(p.c) + b * p.c_batch + r64 * p.ldc + col0;
+#pragma unroll
+    for (int g = 0; g < 4; ++g) {
+      uint32_t w[8];
+      ld_global_v8(cp + g * 8, w);
+#pragma unroll
+      for (int j = 0; j < 8; ++j) v[g * 8 + j] += p.beta * __uint_as_float(w[j]);
+    }
+  }
+  if (p.epi_mode != 0) {
+    __nv_bfloat16* dp = static_cast<__nv_bfloat16*>(p.d) + r64 * p.ldd + col0;
+    __nv_bfloat16* op = p.out2 + r64 * p.ld_out2 + col0;
+    const __nv_bfloat16* a0 = p.aux0 + r64 * p.ld_aux0 + col0;
+    const __nv_bfloat16* a1 = p.aux1 + r64 * p.ld_aux1 + col0;  // only dereferenced in mode 2
+#pragma unroll
+    for (int g = 0; g < 2; ++g) {
+      uint32_t w0[8], w1[8], q1[8], q2[8];
+      ld_global_v8(a0 + g * 16, w0);
+      if (p.epi_mode == 2) ld_global_v8(a1 + g * 16, w1);
+#pragma unroll
+      for (int j = 0; j < 8; ++j) {
+        float o1[2], o2[2];
+#pragma unroll
+        for (int e = 0; e < 2; ++e) {
+          const float rr = v[g * 16 + 2 * j + e];
+          const float x0 = e ? bf16_hi(w0[j]) : bf16_lo(w0[j]);
+          if (p.epi_mode == 1) {
+            o1[e] = rr;
+            o2[e] = rr * fast_sigmoid(rr) * x0;
+          } else {
+            const float x1 = e ? bf16_hi(w1[j]) : bf16_lo(w1[j]);
+            const float sg = fast_sigmoid(x0);
+            o1[e] = x0 * sg * rr;
+            o2[e] = rr * x1 * (sg + x0 * sg * (1.0f - sg));
+          }
+        }
+        q1[j] = pack_bf16x2(o1[0], o1[1]);
+        q2[j] = pack_bf16x2(o2[0], o2[1]);
+      }
+      st_global_v8(dp + g * 16, q1);
+      st_global_v8(op + g * 16, q2);
+    }
+  } else if (p.out_f32) {
+    float* dp = static_cast<float*>(p.d) + b * p.d_batch + r64 * p.ldd + col0;
+#pragma unroll
+    for (int g = 0; g < 4; ++g) {
+      uint32_t w[8];
+#pragma unroll
+      for (int j = 0; j < 8; ++j) w[j] = __float_as_uint(v[g * 8 + j]);
+      st_global_v8(dp + g * 8, w);
+    }
+  } else {
+    __nv_bfloat16* dp = static_cast<__nv_bfloat16*>(p.d) + b * p.d_batch + r64 * p.ldd + col0;
+#pragma unroll
+    for (int g = 0; g < 2; ++g) {
+      uint32_t w[8];
+#pragma unroll
+      for (int j = 0; j < 8; ++j) w[j] = pack_bf16x2(v[g * 16 + 2 * j], v[g * 16 + 2 * j + 1]);
+      st_global_v8(dp + g * 16, w);
+    }
+  }
+}
+
 // Epilogue of one accumulator for the calling warp: thread `lane` owns output row `row`
 // (TMEM lane = its lane inside the warp's quadrant); t_row addresses column 0 of the accumulator
-// at the warp's first lane.  Applies alpha / beta * C, converts and stores 256 columns.
+// at the warp's first lane.  Applies alpha / beta * C, converts and stores 128 columns (the warp's half of the tile).
 __device__ __forceinline__ void store_tile_rows(const Params& p, uint32_t t_row, int b, int row,
                                                 int col_base) {
   const bool row_ok = row < p.M;
 #pragma unroll 1
-  for (int ch = 0; ch < BN / 32; ++ch) {
+  for (int ch = 0; ch < BN / 64; ++ch) {
     const int col0 = col_base + ch * 32;
     if (col0 >= p.N) break;  // warp-uniform
     uint32_t r[32];
@@ -94,6 +194,13 @@ __device__ __forceinline__ void store_tile_rows(const Params& p, uint32_t t_row,
       float v[32];
 #pragma unroll
       for (int j = 0; j < 32; ++j) v[j] = p.alpha * __uint_as_float(r[j]);
+      if (p.wide && !p.atomic_out && col0 + 32 <= p.N) {
+        // Fast path: every row involved is 32-byte aligned, so each thread moves whole 32-byte
+        // sectors with 256-bit accesses (a thread owns a row, so narrower accesses would touch
+        // every sector twice).
+        store_chunk_wide(p, v, b, row, col0);
+        continue;
+      }
       if (p.c_mode == 1) {
         const __nv_bfloat16* cp = static_cast<const __nv_bfloat16*>(p.c) +
                                   b * p.c_batch + static_cast<long long>(row) * p.ldc + col0;
@@ -132,7 +239,49 @@ __device__ __forceinline__ void store_tile_rows(const Params& p, uint32_t t_row,
           }
         }
       }
-      if (p.atomic_out) {
+      if (p.epi_mode != 0) {
+        // sigmoid via ex2 / rcp approximations, as in the reference's fused epilogues
+        // (crates/cleandl/rust-kernels/src/sky_matmul/tcgen05_bf16.rs:851-877).
+        __nv_bfloat16* dp = static_cast<__nv_bfloat16*>(p.d) + static_cast<long long>(row) * p.ldd + col0;
+        __nv_bfloat16* op = p.out2 + static_cast<long long>(row) * p.ld_out2 + col0;
+        const __nv_bfloat16* a0 = p.aux0 + static_cast<long long>(row) * p.ld_aux0 + col0;
+        const __nv_bfloat16* a1 = p.epi_mode == 2 ? p.aux1 + static_cast<long long>(row) * p.ld_aux1 + col0 : nullptr;
+#pragma unroll
+        for (int g = 0; g < 4; ++g) {
+          if (col0 + g * 8 + 8 <= p.N) {  // N % 8 == 0 is checked on the host
+            const uint4 q0 = *reinterpret_cast<const uint4*>(a0 + g * 8);
+            const uint32_t w0[4] = {q0.x, q0.y, q0.z, q0.w};
+            uint32_t w1[4] = {0, 0, 0, 0};
+            if (p.epi_mode == 2) {
+              const uint4 q1 = *reinterpret_cast<const uint4*>(a1 + g * 8);
+              w1[0] = q1.x; w1[1] = q1.y; w1[2] = q1.z; w1[3] = q1.w;
+            }
+            float o1[8], o2[8];
+#pragma unroll
+            for (int j = 0; j < 8; ++j) {
+              const float r = v[g * 8 + j];
+              const float x0 = (j & 1) ? bf16_hi(w0[j >> 1]) : bf16_lo(w0[j >> 1]);
+              if (p.epi_mode == 1) {
+                const float sg = fast_sigmoid(r);
+                o1[j] = r;
+                o2[j] = r * sg * x0;
+              } else {
+                const float x1 = (j & 1) ? bf16_hi(w1[j >> 1]) : bf16_lo(w1[j >> 1]);
+                const float sg = fast_sigmoid(x0);
+                o1[j] = x0 * sg * r;
+                o2[j] = r * x1 * (sg + x0 * sg * (1.0f - sg));
+              }
+            }
+            uint4 qa, qb;
+            qa.x = pack_bf16x2(o1[0], o1[1]); qa.y = pack_bf16x2(o1[2], o1[3]);
+            qa.z = pack_bf16x2(o1[4], o1[5]); qa.w = pack_bf16x2(o1[6], o1[7]);
+            qb.x = pack_bf16x2(o2[0], o2[1]); qb.y = pack_bf16x2(o2[2], o2[3]);
+            qb.z = pack_bf16x2(o2[4], o2[5]); qb.w = pack_bf16x2(o2[6], o2[7]);
+            *reinterpret_cast<uint4*>(dp + g * 8) = qa;
+            *reinterpret_cast<uint4*>(op + g * 8) = qb;
+          }
+        }
+      } else if (p.atomic_out) {
         // K-sliced accumulation: D (f32, already holding C) += alpha * partial.  Several slices
         // of a tile add concurrently, so the order of the f32 additions is not fixed.
         float* dp = static_cast<float*>(p.d) + b * p.d_batch +
@@ -205,7 +354,7 @@ __global__ void __launch_bounds__(THREADS, 1)
     }
     for (int i = 0; i < 2; ++i) {
       mbar_init(&bars->acc_full[i], 1);
-      mbar_init(&bars->acc_empty[i], 4);
+      mbar_init(&bars->acc_empty[i], EPI_WARPS);
     }
     bars->abort_word = 0;
     fence_mbar_init();
@@ -297,8 +446,9 @@ __global__ void __launch_bounds__(THREADS, 1)
       }
     }
   } else {
-    // ------------------------------------------------------------ epilogue (warps 2..5)
+    // ------------------------------------------------------------ epilogue (warps 2..9)
     const int quad = warp & 3;  // TMEM lane quadrant this warp may read
+    const int half = (warp - 2) >> 2;  // which 128 of the tile's 256 columns
     int t = 0;
     for (int tile = blockIdx.x; tile < p.num_tiles; tile += gridDim.x, ++t) {
       int b, tm, tn;
@@ -307,8 +457,8 @@ __global__ void __launch_bounds__(THREADS, 1)
       const uint32_t acc_ph = (t >> 1) & 1;
       if (!mbar_wait(&bars->acc_full[acc], acc_ph, abort_word, 301)) break;
       tc_fence_after();
-      store_tile_rows(p, tmem_base + (static_cast<uint32_t>(quad * 32) << 16) + acc * BN, b,
-                      tm * BM + quad * 32 + lane, tn * BN);
+      store_tile_rows(p, tmem_base + (static_cast<uint32_t>(quad * 32) << 16) + acc * BN + half * (BN / 2),
+                      b, tm * BM + quad * 32 + lane, tn * BN + half * (BN / 2));
       tc_fence_before();
       __syncwarp();
       if (lane == 0) mbar_arrive(&bars->acc_empty[acc]);
@@ -384,7 +534,7 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(THREADS, 1)
     }
     for (int i = 0; i < 2; ++i) {
       mbar_init(&bars->acc_full[i], 1);
-      mbar_init(&bars->acc_empty[i], 8);  // 4 epilogue warps of each CTA (leader's copy is used)
+      mbar_init(&bars->acc_empty[i], 2 * EPI_WARPS);  // epilogue warps of both CTAs (leader's copy is used)
     }
     bars->abort_word = 0;
     fence_mbar_init();
@@ -489,8 +639,9 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(THREADS, 1)
       }
     }
   } else {
-    // ------------------------------------------------------------ epilogue (warps 2..5, both CTAs)
+    // ------------------------------------------------------------ epilogue (warps 2..9, both CTAs)
     const int quad = warp & 3;
+    const int half = (warp - 2) >> 2;
     int t = 0;
     for (int unit = cluster_id; unit < num_units; unit += num_clusters, ++t) {
       int tile, kb0, kb1, b, tm, tn;
@@ -500,8 +651,9 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(THREADS, 1)
       const uint32_t acc_ph = (t >> 1) & 1;
       if (!mbar_wait(&bars->acc_full[acc], acc_ph, abort_word, 311)) break;
       tc_fence_after();
-      store_tile_rows(p, tmem_base + (static_cast<uint32_t>(quad * 32) << 16) + acc * BN, b,
-                      tm * PAIR_M + static_cast<int>(rank) * BM + quad * 32 + lane, tn * BN);
+      store_tile_rows(p, tmem_base + (static_cast<uint32_t>(quad * 32) << 16) + acc * BN + half * (BN / 2),
+                      b, tm * PAIR_M + static_cast<int>(rank) * BM + quad * 32 + lane,
+                      tn * BN + half * (BN / 2));
       tc_fence_before();
       __syncwarp();
       if (lane == 0) mbar_arrive_cluster(mapa_shared(smem_u32(&bars->acc_empty[acc]), 0));
@@ -567,8 +719,28 @@ static int32_t analyze_operand(const char* name, const cdl_tensor* t, bool contr
 
 }  // namespace gemm
 
+static int32_t check_epi_operand(const char* name, const cdl_tensor* t, long long M, long long N) {
+  if (!t || t->rank != 2 || t->shape[0] != M || t->shape[1] != N || t->dtype != CDL_BF16 ||
+      t->stride[1] != 1 || t->stride[0] % 8 != 0 || (reinterpret_cast<uintptr_t>(t->ptr) & 15) != 0)
+    return fail(CDL_ERR_INVALID,
+                "matmul (fused SwiGLU): %s must be bf16 [%lld, %lld] with 16-byte aligned rows", name, M, N);
+  return CDL_OK;
+}
+
+int32_t matmul_execute_epi(const cdl_tensor* a, const cdl_tensor* b, const cdl_tensor* c,
+                           const cdl_tensor* d, float alpha, float beta, int epi_mode,
+                           const cdl_tensor* aux0, const cdl_tensor* aux1, const cdl_tensor* out2,
+                           cudaStream_t stream);
+
 int32_t matmul_execute(const cdl_tensor* a, const cdl_tensor* b, const cdl_tensor* c,
                        const cdl_tensor* d, float alpha, float beta, cudaStream_t stream) {
+  return matmul_execute_epi(a, b, c, d, alpha, beta, 0, nullptr, nullptr, nullptr, stream);
+}
+
+int32_t matmul_execute_epi(const cdl_tensor* a, const cdl_tensor* b, const cdl_tensor* c,
+                           const cdl_tensor* d, float alpha, float beta, int epi_mode,
+                           const cdl_tensor* aux0, const cdl_tensor* aux1, const cdl_tensor* out2,
+                           cudaStream_t stream) {
   using namespace gemm;
   if (!a || !b || !d) return fail(CDL_ERR_INVALID, "matmul: a, b and d are required");
   if (a->rank != b->rank || (a->rank != 2 && a->rank != 3) || d->rank != a->rank)
@@ -677,6 +849,41 @@ int32_t matmul_execute(const cdl_tensor* a, const cdl_tensor* b, const cdl_tenso
   p.beta = use_c ? beta : 0.0f;
   p.split_k = 1;
   p.atomic_out = 0;
+  p.epi_mode = 0;
+  p.aux0 = p.aux1 = nullptr;
+  p.out2 = nullptr;
+  p.ld_aux0 = p.ld_aux1 = p.ld_out2 = 0;
+  if (epi_mode != 0) {
+    if (r != 2 || use_c || d->dtype != CDL_BF16 || N % 8 != 0 || !p.d_vec)
+      return fail(CDL_ERR_INVALID,
+                  "matmul (fused SwiGLU): rank 2, no C operand, bf16 output with 16-byte aligned rows "
+                  "and N %% 8 == 0 are required");
+    CDL_CHECK(check_epi_operand("aux0", aux0, M, N));
+    CDL_CHECK(check_epi_operand("out2", out2, M, N));
+    if (epi_mode == 2) CDL_CHECK(check_epi_operand("aux1", aux1, M, N));
+    p.epi_mode = epi_mode;
+    p.aux0 = static_cast<const __nv_bfloat16*>(aux0->ptr);
+    p.ld_aux0 = aux0->stride[0];
+    p.out2 = static_cast<__nv_bfloat16*>(out2->ptr);
+    p.ld_out2 = out2->stride[0];
+    if (epi_mode == 2) {
+      p.aux1 = static_cast<const __nv_bfloat16*>(aux1->ptr);
+      p.ld_aux1 = aux1->stride[0];
+    }
+  }
+  {
+    auto al32 = [](const void* ptr, long long ld, long long bstride, size_t es) {
+      return (reinterpret_cast<uintptr_t>(ptr) & 31) == 0 && (ld * es) % 32 == 0 &&
+             (bstride * es) % 32 == 0;
+    };
+    bool w = al32(p.d, p.ldd, p.d_batch, dtype_size(d->dtype));
+    if (use_c) w = w && al32(p.c, p.ldc, p.c_batch, dtype_size(c->dtype));
+    if (p.epi_mode != 0) {
+      w = w && al32(p.aux0, p.ld_aux0, 0, 2) && al32(p.out2, p.ld_out2, 0, 2);
+      if (p.epi_mode == 2) w = w && al32(p.aux1, p.ld_aux1, 0, 2);
+    }
+    p.wide = w ? 1 : 0;
+  }
   p.status = device_status_ptr();
   if (!p.status) return fail(CDL_ERR_CUDA, "cannot resolve the device status word");
 
@@ -760,6 +967,20 @@ int32_t cdl_b200_matmul(const cdl_tensor* a, const cdl_tensor* b, const cdl_tens
   (void)scratch;
   (void)scratch_bytes;
   return cdl::matmul_execute(a, b, c, d, alpha, beta, static_cast<cudaStream_t>(stream));
+}
+
+int32_t cdl_b200_matmul_swiglu_gate(const cdl_tensor* a, const cdl_tensor* b, const cdl_tensor* up,
+                                    const cdl_tensor* gate_out, const cdl_tensor* act_out,
+                                    cdl_stream stream) {
+  return cdl::matmul_execute_epi(a, b, nullptr, gate_out, 1.0f, 0.0f, 1, up, nullptr, act_out,
+                                 static_cast<cudaStream_t>(stream));
+}
+
+int32_t cdl_b200_matmul_swiglu_dgrad(const cdl_tensor* a, const cdl_tensor* b, const cdl_tensor* gate,
+                                     const cdl_tensor* up, const cdl_tensor* d_up_out,
+                                     const cdl_tensor* d_gate_out, cdl_stream stream) {
+  return cdl::matmul_execute_epi(a, b, nullptr, d_up_out, 1.0f, 0.0f, 2, gate, up, d_gate_out,
+                                 static_cast<cudaStream_t>(stream));
 }
 
 int32_t cdl_b200_matmul_scratch_bytes(const cdl_tensor* a, const cdl_tensor* b,

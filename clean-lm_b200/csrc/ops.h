@@ -7,6 +7,12 @@ namespace cdl {
 
 int32_t matmul_execute(const cdl_tensor* a, const cdl_tensor* b, const cdl_tensor* c,
                        const cdl_tensor* d, float alpha, float beta, cudaStream_t stream);
+// epi_mode 1: d = product, out2 = SiLU(product) * aux0.  epi_mode 2: d = SiLU(aux0) * product,
+// out2 = product * aux1 * dSiLU(aux0).
+int32_t matmul_execute_epi(const cdl_tensor* a, const cdl_tensor* b, const cdl_tensor* c,
+                           const cdl_tensor* d, float alpha, float beta, int epi_mode,
+                           const cdl_tensor* aux0, const cdl_tensor* aux1, const cdl_tensor* out2,
+                           cudaStream_t stream);
 int32_t rmsnorm_fwd_execute(const cdl_tensor* x, const cdl_tensor* scale, const cdl_tensor* bias,
                             float eps, const cdl_tensor* y, const cdl_tensor* r_inv,
                             cudaStream_t stream);

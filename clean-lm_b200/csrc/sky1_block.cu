@@ -4,6 +4,7 @@
 // decoder.rs: train_forward :332-520, train_backward :523-695), whose operator module is missing
 // from the reference tree, so only the order of operations, the saved tensors and the
 // accumulate-into-f32-gradient convention are taken from it:
+//   (SwiGLU is fused into the gate GEMM's and the down-projection dgrad's epilogue)
 //   forward   h1 = RMSNorm(x; g1); qkv = h1 Wqkv; RoPE(q, k); attn = causal FA(q, k, v);
 //             o = attn Wo + x; h2 = RMSNorm(o; g2); up = h2 Wup; gate = h2 Wgate;
 //             act = SiLU(gate) * up; out = act Wdown + o.        saved: qkv attn lse o up gate act
@@ -172,8 +173,8 @@ int32_t sky1_block_fwd(const cdl_sky1_config* cfg, const cdl_sky1_weights* wt, c
   CDL_CHECK(matmul_execute(&tattn, &wo, &tx, &to, 1.f, 1.f, st));  // o = attn Wo + x
   CDL_CHECK(rmsnorm_fwd_execute(&to, &g2, nullptr, cfg->eps, &th, nullptr, st));
   CDL_CHECK(matmul_execute(&th, &wup, nullptr, &tup, 1.f, 0.f, st));
-  CDL_CHECK(matmul_execute(&th, &wgate, nullptr, &tgate, 1.f, 0.f, st));
-  CDL_CHECK(swiglu_fwd_execute(&tgate, &tup, &tact, st));
+  // gate = h2 Wgate and act = SiLU(gate) * up in one kernel (fused epilogue)
+  CDL_CHECK(matmul_execute_epi(&th, &wgate, nullptr, &tgate, 1.f, 0.f, 1, &tup, nullptr, &tact, st));
   CDL_CHECK(matmul_execute(&tact, &wdown, &to, &tout, 1.f, 1.f, st));  // out = act Wdown + o
   return CDL_OK;
 }
@@ -221,8 +222,8 @@ int32_t sky1_block_bwd(const cdl_sky1_config* cfg, const cdl_sky1_weights* wt, c
   if (phase != 2) {
   // FFN
   CDL_CHECK(matmul_execute(&actT, &tdy, &gwdown, &gwdown, 1.f, 1.f, st));          // dWdown += act^T dy
-  CDL_CHECK(matmul_execute(&tdy, &wdownT, nullptr, &tdact, 1.f, 0.f, st));          // d_act = dy Wdown^T
-  CDL_CHECK(swiglu_bwd_execute(&tdact, &tgate, &tup, &tdgate, &tdact, st));         // d_up in place of d_act
+  // d_act = dy Wdown^T never reaches memory: the epilogue turns it into d_up and d_gate
+  CDL_CHECK(matmul_execute_epi(&tdy, &wdownT, nullptr, &tdact, 1.f, 0.f, 2, &tgate, &tup, &tdgate, st));
   CDL_CHECK(rmsnorm_fwd_execute(&to, &g2, nullptr, cfg->eps, &th, &tr, st));        // recompute h2, r2
   CDL_CHECK(matmul_execute(&hT, &tdact, &gwup, &gwup, 1.f, 1.f, st));               // dWup += h2^T d_up
   CDL_CHECK(matmul_execute(&tdact, &wupT, nullptr, &tdh, 1.f, 0.f, st));            // dh2 = d_up Wup^T

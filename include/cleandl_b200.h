@@ -85,6 +85,19 @@ int32_t cdl_b200_profile_stop(cdl_profile_record* out, int32_t capacity, int32_t
 int32_t cdl_b200_matmul(const cdl_tensor* a, const cdl_tensor* b, const cdl_tensor* c,
                         const cdl_tensor* d, float alpha, float beta, void* scratch,
                         size_t scratch_bytes, cdl_stream stream);
+/* GEMM with the SwiGLU activation fused into its epilogue, the counterparts of the reference's
+ * sky_matmul_swiglu_gate_train_fwd and sky_matmul_swiglu_down_train_dgrad kernels
+ * (crates/cleandl/rust-kernels/src/sky_matmul/tcgen05_bf16.rs:879-942, 944-1031, entry points
+ * :1201-1223).  All [M, N] operands are bf16 with 16-byte aligned rows, N % 8 == 0.
+ *   gate:  G = A . B;  gate_out = G;  act_out = SiLU(G) * up
+ *   dgrad: R = A . B;  d_up_out = SiLU(gate) * R;  d_gate_out = R * up * dSiLU(gate)
+ * with dSiLU(g) = s + g s (1 - s), s = sigmoid(g). */
+int32_t cdl_b200_matmul_swiglu_gate(const cdl_tensor* a, const cdl_tensor* b, const cdl_tensor* up,
+                                    const cdl_tensor* gate_out, const cdl_tensor* act_out,
+                                    cdl_stream stream);
+int32_t cdl_b200_matmul_swiglu_dgrad(const cdl_tensor* a, const cdl_tensor* b, const cdl_tensor* gate,
+                                     const cdl_tensor* up, const cdl_tensor* d_up_out,
+                                     const cdl_tensor* d_gate_out, cdl_stream stream);
 /* Scratch the call above needs for these operands (Executor::scratch_bytes, op.rs:132-135). */
 int32_t cdl_b200_matmul_scratch_bytes(const cdl_tensor* a, const cdl_tensor* b,
                                       const cdl_tensor* d, size_t* bytes_out);

@@ -158,3 +158,34 @@ def test_empty_and_errors(cdl, gpu_ok):
     with pytest.raises(cdl._lib.CdlError, match="16-byte"):
         cdl.ops.matmul(torch.zeros(37, 65, dtype=torch.bfloat16, device=dev)[:, :64],
                        torch.zeros(64, 8, dtype=torch.bfloat16, device=dev))
+
+
+@pytest.mark.parametrize("m,n,k", [(300, 264, 136), (128, 72, 64), (1024, 512, 256)])
+def test_fused_swiglu_epilogues(cdl, gpu_ok, m, n, k):
+    """GEMM + SwiGLU in one kernel (the reference's swiglu_gate_train_fwd / swiglu_down_train_dgrad
+    kernels) against float64: gate/act forward and d_up/d_gate backward."""
+    L = cdl._lib
+    gen = torch.Generator().manual_seed(21)
+    a = rand_bf16(gen, m, k)
+    b = (torch.randn(k, n, generator=gen) * 0.3).to(torch.bfloat16)
+    up = rand_bf16(gen, m, n)
+    gate_in = (torch.randn(m, n, generator=gen) * 2).to(torch.bfloat16)
+    da, db, dup, dgi = a.cuda(), b.cuda(), up.cuda(), gate_in.cuda()
+    gate_out, act_out = torch.empty_like(dup), torch.empty_like(dup)
+    args = [L.tensor_arg(t) for t in (da, db, dup, gate_out, act_out)]
+    L.check(L.lib.cdl_b200_matmul_swiglu_gate(*(L.ref(x) for x in args), None))
+    d_up, d_gate = torch.empty_like(dup), torch.empty_like(dup)
+    args = [L.tensor_arg(t) for t in (da, db, dgi, dup, d_up, d_gate)]
+    L.check(L.lib.cdl_b200_matmul_swiglu_dgrad(*(L.ref(x) for x in args), None))
+    torch.cuda.synchronize()
+    prod = a.double() @ b.double()
+    sig = torch.sigmoid
+
+    def rel(got, ref):
+        return ((got.double().cpu() - ref).abs().max() / ref.abs().max()).item()
+
+    assert rel(gate_out, prod) <= 2.0 ** -7
+    assert rel(act_out, prod * sig(prod) * up.double()) <= 2.0 ** -6
+    g = gate_in.double()
+    assert rel(d_up, g * sig(g) * prod) <= 2.0 ** -6
+    assert rel(d_gate, prod * up.double() * (sig(g) + g * sig(g) * (1 - sig(g)))) <= 2.0 ** -6
