@@ -295,9 +295,33 @@ def run_ours(args) -> None:
         gemm = by_kind.get("gemm", [0, 0.0, 0.0])
         achieved = gemm[2] / (gemm[1] * 1e-3) / 1e12 if gemm[1] > 0 else None
         kernel_ms = {k: round(v[1] / args.steps, 4) for k, v in by_kind.items()}
-        # kernels launched per step: 15 GEMM, 4 norm fwd, 2 x 2 norm bwd, 1 attn fwd,
-        # 3 attn bwd (+ memset), 2 rope, 2 swiglu, 1 embedding
-        launches_per_step = 15 + 4 + 4 + 1 + 3 + 2 + 2 + 1
+        # kernels launched per step: 15 GEMM (SwiGLU fused into two of them), 4 norm fwd,
+        # 2 x 2 norm bwd, 1 attn fwd, 3 attn bwd, 2 rope, 1 embedding
+        launches_per_step = 15 + 4 + 4 + 1 + 3 + 2 + 1
+        # DRAM traffic of the average GEMM launch: the minimum bytes of each of the block's 15
+        # GEMMs (operands read once, outputs written once, accumulated outputs read and written,
+        # fused-epilogue operands included) scaled by the ratio measured with Nsight Compute on
+        # 8192 x 8192 x 2048 (dram read + write = 191.5 MB against a minimum of 201.3 MB; see
+        # profiles/gemm_bf16_8192x8192x2048.md).
+        Hd, QKV, F = cfg.hidden, cfg.qkv_dim, cfg.ffn
+        gemm_bytes = [
+            2 * (T * Hd + Hd * QKV + T * QKV),              # qkv
+            2 * (T * Hd + Hd * Hd + 2 * T * Hd),            # o + residual
+            2 * (T * Hd + Hd * F + T * F),                  # up
+            2 * (T * Hd + Hd * F + 3 * T * F),              # gate (+ up in, act out)
+            2 * (T * F + F * Hd + 2 * T * Hd),              # down + residual
+            2 * (T * F + T * Hd) + 8 * F * Hd,              # dW down (f32 read + write)
+            2 * (T * Hd + F * Hd + 4 * T * F),              # d_act fused: gate, up in; d_up, d_gate out
+            2 * (T * Hd + T * F) + 8 * Hd * F,              # dW up
+            2 * (T * F + Hd * F + T * Hd),                  # dh2
+            2 * (T * Hd + T * F) + 8 * Hd * F,              # dW gate
+            2 * (T * F + Hd * F + 2 * T * Hd),              # dh2 += (C read)
+            2 * (T * Hd + T * Hd) + 8 * Hd * Hd,            # dW o
+            2 * (T * Hd + Hd * Hd + T * Hd),                # d_attn
+            2 * (T * Hd + T * QKV) + 8 * Hd * QKV,          # dW qkv
+            2 * (T * QKV + Hd * QKV + T * Hd),              # dh1
+        ]
+        gemm_traffic = sum(gemm_bytes) / len(gemm_bytes) * (191.5 / 201.3)
         # CPU baseline on rank 0 at N = 1 only (torchrun pins ranks to one OpenMP thread).
         cpu_value, cpu_threads = cpu_block_tokens_per_s(512, repeats=2) if world == 1 else (None, None)
         line = {
@@ -318,7 +342,8 @@ def run_ours(args) -> None:
             "clocks": clocks,
             "roofline": {"bound": "tensor", "achieved": achieved, "peak": peaks["bf16"],
                          "unit": "TFLOP/s", "frac": (achieved / peaks["bf16"]) if achieved else None,
-                         "traffic": None, "kernel": "gemm_bf16_kernel",
+                         "traffic": gemm_traffic, "traffic_unit": "bytes per launch (mean of the 15 GEMMs)",
+                         "kernel": "gemm_bf16_pair_kernel",
                          "launches": gemm[0], "peak_source": peaks["source"] + " (sustained cuBLAS bf16)"},
             "cpu_baseline": None if cpu_value is None else {
                 "value": cpu_value, "unit": "tokens/s", "cores": cpu_threads, "kind": "port",
@@ -393,13 +418,15 @@ def run_kernel(args) -> None:
     for i in range(args.warmup):
         fns[i % len(fns)]()
     torch.cuda.synchronize()
-    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-    e0.record()
+    # Per-launch CUDA events recorded by the library around its own kernels: unlike events around
+    # the Python call, they do not include host launch overhead, which matters for 20-100 us kernels.
+    L.profile_start(4 * args.steps + 16)
     for i in range(args.steps):
         fns[i % len(fns)]()
-    e1.record()
-    torch.cuda.synchronize()
-    ms = e0.elapsed_time(e1) / args.steps
+    kind = {"gemm": "gemm", "norm_fwd": "norm_fwd", "norm_bwd": "norm_bwd", "attn_fwd": "attn_fwd",
+            "attn_bwd": "attn_bwd"}[k]
+    times = [ms_ for kd, ms_, _ in L.profile_stop(4 * args.steps + 16) if kd == kind]
+    ms = sum(times) / len(times)
     assert L.device_status() == 0
     achieved = work / (ms * 1e-3) / (1e12 if unit == "TFLOP/s" else 1e9)
     print(json.dumps({"kernel": k, "case": desc, "ms": ms, "achieved": achieved, "unit": unit,
@@ -407,6 +434,83 @@ def run_kernel(args) -> None:
                       "peak_source": peaks["source"] + (" burst cuBLAS bf16" if unit == "TFLOP/s"
                                                         else " copy bandwidth"),
                       "steps": args.steps, "warmup": args.warmup}))
+
+
+# ------------------------------------------------------------------ full LM step (config 5)
+def run_lm(args) -> None:
+    """24-layer sky-1-style LM training step (BASELINE config 5): global batch 64 x 2048
+    uniform-random tokens split over the ranks, microbatches of 8 x 2048 with gradient
+    accumulation, per-layer all-reduce overlapped with the backward, AdamW.  Prints one JSON
+    line with tokens/s (device-timed, max over ranks) and the last loss."""
+    import torch
+    import torch.distributed as dist
+
+    import cleanlm_b200 as cdl
+
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    rank = int(os.environ.get("RANK", "0"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    torch.cuda.set_device(local)
+    dev = torch.device("cuda", local)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=dev)
+    blk = cdl.sky1.Sky1Config()
+    cfg = cdl.sky1.Sky1LMConfig(block=blk, layers=args.layers, vocab=VOCAB)
+    model = cdl.sky1.Sky1LM(cfg, seed=4, device=dev)
+    seqs_per_rank = max(1, 64 // world)
+    mb = max(1, seqs_per_rank // blk.batch)
+    global_tokens = mb * blk.tokens * world
+    gen = torch.Generator().manual_seed(4 + 1000 * rank)
+    n = args.warmup + args.steps
+    data = torch.randint(0, VOCAB, (n, mb, blk.batch, blk.seqlen + 1), generator=gen, dtype=torch.int32)
+    tok = data[..., :-1].reshape(n, mb, -1).contiguous().pin_memory()
+    tgt = data[..., 1:].reshape(n, mb, -1).contiguous().pin_memory()
+    d_tok = torch.empty(mb, blk.tokens, dtype=torch.int32, device=dev)
+    d_tgt = torch.empty_like(d_tok)
+    losses = []
+
+    def step(i):
+        d_tok.copy_(tok[i], non_blocking=True)
+        d_tgt.copy_(tgt[i], non_blocking=True)
+        loss = model.train_step(d_tok, d_tgt, global_tokens=global_tokens)
+        if world > 1:
+            dist.all_reduce(loss)
+        losses.append(loss.item())  # the step's result is read back every step
+
+    for i in range(args.warmup):
+        step(i)
+    if world > 1:
+        dist.barrier()
+    torch.cuda.synchronize(dev)
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for i in range(args.steps):
+        step(args.warmup + i)
+    e1.record()
+    if world > 1:
+        dist.barrier()
+    torch.cuda.synchronize(dev)
+    ms = e0.elapsed_time(e1)
+    if world > 1:
+        t = torch.tensor([ms], dtype=torch.float64, device=dev)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        ms = float(t.item())
+    assert cdl._lib.device_status() == 0
+    if rank == 0:
+        flops = (cfg.layers * blk.flops_fwd_bwd() + 3 * 2.0 * blk.tokens * blk.hidden * VOCAB) * mb
+        print(json.dumps({
+            "metric": "sky1_lm_train_tokens_per_s", "value": args.steps * global_tokens / (ms * 1e-3),
+            "unit": "tokens/s", "n_gpus": world, "steps": args.steps, "warmup": args.warmup,
+            "ms_per_step": ms / args.steps, "higher_is_better": True, "scaling": "strong",
+            "dtype": "bf16", "data": "synthetic",
+            "config": {"workload": f"sky-1 LM training step (config 5): {cfg.layers} layers, vocab {VOCAB}, "
+                                   f"global batch 64 x 2048, AdamW lr 3e-4 betas (0.9, 0.95) wd 0.1",
+                       "parallelism": f"dp{world}", "microbatches_per_rank": mb,
+                       "params": cfg.param_count(),
+                       "tflops_per_gpu": flops * args.steps / (ms * 1e-3) / 1e12},
+            "loss_first": losses[0], "loss_last": losses[-1]}))
+    if world > 1:
+        dist.destroy_process_group()
 
 
 def main() -> None:
@@ -429,7 +533,13 @@ def main() -> None:
     ap.add_argument("--batch", type=int, default=8)
     ap.add_argument("--seq", type=int, default=2048)
     ap.add_argument("--heads", type=int, default=16)
+    ap.add_argument("--workload", default="block", choices=["block", "lm"],
+                    help="block = BASELINE config 4 (the headline metric); lm = the 24-layer training step")
+    ap.add_argument("--layers", type=int, default=24)
     args = ap.parse_args()
+    if args.workload == "lm":
+        run_lm(args)
+        return
     if args.kernel:
         args.warmup = max(args.warmup, 3)
         run_kernel(args)

@@ -16,6 +16,9 @@
 #include "host.h"
 #include "ptx.cuh"
 
+#include <stdlib.h>
+#include <string.h>
+
 #include <mutex>
 
 namespace cdl {
@@ -45,7 +48,7 @@ __device__ __forceinline__ uint4 pack8(const float (&f)[8]) {
 
 // NCH = number of 256-column stripes a row spans (cols <= 256 * NCH).
 template <int NCH>
-__global__ void __launch_bounds__(FWD_THREADS)
+__global__ void __launch_bounds__(FWD_THREADS, NCH <= 8 ? 4 : 1)
     rmsnorm_fwd_kernel(const __nv_bfloat16* __restrict__ x, long long ldx,
                        const __nv_bfloat16* __restrict__ scale,
                        const __nv_bfloat16* __restrict__ bias, __nv_bfloat16* __restrict__ y,
@@ -101,6 +104,112 @@ __global__ void __launch_bounds__(FWD_THREADS)
       }
     }
   }
+}
+
+// Pipelined forward: one persistent CTA per SM; warp 8 streams whole rows into a shared-memory
+// ring with 1-D bulk copies (up to 128 KiB in flight per SM, independent of how fast the rows
+// are consumed), warps 0-7 each take every 8th row of the CTA's slice out of the ring, reduce
+// it with shuffles and store y straight from registers.
+constexpr int PIPE_CONSUMERS = 8;
+constexpr int PIPE_THREADS = (PIPE_CONSUMERS + 1) * 32;
+constexpr int PIPE_RING_BYTES = 128 * 1024;
+
+template <int NCH>
+__global__ void __launch_bounds__(PIPE_THREADS, 1)
+    rmsnorm_fwd_pipe_kernel(const __nv_bfloat16* __restrict__ x, long long ldx,
+                            const __nv_bfloat16* __restrict__ scale,
+                            const __nv_bfloat16* __restrict__ bias, __nv_bfloat16* __restrict__ y,
+                            long long ldy, float* __restrict__ r_inv, long long r_inv_stride,
+                            int rows, int cols, float eps, int stages, int* status) {
+  extern __shared__ __align__(128) uint8_t ring[];
+  const int row_bytes = cols * 2;
+  uint64_t* full = reinterpret_cast<uint64_t*>(ring + static_cast<size_t>(stages) * row_bytes);
+  uint64_t* empty = full + stages;
+  volatile int* abort_word = reinterpret_cast<volatile int*>(empty + stages);
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  // contiguous slice of rows for this CTA
+  const int per = (rows + gridDim.x - 1) / gridDim.x;
+  const int row_begin = min(rows, static_cast<int>(blockIdx.x) * per);
+  const int row_end = min(rows, row_begin + per);
+  const int n = row_end - row_begin;
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < stages; ++s) {
+      mbar_init(&full[s], 1);
+      mbar_init(&empty[s], 1);
+    }
+    *abort_word = 0;
+    fence_mbar_init();
+  }
+  __syncthreads();
+  if (warp == PIPE_CONSUMERS) {
+    if (lane == 0) {
+      for (int i = 0; i < n; ++i) {
+        const int s = i % stages;
+        const uint32_t ph = ((i / stages) & 1) ^ 1;
+        if (!mbar_wait(&empty[s], ph, abort_word, 701)) break;
+        mbar_arrive_expect_tx(&full[s], row_bytes);
+        bulk_load_1d(ring + static_cast<size_t>(s) * row_bytes, x + (row_begin + i) * ldx, row_bytes,
+                     &full[s]);
+      }
+    }
+  } else {
+    const float inv_cols = 1.0f / static_cast<float>(cols);
+    // the scale for this lane's columns stays in registers for the whole slice
+    uint4 sc[NCH];
+#pragma unroll
+    for (int c = 0; c < NCH; ++c) {
+      const int col = c * 256 + lane * 8;
+      sc[c] = (scale != nullptr && col < cols) ? __ldg(reinterpret_cast<const uint4*>(scale + col))
+                                               : make_uint4(0x3f803f80u, 0x3f803f80u, 0x3f803f80u, 0x3f803f80u);
+    }
+    for (int i = warp; i < n; i += PIPE_CONSUMERS) {
+      const int s = i % stages;
+      const uint32_t ph = (i / stages) & 1;
+      if (!mbar_wait(&full[s], ph, abort_word, 702)) break;
+      const uint8_t* src = ring + static_cast<size_t>(s) * row_bytes;
+      uint4 v[NCH];
+#pragma unroll
+      for (int c = 0; c < NCH; ++c) {
+        const int col = c * 256 + lane * 8;
+        v[c] = col < cols ? *reinterpret_cast<const uint4*>(src + col * 2) : make_uint4(0, 0, 0, 0);
+      }
+      __syncwarp();
+      if (lane == 0) mbar_arrive(&empty[s]);  // the row is in registers: the slot can be refilled
+      float ss = 0.f;
+#pragma unroll
+      for (int c = 0; c < NCH; ++c) {
+        float f[8];
+        unpack8(v[c], f);
+#pragma unroll
+        for (int j = 0; j < 8; ++j) ss = fmaf(f[j], f[j], ss);
+      }
+      ss = warp_sum(ss);
+      const float r = rsqrtf(ss * inv_cols + eps);
+      const long long row = row_begin + i;
+      if (r_inv != nullptr && lane == 0) r_inv[row * r_inv_stride] = r;
+      __nv_bfloat16* yr = y + row * ldy;
+#pragma unroll
+      for (int c = 0; c < NCH; ++c) {
+        const int col = c * 256 + lane * 8;
+        if (col < cols) {
+          float f[8], sf[8];
+          unpack8(v[c], f);
+          unpack8(sc[c], sf);
+#pragma unroll
+          for (int j = 0; j < 8; ++j) f[j] = (f[j] * r) * sf[j];
+          if (bias != nullptr) {
+            float bf[8];
+            unpack8(__ldg(reinterpret_cast<const uint4*>(bias + col)), bf);
+#pragma unroll
+            for (int j = 0; j < 8; ++j) f[j] += bf[j];
+          }
+          st_cs_v4(yr + col, pack8(f));
+        }
+      }
+    }
+  }
+  __syncthreads();
+  if (threadIdx.x == 0 && *abort_word != 0) atomicExch(status, *abort_word);
 }
 
 // Backward.  Every warp walks rows (grid-stride), keeps per-lane partial sums of
@@ -202,6 +311,144 @@ __global__ void __launch_bounds__(BWD_THREADS, BWD_BLOCKS_PER_SM)
   }
 }
 
+// Pipelined backward (cols <= 2048): like the pipelined forward, warp 8 streams the x, dy (and
+// residual) rows of the CTA's slice into a shared-memory ring with bulk copies; warps 0-7 take
+// every 8th row, keep their partial dscale sums in registers, and the CTA writes one partial
+// row at the end (folded through the ring's memory once the pipeline has drained).
+template <int NCH>
+__global__ void __launch_bounds__(PIPE_THREADS, 1)
+    rmsnorm_bwd_pipe_kernel(const __nv_bfloat16* __restrict__ x, long long ldx,
+                            const __nv_bfloat16* __restrict__ dy, long long lddy,
+                            const __nv_bfloat16* __restrict__ res, long long ldres,
+                            const __nv_bfloat16* __restrict__ scale, const float* __restrict__ r_inv,
+                            long long r_inv_stride, __nv_bfloat16* __restrict__ dx, long long lddx,
+                            float* __restrict__ partials, int rows, int cols, int stages, int* status) {
+  extern __shared__ __align__(128) uint8_t ring[];
+  const int row_bytes = cols * 2;
+  const int ntens = res != nullptr ? 3 : 2;
+  const int stage_bytes = ntens * row_bytes;
+  uint8_t* s_scale = ring + static_cast<size_t>(stages) * stage_bytes;  // bf16 [cols]
+  uint64_t* full = reinterpret_cast<uint64_t*>(s_scale + row_bytes);
+  uint64_t* empty = full + stages;
+  volatile int* abort_word = reinterpret_cast<volatile int*>(empty + stages);
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int per = (rows + gridDim.x - 1) / gridDim.x;
+  const int row_begin = min(rows, static_cast<int>(blockIdx.x) * per);
+  const int row_end = min(rows, row_begin + per);
+  const int n = row_end - row_begin;
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < stages; ++s) {
+      mbar_init(&full[s], 1);
+      mbar_init(&empty[s], 1);
+    }
+    *abort_word = 0;
+    fence_mbar_init();
+  }
+  for (int i = threadIdx.x * 8; i < cols; i += PIPE_THREADS * 8)
+    *reinterpret_cast<uint4*>(s_scale + i * 2) = __ldg(reinterpret_cast<const uint4*>(scale + i));
+  __syncthreads();
+
+  float acc[NCH * 8];
+#pragma unroll
+  for (int i = 0; i < NCH * 8; ++i) acc[i] = 0.f;
+
+  if (warp == PIPE_CONSUMERS) {
+    if (lane == 0) {
+      for (int i = 0; i < n; ++i) {
+        const int s = i % stages;
+        const uint32_t ph = ((i / stages) & 1) ^ 1;
+        if (!mbar_wait(&empty[s], ph, abort_word, 711)) break;
+        uint8_t* dst = ring + static_cast<size_t>(s) * stage_bytes;
+        const long long row = row_begin + i;
+        mbar_arrive_expect_tx(&full[s], stage_bytes);
+        bulk_load_1d(dst, x + row * ldx, row_bytes, &full[s]);
+        bulk_load_1d(dst + row_bytes, dy + row * lddy, row_bytes, &full[s]);
+        if (ntens == 3) bulk_load_1d(dst + 2 * row_bytes, res + row * ldres, row_bytes, &full[s]);
+      }
+    }
+  } else {
+    const float inv_cols = 1.0f / static_cast<float>(cols);
+    for (int i = warp; i < n; i += PIPE_CONSUMERS) {
+      const int s = i % stages;
+      const uint32_t ph = (i / stages) & 1;
+      if (!mbar_wait(&full[s], ph, abort_word, 712)) break;
+      const uint8_t* src = ring + static_cast<size_t>(s) * stage_bytes;
+      const long long row = row_begin + i;
+      const float r = r_inv[row * r_inv_stride];
+      uint4 vx[NCH], vd[NCH];
+#pragma unroll
+      for (int c = 0; c < NCH; ++c) {
+        const int col = c * 256 + lane * 8;
+        const bool in = col < cols;
+        vx[c] = in ? *reinterpret_cast<const uint4*>(src + col * 2) : make_uint4(0, 0, 0, 0);
+        vd[c] = in ? *reinterpret_cast<const uint4*>(src + row_bytes + col * 2) : make_uint4(0, 0, 0, 0);
+      }
+      float dot = 0.f;
+#pragma unroll
+      for (int c = 0; c < NCH; ++c) {
+        const int col = c * 256 + lane * 8;
+        if (col < cols) {
+          float fx[8], fd[8], fs[8];
+          unpack8(vx[c], fx);
+          unpack8(vd[c], fd);
+          unpack8(*reinterpret_cast<const uint4*>(s_scale + col * 2), fs);
+#pragma unroll
+          for (int j = 0; j < 8; ++j) {
+            dot = fmaf(fd[j] * fs[j], fx[j], dot);
+            acc[c * 8 + j] = fmaf(fd[j] * fx[j], r, acc[c * 8 + j]);
+          }
+        }
+      }
+      dot = warp_sum(dot);
+      const float k = r * r * (dot * inv_cols);  // dx = r * (g - x * k)
+      __nv_bfloat16* dxr = dx + row * lddx;
+#pragma unroll
+      for (int c = 0; c < NCH; ++c) {
+        const int col = c * 256 + lane * 8;
+        if (col < cols) {
+          float fx[8], fd[8], fs[8], o[8];
+          unpack8(vx[c], fx);
+          unpack8(vd[c], fd);
+          unpack8(*reinterpret_cast<const uint4*>(s_scale + col * 2), fs);
+#pragma unroll
+          for (int j = 0; j < 8; ++j) o[j] = r * (fd[j] * fs[j] - fx[j] * k);
+          if (ntens == 3) {
+            float fr[8];
+            unpack8(*reinterpret_cast<const uint4*>(src + 2 * row_bytes + col * 2), fr);
+#pragma unroll
+            for (int j = 0; j < 8; ++j) o[j] += fr[j];
+          }
+          st_cs_v4(dxr + col, pack8(o));
+        }
+      }
+      __syncwarp();
+      if (lane == 0) mbar_arrive(&empty[s]);
+    }
+  }
+  // Fold the 8 consumer warps' partial sums in warp order through the (now idle) ring.
+  __syncthreads();
+  float* s_part = reinterpret_cast<float*>(ring);
+  for (int w = 0; w < PIPE_CONSUMERS; ++w) {
+    if (warp == w) {
+#pragma unroll
+      for (int c = 0; c < NCH; ++c) {
+        const int col = c * 256 + lane * 8;
+        if (col < cols) {
+#pragma unroll
+          for (int j = 0; j < 8; ++j) {
+            if (w == 0) s_part[col + j] = acc[c * 8 + j];
+            else s_part[col + j] += acc[c * 8 + j];
+          }
+        }
+      }
+    }
+    __syncthreads();
+  }
+  float* out = partials + static_cast<long long>(blockIdx.x) * cols;
+  for (int i = threadIdx.x; i < cols; i += PIPE_THREADS) out[i] = s_part[i];
+  if (threadIdx.x == 0 && *abort_word != 0) atomicExch(status, *abort_word);
+}
+
 // dscale partials for rows too wide for register accumulators: block (bx, by) sums rows
 // by, by + gridDim.y, ... for 128 columns.
 __global__ void __launch_bounds__(128)
@@ -275,6 +522,31 @@ template <int NCH>
 static void launch_fwd(const cdl_tensor* x, const cdl_tensor* scale, const cdl_tensor* bias,
                        float eps, const cdl_tensor* y, const cdl_tensor* r_inv, int rows, int cols,
                        cudaStream_t stream) {
+  const char* mode = getenv("CDL_B200_NORM");
+  int* status = device_status_ptr();
+  if constexpr (NCH <= 8) {
+  if (status != nullptr && rows >= 2 * sm_count() && mode && strcmp(mode, "pipe") == 0) {
+    const int row_bytes = cols * 2;
+    int stages = PIPE_RING_BYTES / row_bytes;
+    if (stages > 64) stages = 64;
+    const size_t smem = static_cast<size_t>(stages) * row_bytes + 2 * stages * sizeof(uint64_t) + 16;
+    static std::once_flag once[64];
+    int dev = 0;
+    cudaGetDevice(&dev);
+    std::call_once(once[dev & 63], [&] {
+      cudaFuncSetAttribute(rmsnorm_fwd_pipe_kernel<NCH>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                           PIPE_RING_BYTES + 2 * 64 * static_cast<int>(sizeof(uint64_t)) + 16);
+    });
+    rmsnorm_fwd_pipe_kernel<NCH><<<sm_count(), PIPE_THREADS, smem, stream>>>(
+        static_cast<const __nv_bfloat16*>(x->ptr), x->stride[0],
+        scale ? static_cast<const __nv_bfloat16*>(scale->ptr) : nullptr,
+        bias ? static_cast<const __nv_bfloat16*>(bias->ptr) : nullptr,
+        static_cast<__nv_bfloat16*>(y->ptr), y->stride[0],
+        r_inv ? static_cast<float*>(r_inv->ptr) : nullptr, r_inv ? r_inv->stride[0] : 0, rows, cols,
+        eps, stages, status);
+    return;
+  }
+  }
   const int warps = FWD_THREADS / 32;
   const long long want = (static_cast<long long>(rows) + warps - 1) / warps;
   const int grid = static_cast<int>(want < 1 ? 1 : (want > (1 << 24) ? (1 << 24) : want));
@@ -298,6 +570,31 @@ static void launch_bwd(const cdl_tensor* x, const cdl_tensor* dy, const cdl_tens
       res ? static_cast<const __nv_bfloat16*>(res->ptr) : nullptr, res ? res->stride[0] : 0,
       static_cast<const __nv_bfloat16*>(scale->ptr), static_cast<const float*>(r_inv->ptr),
       r_inv->stride[0], static_cast<__nv_bfloat16*>(dx->ptr), dx->stride[0], partials, rows, cols);
+}
+
+template <int NCH>
+static void launch_bwd_pipe(const cdl_tensor* x, const cdl_tensor* dy, const cdl_tensor* res,
+                            const cdl_tensor* scale, const cdl_tensor* r_inv, const cdl_tensor* dx,
+                            float* partials, int rows, int cols, int* status, cudaStream_t stream) {
+  const int row_bytes = cols * 2;
+  const int stage_bytes = (res ? 3 : 2) * row_bytes;
+  int stages = (160 * 1024) / stage_bytes;
+  if (stages > 64) stages = 64;
+  const size_t smem = static_cast<size_t>(stages) * stage_bytes + row_bytes + 2 * stages * sizeof(uint64_t) + 16;
+  static std::once_flag once[64];
+  int dev = 0;
+  cudaGetDevice(&dev);
+  std::call_once(once[dev & 63], [&] {
+    cudaFuncSetAttribute(rmsnorm_bwd_pipe_kernel<NCH>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                         160 * 1024 + 4096 + 2 * 64 * static_cast<int>(sizeof(uint64_t)) + 16);
+  });
+  rmsnorm_bwd_pipe_kernel<NCH><<<sm_count(), PIPE_THREADS, smem, stream>>>(
+      static_cast<const __nv_bfloat16*>(x->ptr), x->stride[0],
+      static_cast<const __nv_bfloat16*>(dy->ptr), dy->stride[0],
+      res ? static_cast<const __nv_bfloat16*>(res->ptr) : nullptr, res ? res->stride[0] : 0,
+      static_cast<const __nv_bfloat16*>(scale->ptr), static_cast<const float*>(r_inv->ptr),
+      r_inv->stride[0], static_cast<__nv_bfloat16*>(dx->ptr), dx->stride[0], partials, rows, cols,
+      stages, status);
 }
 
 }  // namespace norm
@@ -371,8 +668,18 @@ int32_t rmsnorm_bwd_execute(const cdl_tensor* x, const cdl_tensor* dy, const cdl
   const int need = (r + warps - 1) / warps;
   if (grid > need) grid = need;
   int num_partials = grid;
+  const char* mode = getenv("CDL_B200_NORM");
+  const bool pipe = c <= 2048 && r >= 2 * sm_count() && !(mode && strcmp(mode, "simple") == 0);
   ProfileScope ps(PROF_NORM_BWD, (res ? 8.0 : 6.0) * rows * cols + 6.0 * cols + 4.0 * rows, stream);
-  if (c <= 256) launch_bwd<1, true>(x, dy, res, scale, r_inv, dx, partials, grid, r, c, stream);
+  if (pipe) {
+    num_partials = sm_count();
+    int* status = device_status_ptr();
+    if (!status) return fail(CDL_ERR_CUDA, "cannot resolve the device status word");
+    if (c <= 256) launch_bwd_pipe<1>(x, dy, res, scale, r_inv, dx, partials, r, c, status, stream);
+    else if (c <= 512) launch_bwd_pipe<2>(x, dy, res, scale, r_inv, dx, partials, r, c, status, stream);
+    else if (c <= 1024) launch_bwd_pipe<4>(x, dy, res, scale, r_inv, dx, partials, r, c, status, stream);
+    else launch_bwd_pipe<8>(x, dy, res, scale, r_inv, dx, partials, r, c, status, stream);
+  } else if (c <= 256) launch_bwd<1, true>(x, dy, res, scale, r_inv, dx, partials, grid, r, c, stream);
   else if (c <= 512) launch_bwd<2, true>(x, dy, res, scale, r_inv, dx, partials, grid, r, c, stream);
   else if (c <= 1024) launch_bwd<4, true>(x, dy, res, scale, r_inv, dx, partials, grid, r, c, stream);
   else if (c <= 2048) launch_bwd<8, true>(x, dy, res, scale, r_inv, dx, partials, grid, r, c, stream);
