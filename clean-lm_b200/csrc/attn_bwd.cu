@@ -28,6 +28,7 @@
 #include "ptx.cuh"
 
 #include <math.h>
+#include <stdlib.h>
 #include <string.h>
 
 #include <mutex>
@@ -37,6 +38,7 @@ namespace cdl {
 int32_t attn_check_operand(const char* op, const char* name, const cdl_tensor* t, long long B,
                            long long S, long long H, long long D);
 int32_t attn_encode_tmap(CUtensorMap* out, const cdl_tensor* t);
+int32_t attn_encode_tmap_rows(CUtensorMap* out, const cdl_tensor* t, uint32_t box_rows);
 
 namespace attn_bwd {
 
@@ -50,9 +52,11 @@ constexpr int TMEM_COLS = 512;
 // dK/dV kernel: K, V, Q x 2 stages, dO x 2 stages, dS^T, row statistics, barriers
 constexpr int KV_COL_S = 0, KV_COL_DP = 128, KV_COL_DV = 256, KV_COL_DK = 384;
 constexpr size_t KV_SMEM_BYTES = 7 * TILE_BYTES + 2 * 2 * 128 * sizeof(float) + 256;
-// dQ kernel: Q, dO, K x 2 stages, V x 2 stages, barriers
+// dQ kernel: Q, dO, K x 3 stages (S of block j+1 is issued a block ahead and dQ of block j reads
+// its K last, so two stages would expose the TMA latency every block), V x 2 stages, barriers
 constexpr int Q_COL_S = 0, Q_COL_DP = 256, Q_COL_DQ = 384;  // S is double-buffered: [0,128) [128,256)
-constexpr size_t Q_SMEM_BYTES = 6 * TILE_BYTES + 256;
+constexpr int QK_STAGES = 3;
+constexpr size_t Q_SMEM_BYTES = (4 + QK_STAGES) * TILE_BYTES + 256;
 static_assert(KV_SMEM_BYTES <= 232448 && Q_SMEM_BYTES <= 232448,
               "exceeds the 227 KiB of shared memory a CTA can opt in to");
 
@@ -79,7 +83,7 @@ struct KvBarriers {
 
 struct QBarriers {
   uint64_t qdo_full;
-  uint64_t k_full[2], k_empty[2], v_full[2], v_empty[2];
+  uint64_t k_full[QK_STAGES], k_empty[QK_STAGES], v_full[2], v_empty[2];
   uint64_t s_full[2], dp_full, ds_ready, dq_done;
   uint32_t tmem_base;
   int abort_word;
@@ -91,20 +95,62 @@ __device__ __forceinline__ float ex2(float x) {
   return y;
 }
 
+// 2^x for x <= ~0 on the FMA and integer pipes instead of the MUFU pipe (16 results per clock per
+// SM, the scarcest resource of the softmax recomputation): x = n + f with n = round(x) read from
+// the low mantissa bits of x + 1.5 * 2^23, f in [-0.5, 0.5], a degree-3 polynomial for 2^f
+// (relative error 1.4e-4 in f32, far below the bf16 rounding that follows) and n added to the
+// exponent field.  Inputs below -126 give 2^-126.
+__device__ __forceinline__ float exp2_poly(float x) {
+  x = fmaxf(x, -126.0f);
+  const float t = x + 12582912.0f;
+  const float f = x - (t - 12582912.0f);
+  float r = fmaf(f, 0.0551716685f, 0.2426111251f);
+  r = fmaf(r, f, 0.6932609677f);
+  r = fmaf(r, f, 0.9999280572f);
+  return __int_as_float(__float_as_int(r) + (__float_as_int(t) << 23));
+}
+// Of every 16 exponentials, this many go to the polynomial: it balances the MUFU pipe against the
+// FMA pipe for the instruction mix of the P phases (one FMA per element plus six per polynomial).
+constexpr int POLY_OF_16 = 7;
+template <int C>
+__device__ __forceinline__ float exp2_mixed(float x) {
+  if constexpr ((C & 15) < POLY_OF_16) return exp2_poly(x);
+  else return ex2(x);
+}
+
+template <int C>
+__device__ __forceinline__ void exp2_row_step(const float (&x)[64], float (&y)[64]) {
+  if constexpr (C < 64) {
+    y[C] = exp2_mixed<C>(x[C]);
+    exp2_row_step<C + 1>(x, y);
+  }
+}
+// y[c] = 2^x[c] for a thread's 64 elements, the two pipes interleaved element by element.
+__device__ __forceinline__ void exp2_row64(const float (&x)[64], float (&y)[64]) {
+  exp2_row_step<0>(x, y);
+}
+
 __device__ __forceinline__ void compute_bar_sync() {
   asm volatile("bar.sync 1, 256;" ::: "memory");
 }
 
-// Descriptors of one kernel differ only in the start address: the constant part is built once
-// and the 16-byte-granular address goes into the low word.
-__device__ __forceinline__ uint64_t desc_kmajor(uint64_t base, uint32_t addr, int k) {
-  // 128 x 128 bf16 tile as two 64-wide K panels; one MMA covers 16 elements of K (32 bytes)
-  return base | static_cast<uint64_t>(((addr + (k >> 2) * PANEL_BYTES + (k & 3) * 32) & 0x3FFFFu) >> 4);
+// The issuing thread builds a descriptor with one 32-bit add: the low word (start address and
+// leading byte offset) is computed once per tile, the K step adds a compile-time constant, the high
+// word is constant.  Between two products it executes as little as possible: whatever it does
+// there is time the tensor pipe may idle.
+constexpr uint32_t DESC_HI = (1024u >> 4) | (1u << 14) | (2u << 29);  // SBO 1024, version 1, SW128
+__device__ __forceinline__ uint32_t desc_lo(uint32_t addr, uint32_t lbo_bytes) {
+  return ((addr & 0x3FFFFu) >> 4) | ((lbo_bytes >> 4) << 16);
 }
-__device__ __forceinline__ uint64_t desc_mnmajor(uint64_t base, uint32_t addr, int k) {
-  // rows are the K index (128 bytes each); one MMA covers 16 rows
-  return base | static_cast<uint64_t>(((addr + k * 2048) & 0x3FFFFu) >> 4);
+__device__ __forceinline__ uint64_t desc_at(uint32_t lo, uint32_t byte_off) {
+  return (static_cast<uint64_t>(DESC_HI) << 32) | (lo + (byte_off >> 4));
 }
+// Byte offset of K step k (16 elements): K-major tile (two 16 KiB panels of 64 elements) and
+// MN-major tile (16 rows of 128 bytes per step).
+__device__ __forceinline__ constexpr uint32_t koff_k(int k) { return (k >> 2) * PANEL_BYTES + (k & 3) * 32; }
+__device__ __forceinline__ constexpr uint32_t koff_mn(int k) { return k * 2048; }
+// TMEM column of K step k of a bf16 A operand stored as two 32-column halves at +0 and +64.
+__device__ __forceinline__ constexpr uint32_t acol(int k) { return (k >> 2) * 64 + (k & 3) * 8; }
 
 // ---------------------------------------------------------------- preprocess
 // Half a warp per (b, h, padded row): 16 lanes x 8 bf16 = one 256-byte row of O and of dO.
@@ -253,24 +299,24 @@ __global__ void __launch_bounds__(THREADS, 1)
     if (elect_one() && iters > 0) {
       const uint32_t idesc_kk = make_idesc_bf16(128, 128, 0, 0);  // both operands K-major
       const uint32_t idesc_kmn = make_idesc_bf16(128, 128, 0, 1); // A K-major / TMEM, B MN-major
-      const uint64_t dk_base = smem_desc_sw128(0, 16, 1024);
-      const uint64_t dmn_base = smem_desc_sw128(0, PANEL_BYTES, 1024);
-      const uint32_t k_addr = smem_u32(s_k), v_addr = smem_u32(s_v), q_addr = smem_u32(s_q);
-      const uint32_t do_addr = smem_u32(s_do), ds_addr = smem_u32(s_ds);
-      auto issue_s = [&](int it) {  // S^T = K Q^T
-        const uint32_t qa = q_addr + (it & 1) * TILE_BYTES;
+      const uint32_t k_lo = desc_lo(smem_u32(s_k), 16), v_lo = desc_lo(smem_u32(s_v), 16);
+      const uint32_t q_lo = desc_lo(smem_u32(s_q), 16), do_lo = desc_lo(smem_u32(s_do), 16);
+      const uint32_t ds_lo = desc_lo(smem_u32(s_ds), 16);
+      const uint32_t q_mn_lo = desc_lo(smem_u32(s_q), PANEL_BYTES), do_mn_lo = desc_lo(smem_u32(s_do), PANEL_BYTES);
+      const uint32_t d_s = tmem_base + KV_COL_S, d_dp = tmem_base + KV_COL_DP;
+      const uint32_t d_dv = tmem_base + KV_COL_DV, d_dk = tmem_base + KV_COL_DK;
+      auto issue_s = [&](uint32_t stage) {  // S^T = K Q^T
+        const uint32_t qa = q_lo + stage * (TILE_BYTES >> 4);
 #pragma unroll
         for (int k = 0; k < 8; ++k)
-          umma_ss(tmem_base + KV_COL_S, desc_kmajor(dk_base, k_addr, k), desc_kmajor(dk_base, qa, k),
-                  idesc_kk, k != 0);
+          umma_ss(d_s, desc_at(k_lo, koff_k(k)), desc_at(qa, koff_k(k)), idesc_kk, k != 0);
         umma_commit(&bars->s_full);
       };
-      auto issue_dp = [&](int it) {  // dP^T = V dO^T
-        const uint32_t da = do_addr + (it & 1) * TILE_BYTES;
+      auto issue_dp = [&](uint32_t stage) {  // dP^T = V dO^T
+        const uint32_t da = do_lo + stage * (TILE_BYTES >> 4);
 #pragma unroll
         for (int k = 0; k < 8; ++k)
-          umma_ss(tmem_base + KV_COL_DP, desc_kmajor(dk_base, v_addr, k), desc_kmajor(dk_base, da, k),
-                  idesc_kk, k != 0);
+          umma_ss(d_dp, desc_at(v_lo, koff_k(k)), desc_at(da, koff_k(k)), idesc_kk, k != 0);
         umma_commit(&bars->dp_full);
       };
       bool ok = mbar_wait(&bars->kv_full, 0, abort_word, 221) &&
@@ -285,42 +331,37 @@ __global__ void __launch_bounds__(THREADS, 1)
         issue_dp(0);
       }
       for (int it = 0; it < iters && ok; ++it) {
-        const int s = it & 1;
+        const uint32_t s = it & 1;
         const uint32_t ph = it & 1;
-        const uint32_t ph_next = ((it + 1) >> 1) & 1;
-        const uint32_t qa = q_addr + s * TILE_BYTES, da = do_addr + s * TILE_BYTES;
-        // dV += P^T dO
+        const bool has_next = it + 1 < iters;
+        if (has_next) {  // Q and dO of the next block: loaded an iteration ago as a rule
+          const uint32_t ph_next = ((it + 1) >> 1) & 1;
+          ok = mbar_wait(&bars->q_full[s ^ 1], ph_next, abort_word, 227) &&
+               mbar_wait(&bars->do_full[s ^ 1], ph_next, abort_word, 228);
+          if (!ok) break;
+        }
+        const uint32_t acc = it > 0 ? 1u : 0u;
+        const uint32_t qf = q_mn_lo + s * (TILE_BYTES >> 4), df = do_mn_lo + s * (TILE_BYTES >> 4);
+        // dV += P^T dO  (A = P^T from TMEM)
         ok = mbar_wait(&bars->p_ready, ph, abort_word, 225);
         if (!ok) break;
         tc_fence_after();
 #pragma unroll
         for (int k = 0; k < 8; ++k)
-          umma_ts(tmem_base + KV_COL_DV, tmem_base + KV_COL_S + k * 8, desc_mnmajor(dmn_base, da, k),
-                  idesc_kmn, (it > 0 || k != 0) ? 1u : 0u);
+          umma_ts(d_dv, d_s + acol(k), desc_at(df, koff_mn(k)), idesc_kmn, k != 0 ? 1u : acc);
         umma_commit(&bars->do_empty[s]);  // dP^T(it) and dV(it) were the readers of this dO stage
         // S^T of the next query block; it overwrites P^T, which dV (issued above) reads first.
-        if (it + 1 < iters) {
-          ok = mbar_wait(&bars->q_full[s ^ 1], ph_next, abort_word, 227);
-          if (!ok) break;
-          tc_fence_after();
-          issue_s(it + 1);
-        }
-        // dK += dS^T Q
+        if (has_next) issue_s(s ^ 1);
+        // dK += dS^T Q  (A = dS^T from shared memory)
         ok = mbar_wait(&bars->ds_ready, ph, abort_word, 226);
         if (!ok) break;
         tc_fence_after();
 #pragma unroll
         for (int k = 0; k < 8; ++k)
-          umma_ss(tmem_base + KV_COL_DK, desc_kmajor(dk_base, ds_addr, k), desc_mnmajor(dmn_base, qa, k),
-                  idesc_kmn, (it > 0 || k != 0) ? 1u : 0u);
+          umma_ss(d_dk, desc_at(ds_lo, koff_k(k)), desc_at(qf, koff_mn(k)), idesc_kmn, k != 0 ? 1u : acc);
         umma_commit(&bars->q_empty[s]);
         // dP^T of the next block: its TMEM columns were read by the dS^T phase that just arrived.
-        if (it + 1 < iters) {
-          ok = mbar_wait(&bars->do_full[s ^ 1], ph_next, abort_word, 228);
-          if (!ok) break;
-          tc_fence_after();
-          issue_dp(it + 1);
-        }
+        if (has_next) issue_dp(s ^ 1);
       }
       if (ok) umma_commit(&bars->dk_done);
     }
@@ -364,28 +405,32 @@ __global__ void __launch_bounds__(THREADS, 1)
         tmem_ld32(tmem_base + lane_addr + KV_COL_S + wg * 64, sr[0]);
         tmem_ld32(tmem_base + lane_addr + KV_COL_S + wg * 64 + 32, sr[1]);
         tmem_wait_ld();
+        float x[64];
 #pragma unroll
         for (int c4 = 0; c4 < 16; ++c4) {
           const float4 l4 = lse_s[c4];
-          const float l[4] = {l4.x, l4.y, l4.z, l4.w};
+          x[c4 * 4 + 0] = fmaf(__uint_as_float(sr[(c4 * 4 + 0) >> 5][(c4 * 4 + 0) & 31]), p.scale_log2, -l4.x);
+          x[c4 * 4 + 1] = fmaf(__uint_as_float(sr[(c4 * 4 + 1) >> 5][(c4 * 4 + 1) & 31]), p.scale_log2, -l4.y);
+          x[c4 * 4 + 2] = fmaf(__uint_as_float(sr[(c4 * 4 + 2) >> 5][(c4 * 4 + 2) & 31]), p.scale_log2, -l4.z);
+          x[c4 * 4 + 3] = fmaf(__uint_as_float(sr[(c4 * 4 + 3) >> 5][(c4 * 4 + 3) & 31]), p.scale_log2, -l4.w);
+        }
+        exp2_row64(x, pr);
+        if (need_mask) {  // warp-uniform; only blocks on the diagonal or at the end of the keys
 #pragma unroll
-          for (int j = 0; j < 4; ++j) {
-            const int c = c4 * 4 + j;
-            float v = ex2(fmaf(__uint_as_float(sr[c >> 5][c & 31]), p.scale_log2, -l[j]));
-            if (need_mask) {
-              const int qrow = q0 + wg * 64 + c;
-              if (key >= p.Sk || (p.causal && key > qrow + shift)) v = 0.f;
-            }
-            pr[c] = v;
+          for (int c = 0; c < 64; ++c) {
+            const int qrow = q0 + wg * 64 + c;
+            if (key >= p.Sk || (p.causal && key > qrow + shift)) pr[c] = 0.f;
           }
         }
       }
-      compute_bar_sync();  // both halves have read S^T before P^T overwrites its columns
       {
+        // P^T (bf16 pairs) of this thread's 64 queries goes over the first 32 of the 64 S^T columns
+        // it has just read (queries 0-63 in columns [0,32), queries 64-127 in columns [64,96)), so
+        // the two column halves need no barrier between their loads and stores.
         uint32_t pk[32];
 #pragma unroll
         for (int c = 0; c < 32; ++c) pk[c] = pack_bf16x2(pr[2 * c], pr[2 * c + 1]);
-        tmem_st32(tmem_base + lane_addr + KV_COL_S + wg * 32, pk);
+        tmem_st32(tmem_base + lane_addr + KV_COL_S + wg * 64, pk);
         tmem_wait_st();
       }
       tc_fence_before();
@@ -405,7 +450,7 @@ __global__ void __launch_bounds__(THREADS, 1)
       const uint32_t ph = it & 1;
       if (it + 2 < iters) stat_next = fetch_stat(it + 2);  // lands while this iteration computes
 
-      // ---- dS^T = P^T o (dP^T - delta) * scale  -> shared memory (128-byte swizzle)
+      // ---- dS^T / scale = P^T o (dP^T - delta)  -> shared memory (128-byte swizzle)
       if (!mbar_wait(&bars->dp_full, ph, abort_word, 322)) { ok = false; break; }
       tc_fence_after();
       {
@@ -423,7 +468,7 @@ __global__ void __launch_bounds__(THREADS, 1)
 #pragma unroll
           for (int j = 0; j < 8; ++j) {
             const int c = ch * 8 + j;
-            d[j] = pr[c] * (__uint_as_float(dr[c >> 5][c & 31]) - dl[j]) * p.scale;
+            d[j] = pr[c] * (__uint_as_float(dr[c >> 5][c & 31]) - dl[j]);  // scale: dK epilogue
           }
           uint4 q;
           q.x = pack_bf16x2(d[0], d[1]);
@@ -471,13 +516,14 @@ __global__ void __launch_bounds__(THREADS, 1)
             for (int i = 0; i < 32; ++i) a[i] = 0u;
           }
           if (row_ok) {
+            const float sc = which == 0 ? 1.0f : p.scale;  // dS^T was accumulated without the scale
 #pragma unroll
             for (int g = 0; g < 4; ++g) {
               uint4 q;
-              q.x = pack_bf16x2(__uint_as_float(a[g * 8 + 0]), __uint_as_float(a[g * 8 + 1]));
-              q.y = pack_bf16x2(__uint_as_float(a[g * 8 + 2]), __uint_as_float(a[g * 8 + 3]));
-              q.z = pack_bf16x2(__uint_as_float(a[g * 8 + 4]), __uint_as_float(a[g * 8 + 5]));
-              q.w = pack_bf16x2(__uint_as_float(a[g * 8 + 6]), __uint_as_float(a[g * 8 + 7]));
+              q.x = pack_bf16x2(__uint_as_float(a[g * 8 + 0]) * sc, __uint_as_float(a[g * 8 + 1]) * sc);
+              q.y = pack_bf16x2(__uint_as_float(a[g * 8 + 2]) * sc, __uint_as_float(a[g * 8 + 3]) * sc);
+              q.z = pack_bf16x2(__uint_as_float(a[g * 8 + 4]) * sc, __uint_as_float(a[g * 8 + 5]) * sc);
+              q.w = pack_bf16x2(__uint_as_float(a[g * 8 + 6]) * sc, __uint_as_float(a[g * 8 + 7]) * sc);
               *reinterpret_cast<uint4*>(dst + half * 32 + g * 8) = q;
             }
           }
@@ -522,9 +568,9 @@ __global__ void __launch_bounds__(THREADS, 1)
   }
   uint8_t* s_q = smem;
   uint8_t* s_do = smem + TILE_BYTES;
-  uint8_t* s_k = smem + 2 * TILE_BYTES;  // 2 stages
-  uint8_t* s_v = smem + 4 * TILE_BYTES;  // 2 stages
-  QBarriers* bars = reinterpret_cast<QBarriers*>(smem + 6 * TILE_BYTES);
+  uint8_t* s_k = smem + 2 * TILE_BYTES;                 // QK_STAGES stages
+  uint8_t* s_v = s_k + QK_STAGES * TILE_BYTES;          // 2 stages
+  QBarriers* bars = reinterpret_cast<QBarriers*>(s_v + 2 * TILE_BYTES);
   volatile int* abort_word = &bars->abort_word;
 
   const int warp = threadIdx.x >> 5;
@@ -538,9 +584,11 @@ __global__ void __launch_bounds__(THREADS, 1)
 
   if (threadIdx.x == 0) {
     mbar_init(&bars->qdo_full, 1);
-    for (int i = 0; i < 2; ++i) {
+    for (int i = 0; i < QK_STAGES; ++i) {
       mbar_init(&bars->k_full[i], 1);
       mbar_init(&bars->k_empty[i], 1);
+    }
+    for (int i = 0; i < 2; ++i) {
       mbar_init(&bars->v_full[i], 1);
       mbar_init(&bars->v_empty[i], 1);
       mbar_init(&bars->s_full[i], 1);
@@ -577,14 +625,15 @@ __global__ void __launch_bounds__(THREADS, 1)
         tma_load_4d(s_do + dh * PANEL_BYTES, &tmap_do, &bars->qdo_full, dh * 64, q0, h, b);
       }
       for (int j = 0; j < n_kv; ++j) {
-        const int s = j & 1;
-        const uint32_t ph = ((j >> 1) & 1) ^ 1;
-        if (!mbar_wait(&bars->k_empty[s], ph, abort_word, 131)) break;
-        mbar_arrive_expect_tx(&bars->k_full[s], TILE_BYTES);
+        const int sk = j % QK_STAGES;
+        if (!mbar_wait(&bars->k_empty[sk], ((j / QK_STAGES) & 1) ^ 1, abort_word, 131)) break;
+        mbar_arrive_expect_tx(&bars->k_full[sk], TILE_BYTES);
 #pragma unroll
         for (int dh = 0; dh < 2; ++dh)
-          tma_load_4d(s_k + s * TILE_BYTES + dh * PANEL_BYTES, &tmap_k, &bars->k_full[s], dh * 64,
+          tma_load_4d(s_k + sk * TILE_BYTES + dh * PANEL_BYTES, &tmap_k, &bars->k_full[sk], dh * 64,
                       j * BKV, kvh, b);
+        const int s = j & 1;
+        const uint32_t ph = ((j >> 1) & 1) ^ 1;
         if (!mbar_wait(&bars->v_empty[s], ph, abort_word, 132)) break;
         mbar_arrive_expect_tx(&bars->v_full[s], TILE_BYTES);
 #pragma unroll
@@ -600,64 +649,65 @@ __global__ void __launch_bounds__(THREADS, 1)
     if (elect_one() && n_kv > 0) {
       const uint32_t idesc_kk = make_idesc_bf16(128, 128, 0, 0);
       const uint32_t idesc_kmn = make_idesc_bf16(128, 128, 0, 1);
-      const uint64_t dk_base = smem_desc_sw128(0, 16, 1024);
-      const uint64_t dmn_base = smem_desc_sw128(0, PANEL_BYTES, 1024);
-      const uint32_t q_addr = smem_u32(s_q), do_addr = smem_u32(s_do);
-      const uint32_t k_addr = smem_u32(s_k), v_addr = smem_u32(s_v);
-      auto issue_s = [&](int j) {  // S = Q K_j^T
-        const uint32_t ka = k_addr + (j & 1) * TILE_BYTES;
+      const uint32_t q_lo = desc_lo(smem_u32(s_q), 16), do_lo = desc_lo(smem_u32(s_do), 16);
+      const uint32_t k_lo = desc_lo(smem_u32(s_k), 16), v_lo = desc_lo(smem_u32(s_v), 16);
+      const uint32_t k_mn_lo = desc_lo(smem_u32(s_k), PANEL_BYTES);
+      const uint32_t d_s = tmem_base + Q_COL_S, d_dp = tmem_base + Q_COL_DP, d_dq = tmem_base + Q_COL_DQ;
+      auto issue_s = [&](uint32_t buf, uint32_t stage) {  // S = Q K_j^T
+        const uint32_t ka = k_lo + stage * (TILE_BYTES >> 4);
+        const uint32_t d = d_s + buf * 128;
 #pragma unroll
         for (int k = 0; k < 8; ++k)
-          umma_ss(tmem_base + Q_COL_S + (j & 1) * 128, desc_kmajor(dk_base, q_addr, k),
-                  desc_kmajor(dk_base, ka, k), idesc_kk, k != 0);
-        umma_commit(&bars->s_full[j & 1]);
+          umma_ss(d, desc_at(q_lo, koff_k(k)), desc_at(ka, koff_k(k)), idesc_kk, k != 0);
+        umma_commit(&bars->s_full[buf]);
       };
-      auto issue_dp = [&](int j) {  // dP = dO V_j^T
-        const uint32_t va = v_addr + (j & 1) * TILE_BYTES;
+      auto issue_dp = [&](uint32_t stage) {  // dP = dO V_j^T
+        const uint32_t va = v_lo + stage * (TILE_BYTES >> 4);
 #pragma unroll
         for (int k = 0; k < 8; ++k)
-          umma_ss(tmem_base + Q_COL_DP, desc_kmajor(dk_base, do_addr, k), desc_kmajor(dk_base, va, k),
-                  idesc_kk, k != 0);
+          umma_ss(d_dp, desc_at(do_lo, koff_k(k)), desc_at(va, koff_k(k)), idesc_kk, k != 0);
         umma_commit(&bars->dp_full);
-        umma_commit(&bars->v_empty[j & 1]);
+        umma_commit(&bars->v_empty[stage]);
       };
       bool ok = mbar_wait(&bars->qdo_full, 0, abort_word, 231) &&
                 mbar_wait(&bars->k_full[0], 0, abort_word, 232);
       if (ok) {
         tc_fence_after();
-        issue_s(0);
+        issue_s(0, 0);
         ok = mbar_wait(&bars->v_full[0], 0, abort_word, 233);
       }
       if (ok) {
         tc_fence_after();
         issue_dp(0);
       }
+      uint32_t sk = 0;  // K stage of block j
       for (int j = 0; j < n_kv && ok; ++j) {
-        const int s = j & 1;
-        const uint32_t ph_next = ((j + 1) >> 1) & 1;
-        if (j + 1 < n_kv) {
-          // S buffer s ^ 1 held dS(j-1), whose reader dQ(j-1) was issued before this point.
-          ok = mbar_wait(&bars->k_full[s ^ 1], ph_next, abort_word, 234);
+        const uint32_t s = j & 1;  // S buffer and V stage
+        const uint32_t sk1 = sk + 1 == QK_STAGES ? 0 : sk + 1;
+        const bool has_next = j + 1 < n_kv;
+        if (has_next) {
+          // K and V of the next block (loaded a block ago as a rule).  S buffer s ^ 1 held
+          // dS(j-1), whose reader dQ(j-1) was issued before this point.
+          ok = mbar_wait(&bars->k_full[sk1], ((j + 1) / QK_STAGES) & 1, abort_word, 234) &&
+               mbar_wait(&bars->v_full[s ^ 1], ((j + 1) >> 1) & 1, abort_word, 236);
           if (!ok) break;
           tc_fence_after();
-          issue_s(j + 1);
+          issue_s(s ^ 1, sk1);
         }
         ok = mbar_wait(&bars->ds_ready, j & 1, abort_word, 235);
         if (!ok) break;
         tc_fence_after();
-        if (j + 1 < n_kv) {
-          ok = mbar_wait(&bars->v_full[s ^ 1], ph_next, abort_word, 236);
-          if (!ok) break;
-          tc_fence_after();
-          issue_dp(j + 1);
-        }
-        // dQ += dS K_j : A = dS (bf16 pairs in the S buffer's first 64 columns), B = K_j MN-major
-        const uint32_t ka = k_addr + s * TILE_BYTES;
+        if (has_next) issue_dp(s ^ 1);
+        // dQ += dS K_j : A = dS (bf16 pairs in columns [0,32) and [64,96) of the S buffer),
+        // B = K_j MN-major
+        const uint32_t kf = k_mn_lo + sk * (TILE_BYTES >> 4);
+        const uint32_t a_ds = d_s + s * 128;
+        const uint32_t acc = j > 0 ? 1u : 0u;
 #pragma unroll
         for (int k = 0; k < 8; ++k)
-          umma_ts(tmem_base + Q_COL_DQ, tmem_base + Q_COL_S + s * 128 + k * 8,
-                  desc_mnmajor(dmn_base, ka, k), idesc_kmn, (j > 0 || k != 0) ? 1u : 0u);
-        umma_commit(&bars->k_empty[s]);
+          umma_ts(d_dq, a_ds + acol(k), desc_at(kf, koff_mn(k)), idesc_kmn, k != 0 ? 1u : acc);
+        umma_commit(&bars->k_empty[sk]);
+        sk = sk1;
       }
       if (ok) umma_commit(&bars->dq_done);
     }
@@ -690,11 +740,14 @@ __global__ void __launch_bounds__(THREADS, 1)
         tmem_ld32(tmem_base + lane_addr + Q_COL_S + s * 128 + wg * 64, sr[0]);
         tmem_ld32(tmem_base + lane_addr + Q_COL_S + s * 128 + wg * 64 + 32, sr[1]);
         tmem_wait_ld();
+        float x[64];
 #pragma unroll
-        for (int c = 0; c < 64; ++c) {
-          float v = ex2(fmaf(__uint_as_float(sr[c >> 5][c & 31]), p.scale_log2, -lse2));
-          if (need_mask && key0 + c > key_limit) v = 0.f;
-          pr[c] = v;
+        for (int c = 0; c < 64; ++c) x[c] = fmaf(__uint_as_float(sr[c >> 5][c & 31]), p.scale_log2, -lse2);
+        exp2_row64(x, pr);
+        if (need_mask) {  // warp-uniform
+#pragma unroll
+          for (int c = 0; c < 64; ++c)
+            if (key0 + c > key_limit) pr[c] = 0.f;
         }
       }
       if (!mbar_wait(&bars->dp_full, j & 1, abort_word, 332)) { ok = false; break; }
@@ -707,13 +760,16 @@ __global__ void __launch_bounds__(THREADS, 1)
         tmem_wait_ld();
 #pragma unroll
         for (int c = 0; c < 32; ++c) {
-          const float d0 = pr[2 * c] * (__uint_as_float(dr[(2 * c) >> 5][(2 * c) & 31]) - delta) * p.scale;
-          const float d1 = pr[2 * c + 1] * (__uint_as_float(dr[(2 * c + 1) >> 5][(2 * c + 1) & 31]) - delta) * p.scale;
+          // without the softmax scale: it is applied once, when dQ leaves tensor memory
+          const float d0 = pr[2 * c] * (__uint_as_float(dr[(2 * c) >> 5][(2 * c) & 31]) - delta);
+          const float d1 = pr[2 * c + 1] * (__uint_as_float(dr[(2 * c + 1) >> 5][(2 * c + 1) & 31]) - delta);
           pk[c] = pack_bf16x2(d0, d1);
         }
       }
-      compute_bar_sync();  // both halves have read S before dS overwrites its first 64 columns
-      tmem_st32(tmem_base + lane_addr + Q_COL_S + s * 128 + wg * 32, pk);
+      // dS (bf16 pairs) of this thread's 64 keys goes over the first 32 of the 64 S columns it has
+      // read (keys 0-63 in columns [0,32), keys 64-127 in columns [64,96) of the buffer): no barrier
+      // between the two column halves is needed.
+      tmem_st32(tmem_base + lane_addr + Q_COL_S + s * 128 + wg * 64, pk);
       tmem_wait_st();
       tc_fence_before();
       mbar_arrive(&bars->ds_ready);
@@ -737,13 +793,14 @@ __global__ void __launch_bounds__(THREADS, 1)
           for (int i = 0; i < 32; ++i) a[i] = 0u;
         }
         if (row < p.Sq) {
+          const float sc = p.scale;
 #pragma unroll
           for (int g = 0; g < 4; ++g) {
             uint4 q;
-            q.x = pack_bf16x2(__uint_as_float(a[g * 8 + 0]), __uint_as_float(a[g * 8 + 1]));
-            q.y = pack_bf16x2(__uint_as_float(a[g * 8 + 2]), __uint_as_float(a[g * 8 + 3]));
-            q.z = pack_bf16x2(__uint_as_float(a[g * 8 + 4]), __uint_as_float(a[g * 8 + 5]));
-            q.w = pack_bf16x2(__uint_as_float(a[g * 8 + 6]), __uint_as_float(a[g * 8 + 7]));
+            q.x = pack_bf16x2(__uint_as_float(a[g * 8 + 0]) * sc, __uint_as_float(a[g * 8 + 1]) * sc);
+            q.y = pack_bf16x2(__uint_as_float(a[g * 8 + 2]) * sc, __uint_as_float(a[g * 8 + 3]) * sc);
+            q.z = pack_bf16x2(__uint_as_float(a[g * 8 + 4]) * sc, __uint_as_float(a[g * 8 + 5]) * sc);
+            q.w = pack_bf16x2(__uint_as_float(a[g * 8 + 6]) * sc, __uint_as_float(a[g * 8 + 7]) * sc);
             *reinterpret_cast<uint4*>(dst + half * 32 + g * 8) = q;
           }
         }

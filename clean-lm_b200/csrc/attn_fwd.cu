@@ -388,7 +388,14 @@ int32_t attn_check_operand(const char* op, const char* name, const cdl_tensor* t
   return CDL_OK;
 }
 
+int32_t attn_encode_tmap_rows(CUtensorMap* out, const cdl_tensor* t, uint32_t box_rows);
+
 int32_t attn_encode_tmap(CUtensorMap* out, const cdl_tensor* t) {
+  return attn_encode_tmap_rows(out, t, 128);
+}
+
+// Same view with a box of `box_rows` sequence positions x 64 head-dimension elements.
+int32_t attn_encode_tmap_rows(CUtensorMap* out, const cdl_tensor* t, uint32_t box_rows) {
   // innermost-first: D, S, H, B
   const uint64_t dims[4] = {static_cast<uint64_t>(t->shape[3]), static_cast<uint64_t>(t->shape[1]),
                             static_cast<uint64_t>(t->shape[2]), static_cast<uint64_t>(t->shape[0])};
@@ -397,7 +404,7 @@ int32_t attn_encode_tmap(CUtensorMap* out, const cdl_tensor* t) {
   };
   const long long row = t->shape[3];
   const uint64_t strides[4] = {0, st(1, row), st(2, row), st(0, row)};
-  const uint32_t box[4] = {64, 128, 1, 1};
+  const uint32_t box[4] = {64, box_rows, 1, 1};
   return encode_tmap(out, t->ptr, CDL_BF16, 4, dims, strides, box, true);
 }
 
