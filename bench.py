@@ -395,11 +395,12 @@ def run_kernel(args) -> None:
             r_inv = cdl.ops.norm_fwd(xs[0], cdl.ops.NormFwdOpts(scale=w, save_stats=True)).r_inv
             ds = torch.zeros(cols, device=dev)
             scr = torch.empty(cdl.ops.norm_bwd_scratch_bytes(rows, cols), dtype=torch.uint8, device=dev)
-            fns = [(lambda x=x, dy=dy: cdl.ops.norm_bwd(x, dy, w, r_inv, ds, scratch=scr))
-                   for x, dy in zip(xs, dys)]
-            work = 6.0 * rows * cols + 6 * cols + 4 * rows
+            ress = [rnd(rows, cols) for _ in range(nbuf)] if args.residual else [None] * nbuf
+            fns = [(lambda x=x, dy=dy, rs=rs: cdl.ops.norm_bwd(x, dy, w, r_inv, ds, scratch=scr, residual_dy=rs))
+                   for x, dy, rs in zip(xs, dys, ress)]
+            work = (8.0 if args.residual else 6.0) * rows * cols + 6 * cols + 4 * rows
         unit, peak = "GB/s", peaks["hbm"]
-        desc = f"{k} x[{rows},{cols}] bf16"
+        desc = f"{k} x[{rows},{cols}] bf16" + (" + residual gradient" if k == "norm_bwd" and args.residual else "")
     else:
         bsz, s_, h = args.batch, args.seq, args.heads
         q, kx, v, do = (rnd(bsz, s_, h, 128) for _ in range(4))
@@ -418,18 +419,37 @@ def run_kernel(args) -> None:
     for i in range(args.warmup):
         fns[i % len(fns)]()
     torch.cuda.synchronize()
-    # Per-launch CUDA events recorded by the library around its own kernels: unlike events around
-    # the Python call, they do not include host launch overhead, which matters for 20-100 us kernels.
+    # The `steps` launches are captured into one CUDA graph and replayed, so that they run back to
+    # back on the device: through Python a launch costs more host time than a 25-100 us kernel
+    # runs, and an event pair around every single launch adds several microseconds to each.
+    graph = torch.cuda.CUDAGraph()
+    with torch.cuda.graph(graph):
+        for i in range(args.steps):
+            fns[i % len(fns)]()
+    graph.replay()
+    torch.cuda.synchronize()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    reps = []
+    for _ in range(3):
+        e0.record()
+        graph.replay()
+        e1.record()
+        torch.cuda.synchronize()
+        reps.append(e0.elapsed_time(e1) / args.steps)
+    ms = min(reps)
+    # Per-launch CUDA events recorded by the library around its own kernels, for comparison.
     L.profile_start(4 * args.steps + 16)
     for i in range(args.steps):
         fns[i % len(fns)]()
     kind = {"gemm": "gemm", "norm_fwd": "norm_fwd", "norm_bwd": "norm_bwd", "attn_fwd": "attn_fwd",
             "attn_bwd": "attn_bwd"}[k]
     times = [ms_ for kd, ms_, _ in L.profile_stop(4 * args.steps + 16) if kd == kind]
-    ms = sum(times) / len(times)
+    ms_events = sum(times) / len(times)
     assert L.device_status() == 0
     achieved = work / (ms * 1e-3) / (1e12 if unit == "TFLOP/s" else 1e9)
-    print(json.dumps({"kernel": k, "case": desc, "ms": ms, "achieved": achieved, "unit": unit,
+    print(json.dumps({"kernel": k, "case": desc, "ms": ms, "ms_per_launch_events": ms_events,
+                      "timing": "CUDA graph of `steps` back-to-back launches, best of 3 replays",
+                      "achieved": achieved, "unit": unit,
                       "peak": peak, "frac": achieved / peak,
                       "peak_source": peaks["source"] + (" burst cuBLAS bf16" if unit == "TFLOP/s"
                                                         else " copy bandwidth"),
@@ -528,6 +548,8 @@ def main() -> None:
     ap.add_argument("--layout", default="nn", choices=["nn", "nt", "tn", "tt"],
                     help="gemm: n = row-major operand, t = transposed view (A then B)")
     ap.add_argument("--accumulate", action="store_true", help="gemm: D (f32) += A.B, the wgrad form")
+    ap.add_argument("--residual", action="store_true",
+                    help="norm_bwd: add a residual gradient into dx (the form the block uses)")
     ap.add_argument("--rows", type=int, default=16384)
     ap.add_argument("--cols", type=int, default=2048)
     ap.add_argument("--batch", type=int, default=8)

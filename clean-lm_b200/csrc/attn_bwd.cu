@@ -14,7 +14,7 @@
 //        S^T  = K Q^T   (SS) -> TMEM [0,128)     P^T (bf16) overwrites it in place
 //        dP^T = V dO^T  (SS) -> TMEM [128,256)
 //        dV  += P^T dO  (A = P^T from TMEM)      -> TMEM [256,384)
-//        dK  += dS^T Q  (A = dS^T from shared)   -> TMEM [384,512)
+//        dK  += dS^T Q  (A = dS^T from TMEM, written over dP^T) -> TMEM [384,512)
 //   3. dQ: one CTA per (128-query block, head, batch) walks the key blocks it sees and recomputes
 //      S and dP (two extra products per block pair) so that dQ accumulates in TMEM instead of
 //      being reduced through global memory from the dK/dV kernel -- measured on B200, the L2
@@ -49,9 +49,9 @@ constexpr int TILE_BYTES = 128 * 128 * 2;
 constexpr int PANEL_BYTES = TILE_BYTES / 2;
 constexpr int THREADS = 384;  // warps 0-3 control (TMA, MMA, 2 idle), warps 4-11 compute
 constexpr int TMEM_COLS = 512;
-// dK/dV kernel: K, V, Q x 2 stages, dO x 2 stages, dS^T, row statistics, barriers
+// dK/dV kernel: K, V, Q x 2 stages, dO x 2 stages, row statistics, barriers
 constexpr int KV_COL_S = 0, KV_COL_DP = 128, KV_COL_DV = 256, KV_COL_DK = 384;
-constexpr size_t KV_SMEM_BYTES = 7 * TILE_BYTES + 2 * 2 * 128 * sizeof(float) + 256;
+constexpr size_t KV_SMEM_BYTES = 6 * TILE_BYTES + 2 * 2 * 128 * sizeof(float) + 256;
 // dQ kernel: Q, dO, K x 3 stages (S of block j+1 is issued a block ahead and dQ of block j reads
 // its K last, so two stages would expose the TMA latency every block), V x 2 stages, barriers
 constexpr int Q_COL_S = 0, Q_COL_DP = 256, Q_COL_DQ = 384;  // S is double-buffered: [0,128) [128,256)
@@ -111,7 +111,10 @@ __device__ __forceinline__ float exp2_poly(float x) {
 }
 // Of every 16 exponentials, this many go to the polynomial: it balances the MUFU pipe against the
 // FMA pipe for the instruction mix of the P phases (one FMA per element plus six per polynomial).
-constexpr int POLY_OF_16 = 7;
+#ifndef CDL_POLY_OF_16
+#define CDL_POLY_OF_16 6
+#endif
+constexpr int POLY_OF_16 = CDL_POLY_OF_16;
 template <int C>
 __device__ __forceinline__ float exp2_mixed(float x) {
   if constexpr ((C & 15) < POLY_OF_16) return exp2_poly(x);
@@ -210,8 +213,7 @@ __global__ void __launch_bounds__(THREADS, 1)
   uint8_t* s_v = smem + TILE_BYTES;
   uint8_t* s_q = smem + 2 * TILE_BYTES;   // 2 stages
   uint8_t* s_do = smem + 4 * TILE_BYTES;  // 2 stages
-  uint8_t* s_ds = smem + 6 * TILE_BYTES;
-  float* s_lse = reinterpret_cast<float*>(smem + 7 * TILE_BYTES);  // [2][128]
+  float* s_lse = reinterpret_cast<float*>(smem + 6 * TILE_BYTES);  // [2][128]
   float* s_delta = s_lse + 2 * 128;                                // [2][128]
   KvBarriers* bars = reinterpret_cast<KvBarriers*>(s_delta + 2 * 128);
   volatile int* abort_word = &bars->abort_word;
@@ -301,7 +303,6 @@ __global__ void __launch_bounds__(THREADS, 1)
       const uint32_t idesc_kmn = make_idesc_bf16(128, 128, 0, 1); // A K-major / TMEM, B MN-major
       const uint32_t k_lo = desc_lo(smem_u32(s_k), 16), v_lo = desc_lo(smem_u32(s_v), 16);
       const uint32_t q_lo = desc_lo(smem_u32(s_q), 16), do_lo = desc_lo(smem_u32(s_do), 16);
-      const uint32_t ds_lo = desc_lo(smem_u32(s_ds), 16);
       const uint32_t q_mn_lo = desc_lo(smem_u32(s_q), PANEL_BYTES), do_mn_lo = desc_lo(smem_u32(s_do), PANEL_BYTES);
       const uint32_t d_s = tmem_base + KV_COL_S, d_dp = tmem_base + KV_COL_DP;
       const uint32_t d_dv = tmem_base + KV_COL_DV, d_dk = tmem_base + KV_COL_DK;
@@ -352,15 +353,15 @@ __global__ void __launch_bounds__(THREADS, 1)
         umma_commit(&bars->do_empty[s]);  // dP^T(it) and dV(it) were the readers of this dO stage
         // S^T of the next query block; it overwrites P^T, which dV (issued above) reads first.
         if (has_next) issue_s(s ^ 1);
-        // dK += dS^T Q  (A = dS^T from shared memory)
+        // dK += dS^T Q  (A = dS^T from TMEM, written over dP^T)
         ok = mbar_wait(&bars->ds_ready, ph, abort_word, 226);
         if (!ok) break;
         tc_fence_after();
 #pragma unroll
         for (int k = 0; k < 8; ++k)
-          umma_ss(d_dk, desc_at(ds_lo, koff_k(k)), desc_at(qf, koff_mn(k)), idesc_kmn, k != 0 ? 1u : acc);
+          umma_ts(d_dk, d_dp + acol(k), desc_at(qf, koff_mn(k)), idesc_kmn, k != 0 ? 1u : acc);
         umma_commit(&bars->q_empty[s]);
-        // dP^T of the next block: its TMEM columns were read by the dS^T phase that just arrived.
+        // dP^T of the next block overwrites dS^T, which dK (issued above) reads first.
         if (has_next) issue_dp(s ^ 1);
       }
       if (ok) umma_commit(&bars->dk_done);
@@ -450,7 +451,7 @@ __global__ void __launch_bounds__(THREADS, 1)
       const uint32_t ph = it & 1;
       if (it + 2 < iters) stat_next = fetch_stat(it + 2);  // lands while this iteration computes
 
-      // ---- dS^T / scale = P^T o (dP^T - delta)  -> shared memory (128-byte swizzle)
+      // ---- dS^T / scale = P^T o (dP^T - delta)  -> TMEM (bf16) over the dP^T columns
       if (!mbar_wait(&bars->dp_full, ph, abort_word, 322)) { ok = false; break; }
       tc_fence_after();
       {
@@ -459,7 +460,7 @@ __global__ void __launch_bounds__(THREADS, 1)
         tmem_ld32(tmem_base + lane_addr + KV_COL_DP + wg * 64, dr[0]);
         tmem_ld32(tmem_base + lane_addr + KV_COL_DP + wg * 64 + 32, dr[1]);
         tmem_wait_ld();
-        uint8_t* row_ptr = s_ds + wg * PANEL_BYTES + r * 128;
+        uint32_t pk[32];
 #pragma unroll
         for (int ch = 0; ch < 8; ++ch) {
           const float4 d0 = delta_s[ch * 2], d1 = delta_s[ch * 2 + 1];
@@ -470,16 +471,19 @@ __global__ void __launch_bounds__(THREADS, 1)
             const int c = ch * 8 + j;
             d[j] = pr[c] * (__uint_as_float(dr[c >> 5][c & 31]) - dl[j]);  // scale: dK epilogue
           }
-          uint4 q;
-          q.x = pack_bf16x2(d[0], d[1]);
-          q.y = pack_bf16x2(d[2], d[3]);
-          q.z = pack_bf16x2(d[4], d[5]);
-          q.w = pack_bf16x2(d[6], d[7]);
-          *reinterpret_cast<uint4*>(row_ptr + ((ch ^ (r & 7)) << 4)) = q;
+          pk[ch * 4 + 0] = pack_bf16x2(d[0], d[1]);
+          pk[ch * 4 + 1] = pack_bf16x2(d[2], d[3]);
+          pk[ch * 4 + 2] = pack_bf16x2(d[4], d[5]);
+          pk[ch * 4 + 3] = pack_bf16x2(d[6], d[7]);
         }
+        // dS^T (bf16 pairs) goes over the first 32 of the 64 dP^T columns this thread has read,
+        // like P^T over S^T: the dK product reads its A operand from tensor memory (a TS MMA
+        // issues every ~82 clk, an SS one every ~112 clk), and no shared-memory tile, proxy fence
+        // or barrier between the two column halves is needed.
+        tmem_st32(tmem_base + lane_addr + KV_COL_DP + wg * 64, pk);
+        tmem_wait_st();
       }
       tc_fence_before();
-      fence_proxy_async_smem();
       mbar_arrive(&bars->ds_ready);
 
       // ---- P^T of the next query block (overlaps the dK product of this one)

@@ -669,7 +669,12 @@ int32_t rmsnorm_bwd_execute(const cdl_tensor* x, const cdl_tensor* dy, const cdl
   if (grid > need) grid = need;
   int num_partials = grid;
   const char* mode = getenv("CDL_B200_NORM");
-  const bool pipe = c <= 2048 && r >= 2 * sm_count() && !(mode && strcmp(mode, "simple") == 0);
+  // Measured back to back at [16384, 2048]: without a residual gradient the warp-per-row kernel
+  // is faster (47 us against 55 us); with one, the pipelined kernel is (60 us against 72 us: the
+  // third row does not fit the other kernel's registers next to the dscale accumulators).
+  const bool pipe = c <= 2048 && r >= 2 * sm_count() &&
+                    (mode ? strcmp(mode, "pipe") == 0 || (res != nullptr && strcmp(mode, "simple") != 0)
+                          : res != nullptr);
   ProfileScope ps(PROF_NORM_BWD, (res ? 8.0 : 6.0) * rows * cols + 6.0 * cols + 4.0 * rows, stream);
   if (pipe) {
     num_partials = sm_count();
