@@ -95,20 +95,6 @@ __device__ __forceinline__ float ex2(float x) {
   return y;
 }
 
-// 2^x for x <= ~0 on the FMA and integer pipes instead of the MUFU pipe (16 results per clock per
-// SM, the scarcest resource of the softmax recomputation): x = n + f with n = round(x) read from
-// the low mantissa bits of x + 1.5 * 2^23, f in [-0.5, 0.5], a degree-3 polynomial for 2^f
-// (relative error 1.4e-4 in f32, far below the bf16 rounding that follows) and n added to the
-// exponent field.  Inputs below -126 give 2^-126.
-__device__ __forceinline__ float exp2_poly(float x) {
-  x = fmaxf(x, -126.0f);
-  const float t = x + 12582912.0f;
-  const float f = x - (t - 12582912.0f);
-  float r = fmaf(f, 0.0551716685f, 0.2426111251f);
-  r = fmaf(r, f, 0.6932609677f);
-  r = fmaf(r, f, 0.9999280572f);
-  return __int_as_float(__float_as_int(r) + (__float_as_int(t) << 23));
-}
 // Of every 16 exponentials, this many go to the polynomial: it balances the MUFU pipe against the
 // FMA pipe for the instruction mix of the P phases (one FMA per element plus six per polynomial).
 #ifndef CDL_POLY_OF_16

@@ -163,26 +163,35 @@ __global__ void __launch_bounds__(THREADS, 1)
     if (elect_one() && n_max > 0) {
       const uint32_t idesc_qk = make_idesc_bf16(BQ, BKV, 0, 0);
       const uint32_t idesc_pv = make_idesc_bf16(BQ, D, 0, 1);
-      const uint32_t q_addr = smem_u32(s_q), k_addr = smem_u32(s_k), v_addr = smem_u32(s_v);
+      // A descriptor costs the issuing thread one 32-bit add: the low word (start address and
+      // leading byte offset) is computed once per operand, a K step adds a constant, the high
+      // word (SBO 1024, version 1, 128-byte swizzle) is constant.
+      constexpr uint32_t DESC_HI = (1024u >> 4) | (1u << 14) | (2u << 29);
+      auto lo_of = [](uint32_t addr, uint32_t lbo) { return ((addr & 0x3FFFFu) >> 4) | ((lbo >> 4) << 16); };
+      auto desc = [&](uint32_t lo, uint32_t off) {
+        return (static_cast<uint64_t>(DESC_HI) << 32) | (lo + (off >> 4));
+      };
+      const uint32_t q_lo = lo_of(smem_u32(s_q), 16), k_lo = lo_of(smem_u32(s_k), 16);
+      const uint32_t v_lo = lo_of(smem_u32(s_v), PANEL_BYTES);
       const int n_t[2] = {n0, n1};
       // S_t = Q_t K_j^T : 8 MMAs of K = 16 over the two 64-wide d panels.
       auto issue_qk = [&](int t, int stage) {
-        const uint32_t qa = q_addr + t * TILE_BYTES, ka = k_addr + stage * TILE_BYTES;
+        const uint32_t qa = q_lo + t * (TILE_BYTES >> 4), ka = k_lo + stage * (TILE_BYTES >> 4);
+        const uint32_t d = tmem_base + t * 128;
 #pragma unroll
         for (int k = 0; k < D / 16; ++k) {
           const uint32_t off = (k >> 2) * PANEL_BYTES + (k & 3) * 32;
-          umma_ss(tmem_base + t * 128, smem_desc_sw128(qa + off, 16, 1024),
-                  smem_desc_sw128(ka + off, 16, 1024), idesc_qk, k != 0);
+          umma_ss(d, desc(qa, off), desc(ka, off), idesc_qk, k != 0);
         }
       };
       // O_t (+)= P_t V_j : A = P (bf16 pairs in TMEM columns), B = V as an MN-major tile.
       auto issue_pv = [&](int t, int stage, bool accumulate) {
-        const uint32_t va = v_addr + stage * TILE_BYTES;
+        const uint32_t va = v_lo + stage * (TILE_BYTES >> 4);
+        const uint32_t d = tmem_base + 256 + t * 128, a = tmem_base + t * 128;
+        const uint32_t acc = accumulate ? 1u : 0u;
 #pragma unroll
         for (int k = 0; k < BKV / 16; ++k)
-          umma_ts(tmem_base + 256 + t * 128, tmem_base + t * 128 + k * 8,
-                  smem_desc_sw128(va + k * 2048, PANEL_BYTES, 1024), idesc_pv,
-                  (accumulate || k != 0) ? 1u : 0u);
+          umma_ts(d, a + k * 8, desc(va, k * 2048), idesc_pv, k != 0 ? 1u : acc);
       };
       bool ok = mbar_wait(&bars->q_full, 0, abort_word, 211);
       ok = ok && mbar_wait(&bars->k_full[0], 0, abort_word, 212);
@@ -302,6 +311,9 @@ __global__ void __launch_bounds__(THREADS, 1)
         uint32_t pk[16];
 #pragma unroll
         for (int i = 0; i < 16; ++i) {
+          // (All exponentials on the MUFU pipe: moving a share of them to a polynomial on the FMA
+          // pipe, which pays in the backward kernels, measured slower here -- this kernel waits
+          // on the tensor pipe, not on MUFU.)
           const float p0 = ex2(fmaf(__uint_as_float(sr[c][2 * i]), p.scale_log2, -m_eff));
           const float p1 = ex2(fmaf(__uint_as_float(sr[c][2 * i + 1]), p.scale_log2, -m_eff));
           suma[(i & 1) * 2] += p0;

@@ -334,6 +334,21 @@ __device__ __forceinline__ void umma_commit_pair(uint32_t bar_cluster_addr) {
       : "memory");
 }
 
+// 2^x for x <= ~0 on the FMA and integer pipes instead of the MUFU pipe (16 results per clock per
+// SM, the scarcest resource of a softmax): x = n + f with n = round(x) read from the low mantissa
+// bits of x + 1.5 * 2^23, f in [-0.5, 0.5], a degree-3 polynomial for 2^f (relative error 1.4e-4 in
+// f32, far below the bf16 rounding that follows) and n added to the exponent field.  Inputs below
+// -126 (including -inf) give 2^-126.
+__device__ __forceinline__ float exp2_poly(float x) {
+  x = fmaxf(x, -126.0f);
+  const float t = x + 12582912.0f;
+  const float f = x - (t - 12582912.0f);
+  float r = fmaf(f, 0.0551716685f, 0.2426111251f);
+  r = fmaf(r, f, 0.6932609677f);
+  r = fmaf(r, f, 0.9999280572f);
+  return __int_as_float(__float_as_int(r) + (__float_as_int(t) << 23));
+}
+
 // ---------------------------------------------------------------- descriptors
 // Shared-memory matrix descriptor, 128-byte swizzle (layout type 2), descriptor version 1.
 //   bits  0-13 start address >> 4      bits 16-29 leading byte offset >> 4
