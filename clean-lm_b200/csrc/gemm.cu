@@ -87,13 +87,16 @@ __device__ __forceinline__ void tile_coords(const Params& p, int tile, int& b, i
   n = first_n + (r - m * width);
 }
 
-// sigmoid(x) = rcp.approx(1 + ex2.approx(-x log2 e)), as in the reference's fused epilogues
-// (crates/cleandl/rust-kernels/src/sky_matmul/tcgen05_bf16.rs:851-854).
+// sigmoid(x) = 0.5 + 0.5 tanh(x / 2): one MUFU operation per element (tanh.approx, relative error
+// about 2^-11, below the bf16 rounding of the outputs).  The reference's fused epilogues use
+// rcp.approx(1 + ex2.approx(-x log2 e)) (crates/cleandl/rust-kernels/src/sky_matmul/
+// tcgen05_bf16.rs:851-854), two MUFU operations; at 16 per clock per SM the 65536 elements of a
+// 256 x 256 tile then cost half the time of the tile's main loop, and the epilogue warps, not the
+// tensor pipe, set the pace of the fused GEMMs.
 __device__ __forceinline__ float fast_sigmoid(float x) {
-  float e, r;
-  asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(e) : "f"(-x * 1.4426950408889634f));
-  asm("rcp.approx.ftz.f32 %0, %1;" : "=f"(r) : "f"(1.0f + e));
-  return r;
+  float t;
+  asm("tanh.approx.f32 %0, %1;" : "=f"(t) : "f"(0.5f * x));
+  return fmaf(0.5f, t, 0.5f);
 }
 
 // 32 consecutive columns of one output row, all operands 32-byte aligned: C read, fused
