@@ -98,6 +98,13 @@ SIGNATURES = {
     "cdl_b200_attn_bwd": ([ctypes.POINTER(CdlAttnDesc), _T, _T, _T, _T, _T, _T, _T, _T, _T, _vp,
                            _sz, _vp], ctypes.c_int32),
     "cdl_b200_attn_bwd_scratch_bytes": ([_T, _T, ctypes.POINTER(_sz)], ctypes.c_int32),
+    "cdl_b200_attn_fwd_packed": ([ctypes.POINTER(CdlAttnDesc), _T, _T, _T, _T, _T, ctypes.c_int64,
+                                  ctypes.c_int64, _T, _T, _vp], ctypes.c_int32),
+    "cdl_b200_attn_bwd_packed": ([ctypes.POINTER(CdlAttnDesc), _T, _T, _T, _T, _T, _T, _T, _T,
+                                  ctypes.c_int64, ctypes.c_int64, _T, _T, _T, _vp, _sz, _vp],
+                                 ctypes.c_int32),
+    "cdl_b200_attn_bwd_packed_scratch_bytes": ([ctypes.c_int64, ctypes.c_int64, ctypes.c_int64,
+                                                ctypes.POINTER(_sz)], ctypes.c_int32),
     "cdl_b200_rope": ([_T, _T, ctypes.c_int32, ctypes.c_int32, ctypes.c_int32, _vp], ctypes.c_int32),
     "cdl_b200_swiglu_fwd": ([_T, _T, _T, _vp], ctypes.c_int32),
     "cdl_b200_swiglu_bwd": ([_T, _T, _T, _T, _T, _vp], ctypes.c_int32),

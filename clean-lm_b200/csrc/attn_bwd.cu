@@ -39,6 +39,9 @@ int32_t attn_check_operand(const char* op, const char* name, const cdl_tensor* t
                            long long S, long long H, long long D);
 int32_t attn_encode_tmap(CUtensorMap* out, const cdl_tensor* t);
 int32_t attn_encode_tmap_rows(CUtensorMap* out, const cdl_tensor* t, uint32_t box_rows);
+int32_t attn_packed_view(const char* op, const char* name, const cdl_tensor* t, long long total,
+                         long long heads, cdl_tensor* view);
+int32_t attn_check_cu_seqlens(const char* op, const char* name, const cdl_tensor* t, long long batch);
 
 namespace attn_bwd {
 
@@ -70,6 +73,11 @@ struct Params {
   __nv_bfloat16* dk;
   __nv_bfloat16* dv;
   long long dq_sb, dq_ss, dq_sh, dk_sb, dk_ss, dk_sh, dv_sb, dv_ss, dv_sh;
+  // Packed layout: sequence b is rows cu_q[b] .. cu_q[b + 1] of q / o / dO / dQ and
+  // cu_k[b] .. cu_k[b + 1] of k / v / dK / dV; Sq / Sk are then the bounds the grids were sized
+  // with (Sq_pad pads that bound).  nullptr: dense layout.
+  const int* cu_q;
+  const int* cu_k;
   int* status;
 };
 
@@ -150,7 +158,8 @@ __global__ void __launch_bounds__(256)
                                long long do_sb, long long do_ss, long long do_sh,
                                const float* __restrict__ lse, long long lse_sb, long long lse_sh,
                                long long lse_ss, float* __restrict__ lse2,
-                               float* __restrict__ delta, int B, int H, int Sq, int Sq_pad) {
+                               float* __restrict__ delta, int B, int H, int Sq, int Sq_pad,
+                               const int* __restrict__ cu_q) {
   const long long item = (static_cast<long long>(blockIdx.x) * 256 + threadIdx.x) >> 4;
   const int sub = threadIdx.x & 15;
   const long long total = static_cast<long long>(B) * H * Sq_pad;
@@ -160,10 +169,19 @@ __global__ void __launch_bounds__(256)
   const int h = static_cast<int>((it / Sq_pad) % H);
   const int b = static_cast<int>(it / (static_cast<long long>(Sq_pad) * H));
   float dl = 0.f, l2 = INFINITY;
-  const bool in = live && row < Sq;
+  // packed layout: the rows of sequence b start at cu_q[b] of a single batch
+  long long grow = row, gb = b;
+  int len = Sq;
+  if (cu_q != nullptr) {
+    const int base = cu_q[b];
+    len = cu_q[b + 1] - base;
+    grow = static_cast<long long>(base) + row;
+    gb = 0;
+  }
+  const bool in = live && row < len;
   if (in) {
-    const uint4 vo = ld_nc_v4(o + b * o_sb + row * o_ss + h * o_sh + sub * 8);
-    const uint4 vd = ld_nc_v4(d_o + b * do_sb + row * do_ss + h * do_sh + sub * 8);
+    const uint4 vo = ld_nc_v4(o + gb * o_sb + grow * o_ss + h * o_sh + sub * 8);
+    const uint4 vd = ld_nc_v4(d_o + gb * do_sb + grow * do_ss + h * do_sh + sub * 8);
     dl = bf16_lo(vo.x) * bf16_lo(vd.x) + bf16_hi(vo.x) * bf16_hi(vd.x) +
          bf16_lo(vo.y) * bf16_lo(vd.y) + bf16_hi(vo.y) * bf16_hi(vd.y) +
          bf16_lo(vo.z) * bf16_lo(vd.z) + bf16_hi(vo.z) * bf16_hi(vd.z) +
@@ -172,7 +190,7 @@ __global__ void __launch_bounds__(256)
 #pragma unroll
   for (int s = 8; s > 0; s >>= 1) dl += __shfl_xor_sync(0xffffffffu, dl, s);
   if (in && sub == 0) {
-    const float l = lse[b * lse_sb + h * lse_sh + row * lse_ss];
+    const float l = lse[gb * lse_sb + h * lse_sh + grow * lse_ss];
     l2 = l == -INFINITY ? INFINITY : l * 1.4426950408889634f;
   }
   if (live && sub == 0) {
@@ -187,7 +205,20 @@ __global__ void __launch_bounds__(THREADS, 1)
     attn_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap tmap_q,
                          const __grid_constant__ CUtensorMap tmap_k,
                          const __grid_constant__ CUtensorMap tmap_v,
-                         const __grid_constant__ CUtensorMap tmap_do, const Params p) {
+                         const __grid_constant__ CUtensorMap tmap_do, const Params p_in) {
+  // Per-sequence view: in the packed layout a sequence has its own lengths and its rows start at
+  // q_base / k_base of a single batch (bt = 0).  Rows a tile loads beyond its sequence belong to
+  // the next one: keys beyond Sk are masked, queries beyond Sq carry lse2 = +inf (P = 0), and
+  // neither is stored.
+  Params p = p_in;
+  int q_base = 0, k_base = 0, bt = blockIdx.z;
+  if (p_in.cu_q != nullptr) {
+    q_base = p_in.cu_q[blockIdx.z];
+    p.Sq = p_in.cu_q[blockIdx.z + 1] - q_base;
+    k_base = p_in.cu_k[blockIdx.z];
+    p.Sk = p_in.cu_k[blockIdx.z + 1] - k_base;
+    bt = 0;
+  }
   // Shared memory is used to the last kilobytes, so there is no room for manual alignment slack:
   // the 1024-byte alignment the swizzled tiles need is requested from the compiler and verified.
   extern __shared__ __align__(1024) uint8_t smem[];
@@ -216,7 +247,7 @@ __global__ void __launch_bounds__(THREADS, 1)
   const int m_start = p.causal ? max(0, key0 - shift) / BQ : 0;
   const int m_count = max(0, num_q_blocks - m_start);
   // iteration it -> head kvh * group + it / m_count, query block m_start + it % m_count
-  const int iters = m_count * group;
+  const int iters = key0 < p.Sk ? m_count * group : 0;  // (a key block beyond a packed sequence)
 
   if (threadIdx.x == 0) {
     mbar_init(&bars->kv_full, 1);
@@ -256,8 +287,8 @@ __global__ void __launch_bounds__(THREADS, 1)
       mbar_arrive_expect_tx(&bars->kv_full, 2 * TILE_BYTES);
 #pragma unroll
       for (int dh = 0; dh < 2; ++dh) {
-        tma_load_4d(s_k + dh * PANEL_BYTES, &tmap_k, &bars->kv_full, dh * 64, key0, kvh, b);
-        tma_load_4d(s_v + dh * PANEL_BYTES, &tmap_v, &bars->kv_full, dh * 64, key0, kvh, b);
+        tma_load_4d(s_k + dh * PANEL_BYTES, &tmap_k, &bars->kv_full, dh * 64, k_base + key0, kvh, bt);
+        tma_load_4d(s_v + dh * PANEL_BYTES, &tmap_v, &bars->kv_full, dh * 64, k_base + key0, kvh, bt);
       }
       for (int it = 0; it < iters; ++it) {
         const int h = kvh * group + it / m_count;
@@ -269,13 +300,13 @@ __global__ void __launch_bounds__(THREADS, 1)
 #pragma unroll
         for (int dh = 0; dh < 2; ++dh)
           tma_load_4d(s_q + s * TILE_BYTES + dh * PANEL_BYTES, &tmap_q, &bars->q_full[s], dh * 64,
-                      q0, h, b);
+                      q_base + q0, h, bt);
         if (!mbar_wait(&bars->do_empty[s], ph, abort_word, 122)) break;
         mbar_arrive_expect_tx(&bars->do_full[s], TILE_BYTES);
 #pragma unroll
         for (int dh = 0; dh < 2; ++dh)
           tma_load_4d(s_do + s * TILE_BYTES + dh * PANEL_BYTES, &tmap_do, &bars->do_full[s],
-                      dh * 64, q0, h, b);
+                      dh * 64, q_base + q0, h, bt);
       }
     }
   } else if (warp == 1) {
@@ -489,8 +520,8 @@ __global__ void __launch_bounds__(THREADS, 1)
     }
     if (ok) {
       const bool row_ok = key < p.Sk;
-      __nv_bfloat16* dv_row = p.dv + b * p.dv_sb + static_cast<long long>(key) * p.dv_ss + kvh * p.dv_sh + wg * 64;
-      __nv_bfloat16* dk_row = p.dk + b * p.dk_sb + static_cast<long long>(key) * p.dk_ss + kvh * p.dk_sh + wg * 64;
+      __nv_bfloat16* dv_row = p.dv + bt * p.dv_sb + static_cast<long long>(k_base + key) * p.dv_ss + kvh * p.dv_sh + wg * 64;
+      __nv_bfloat16* dk_row = p.dk + bt * p.dk_sb + static_cast<long long>(k_base + key) * p.dk_ss + kvh * p.dk_sh + wg * 64;
 #pragma unroll
       for (int which = 0; which < 2; ++which) {
         __nv_bfloat16* dst = which == 0 ? dv_row : dk_row;
@@ -550,8 +581,17 @@ __global__ void __launch_bounds__(THREADS, 1)
     attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmap_q,
                        const __grid_constant__ CUtensorMap tmap_k,
                        const __grid_constant__ CUtensorMap tmap_v,
-                       const __grid_constant__ CUtensorMap tmap_do, const Params p) {
+                       const __grid_constant__ CUtensorMap tmap_do, const Params p_in) {
   extern __shared__ __align__(1024) uint8_t smem[];
+  Params p = p_in;  // per-sequence view, as in the dK/dV kernel
+  int q_base = 0, k_base = 0, bt = blockIdx.z;
+  if (p_in.cu_q != nullptr) {
+    q_base = p_in.cu_q[blockIdx.z];
+    p.Sq = p_in.cu_q[blockIdx.z + 1] - q_base;
+    k_base = p_in.cu_k[blockIdx.z];
+    p.Sk = p_in.cu_k[blockIdx.z + 1] - k_base;
+    bt = 0;
+  }
   if ((smem_u32(smem) & 1023u) != 0) {
     if (threadIdx.x == 0) atomicExch(p.status, 902);
     return;
@@ -611,8 +651,8 @@ __global__ void __launch_bounds__(THREADS, 1)
       mbar_arrive_expect_tx(&bars->qdo_full, 2 * TILE_BYTES);
 #pragma unroll
       for (int dh = 0; dh < 2; ++dh) {
-        tma_load_4d(s_q + dh * PANEL_BYTES, &tmap_q, &bars->qdo_full, dh * 64, q0, h, b);
-        tma_load_4d(s_do + dh * PANEL_BYTES, &tmap_do, &bars->qdo_full, dh * 64, q0, h, b);
+        tma_load_4d(s_q + dh * PANEL_BYTES, &tmap_q, &bars->qdo_full, dh * 64, q_base + q0, h, bt);
+        tma_load_4d(s_do + dh * PANEL_BYTES, &tmap_do, &bars->qdo_full, dh * 64, q_base + q0, h, bt);
       }
       for (int j = 0; j < n_kv; ++j) {
         const int sk = j % QK_STAGES;
@@ -621,7 +661,7 @@ __global__ void __launch_bounds__(THREADS, 1)
 #pragma unroll
         for (int dh = 0; dh < 2; ++dh)
           tma_load_4d(s_k + sk * TILE_BYTES + dh * PANEL_BYTES, &tmap_k, &bars->k_full[sk], dh * 64,
-                      j * BKV, kvh, b);
+                      k_base + j * BKV, kvh, bt);
         const int s = j & 1;
         const uint32_t ph = ((j >> 1) & 1) ^ 1;
         if (!mbar_wait(&bars->v_empty[s], ph, abort_word, 132)) break;
@@ -629,7 +669,7 @@ __global__ void __launch_bounds__(THREADS, 1)
 #pragma unroll
         for (int dh = 0; dh < 2; ++dh)
           tma_load_4d(s_v + s * TILE_BYTES + dh * PANEL_BYTES, &tmap_v, &bars->v_full[s], dh * 64,
-                      j * BKV, kvh, b);
+                      k_base + j * BKV, kvh, bt);
       }
     }
   } else if (warp == 1) {
@@ -771,7 +811,7 @@ __global__ void __launch_bounds__(THREADS, 1)
       tc_fence_after();
     }
     if (ok && q0 < p.Sq) {
-      __nv_bfloat16* dst = p.dq + b * p.dq_sb + static_cast<long long>(row) * p.dq_ss + h * p.dq_sh + wg * 64;
+      __nv_bfloat16* dst = p.dq + bt * p.dq_sb + static_cast<long long>(q_base + row) * p.dq_ss + h * p.dq_sh + wg * 64;
 #pragma unroll
       for (int half = 0; half < 2; ++half) {
         uint32_t a[32];
@@ -819,6 +859,70 @@ static long long pad128(long long v) { return (v + 127) / 128 * 128; }
 
 size_t attn_bwd_scratch_bytes(long long B, long long Sq, long long H) {
   return 2 * static_cast<size_t>(B) * H * attn_bwd::pad128(Sq) * sizeof(float);
+}
+
+// Launches preprocess, dK/dV and dQ for a filled-in Params (p.Sq / p.Sk: the lengths the grids
+// are sized with; q .. d_o: [B, S, H, D] views; lse strides as (batch, head, row)).
+static int32_t bwd_run(const attn_bwd::Params& p, const cdl_tensor* q, const cdl_tensor* k,
+                       const cdl_tensor* v, const cdl_tensor* o, const cdl_tensor* d_o,
+                       const float* lse, long long lse_sb, long long lse_sh, long long lse_ss,
+                       double work, cudaStream_t stream) {
+  using namespace attn_bwd;
+  static std::once_flag attr_once[64];
+  int dev = 0;
+  CDL_CUDA(cudaGetDevice(&dev));
+  cudaError_t attr_err = cudaSuccess;
+  std::call_once(attr_once[dev & 63], [&] {
+    attr_err = cudaFuncSetAttribute(attn_bwd_dkdv_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                    static_cast<int>(KV_SMEM_BYTES));
+    if (attr_err == cudaSuccess)
+      attr_err = cudaFuncSetAttribute(attn_bwd_dq_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                      static_cast<int>(Q_SMEM_BYTES));
+  });
+  if (attr_err != cudaSuccess)
+    return fail(CDL_ERR_CUDA, "cudaFuncSetAttribute failed: %s", cudaGetErrorString(attr_err));
+
+  const long long B = p.B, H = p.H, Hkv = p.Hkv, Sq = p.Sq, Sk = p.Sk;
+  const bool have_q = q->shape[1] > 0 && Sq > 0, have_k = k->shape[1] > 0 && Sk > 0;
+  ProfileScope ps(PROF_ATTN_BWD, work, stream);
+  if (have_q) {
+    const long long items = B * H * p.Sq_pad;
+    const unsigned blocks = static_cast<unsigned>((items * 16 + 255) / 256);
+    attn_bwd_preprocess_kernel<<<blocks, 256, 0, stream>>>(
+        static_cast<const __nv_bfloat16*>(o->ptr), o->stride[0], o->stride[1], o->stride[2],
+        static_cast<const __nv_bfloat16*>(d_o->ptr), d_o->stride[0], d_o->stride[1], d_o->stride[2],
+        lse, lse_sb, lse_sh, lse_ss, const_cast<float*>(p.lse2), const_cast<float*>(p.delta), p.B,
+        p.H, p.Sq, p.Sq_pad, p.cu_q);
+    CDL_CUDA(cudaGetLastError());
+  }
+  CUtensorMap tq, tk, tv, tdo;
+  if (have_q) {
+    CDL_CHECK(attn_encode_tmap(&tq, q));
+    CDL_CHECK(attn_encode_tmap(&tdo, d_o));
+  } else {
+    memset(&tq, 0, sizeof tq);
+    tdo = tq;
+  }
+  if (have_k) {
+    CDL_CHECK(attn_encode_tmap(&tk, k));
+    CDL_CHECK(attn_encode_tmap(&tv, v));
+  } else {
+    memset(&tk, 0, sizeof tk);
+    tv = tk;
+  }
+  if (have_k) {
+    dim3 grid(static_cast<unsigned>((Sk + BKV - 1) / BKV), static_cast<unsigned>(Hkv),
+              static_cast<unsigned>(B));
+    attn_bwd_dkdv_kernel<<<grid, THREADS, KV_SMEM_BYTES, stream>>>(tq, tk, tv, tdo, p);
+    CDL_CUDA(cudaGetLastError());
+  }
+  if (have_q) {
+    dim3 grid(static_cast<unsigned>((Sq + BQ - 1) / BQ), static_cast<unsigned>(H),
+              static_cast<unsigned>(B));
+    attn_bwd_dq_kernel<<<grid, THREADS, Q_SMEM_BYTES, stream>>>(tq, tk, tv, tdo, p);
+    CDL_CUDA(cudaGetLastError());
+  }
+  return CDL_OK;
 }
 
 int32_t attn_bwd_execute(const cdl_attn_desc* desc, const cdl_tensor* q, const cdl_tensor* k,
@@ -884,67 +988,114 @@ int32_t attn_bwd_execute(const cdl_attn_desc* desc, const cdl_tensor* q, const c
   p.status = device_status_ptr();
   if (!p.status) return fail(CDL_ERR_CUDA, "cannot resolve the device status word");
 
-  static std::once_flag attr_once[64];
-  int dev = 0;
-  CDL_CUDA(cudaGetDevice(&dev));
-  cudaError_t attr_err = cudaSuccess;
-  std::call_once(attr_once[dev & 63], [&] {
-    attr_err = cudaFuncSetAttribute(attn_bwd_dkdv_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                    static_cast<int>(KV_SMEM_BYTES));
-    if (attr_err == cudaSuccess)
-      attr_err = cudaFuncSetAttribute(attn_bwd_dq_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                      static_cast<int>(Q_SMEM_BYTES));
-  });
-  if (attr_err != cudaSuccess)
-    return fail(CDL_ERR_CUDA, "cudaFuncSetAttribute failed: %s", cudaGetErrorString(attr_err));
-
+  p.cu_q = nullptr;
+  p.cu_k = nullptr;
   // 14 B H Sq Sk D with the recomputed S and dP of the dQ kernel; reported as the conventional
   // 10 B H Sq Sk D (2.5 x forward), halved for the causal mask.
-  ProfileScope ps(PROF_ATTN_BWD, 10.0 * B * H * Sq * Sk * D * (p.causal ? 0.5 : 1.0), stream);
-  if (Sq > 0) {
-    const long long items = B * H * Sq_pad;
-    const unsigned blocks = static_cast<unsigned>((items * 16 + 255) / 256);
-    attn_bwd_preprocess_kernel<<<blocks, 256, 0, stream>>>(
-        static_cast<const __nv_bfloat16*>(o->ptr), o->stride[0], o->stride[1], o->stride[2],
-        static_cast<const __nv_bfloat16*>(d_o->ptr), d_o->stride[0], d_o->stride[1], d_o->stride[2],
-        static_cast<const float*>(lse->ptr), lse->stride[0], lse->stride[1], lse->stride[2], lse2,
-        delta, p.B, p.H, p.Sq, p.Sq_pad);
-    CDL_CUDA(cudaGetLastError());
-  }
+  return bwd_run(p, q, k, v, o, d_o, static_cast<const float*>(lse->ptr), lse->stride[0],
+                 lse->stride[1], lse->stride[2], 10.0 * B * H * Sq * Sk * D * (p.causal ? 0.5 : 1.0),
+                 stream);
+}
 
-  CUtensorMap tq, tk, tv, tdo;
-  if (Sq > 0) {
-    CDL_CHECK(attn_encode_tmap(&tq, q));
-    CDL_CHECK(attn_encode_tmap(&tdo, d_o));
-  } else {
-    memset(&tq, 0, sizeof tq);
-    tdo = tq;
-  }
-  if (Sk > 0) {
-    CDL_CHECK(attn_encode_tmap(&tk, k));
-    CDL_CHECK(attn_encode_tmap(&tv, v));
-  } else {
-    memset(&tk, 0, sizeof tk);
-    tv = tk;
-  }
-  if (Sk > 0) {
-    dim3 grid(static_cast<unsigned>((Sk + BKV - 1) / BKV), static_cast<unsigned>(Hkv),
-              static_cast<unsigned>(B));
-    attn_bwd_dkdv_kernel<<<grid, THREADS, KV_SMEM_BYTES, stream>>>(tq, tk, tv, tdo, p);
-    CDL_CUDA(cudaGetLastError());
-  }
-  if (Sq > 0) {
-    dim3 grid(static_cast<unsigned>((Sq + BQ - 1) / BQ), static_cast<unsigned>(H),
-              static_cast<unsigned>(B));
-    attn_bwd_dq_kernel<<<grid, THREADS, Q_SMEM_BYTES, stream>>>(tq, tk, tv, tdo, p);
-    CDL_CUDA(cudaGetLastError());
-  }
-  return CDL_OK;
+size_t attn_bwd_packed_scratch_bytes(long long batch, long long max_seqlen_q, long long H) {
+  return attn_bwd_scratch_bytes(batch, max_seqlen_q, H);
+}
+
+int32_t attn_bwd_packed_execute(const cdl_attn_desc* desc, const cdl_tensor* q, const cdl_tensor* k,
+                                const cdl_tensor* v, const cdl_tensor* o, const cdl_tensor* d_o,
+                                const cdl_tensor* lse, const cdl_tensor* cu_q, const cdl_tensor* cu_k,
+                                long long max_q, long long max_k, const cdl_tensor* dq,
+                                const cdl_tensor* dk, const cdl_tensor* dv, void* scratch,
+                                size_t scratch_bytes, cudaStream_t stream) {
+  using namespace attn_bwd;
+  const char* op = "attention_bwd (packed)";
+  if (!desc || !q || !k || !v || !o || !d_o || !lse || !dq || !dk || !dv || !cu_q || !cu_k)
+    return fail(CDL_ERR_INVALID, "%s: every operand is required", op);
+  if (q->rank != 3 || k->rank != 3)
+    return fail(CDL_ERR_INVALID, "%s: q and k must be [total, heads, head_dim]", op);
+  const long long Tq = q->shape[0], H = q->shape[1], Dh = q->shape[2];
+  const long long Tk = k->shape[0], Hkv = k->shape[1];
+  const long long B = cu_q->rank == 1 ? cu_q->shape[0] - 1 : -1;
+  if (Dh != D)
+    return fail(CDL_ERR_UNSUPPORTED, "%s: head dimension %lld is not implemented (only 128)", op, Dh);
+  if (Hkv <= 0 || H % Hkv != 0)
+    return fail(CDL_ERR_INVALID, "%s: query heads (%lld) must be a multiple of kv heads (%lld)", op,
+                H, Hkv);
+  if (B < 0) return fail(CDL_ERR_INVALID, "%s: cu_seqlens_q must hold batch + 1 entries", op);
+  CDL_CHECK(attn_check_cu_seqlens(op, "cu_seqlens_q", cu_q, B));
+  CDL_CHECK(attn_check_cu_seqlens(op, "cu_seqlens_k", cu_k, B));
+  cdl_tensor q4, k4, v4, o4, do4, dq4, dk4, dv4;
+  CDL_CHECK(attn_packed_view(op, "q", q, Tq, H, &q4));
+  CDL_CHECK(attn_packed_view(op, "k", k, Tk, Hkv, &k4));
+  CDL_CHECK(attn_packed_view(op, "v", v, Tk, Hkv, &v4));
+  CDL_CHECK(attn_packed_view(op, "out", o, Tq, H, &o4));
+  CDL_CHECK(attn_packed_view(op, "d_out", d_o, Tq, H, &do4));
+  CDL_CHECK(attn_packed_view(op, "dq", dq, Tq, H, &dq4));
+  CDL_CHECK(attn_packed_view(op, "dk", dk, Tk, Hkv, &dk4));
+  CDL_CHECK(attn_packed_view(op, "dv", dv, Tk, Hkv, &dv4));
+  if (lse->rank != 2 || lse->shape[0] != H || lse->shape[1] != Tq || lse->dtype != CDL_F32)
+    return fail(CDL_ERR_INVALID, "%s: lse must be f32 [heads, total_q]", op);
+  if (max_q <= 0 || max_q > Tq) max_q = Tq;
+  if (max_k <= 0 || max_k > Tk) max_k = Tk;
+  if (B == 0 || H == 0 || (Tq == 0 && Tk == 0)) return CDL_OK;
+  if (B > 65535 || H > 65535 || Tq > (1 << 30) || Tk > (1 << 30))
+    return fail(CDL_ERR_UNSUPPORTED, "%s: dimension too large", op);
+  const size_t need = attn_bwd_packed_scratch_bytes(B, max_q, H);
+  if (need > 0 && (scratch == nullptr || scratch_bytes < need ||
+                   (reinterpret_cast<uintptr_t>(scratch) & 15) != 0))
+    return fail(CDL_ERR_INVALID, "%s: scratch must be 16-byte aligned and hold %zu bytes (got %zu)",
+                op, need, scratch_bytes);
+  const long long Sq_pad = pad128(max_q);
+  Params p;
+  p.B = static_cast<int>(B);
+  p.H = static_cast<int>(H);
+  p.Hkv = static_cast<int>(Hkv);
+  p.Sq = static_cast<int>(max_q);
+  p.Sk = static_cast<int>(max_k);
+  p.Sq_pad = static_cast<int>(Sq_pad);
+  p.causal = desc->causal != 0;
+  p.scale = desc->softmax_scale > 0.f ? desc->softmax_scale : 1.0f / sqrtf(static_cast<float>(D));
+  p.scale_log2 = p.scale * 1.4426950408889634f;
+  p.lse2 = static_cast<float*>(scratch);
+  p.delta = p.lse2 + B * H * Sq_pad;
+  p.dq = static_cast<__nv_bfloat16*>(dq->ptr);
+  p.dk = static_cast<__nv_bfloat16*>(dk->ptr);
+  p.dv = static_cast<__nv_bfloat16*>(dv->ptr);
+  p.dq_sb = 0; p.dq_ss = dq->stride[0]; p.dq_sh = dq->stride[1];
+  p.dk_sb = 0; p.dk_ss = dk->stride[0]; p.dk_sh = dk->stride[1];
+  p.dv_sb = 0; p.dv_ss = dv->stride[0]; p.dv_sh = dv->stride[1];
+  p.cu_q = static_cast<const int*>(cu_q->ptr);
+  p.cu_k = static_cast<const int*>(cu_k->ptr);
+  p.status = device_status_ptr();
+  if (!p.status) return fail(CDL_ERR_CUDA, "cannot resolve the device status word");
+  const double mean_q = static_cast<double>(Tq) / B, mean_k = static_cast<double>(Tk) / B;
+  return bwd_run(p, &q4, &k4, &v4, &o4, &do4, static_cast<const float*>(lse->ptr), 0, lse->stride[0],
+                 lse->stride[1], 10.0 * B * H * mean_q * mean_k * D * (p.causal ? 0.5 : 1.0), stream);
 }
 
 }  // namespace cdl
 
 extern "C" {
+
+int32_t cdl_b200_attn_bwd_packed(const cdl_attn_desc* desc, const cdl_tensor* q, const cdl_tensor* k,
+                                 const cdl_tensor* v, const cdl_tensor* o, const cdl_tensor* d_out,
+                                 const cdl_tensor* lse, const cdl_tensor* cu_seqlens_q,
+                                 const cdl_tensor* cu_seqlens_k, int64_t max_seqlen_q,
+                                 int64_t max_seqlen_k, const cdl_tensor* dq, const cdl_tensor* dk,
+                                 const cdl_tensor* dv, void* scratch, size_t scratch_bytes,
+                                 cdl_stream stream) {
+  return cdl::attn_bwd_packed_execute(desc, q, k, v, o, d_out, lse, cu_seqlens_q, cu_seqlens_k,
+                                      max_seqlen_q, max_seqlen_k, dq, dk, dv, scratch, scratch_bytes,
+                                      static_cast<cudaStream_t>(stream));
+}
+
+int32_t cdl_b200_attn_bwd_packed_scratch_bytes(int64_t batch, int64_t max_seqlen_q, int64_t heads,
+                                               size_t* bytes_out) {
+  if (batch < 0 || max_seqlen_q < 0 || heads < 0)
+    return cdl::fail(CDL_ERR_INVALID, "attention_bwd (packed): negative dimension");
+  if (bytes_out) *bytes_out = cdl::attn_bwd_packed_scratch_bytes(batch, max_seqlen_q, heads);
+  return CDL_OK;
+}
 
 int32_t cdl_b200_attn_bwd(const cdl_attn_desc* desc, const cdl_tensor* q, const cdl_tensor* k,
                           const cdl_tensor* v, const cdl_tensor* o, const cdl_tensor* d_out,

@@ -46,6 +46,11 @@ struct Params {
   long long o_sb, o_ss, o_sh;  // element strides of O [B, Sq, H, D]
   float* lse;                  // [B, H, Sq] or nullptr
   long long lse_sb, lse_sh, lse_ss;
+  // Packed layout (q [total_q, H, D], k / v [total_k, Hkv, D]): sequence b is rows
+  // cu_q[b] .. cu_q[b + 1] of q and cu_k[b] .. cu_k[b + 1] of k and v; Sq / Sk above are then the
+  // bounds the grid was sized with.  nullptr: dense layout.
+  const int* cu_q;
+  const int* cu_k;
   int* status;
 };
 
@@ -77,7 +82,7 @@ __device__ __forceinline__ int kv_blocks_for_tile(const Params& p, int r0) {
 __global__ void __launch_bounds__(THREADS, 1)
     attn_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q,
                     const __grid_constant__ CUtensorMap tmap_k,
-                    const __grid_constant__ CUtensorMap tmap_v, const Params p) {
+                    const __grid_constant__ CUtensorMap tmap_v, const Params p_in) {
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) &
                                              ~static_cast<uintptr_t>(1023));
@@ -93,6 +98,19 @@ __global__ void __launch_bounds__(THREADS, 1)
   const int q_block = gridDim.x - 1 - blockIdx.x;
   const int h = blockIdx.y;
   const int b = blockIdx.z;
+  // Per-sequence view of the problem: in the packed layout every sequence has its own lengths
+  // and its rows start at q_base / k_base of a single "batch" (bt = 0).  Rows a tile loads beyond
+  // its sequence belong to the next one (or are zero beyond the tensor): their scores are masked
+  // like keys beyond Sk, their outputs are not stored.
+  Params p = p_in;
+  int q_base = 0, k_base = 0, bt = b;
+  if (p_in.cu_q != nullptr) {
+    q_base = p_in.cu_q[b];
+    p.Sq = p_in.cu_q[b + 1] - q_base;
+    k_base = p_in.cu_k[b];
+    p.Sk = p_in.cu_k[b + 1] - k_base;
+    bt = 0;
+  }
   const int kvh = h / (p.H / p.Hkv);
   const int m0 = q_block * 2 * BQ;
   const int n0 = kv_blocks_for_tile(p, m0);
@@ -139,7 +157,7 @@ __global__ void __launch_bounds__(THREADS, 1)
 #pragma unroll
         for (int dh = 0; dh < 2; ++dh)
           tma_load_4d(s_q + t * TILE_BYTES + dh * PANEL_BYTES, &tmap_q, &bars->q_full, dh * 64,
-                      m0 + t * BQ, h, b);
+                      q_base + m0 + t * BQ, h, bt);
       for (int j = 0; j < n_max; ++j) {
         const int s = j & 1;
         const uint32_t ph = (j >> 1) & 1;
@@ -148,13 +166,13 @@ __global__ void __launch_bounds__(THREADS, 1)
 #pragma unroll
         for (int dh = 0; dh < 2; ++dh)
           tma_load_4d(s_k + s * TILE_BYTES + dh * PANEL_BYTES, &tmap_k, &bars->k_full[s], dh * 64,
-                      j * BKV, kvh, b);
+                      k_base + j * BKV, kvh, bt);
         if (!mbar_wait(&bars->v_empty[s], ph ^ 1, abort_word, 112)) break;
         mbar_arrive_expect_tx(&bars->v_full[s], TILE_BYTES);
 #pragma unroll
         for (int dh = 0; dh < 2; ++dh)
           tma_load_4d(s_v + s * TILE_BYTES + dh * PANEL_BYTES, &tmap_v, &bars->v_full[s], dh * 64,
-                      j * BKV, kvh, b);
+                      k_base + j * BKV, kvh, bt);
       }
     }
   } else if (warp == 1) {
@@ -335,7 +353,7 @@ __global__ void __launch_bounds__(THREADS, 1)
     }
     if (ok && m0 + t * BQ < p.Sq) {
       const float inv_l = l > 0.f ? 1.f / l : 0.f;
-      __nv_bfloat16* orow_ptr = p.o + b * p.o_sb + static_cast<long long>(row) * p.o_ss + h * p.o_sh;
+      __nv_bfloat16* orow_ptr = p.o + bt * p.o_sb + static_cast<long long>(q_base + row) * p.o_ss + h * p.o_sh;
 #pragma unroll
       for (int c = 0; c < 4; ++c) {
         uint32_t orow[32];
@@ -360,7 +378,7 @@ __global__ void __launch_bounds__(THREADS, 1)
       }
       if (row_ok && p.lse != nullptr) {
         const float lse = l > 0.f ? (m_used + log2f(l)) * 0.6931471805599453f : -INFINITY;
-        p.lse[b * p.lse_sb + h * p.lse_sh + static_cast<long long>(row) * p.lse_ss] = lse;
+        p.lse[bt * p.lse_sb + h * p.lse_sh + static_cast<long long>(q_base + row) * p.lse_ss] = lse;
       }
     }
   }
@@ -420,6 +438,21 @@ int32_t attn_encode_tmap_rows(CUtensorMap* out, const cdl_tensor* t, uint32_t bo
   return encode_tmap(out, t->ptr, CDL_BF16, 4, dims, strides, box, true);
 }
 
+static int32_t fwd_set_attributes() {
+  static std::once_flag attr_once[64];
+  int dev = 0;
+  CDL_CUDA(cudaGetDevice(&dev));
+  cudaError_t attr_err = cudaSuccess;
+  std::call_once(attr_once[dev & 63], [&] {
+    attr_err = cudaFuncSetAttribute(attn_fwd::attn_fwd_kernel,
+                                    cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                    static_cast<int>(attn_fwd::SMEM_BYTES));
+  });
+  if (attr_err != cudaSuccess)
+    return fail(CDL_ERR_CUDA, "cudaFuncSetAttribute failed: %s", cudaGetErrorString(attr_err));
+  return CDL_OK;
+}
+
 int32_t attn_fwd_execute(const cdl_attn_desc* desc, const cdl_tensor* q, const cdl_tensor* k,
                          const cdl_tensor* v, const cdl_tensor* o, const cdl_tensor* lse,
                          cudaStream_t stream) {
@@ -466,6 +499,8 @@ int32_t attn_fwd_execute(const cdl_attn_desc* desc, const cdl_tensor* q, const c
   p.lse_sb = lse ? lse->stride[0] : 0;
   p.lse_sh = lse ? lse->stride[1] : 0;
   p.lse_ss = lse ? lse->stride[2] : 0;
+  p.cu_q = nullptr;
+  p.cu_k = nullptr;
   p.status = device_status_ptr();
   if (!p.status) return fail(CDL_ERR_CUDA, "cannot resolve the device status word");
 
@@ -481,17 +516,7 @@ int32_t attn_fwd_execute(const cdl_attn_desc* desc, const cdl_tensor* q, const c
     tv = tq;
   }
 
-  static std::once_flag attr_once[64];
-  int dev = 0;
-  CDL_CUDA(cudaGetDevice(&dev));
-  cudaError_t attr_err = cudaSuccess;
-  std::call_once(attr_once[dev & 63], [&] {
-    attr_err = cudaFuncSetAttribute(attn_fwd_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                    static_cast<int>(SMEM_BYTES));
-  });
-  if (attr_err != cudaSuccess)
-    return fail(CDL_ERR_CUDA, "cudaFuncSetAttribute failed: %s", cudaGetErrorString(attr_err));
-
+  CDL_CHECK(fwd_set_attributes());
   dim3 grid(static_cast<unsigned>((Sq + 2 * BQ - 1) / (2 * BQ)), static_cast<unsigned>(H),
             static_cast<unsigned>(B));
   // FLOP by the flash-attention convention: 4 B H Sq Sk D, halved for the causal mask.
@@ -501,9 +526,129 @@ int32_t attn_fwd_execute(const cdl_attn_desc* desc, const cdl_tensor* q, const c
   return CDL_OK;
 }
 
+
+// Checks a packed [total, heads, 128] bf16 operand and returns its [1, total, heads, 128] view.
+int32_t attn_packed_view(const char* op, const char* name, const cdl_tensor* t, long long total,
+                         long long heads, cdl_tensor* view) {
+  if (!t) return fail(CDL_ERR_INVALID, "%s: %s is required", op, name);
+  if (t->rank != 3 || t->shape[0] != total || t->shape[1] != heads || t->shape[2] != attn_fwd::D)
+    return fail(CDL_ERR_INVALID, "%s: %s must have shape [%lld, %lld, %d]", op, name, total, heads,
+                attn_fwd::D);
+  view->ptr = t->ptr;
+  view->dtype = t->dtype;
+  view->rank = 4;
+  view->shape[0] = 1;
+  view->shape[1] = total;
+  view->shape[2] = heads;
+  view->shape[3] = attn_fwd::D;
+  view->stride[0] = 0;
+  view->stride[1] = t->stride[0];
+  view->stride[2] = t->stride[1];
+  view->stride[3] = t->stride[2];
+  return attn_check_operand(op, name, view, 1, total, heads, attn_fwd::D);
+}
+
+// Checks an i32 [batch + 1] device vector of cumulative sequence lengths.
+int32_t attn_check_cu_seqlens(const char* op, const char* name, const cdl_tensor* t, long long batch) {
+  if (!t || t->rank != 1 || t->dtype != CDL_I32 || t->shape[0] != batch + 1 || t->stride[0] != 1 ||
+      (reinterpret_cast<uintptr_t>(t->ptr) & 3) != 0)
+    return fail(CDL_ERR_INVALID, "%s: %s must be a contiguous i32 vector of batch + 1 = %lld entries",
+                op, name, batch + 1);
+  return CDL_OK;
+}
+
+int32_t attn_fwd_packed_execute(const cdl_attn_desc* desc, const cdl_tensor* q, const cdl_tensor* k,
+                                const cdl_tensor* v, const cdl_tensor* cu_q, const cdl_tensor* cu_k,
+                                long long max_q, long long max_k, const cdl_tensor* o,
+                                const cdl_tensor* lse, cudaStream_t stream) {
+  using namespace attn_fwd;
+  const char* op = "attention_fwd (packed)";
+  if (!desc || !q || !k || !v || !o || !cu_q || !cu_k)
+    return fail(CDL_ERR_INVALID, "%s: desc, q, k, v, cu_seqlens_q, cu_seqlens_k, o are required", op);
+  if (q->rank != 3 || k->rank != 3)
+    return fail(CDL_ERR_INVALID, "%s: q and k must be [total, heads, head_dim]", op);
+  const long long Tq = q->shape[0], H = q->shape[1], Dh = q->shape[2];
+  const long long Tk = k->shape[0], Hkv = k->shape[1];
+  const long long B = cu_q->rank == 1 ? cu_q->shape[0] - 1 : -1;
+  if (Dh != D)
+    return fail(CDL_ERR_UNSUPPORTED, "%s: head dimension %lld is not implemented (only 128)", op, Dh);
+  if (Hkv <= 0 || H % Hkv != 0)
+    return fail(CDL_ERR_INVALID, "%s: query heads (%lld) must be a multiple of kv heads (%lld)", op,
+                H, Hkv);
+  if (B < 0) return fail(CDL_ERR_INVALID, "%s: cu_seqlens_q must hold batch + 1 entries", op);
+  CDL_CHECK(attn_check_cu_seqlens(op, "cu_seqlens_q", cu_q, B));
+  CDL_CHECK(attn_check_cu_seqlens(op, "cu_seqlens_k", cu_k, B));
+  cdl_tensor q4, k4, v4, o4;
+  CDL_CHECK(attn_packed_view(op, "q", q, Tq, H, &q4));
+  CDL_CHECK(attn_packed_view(op, "k", k, Tk, Hkv, &k4));
+  CDL_CHECK(attn_packed_view(op, "v", v, Tk, Hkv, &v4));
+  CDL_CHECK(attn_packed_view(op, "out", o, Tq, H, &o4));
+  if (lse) {
+    if (lse->rank != 2 || lse->shape[0] != H || lse->shape[1] != Tq || lse->dtype != CDL_F32)
+      return fail(CDL_ERR_INVALID, "%s: lse must be f32 [heads, total_q]", op);
+  }
+  if (max_q <= 0 || max_q > Tq) max_q = Tq;  // the bound only sizes the grid
+  if (max_k <= 0 || max_k > Tk) max_k = Tk;
+  if (B == 0 || Tq == 0 || H == 0) return CDL_OK;
+  if (B > 65535 || H > 65535 || Tq > (1 << 30) || Tk > (1 << 30))
+    return fail(CDL_ERR_UNSUPPORTED, "%s: dimension too large", op);
+
+  Params p;
+  p.B = static_cast<int>(B);
+  p.H = static_cast<int>(H);
+  p.Hkv = static_cast<int>(Hkv);
+  p.Sq = static_cast<int>(max_q);
+  p.Sk = static_cast<int>(max_k);
+  p.causal = desc->causal != 0;
+  const float scale = desc->softmax_scale > 0.f ? desc->softmax_scale : 1.0f / sqrtf(static_cast<float>(D));
+  p.scale_log2 = scale * 1.4426950408889634f;
+  p.o = static_cast<__nv_bfloat16*>(o->ptr);
+  p.o_sb = 0;
+  p.o_ss = o->stride[0];
+  p.o_sh = o->stride[1];
+  p.lse = lse ? static_cast<float*>(lse->ptr) : nullptr;
+  p.lse_sb = 0;
+  p.lse_sh = lse ? lse->stride[0] : 0;
+  p.lse_ss = lse ? lse->stride[1] : 0;
+  p.cu_q = static_cast<const int*>(cu_q->ptr);
+  p.cu_k = static_cast<const int*>(cu_k->ptr);
+  p.status = device_status_ptr();
+  if (!p.status) return fail(CDL_ERR_CUDA, "cannot resolve the device status word");
+
+  CUtensorMap tq, tk, tv;
+  if (Tk > 0) {
+    CDL_CHECK(attn_encode_tmap(&tq, &q4));
+    CDL_CHECK(attn_encode_tmap(&tk, &k4));
+    CDL_CHECK(attn_encode_tmap(&tv, &v4));
+  } else {
+    memset(&tq, 0, sizeof tq);
+    tk = tq;
+    tv = tq;
+  }
+  CDL_CHECK(fwd_set_attributes());
+  dim3 grid(static_cast<unsigned>((max_q + 2 * BQ - 1) / (2 * BQ)), static_cast<unsigned>(H),
+            static_cast<unsigned>(B));
+  // The sequence lengths live on the device: the work figure uses the packed totals as if every
+  // sequence had the mean length.
+  const double mean_q = static_cast<double>(Tq) / B, mean_k = static_cast<double>(Tk) / B;
+  ProfileScope ps(PROF_ATTN_FWD, 4.0 * B * H * mean_q * mean_k * D * (p.causal ? 0.5 : 1.0), stream);
+  attn_fwd_kernel<<<grid, THREADS, SMEM_BYTES, stream>>>(tq, tk, tv, p);
+  CDL_CUDA(cudaGetLastError());
+  return CDL_OK;
+}
+
 }  // namespace cdl
 
 extern "C" {
+
+int32_t cdl_b200_attn_fwd_packed(const cdl_attn_desc* desc, const cdl_tensor* q, const cdl_tensor* k,
+                                 const cdl_tensor* v, const cdl_tensor* cu_seqlens_q,
+                                 const cdl_tensor* cu_seqlens_k, int64_t max_seqlen_q,
+                                 int64_t max_seqlen_k, const cdl_tensor* o, const cdl_tensor* lse,
+                                 cdl_stream stream) {
+  return cdl::attn_fwd_packed_execute(desc, q, k, v, cu_seqlens_q, cu_seqlens_k, max_seqlen_q,
+                                      max_seqlen_k, o, lse, static_cast<cudaStream_t>(stream));
+}
 
 int32_t cdl_b200_attn_fwd(const cdl_attn_desc* desc, const cdl_tensor* q, const cdl_tensor* k,
                           const cdl_tensor* v, const cdl_tensor* o, const cdl_tensor* lse,

@@ -30,6 +30,17 @@ int32_t attn_bwd_execute(const cdl_attn_desc* desc, const cdl_tensor* q, const c
                          const cdl_tensor* lse, const cdl_tensor* dq, const cdl_tensor* dk,
                          const cdl_tensor* dv, void* scratch, size_t scratch_bytes,
                          cudaStream_t stream);
+int32_t attn_fwd_packed_execute(const cdl_attn_desc* desc, const cdl_tensor* q, const cdl_tensor* k,
+                                const cdl_tensor* v, const cdl_tensor* cu_q, const cdl_tensor* cu_k,
+                                long long max_q, long long max_k, const cdl_tensor* o,
+                                const cdl_tensor* lse, cudaStream_t stream);
+size_t attn_bwd_packed_scratch_bytes(long long batch, long long max_seqlen_q, long long H);
+int32_t attn_bwd_packed_execute(const cdl_attn_desc* desc, const cdl_tensor* q, const cdl_tensor* k,
+                                const cdl_tensor* v, const cdl_tensor* o, const cdl_tensor* d_o,
+                                const cdl_tensor* lse, const cdl_tensor* cu_q, const cdl_tensor* cu_k,
+                                long long max_q, long long max_k, const cdl_tensor* dq,
+                                const cdl_tensor* dk, const cdl_tensor* dv, void* scratch,
+                                size_t scratch_bytes, cudaStream_t stream);
 int32_t rope_execute(const cdl_tensor* x, const cdl_tensor* cos_sin, int32_t rot_heads,
                      int32_t seqlen, int32_t backward, cudaStream_t stream);
 int32_t swiglu_fwd_execute(const cdl_tensor* gate, const cdl_tensor* up, const cdl_tensor* act,

@@ -117,16 +117,31 @@ def norm_bwd(x, dy, scale, r_inv, dscale, residual_dy=None, scratch=None) -> tor
 @dataclass
 class AttentionOpts:
     """The subset of `AttentionOpts` (ops/attention/mod.rs:94-112) this library implements:
-    dense layouts, mask None or Causal, no softcap."""
+    dense or packed layouts, mask None or Causal, no softcap.
+
+    Packed layout (`QueryLayout::Packed` / `KvLayout::Packed`, mod.rs:55-79): q is
+    [total_q, heads, head_dim], k and v are [total_k, kv_heads, head_dim], sequence b is rows
+    cu_seqlens[b] .. cu_seqlens[b + 1]; both cu_seqlens (i32 [batch + 1], on the device) must be
+    given together.  max_seqlen bounds every sequence's length; None is the packed total."""
 
     softmax_scale: Optional[float] = None  # None is 1 / sqrt(head_dim)
     causal: bool = True
+    cu_seqlens_q: Optional[torch.Tensor] = None
+    cu_seqlens_k: Optional[torch.Tensor] = None
+    max_seqlen_q: Optional[int] = None
+    max_seqlen_k: Optional[int] = None
+
+    @property
+    def packed(self) -> bool:
+        if (self.cu_seqlens_q is None) != (self.cu_seqlens_k is None):
+            raise _lib.CdlError(-1, "attention: cu_seqlens_q and cu_seqlens_k must be given together")
+        return self.cu_seqlens_q is not None
 
 
 @dataclass
 class AttentionFwdOutputs:
     out: torch.Tensor
-    lse: Optional[torch.Tensor]  # f32 [batch, heads, seqlen_q], natural log
+    lse: Optional[torch.Tensor]  # f32 [batch, heads, seqlen_q] (packed: [heads, total_q]), natural log
 
 
 def _attn_desc(opts: AttentionOpts) -> CdlAttnDesc:
@@ -139,6 +154,19 @@ def _attn_desc(opts: AttentionOpts) -> CdlAttnDesc:
 def attention_fwd(q, k, v, opts: AttentionOpts | None = None, lse: bool = True) -> AttentionFwdOutputs:
     opts = opts or AttentionOpts()
     _require_cuda(q, k, v)
+    if opts.packed:
+        if q.dim() != 3:
+            raise _lib.CdlError(-1, "attention: packed q must be [total_q, heads, head_dim]")
+        out = torch.empty(q.shape, dtype=q.dtype, device=q.device)
+        lse_t = (torch.empty(q.shape[1], q.shape[0], dtype=torch.float32, device=q.device)
+                 if lse else None)
+        desc = _attn_desc(opts)
+        a = [tensor_arg(t) for t in (q, k, v, opts.cu_seqlens_q, opts.cu_seqlens_k)]
+        b = [tensor_arg(t) for t in (out, lse_t)]
+        check(lib.cdl_b200_attn_fwd_packed(ctypes.byref(desc), *(ref(x) for x in a),
+                                           int(opts.max_seqlen_q or 0), int(opts.max_seqlen_k or 0),
+                                           *(ref(x) for x in b), _stream()))
+        return AttentionFwdOutputs(out, lse_t)
     if q.dim() != 4:
         raise _lib.CdlError(-1, "attention: q must be [batch, seqlen, heads, head_dim]")
     out = torch.empty(q.shape, dtype=q.dtype, device=q.device)
@@ -165,6 +193,24 @@ def attention_bwd(q, k, v, out, d_out, lse, opts: AttentionOpts | None = None, s
     dq = torch.empty(q.shape, dtype=q.dtype, device=q.device) if dq is None else dq
     dk = torch.empty(k.shape, dtype=k.dtype, device=k.device) if dk is None else dk
     dv = torch.empty(v.shape, dtype=v.dtype, device=v.device) if dv is None else dv
+    if opts.packed:
+        if q.dim() != 3:
+            raise _lib.CdlError(-1, "attention: packed q must be [total_q, heads, head_dim]")
+        batch = opts.cu_seqlens_q.shape[0] - 1
+        max_q = int(opts.max_seqlen_q or 0)
+        n = ctypes.c_size_t(0)
+        check(lib.cdl_b200_attn_bwd_packed_scratch_bytes(
+            batch, max_q if 0 < max_q <= q.shape[0] else q.shape[0], q.shape[1], ctypes.byref(n)))
+        if scratch is None:
+            scratch = torch.empty(max(n.value, 16), dtype=torch.uint8, device=q.device)
+        desc = _attn_desc(opts)
+        a = [tensor_arg(t) for t in (q, k, v, out, d_out, lse, opts.cu_seqlens_q, opts.cu_seqlens_k)]
+        b = [tensor_arg(t) for t in (dq, dk, dv)]
+        check(lib.cdl_b200_attn_bwd_packed(ctypes.byref(desc), *(ref(x) for x in a), max_q,
+                                           int(opts.max_seqlen_k or 0), *(ref(x) for x in b),
+                                           ctypes.c_void_p(scratch.data_ptr()),
+                                           scratch.numel() * scratch.element_size(), _stream()))
+        return dq, dk, dv
     need = attention_bwd_scratch_bytes(q, k)
     if scratch is None:
         scratch = torch.empty(max(need, 16), dtype=torch.uint8, device=q.device)

@@ -172,6 +172,30 @@ int32_t cdl_b200_attn_bwd(const cdl_attn_desc* desc, const cdl_tensor* q, const 
 int32_t cdl_b200_attn_bwd_scratch_bytes(const cdl_tensor* q, const cdl_tensor* k,
                                         size_t* bytes_out);
 
+/* Packed ("varlen") layout of the reference's QueryLayout::Packed / KvLayout::Packed
+ * (attention/mod.rs:55-79): q, out, d_out, dq are [total_q, heads, 128] and k, v, dk, dv are
+ * [total_k, kv_heads, 128]; sequence b is rows cu_seqlens_q[b] .. cu_seqlens_q[b + 1] of the former
+ * and cu_seqlens_k[b] .. cu_seqlens_k[b + 1] of the latter (i32 [batch + 1] in device memory); the
+ * mask is aligned bottom-right per sequence; lse is f32 [heads, total_q] (mod.rs:674-677).
+ * max_seqlen_q / max_seqlen_k bound every sequence's length and only size the grids (<= 0: the
+ * packed total, as `None` does in the reference).  Rows outside every sequence (padding at the
+ * end) are neither read into a result nor written; they must hold finite values, because a key
+ * row that a tile loads beyond its sequence is multiplied by a zero probability, not skipped. */
+int32_t cdl_b200_attn_fwd_packed(const cdl_attn_desc* desc, const cdl_tensor* q, const cdl_tensor* k,
+                                 const cdl_tensor* v, const cdl_tensor* cu_seqlens_q,
+                                 const cdl_tensor* cu_seqlens_k, int64_t max_seqlen_q,
+                                 int64_t max_seqlen_k, const cdl_tensor* o, const cdl_tensor* lse,
+                                 cdl_stream stream);
+int32_t cdl_b200_attn_bwd_packed(const cdl_attn_desc* desc, const cdl_tensor* q, const cdl_tensor* k,
+                                 const cdl_tensor* v, const cdl_tensor* o, const cdl_tensor* d_out,
+                                 const cdl_tensor* lse, const cdl_tensor* cu_seqlens_q,
+                                 const cdl_tensor* cu_seqlens_k, int64_t max_seqlen_q,
+                                 int64_t max_seqlen_k, const cdl_tensor* dq, const cdl_tensor* dk,
+                                 const cdl_tensor* dv, void* scratch, size_t scratch_bytes,
+                                 cdl_stream stream);
+int32_t cdl_b200_attn_bwd_packed_scratch_bytes(int64_t batch, int64_t max_seqlen_q, int64_t heads,
+                                               size_t* bytes_out);
+
 /* ---- Elementwise glue of the sky-1 block -----------------------------------------------
  * The reference's kernels for these lived in its legacy `cleandl::operators` module, which is
  * absent from its tree; the call sites are crates/sky-1/src/training/model/decoder.rs:363-378

@@ -186,3 +186,98 @@ def test_bwd_scratch_is_checked(cdl, gpu_ok):
     small = torch.empty(64, dtype=torch.uint8, device="cuda")
     with pytest.raises(cdl._lib.CdlError, match="scratch"):
         cdl.ops.attention_bwd(q, k, v, fwd.out, do, fwd.lse, scratch=small)
+
+
+# ---------------------------------------------------------------------------------------------
+# Packed ("varlen") layout: QueryLayout::Packed / KvLayout::Packed of the reference
+# (ops/attention/mod.rs:55-79), tested there by `Case::varlen` with 5 unused query rows and 3
+# unused key rows at the end of the packed buffers (crates/cleandl/tests/attention.rs:118-127,
+# 273-299).  The oracle runs one sequence at a time on the dense restatement.
+
+def make_packed(seqlens_q, seqlens_k, hq, hk, pad_q=5, pad_k=3, seed=11, d=128):
+    gen = torch.Generator().manual_seed(seed)
+    tq, tk = sum(seqlens_q) + pad_q, sum(seqlens_k) + pad_k
+    q = torch.randn(tq, hq, d, generator=gen).to(torch.bfloat16)
+    k = torch.randn(tk, hk, d, generator=gen).to(torch.bfloat16)
+    v = torch.randn(tk, hk, d, generator=gen).to(torch.bfloat16)
+    do = torch.randn(tq, hq, d, generator=gen).to(torch.bfloat16)
+    cu_q = torch.tensor([0] + list(np.cumsum(seqlens_q)), dtype=torch.int32)
+    cu_k = torch.tensor([0] + list(np.cumsum(seqlens_k)), dtype=torch.int32)
+    return q, k, v, do, cu_q, cu_k
+
+
+PACKED_CASES = [
+    # seqlens_q, seqlens_k, hq, hk, causal, give max_seqlen
+    ([128, 256], [128, 256], 2, 2, True, True),
+    ([200, 77, 333], [200, 77, 333], 2, 1, True, True),       # ragged, GQA
+    ([100, 300, 1], [260, 300, 40], 2, 2, True, False),       # sq != sk per sequence, no bound given
+    ([64, 0, 190], [64, 50, 190], 1, 1, True, True),          # an empty query sequence
+    ([130, 250], [300, 129], 4, 2, False, True),              # dense mask
+]
+
+
+@pytest.mark.parametrize("sq,sk,hq,hk,causal,bound", PACKED_CASES)
+def test_packed_fwd_bwd(cdl, gpu_ok, sq, sk, hq, hk, causal, bound):
+    q, k, v, do, cu_q, cu_k = make_packed(sq, sk, hq, hk)
+    opts = cdl.ops.AttentionOpts(causal=causal, cu_seqlens_q=cu_q.cuda(), cu_seqlens_k=cu_k.cuda(),
+                                 max_seqlen_q=max(sq) if bound else None,
+                                 max_seqlen_k=max(sk) if bound else None)
+    qd, kd, vd, dod = q.cuda(), k.cuda(), v.cuda(), do.cuda()
+    fwd = cdl.ops.attention_fwd(qd, kd, vd, opts)
+    # rows outside every sequence are not written: mark them to check that
+    dq = torch.full_like(qd, 7.0)
+    dk = torch.full_like(kd, 7.0)
+    dv = torch.full_like(vd, 7.0)
+    cdl.ops.attention_bwd(qd, kd, vd, fwd.out, dod, fwd.lse, opts, dq=dq, dk=dk, dv=dv)
+    assert fwd.lse.shape == (hq, q.shape[0])
+    for b in range(len(sq)):
+        q0, q1, k0, k1 = int(cu_q[b]), int(cu_q[b + 1]), int(cu_k[b]), int(cu_k[b + 1])
+        if q1 == q0:
+            assert float(dk[k0:k1].float().abs().max()) == 0.0 if k1 > k0 else True
+            continue
+        ref = oracle.attention(to_f32(q[None, q0:q1]), to_f32(k[None, k0:k1]), to_f32(v[None, k0:k1]),
+                               to_f32(do[None, q0:q1]), causal=causal)
+        assert_all_close(f"out[{b}]", to_f32(fwd.out[q0:q1])[None], ref["out"],
+                         oracle.attention_tolerance(ref["out"], 1e-2, 1e-2))
+        got_lse = to_f32(fwd.lse[:, q0:q1])[None]
+        exp_lse = np.where(np.isneginf(ref["lse"]), -1e30, ref["lse"])
+        assert_all_close(f"lse[{b}]", np.where(np.isneginf(got_lse), -1e30, got_lse), exp_lse,
+                         oracle.attention_tolerance(ref["lse"], 1e-4, 1e-3))
+        for name, got, lo, hi in (("dq", dq, q0, q1), ("dk", dk, k0, k1), ("dv", dv, k0, k1)):
+            assert_all_close(f"{name}[{b}]", to_f32(got[lo:hi])[None], ref[name],
+                             oracle.attention_tolerance(ref[name], 2e-2, 2e-2))
+    # the unused rows at the end keep their marker
+    assert float(dq[int(cu_q[-1]):].float().min()) == 7.0
+    assert float(dk[int(cu_k[-1]):].float().min()) == 7.0
+    assert float(dv[int(cu_k[-1]):].float().min()) == 7.0
+
+
+def test_packed_equals_dense_for_equal_lengths(cdl, gpu_ok):
+    """Equal-length sequences: the packed call must reproduce the dense call bit for bit."""
+    b, s, h = 3, 384, 2
+    q, k, v, do = make(b, s, s, h, h, seed=5)
+    dense = cdl.ops.attention_fwd(q.cuda(), k.cuda(), v.cuda())
+    ddq, ddk, ddv = cdl.ops.attention_bwd(q.cuda(), k.cuda(), v.cuda(), dense.out, do.cuda(), dense.lse)
+    cu = torch.arange(0, (b + 1) * s, s, dtype=torch.int32).cuda()
+    opts = cdl.ops.AttentionOpts(cu_seqlens_q=cu, cu_seqlens_k=cu, max_seqlen_q=s, max_seqlen_k=s)
+    flat = lambda t: t.reshape(b * s, h, 128).cuda()
+    packed = cdl.ops.attention_fwd(flat(q), flat(k), flat(v), opts)
+    assert torch.equal(packed.out.view(b, s, h, 128), dense.out)
+    assert torch.equal(packed.lse.view(h, b, s).permute(1, 0, 2), dense.lse)
+    pdq, pdk, pdv = cdl.ops.attention_bwd(flat(q), flat(k), flat(v), packed.out, flat(do), packed.lse, opts)
+    assert torch.equal(pdq.view(b, s, h, 128), ddq)
+    assert torch.equal(pdk.view(b, s, h, 128), ddk)
+    assert torch.equal(pdv.view(b, s, h, 128), ddv)
+
+
+def test_packed_rejections(cdl, gpu_ok):
+    z = lambda *s: torch.zeros(*s, dtype=torch.bfloat16, device="cuda")
+    cu = torch.tensor([0, 8], dtype=torch.int32, device="cuda")
+    with pytest.raises(cdl._lib.CdlError, match="together"):
+        cdl.ops.attention_fwd(z(8, 2, 128), z(8, 2, 128), z(8, 2, 128), cdl.ops.AttentionOpts(cu_seqlens_q=cu))
+    with pytest.raises(cdl._lib.CdlError, match="total_q, heads, head_dim"):
+        cdl.ops.attention_fwd(z(1, 8, 2, 128), z(1, 8, 2, 128), z(1, 8, 2, 128),
+                              cdl.ops.AttentionOpts(cu_seqlens_q=cu, cu_seqlens_k=cu))
+    with pytest.raises(cdl._lib.CdlError, match="i32"):
+        cdl.ops.attention_fwd(z(8, 2, 128), z(8, 2, 128), z(8, 2, 128),
+                              cdl.ops.AttentionOpts(cu_seqlens_q=cu.float(), cu_seqlens_k=cu))
