@@ -48,6 +48,11 @@ class CdlSky1Config(ctypes.Structure):
                     ("eps", ctypes.c_float)]
 
 
+class CdlSky1Ragged(ctypes.Structure):
+    _fields_ = [("cu_seqlens", ctypes.c_void_p), ("num_seqs", ctypes.c_int32),
+                ("max_seqlen", ctypes.c_int32)]
+
+
 _BLOCK_PARAMS = ("norm1", "wqkv", "wo", "norm2", "wup", "wgate", "wdown")
 
 
@@ -106,6 +111,7 @@ SIGNATURES = {
     "cdl_b200_attn_bwd_packed_scratch_bytes": ([ctypes.c_int64, ctypes.c_int64, ctypes.c_int64,
                                                 ctypes.POINTER(_sz)], ctypes.c_int32),
     "cdl_b200_rope": ([_T, _T, ctypes.c_int32, ctypes.c_int32, ctypes.c_int32, _vp], ctypes.c_int32),
+    "cdl_b200_rope_ragged": ([_T, _T, ctypes.c_int32, _T, ctypes.c_int32, _vp], ctypes.c_int32),
     "cdl_b200_swiglu_fwd": ([_T, _T, _T, _vp], ctypes.c_int32),
     "cdl_b200_swiglu_bwd": ([_T, _T, _T, _T, _T, _vp], ctypes.c_int32),
     "cdl_b200_cross_entropy": ([_T, _T, _T, ctypes.c_float, _vp], ctypes.c_int32),
@@ -116,6 +122,16 @@ SIGNATURES = {
                         ctypes.POINTER(CdlAdamwParams), _vp], ctypes.c_int32),
     "cdl_b200_sky1_block_workspace_bytes": ([ctypes.POINTER(CdlSky1Config), ctypes.POINTER(_sz),
                                              ctypes.POINTER(_sz)], ctypes.c_int32),
+    "cdl_b200_sky1_block_workspace_bytes_ragged": ([ctypes.POINTER(CdlSky1Config),
+                                                    ctypes.POINTER(CdlSky1Ragged), ctypes.POINTER(_sz),
+                                                    ctypes.POINTER(_sz)], ctypes.c_int32),
+    "cdl_b200_sky1_block_fwd_ragged": ([ctypes.POINTER(CdlSky1Config), ctypes.POINTER(CdlSky1Weights),
+                                        _vp, _vp, ctypes.POINTER(CdlSky1Ragged),
+                                        ctypes.POINTER(CdlSky1Saved), _vp, _vp, _sz, _vp], ctypes.c_int32),
+    "cdl_b200_sky1_block_bwd_ragged": ([ctypes.POINTER(CdlSky1Config), ctypes.POINTER(CdlSky1Weights),
+                                        _vp, _vp, ctypes.POINTER(CdlSky1Ragged),
+                                        ctypes.POINTER(CdlSky1Saved), _vp, ctypes.POINTER(CdlSky1Grads),
+                                        _vp, _vp, _sz, ctypes.c_int32, _vp], ctypes.c_int32),
     "cdl_b200_sky1_block_fwd": ([ctypes.POINTER(CdlSky1Config), ctypes.POINTER(CdlSky1Weights), _vp,
                                  _vp, ctypes.POINTER(CdlSky1Saved), _vp, _vp, _sz, _vp],
                                 ctypes.c_int32),

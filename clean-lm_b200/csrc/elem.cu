@@ -28,7 +28,7 @@ __device__ __forceinline__ uint4 pack8(const float (&f)[8]) {
 __global__ void __launch_bounds__(256)
     rope_kernel(__nv_bfloat16* __restrict__ x, long long token_stride, long long head_stride,
                 const float* __restrict__ cos_sin, long long tokens, int seqlen, int rot_heads,
-                int half_dim, float sign) {
+                int half_dim, float sign, const int* __restrict__ cu_seqlens, int num_seqs) {
   const int groups = half_dim / 8;  // 8-element groups per half
   const long long idx = static_cast<long long>(blockIdx.x) * 256 + threadIdx.x;
   const long long total = tokens * rot_heads * groups;
@@ -36,7 +36,20 @@ __global__ void __launch_bounds__(256)
   const int g = static_cast<int>(idx % groups);
   const int head = static_cast<int>((idx / groups) % rot_heads);
   const long long token = idx / groups / rot_heads;
-  const int pos = static_cast<int>(token % seqlen);
+  int pos;
+  if (cu_seqlens != nullptr) {
+    // ragged batch: the position restarts at every sequence; `seqlen` is the table's row count
+    if (token >= cu_seqlens[num_seqs]) return;  // padding rows after the last sequence
+    int lo_i = 0, hi_i = num_seqs;              // largest b with cu_seqlens[b] <= token
+    while (hi_i - lo_i > 1) {
+      const int mid = (lo_i + hi_i) >> 1;
+      if (cu_seqlens[mid] <= token) lo_i = mid;
+      else hi_i = mid;
+    }
+    pos = min(static_cast<int>(token - cu_seqlens[lo_i]), seqlen - 1);
+  } else {
+    pos = static_cast<int>(token % seqlen);
+  }
   __nv_bfloat16* p = x + token * token_stride + head * head_stride + g * 8;
   const uint4 lo_q = *reinterpret_cast<const uint4*>(p);
   const uint4 hi_q = *reinterpret_cast<const uint4*>(p + half_dim);
@@ -117,9 +130,24 @@ __global__ void __launch_bounds__(256)
 
 static bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15) == 0; }
 
+int32_t rope_ragged_execute(const cdl_tensor* x, const cdl_tensor* cos_sin, int32_t rot_heads,
+                            int32_t seqlen, const cdl_tensor* cu_seqlens, int32_t backward,
+                            cudaStream_t stream);
+
 int32_t rope_execute(const cdl_tensor* x, const cdl_tensor* cos_sin, int32_t rot_heads,
                      int32_t seqlen, int32_t backward, cudaStream_t stream) {
+  return rope_ragged_execute(x, cos_sin, rot_heads, seqlen, nullptr, backward, stream);
+}
+
+// cu_seqlens (nullable): i32 [num_seqs + 1]; with it, token t of sequence b has position
+// t - cu_seqlens[b] and `seqlen` is only the number of table rows that may be used.
+int32_t rope_ragged_execute(const cdl_tensor* x, const cdl_tensor* cos_sin, int32_t rot_heads,
+                            int32_t seqlen, const cdl_tensor* cu_seqlens, int32_t backward,
+                            cudaStream_t stream) {
   const char* op = "rope";
+  if (cu_seqlens && (cu_seqlens->rank != 1 || cu_seqlens->dtype != CDL_I32 || cu_seqlens->shape[0] < 1 ||
+                     cu_seqlens->stride[0] != 1))
+    return fail(CDL_ERR_INVALID, "%s: cu_seqlens must be a contiguous i32 vector of batch + 1 entries", op);
   if (!x || !cos_sin) return fail(CDL_ERR_INVALID, "%s: x and cos_sin are required", op);
   if (x->rank != 3 || x->dtype != CDL_BF16)
     return fail(CDL_ERR_INVALID, "%s: x must be bf16 [tokens, heads, head_dim]", op);
@@ -139,7 +167,8 @@ int32_t rope_execute(const cdl_tensor* x, const cdl_tensor* cos_sin, int32_t rot
   elem::rope_kernel<<<static_cast<unsigned>((total + 255) / 256), 256, 0, stream>>>(
       static_cast<__nv_bfloat16*>(x->ptr), x->stride[0], x->stride[1],
       static_cast<const float*>(cos_sin->ptr), tokens, seqlen, rot_heads, static_cast<int>(d / 2),
-      backward ? -1.0f : 1.0f);
+      backward ? -1.0f : 1.0f, cu_seqlens ? static_cast<const int*>(cu_seqlens->ptr) : nullptr,
+      cu_seqlens ? static_cast<int>(cu_seqlens->shape[0] - 1) : 0);
   CDL_CUDA(cudaGetLastError());
   return CDL_OK;
 }
@@ -238,6 +267,13 @@ int32_t cdl_b200_embedding_fwd(const cdl_tensor* tokens, const cdl_tensor* table
 int32_t cdl_b200_rope(const cdl_tensor* x, const cdl_tensor* cos_sin, int32_t rot_heads,
                       int32_t seqlen, int32_t backward, cdl_stream stream) {
   return cdl::rope_execute(x, cos_sin, rot_heads, seqlen, backward, static_cast<cudaStream_t>(stream));
+}
+int32_t cdl_b200_rope_ragged(const cdl_tensor* x, const cdl_tensor* cos_sin, int32_t rot_heads,
+                             const cdl_tensor* cu_seqlens, int32_t backward, cdl_stream stream) {
+  if (!cu_seqlens || !cos_sin || cos_sin->rank != 2)
+    return cdl::fail(CDL_ERR_INVALID, "rope: cu_seqlens and a [positions, head_dim] table are required");
+  return cdl::rope_ragged_execute(x, cos_sin, rot_heads, static_cast<int32_t>(cos_sin->shape[0]),
+                                  cu_seqlens, backward, static_cast<cudaStream_t>(stream));
 }
 int32_t cdl_b200_swiglu_fwd(const cdl_tensor* gate, const cdl_tensor* up, const cdl_tensor* act,
                             cdl_stream stream) {

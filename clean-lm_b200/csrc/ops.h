@@ -43,6 +43,9 @@ int32_t attn_bwd_packed_execute(const cdl_attn_desc* desc, const cdl_tensor* q, 
                                 size_t scratch_bytes, cudaStream_t stream);
 int32_t rope_execute(const cdl_tensor* x, const cdl_tensor* cos_sin, int32_t rot_heads,
                      int32_t seqlen, int32_t backward, cudaStream_t stream);
+int32_t rope_ragged_execute(const cdl_tensor* x, const cdl_tensor* cos_sin, int32_t rot_heads,
+                            int32_t seqlen, const cdl_tensor* cu_seqlens, int32_t backward,
+                            cudaStream_t stream);
 int32_t swiglu_fwd_execute(const cdl_tensor* gate, const cdl_tensor* up, const cdl_tensor* act,
                            cudaStream_t stream);
 int32_t swiglu_bwd_execute(const cdl_tensor* d_act, const cdl_tensor* gate, const cdl_tensor* up,

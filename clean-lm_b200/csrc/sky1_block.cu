@@ -23,7 +23,20 @@ namespace {
 
 struct Dims {
   long long T, S, B, Hd, H, Hkv, D, F, QKV;
+  // ragged batch (nullptr: B sequences of S tokens): sequence b is tokens cu[b] .. cu[b + 1] of the T
+  const cdl_sky1_ragged* rg = nullptr;
 };
+
+int32_t read_ragged(const cdl_sky1_ragged* rg, Dims* d) {
+  d->rg = rg;
+  if (!rg) return CDL_OK;
+  if (!rg->cu_seqlens || rg->num_seqs <= 0 || rg->max_seqlen <= 0)
+    return fail(CDL_ERR_INVALID, "sky1_block: ragged batches need cu_seqlens, num_seqs > 0 and max_seqlen > 0");
+  if (rg->max_seqlen > d->T)
+    return fail(CDL_ERR_INVALID, "sky1_block: max_seqlen %d exceeds the %lld tokens of the buffers",
+                rg->max_seqlen, d->T);
+  return CDL_OK;
+}
 
 int32_t read_config(const cdl_sky1_config* c, Dims* d) {
   if (!c) return fail(CDL_ERR_INVALID, "sky1_block: config is required");
@@ -75,7 +88,8 @@ BwdBuffers carve_bwd(Workspace& w, const Dims& d) {
   b.d_o = w.take(d.T * d.Hd * 2);
   b.dattn = w.take(d.T * d.H * d.D * 2);
   b.dqkv = w.take(d.T * d.QKV * 2);
-  b.attn_scratch_bytes = attn_bwd_scratch_bytes(d.B, d.S, d.H);
+  b.attn_scratch_bytes = d.rg ? attn_bwd_packed_scratch_bytes(d.rg->num_seqs, d.rg->max_seqlen, d.H)
+                              : attn_bwd_scratch_bytes(d.B, d.S, d.H);
   b.attn_scratch = w.take(b.attn_scratch_bytes);
   b.norm_scratch_bytes = rmsnorm_bwd_scratch_bytes(d.T, d.Hd);
   b.norm_scratch = w.take(b.norm_scratch_bytes);
@@ -90,6 +104,43 @@ cdl_tensor head_view(const void* qkv, const Dims& d, long long first_head, long 
   t.rank = 4;
   t.shape[0] = d.B; t.shape[1] = d.S; t.shape[2] = heads; t.shape[3] = d.D;
   t.stride[0] = d.S * d.QKV; t.stride[1] = d.QKV; t.stride[2] = d.D; t.stride[3] = 1;
+  return t;
+}
+// The same heads of the fused qkv buffer as a packed [T, heads, D] view (ragged batches).
+cdl_tensor head_view_packed(const void* qkv, const Dims& d, long long first_head, long long heads) {
+  cdl_tensor t{};
+  t.ptr = static_cast<uint8_t*>(const_cast<void*>(qkv)) + first_head * d.D * 2;
+  t.dtype = CDL_BF16;
+  t.rank = 3;
+  t.shape[0] = d.T; t.shape[1] = heads; t.shape[2] = d.D;
+  t.stride[0] = d.QKV; t.stride[1] = d.D; t.stride[2] = 1;
+  return t;
+}
+cdl_tensor attn_view_packed(const void* p, const Dims& d) {
+  cdl_tensor t{};
+  t.ptr = const_cast<void*>(p);
+  t.dtype = CDL_BF16;
+  t.rank = 3;
+  t.shape[0] = d.T; t.shape[1] = d.H; t.shape[2] = d.D;
+  t.stride[0] = d.H * d.D; t.stride[1] = d.D; t.stride[2] = 1;
+  return t;
+}
+cdl_tensor lse_view_packed(const float* p, const Dims& d) {  // [heads, T]
+  cdl_tensor t{};
+  t.ptr = const_cast<float*>(p);
+  t.dtype = CDL_F32;
+  t.rank = 2;
+  t.shape[0] = d.H; t.shape[1] = d.T;
+  t.stride[0] = d.T; t.stride[1] = 1;
+  return t;
+}
+cdl_tensor cu_view(const Dims& d) {
+  cdl_tensor t{};
+  t.ptr = const_cast<int32_t*>(d.rg->cu_seqlens);
+  t.dtype = CDL_I32;
+  t.rank = 1;
+  t.shape[0] = d.rg->num_seqs + 1;
+  t.stride[0] = 1;
   return t;
 }
 cdl_tensor attn_view(const void* p, const Dims& d) {
@@ -135,9 +186,11 @@ size_t sky1_block_bwd_workspace(const Dims& d) {
 
 int32_t sky1_block_fwd(const cdl_sky1_config* cfg, const cdl_sky1_weights* wt, const void* x,
                        const float* rope_cos_sin, const cdl_sky1_saved* sv, void* out,
-                       void* workspace, size_t workspace_bytes, cudaStream_t st) {
+                       void* workspace, size_t workspace_bytes, const cdl_sky1_ragged* rg,
+                       cudaStream_t st) {
   Dims d;
   CDL_CHECK(read_config(cfg, &d));
+  CDL_CHECK(read_ragged(rg, &d));
   if (!wt || !x || !rope_cos_sin || !sv || !out)
     return fail(CDL_ERR_INVALID, "sky1_block_fwd: weights, x, rope table, saved and out are required");
   if (!workspace || workspace_bytes < sky1_block_fwd_workspace(d) ||
@@ -159,17 +212,32 @@ int32_t sky1_block_fwd(const cdl_sky1_config* cfg, const cdl_sky1_weights* wt, c
   const cdl_tensor wup = view2(wt->wup, CDL_BF16, d.Hd, d.F), wgate = view2(wt->wgate, CDL_BF16, d.Hd, d.F);
   const cdl_tensor wdown = view2(wt->wdown, CDL_BF16, d.F, d.Hd);
   const cdl_tensor tout = view2(out, CDL_BF16, d.T, d.Hd);
-  const cdl_tensor cs = view2(rope_cos_sin, CDL_F32, d.S, d.D);
+  const long long table_rows = d.rg ? d.rg->max_seqlen : d.S;
+  const cdl_tensor cs = view2(rope_cos_sin, CDL_F32, table_rows, d.D);
   const cdl_attn_desc ad{0.0f, 1};
 
   CDL_CHECK(rmsnorm_fwd_execute(&tx, &g1, nullptr, cfg->eps, &th, nullptr, st));
   CDL_CHECK(matmul_execute(&th, &wqkv, nullptr, &tqkv, 1.f, 0.f, st));
   const cdl_tensor rv = rope_view(sv->qkv, d);
-  CDL_CHECK(rope_execute(&rv, &cs, static_cast<int32_t>(d.H + d.Hkv), static_cast<int32_t>(d.S), 0, st));
-  const cdl_tensor q = head_view(sv->qkv, d, 0, d.H), k = head_view(sv->qkv, d, d.H, d.Hkv),
-                   v = head_view(sv->qkv, d, d.H + d.Hkv, d.Hkv);
-  const cdl_tensor ao = attn_view(sv->attn, d), lse = lse_view(sv->lse, d);
-  CDL_CHECK(attn_fwd_execute(&ad, &q, &k, &v, &ao, &lse, st));
+  if (d.rg) {
+    const cdl_tensor cu = cu_view(d);
+    CDL_CHECK(rope_ragged_execute(&rv, &cs, static_cast<int32_t>(d.H + d.Hkv),
+                                  static_cast<int32_t>(table_rows), &cu, 0, st));
+    const cdl_tensor q = head_view_packed(sv->qkv, d, 0, d.H), k = head_view_packed(sv->qkv, d, d.H, d.Hkv),
+                     v = head_view_packed(sv->qkv, d, d.H + d.Hkv, d.Hkv);
+    const cdl_tensor ao = attn_view_packed(sv->attn, d), lse = lse_view_packed(sv->lse, d);
+    // Rows after the last sequence are not written by the attention kernel; they are read by the
+    // output projection and, in the backward, by dWo += attn^T d_o, so they must not hold NaNs.
+    CDL_CUDA(cudaMemsetAsync(sv->attn, 0, static_cast<size_t>(d.T) * d.H * d.D * 2, st));
+    CDL_CHECK(attn_fwd_packed_execute(&ad, &q, &k, &v, &cu, &cu, d.rg->max_seqlen, d.rg->max_seqlen,
+                                      &ao, &lse, st));
+  } else {
+    CDL_CHECK(rope_execute(&rv, &cs, static_cast<int32_t>(d.H + d.Hkv), static_cast<int32_t>(d.S), 0, st));
+    const cdl_tensor q = head_view(sv->qkv, d, 0, d.H), k = head_view(sv->qkv, d, d.H, d.Hkv),
+                     v = head_view(sv->qkv, d, d.H + d.Hkv, d.Hkv);
+    const cdl_tensor ao = attn_view(sv->attn, d), lse = lse_view(sv->lse, d);
+    CDL_CHECK(attn_fwd_execute(&ad, &q, &k, &v, &ao, &lse, st));
+  }
   CDL_CHECK(matmul_execute(&tattn, &wo, &tx, &to, 1.f, 1.f, st));  // o = attn Wo + x
   CDL_CHECK(rmsnorm_fwd_execute(&to, &g2, nullptr, cfg->eps, &th, nullptr, st));
   CDL_CHECK(matmul_execute(&th, &wup, nullptr, &tup, 1.f, 0.f, st));
@@ -182,9 +250,10 @@ int32_t sky1_block_fwd(const cdl_sky1_config* cfg, const cdl_sky1_weights* wt, c
 int32_t sky1_block_bwd(const cdl_sky1_config* cfg, const cdl_sky1_weights* wt, const void* x,
                        const float* rope_cos_sin, const cdl_sky1_saved* sv, const void* dy,
                        const cdl_sky1_grads* gr, void* dx, void* workspace, size_t workspace_bytes,
-                       int32_t phase, cudaStream_t st) {
+                       int32_t phase, const cdl_sky1_ragged* rg, cudaStream_t st) {
   Dims d;
   CDL_CHECK(read_config(cfg, &d));
+  CDL_CHECK(read_ragged(rg, &d));
   if (!wt || !x || !rope_cos_sin || !sv || !dy || !gr || !dx)
     return fail(CDL_ERR_INVALID, "sky1_block_bwd: every argument is required");
   if (!workspace || workspace_bytes < sky1_block_bwd_workspace(d) ||
@@ -212,7 +281,7 @@ int32_t sky1_block_bwd(const cdl_sky1_config* cfg, const cdl_sky1_weights* wt, c
   const cdl_tensor tdact = view2(b.dact, CDL_BF16, d.T, d.F), tdgate = view2(b.dgate, CDL_BF16, d.T, d.F);
   const cdl_tensor tdh = view2(b.dh, CDL_BF16, d.T, d.Hd), tdo = view2(b.d_o, CDL_BF16, d.T, d.Hd);
   const cdl_tensor tdattn = view2(b.dattn, CDL_BF16, d.T, HD), tdqkv = view2(b.dqkv, CDL_BF16, d.T, d.QKV);
-  const cdl_tensor cs = view2(rope_cos_sin, CDL_F32, d.S, d.D);
+  const cdl_tensor cs = view2(rope_cos_sin, CDL_F32, d.rg ? d.rg->max_seqlen : d.S, d.D);
   const cdl_attn_desc ad{0.0f, 1};
   const cdl_tensor actT = transposed(tact), hT = transposed(th), attnT = transposed(tattn);
   const cdl_tensor wdownT = transposed(wdown), wupT = transposed(wup), wgateT = transposed(wgate);
@@ -236,15 +305,33 @@ int32_t sky1_block_bwd(const cdl_sky1_config* cfg, const cdl_sky1_weights* wt, c
   // attention
   CDL_CHECK(matmul_execute(&attnT, &tdo, &gwo, &gwo, 1.f, 1.f, st));                // dWo += attn^T d_o
   CDL_CHECK(matmul_execute(&tdo, &woT, nullptr, &tdattn, 1.f, 0.f, st));            // d_attn = d_o Wo^T
-  const cdl_tensor q = head_view(sv->qkv, d, 0, d.H), k = head_view(sv->qkv, d, d.H, d.Hkv),
-                   v = head_view(sv->qkv, d, d.H + d.Hkv, d.Hkv);
-  const cdl_tensor dq = head_view(b.dqkv, d, 0, d.H), dk = head_view(b.dqkv, d, d.H, d.Hkv),
-                   dv = head_view(b.dqkv, d, d.H + d.Hkv, d.Hkv);
-  const cdl_tensor ao = attn_view(sv->attn, d), dao = attn_view(b.dattn, d), lse = lse_view(sv->lse, d);
-  CDL_CHECK(attn_bwd_execute(&ad, &q, &k, &v, &ao, &dao, &lse, &dq, &dk, &dv, b.attn_scratch,
-                             b.attn_scratch_bytes, st));
   const cdl_tensor rv = rope_view(b.dqkv, d);
-  CDL_CHECK(rope_execute(&rv, &cs, static_cast<int32_t>(d.H + d.Hkv), static_cast<int32_t>(d.S), 1, st));
+  if (d.rg) {
+    const cdl_tensor cu = cu_view(d);
+    // Rows after the last sequence get no gradient from the attention kernels: clear the buffer
+    // so that the GEMMs that read all T rows of d_qkv see zeros there.
+    CDL_CUDA(cudaMemsetAsync(b.dqkv, 0, static_cast<size_t>(d.T) * d.QKV * 2, st));
+    const cdl_tensor q = head_view_packed(sv->qkv, d, 0, d.H), k = head_view_packed(sv->qkv, d, d.H, d.Hkv),
+                     v = head_view_packed(sv->qkv, d, d.H + d.Hkv, d.Hkv);
+    const cdl_tensor dq = head_view_packed(b.dqkv, d, 0, d.H), dk = head_view_packed(b.dqkv, d, d.H, d.Hkv),
+                     dv = head_view_packed(b.dqkv, d, d.H + d.Hkv, d.Hkv);
+    const cdl_tensor ao = attn_view_packed(sv->attn, d), dao = attn_view_packed(b.dattn, d),
+                     lse = lse_view_packed(sv->lse, d);
+    CDL_CHECK(attn_bwd_packed_execute(&ad, &q, &k, &v, &ao, &dao, &lse, &cu, &cu, d.rg->max_seqlen,
+                                      d.rg->max_seqlen, &dq, &dk, &dv, b.attn_scratch,
+                                      b.attn_scratch_bytes, st));
+    CDL_CHECK(rope_ragged_execute(&rv, &cs, static_cast<int32_t>(d.H + d.Hkv),
+                                  static_cast<int32_t>(d.rg->max_seqlen), &cu, 1, st));
+  } else {
+    const cdl_tensor q = head_view(sv->qkv, d, 0, d.H), k = head_view(sv->qkv, d, d.H, d.Hkv),
+                     v = head_view(sv->qkv, d, d.H + d.Hkv, d.Hkv);
+    const cdl_tensor dq = head_view(b.dqkv, d, 0, d.H), dk = head_view(b.dqkv, d, d.H, d.Hkv),
+                     dv = head_view(b.dqkv, d, d.H + d.Hkv, d.Hkv);
+    const cdl_tensor ao = attn_view(sv->attn, d), dao = attn_view(b.dattn, d), lse = lse_view(sv->lse, d);
+    CDL_CHECK(attn_bwd_execute(&ad, &q, &k, &v, &ao, &dao, &lse, &dq, &dk, &dv, b.attn_scratch,
+                               b.attn_scratch_bytes, st));
+    CDL_CHECK(rope_execute(&rv, &cs, static_cast<int32_t>(d.H + d.Hkv), static_cast<int32_t>(d.S), 1, st));
+  }
   CDL_CHECK(rmsnorm_fwd_execute(&tx, &g1, nullptr, cfg->eps, &th, &tr, st));        // recompute h1, r1
   CDL_CHECK(matmul_execute(&hT, &tdqkv, &gwqkv, &gwqkv, 1.f, 1.f, st));             // dWqkv += h1^T d_qkv
   CDL_CHECK(matmul_execute(&tdqkv, &wqkvT, nullptr, &tdh, 1.f, 0.f, st));           // dh1 = d_qkv Wqkv^T
@@ -256,6 +343,38 @@ int32_t sky1_block_bwd(const cdl_sky1_config* cfg, const cdl_sky1_weights* wt, c
 }  // namespace cdl
 
 extern "C" {
+
+int32_t cdl_b200_sky1_block_workspace_bytes_ragged(const cdl_sky1_config* cfg,
+                                                   const cdl_sky1_ragged* ragged, size_t* fwd_bytes,
+                                                   size_t* bwd_bytes) {
+  cdl::Dims d;
+  CDL_CHECK(cdl::read_config(cfg, &d));
+  CDL_CHECK(cdl::read_ragged(ragged, &d));
+  if (fwd_bytes) *fwd_bytes = cdl::sky1_block_fwd_workspace(d);
+  if (bwd_bytes) *bwd_bytes = cdl::sky1_block_bwd_workspace(d);
+  return CDL_OK;
+}
+
+int32_t cdl_b200_sky1_block_fwd_ragged(const cdl_sky1_config* cfg, const cdl_sky1_weights* weights,
+                                       const void* x, const float* rope_cos_sin,
+                                       const cdl_sky1_ragged* ragged, const cdl_sky1_saved* saved,
+                                       void* out, void* workspace, size_t workspace_bytes,
+                                       cdl_stream stream) {
+  if (!ragged) return cdl::fail(CDL_ERR_INVALID, "sky1_block_fwd_ragged: the ragged descriptor is required");
+  return cdl::sky1_block_fwd(cfg, weights, x, rope_cos_sin, saved, out, workspace, workspace_bytes,
+                             ragged, static_cast<cudaStream_t>(stream));
+}
+
+int32_t cdl_b200_sky1_block_bwd_ragged(const cdl_sky1_config* cfg, const cdl_sky1_weights* weights,
+                                       const void* x, const float* rope_cos_sin,
+                                       const cdl_sky1_ragged* ragged, const cdl_sky1_saved* saved,
+                                       const void* dy, const cdl_sky1_grads* grads, void* dx,
+                                       void* workspace, size_t workspace_bytes, int32_t phase,
+                                       cdl_stream stream) {
+  if (!ragged) return cdl::fail(CDL_ERR_INVALID, "sky1_block_bwd_ragged: the ragged descriptor is required");
+  return cdl::sky1_block_bwd(cfg, weights, x, rope_cos_sin, saved, dy, grads, dx, workspace,
+                             workspace_bytes, phase, ragged, static_cast<cudaStream_t>(stream));
+}
 
 int32_t cdl_b200_sky1_block_workspace_bytes(const cdl_sky1_config* cfg, size_t* fwd_bytes,
                                             size_t* bwd_bytes) {
@@ -271,7 +390,7 @@ int32_t cdl_b200_sky1_block_fwd(const cdl_sky1_config* cfg, const cdl_sky1_weigh
                                 const cdl_sky1_saved* saved, void* out, void* workspace,
                                 size_t workspace_bytes, cdl_stream stream) {
   return cdl::sky1_block_fwd(cfg, weights, x, rope_cos_sin, saved, out, workspace, workspace_bytes,
-                             static_cast<cudaStream_t>(stream));
+                             nullptr, static_cast<cudaStream_t>(stream));
 }
 
 int32_t cdl_b200_sky1_block_bwd(const cdl_sky1_config* cfg, const cdl_sky1_weights* weights,
@@ -280,7 +399,7 @@ int32_t cdl_b200_sky1_block_bwd(const cdl_sky1_config* cfg, const cdl_sky1_weigh
                                 const cdl_sky1_grads* grads, void* dx, void* workspace,
                                 size_t workspace_bytes, int32_t phase, cdl_stream stream) {
   return cdl::sky1_block_bwd(cfg, weights, x, rope_cos_sin, saved, dy, grads, dx, workspace,
-                             workspace_bytes, phase, static_cast<cudaStream_t>(stream));
+                             workspace_bytes, phase, nullptr, static_cast<cudaStream_t>(stream));
 }
 
 }  // extern "C"

@@ -85,9 +85,21 @@ class Sky1Block:
     """One decoder block: device weights, f32 gradient buffers, saved activations."""
 
     def __init__(self, cfg: Sky1Config, params: dict, device="cuda", grads: dict | None = None,
-                 workspace: torch.Tensor | None = None, table: torch.Tensor | None = None):
+                 workspace: torch.Tensor | None = None, table: torch.Tensor | None = None,
+                 cu_seqlens: torch.Tensor | None = None, max_seqlen: int | None = None):
+        """`cu_seqlens` (i32 [num_seqs + 1], device) makes the cfg.tokens rows a ragged batch: sequence
+        b is rows cu_seqlens[b] .. cu_seqlens[b + 1] (the layout of the reference's
+        `decoder_ragged_seqlen`, decoder.rs:372-378); `max_seqlen` bounds every length.  Rows after
+        the last sequence are padding: x there must be finite and dy zero."""
         self.cfg = cfg
         self.device = device
+        self.cu_seqlens = cu_seqlens
+        self._rg_c = None
+        if cu_seqlens is not None:
+            if cu_seqlens.dtype != torch.int32 or not cu_seqlens.is_cuda or cu_seqlens.dim() != 1:
+                raise _lib.CdlError(-1, "cu_seqlens must be an i32 vector on the device")
+            max_seqlen = int(max_seqlen if max_seqlen else cfg.tokens)
+            self._rg_c = _lib.CdlSky1Ragged(cu_seqlens.data_ptr(), cu_seqlens.numel() - 1, max_seqlen)
         def on_device(p):  # views of a caller-owned flat buffer are used in place, not copied
             if p.is_cuda and p.dtype == torch.bfloat16 and p.is_contiguous():
                 return p
@@ -105,18 +117,23 @@ class Sky1Block:
         self.saved = {
             "qkv": torch.empty(t, cfg.qkv_dim, **bf),
             "attn": torch.empty(t, cfg.heads * cfg.head_dim, **bf),
+            # dense: [batch, heads, seqlen]; ragged: [heads, tokens] -- the same number of elements
             "lse": torch.empty(cfg.batch, cfg.heads, cfg.seqlen, dtype=torch.float32, device=device),
             "o": torch.empty(t, cfg.hidden, **bf),
             "up": torch.empty(t, cfg.ffn, **bf),
             "gate": torch.empty(t, cfg.ffn, **bf),
             "act": torch.empty(t, cfg.ffn, **bf),
         }
-        self.table = table if table is not None else rope_table(cfg.seqlen, cfg.head_dim,
-                                                                 cfg.rope_base, device)
+        rows = self._rg_c.max_seqlen if self._rg_c is not None else cfg.seqlen
+        self.table = table if table is not None else rope_table(rows, cfg.head_dim, cfg.rope_base, device)
         self._cfg_c = cfg.c_struct()
         fwd, bwd = ctypes.c_size_t(0), ctypes.c_size_t(0)
-        check(lib.cdl_b200_sky1_block_workspace_bytes(ctypes.byref(self._cfg_c), ctypes.byref(fwd),
-                                                      ctypes.byref(bwd)))
+        if self._rg_c is not None:
+            check(lib.cdl_b200_sky1_block_workspace_bytes_ragged(
+                ctypes.byref(self._cfg_c), ctypes.byref(self._rg_c), ctypes.byref(fwd), ctypes.byref(bwd)))
+        else:
+            check(lib.cdl_b200_sky1_block_workspace_bytes(ctypes.byref(self._cfg_c), ctypes.byref(fwd),
+                                                          ctypes.byref(bwd)))
         self.workspace_bytes = max(fwd.value, bwd.value)
         self.workspace = workspace if workspace is not None else torch.empty(
             self.workspace_bytes, dtype=torch.uint8, device=device)
@@ -137,6 +154,13 @@ class Sky1Block:
         if x.dtype != torch.bfloat16 or x.numel() != cfg.tokens * cfg.hidden or not x.is_contiguous():
             raise _lib.CdlError(-1, "x must be a contiguous bf16 tensor of [tokens, hidden]")
         out = torch.empty_like(x) if out is None else out
+        if self._rg_c is not None:
+            check(lib.cdl_b200_sky1_block_fwd_ragged(
+                ctypes.byref(self._cfg_c), ctypes.byref(self._w_c), x.data_ptr(), self.table.data_ptr(),
+                ctypes.byref(self._rg_c), ctypes.byref(self._s_c), out.data_ptr(),
+                self.workspace.data_ptr(), self.workspace.numel(), self._stream()))
+            self._x = x
+            return out
         check(lib.cdl_b200_sky1_block_fwd(
             ctypes.byref(self._cfg_c), ctypes.byref(self._w_c), x.data_ptr(), self.table.data_ptr(),
             ctypes.byref(self._s_c), out.data_ptr(), self.workspace.data_ptr(),
@@ -152,6 +176,13 @@ class Sky1Block:
         if dy.dtype != torch.bfloat16 or dy.numel() != self._x.numel() or not dy.is_contiguous():
             raise _lib.CdlError(-1, "dy must be a contiguous bf16 tensor shaped like x")
         dx = torch.empty_like(dy) if dx is None else dx
+        if self._rg_c is not None:
+            check(lib.cdl_b200_sky1_block_bwd_ragged(
+                ctypes.byref(self._cfg_c), ctypes.byref(self._w_c), self._x.data_ptr(),
+                self.table.data_ptr(), ctypes.byref(self._rg_c), ctypes.byref(self._s_c), dy.data_ptr(),
+                ctypes.byref(self._g_c), dx.data_ptr(), self.workspace.data_ptr(),
+                self.workspace.numel(), phase, self._stream()))
+            return dx
         check(lib.cdl_b200_sky1_block_bwd(
             ctypes.byref(self._cfg_c), ctypes.byref(self._w_c), self._x.data_ptr(),
             self.table.data_ptr(), ctypes.byref(self._s_c), dy.data_ptr(), ctypes.byref(self._g_c),

@@ -209,6 +209,11 @@ int32_t cdl_b200_attn_bwd_packed_scratch_bytes(int64_t batch, int64_t max_seqlen
 int32_t cdl_b200_rope(const cdl_tensor* x, const cdl_tensor* cos_sin, int32_t rot_heads,
                       int32_t seqlen, int32_t backward, cdl_stream stream);
 /* act = SiLU(gate) * up, packed bf16 tensors of equal size. */
+/* RoPE over a ragged batch: token t of sequence b (rows cu_seqlens[b] .. cu_seqlens[b + 1]) has
+ * position t - cu_seqlens[b]; the table has one row per position; rows after the last sequence are
+ * left untouched. */
+int32_t cdl_b200_rope_ragged(const cdl_tensor* x, const cdl_tensor* cos_sin, int32_t rot_heads,
+                             const cdl_tensor* cu_seqlens, int32_t backward, cdl_stream stream);
 int32_t cdl_b200_swiglu_fwd(const cdl_tensor* gate, const cdl_tensor* up, const cdl_tensor* act,
                             cdl_stream stream);
 /* d_up = d_act * SiLU(gate);  d_gate = d_act * up * dSiLU(gate).  d_up may alias d_act. */
@@ -282,6 +287,35 @@ typedef struct { /* activations the forward saves for the backward (decoder.rs:5
   void* gate; /* bf16 [T, ffn] */
   void* act;  /* bf16 [T, ffn] */
 } cdl_sky1_saved;
+
+/* Ragged batch (the layout sky-1 trains with: `decoder_ragged_seqlen.cu_seqlen()`,
+ * crates/sky-1/src/training/model/decoder.rs:372-378, 440-455): the T = batch * seqlen token rows
+ * of the block's buffers hold num_seqs sequences, sequence b in rows cu_seqlens[b] ..
+ * cu_seqlens[b + 1] (i32 [num_seqs + 1], device memory); RoPE positions restart at every
+ * sequence, attention is causal within a sequence, the saved lse is f32 [heads, T], the RoPE table
+ * has max_seqlen rows.  Rows after the last sequence are padding: x there must be finite and dy
+ * must be zero (their attention output and their d_qkv are zeroed by the library), so that they add
+ * nothing to the weight gradients. */
+typedef struct {
+  const int32_t* cu_seqlens;
+  int32_t num_seqs;
+  int32_t max_seqlen; /* bound on every sequence's length */
+} cdl_sky1_ragged;
+
+int32_t cdl_b200_sky1_block_workspace_bytes_ragged(const cdl_sky1_config* cfg,
+                                                   const cdl_sky1_ragged* ragged, size_t* fwd_bytes,
+                                                   size_t* bwd_bytes);
+int32_t cdl_b200_sky1_block_fwd_ragged(const cdl_sky1_config* cfg, const cdl_sky1_weights* weights,
+                                       const void* x, const float* rope_cos_sin,
+                                       const cdl_sky1_ragged* ragged, const cdl_sky1_saved* saved,
+                                       void* out, void* workspace, size_t workspace_bytes,
+                                       cdl_stream stream);
+int32_t cdl_b200_sky1_block_bwd_ragged(const cdl_sky1_config* cfg, const cdl_sky1_weights* weights,
+                                       const void* x, const float* rope_cos_sin,
+                                       const cdl_sky1_ragged* ragged, const cdl_sky1_saved* saved,
+                                       const void* dy, const cdl_sky1_grads* grads, void* dx,
+                                       void* workspace, size_t workspace_bytes, int32_t phase,
+                                       cdl_stream stream);
 
 int32_t cdl_b200_sky1_block_workspace_bytes(const cdl_sky1_config* cfg, size_t* fwd_bytes,
                                             size_t* bwd_bytes);

@@ -101,3 +101,67 @@ def test_block_rejects_bad_arguments(cdl, gpu_ok):
         blk.forward(torch.zeros(cfg.tokens, cfg.hidden, device="cuda"))
     with pytest.raises(cdl._lib.CdlError, match="before forward"):
         blk.backward(torch.zeros(cfg.tokens, cfg.hidden, device="cuda", dtype=torch.bfloat16))
+
+
+def test_ragged_block_vs_oracle_per_sequence(cdl, gpu_ok):
+    """Ragged batch (cu_seqlens; RoPE positions restart, attention stays inside a sequence; the
+    layout of the reference's decoder_ragged_seqlen, decoder.rs:372-378, 440-455): outputs and dx
+    of every sequence equal the dense oracle run on that sequence alone, and the weight gradients
+    equal the sum of the per-sequence ones.  6 padding rows follow the last sequence."""
+    sky1 = cdl.sky1
+    seqlens = [150, 37, 260, 128]
+    pad = 6
+    total = sum(seqlens) + pad
+    cfg = sky1.Sky1Config(batch=1, seqlen=total, hidden=256, heads=2, kv_heads=1, head_dim=128, ffn=384)
+    params = sky1.init_params(cfg, seed=5, std=0.05)
+    gen = torch.Generator().manual_seed(5)
+    params["norm1"] = (1 + 0.1 * torch.randn(cfg.hidden, generator=gen)).to(torch.bfloat16)
+    params["norm2"] = (1 + 0.1 * torch.randn(cfg.hidden, generator=gen)).to(torch.bfloat16)
+    x = torch.randn(total, cfg.hidden, generator=gen).to(torch.bfloat16)
+    dy = torch.randn(total, cfg.hidden, generator=gen).to(torch.bfloat16)
+    dy[total - pad:] = 0  # padding rows carry no gradient
+    cu = torch.tensor([0] + list(torch.tensor(seqlens).cumsum(0)), dtype=torch.int32)
+    blk = sky1.Sky1Block(cfg, params, cu_seqlens=cu.cuda(), max_seqlen=max(seqlens))
+    blk.saved["attn"].fill_(float("nan"))  # stale contents must not leak into the padding rows
+    out = blk.forward(x.cuda())
+    dx = blk.backward(dy.cuda())
+    torch.cuda.synchronize()
+    assert blk.saved["lse"].numel() == cfg.heads * total
+
+    c = dict(heads=cfg.heads, kv_heads=cfg.kv_heads, head_dim=cfg.head_dim, eps=cfg.eps)
+    g_sum = {n: torch.zeros(s, dtype=torch.float64) for n, s in cfg.param_shapes().items()}
+    for b, n_tok in enumerate(seqlens):
+        lo, hi = int(cu[b]), int(cu[b + 1])
+        table = block_ref.rope_table(n_tok, cfg.head_dim)
+        o_ref, dx_ref, g_ref = block_ref.block_forward_backward(x[None, lo:hi], params, dy[None, lo:hi], c, table)
+        assert rel_err(out[lo:hi], o_ref[0]) <= 2e-2, b
+        assert rel_err(dx[lo:hi], dx_ref[0]) <= 2e-2, b
+        for n in g_sum:
+            g_sum[n] += g_ref[n]
+    for n in sky1.PARAM_NAMES:
+        got = blk.grads[n].double().cpu()
+        assert torch.isfinite(got).all(), n
+        err = ((got - g_sum[n]).abs().max() / g_sum[n].abs().max()).item()
+        assert err <= 2e-2, (n, err)
+
+
+def test_rope_ragged_positions(cdl, gpu_ok):
+    L = cdl._lib
+    heads, d = 3, 128
+    seqlens = [5, 1, 9]
+    total = sum(seqlens) + 2
+    gen = torch.Generator().manual_seed(1)
+    x = torch.randn(total, heads, d, generator=gen).to(torch.bfloat16)
+    table = block_ref.rope_table(max(seqlens), d)
+    cu = torch.tensor([0, 5, 6, 15], dtype=torch.int32).cuda()
+    xd = x.cuda().clone()
+    tx, tt, tc = L.tensor_arg(xd), L.tensor_arg(table.float().cuda()), L.tensor_arg(cu)
+    L.check(L.lib.cdl_b200_rope_ragged(L.ref(tx), L.ref(tt), 2, L.ref(tc), 0, None))
+    torch.cuda.synchronize()
+    lo = 0
+    for n_tok in seqlens:
+        ref = block_ref.rope(x.double()[None, lo:lo + n_tok, :2], table[:n_tok])[0]
+        assert rel_err(xd[lo:lo + n_tok, :2], ref) <= 2.0 ** -7
+        lo += n_tok
+    assert torch.equal(xd[:, 2], x.cuda()[:, 2])      # the third head is not rotated
+    assert torch.equal(xd[lo:], x.cuda()[lo:])        # padding rows are untouched
