@@ -1,7 +1,7 @@
 #!/usr/bin/env python
 """Benchmark of the hot path: sky-1 decoder block forward + backward, tokens/s.
 
-Workload (BASELINE config 4): hidden 2048, 16 heads x 128, RoPE, pre-RMSNorm, SwiGLU FFN 5632,
+Workload (benchmark configuration 4): hidden 2048, 16 heads x 128, RoPE, pre-RMSNorm, SwiGLU FFN 5632,
 batch 8 x seq 2048 per GPU, weights ~ N(0, 0.02) bf16, tokens uniform over a 32768-token vocabulary,
 seed 3.  One step = token embedding lookup -> block forward -> block backward (weight gradients
 accumulated in f32) for one batch; at N > 1 every rank runs its own batch (weak scaling, data
@@ -458,7 +458,7 @@ def run_kernel(args) -> None:
 
 # ------------------------------------------------------------------ full LM step (config 5)
 def run_lm(args) -> None:
-    """24-layer sky-1-style LM training step (BASELINE config 5): global batch 64 x 2048
+    """24-layer sky-1-style LM training step (benchmark configuration 5): global batch 64 x 2048
     uniform-random tokens split over the ranks, microbatches of 8 x 2048 with gradient
     accumulation, per-layer all-reduce overlapped with the backward, AdamW.  Prints one JSON
     line with tokens/s (device-timed, max over ranks) and the last loss."""
@@ -556,7 +556,7 @@ def main() -> None:
     ap.add_argument("--seq", type=int, default=2048)
     ap.add_argument("--heads", type=int, default=16)
     ap.add_argument("--workload", default="block", choices=["block", "lm"],
-                    help="block = BASELINE config 4 (the headline metric); lm = the 24-layer training step")
+                    help="block = benchmark configuration 4 (the headline metric); lm = the 24-layer training step")
     ap.add_argument("--layers", type=int, default=24)
     args = ap.parse_args()
     if args.workload == "lm":

@@ -197,7 +197,7 @@ class Sky1Block:
 # ======================================================================= full LM training step
 @dataclass
 class Sky1LMConfig:
-    """24-layer sky-1-style LM of BASELINE config 5 by default."""
+    """24-layer sky-1-style LM of benchmark configuration 5 by default."""
 
     block: Sky1Config
     layers: int = 24

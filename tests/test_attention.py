@@ -76,7 +76,7 @@ def test_fwd_large_logits_rescale(cdl, gpu_ok):
 
 
 def test_fwd_deterministic_and_sdpa_at_config3_shape(cdl, gpu_ok):
-    """BASELINE config 3 shape (B=8, H=16, S=2048, D=128, seed 2): the f64 oracle would need
+    """benchmark configuration 3 shape (B=8, H=16, S=2048, D=128, seed 2): the f64 oracle would need
     minutes, so the full size is compared with torch's fp32 attention on the GPU and one
     (batch, head) slice with the oracle."""
     gen = torch.Generator().manual_seed(2)
@@ -160,7 +160,7 @@ def test_bwd_fused_qkv_views(cdl, gpu_ok):
 
 
 def test_bwd_config3_shape_vs_torch_autograd(cdl, gpu_ok):
-    """BASELINE config 3 (B=8, H=16, S=2048, D=128, seed 2) against fp32 autograd through
+    """benchmark configuration 3 (B=8, H=16, S=2048, D=128, seed 2) against fp32 autograd through
     torch's attention on the same GPU for two batches, and one (batch, head) against the oracle."""
     gen = torch.Generator().manual_seed(2)
     q, k, v, do = (torch.randn(8, 2048, 16, 128, generator=gen).to(torch.bfloat16).cuda()

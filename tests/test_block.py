@@ -1,6 +1,6 @@
 """GPU parity of the sky-1 decoder block (forward + backward) against the float64 restatement of
 the reference's dataflow (oracle/block_ref.py), on reduced dimensions the CPU finishes in seconds,
-and of the elementwise kernels it uses.  Bound: BASELINE's 2e-2 of the largest magnitude for bf16
+and of the elementwise kernels it uses.  Bound: the acceptance bound of 2e-2 of the largest magnitude for bf16
 tensors produced by chains of bf16 GEMMs; gradients likewise."""
 import numpy as np
 import pytest

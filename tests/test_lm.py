@@ -1,6 +1,6 @@
 """GPU parity of the LM-step kernels (cross-entropy, embedding scatter-add, reduction, AdamW) and of
 a 50-step training run of a small sky-1-style LM against the torch restatement (oracle/lm_ref.py):
-BASELINE's bound is a loss curve within 1 % of the reference over 50 steps."""
+The acceptance bound is a loss curve within 1 % of the reference over 50 steps."""
 import ctypes
 
 import numpy as np
@@ -110,7 +110,7 @@ def _run_curve(cdl, cfg, batches, lr):
 
 
 def test_lm_loss_curve_50_steps_baseline_regime(cdl, gpu_ok):
-    """BASELINE config 5's regime at reduced size: fresh uniform-random tokens every step, AdamW
+    """benchmark configuration 5's regime at reduced size: fresh uniform-random tokens every step, AdamW
     lr 3e-4, betas (0.9, 0.95), wd 0.1, 50 steps; every loss within 1 % of the torch restatement."""
     cfg = small_lm(cdl)
     b = cfg.block

@@ -3,7 +3,7 @@
 Cases follow crates/cleandl/tests/matmul.rs: shapes and output types (:212-240), transposed views
 (:268-310), sliced views (:313-339), batched (:666-687), batched + transposed + C with alpha/beta
 (:632-663), accumulate into C (:690-725), K = 0 (:825-843), rejection messages (:355-468), with the
-tolerance of :199-202.  BASELINE's acceptance bound (max relative error 2e-2 against an
+tolerance of :199-202.  The acceptance bound of this build (max relative error 2e-2 against an
 f32-accumulated reference) is checked as well.
 """
 import numpy as np
@@ -37,7 +37,7 @@ def run_case(cdl, a, b, out_dtype, c=None, alpha=1.0, beta=0.0, in_place=False):
     expected, bound = oracle.matmul(to_f32(a), to_f32(b), None if c is None else to_f32(c), alpha, beta)
     tol = oracle.matmul_tolerance(expected, bound, out_dtype == torch.bfloat16)
     assert_all_close("matmul", to_f32(d), expected, tol)
-    # BASELINE bound: max relative error 2e-2 (relative to the largest magnitude of the output).
+    # Acceptance bound: max relative error 2e-2 (relative to the largest magnitude of the output).
     scale = max(float(np.abs(expected).max()), 1e-6)
     assert float(np.abs(to_f32(d) - expected).max()) / scale <= 2e-2
     return d

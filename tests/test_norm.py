@@ -3,7 +3,7 @@
 Forward cases and tolerances follow crates/cleandl/tests/norm.rs: inputs x ~ N(0.5, 2.0),
 scale ~ U(0.5, 1.5), bias ~ N(0, 1) (:220-228); specialized cases (:322-380); bf16 output within
 1e-5 + 2^-7 |e| (:261-268), r_inv within 1e-6 + 1e-4 |e| (:309-315); strided rows (:586-621).
-The backward has no reference test; it is held to BASELINE's 1e-2 bound and to the bf16 rounding
+The backward has no reference test; it is held to the acceptance bound of 1e-2 and to the bf16 rounding
 bound of the forward.
 """
 import numpy as np
@@ -55,7 +55,7 @@ def test_fwd_strided_rows_no_stats(cdl, gpu_ok):
 
 
 def test_fwd_config2_and_determinism(cdl, gpu_ok):
-    """BASELINE config 2: x[16384, 2048] ~ N(0,1), weight 1 + N(0, 0.02), eps 1e-6, seed 1."""
+    """benchmark configuration 2: x[16384, 2048] ~ N(0,1), weight 1 + N(0, 0.02), eps 1e-6, seed 1."""
     gen = torch.Generator().manual_seed(1)
     x = torch.randn(16384, 2048, generator=gen).to(torch.bfloat16)
     w = (1 + 0.02 * torch.randn(2048, generator=gen)).to(torch.bfloat16)
