@@ -205,7 +205,9 @@ __global__ void __launch_bounds__(THREADS, 1)
     attn_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap tmap_q,
                          const __grid_constant__ CUtensorMap tmap_k,
                          const __grid_constant__ CUtensorMap tmap_v,
-                         const __grid_constant__ CUtensorMap tmap_do, const Params p_in) {
+                         const __grid_constant__ CUtensorMap tmap_do,
+                         const __grid_constant__ CUtensorMap tmap_dk,
+                         const __grid_constant__ CUtensorMap tmap_dv, const Params p_in) {
   // Per-sequence view: in the packed layout a sequence has its own lengths and its rows start at
   // q_base / k_base of a single batch (bt = 0).  Rows a tile loads beyond its sequence belong to
   // the next one: keys beyond Sk are masked, queries beyond Sq carry lse2 = +inf (P = 0), and
@@ -519,12 +521,20 @@ __global__ void __launch_bounds__(THREADS, 1)
       tc_fence_after();
     }
     if (ok) {
+      // The tiles go out through shared memory and one TMA store per 64-column panel: a thread
+      // owns a row, so direct stores would touch 32 rows per instruction.  The Q stages are free
+      // (every product has completed); the panel layout is the loads' 128-byte swizzle.  A store
+      // clips rows beyond the tensor, not rows of the next packed sequence: a partial block of a
+      // packed sequence stores its rows directly.
+      const bool staged = p.cu_k == nullptr || key0 + BKV <= p.Sk;
       const bool row_ok = key < p.Sk;
       __nv_bfloat16* dv_row = p.dv + bt * p.dv_sb + static_cast<long long>(k_base + key) * p.dv_ss + kvh * p.dv_sh + wg * 64;
       __nv_bfloat16* dk_row = p.dk + bt * p.dk_sb + static_cast<long long>(k_base + key) * p.dk_ss + kvh * p.dk_sh + wg * 64;
 #pragma unroll
       for (int which = 0; which < 2; ++which) {
         __nv_bfloat16* dst = which == 0 ? dv_row : dk_row;
+        uint8_t* stage = s_q + which * TILE_BYTES;
+        uint8_t* stage_row = stage + wg * PANEL_BYTES + r * 128;
         const uint32_t col = (which == 0 ? KV_COL_DV : KV_COL_DK) + wg * 64;
 #pragma unroll
         for (int half = 0; half < 2; ++half) {
@@ -536,20 +546,32 @@ __global__ void __launch_bounds__(THREADS, 1)
 #pragma unroll
             for (int i = 0; i < 32; ++i) a[i] = 0u;
           }
-          if (row_ok) {
-            const float sc = which == 0 ? 1.0f : p.scale;  // dS^T was accumulated without the scale
+          const float sc = which == 0 ? 1.0f : p.scale;  // dS^T was accumulated without the scale
 #pragma unroll
-            for (int g = 0; g < 4; ++g) {
-              uint4 q;
-              q.x = pack_bf16x2(__uint_as_float(a[g * 8 + 0]) * sc, __uint_as_float(a[g * 8 + 1]) * sc);
-              q.y = pack_bf16x2(__uint_as_float(a[g * 8 + 2]) * sc, __uint_as_float(a[g * 8 + 3]) * sc);
-              q.z = pack_bf16x2(__uint_as_float(a[g * 8 + 4]) * sc, __uint_as_float(a[g * 8 + 5]) * sc);
-              q.w = pack_bf16x2(__uint_as_float(a[g * 8 + 6]) * sc, __uint_as_float(a[g * 8 + 7]) * sc);
+          for (int g = 0; g < 4; ++g) {
+            uint4 q;
+            q.x = pack_bf16x2(__uint_as_float(a[g * 8 + 0]) * sc, __uint_as_float(a[g * 8 + 1]) * sc);
+            q.y = pack_bf16x2(__uint_as_float(a[g * 8 + 2]) * sc, __uint_as_float(a[g * 8 + 3]) * sc);
+            q.z = pack_bf16x2(__uint_as_float(a[g * 8 + 4]) * sc, __uint_as_float(a[g * 8 + 5]) * sc);
+            q.w = pack_bf16x2(__uint_as_float(a[g * 8 + 6]) * sc, __uint_as_float(a[g * 8 + 7]) * sc);
+            if (staged)
+              *reinterpret_cast<uint4*>(stage_row + (((half * 4 + g) ^ (r & 7)) << 4)) = q;
+            else if (row_ok)
               *reinterpret_cast<uint4*>(dst + half * 32 + g * 8) = q;
-            }
+          }
+        }
+        if (staged) {
+          fence_proxy_async_smem();
+          compute_bar_sync();
+          if (ct == 0) {
+            const CUtensorMap* tm = which == 0 ? &tmap_dv : &tmap_dk;
+            tma_store_4d(tm, stage, 0, k_base + key0, kvh, bt);
+            tma_store_4d(tm, stage + PANEL_BYTES, 64, k_base + key0, kvh, bt);
+            tma_store_commit();
           }
         }
       }
+      if (staged && ct == 0) tma_store_wait_read<0>();  // shared memory is read before the CTA ends
     }
   }
 
@@ -581,7 +603,8 @@ __global__ void __launch_bounds__(THREADS, 1)
     attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmap_q,
                        const __grid_constant__ CUtensorMap tmap_k,
                        const __grid_constant__ CUtensorMap tmap_v,
-                       const __grid_constant__ CUtensorMap tmap_do, const Params p_in) {
+                       const __grid_constant__ CUtensorMap tmap_do,
+                       const __grid_constant__ CUtensorMap tmap_dq, const Params p_in) {
   extern __shared__ __align__(1024) uint8_t smem[];
   Params p = p_in;  // per-sequence view, as in the dK/dV kernel
   int q_base = 0, k_base = 0, bt = blockIdx.z;
@@ -811,7 +834,10 @@ __global__ void __launch_bounds__(THREADS, 1)
       tc_fence_after();
     }
     if (ok && q0 < p.Sq) {
+      // Through shared memory and TMA stores, as in the dK/dV kernel; the first K stage is free.
+      const bool staged = p.cu_q == nullptr || q0 + BQ <= p.Sq;
       __nv_bfloat16* dst = p.dq + bt * p.dq_sb + static_cast<long long>(q_base + row) * p.dq_ss + h * p.dq_sh + wg * 64;
+      uint8_t* stage_row = s_k + wg * PANEL_BYTES + r * 128;
 #pragma unroll
       for (int half = 0; half < 2; ++half) {
         uint32_t a[32];
@@ -822,17 +848,28 @@ __global__ void __launch_bounds__(THREADS, 1)
 #pragma unroll
           for (int i = 0; i < 32; ++i) a[i] = 0u;
         }
-        if (row < p.Sq) {
-          const float sc = p.scale;
+        const float sc = p.scale;
 #pragma unroll
-          for (int g = 0; g < 4; ++g) {
-            uint4 q;
-            q.x = pack_bf16x2(__uint_as_float(a[g * 8 + 0]) * sc, __uint_as_float(a[g * 8 + 1]) * sc);
-            q.y = pack_bf16x2(__uint_as_float(a[g * 8 + 2]) * sc, __uint_as_float(a[g * 8 + 3]) * sc);
-            q.z = pack_bf16x2(__uint_as_float(a[g * 8 + 4]) * sc, __uint_as_float(a[g * 8 + 5]) * sc);
-            q.w = pack_bf16x2(__uint_as_float(a[g * 8 + 6]) * sc, __uint_as_float(a[g * 8 + 7]) * sc);
+        for (int g = 0; g < 4; ++g) {
+          uint4 q;
+          q.x = pack_bf16x2(__uint_as_float(a[g * 8 + 0]) * sc, __uint_as_float(a[g * 8 + 1]) * sc);
+          q.y = pack_bf16x2(__uint_as_float(a[g * 8 + 2]) * sc, __uint_as_float(a[g * 8 + 3]) * sc);
+          q.z = pack_bf16x2(__uint_as_float(a[g * 8 + 4]) * sc, __uint_as_float(a[g * 8 + 5]) * sc);
+          q.w = pack_bf16x2(__uint_as_float(a[g * 8 + 6]) * sc, __uint_as_float(a[g * 8 + 7]) * sc);
+          if (staged)
+            *reinterpret_cast<uint4*>(stage_row + (((half * 4 + g) ^ (r & 7)) << 4)) = q;
+          else if (row < p.Sq)
             *reinterpret_cast<uint4*>(dst + half * 32 + g * 8) = q;
-          }
+        }
+      }
+      if (staged) {
+        fence_proxy_async_smem();
+        compute_bar_sync();
+        if (threadIdx.x == 128) {
+          tma_store_4d(&tmap_dq, s_k, 0, q_base + q0, h, bt);
+          tma_store_4d(&tmap_dq, s_k + PANEL_BYTES, 64, q_base + q0, h, bt);
+          tma_store_commit();
+          tma_store_wait_read<0>();
         }
       }
     }
@@ -866,6 +903,7 @@ size_t attn_bwd_scratch_bytes(long long B, long long Sq, long long H) {
 static int32_t bwd_run(const attn_bwd::Params& p, const cdl_tensor* q, const cdl_tensor* k,
                        const cdl_tensor* v, const cdl_tensor* o, const cdl_tensor* d_o,
                        const float* lse, long long lse_sb, long long lse_sh, long long lse_ss,
+                       const cdl_tensor* dq, const cdl_tensor* dk, const cdl_tensor* dv,
                        double work, cudaStream_t stream) {
   using namespace attn_bwd;
   static std::once_flag attr_once[64];
@@ -895,31 +933,37 @@ static int32_t bwd_run(const attn_bwd::Params& p, const cdl_tensor* q, const cdl
         p.H, p.Sq, p.Sq_pad, p.cu_q);
     CDL_CUDA(cudaGetLastError());
   }
-  CUtensorMap tq, tk, tv, tdo;
+  CUtensorMap tq, tk, tv, tdo, tdq, tdk, tdv;
   if (have_q) {
     CDL_CHECK(attn_encode_tmap(&tq, q));
     CDL_CHECK(attn_encode_tmap(&tdo, d_o));
+    CDL_CHECK(attn_encode_tmap(&tdq, dq));
   } else {
     memset(&tq, 0, sizeof tq);
     tdo = tq;
+    tdq = tq;
   }
   if (have_k) {
     CDL_CHECK(attn_encode_tmap(&tk, k));
     CDL_CHECK(attn_encode_tmap(&tv, v));
+    CDL_CHECK(attn_encode_tmap(&tdk, dk));
+    CDL_CHECK(attn_encode_tmap(&tdv, dv));
   } else {
     memset(&tk, 0, sizeof tk);
     tv = tk;
+    tdk = tk;
+    tdv = tk;
   }
   if (have_k) {
     dim3 grid(static_cast<unsigned>((Sk + BKV - 1) / BKV), static_cast<unsigned>(Hkv),
               static_cast<unsigned>(B));
-    attn_bwd_dkdv_kernel<<<grid, THREADS, KV_SMEM_BYTES, stream>>>(tq, tk, tv, tdo, p);
+    attn_bwd_dkdv_kernel<<<grid, THREADS, KV_SMEM_BYTES, stream>>>(tq, tk, tv, tdo, tdk, tdv, p);
     CDL_CUDA(cudaGetLastError());
   }
   if (have_q) {
     dim3 grid(static_cast<unsigned>((Sq + BQ - 1) / BQ), static_cast<unsigned>(H),
               static_cast<unsigned>(B));
-    attn_bwd_dq_kernel<<<grid, THREADS, Q_SMEM_BYTES, stream>>>(tq, tk, tv, tdo, p);
+    attn_bwd_dq_kernel<<<grid, THREADS, Q_SMEM_BYTES, stream>>>(tq, tk, tv, tdo, tdq, p);
     CDL_CUDA(cudaGetLastError());
   }
   return CDL_OK;
@@ -993,7 +1037,7 @@ int32_t attn_bwd_execute(const cdl_attn_desc* desc, const cdl_tensor* q, const c
   // 14 B H Sq Sk D with the recomputed S and dP of the dQ kernel; reported as the conventional
   // 10 B H Sq Sk D (2.5 x forward), halved for the causal mask.
   return bwd_run(p, q, k, v, o, d_o, static_cast<const float*>(lse->ptr), lse->stride[0],
-                 lse->stride[1], lse->stride[2], 10.0 * B * H * Sq * Sk * D * (p.causal ? 0.5 : 1.0),
+                 lse->stride[1], lse->stride[2], dq, dk, dv, 10.0 * B * H * Sq * Sk * D * (p.causal ? 0.5 : 1.0),
                  stream);
 }
 
@@ -1070,7 +1114,7 @@ int32_t attn_bwd_packed_execute(const cdl_attn_desc* desc, const cdl_tensor* q, 
   if (!p.status) return fail(CDL_ERR_CUDA, "cannot resolve the device status word");
   const double mean_q = static_cast<double>(Tq) / B, mean_k = static_cast<double>(Tk) / B;
   return bwd_run(p, &q4, &k4, &v4, &o4, &do4, static_cast<const float*>(lse->ptr), 0, lse->stride[0],
-                 lse->stride[1], 10.0 * B * H * mean_q * mean_k * D * (p.causal ? 0.5 : 1.0), stream);
+                 lse->stride[1], &dq4, &dk4, &dv4, 10.0 * B * H * mean_q * mean_k * D * (p.causal ? 0.5 : 1.0), stream);
 }
 
 }  // namespace cdl
