@@ -401,6 +401,27 @@ def run_kernel(args) -> None:
             work = (8.0 if args.residual else 6.0) * rows * cols + 6 * cols + 4 * rows
         unit, peak = "GB/s", peaks["hbm"]
         desc = f"{k} x[{rows},{cols}] bf16" + (" + residual gradient" if k == "norm_bwd" and args.residual else "")
+    elif k == "gemm_mx":
+        # D[m, n] = A[m, k] . B[k, n] with MXFP8 operands (quantised once, outside the timing)
+        m, n, kk = args.m, args.n, args.k
+        qa, _ = cdl.mx.quantize(rnd(m, kk), rowwise=True)
+        _, qb = cdl.mx.quantize(rnd(kk, n), rowwise=False, colwise=True)
+        d = torch.zeros(m, n, device=dev, dtype=torch.bfloat16)
+        fns = [lambda: cdl.mx.matmul_mx(qa, qb, out=d)]
+        work, unit, peak = 2.0 * m * n * kk, "TFLOP/s", peaks["bf16_burst"]
+        desc = f"gemm_mx (MXFP8 operands, bf16 out) {m}x{n}x{kk}"
+    elif k == "norm_fwd_mx":
+        rows, cols = args.rows, args.cols
+        nbuf = max(2, int(300e6 // (rows * cols * 2)) + 1)
+        xs = [rnd(rows, cols) for _ in range(nbuf)]
+        w = (1 + 0.02 * torch.randn(cols, device=dev, generator=gen)).to(torch.bfloat16)
+        outs = [cdl.mx.norm_fwd_mx(x, w, colwise=args.colwise, save_stats=True) for x in xs]
+        fns = [(lambda x=x, o=o: cdl.mx.norm_fwd_mx(x, w, colwise=args.colwise, save_stats=True, out=o))
+               for x, o in zip(xs, outs)]
+        n_out = 2 if args.colwise else 1
+        work = 2.0 * rows * cols + n_out * rows * cols * (1 + 1 / 32) + 2 * cols + 4 * rows
+        unit, peak = "GB/s", peaks["hbm"]
+        desc = f"norm_fwd_mx x[{rows},{cols}] bf16 -> MXFP8 rowwise" + (" + colwise" if args.colwise else "")
     else:
         bsz, s_, h = args.batch, args.seq, args.heads
         q, kx, v, do = (rnd(bsz, s_, h, 128) for _ in range(4))
@@ -442,7 +463,7 @@ def run_kernel(args) -> None:
     for i in range(args.steps):
         fns[i % len(fns)]()
     kind = {"gemm": "gemm", "norm_fwd": "norm_fwd", "norm_bwd": "norm_bwd", "attn_fwd": "attn_fwd",
-            "attn_bwd": "attn_bwd"}[k]
+            "attn_bwd": "attn_bwd", "gemm_mx": "gemm", "norm_fwd_mx": "norm_fwd"}[k]
     times = [ms_ for kd, ms_, _ in L.profile_stop(4 * args.steps + 16) if kd == kind]
     ms_events = sum(times) / len(times)
     assert L.device_status() == 0
@@ -540,7 +561,7 @@ def main() -> None:
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--kernel", default=None,
-                    choices=["gemm", "norm_fwd", "norm_bwd", "attn_fwd", "attn_bwd"],
+                    choices=["gemm", "norm_fwd", "norm_bwd", "attn_fwd", "attn_bwd", "gemm_mx", "norm_fwd_mx"],
                     help="time one operator alone instead of the block")
     ap.add_argument("--m", type=int, default=8192)
     ap.add_argument("--n", type=int, default=8192)
@@ -550,6 +571,8 @@ def main() -> None:
     ap.add_argument("--accumulate", action="store_true", help="gemm: D (f32) += A.B, the wgrad form")
     ap.add_argument("--residual", action="store_true",
                     help="norm_bwd: add a residual gradient into dx (the form the block uses)")
+    ap.add_argument("--colwise", action="store_true",
+                    help="norm_fwd_mx: also produce the colwise (transposed-block) output")
     ap.add_argument("--rows", type=int, default=16384)
     ap.add_argument("--cols", type=int, default=2048)
     ap.add_argument("--batch", type=int, default=8)

@@ -53,6 +53,15 @@ class CdlSky1Ragged(ctypes.Structure):
                 ("max_seqlen", ctypes.c_int32)]
 
 
+class CdlMxTensor(ctypes.Structure):
+    _fields_ = [("values", ctypes.c_void_p), ("scale_factors", ctypes.c_void_p),
+                ("format", ctypes.c_int32), ("dim", ctypes.c_int32),
+                ("rows", ctypes.c_int64), ("cols", ctypes.c_int64)]
+
+
+CDL_MXFP8, CDL_NVFP4 = 0, 1
+CDL_MX_ROWWISE, CDL_MX_COLWISE = 0, 1
+
 _BLOCK_PARAMS = ("norm1", "wqkv", "wo", "norm2", "wup", "wgate", "wdown")
 
 
@@ -77,6 +86,7 @@ if not LIB_PATH.exists():
 lib = ctypes.CDLL(str(LIB_PATH))
 
 _T = ctypes.POINTER(CdlTensor)
+_MX = ctypes.POINTER(CdlMxTensor)
 _vp = ctypes.c_void_p
 _sz = ctypes.c_size_t
 
@@ -99,6 +109,12 @@ SIGNATURES = {
     "cdl_b200_rmsnorm_bwd_static": ([_T, _T, _T, _T, _T, _T, _T, _vp], ctypes.c_int32),
     "cdl_b200_rmsnorm_bwd_scratch_bytes": ([ctypes.c_int64, ctypes.c_int64, ctypes.POINTER(_sz)],
                                            ctypes.c_int32),
+    "cdl_b200_mx_layout": ([ctypes.c_int32, ctypes.c_int32, ctypes.c_int64, ctypes.c_int64,
+                            ctypes.POINTER(_sz), ctypes.POINTER(_sz)], ctypes.c_int32),
+    "cdl_b200_mx_quantize": ([_T, _MX, _MX, _vp], ctypes.c_int32),
+    "cdl_b200_mx_dequantize": ([_MX, _T, _vp], ctypes.c_int32),
+    "cdl_b200_rmsnorm_fwd_mx": ([_T, _T, _T, ctypes.c_float, _MX, _MX, _T, _vp], ctypes.c_int32),
+    "cdl_b200_matmul_mx": ([_MX, _MX, _T, ctypes.c_float, _vp], ctypes.c_int32),
     "cdl_b200_attn_fwd": ([ctypes.POINTER(CdlAttnDesc), _T, _T, _T, _T, _T, _vp], ctypes.c_int32),
     "cdl_b200_attn_bwd": ([ctypes.POINTER(CdlAttnDesc), _T, _T, _T, _T, _T, _T, _T, _T, _T, _vp,
                            _sz, _vp], ctypes.c_int32),

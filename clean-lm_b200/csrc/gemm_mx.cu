@@ -1,0 +1,392 @@
+// Matmul with block-scaled (MXFP8) operands: D = alpha * dequant(A) . dequant(B), f32 accumulate.
+//
+// The reference forwards this case to cuBLASLt block scaling
+// (crates/cleandl/src/execgraph/ops/matmul.rs:808-838, InputKind::Mx; tests
+// crates/cleandl/tests/matmul.rs:1041-1060); its own block-scaled tcgen05 kernel generator is
+// crates/cleandl-specialized-kernels/src/kernels/matmul/tcgen05.rs.  A is rowwise [M, K], B is
+// colwise [K, N]: both value matrices are K-contiguous bytes, both scale tensors are in the
+// 128 x 4 tiled layout, which is what the hardware reads.
+//
+// Kernel: persistent, one CTA per SM, 128 x 256 output tiles, K in steps of 128 bytes (one
+// 128-byte swizzled row per operand row, four K = 32 instructions).  Per stage the producer warp
+// brings A (16 KiB) and B (32 KiB) with TMA and the three 512-byte scale tiles (one of A's 128
+// rows, two of B's 256) with bulk copies; the MMA thread copies the scale tiles into tensor
+// memory (tcgen05.cp, ordered with its MMAs) and issues
+// tcgen05.mma.kind::mxf8f6f4.block_scale, selecting the K block's scale byte in the instruction
+// descriptor.
+//
+// Tensor memory holds 512 columns: two 256-column accumulators do not fit beside the 12 scale
+// columns, so the accumulators OVERLAP by 16 columns (columns [0,256) and [240,496), scales at
+// [496,508)).  The epilogue of a tile drains the 16 shared columns first and signals; the first
+// MMA of the next tile waits for that signal only, so the rest of the epilogue still overlaps
+// the next tile's main loop.
+#include "host.h"
+#include "ops.h"
+#include "ptx.cuh"
+
+#include <mutex>
+
+namespace cdl {
+namespace gemm_mx {
+
+constexpr int BM = 128;
+constexpr int BN = 256;
+constexpr int BK = 128;  // elements == bytes
+constexpr int STAGES = 4;
+constexpr int A_BYTES = BM * BK;
+constexpr int B_BYTES = BN * BK;
+constexpr int SF_TILE = 512;  // scales of 128 rows x 4 blocks
+constexpr int SF_OFF = A_BYTES + B_BYTES;
+constexpr int STAGE_BYTES = 50 * 1024;  // A, B, 3 scale tiles, padded to keep stages 1024-aligned
+static_assert(SF_OFF + 3 * SF_TILE <= STAGE_BYTES, "stage layout");
+constexpr int THREADS = 320;  // warp 0 TMA, warp 1 MMA, warps 2-9 epilogue
+constexpr int EPI_WARPS = 8;
+constexpr int TMEM_COLS = 512;
+constexpr int ACC1_COL = 240;  // accumulator 0 starts at column 0, accumulator 1 here
+constexpr int SFA_COL = 496, SFB_COL = 500;
+constexpr int RASTER_W = 8;
+constexpr size_t SMEM_BYTES = 1024 + STAGES * STAGE_BYTES + 256;
+static_assert(SMEM_BYTES <= 232448, "exceeds the 227 KiB of shared memory a CTA can opt in to");
+
+struct Params {
+  int M, N, K;
+  int num_m_tiles, num_n_tiles, num_tiles, k_tiles;
+  const uint8_t* sfa;  // scale tiles of A: [ceil(M/128)][sf_k_tiles][512]
+  const uint8_t* sfb;  // scale tiles of B: [ceil(N/128)][sf_k_tiles][512]
+  int sf_k_tiles;      // ceil(K / 128)
+  void* d;
+  long long ldd;
+  int out_f32, wide;
+  float alpha;
+  int* status;
+};
+
+struct Barriers {
+  uint64_t full[STAGES];
+  uint64_t empty[STAGES];
+  uint64_t acc_full[2];
+  uint64_t acc_empty[2];
+  uint64_t overlap_free;
+  uint32_t tmem_base;
+  int abort_word;
+};
+
+__device__ __forceinline__ void tile_coords(const Params& p, int tile, int& m, int& n) {
+  const int panel_tiles = RASTER_W * p.num_m_tiles;
+  const int panel = tile / panel_tiles;
+  const int first_n = panel * RASTER_W;
+  const int width = min(RASTER_W, p.num_n_tiles - first_n);
+  const int r = tile - panel * panel_tiles;
+  m = r / width;
+  n = first_n + (r - m * width);
+}
+
+// 32 consecutive columns of one output row.
+__device__ __forceinline__ void store32(const Params& p, const uint32_t (&r)[32], int row, int col0) {
+  float v[32];
+#pragma unroll
+  for (int j = 0; j < 32; ++j) v[j] = p.alpha * __uint_as_float(r[j]);
+  const bool full = col0 + 32 <= p.N;
+  if (p.out_f32) {
+    float* dp = static_cast<float*>(p.d) + static_cast<long long>(row) * p.ldd + col0;
+    if (p.wide && full) {
+#pragma unroll
+      for (int g = 0; g < 4; ++g) {
+        uint32_t w[8];
+#pragma unroll
+        for (int j = 0; j < 8; ++j) w[j] = __float_as_uint(v[g * 8 + j]);
+        st_global_v8(dp + g * 8, w);
+      }
+    } else {
+#pragma unroll
+      for (int j = 0; j < 32; ++j)
+        if (col0 + j < p.N) dp[j] = v[j];
+    }
+  } else {
+    __nv_bfloat16* dp = static_cast<__nv_bfloat16*>(p.d) + static_cast<long long>(row) * p.ldd + col0;
+    if (p.wide && full) {
+#pragma unroll
+      for (int g = 0; g < 2; ++g) {
+        uint32_t w[8];
+#pragma unroll
+        for (int j = 0; j < 8; ++j) w[j] = pack_bf16x2(v[g * 16 + 2 * j], v[g * 16 + 2 * j + 1]);
+        st_global_v8(dp + g * 16, w);
+      }
+    } else {
+#pragma unroll
+      for (int j = 0; j < 32; ++j)
+        if (col0 + j < p.N) dp[j] = __float2bfloat16_rn(v[j]);
+    }
+  }
+}
+
+__global__ void __launch_bounds__(THREADS, 1)
+    gemm_mxfp8_kernel(const __grid_constant__ CUtensorMap tmap_a,
+                      const __grid_constant__ CUtensorMap tmap_b, const Params p) {
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) &
+                                             ~static_cast<uintptr_t>(1023));
+  Barriers* bars = reinterpret_cast<Barriers*>(smem + STAGES * STAGE_BYTES);
+  volatile int* abort_word = &bars->abort_word;
+
+  const int warp = threadIdx.x >> 5;
+  const int lane = threadIdx.x & 31;
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < STAGES; ++s) {
+      mbar_init(&bars->full[s], 1);
+      mbar_init(&bars->empty[s], 1);
+    }
+    for (int i = 0; i < 2; ++i) {
+      mbar_init(&bars->acc_full[i], 1);
+      mbar_init(&bars->acc_empty[i], EPI_WARPS);
+    }
+    mbar_init(&bars->overlap_free, 4);
+    bars->abort_word = 0;
+    fence_mbar_init();
+  }
+  if (warp == 1) {
+    tmem_alloc(&bars->tmem_base, TMEM_COLS);
+    tmem_relinquish();
+  }
+  if (warp == 0 && lane == 0) {
+    tma_prefetch_desc(&tmap_a);
+    tma_prefetch_desc(&tmap_b);
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = bars->tmem_base;
+
+  if (warp == 0) {
+    // ------------------------------------------------------------ producer
+    if (elect_one()) {
+      uint32_t it = 0;
+      bool ok = true;
+      for (int tile = blockIdx.x; tile < p.num_tiles && ok; tile += gridDim.x) {
+        int tm, tn;
+        tile_coords(p, tile, tm, tn);
+        const int m0 = tm * BM, n0 = tn * BN;
+        // The second scale tile of B exists only if the tensor has rows beyond n0 + 128.
+        const bool sfb2 = n0 + 128 < p.N;
+        const uint8_t* sfa_row = p.sfa + static_cast<long long>(tm) * p.sf_k_tiles * SF_TILE;
+        const uint8_t* sfb_row = p.sfb + static_cast<long long>(2 * tn) * p.sf_k_tiles * SF_TILE;
+        for (int kt = 0; kt < p.k_tiles; ++kt, ++it) {
+          const int s = it % STAGES;
+          const uint32_t ph = (it / STAGES) & 1;
+          if (!mbar_wait(&bars->empty[s], ph ^ 1, abort_word, 401)) {
+            ok = false;
+            break;
+          }
+          uint8_t* sa = smem + s * STAGE_BYTES;
+          uint8_t* sb = sa + A_BYTES;
+          uint8_t* ssf = sa + SF_OFF;
+          mbar_arrive_expect_tx(&bars->full[s], A_BYTES + B_BYTES + (sfb2 ? 3 : 2) * SF_TILE);
+          const int k0 = kt * BK;
+          tma_load_3d(sa, &tmap_a, &bars->full[s], k0, m0, 0);
+          tma_load_3d(sb, &tmap_b, &bars->full[s], k0, n0, 0);
+          bulk_load_1d(ssf, sfa_row + static_cast<long long>(kt) * SF_TILE, SF_TILE, &bars->full[s]);
+          bulk_load_1d(ssf + SF_TILE, sfb_row + static_cast<long long>(kt) * SF_TILE, SF_TILE,
+                       &bars->full[s]);
+          if (sfb2)
+            bulk_load_1d(ssf + 2 * SF_TILE,
+                         sfb_row + (static_cast<long long>(p.sf_k_tiles) + kt) * SF_TILE, SF_TILE,
+                         &bars->full[s]);
+        }
+      }
+    }
+  } else if (warp == 1) {
+    // ------------------------------------------------------------ MMA issuer
+    if (elect_one()) {
+      uint32_t it = 0;
+      int t = 0;
+      bool ok = true;
+      const uint32_t sfa_t = tmem_base + SFA_COL, sfb_t = tmem_base + SFB_COL;
+      for (int tile = blockIdx.x; tile < p.num_tiles && ok; tile += gridDim.x, ++t) {
+        const int acc = t & 1;
+        const uint32_t acc_ph = (t >> 1) & 1;
+        if (!mbar_wait(&bars->acc_empty[acc], acc_ph ^ 1, abort_word, 402)) break;
+        // the columns this accumulator shares with the previous tile's have been drained
+        if (t > 0 && !mbar_wait(&bars->overlap_free, (t - 1) & 1, abort_word, 403)) break;
+        tc_fence_after();
+        const uint32_t d_tmem = tmem_base + acc * ACC1_COL;
+        for (int kt = 0; kt < p.k_tiles; ++kt, ++it) {
+          const int s = it % STAGES;
+          const uint32_t ph = (it / STAGES) & 1;
+          if (!mbar_wait(&bars->full[s], ph, abort_word, 404)) {
+            ok = false;
+            break;
+          }
+          tc_fence_after();
+          const uint32_t sa = smem_u32(smem + s * STAGE_BYTES);
+          const uint32_t sb = sa + A_BYTES;
+          const uint32_t ssf = sa + SF_OFF;
+          tmem_cp_32x128b_warpx4(sfa_t, smem_desc_rows16(ssf));
+          tmem_cp_32x128b_warpx4(sfb_t, smem_desc_rows16(ssf + SF_TILE));
+          tmem_cp_32x128b_warpx4(sfb_t + 4, smem_desc_rows16(ssf + 2 * SF_TILE));
+          const int kblocks = min(4, (p.K - kt * BK) / 32);  // K % 32 == 0; the tail has fewer
+#pragma unroll
+          for (int k = 0; k < 4; ++k) {
+            if (k < kblocks) {
+              const uint64_t da = smem_desc_sw128(sa + k * 32, 16, 1024);
+              const uint64_t db = smem_desc_sw128(sb + k * 32, 16, 1024);
+              umma_mxf8_ss(d_tmem, da, db, make_idesc_mxf8(BM, BN, k, k), sfa_t, sfb_t,
+                           (kt | k) != 0 ? 1u : 0u);
+            }
+          }
+          umma_commit(&bars->empty[s]);
+        }
+        if (ok) umma_commit(&bars->acc_full[acc]);
+      }
+    }
+  } else {
+    // ------------------------------------------------------------ epilogue (warps 2..9)
+    const int quad = warp & 3;         // TMEM lane quadrant this warp may read
+    const int half = (warp - 2) >> 2;  // which 128 of the tile's 256 columns
+    int t = 0;
+    for (int tile = blockIdx.x; tile < p.num_tiles; tile += gridDim.x, ++t) {
+      int tm, tn;
+      tile_coords(p, tile, tm, tn);
+      const int acc = t & 1;
+      const uint32_t acc_ph = (t >> 1) & 1;
+      if (!mbar_wait(&bars->acc_full[acc], acc_ph, abort_word, 405)) break;
+      tc_fence_after();
+      const uint32_t t_row = tmem_base + (static_cast<uint32_t>(quad * 32) << 16) + acc * ACC1_COL + half * 128;
+      const int row = tm * BM + quad * 32 + lane;
+      const int col_base = tn * BN + half * 128;
+      // The 16 columns shared with the other accumulator are the last of accumulator 0 (its
+      // second half's chunk 3) and the first of accumulator 1 (its first half's chunk 0): the
+      // half that owns them reads that chunk first and frees the columns.
+      const bool owner = half == (acc == 0 ? 1 : 0);
+      const int first = (owner && acc == 0) ? 3 : 0;
+#pragma unroll 1
+      for (int i = 0; i < 4; ++i) {
+        const int ch = (first + i) & 3;
+        uint32_t r[32];
+        tmem_ld32(t_row + ch * 32, r);
+        tmem_wait_ld();
+        if (i == 0 && owner) {
+          tc_fence_before();
+          __syncwarp();
+          if (lane == 0) mbar_arrive(&bars->overlap_free);
+        }
+        const int col0 = col_base + ch * 32;
+        if (row < p.M && col0 < p.N) store32(p, r, row, col0);
+      }
+      tc_fence_before();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(&bars->acc_empty[acc]);
+    }
+  }
+
+  // ------------------------------------------------------------ tear-down
+  __syncwarp();
+  if (*abort_word != 0) {
+    // Give loads that may still be in flight time to land before shared memory is released.
+    const unsigned long long t0 = globaltimer_ns();
+    while (globaltimer_ns() - t0 < 200000ull) __nanosleep(1000);
+  }
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 1) {
+    tc_fence_after();
+    tmem_dealloc(tmem_base, TMEM_COLS);
+  }
+  if (threadIdx.x == 0 && *abort_word != 0) atomicExch(p.status, *abort_word);
+}
+
+}  // namespace gemm_mx
+
+int32_t matmul_mx_execute(const cdl_mx_tensor* a, const cdl_mx_tensor* b, const cdl_tensor* d,
+                          float alpha, cudaStream_t stream) {
+  using namespace gemm_mx;
+  const char* op = "matmul (mxfp8)";
+  if (!a || !b || !d) return fail(CDL_ERR_INVALID, "%s: a, b and d are required", op);
+  if (a->format != CDL_MXFP8 || b->format != CDL_MXFP8)
+    return fail(CDL_ERR_UNSUPPORTED, "%s: only MXFP8 operands are implemented", op);
+  if (a->dim != CDL_MX_ROWWISE)
+    return fail(CDL_ERR_INVALID,
+                "%s: block-scaled A must have its blocks along the contraction dimension (rowwise)", op);
+  if (b->dim != CDL_MX_COLWISE)
+    return fail(CDL_ERR_INVALID,
+                "%s: block-scaled B must have its blocks along the contraction dimension (colwise)", op);
+  const long long M = a->rows, K = a->cols, N = b->cols;
+  if (b->rows != K)
+    return fail(CDL_ERR_INVALID, "%s: contraction dimensions differ: A is [%lld, %lld], B is [%lld, %lld]",
+                op, M, K, static_cast<long long>(b->rows), N);
+  CDL_CHECK(mx_check(op, "a", a, CDL_MX_ROWWISE, M, K));
+  CDL_CHECK(mx_check(op, "b", b, CDL_MX_COLWISE, K, N));
+  if (d->rank != 2 || d->shape[0] != M || d->shape[1] != N)
+    return fail(CDL_ERR_INVALID, "%s: d must have shape [%lld, %lld]", op, M, N);
+  if (d->dtype != CDL_BF16 && d->dtype != CDL_F32)
+    return fail(CDL_ERR_UNSUPPORTED, "%s: the output must be f32 or bf16", op);
+  if (N > 1 && d->stride[1] != 1)
+    return fail(CDL_ERR_UNSUPPORTED, "%s: d must have contiguous rows", op);
+  if (M == 0 || N == 0) return CDL_OK;
+  if (K == 0) return fail(CDL_ERR_INVALID, "%s: K is zero", op);
+  if (M > (1 << 30) || N > (1 << 30) || K > (1 << 30))
+    return fail(CDL_ERR_UNSUPPORTED, "%s: dimension too large", op);
+  if ((reinterpret_cast<uintptr_t>(d->ptr) & (dtype_size(d->dtype) - 1)) != 0)
+    return fail(CDL_ERR_INVALID, "%s: d is not aligned to its element size", op);
+
+  static std::once_flag attr_once[64];
+  int dev = 0;
+  CDL_CUDA(cudaGetDevice(&dev));
+  cudaError_t attr_err = cudaSuccess;
+  std::call_once(attr_once[dev & 63], [&] {
+    attr_err = cudaFuncSetAttribute(gemm_mxfp8_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                    static_cast<int>(SMEM_BYTES));
+  });
+  if (attr_err != cudaSuccess)
+    return fail(CDL_ERR_CUDA, "cudaFuncSetAttribute failed: %s", cudaGetErrorString(attr_err));
+
+  Params p{};
+  p.M = static_cast<int>(M);
+  p.N = static_cast<int>(N);
+  p.K = static_cast<int>(K);
+  p.num_m_tiles = static_cast<int>((M + BM - 1) / BM);
+  p.num_n_tiles = static_cast<int>((N + BN - 1) / BN);
+  p.num_tiles = p.num_m_tiles * p.num_n_tiles;
+  p.k_tiles = static_cast<int>((K + BK - 1) / BK);
+  p.sf_k_tiles = p.k_tiles;  // ceil((K / 32) / 4)
+  p.sfa = static_cast<const uint8_t*>(a->scale_factors);
+  p.sfb = static_cast<const uint8_t*>(b->scale_factors);
+  p.d = d->ptr;
+  p.ldd = d->stride[0];
+  p.out_f32 = d->dtype == CDL_F32;
+  p.wide = (reinterpret_cast<uintptr_t>(d->ptr) & 31) == 0 &&
+           (M == 1 || (d->stride[0] * dtype_size(d->dtype)) % 32 == 0);
+  p.alpha = alpha;
+  p.status = device_status_ptr();
+  if (!p.status) return fail(CDL_ERR_CUDA, "cannot resolve the device status word");
+
+  CUtensorMap ta, tb;
+  {
+    const uint64_t dims[3] = {static_cast<uint64_t>(K), static_cast<uint64_t>(M), 1};
+    const uint64_t strides[3] = {1, static_cast<uint64_t>(K), static_cast<uint64_t>(K) * M};
+    const uint32_t box[3] = {BK, BM, 1};
+    CDL_CHECK(encode_tmap(&ta, a->values, TMAP_U8, 3, dims, strides, box, true));
+  }
+  {
+    const uint64_t dims[3] = {static_cast<uint64_t>(K), static_cast<uint64_t>(N), 1};
+    const uint64_t strides[3] = {1, static_cast<uint64_t>(K), static_cast<uint64_t>(K) * N};
+    const uint32_t box[3] = {BK, BN, 1};
+    CDL_CHECK(encode_tmap(&tb, b->values, TMAP_U8, 3, dims, strides, box, true));
+  }
+  const int grid = p.num_tiles < sm_count() ? p.num_tiles : sm_count();
+  ProfileScope ps(PROF_GEMM, 2.0 * M * N * K, stream);
+  gemm_mxfp8_kernel<<<grid, THREADS, SMEM_BYTES, stream>>>(ta, tb, p);
+  CDL_CUDA(cudaGetLastError());
+  return CDL_OK;
+}
+
+}  // namespace cdl
+
+extern "C" {
+
+int32_t cdl_b200_matmul_mx(const cdl_mx_tensor* a, const cdl_mx_tensor* b, const cdl_tensor* d,
+                           float alpha, cdl_stream stream) {
+  return cdl::matmul_mx_execute(a, b, d, alpha, static_cast<cudaStream_t>(stream));
+}
+
+}  // extern "C"

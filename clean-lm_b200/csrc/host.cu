@@ -89,8 +89,9 @@ int32_t encode_tmap(CUtensorMap* out, const void* base, int32_t dtype, int rank,
     estr[i] = 1;
     if (i > 0) gstr[i - 1] = strides_bytes[i];
   }
-  CUtensorMapDataType dt =
-      dtype == CDL_BF16 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT32;
+  CUtensorMapDataType dt = dtype == CDL_BF16 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16
+                           : dtype == TMAP_U8  ? CU_TENSOR_MAP_DATA_TYPE_UINT8
+                                               : CU_TENSOR_MAP_DATA_TYPE_FLOAT32;
   CUresult r = fn(out, dt, static_cast<cuuint32_t>(rank), const_cast<void*>(base), gdim, gstr, bx,
                   estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
                   swizzle128 ? CU_TENSOR_MAP_SWIZZLE_128B : CU_TENSOR_MAP_SWIZZLE_NONE,

@@ -42,7 +42,10 @@ int* device_status_ptr();  // device address for the current device; nullptr on 
 // The number of SMs of the current device (cached per device).
 int sm_count();
 
-// Encodes a tiled tensor map over bf16/f32 data.  dims/strides are innermost-first; strides are
+// Element type of a tensor map over bytes (block-scaled FP8 values); not a cdl_dtype.
+constexpr int32_t TMAP_U8 = 100;
+
+// Encodes a tiled tensor map over bf16 / f32 / byte data.  dims/strides are innermost-first; strides are
 // in BYTES for dims 1.. (the innermost is contiguous).  box is innermost-first.
 int32_t encode_tmap(CUtensorMap* out, const void* base, int32_t dtype, int rank,
                     const uint64_t* dims, const uint64_t* strides_bytes, const uint32_t* box,

@@ -1,0 +1,409 @@
+// Block-scaled (MXFP8) tensors: layout, quantisation, and RMSNorm with block-scaled outputs.
+//
+// Format (crates/cleandl/src/mx_tensor.rs:11-20, 339-372): a 2-D tensor whose blocks of 32
+// elements along the block dimension share one UE8M0 scale 2^(e - 127); values are FP8 E4M3.
+// Rowwise: blocks run along a row, values are a packed [rows, cols] byte matrix.  Colwise: blocks
+// run down a column, values are the packed TRANSPOSE [cols, rows].  Scale factors live in the
+// 128 x 4 tiled, partition-swizzled layout tcgen05 block-scaled MMAs read
+// (crates/cleandl-specialized-kernels/src/utils/block_scale.rs:70-80): the scale of block
+// (outer o, block b) is byte  ((o / 128) * ceil(B / 4) + b / 4) * 512 + (o % 32) * 16 +
+// ((o % 128) / 32) * 4 + b % 4,  with B blocks per outer index; the buffer is padded to
+// 128 outer rows x 4 blocks.
+//
+// Quantisation follows the reference's norm kernel (block_scale.rs:24-55): the value is rounded
+// to bf16, the scale is amax / 448 rounded UP to a power of two, the element is value * 2^-e
+// rounded to nearest E4M3 with saturation.  The division is exact here (the reference uses an
+// approximate one), which makes the result a pure function of the bf16 values.
+//
+// NormFwd with NormOutput::{Mxfp8Rowwise, Mxfp8RowwiseAndColwise}
+// (crates/cleandl/src/execgraph/ops/norm/mod.rs:33-62, kernel
+// crates/cleandl-specialized-kernels/src/kernels/norm/forward.rs:509-785): HBM-bound.  One warp
+// owns a row; a lane holds 8 consecutive bf16 of every 256-column stripe, so the four lanes of a
+// 32-element block reduce their amax with two shuffles.  With the colwise output a CTA owns 32
+// consecutive rows (one warp each): the bf16 results of 1024 columns go through shared memory and
+// one thread per column quantises the 32 rows of its block and stores one 32-byte sector of the
+// transposed output.  NVFP4 is not implemented.
+#include "host.h"
+#include "ops.h"
+#include "ptx.cuh"
+
+#include <cuda_fp8.h>
+
+#include <mutex>
+
+namespace cdl {
+namespace mx {
+
+constexpr int BLOCK = 32;
+constexpr int COL_GROUP = 1024;            // columns staged per colwise phase (4 stripes)
+constexpr int TILE_LD = COL_GROUP + 8;     // bf16 elements per staged row (16-byte aligned rows)
+constexpr size_t COL_SMEM_BYTES = 32 * TILE_LD * 2;
+
+struct Params {
+  const __nv_bfloat16* x;
+  long long ldx;
+  int rows, cols;
+  const __nv_bfloat16* gamma;  // nullable
+  const __nv_bfloat16* beta;   // nullable
+  float eps;
+  float* r_inv;  // nullable
+  long long r_inv_stride;
+  uint8_t* row_values;  // [rows, cols]; nullable
+  uint8_t* row_sf;
+  uint8_t* col_values;  // [cols, rows]; nullable
+  uint8_t* col_sf;
+};
+
+__device__ __forceinline__ long long sf_index(int outer, int block, int blocks) {
+  return (static_cast<long long>(outer >> 7) * ((blocks + 3) >> 2) + (block >> 2)) * 512 +
+         (outer & 31) * 16 + ((outer & 127) >> 5) * 4 + (block & 3);
+}
+
+// Biased exponent e of the smallest power of two s = 2^(e - 127) with amax / s <= 448.
+__device__ __forceinline__ uint32_t scale_exponent(float amax) {
+  const uint32_t bits = __float_as_uint(__fdiv_rn(amax, 448.0f));
+  uint32_t e = (bits + 0x7FFFFFu) >> 23;  // round the quotient up to a power of two
+  return e > 254u ? 254u : e;
+}
+// 2^(127 - e), exact (a subnormal for e = 254).
+__device__ __forceinline__ float descale_of(uint32_t e) {
+  const uint32_t de = 254u - e;
+  return __uint_as_float(de != 0 ? de << 23 : 0x00400000u);
+}
+__device__ __forceinline__ uint32_t fp8x4(float a, float b, float c, float d) {
+  const uint32_t lo = __nv_cvt_float2_to_fp8x2(make_float2(a, b), __NV_SATFINITE, __NV_E4M3);
+  const uint32_t hi = __nv_cvt_float2_to_fp8x2(make_float2(c, d), __NV_SATFINITE, __NV_E4M3);
+  return lo | (hi << 16);
+}
+__device__ __forceinline__ float bf16_round(float v) {
+  return __bfloat162float(__float2bfloat16_rn(v));
+}
+__device__ __forceinline__ void unpack8(const uint4& q, float (&f)[8]) {
+  f[0] = bf16_lo(q.x); f[1] = bf16_hi(q.x); f[2] = bf16_lo(q.y); f[3] = bf16_hi(q.y);
+  f[4] = bf16_lo(q.z); f[5] = bf16_hi(q.z); f[6] = bf16_lo(q.w); f[7] = bf16_hi(q.w);
+}
+
+// NORM: y = x * r * gamma + beta with r = rsqrt(mean x^2 + eps); otherwise y = x.
+// COL: the CTA has 32 warps and owns rows [32 * blockIdx.x, +32); otherwise any number of warps,
+// each striding over rows.
+template <bool NORM, bool COL>
+__global__ void __launch_bounds__(COL ? 1024 : 256, 1) mx_rows_kernel(const Params p) {
+  extern __shared__ __align__(16) uint8_t smem_raw[];
+  __nv_bfloat16* tile = reinterpret_cast<__nv_bfloat16*>(smem_raw);  // [32][TILE_LD] (COL only)
+  const int lane = threadIdx.x & 31;
+  const int warp = threadIdx.x >> 5;
+  const int warps = blockDim.x >> 5;
+  const int row_blocks = p.cols / BLOCK;  // blocks per row (rowwise)
+  const int col_blocks = p.rows / BLOCK;  // blocks per column (colwise)
+  const float inv_cols = 1.0f / static_cast<float>(p.cols);
+
+  const long long row_step = COL ? static_cast<long long>(gridDim.x) * 32
+                                 : static_cast<long long>(gridDim.x) * warps;
+  for (long long row0 = COL ? static_cast<long long>(blockIdx.x) * 32
+                            : static_cast<long long>(blockIdx.x) * warps;
+       row0 < p.rows; row0 += row_step) {
+    const long long row = row0 + warp;
+    const bool row_ok = row < p.rows;
+    const __nv_bfloat16* xr = p.x + row * p.ldx;
+    float r = 1.0f;
+    if (NORM && row_ok) {
+      float ss = 0.f;
+      for (int c = lane * 8; c < p.cols; c += 256) {
+        float f[8];
+        unpack8(*reinterpret_cast<const uint4*>(xr + c), f);
+#pragma unroll
+        for (int j = 0; j < 8; ++j) ss = fmaf(f[j], f[j], ss);
+      }
+#pragma unroll
+      for (int o = 16; o > 0; o >>= 1) ss += __shfl_xor_sync(0xffffffffu, ss, o);
+      r = rsqrtf(ss * inv_cols + p.eps);
+      if (lane == 0 && p.r_inv != nullptr) p.r_inv[row * p.r_inv_stride] = r;
+    }
+
+    for (int g0 = 0; g0 < p.cols; g0 += COL_GROUP) {
+      const int g_cols = min(COL_GROUP, p.cols - g0);
+      // ---- a warp's row: results of up to four stripes, rowwise output, staging for colwise
+      if (row_ok) {
+        for (int c0 = g0; c0 < g0 + g_cols; c0 += 256) {  // warp-uniform: the shuffles need all lanes
+          const int c = c0 + lane * 8;
+          const bool active = c < g0 + g_cols;
+          float f[8];
+#pragma unroll
+          for (int j = 0; j < 8; ++j) f[j] = 0.f;
+          if (active) {
+            unpack8(*reinterpret_cast<const uint4*>(xr + c), f);
+            if (NORM) {
+              float gm[8], bt[8];
+              if (p.gamma != nullptr) unpack8(*reinterpret_cast<const uint4*>(p.gamma + c), gm);
+              if (p.beta != nullptr) unpack8(*reinterpret_cast<const uint4*>(p.beta + c), bt);
+#pragma unroll
+              for (int j = 0; j < 8; ++j) {
+                float v = f[j] * r;
+                if (p.gamma != nullptr) v *= gm[j];
+                if (p.beta != nullptr) v += bt[j];
+                f[j] = bf16_round(v);
+              }
+            }
+            if (COL) {
+              uint4 q;
+              q.x = pack_bf16x2(f[0], f[1]); q.y = pack_bf16x2(f[2], f[3]);
+              q.z = pack_bf16x2(f[4], f[5]); q.w = pack_bf16x2(f[6], f[7]);
+              *reinterpret_cast<uint4*>(tile + warp * TILE_LD + (c - g0)) = q;
+            }
+          }
+          if (p.row_values != nullptr) {
+            // the four lanes of a 32-element block are all active or all idle (cols % 32 == 0)
+            float amax = 0.f;
+#pragma unroll
+            for (int j = 0; j < 8; ++j) amax = fmaxf(amax, fabsf(f[j]));
+            amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, 1));
+            amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, 2));
+            if (active) {
+              const uint32_t e = scale_exponent(amax);
+              const float ds = descale_of(e);
+              uint2 out;
+              out.x = fp8x4(f[0] * ds, f[1] * ds, f[2] * ds, f[3] * ds);
+              out.y = fp8x4(f[4] * ds, f[5] * ds, f[6] * ds, f[7] * ds);
+              *reinterpret_cast<uint2*>(p.row_values + row * p.cols + c) = out;
+              if ((lane & 3) == 0)
+                p.row_sf[sf_index(static_cast<int>(row), c / BLOCK, row_blocks)] = static_cast<uint8_t>(e);
+            }
+          }
+        }
+      }
+      if (COL) {
+        __syncthreads();
+        const int c = threadIdx.x;
+        if (c < g_cols) {
+          // rows % 32 == 0: all 32 staged rows exist
+          float v[32];
+          float amax = 0.f;
+#pragma unroll
+          for (int j = 0; j < 32; ++j) {
+            v[j] = __bfloat162float(tile[j * TILE_LD + c]);
+            amax = fmaxf(amax, fabsf(v[j]));
+          }
+          const uint32_t e = scale_exponent(amax);
+          const float ds = descale_of(e);
+          uint32_t w[8];
+#pragma unroll
+          for (int j = 0; j < 8; ++j)
+            w[j] = fp8x4(v[4 * j] * ds, v[4 * j + 1] * ds, v[4 * j + 2] * ds, v[4 * j + 3] * ds);
+          st_global_v8(p.col_values + static_cast<long long>(g0 + c) * p.rows + row0, w);
+          p.col_sf[sf_index(g0 + c, static_cast<int>(row0 / BLOCK), col_blocks)] = static_cast<uint8_t>(e);
+        }
+        __syncthreads();
+      }
+    }
+  }
+}
+
+// One thread per block of 32 values: y[r, c] = value * 2^(e - 127).
+__global__ void mx_dequantize_kernel(const uint8_t* __restrict__ values,
+                                     const uint8_t* __restrict__ sf, int outer, int inner,
+                                     int colwise, void* y, int y_f32, long long ldy) {
+  const int blocks = inner / BLOCK;
+  const long long idx = static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x;
+  if (idx >= static_cast<long long>(outer) * blocks) return;
+  const int o = static_cast<int>(idx / blocks), b = static_cast<int>(idx % blocks);
+  const uint32_t e = sf[sf_index(o, b, blocks)];
+  const float s = e == 0xFFu ? __int_as_float(0x7FC00000)
+                             : __uint_as_float(e != 0 ? e << 23 : 0x00400000u);
+  const uint8_t* src = values + static_cast<long long>(o) * inner + b * BLOCK;
+  for (int j = 0; j < BLOCK; ++j) {
+    const __half_raw h = __nv_cvt_fp8_to_halfraw(src[j], __NV_E4M3);
+    const float v = __half2float(__half(h)) * s;
+    const long long r = colwise ? b * BLOCK + j : o, c = colwise ? o : b * BLOCK + j;
+    if (y_f32) static_cast<float*>(y)[r * ldy + c] = v;
+    else static_cast<__nv_bfloat16*>(y)[r * ldy + c] = __float2bfloat16_rn(v);
+  }
+}
+
+}  // namespace mx
+
+int32_t mx_layout(int32_t format, int32_t dim, long long rows, long long cols, size_t* values_bytes,
+                  size_t* scale_bytes) {
+  if (format != CDL_MXFP8)
+    return fail(CDL_ERR_UNSUPPORTED, "block-scaled format %d is not implemented (only MXFP8)", format);
+  if (dim != CDL_MX_ROWWISE && dim != CDL_MX_COLWISE)
+    return fail(CDL_ERR_INVALID, "block-scaled tensors: unknown block dimension %d", dim);
+  if (rows < 0 || cols < 0) return fail(CDL_ERR_INVALID, "block-scaled tensors: negative shape");
+  const long long outer = dim == CDL_MX_ROWWISE ? rows : cols;
+  const long long inner = dim == CDL_MX_ROWWISE ? cols : rows;
+  if (inner % mx::BLOCK != 0)
+    return fail(CDL_ERR_INVALID,
+                "block dimension of shape [%lld, %lld] must be a multiple of the MXFP8 block size 32",
+                rows, cols);
+  if (values_bytes) *values_bytes = static_cast<size_t>(outer) * inner;
+  if (scale_bytes)
+    *scale_bytes = static_cast<size_t>((outer + 127) / 128 * 128) * ((inner / mx::BLOCK + 3) / 4 * 4);
+  return CDL_OK;
+}
+
+int32_t mx_check(const char* op, const char* name, const cdl_mx_tensor* t, int32_t dim, long long rows,
+                 long long cols) {
+  if (t->format != CDL_MXFP8)
+    return fail(CDL_ERR_UNSUPPORTED, "%s: %s: block-scaled format %d is not implemented (only MXFP8)",
+                op, name, t->format);
+  if (t->dim != dim)
+    return fail(CDL_ERR_INVALID, "%s: %s must have its blocks along the %s", op, name,
+                dim == CDL_MX_ROWWISE ? "rows (rowwise)" : "columns (colwise)");
+  if (t->rows != rows || t->cols != cols)
+    return fail(CDL_ERR_INVALID, "%s: %s must have shape [%lld, %lld], got [%lld, %lld]", op, name,
+                rows, cols, static_cast<long long>(t->rows), static_cast<long long>(t->cols));
+  CDL_CHECK(mx_layout(t->format, t->dim, rows, cols, nullptr, nullptr));
+  if (rows > 0 && cols > 0) {
+    if (!t->values || !t->scale_factors)
+      return fail(CDL_ERR_INVALID, "%s: %s has no values or scale factors", op, name);
+    if ((reinterpret_cast<uintptr_t>(t->values) & 31) != 0 ||
+        (reinterpret_cast<uintptr_t>(t->scale_factors) & 15) != 0)
+      return fail(CDL_ERR_UNSUPPORTED,
+                  "%s: %s: values must be 32-byte and scale factors 16-byte aligned", op, name);
+  }
+  return CDL_OK;
+}
+
+static int32_t mx_rows_run(const char* op, const cdl_tensor* x, const cdl_tensor* scale,
+                           const cdl_tensor* bias, float eps, bool norm, const cdl_mx_tensor* y_row,
+                           const cdl_mx_tensor* y_col, const cdl_tensor* r_inv, cudaStream_t stream) {
+  using namespace mx;
+  if (!x) return fail(CDL_ERR_INVALID, "%s: x is required", op);
+  if (!y_row && !y_col) return fail(CDL_ERR_INVALID, "%s: at least one output is required", op);
+  if (x->rank != 2) return fail(CDL_ERR_INVALID, "%s: x must be a 2D tensor", op);
+  if (x->dtype != CDL_BF16) return fail(CDL_ERR_UNSUPPORTED, "%s: x must be bf16", op);
+  const long long rows = x->shape[0], cols = x->shape[1];
+  if (cols > 1 && x->stride[1] != 1)
+    return fail(CDL_ERR_UNSUPPORTED, "%s: x must have packed rows (contiguous columns)", op);
+  if ((reinterpret_cast<uintptr_t>(x->ptr) & 15) != 0 || (rows > 1 && x->stride[0] % 8 != 0))
+    return fail(CDL_ERR_UNSUPPORTED, "%s: x must be 16-byte aligned (pointer and row stride)", op);
+  if (cols % BLOCK != 0)
+    return fail(CDL_ERR_INVALID,
+                "%s: the number of columns (%lld) must be a multiple of the MXFP8 block size 32", op,
+                cols);
+  if (y_row) CDL_CHECK(mx_check(op, "rowwise output", y_row, CDL_MX_ROWWISE, rows, cols));
+  if (y_col) CDL_CHECK(mx_check(op, "colwise output", y_col, CDL_MX_COLWISE, rows, cols));
+  for (const cdl_tensor* v : {scale, bias}) {
+    if (!v) continue;
+    if (v->rank != 1 || v->shape[0] != cols || v->dtype != CDL_BF16 || v->stride[0] != 1 ||
+        (reinterpret_cast<uintptr_t>(v->ptr) & 15) != 0)
+      return fail(CDL_ERR_INVALID, "%s: scale and bias must be contiguous 16-byte aligned bf16 [%lld]",
+                  op, cols);
+  }
+  if (r_inv && (r_inv->rank != 1 || r_inv->shape[0] != rows || r_inv->dtype != CDL_F32))
+    return fail(CDL_ERR_INVALID, "%s: r_inv must be f32 [%lld]", op, rows);
+  if (rows == 0 || cols == 0) return CDL_OK;
+  if (rows > INT32_MAX / 2 || cols > 65536)
+    return fail(CDL_ERR_UNSUPPORTED, "%s: shape [%lld, %lld] is too large", op, rows, cols);
+
+  Params p{};
+  p.x = static_cast<const __nv_bfloat16*>(x->ptr);
+  p.ldx = x->stride[0];
+  p.rows = static_cast<int>(rows);
+  p.cols = static_cast<int>(cols);
+  p.gamma = scale ? static_cast<const __nv_bfloat16*>(scale->ptr) : nullptr;
+  p.beta = bias ? static_cast<const __nv_bfloat16*>(bias->ptr) : nullptr;
+  p.eps = eps;
+  p.r_inv = r_inv ? static_cast<float*>(r_inv->ptr) : nullptr;
+  p.r_inv_stride = r_inv ? r_inv->stride[0] : 0;
+  if (y_row) {
+    p.row_values = static_cast<uint8_t*>(y_row->values);
+    p.row_sf = static_cast<uint8_t*>(y_row->scale_factors);
+  }
+  if (y_col) {
+    p.col_values = static_cast<uint8_t*>(y_col->values);
+    p.col_sf = static_cast<uint8_t*>(y_col->scale_factors);
+  }
+  // algorithmic bytes: x read, one byte per element and output, one scale byte per 32
+  const double bytes = 2.0 * rows * cols + ((y_row ? 1 : 0) + (y_col ? 1 : 0)) * (rows * cols * (1.0 + 1.0 / 32));
+  ProfileScope ps(PROF_NORM_FWD, bytes, stream);
+  if (y_col) {
+    static std::once_flag once[64];
+    int dev = 0;
+    CDL_CUDA(cudaGetDevice(&dev));
+    cudaError_t err = cudaSuccess;
+    std::call_once(once[dev & 63], [&] {
+      err = cudaFuncSetAttribute(mx_rows_kernel<true, true>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                 static_cast<int>(COL_SMEM_BYTES));
+      if (err == cudaSuccess)
+        err = cudaFuncSetAttribute(mx_rows_kernel<false, true>,
+                                   cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                   static_cast<int>(COL_SMEM_BYTES));
+    });
+    if (err != cudaSuccess)
+      return fail(CDL_ERR_CUDA, "cudaFuncSetAttribute failed: %s", cudaGetErrorString(err));
+    const unsigned grid = static_cast<unsigned>(rows / 32);
+    if (norm) mx_rows_kernel<true, true><<<grid, 1024, COL_SMEM_BYTES, stream>>>(p);
+    else mx_rows_kernel<false, true><<<grid, 1024, COL_SMEM_BYTES, stream>>>(p);
+  } else {
+    const long long want = (rows + 7) / 8;
+    const unsigned grid = static_cast<unsigned>(want < 8LL * sm_count() ? want : 8LL * sm_count());
+    if (norm) mx_rows_kernel<true, false><<<grid, 256, 0, stream>>>(p);
+    else mx_rows_kernel<false, false><<<grid, 256, 0, stream>>>(p);
+  }
+  CDL_CUDA(cudaGetLastError());
+  return CDL_OK;
+}
+
+int32_t rmsnorm_fwd_mx_execute(const cdl_tensor* x, const cdl_tensor* scale, const cdl_tensor* bias,
+                               float eps, const cdl_mx_tensor* y_row, const cdl_mx_tensor* y_col,
+                               const cdl_tensor* r_inv, cudaStream_t stream) {
+  if (!y_row)
+    return fail(CDL_ERR_INVALID, "norm_fwd (mxfp8): the rowwise output is required "
+                                 "(the outputs are rowwise, or rowwise and colwise)");
+  return mx_rows_run("norm_fwd (mxfp8)", x, scale, bias, eps, true, y_row, y_col, r_inv, stream);
+}
+
+int32_t mx_quantize_execute(const cdl_tensor* x, const cdl_mx_tensor* y_row,
+                            const cdl_mx_tensor* y_col, cudaStream_t stream) {
+  return mx_rows_run("mx_quantize", x, nullptr, nullptr, 0.f, false, y_row, y_col, nullptr, stream);
+}
+
+int32_t mx_dequantize_execute(const cdl_mx_tensor* x, const cdl_tensor* y, cudaStream_t stream) {
+  const char* op = "mx_dequantize";
+  if (!x || !y) return fail(CDL_ERR_INVALID, "%s: x and y are required", op);
+  CDL_CHECK(mx_check(op, "x", x, x->dim, x->rows, x->cols));
+  if (y->rank != 2 || y->shape[0] != x->rows || y->shape[1] != x->cols ||
+      (y->dtype != CDL_BF16 && y->dtype != CDL_F32) || (x->cols > 1 && y->stride[1] != 1))
+    return fail(CDL_ERR_INVALID, "%s: y must be a bf16 or f32 [%lld, %lld] tensor with packed rows", op,
+                static_cast<long long>(x->rows), static_cast<long long>(x->cols));
+  if (x->rows == 0 || x->cols == 0) return CDL_OK;
+  const bool colwise = x->dim == CDL_MX_COLWISE;
+  const long long outer = colwise ? x->cols : x->rows, inner = colwise ? x->rows : x->cols;
+  if (outer > INT32_MAX / 2 || inner > INT32_MAX / 2)
+    return fail(CDL_ERR_UNSUPPORTED, "%s: shape too large", op);
+  const long long n = outer * (inner / mx::BLOCK);
+  mx::mx_dequantize_kernel<<<static_cast<unsigned>((n + 255) / 256), 256, 0, stream>>>(
+      static_cast<const uint8_t*>(x->values), static_cast<const uint8_t*>(x->scale_factors),
+      static_cast<int>(outer), static_cast<int>(inner), colwise ? 1 : 0, y->ptr,
+      y->dtype == CDL_F32 ? 1 : 0, y->stride[0]);
+  CDL_CUDA(cudaGetLastError());
+  return CDL_OK;
+}
+
+}  // namespace cdl
+
+extern "C" {
+
+int32_t cdl_b200_mx_layout(int32_t format, int32_t dim, int64_t rows, int64_t cols,
+                           size_t* values_bytes, size_t* scale_bytes) {
+  return cdl::mx_layout(format, dim, rows, cols, values_bytes, scale_bytes);
+}
+
+int32_t cdl_b200_mx_quantize(const cdl_tensor* x, const cdl_mx_tensor* y_rowwise,
+                             const cdl_mx_tensor* y_colwise, cdl_stream stream) {
+  return cdl::mx_quantize_execute(x, y_rowwise, y_colwise, static_cast<cudaStream_t>(stream));
+}
+
+int32_t cdl_b200_mx_dequantize(const cdl_mx_tensor* x, const cdl_tensor* y, cdl_stream stream) {
+  return cdl::mx_dequantize_execute(x, y, static_cast<cudaStream_t>(stream));
+}
+
+int32_t cdl_b200_rmsnorm_fwd_mx(const cdl_tensor* x, const cdl_tensor* scale, const cdl_tensor* bias,
+                                float eps, const cdl_mx_tensor* y_rowwise,
+                                const cdl_mx_tensor* y_colwise, const cdl_tensor* r_inv,
+                                cdl_stream stream) {
+  return cdl::rmsnorm_fwd_mx_execute(x, scale, bias, eps, y_rowwise, y_colwise, r_inv,
+                                     static_cast<cudaStream_t>(stream));
+}
+
+}  // extern "C"

@@ -51,6 +51,20 @@ int32_t swiglu_fwd_execute(const cdl_tensor* gate, const cdl_tensor* up, const c
 int32_t swiglu_bwd_execute(const cdl_tensor* d_act, const cdl_tensor* gate, const cdl_tensor* up,
                            const cdl_tensor* d_gate, const cdl_tensor* d_up, cudaStream_t stream);
 
+// Block-scaled (MXFP8) tensors.
+int32_t mx_layout(int32_t format, int32_t dim, long long rows, long long cols, size_t* values_bytes,
+                  size_t* scale_bytes);
+int32_t mx_check(const char* op, const char* name, const cdl_mx_tensor* t, int32_t dim, long long rows,
+                 long long cols);
+int32_t mx_quantize_execute(const cdl_tensor* x, const cdl_mx_tensor* y_row,
+                            const cdl_mx_tensor* y_col, cudaStream_t stream);
+int32_t mx_dequantize_execute(const cdl_mx_tensor* x, const cdl_tensor* y, cudaStream_t stream);
+int32_t rmsnorm_fwd_mx_execute(const cdl_tensor* x, const cdl_tensor* scale, const cdl_tensor* bias,
+                               float eps, const cdl_mx_tensor* y_row, const cdl_mx_tensor* y_col,
+                               const cdl_tensor* r_inv, cudaStream_t stream);
+int32_t matmul_mx_execute(const cdl_mx_tensor* a, const cdl_mx_tensor* b, const cdl_tensor* d,
+                          float alpha, cudaStream_t stream);
+
 // Packed row-major views.
 inline cdl_tensor view2(const void* p, int32_t dt, long long r, long long c) {
   cdl_tensor t{};

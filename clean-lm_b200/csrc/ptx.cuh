@@ -378,6 +378,45 @@ __host__ __device__ constexpr uint32_t make_idesc_bf16(int m, int n, int a_mn_ma
          (static_cast<uint32_t>(m >> 4) << 24);
 }
 
+// ---------------------------------------------------------------- block-scaled MMA (MXFP8)
+// D[tmem] (+)= (A * SFA) . (B * SFB): FP8 E4M3 operands in shared memory (K = 32 per instruction),
+// one UE8M0 scale per row and instruction read from tensor memory.  Scale layout in TMEM: the
+// scale of row r sits on lane r % 32 (replicated over the four lane quadrants) of column
+// base + r / 32, in the byte the instruction descriptor selects (a_sf_id / b_sf_id).
+__device__ __forceinline__ void umma_mxf8_ss(uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc,
+                                             uint32_t idesc, uint32_t sfa_tmem, uint32_t sfb_tmem,
+                                             uint32_t accumulate) {
+  asm volatile(
+      "{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %6, 0;\n\t"
+      "tcgen05.mma.cta_group::1.kind::mxf8f6f4.block_scale [%0], %1, %2, %3, [%4], [%5], p;\n\t}\n" ::"r"(
+          d_tmem),
+      "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(sfa_tmem), "r"(sfb_tmem), "r"(accumulate)
+      : "memory");
+}
+// Instruction descriptor of kind::mxf8f6f4 with E4M3 A / B (both K-major), UE8M0 scales, f32
+// accumulate:  bits 4-5 B scale byte, 7-9 A format (0 = E4M3), 10-12 B format, 15 / 16 A / B major
+// (0 = K), 17-22 N >> 3, 23 scale format (1 = UE8M0), 24-28 M >> 4, 29-30 A scale byte.
+__host__ __device__ constexpr uint32_t make_idesc_mxf8(int m, int n, uint32_t a_sf_byte,
+                                                       uint32_t b_sf_byte) {
+  return (b_sf_byte << 4) | (static_cast<uint32_t>(n >> 3) << 17) | (1u << 23) |
+         (static_cast<uint32_t>(m >> 4) << 24) | (a_sf_byte << 29);
+}
+// Shared memory -> tensor memory copy of 32 rows x 16 bytes, replicated to the four lane
+// quadrants: the 512-byte scale-factor tile of 128 rows x 4 blocks lands in 4 columns with
+// row r on lane r % 32 of column r / 32.  Ordered with the MMAs of the issuing thread.
+__device__ __forceinline__ void tmem_cp_32x128b_warpx4(uint32_t taddr, uint64_t s_desc) {
+  asm volatile("tcgen05.cp.cta_group::1.32x128b.warpx4 [%0], %1;" ::"r"(taddr), "l"(s_desc)
+               : "memory");
+}
+// Descriptor of an unswizzled K-major tile of 16-byte rows: 8-row groups SBO = 128 bytes apart.
+__device__ __forceinline__ uint64_t smem_desc_rows16(uint32_t saddr) {
+  uint64_t d = 0;
+  d |= static_cast<uint64_t>((saddr & 0x3FFFFu) >> 4);
+  d |= static_cast<uint64_t>(128u >> 4) << 32;
+  d |= 1ull << 46;
+  return d;
+}
+
 // ---------------------------------------------------------------- small helpers
 __device__ __forceinline__ uint32_t pack_bf16x2(float lo, float hi) {
   __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi);

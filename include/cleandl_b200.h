@@ -147,6 +147,62 @@ int32_t cdl_b200_rmsnorm_bwd_static(const cdl_tensor* x, const cdl_tensor* dy,
                                     const cdl_tensor* r_inv, const cdl_tensor* dx,
                                     const cdl_tensor* dscale, cdl_stream stream);
 
+/* ---- Block-scaled (MX) tensors ------------------------------------------------------------
+ * The reference's MxTensor (crates/cleandl/src/mx_tensor.rs:11-30, layout MxLayout::new
+ * :339-372): a 2-D tensor quantised in blocks of 32 elements that share one UE8M0 scale; values
+ * are FP8 E4M3 (MXFP8).  dim says along which logical dimension the blocks run:
+ *   rowwise  values = packed bytes [rows, cols], blocks along a row    (cols % 32 == 0)
+ *   colwise  values = packed bytes [cols, rows] (the transpose), blocks down a column (rows % 32 == 0)
+ * scale_factors is the 128 x 4 tiled, partition-swizzled byte layout block-scaled tensor-core
+ * instructions read: with outer = the non-block dimension and B = blocks per outer index, the
+ * scale of block (o, b) is byte ((o / 128) * ceil(B / 4) + b / 4) * 512 + (o % 32) * 16 +
+ * ((o % 128) / 32) * 4 + b % 4 of a buffer of round_up(outer, 128) * round_up(B, 4) bytes
+ * (crates/cleandl/tests/common/mod.rs:124-129).  values must be 32-byte and scale_factors 16-byte
+ * aligned.  NVFP4 (MxFormat::Nvfp4) is not implemented: CDL_ERR_UNSUPPORTED. */
+typedef enum { CDL_MXFP8 = 0, CDL_NVFP4 = 1 } cdl_mx_format;
+typedef enum { CDL_MX_ROWWISE = 0, CDL_MX_COLWISE = 1 } cdl_mx_dim;
+typedef struct {
+  void* values;
+  void* scale_factors;
+  int32_t format; /* cdl_mx_format */
+  int32_t dim;    /* cdl_mx_dim */
+  int64_t rows, cols; /* logical shape */
+} cdl_mx_tensor;
+
+/* Bytes of the two buffers of a block-scaled tensor (MxLayout::new, mx_tensor.rs:339-372). */
+int32_t cdl_b200_mx_layout(int32_t format, int32_t dim, int64_t rows, int64_t cols,
+                           size_t* values_bytes, size_t* scale_bytes);
+
+/* Quantises bf16 x [rows, cols] (packed rows, 16-byte aligned) into a rowwise and / or a colwise
+ * block-scaled tensor (either may be NULL, not both): per block, scale = amax / 448 rounded up
+ * to a power of two, element = x / scale rounded to nearest E4M3, saturating
+ * (crates/cleandl-specialized-kernels/src/utils/block_scale.rs:24-55; the host quantiser of
+ * crates/cleandl/tests/matmul.rs:885-952 gives the same bits).  Scale bytes of the padding are
+ * not written. */
+int32_t cdl_b200_mx_quantize(const cdl_tensor* x, const cdl_mx_tensor* y_rowwise,
+                             const cdl_mx_tensor* y_colwise, cdl_stream stream);
+
+/* y (bf16 or f32 [rows, cols], packed rows) = values * scale.  A test and debugging aid. */
+int32_t cdl_b200_mx_dequantize(const cdl_mx_tensor* x, const cdl_tensor* y, cdl_stream stream);
+
+/* RMSNorm forward with block-scaled outputs: NormFwd with NormOutput::Mxfp8Rowwise (y_colwise
+ * NULL) or ::Mxfp8RowwiseAndColwise (crates/cleandl/src/execgraph/ops/norm/mod.rs:33-62; kernel
+ * crates/cleandl-specialized-kernels/src/kernels/norm/forward.rs:509-785).  Operands as for
+ * cdl_b200_rmsnorm_fwd; the result is rounded to bf16 and then quantised as by
+ * cdl_b200_mx_quantize.  The colwise output needs rows % 32 == 0 (norm/mod.rs validation). */
+int32_t cdl_b200_rmsnorm_fwd_mx(const cdl_tensor* x, const cdl_tensor* scale, const cdl_tensor* bias,
+                                float eps, const cdl_mx_tensor* y_rowwise,
+                                const cdl_mx_tensor* y_colwise, const cdl_tensor* r_inv,
+                                cdl_stream stream);
+
+/* D = alpha * A . B with block-scaled operands: Matmul with InputKind::Mx(Mxfp8)
+ * (crates/cleandl/src/execgraph/ops/matmul.rs:808-838, forwarded to cuBLASLt block scaling by the
+ * reference; tests crates/cleandl/tests/matmul.rs:1041-1060).  A is rowwise [M, K], B is colwise
+ * [K, N] (both K-contiguous), D is bf16 or f32 [M, N] with packed rows; accumulation is f32.
+ * K % 32 == 0.  Block-scaled OUTPUTS (MatmulOutput::BlockScaled) are not implemented. */
+int32_t cdl_b200_matmul_mx(const cdl_mx_tensor* a, const cdl_mx_tensor* b, const cdl_tensor* d,
+                           float alpha, cdl_stream stream);
+
 /* ---- Flash attention -------------------------------------------------------------------
  * Replaces AttentionExecutor::execute (crates/cleandl/src/execgraph/ops/attention/exec.rs:
  * 358-416), which forwards to flash-attention-rs.  Dense layout only: q [B,Sq,H,D], k and v

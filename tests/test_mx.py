@@ -1,0 +1,247 @@
+"""Block-scaled (MXFP8) tensors: oracle pins on CPU, GPU parity through the C ABI.
+
+Follows the reference's tests of the format: the host quantiser and the dequantised checks of
+crates/cleandl/tests/matmul.rs:885-952, 1041-1060 (block-scaled matmul inputs, tolerance of
+`tolerance(out, bounds)` :199-202), and the block-scaled norm outputs of
+crates/cleandl/tests/norm.rs:134-149, 322-380 (|got - y| <= 0.07 |y| + 2^-9 * block scale).
+"""
+import ctypes
+
+import numpy as np
+import pytest
+import torch
+
+from helpers import assert_all_close, to_f32
+from oracle import cpu_oracle as oracle
+from oracle import mx_ref
+
+ROW, COL = mx_ref.ROWWISE, mx_ref.COLWISE
+
+
+# ------------------------------------------------------------------------------ CPU: the oracle
+def test_e4m3_table_pins():
+    t = mx_ref.E4M3_VALUES
+    assert t[0x00] == 0.0 and t[0x01] == 2.0 ** -9 and t[0x08] == 2.0 ** -6
+    assert t[0x38] == 1.0 and t[0x7E] == 448.0 and np.isnan(t[0x7F]) and t[0xFE] == -448.0
+    finite = t[:0x7F]
+    assert np.all(np.diff(finite) > 0)
+    # every code encodes to itself; ties go to the even code; overflow saturates
+    codes = np.arange(0x7F, dtype=np.uint8)
+    assert np.array_equal(mx_ref.e4m3_encode(finite), codes)
+    ties = (finite[:-1] + finite[1:]) / 2
+    enc = mx_ref.e4m3_encode(ties)
+    assert np.all(enc % 2 == 0) and np.all(np.abs(enc.astype(int) - codes[:-1]) <= 1)
+    assert mx_ref.e4m3_encode(np.array([1e9, -1e9, 449.0]))[:].tolist() == [0x7E, 0xFE, 0x7E]
+
+
+def test_e4m3_encode_matches_torch():
+    rng = np.random.default_rng(0)
+    x = (rng.standard_normal(100000) * rng.choice([1e-3, 0.02, 1, 40, 200], 100000)).astype(np.float32)
+    x = np.clip(x, -448, 448)
+    want = torch.from_numpy(x).to(torch.float8_e4m3fn).view(torch.uint8).numpy()
+    assert np.array_equal(mx_ref.e4m3_encode(x), want)
+
+
+def test_scale_factor_index_is_a_bijection_on_tiles():
+    # closed form of crates/cleandl/tests/common/mod.rs:124-129 on a padded 256 x 8 block grid
+    r, b = np.meshgrid(np.arange(256), np.arange(8), indexing="ij")
+    idx = mx_ref.sf_index(r, b, 8)
+    assert sorted(idx.ravel().tolist()) == list(range(256 * 8))
+    assert mx_ref.sf_index(0, 0, 8) == 0 and mx_ref.sf_index(1, 0, 8) == 16
+    assert mx_ref.sf_index(32, 0, 8) == 4 and mx_ref.sf_index(0, 1, 8) == 1
+    assert mx_ref.sf_index(0, 4, 8) == 512 and mx_ref.sf_index(128, 0, 8) == 1024
+    assert mx_ref.sf_index(5, 2, 3) == 5 * 16 + 2  # 3 block columns pad to one tile of 4
+
+
+def test_scale_exponent():
+    # amax = 448 * 2^k needs exactly scale 2^k; anything above rounds up; zero blocks get 2^-127
+    e = mx_ref.scale_exponent(np.array([448.0, 448.0001, 1.0, 0.0, 3.4e38], dtype=np.float32))
+    assert e.tolist() == [127, 128, 127 - 8, 0, 247]
+
+
+@pytest.mark.parametrize("dim", [ROW, COL])
+def test_quantize_roundtrip_within_format_error(dim):
+    rng = np.random.default_rng(1)
+    m = (rng.standard_normal((192, 160)) * np.exp(rng.standard_normal((192, 160)) * 2)).astype(np.float32)
+    v, s = mx_ref.quantize(m, dim)
+    outer, inner, sf_rows, sf_cols = mx_ref.layout(192, 160, dim)
+    assert v.shape == (outer, inner) and s.shape == (sf_rows * sf_cols,)
+    d, es = mx_ref.dequantize(v, s, 192, 160, dim)
+    assert np.all(np.abs(d - m) <= 2.0 ** -4 * np.abs(m) + 2.0 ** -10 * es * 1.0001)
+    # no element overflows its block: |x| / scale <= 448
+    assert np.all(np.abs(m) <= 448.0 * es)
+
+
+def test_layout_through_the_c_abi(cdl):
+    for rows, cols in [(1, 128), (300, 2048), (96, 512), (256, 160)]:
+        for dim in (ROW, COL):
+            try:
+                outer, inner, sf_rows, sf_cols = mx_ref.layout(rows, cols, dim)
+            except ValueError:
+                with pytest.raises(cdl._lib.CdlError, match="block size"):
+                    cdl.mx.layout_bytes(rows, cols, dim)
+                continue
+            assert cdl.mx.layout_bytes(rows, cols, dim) == (outer * inner, sf_rows * sf_cols)
+    with pytest.raises(cdl._lib.CdlError, match="not implemented"):
+        cdl.mx.layout_bytes(128, 128, ROW, fmt=cdl._lib.CDL_NVFP4)
+
+
+def test_host_validation_needs_no_gpu(cdl):
+    L = cdl._lib
+    x = L.CdlTensor(ptr=256, dtype=L.CDL_BF16, rank=2)
+    x.shape[0], x.shape[1], x.stride[0], x.stride[1] = 4, 48, 48, 1
+    y = L.CdlMxTensor(512, 1024, L.CDL_MXFP8, L.CDL_MX_ROWWISE, 4, 48)
+    st = L.lib.cdl_b200_rmsnorm_fwd_mx(ctypes.byref(x), None, None, 1e-6, ctypes.byref(y), None, None, None)
+    assert st == -1 and "block size" in L.last_error()
+    x.shape[0], x.shape[1], x.stride[0] = 48, 64, 64
+    y = L.CdlMxTensor(512, 1024, L.CDL_MXFP8, L.CDL_MX_ROWWISE, 48, 64)
+    yc = L.CdlMxTensor(512, 1024, L.CDL_MXFP8, L.CDL_MX_COLWISE, 48, 64)
+    st = L.lib.cdl_b200_rmsnorm_fwd_mx(ctypes.byref(x), None, None, 1e-6, ctypes.byref(y), ctypes.byref(yc),
+                                       None, None)
+    assert st == -1 and "block size" in L.last_error()
+    # matmul: A must be rowwise, B colwise, contraction dimensions equal
+    a = L.CdlMxTensor(512, 1024, L.CDL_MXFP8, L.CDL_MX_COLWISE, 128, 64)
+    b = L.CdlMxTensor(512, 1024, L.CDL_MXFP8, L.CDL_MX_COLWISE, 64, 128)
+    d = L.CdlTensor(ptr=2048, dtype=L.CDL_BF16, rank=2)
+    d.shape[0], d.shape[1], d.stride[0], d.stride[1] = 128, 128, 128, 1
+    st = L.lib.cdl_b200_matmul_mx(ctypes.byref(a), ctypes.byref(b), ctypes.byref(d), 1.0, None)
+    assert st == -1 and "contraction" in L.last_error()
+    a = L.CdlMxTensor(512, 1024, L.CDL_MXFP8, L.CDL_MX_ROWWISE, 128, 64)
+    b = L.CdlMxTensor(512, 1024, L.CDL_MXFP8, L.CDL_MX_COLWISE, 96, 128)
+    st = L.lib.cdl_b200_matmul_mx(ctypes.byref(a), ctypes.byref(b), ctypes.byref(d), 1.0, None)
+    assert st == -1 and "contraction" in L.last_error()
+    a = L.CdlMxTensor(512, 1024, L.CDL_NVFP4, L.CDL_MX_ROWWISE, 128, 64)
+    st = L.lib.cdl_b200_matmul_mx(ctypes.byref(a), ctypes.byref(b), ctypes.byref(d), 1.0, None)
+    assert st == -2 and "MXFP8" in L.last_error()
+
+
+# ------------------------------------------------------------------------------ GPU parity
+def valid_scales(t, scales_np):
+    """Scale bytes of the real blocks of an MxTensor (padding bytes are unspecified)."""
+    outer, inner, _, _ = mx_ref.layout(t.rows, t.cols, t.dim)
+    blocks = inner // 32
+    o, b = np.meshgrid(np.arange(outer), np.arange(blocks), indexing="ij")
+    return scales_np[mx_ref.sf_index(o, b, blocks)]
+
+
+def rand_bf16(rows, cols, seed, spread=2.0):
+    gen = torch.Generator().manual_seed(seed)
+    x = torch.randn(rows, cols, generator=gen) * torch.exp(torch.randn(rows, cols, generator=gen) * spread)
+    return x.to(torch.bfloat16)
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("rows,cols", [(1, 128), (37, 4096), (300, 2048), (128, 8192), (96, 512),
+                                        (64, 160), (256, 7168)])
+def test_quantize_is_bit_exact(cdl, gpu_ok, rows, cols):
+    x = rand_bf16(rows, cols, 10)
+    x[0, :32] = 0  # an all-zero block
+    if rows > 1:
+        x[1, :32] = 448.0  # exactly representable amax
+    col = rows % 32 == 0
+    yr, yc = cdl.mx.quantize(x.cuda(), rowwise=True, colwise=col)
+    for t, dim in ((yr, ROW), (yc, COL)):
+        if t is None:
+            continue
+        v_ref, s_ref = mx_ref.quantize(to_f32(x), dim)
+        assert np.array_equal(t.values.cpu().numpy(), v_ref), f"values dim {dim}"
+        assert np.array_equal(valid_scales(t, t.scale_factors.cpu().numpy()), valid_scales(t, s_ref))
+        d_ref, _ = mx_ref.dequantize(v_ref, s_ref, rows, cols, dim)
+        assert np.array_equal(to_f32(cdl.mx.dequantize(t)), d_ref)
+
+
+@pytest.mark.gpu
+def test_quantize_strided_rows(cdl, gpu_ok):
+    big = rand_bf16(64, 1024, 11).cuda()
+    x = big[:, 256:768]
+    yr, yc = cdl.mx.quantize(x, rowwise=True, colwise=True)
+    v_ref, _ = mx_ref.quantize(to_f32(x), ROW)
+    assert np.array_equal(yr.values.cpu().numpy(), v_ref)
+    v_ref, _ = mx_ref.quantize(to_f32(x), COL)
+    assert np.array_equal(yc.values.cpu().numpy(), v_ref)
+
+
+NORM_CASES = [(1, 128), (37, 4096), (300, 2048), (128, 8192), (100, 7168), (5, 1024), (96, 512),
+              (320, 1536), (16384, 2048)]
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("rows,cols", NORM_CASES)
+@pytest.mark.parametrize("affine", ["none", "scale", "scale_bias"])
+def test_norm_fwd_mx(cdl, gpu_ok, rows, cols, affine):
+    if rows == 16384 and affine != "scale":
+        pytest.skip("the full-size case runs once")
+    gen = torch.Generator().manual_seed(1)
+    x = (torch.randn(rows, cols, generator=gen) * 2.0 + 0.5).to(torch.bfloat16)
+    scale = (torch.rand(cols, generator=gen) + 0.5).to(torch.bfloat16) if affine != "none" else None
+    bias = torch.randn(cols, generator=gen).to(torch.bfloat16) if affine == "scale_bias" else None
+    col = rows % 32 == 0
+    out = cdl.mx.norm_fwd_mx(x.cuda(), None if scale is None else scale.cuda(),
+                             None if bias is None else bias.cuda(), 1e-6, colwise=col, save_stats=True)
+    y_ref, r_ref = oracle.rmsnorm_fwd(to_f32(x), None if scale is None else to_f32(scale),
+                                      None if bias is None else to_f32(bias), 1e-6)
+    assert_all_close("r_inv", to_f32(out.r_inv), r_ref, oracle.abs_rel_tolerance(r_ref, 1e-6, 1e-4))
+    # what quantising the bf16-rounded f64 result gives; the kernel's f32 result can differ from
+    # it by a bf16 ulp in a few places, so bits are compared statistically, values by tolerance
+    yb = oracle.bf16_round(y_ref.astype(np.float32))
+    for t, dim in ((out.y, ROW), (out.y_col, COL)):
+        if t is None:
+            continue
+        got, es = mx_ref.dequantize(t.values.cpu().numpy(), t.scale_factors.cpu().numpy(), rows, cols, dim)
+        assert_all_close(f"y dim {dim}", got, y_ref, mx_ref.output_tolerance(y_ref, es))
+        v_ref, s_ref = mx_ref.quantize(yb, dim)
+        same_scale = valid_scales(t, t.scale_factors.cpu().numpy()) == valid_scales(t, s_ref)
+        assert same_scale.mean() > 0.995, f"scales dim {dim}: {same_scale.mean()}"
+        assert (t.values.cpu().numpy() == v_ref).mean() > 0.98, f"codes dim {dim}"
+        # the device's own dequantiser agrees with the oracle's
+        assert np.array_equal(to_f32(cdl.mx.dequantize(t)), got)
+
+
+MM_CASES = [(192, 256, 160), (128, 32, 64), (128, 128, 256), (256, 2048, 512), (100, 96, 24),
+            (384, 416, 300), (1024, 1024, 2048)]
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("m,k,n", MM_CASES)
+@pytest.mark.parametrize("out", ["bf16", "f32"])
+def test_matmul_mx(cdl, gpu_ok, m, k, n, out):
+    """The reference's mxfp8_inputs test: the expected product is the f64 product of the
+    DEQUANTISED operands; tolerance as for a plain matmul of those values."""
+    gen = torch.Generator().manual_seed(80)
+    a = torch.randn(m, k, generator=gen).to(torch.bfloat16)
+    b = torch.randn(k, n, generator=gen).to(torch.bfloat16)
+    qa, _ = cdl.mx.quantize(a.cuda(), rowwise=True)
+    _, qb = cdl.mx.quantize(b.cuda(), rowwise=False, colwise=True)
+    da, _ = mx_ref.dequantize(qa.values.cpu().numpy(), qa.scale_factors.cpu().numpy(), m, k, ROW)
+    db, _ = mx_ref.dequantize(qb.values.cpu().numpy(), qb.scale_factors.cpu().numpy(), k, n, COL)
+    dtype = torch.bfloat16 if out == "bf16" else torch.float32
+    d = cdl.mx.matmul_mx(qa, qb, out_dtype=dtype)
+    expected = da.astype(np.float64) @ db.astype(np.float64)
+    bound = np.abs(da).astype(np.float64) @ np.abs(db).astype(np.float64)
+    assert_all_close(f"mxfp8 {m}x{k}x{n} -> {out}", to_f32(d), expected,
+                     oracle.matmul_tolerance(expected, bound, out == "bf16"))
+
+
+@pytest.mark.gpu
+def test_matmul_mx_many_tiles_and_alpha(cdl, gpu_ok):
+    """More tiles than SMs (both accumulators and their shared columns in use), alpha != 1, and
+    linearity in the block scales: doubling every scale of A doubles the product exactly."""
+    m, k, n = 2048, 512, 4864
+    gen = torch.Generator().manual_seed(81)
+    a = torch.randn(m, k, generator=gen).to(torch.bfloat16)
+    b = torch.randn(k, n, generator=gen).to(torch.bfloat16)
+    qa, _ = cdl.mx.quantize(a.cuda(), rowwise=True)
+    _, qb = cdl.mx.quantize(b.cuda(), rowwise=False, colwise=True)
+    d1 = cdl.mx.matmul_mx(qa, qb, out_dtype=torch.float32)
+    da, _ = mx_ref.dequantize(qa.values.cpu().numpy(), qa.scale_factors.cpu().numpy(), m, k, ROW)
+    db, _ = mx_ref.dequantize(qb.values.cpu().numpy(), qb.scale_factors.cpu().numpy(), k, n, COL)
+    expected = da.astype(np.float64) @ db.astype(np.float64)
+    bound = np.abs(da).astype(np.float64) @ np.abs(db).astype(np.float64)
+    assert_all_close("product", to_f32(d1), expected, oracle.matmul_tolerance(expected, bound, False))
+    d_half = cdl.mx.matmul_mx(qa, qb, out_dtype=torch.float32, alpha=0.5)
+    assert torch.equal(d_half, d1 * 0.5)
+    qa2 = cdl.mx.MxTensor(qa.values, qa.scale_factors + 1, qa.dim, qa.rows, qa.cols)
+    d2 = cdl.mx.matmul_mx(qa2, qb, out_dtype=torch.float32)
+    assert torch.equal(d2, d1 * 2)
+    # repeated runs give identical bits (a fixed accumulation order)
+    assert torch.equal(cdl.mx.matmul_mx(qa, qb, out_dtype=torch.float32), d1)
