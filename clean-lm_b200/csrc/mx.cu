@@ -276,9 +276,12 @@ static int32_t mx_rows_run(const char* op, const cdl_tensor* x, const cdl_tensor
     return fail(CDL_ERR_UNSUPPORTED, "%s: x must have packed rows (contiguous columns)", op);
   if ((reinterpret_cast<uintptr_t>(x->ptr) & 15) != 0 || (rows > 1 && x->stride[0] % 8 != 0))
     return fail(CDL_ERR_UNSUPPORTED, "%s: x must be 16-byte aligned (pointer and row stride)", op);
-  if (cols % BLOCK != 0)
+  if (y_row && cols % BLOCK != 0)
     return fail(CDL_ERR_INVALID,
                 "%s: the number of columns (%lld) must be a multiple of the MXFP8 block size 32", op,
+                cols);
+  if (cols % 8 != 0)
+    return fail(CDL_ERR_UNSUPPORTED, "%s: the number of columns (%lld) must be a multiple of 8", op,
                 cols);
   if (y_row) CDL_CHECK(mx_check(op, "rowwise output", y_row, CDL_MX_ROWWISE, rows, cols));
   if (y_col) CDL_CHECK(mx_check(op, "colwise output", y_col, CDL_MX_COLWISE, rows, cols));
