@@ -24,6 +24,8 @@
 #include "ops.h"
 #include "ptx.cuh"
 
+#include <cuda_fp8.h>
+
 #include <mutex>
 
 namespace cdl {
@@ -57,6 +59,10 @@ struct Params {
   void* d;
   long long ldd;
   int out_f32, wide;
+  // Block-scaled output (out_mx 1 = rowwise, 2 = colwise): MXFP8 values and scale tiles.
+  int out_mx;
+  uint8_t* out_values;
+  uint8_t* out_sf;
   float alpha;
   int* status;
 };
@@ -116,6 +122,67 @@ __device__ __forceinline__ void store32(const Params& p, const uint32_t (&r)[32]
 #pragma unroll
       for (int j = 0; j < 32; ++j)
         if (col0 + j < p.N) dp[j] = __float2bfloat16_rn(v[j]);
+    }
+  }
+}
+
+__device__ __forceinline__ long long sf_index(int outer, int block, int blocks) {
+  return (static_cast<long long>(outer >> 7) * ((blocks + 3) >> 2) + (block >> 2)) * 512 +
+         (outer & 31) * 16 + ((outer & 127) >> 5) * 4 + (block & 3);
+}
+// Scale exponent and descale factor of a block with maximum magnitude amax (the quantiser of
+// mx.cu: amax / 448 rounded up to a power of two).
+__device__ __forceinline__ uint32_t scale_exponent(float amax) {
+  const uint32_t bits = __float_as_uint(amax);
+  const int e = static_cast<int>(bits >> 23) - 8 + ((bits & 0x7FFFFFu) > 0x600000u ? 1 : 0);
+  return static_cast<uint32_t>(min(max(e, 0), 254));
+}
+__device__ __forceinline__ float descale_of(uint32_t e) {
+  const uint32_t de = 254u - e;
+  return __uint_as_float(de != 0 ? de << 23 : 0x00400000u);
+}
+__device__ __forceinline__ uint32_t fp8x4(float a, float b, float c, float d) {
+  const uint32_t lo = __nv_cvt_float2_to_fp8x2(make_float2(a, b), __NV_SATFINITE, __NV_E4M3);
+  const uint32_t hi = __nv_cvt_float2_to_fp8x2(make_float2(c, d), __NV_SATFINITE, __NV_E4M3);
+  return lo | (hi << 16);
+}
+
+// Block-scaled store of 32 consecutive columns of the warp's 32 rows (lane = row).  Rowwise: the
+// thread's 32 columns are one block of its row.  Colwise: a column's block is the 32 rows of the
+// warp, so the maximum is taken across lanes and the transposed value matrix receives 32
+// consecutive bytes per column.  Called by all lanes of a warp with a valid row range.
+__device__ __forceinline__ void store32_mx(const Params& p, const uint32_t (&r)[32], int row, int col0,
+                                           int lane) {
+  float v[32];
+#pragma unroll
+  for (int j = 0; j < 32; ++j) v[j] = p.alpha * __uint_as_float(r[j]);
+  if (p.out_mx == 1) {
+    if (row >= p.M) return;
+    float amax = 0.f;
+#pragma unroll
+    for (int j = 0; j < 32; ++j) amax = fmaxf(amax, fabsf(v[j]));
+    const uint32_t e = scale_exponent(amax);
+    const float ds = descale_of(e);
+    uint32_t w[8];
+#pragma unroll
+    for (int j = 0; j < 8; ++j)
+      w[j] = fp8x4(v[4 * j] * ds, v[4 * j + 1] * ds, v[4 * j + 2] * ds, v[4 * j + 3] * ds);
+    st_global_v8(p.out_values + static_cast<long long>(row) * p.N + col0, w);  // N % 32 == 0
+    p.out_sf[sf_index(row, col0 >> 5, p.N >> 5)] = static_cast<uint8_t>(e);
+  } else {
+    const int row0 = row - lane;  // M % 32 == 0: the warp's rows are one block of every column
+#pragma unroll
+    for (int j = 0; j < 32; ++j) {
+      if (col0 + j < p.N) {  // warp-uniform
+        float amax = fabsf(v[j]);
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, o));
+        const uint32_t e = scale_exponent(amax);
+        const uint32_t q = __nv_cvt_float2_to_fp8x2(make_float2(v[j] * descale_of(e), 0.f),
+                                                    __NV_SATFINITE, __NV_E4M3);
+        p.out_values[static_cast<long long>(col0 + j) * p.M + row] = static_cast<uint8_t>(q & 0xFFu);
+        if (lane == 0) p.out_sf[sf_index(col0 + j, row0 >> 5, p.M >> 5)] = static_cast<uint8_t>(e);
+      }
     }
   }
 }
@@ -271,7 +338,11 @@ __global__ void __launch_bounds__(THREADS, 1)
           if (lane == 0) mbar_arrive(&bars->overlap_free);
         }
         const int col0 = col_base + ch * 32;
-        if (row < p.M && col0 < p.N) store32(p, r, row, col0);
+        if (p.out_mx == 0) {
+          if (row < p.M && col0 < p.N) store32(p, r, row, col0);
+        } else if (row - lane < p.M && col0 < p.N) {  // whole warps: the block dimension is padded to 32
+          store32_mx(p, r, row, col0, lane);
+        }
       }
       tc_fence_before();
       __syncwarp();
@@ -297,11 +368,11 @@ __global__ void __launch_bounds__(THREADS, 1)
 
 }  // namespace gemm_mx
 
-int32_t matmul_mx_execute(const cdl_mx_tensor* a, const cdl_mx_tensor* b, const cdl_tensor* d,
-                          float alpha, cudaStream_t stream) {
+static int32_t matmul_mx_run(const char* op, const cdl_mx_tensor* a, const cdl_mx_tensor* b,
+                             const cdl_tensor* d, const cdl_mx_tensor* d_mx, float alpha,
+                             cudaStream_t stream) {
   using namespace gemm_mx;
-  const char* op = "matmul (mxfp8)";
-  if (!a || !b || !d) return fail(CDL_ERR_INVALID, "%s: a, b and d are required", op);
+  if (!a || !b || (!d && !d_mx)) return fail(CDL_ERR_INVALID, "%s: a, b and d are required", op);
   if (a->format != CDL_MXFP8 || b->format != CDL_MXFP8)
     return fail(CDL_ERR_UNSUPPORTED, "%s: only MXFP8 operands are implemented", op);
   if (a->dim != CDL_MX_ROWWISE)
@@ -316,18 +387,24 @@ int32_t matmul_mx_execute(const cdl_mx_tensor* a, const cdl_mx_tensor* b, const 
                 op, M, K, static_cast<long long>(b->rows), N);
   CDL_CHECK(mx_check(op, "a", a, CDL_MX_ROWWISE, M, K));
   CDL_CHECK(mx_check(op, "b", b, CDL_MX_COLWISE, K, N));
-  if (d->rank != 2 || d->shape[0] != M || d->shape[1] != N)
-    return fail(CDL_ERR_INVALID, "%s: d must have shape [%lld, %lld]", op, M, N);
-  if (d->dtype != CDL_BF16 && d->dtype != CDL_F32)
-    return fail(CDL_ERR_UNSUPPORTED, "%s: the output must be f32 or bf16", op);
-  if (N > 1 && d->stride[1] != 1)
-    return fail(CDL_ERR_UNSUPPORTED, "%s: d must have contiguous rows", op);
+  if (d_mx) {
+    if (d_mx->dim != CDL_MX_ROWWISE && d_mx->dim != CDL_MX_COLWISE)
+      return fail(CDL_ERR_INVALID, "%s: unknown block dimension of the output", op);
+    CDL_CHECK(mx_check(op, "d", d_mx, d_mx->dim, M, N));
+  } else {
+    if (d->rank != 2 || d->shape[0] != M || d->shape[1] != N)
+      return fail(CDL_ERR_INVALID, "%s: d must have shape [%lld, %lld]", op, M, N);
+    if (d->dtype != CDL_BF16 && d->dtype != CDL_F32)
+      return fail(CDL_ERR_UNSUPPORTED, "%s: the output must be f32 or bf16", op);
+    if (N > 1 && d->stride[1] != 1)
+      return fail(CDL_ERR_UNSUPPORTED, "%s: d must have contiguous rows", op);
+    if ((reinterpret_cast<uintptr_t>(d->ptr) & (dtype_size(d->dtype) - 1)) != 0)
+      return fail(CDL_ERR_INVALID, "%s: d is not aligned to its element size", op);
+  }
   if (M == 0 || N == 0) return CDL_OK;
   if (K == 0) return fail(CDL_ERR_INVALID, "%s: K is zero", op);
   if (M > (1 << 30) || N > (1 << 30) || K > (1 << 30))
     return fail(CDL_ERR_UNSUPPORTED, "%s: dimension too large", op);
-  if ((reinterpret_cast<uintptr_t>(d->ptr) & (dtype_size(d->dtype) - 1)) != 0)
-    return fail(CDL_ERR_INVALID, "%s: d is not aligned to its element size", op);
 
   static std::once_flag attr_once[64];
   int dev = 0;
@@ -351,11 +428,17 @@ int32_t matmul_mx_execute(const cdl_mx_tensor* a, const cdl_mx_tensor* b, const 
   p.sf_k_tiles = p.k_tiles;  // ceil((K / 32) / 4)
   p.sfa = static_cast<const uint8_t*>(a->scale_factors);
   p.sfb = static_cast<const uint8_t*>(b->scale_factors);
-  p.d = d->ptr;
-  p.ldd = d->stride[0];
-  p.out_f32 = d->dtype == CDL_F32;
-  p.wide = (reinterpret_cast<uintptr_t>(d->ptr) & 31) == 0 &&
-           (M == 1 || (d->stride[0] * dtype_size(d->dtype)) % 32 == 0);
+  if (d_mx) {
+    p.out_mx = d_mx->dim == CDL_MX_ROWWISE ? 1 : 2;
+    p.out_values = static_cast<uint8_t*>(d_mx->values);
+    p.out_sf = static_cast<uint8_t*>(d_mx->scale_factors);
+  } else {
+    p.d = d->ptr;
+    p.ldd = d->stride[0];
+    p.out_f32 = d->dtype == CDL_F32;
+    p.wide = (reinterpret_cast<uintptr_t>(d->ptr) & 31) == 0 &&
+             (M == 1 || (d->stride[0] * dtype_size(d->dtype)) % 32 == 0);
+  }
   p.alpha = alpha;
   p.status = device_status_ptr();
   if (!p.status) return fail(CDL_ERR_CUDA, "cannot resolve the device status word");
@@ -380,6 +463,17 @@ int32_t matmul_mx_execute(const cdl_mx_tensor* a, const cdl_mx_tensor* b, const 
   return CDL_OK;
 }
 
+int32_t matmul_mx_execute(const cdl_mx_tensor* a, const cdl_mx_tensor* b, const cdl_tensor* d,
+                          float alpha, cudaStream_t stream) {
+  return matmul_mx_run("matmul (mxfp8)", a, b, d, nullptr, alpha, stream);
+}
+
+int32_t matmul_mx_out_execute(const cdl_mx_tensor* a, const cdl_mx_tensor* b, const cdl_mx_tensor* d,
+                              float alpha, cudaStream_t stream) {
+  if (!d) return fail(CDL_ERR_INVALID, "matmul (mxfp8, block-scaled output): d is required");
+  return matmul_mx_run("matmul (mxfp8, block-scaled output)", a, b, nullptr, d, alpha, stream);
+}
+
 }  // namespace cdl
 
 extern "C" {
@@ -387,6 +481,11 @@ extern "C" {
 int32_t cdl_b200_matmul_mx(const cdl_mx_tensor* a, const cdl_mx_tensor* b, const cdl_tensor* d,
                            float alpha, cdl_stream stream) {
   return cdl::matmul_mx_execute(a, b, d, alpha, static_cast<cudaStream_t>(stream));
+}
+
+int32_t cdl_b200_matmul_mx_out(const cdl_mx_tensor* a, const cdl_mx_tensor* b, const cdl_mx_tensor* d,
+                               float alpha, cdl_stream stream) {
+  return cdl::matmul_mx_out_execute(a, b, d, alpha, static_cast<cudaStream_t>(stream));
 }
 
 }  // extern "C"

@@ -64,6 +64,8 @@ int32_t rmsnorm_fwd_mx_execute(const cdl_tensor* x, const cdl_tensor* scale, con
                                const cdl_tensor* r_inv, cudaStream_t stream);
 int32_t matmul_mx_execute(const cdl_mx_tensor* a, const cdl_mx_tensor* b, const cdl_tensor* d,
                           float alpha, cudaStream_t stream);
+int32_t matmul_mx_out_execute(const cdl_mx_tensor* a, const cdl_mx_tensor* b, const cdl_mx_tensor* d,
+                              float alpha, cudaStream_t stream);
 
 // Packed row-major views.
 inline cdl_tensor view2(const void* p, int32_t dt, long long r, long long c) {

@@ -199,9 +199,17 @@ int32_t cdl_b200_rmsnorm_fwd_mx(const cdl_tensor* x, const cdl_tensor* scale, co
  * (crates/cleandl/src/execgraph/ops/matmul.rs:808-838, forwarded to cuBLASLt block scaling by the
  * reference; tests crates/cleandl/tests/matmul.rs:1041-1060).  A is rowwise [M, K], B is colwise
  * [K, N] (both K-contiguous), D is bf16 or f32 [M, N] with packed rows; accumulation is f32.
- * K % 32 == 0.  Block-scaled OUTPUTS (MatmulOutput::BlockScaled) are not implemented. */
+ * K % 32 == 0. */
 int32_t cdl_b200_matmul_mx(const cdl_mx_tensor* a, const cdl_mx_tensor* b, const cdl_tensor* d,
                            float alpha, cdl_stream stream);
+
+/* The same product with a block-scaled output: MatmulOutput::BlockScaled { Mxfp8, dim }
+ * (crates/cleandl/src/execgraph/ops/matmul.rs:826-834; test crates/cleandl/tests/matmul.rs:
+ * 1083-1115).  d is an MXFP8 tensor of logical shape [M, N], rowwise (N % 32 == 0) or colwise
+ * (M % 32 == 0); the f32 accumulator times alpha is quantised block by block in the epilogue as
+ * by cdl_b200_mx_quantize (without the intermediate rounding to bf16). */
+int32_t cdl_b200_matmul_mx_out(const cdl_mx_tensor* a, const cdl_mx_tensor* b, const cdl_mx_tensor* d,
+                               float alpha, cdl_stream stream);
 
 /* ---- Flash attention -------------------------------------------------------------------
  * Replaces AttentionExecutor::execute (crates/cleandl/src/execgraph/ops/attention/exec.rs:

@@ -245,3 +245,43 @@ def test_matmul_mx_many_tiles_and_alpha(cdl, gpu_ok):
     assert torch.equal(d2, d1 * 2)
     # repeated runs give identical bits (a fixed accumulation order)
     assert torch.equal(cdl.mx.matmul_mx(qa, qb, out_dtype=torch.float32), d1)
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("m,k,n", [(256, 128, 192), (100, 96, 64), (1024, 512, 2048)])
+@pytest.mark.parametrize("dim", [ROW, COL])
+def test_matmul_mx_block_scaled_output(cdl, gpu_ok, m, k, n, dim):
+    """The reference's block_scaled_outputs test (crates/cleandl/tests/matmul.rs:1083-1115): the
+    dequantised output against the f64 product of the dequantised operands, within half an ulp of
+    E4M3 relative to the block scale plus the accumulation error."""
+    if dim == COL and m % 32:
+        pytest.skip("a colwise output needs a row count that is a multiple of 32")
+    gen = torch.Generator().manual_seed(100)
+    a = torch.randn(m, k, generator=gen).to(torch.bfloat16)
+    b = torch.randn(k, n, generator=gen).to(torch.bfloat16)
+    qa, _ = cdl.mx.quantize(a.cuda(), rowwise=True)
+    _, qb = cdl.mx.quantize(b.cuda(), rowwise=False, colwise=True)
+    da, _ = mx_ref.dequantize(qa.values.cpu().numpy(), qa.scale_factors.cpu().numpy(), m, k, ROW)
+    db, _ = mx_ref.dequantize(qb.values.cpu().numpy(), qb.scale_factors.cpu().numpy(), k, n, COL)
+    expected = da.astype(np.float64) @ db.astype(np.float64)
+    bound = np.abs(da).astype(np.float64) @ np.abs(db).astype(np.float64)
+    d = cdl.mx.matmul_mx_out(qa, qb, dim=dim)
+    assert d.dim == dim and (d.rows, d.cols) == (m, n)
+    got, es = mx_ref.dequantize(d.values.cpu().numpy(), d.scale_factors.cpu().numpy(), m, n, dim)
+    assert_all_close(f"mxfp8 output dim {dim}", got, expected,
+                     2.0 ** -4 * np.abs(expected) + 2.0 ** -9 * es + 1e-4 * bound)
+    # the output equals quantising the plain f32 product of the same kernel (same accumulation
+    # order), bit for bit
+    plain = cdl.mx.matmul_mx(qa, qb, out_dtype=torch.float32)
+    v_ref, s_ref = mx_ref.quantize(to_f32(plain), dim)
+    assert np.array_equal(d.values.cpu().numpy(), v_ref)
+    assert np.array_equal(valid_scales(d, d.scale_factors.cpu().numpy()), valid_scales(d, s_ref))
+    # and feeds a following matmul: (A.B) rowwise times a colwise C
+    if dim == ROW and n % 32 == 0:
+        c = torch.randn(n, 64, generator=gen).to(torch.bfloat16)
+        _, qc = cdl.mx.quantize(c.cuda(), rowwise=False, colwise=True)
+        dc, _ = mx_ref.dequantize(qc.values.cpu().numpy(), qc.scale_factors.cpu().numpy(), n, 64, COL)
+        e2 = got.astype(np.float64) @ dc.astype(np.float64)
+        b2 = np.abs(got).astype(np.float64) @ np.abs(dc).astype(np.float64)
+        out2 = cdl.mx.matmul_mx(d, qc, out_dtype=torch.float32)
+        assert_all_close("chained", to_f32(out2), e2, oracle.matmul_tolerance(e2, b2, False))
