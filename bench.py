@@ -404,24 +404,32 @@ def run_kernel(args) -> None:
     elif k == "gemm_mx":
         # D[m, n] = A[m, k] . B[k, n] with MXFP8 operands (quantised once, outside the timing)
         m, n, kk = args.m, args.n, args.k
-        qa, _ = cdl.mx.quantize(rnd(m, kk), rowwise=True)
-        _, qb = cdl.mx.quantize(rnd(kk, n), rowwise=False, colwise=True)
+        if args.mx_format == "nvfp4":
+            qa, _ = cdl.mx.quantize(rnd(m, kk), rowwise=True, fmt=cdl.mx.NVFP4)
+            qb = cdl.mx.quantize(rnd(n, kk), rowwise=True, fmt=cdl.mx.NVFP4)[0].transposed()
+        else:
+            qa, _ = cdl.mx.quantize(rnd(m, kk), rowwise=True)
+            _, qb = cdl.mx.quantize(rnd(kk, n), rowwise=False, colwise=True)
         d = torch.zeros(m, n, device=dev, dtype=torch.bfloat16)
         fns = [lambda: cdl.mx.matmul_mx(qa, qb, out=d)]
         work, unit, peak = 2.0 * m * n * kk, "TFLOP/s", peaks["bf16_burst"]
-        desc = f"gemm_mx (MXFP8 operands, bf16 out) {m}x{n}x{kk}"
+        desc = f"gemm_mx ({args.mx_format.upper()} operands, bf16 out) {m}x{n}x{kk}"
     elif k == "norm_fwd_mx":
         rows, cols = args.rows, args.cols
         nbuf = max(2, int(300e6 // (rows * cols * 2)) + 1)
         xs = [rnd(rows, cols) for _ in range(nbuf)]
         w = (1 + 0.02 * torch.randn(cols, device=dev, generator=gen)).to(torch.bfloat16)
-        outs = [cdl.mx.norm_fwd_mx(x, w, colwise=args.colwise, save_stats=True) for x in xs]
-        fns = [(lambda x=x, o=o: cdl.mx.norm_fwd_mx(x, w, colwise=args.colwise, save_stats=True, out=o))
+        fmt = cdl.mx.NVFP4 if args.mx_format == "nvfp4" else cdl.mx.MXFP8
+        outs = [cdl.mx.norm_fwd_mx(x, w, colwise=args.colwise, save_stats=True, fmt=fmt) for x in xs]
+        fns = [(lambda x=x, o=o: cdl.mx.norm_fwd_mx(x, w, colwise=args.colwise, save_stats=True, out=o,
+                                                    fmt=fmt))
                for x, o in zip(xs, outs)]
         n_out = 2 if args.colwise else 1
-        work = 2.0 * rows * cols + n_out * rows * cols * (1 + 1 / 32) + 2 * cols + 4 * rows
+        per_elem = (0.5 + 1 / 16) if args.mx_format == "nvfp4" else (1 + 1 / 32)
+        work = 2.0 * rows * cols + n_out * rows * cols * per_elem + 2 * cols + 4 * rows
         unit, peak = "GB/s", peaks["hbm"]
-        desc = f"norm_fwd_mx x[{rows},{cols}] bf16 -> MXFP8 rowwise" + (" + colwise" if args.colwise else "")
+        desc = f"norm_fwd_mx x[{rows},{cols}] bf16 -> {args.mx_format.upper()} rowwise" + (
+            " + colwise" if args.colwise else "")
     else:
         bsz, s_, h = args.batch, args.seq, args.heads
         q, kx, v, do = (rnd(bsz, s_, h, 128) for _ in range(4))
@@ -571,6 +579,8 @@ def main() -> None:
     ap.add_argument("--accumulate", action="store_true", help="gemm: D (f32) += A.B, the wgrad form")
     ap.add_argument("--residual", action="store_true",
                     help="norm_bwd: add a residual gradient into dx (the form the block uses)")
+    ap.add_argument("--mx-format", default="mxfp8", choices=["mxfp8", "nvfp4"],
+                    help="gemm_mx / norm_fwd_mx: the block-scaled format")
     ap.add_argument("--colwise", action="store_true",
                     help="norm_fwd_mx: also produce the colwise (transposed-block) output")
     ap.add_argument("--rows", type=int, default=16384)

@@ -39,23 +39,39 @@ constexpr int A_BYTES = BM * BK;
 constexpr int B_BYTES = BN * BK;
 constexpr int SF_TILE = 512;  // scales of 128 rows x 4 blocks
 constexpr int SF_OFF = A_BYTES + B_BYTES;
-constexpr int STAGE_BYTES = 50 * 1024;  // A, B, 3 scale tiles, padded to keep stages 1024-aligned
-static_assert(SF_OFF + 3 * SF_TILE <= STAGE_BYTES, "stage layout");
 constexpr int THREADS = 320;  // warp 0 TMA, warp 1 MMA, warps 2-9 epilogue
 constexpr int EPI_WARPS = 8;
 constexpr int TMEM_COLS = 512;
-constexpr int ACC1_COL = 240;  // accumulator 0 starts at column 0, accumulator 1 here
-constexpr int SFA_COL = 496, SFB_COL = 500;
 constexpr int RASTER_W = 8;
-constexpr size_t SMEM_BYTES = 1024 + STAGES * STAGE_BYTES + 256;
-static_assert(SMEM_BYTES <= 232448, "exceeds the 227 KiB of shared memory a CTA can opt in to");
+
+// What differs between the two formats.  A stage is always 128 bytes of K per operand row and four
+// instructions.  MXFP8: 128 elements, one scale byte per row and instruction, so one 512-byte
+// scale tile per 128 rows and stage, the instruction picks its byte.  NVFP4: 256 elements, four
+// scale bytes per row and instruction, so four scale tiles per 128 rows and stage and 48 scale
+// columns in tensor memory; the accumulators then overlap by 48 columns.
+template <int FP4>
+struct Cfg {
+  static constexpr int SFT = FP4 ? 4 : 1;        // scale tiles per 128 operand rows per stage
+  static constexpr int K_STAGE = FP4 ? 256 : 128;  // elements of K per stage
+  static constexpr int K_MMA = FP4 ? 64 : 32;      // elements of K per instruction
+  static constexpr int STAGE_BYTES = (FP4 ? 54 : 50) * 1024;  // A, B, 3 * SFT scale tiles; 1024-aligned
+  static constexpr int OVERLAP = FP4 ? 48 : 16;    // columns the two accumulators share
+  static constexpr int OVL_CHUNKS = FP4 ? 2 : 1;   // 32-column chunks that cover them
+  static constexpr int ACC1_COL = 256 - OVERLAP;   // accumulator 0 at column 0, accumulator 1 here
+  static constexpr int SFA_COL = 512 - 12 * SFT;
+  static constexpr int SFB_COL = SFA_COL + 4 * SFT;
+  static constexpr size_t SMEM_BYTES = 1024 + STAGES * STAGE_BYTES + 256;
+  static_assert(SF_OFF + 3 * SFT * SF_TILE <= STAGE_BYTES, "stage layout");
+  static_assert(SMEM_BYTES <= 232448, "exceeds the 227 KiB of shared memory a CTA can opt in to");
+  static_assert(ACC1_COL + 256 <= SFA_COL && ACC1_COL % 16 == 0, "tensor memory layout");
+};
 
 struct Params {
   int M, N, K;
   int num_m_tiles, num_n_tiles, num_tiles, k_tiles;
   const uint8_t* sfa;  // scale tiles of A: [ceil(M/128)][sf_k_tiles][512]
   const uint8_t* sfb;  // scale tiles of B: [ceil(N/128)][sf_k_tiles][512]
-  int sf_k_tiles;      // ceil(K / 128)
+  int sf_k_tiles;      // ceil(blocks along K / 4)
   void* d;
   long long ldd;
   int out_f32, wide;
@@ -187,9 +203,13 @@ __device__ __forceinline__ void store32_mx(const Params& p, const uint32_t (&r)[
   }
 }
 
+template <int FP4>
 __global__ void __launch_bounds__(THREADS, 1)
-    gemm_mxfp8_kernel(const __grid_constant__ CUtensorMap tmap_a,
-                      const __grid_constant__ CUtensorMap tmap_b, const Params p) {
+    gemm_mx_kernel(const __grid_constant__ CUtensorMap tmap_a,
+                   const __grid_constant__ CUtensorMap tmap_b, const Params p) {
+  using C = Cfg<FP4>;
+  constexpr int STAGE_BYTES = C::STAGE_BYTES;
+  constexpr int SFT = C::SFT;
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) &
                                              ~static_cast<uintptr_t>(1023));
@@ -248,16 +268,18 @@ __global__ void __launch_bounds__(THREADS, 1)
           uint8_t* sa = smem + s * STAGE_BYTES;
           uint8_t* sb = sa + A_BYTES;
           uint8_t* ssf = sa + SF_OFF;
-          mbar_arrive_expect_tx(&bars->full[s], A_BYTES + B_BYTES + (sfb2 ? 3 : 2) * SF_TILE);
-          const int k0 = kt * BK;
+          // scale tiles of this stage that exist (the K tail may hold fewer than SFT)
+          const uint32_t sf_bytes = static_cast<uint32_t>(min(SFT, p.sf_k_tiles - kt * SFT)) * SF_TILE;
+          mbar_arrive_expect_tx(&bars->full[s], A_BYTES + B_BYTES + (sfb2 ? 3 : 2) * sf_bytes);
+          const int k0 = kt * BK;  // byte coordinate along K
           tma_load_3d(sa, &tmap_a, &bars->full[s], k0, m0, 0);
           tma_load_3d(sb, &tmap_b, &bars->full[s], k0, n0, 0);
-          bulk_load_1d(ssf, sfa_row + static_cast<long long>(kt) * SF_TILE, SF_TILE, &bars->full[s]);
-          bulk_load_1d(ssf + SF_TILE, sfb_row + static_cast<long long>(kt) * SF_TILE, SF_TILE,
-                       &bars->full[s]);
+          const long long sf_off = static_cast<long long>(kt) * SFT * SF_TILE;
+          bulk_load_1d(ssf, sfa_row + sf_off, sf_bytes, &bars->full[s]);
+          bulk_load_1d(ssf + SFT * SF_TILE, sfb_row + sf_off, sf_bytes, &bars->full[s]);
           if (sfb2)
-            bulk_load_1d(ssf + 2 * SF_TILE,
-                         sfb_row + (static_cast<long long>(p.sf_k_tiles) + kt) * SF_TILE, SF_TILE,
+            bulk_load_1d(ssf + 2 * SFT * SF_TILE,
+                         sfb_row + static_cast<long long>(p.sf_k_tiles) * SF_TILE + sf_off, sf_bytes,
                          &bars->full[s]);
         }
       }
@@ -268,7 +290,7 @@ __global__ void __launch_bounds__(THREADS, 1)
       uint32_t it = 0;
       int t = 0;
       bool ok = true;
-      const uint32_t sfa_t = tmem_base + SFA_COL, sfb_t = tmem_base + SFB_COL;
+      const uint32_t sfa_t = tmem_base + C::SFA_COL, sfb_t = tmem_base + C::SFB_COL;
       for (int tile = blockIdx.x; tile < p.num_tiles && ok; tile += gridDim.x, ++t) {
         const int acc = t & 1;
         const uint32_t acc_ph = (t >> 1) & 1;
@@ -276,7 +298,7 @@ __global__ void __launch_bounds__(THREADS, 1)
         // the columns this accumulator shares with the previous tile's have been drained
         if (t > 0 && !mbar_wait(&bars->overlap_free, (t - 1) & 1, abort_word, 403)) break;
         tc_fence_after();
-        const uint32_t d_tmem = tmem_base + acc * ACC1_COL;
+        const uint32_t d_tmem = tmem_base + acc * C::ACC1_COL;
         for (int kt = 0; kt < p.k_tiles; ++kt, ++it) {
           const int s = it % STAGES;
           const uint32_t ph = (it / STAGES) & 1;
@@ -288,17 +310,31 @@ __global__ void __launch_bounds__(THREADS, 1)
           const uint32_t sa = smem_u32(smem + s * STAGE_BYTES);
           const uint32_t sb = sa + A_BYTES;
           const uint32_t ssf = sa + SF_OFF;
-          tmem_cp_32x128b_warpx4(sfa_t, smem_desc_rows16(ssf));
-          tmem_cp_32x128b_warpx4(sfb_t, smem_desc_rows16(ssf + SF_TILE));
-          tmem_cp_32x128b_warpx4(sfb_t + 4, smem_desc_rows16(ssf + 2 * SF_TILE));
-          const int kblocks = min(4, (p.K - kt * BK) / 32);  // K % 32 == 0; the tail has fewer
+          // K % K_MMA == 0; the tail stage issues only the instructions (and copies only the
+          // scale tiles) that exist
+          const int kblocks = min(4, (p.K - kt * C::K_STAGE) / C::K_MMA);
+          const int sf_tiles = FP4 ? kblocks : 1;
+#pragma unroll
+          for (int j = 0; j < SFT; ++j) {
+            if (j < sf_tiles) {
+              // tile j of A; tile j of B's two 128-row chunks, side by side for instruction j
+              tmem_cp_32x128b_warpx4(sfa_t + 4 * j, smem_desc_rows16(ssf + j * SF_TILE));
+              tmem_cp_32x128b_warpx4(sfb_t + 8 * j, smem_desc_rows16(ssf + (SFT + j) * SF_TILE));
+              tmem_cp_32x128b_warpx4(sfb_t + 8 * j + 4,
+                                     smem_desc_rows16(ssf + (2 * SFT + j) * SF_TILE));
+            }
+          }
 #pragma unroll
           for (int k = 0; k < 4; ++k) {
             if (k < kblocks) {
               const uint64_t da = smem_desc_sw128(sa + k * 32, 16, 1024);
               const uint64_t db = smem_desc_sw128(sb + k * 32, 16, 1024);
-              umma_mxf8_ss(d_tmem, da, db, make_idesc_mxf8(BM, BN, k, k), sfa_t, sfb_t,
-                           (kt | k) != 0 ? 1u : 0u);
+              if (FP4)
+                umma_nvf4_ss(d_tmem, da, db, make_idesc_nvf4(BM, BN), sfa_t + 4 * k, sfb_t + 8 * k,
+                             (kt | k) != 0 ? 1u : 0u);
+              else
+                umma_mxf8_ss(d_tmem, da, db, make_idesc_mxf8(BM, BN, k, k), sfa_t, sfb_t,
+                             (kt | k) != 0 ? 1u : 0u);
             }
           }
           umma_commit(&bars->empty[s]);
@@ -318,21 +354,22 @@ __global__ void __launch_bounds__(THREADS, 1)
       const uint32_t acc_ph = (t >> 1) & 1;
       if (!mbar_wait(&bars->acc_full[acc], acc_ph, abort_word, 405)) break;
       tc_fence_after();
-      const uint32_t t_row = tmem_base + (static_cast<uint32_t>(quad * 32) << 16) + acc * ACC1_COL + half * 128;
+      const uint32_t t_row = tmem_base + (static_cast<uint32_t>(quad * 32) << 16) + acc * C::ACC1_COL + half * 128;
       const int row = tm * BM + quad * 32 + lane;
       const int col_base = tn * BN + half * 128;
-      // The 16 columns shared with the other accumulator are the last of accumulator 0 (its
-      // second half's chunk 3) and the first of accumulator 1 (its first half's chunk 0): the
-      // half that owns them reads that chunk first and frees the columns.
+      // The columns shared with the other accumulator are the last of accumulator 0 (the end of
+      // its second half) and the first of accumulator 1 (the start of its first half): the half
+      // that owns them reads those chunks first (accumulator 0: from the last chunk backwards)
+      // and frees the columns.
       const bool owner = half == (acc == 0 ? 1 : 0);
-      const int first = (owner && acc == 0) ? 3 : 0;
+      const bool backwards = owner && acc == 0;
 #pragma unroll 1
       for (int i = 0; i < 4; ++i) {
-        const int ch = (first + i) & 3;
+        const int ch = backwards ? 3 - i : i;
         uint32_t r[32];
         tmem_ld32(t_row + ch * 32, r);
         tmem_wait_ld();
-        if (i == 0 && owner) {
+        if (i == C::OVL_CHUNKS - 1 && owner) {
           tc_fence_before();
           __syncwarp();
           if (lane == 0) mbar_arrive(&bars->overlap_free);
@@ -373,8 +410,10 @@ static int32_t matmul_mx_run(const char* op, const cdl_mx_tensor* a, const cdl_m
                              cudaStream_t stream) {
   using namespace gemm_mx;
   if (!a || !b || (!d && !d_mx)) return fail(CDL_ERR_INVALID, "%s: a, b and d are required", op);
-  if (a->format != CDL_MXFP8 || b->format != CDL_MXFP8)
-    return fail(CDL_ERR_UNSUPPORTED, "%s: only MXFP8 operands are implemented", op);
+  if ((a->format != CDL_MXFP8 && a->format != CDL_NVFP4) || b->format != a->format)
+    return fail(CDL_ERR_UNSUPPORTED,
+                "%s: both operands must be MXFP8, or both NVFP4 (mixed block-scaled formats are not "
+                "accepted, as in the reference)", op);
   if (a->dim != CDL_MX_ROWWISE)
     return fail(CDL_ERR_INVALID,
                 "%s: block-scaled A must have its blocks along the contraction dimension (rowwise)", op);
@@ -387,9 +426,16 @@ static int32_t matmul_mx_run(const char* op, const cdl_mx_tensor* a, const cdl_m
                 op, M, K, static_cast<long long>(b->rows), N);
   CDL_CHECK(mx_check(op, "a", a, CDL_MX_ROWWISE, M, K));
   CDL_CHECK(mx_check(op, "b", b, CDL_MX_COLWISE, K, N));
+  const bool fp4 = a->format == CDL_NVFP4;
+  if (fp4 && K % 64 != 0)
+    return fail(CDL_ERR_UNSUPPORTED, "%s: NVFP4 operands need K to be a multiple of 64 (got %lld)", op, K);
+  if (fp4 && d_mx)
+    return fail(CDL_ERR_UNSUPPORTED, "%s: a block-scaled output with NVFP4 operands is not implemented", op);
   if (d_mx) {
     if (d_mx->dim != CDL_MX_ROWWISE && d_mx->dim != CDL_MX_COLWISE)
       return fail(CDL_ERR_INVALID, "%s: unknown block dimension of the output", op);
+    if (d_mx->format != CDL_MXFP8)
+      return fail(CDL_ERR_UNSUPPORTED, "%s: only MXFP8 block-scaled outputs are implemented", op);
     CDL_CHECK(mx_check(op, "d", d_mx, d_mx->dim, M, N));
   } else {
     if (d->rank != 2 || d->shape[0] != M || d->shape[1] != N)
@@ -411,8 +457,11 @@ static int32_t matmul_mx_run(const char* op, const cdl_mx_tensor* a, const cdl_m
   CDL_CUDA(cudaGetDevice(&dev));
   cudaError_t attr_err = cudaSuccess;
   std::call_once(attr_once[dev & 63], [&] {
-    attr_err = cudaFuncSetAttribute(gemm_mxfp8_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                    static_cast<int>(SMEM_BYTES));
+    attr_err = cudaFuncSetAttribute(gemm_mx_kernel<0>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                    static_cast<int>(Cfg<0>::SMEM_BYTES));
+    if (attr_err == cudaSuccess)
+      attr_err = cudaFuncSetAttribute(gemm_mx_kernel<1>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                      static_cast<int>(Cfg<1>::SMEM_BYTES));
   });
   if (attr_err != cudaSuccess)
     return fail(CDL_ERR_CUDA, "cudaFuncSetAttribute failed: %s", cudaGetErrorString(attr_err));
@@ -424,8 +473,10 @@ static int32_t matmul_mx_run(const char* op, const cdl_mx_tensor* a, const cdl_m
   p.num_m_tiles = static_cast<int>((M + BM - 1) / BM);
   p.num_n_tiles = static_cast<int>((N + BN - 1) / BN);
   p.num_tiles = p.num_m_tiles * p.num_n_tiles;
-  p.k_tiles = static_cast<int>((K + BK - 1) / BK);
-  p.sf_k_tiles = p.k_tiles;  // ceil((K / 32) / 4)
+  const long long k_stage = fp4 ? Cfg<1>::K_STAGE : Cfg<0>::K_STAGE;
+  const long long k_bytes = fp4 ? K / 2 : K;  // bytes of a row of values
+  p.k_tiles = static_cast<int>((K + k_stage - 1) / k_stage);
+  p.sf_k_tiles = static_cast<int>((K / (fp4 ? 16 : 32) + 3) / 4);
   p.sfa = static_cast<const uint8_t*>(a->scale_factors);
   p.sfb = static_cast<const uint8_t*>(b->scale_factors);
   if (d_mx) {
@@ -445,20 +496,21 @@ static int32_t matmul_mx_run(const char* op, const cdl_mx_tensor* a, const cdl_m
 
   CUtensorMap ta, tb;
   {
-    const uint64_t dims[3] = {static_cast<uint64_t>(K), static_cast<uint64_t>(M), 1};
-    const uint64_t strides[3] = {1, static_cast<uint64_t>(K), static_cast<uint64_t>(K) * M};
+    const uint64_t dims[3] = {static_cast<uint64_t>(k_bytes), static_cast<uint64_t>(M), 1};
+    const uint64_t strides[3] = {1, static_cast<uint64_t>(k_bytes), static_cast<uint64_t>(k_bytes) * M};
     const uint32_t box[3] = {BK, BM, 1};
     CDL_CHECK(encode_tmap(&ta, a->values, TMAP_U8, 3, dims, strides, box, true));
   }
   {
-    const uint64_t dims[3] = {static_cast<uint64_t>(K), static_cast<uint64_t>(N), 1};
-    const uint64_t strides[3] = {1, static_cast<uint64_t>(K), static_cast<uint64_t>(K) * N};
+    const uint64_t dims[3] = {static_cast<uint64_t>(k_bytes), static_cast<uint64_t>(N), 1};
+    const uint64_t strides[3] = {1, static_cast<uint64_t>(k_bytes), static_cast<uint64_t>(k_bytes) * N};
     const uint32_t box[3] = {BK, BN, 1};
     CDL_CHECK(encode_tmap(&tb, b->values, TMAP_U8, 3, dims, strides, box, true));
   }
   const int grid = p.num_tiles < sm_count() ? p.num_tiles : sm_count();
   ProfileScope ps(PROF_GEMM, 2.0 * M * N * K, stream);
-  gemm_mxfp8_kernel<<<grid, THREADS, SMEM_BYTES, stream>>>(ta, tb, p);
+  if (fp4) gemm_mx_kernel<1><<<grid, THREADS, Cfg<1>::SMEM_BYTES, stream>>>(ta, tb, p);
+  else gemm_mx_kernel<0><<<grid, THREADS, Cfg<0>::SMEM_BYTES, stream>>>(ta, tb, p);
   CDL_CUDA(cudaGetLastError());
   return CDL_OK;
 }

@@ -23,11 +23,12 @@
 // 32-element block reduce their amax with two shuffles.  With the colwise output a CTA owns 32
 // consecutive rows (one warp each): the bf16 results of 1024 columns go through shared memory and
 // one thread per column quantises the 32 rows of its block and stores one 32-byte sector of the
-// transposed output.  NVFP4 is not implemented.
+// transposed output.  NVFP4 (NormOutput::Nvfp4Rowwise): rowwise only, see nvfp4_rows_kernel.
 #include "host.h"
 #include "ops.h"
 #include "ptx.cuh"
 
+#include <cuda_fp4.h>
 #include <cuda_fp8.h>
 
 #include <mutex>
@@ -377,22 +378,94 @@ __global__ void __launch_bounds__(1024, 1) mx_rowcol_tile_kernel(const Params p)
   }
 }
 
-// One thread per block of 32 values: y[r, c] = value * 2^(e - 127).
+// NVFP4 rowwise output (NormOutput::Nvfp4Rowwise, no global scale): blocks of 16 elements, scale
+// = amax / 6 rounded to nearest E4M3, elements x / scale rounded to nearest E2M1 (ties to even,
+// saturating), two per byte; a block whose scale rounds to zero stores zeros
+// (crates/cleandl-specialized-kernels/src/utils/block_scale.rs:28-31, 55-66, with an exact
+// division where the reference multiplies by an approximate reciprocal).  A lane's 8 elements are
+// half a block: one shuffle.  x is read twice (the second time from cache).
+template <bool NORM>
+__global__ void __launch_bounds__(256, 2) nvfp4_rows_kernel(const Params p) {
+  const int lane = threadIdx.x & 31;
+  const int row_blocks = p.cols / 16;
+  const float inv_cols = 1.0f / static_cast<float>(p.cols);
+  const long long warp_global = static_cast<long long>(blockIdx.x) * 8 + (threadIdx.x >> 5);
+  const long long warp_stride = static_cast<long long>(gridDim.x) * 8;
+  for (long long row = warp_global; row < p.rows; row += warp_stride) {
+    const __nv_bfloat16* xr = p.x + row * p.ldx;
+    float r = 1.0f;
+    if (NORM) {
+      float ss = 0.f;
+      for (int c = lane * 8; c < p.cols; c += 256) {
+        float f[8];
+        unpack8(*reinterpret_cast<const uint4*>(xr + c), f);
+#pragma unroll
+        for (int j = 0; j < 8; ++j) ss = fmaf(f[j], f[j], ss);
+      }
+#pragma unroll
+      for (int o = 16; o > 0; o >>= 1) ss += __shfl_xor_sync(0xffffffffu, ss, o);
+      r = rsqrtf(ss * inv_cols + p.eps);
+      if (lane == 0 && p.r_inv != nullptr) p.r_inv[row * p.r_inv_stride] = r;
+    }
+    for (int c0 = 0; c0 < p.cols; c0 += 256) {  // warp-uniform: the shuffle needs all lanes
+      const int c = c0 + lane * 8;
+      const bool active = c < p.cols;  // cols % 16 == 0: both lanes of a block agree
+      float f[8];
+#pragma unroll
+      for (int j = 0; j < 8; ++j) f[j] = 0.f;
+      if (active) apply_norm8<NORM>(p, *reinterpret_cast<const uint4*>(xr + c), c, r, f);
+      float amax = 0.f;
+#pragma unroll
+      for (int j = 0; j < 8; ++j) amax = fmaxf(amax, fabsf(f[j]));
+      amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, 1));
+      if (active) {
+        const __nv_fp8_storage_t sbits =
+            __nv_cvt_float_to_fp8(__fdiv_rn(amax, 6.0f), __NV_SATFINITE, __NV_E4M3);
+        const float sc = __half2float(__half(__nv_cvt_fp8_to_halfraw(sbits, __NV_E4M3)));
+        uint32_t out = 0;
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+          const float a = sc != 0.f ? __fdiv_rn(f[2 * j], sc) : 0.f;
+          const float b = sc != 0.f ? __fdiv_rn(f[2 * j + 1], sc) : 0.f;
+          out |= static_cast<uint32_t>(__nv_cvt_float2_to_fp4x2(make_float2(a, b), __NV_E2M1, cudaRoundNearest))
+                 << (8 * j);
+        }
+        *reinterpret_cast<uint32_t*>(p.row_values + (row * p.cols + c) / 2) = out;
+        if ((lane & 1) == 0)
+          p.row_sf[sf_index(static_cast<int>(row), c / 16, row_blocks)] = sbits;
+      }
+    }
+  }
+}
+
+// One thread per block: y[r, c] = value * scale (MXFP8: 32 E4M3 values, UE8M0 scale; NVFP4: 16
+// E2M1 values in 8 bytes, E4M3 scale).
 __global__ void mx_dequantize_kernel(const uint8_t* __restrict__ values,
                                      const uint8_t* __restrict__ sf, int outer, int inner,
-                                     int colwise, void* y, int y_f32, long long ldy) {
-  const int blocks = inner / BLOCK;
+                                     int colwise, int fp4, void* y, int y_f32, long long ldy) {
+  const int block = fp4 ? 16 : BLOCK;
+  const int blocks = inner / block;
   const long long idx = static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x;
   if (idx >= static_cast<long long>(outer) * blocks) return;
   const int o = static_cast<int>(idx / blocks), b = static_cast<int>(idx % blocks);
   const uint32_t e = sf[sf_index(o, b, blocks)];
-  const float s = e == 0xFFu ? __int_as_float(0x7FC00000)
-                             : __uint_as_float(e != 0 ? e << 23 : 0x00400000u);
-  const uint8_t* src = values + static_cast<long long>(o) * inner + b * BLOCK;
-  for (int j = 0; j < BLOCK; ++j) {
-    const __half_raw h = __nv_cvt_fp8_to_halfraw(src[j], __NV_E4M3);
-    const float v = __half2float(__half(h)) * s;
-    const long long r = colwise ? b * BLOCK + j : o, c = colwise ? o : b * BLOCK + j;
+  float s;
+  if (fp4) s = __half2float(__half(__nv_cvt_fp8_to_halfraw(static_cast<__nv_fp8_storage_t>(e), __NV_E4M3)));
+  else s = e == 0xFFu ? __int_as_float(0x7FC00000) : __uint_as_float(e != 0 ? e << 23 : 0x00400000u);
+  const long long first = static_cast<long long>(o) * inner + b * block;  // element index
+  for (int j = 0; j < block; ++j) {
+    float v;
+    if (fp4) {
+      const uint8_t byte = values[(first + j) >> 1];
+      const uint32_t nib = (j & 1) ? byte >> 4 : byte & 0xF;
+      const float mag = (nib & 7) < 2 ? 0.5f * (nib & 7) : (nib & 7) < 4 ? 0.5f * (nib & 7)
+                        : (nib & 7) == 4 ? 2.f : (nib & 7) == 5 ? 3.f : (nib & 7) == 6 ? 4.f : 6.f;
+      v = (nib & 8) ? -mag : mag;
+    } else {
+      v = __half2float(__half(__nv_cvt_fp8_to_halfraw(values[first + j], __NV_E4M3)));
+    }
+    v *= s;
+    const long long r = colwise ? b * block + j : o, c = colwise ? o : b * block + j;
     if (y_f32) static_cast<float*>(y)[r * ldy + c] = v;
     else static_cast<__nv_bfloat16*>(y)[r * ldy + c] = __float2bfloat16_rn(v);
   }
@@ -402,28 +475,26 @@ __global__ void mx_dequantize_kernel(const uint8_t* __restrict__ values,
 
 int32_t mx_layout(int32_t format, int32_t dim, long long rows, long long cols, size_t* values_bytes,
                   size_t* scale_bytes) {
-  if (format != CDL_MXFP8)
-    return fail(CDL_ERR_UNSUPPORTED, "block-scaled format %d is not implemented (only MXFP8)", format);
+  if (format != CDL_MXFP8 && format != CDL_NVFP4)
+    return fail(CDL_ERR_INVALID, "block-scaled tensors: unknown format %d", format);
   if (dim != CDL_MX_ROWWISE && dim != CDL_MX_COLWISE)
     return fail(CDL_ERR_INVALID, "block-scaled tensors: unknown block dimension %d", dim);
   if (rows < 0 || cols < 0) return fail(CDL_ERR_INVALID, "block-scaled tensors: negative shape");
   const long long outer = dim == CDL_MX_ROWWISE ? rows : cols;
   const long long inner = dim == CDL_MX_ROWWISE ? cols : rows;
-  if (inner % mx::BLOCK != 0)
+  const int block = format == CDL_MXFP8 ? 32 : 16;
+  if (inner % block != 0)
     return fail(CDL_ERR_INVALID,
-                "block dimension of shape [%lld, %lld] must be a multiple of the MXFP8 block size 32",
-                rows, cols);
-  if (values_bytes) *values_bytes = static_cast<size_t>(outer) * inner;
+                "block dimension of shape [%lld, %lld] must be a multiple of the %s block size %d",
+                rows, cols, format == CDL_MXFP8 ? "MXFP8" : "NVFP4", block);
+  if (values_bytes) *values_bytes = static_cast<size_t>(outer) * inner / (format == CDL_MXFP8 ? 1 : 2);
   if (scale_bytes)
-    *scale_bytes = static_cast<size_t>((outer + 127) / 128 * 128) * ((inner / mx::BLOCK + 3) / 4 * 4);
+    *scale_bytes = static_cast<size_t>((outer + 127) / 128 * 128) * ((inner / block + 3) / 4 * 4);
   return CDL_OK;
 }
 
 int32_t mx_check(const char* op, const char* name, const cdl_mx_tensor* t, int32_t dim, long long rows,
                  long long cols) {
-  if (t->format != CDL_MXFP8)
-    return fail(CDL_ERR_UNSUPPORTED, "%s: %s: block-scaled format %d is not implemented (only MXFP8)",
-                op, name, t->format);
   if (t->dim != dim)
     return fail(CDL_ERR_INVALID, "%s: %s must have its blocks along the %s", op, name,
                 dim == CDL_MX_ROWWISE ? "rows (rowwise)" : "columns (colwise)");
@@ -455,15 +526,24 @@ static int32_t mx_rows_run(const char* op, const cdl_tensor* x, const cdl_tensor
     return fail(CDL_ERR_UNSUPPORTED, "%s: x must have packed rows (contiguous columns)", op);
   if ((reinterpret_cast<uintptr_t>(x->ptr) & 15) != 0 || (rows > 1 && x->stride[0] % 8 != 0))
     return fail(CDL_ERR_UNSUPPORTED, "%s: x must be 16-byte aligned (pointer and row stride)", op);
-  if (y_row && cols % BLOCK != 0)
+  if (y_row && y_row->format == CDL_MXFP8 && cols % BLOCK != 0)
     return fail(CDL_ERR_INVALID,
                 "%s: the number of columns (%lld) must be a multiple of the MXFP8 block size 32", op,
+                cols);
+  if (y_row && y_row->format == CDL_NVFP4 && cols % 16 != 0)
+    return fail(CDL_ERR_INVALID,
+                "%s: the number of columns (%lld) must be a multiple of the NVFP4 block size 16", op,
                 cols);
   if (cols % 8 != 0)
     return fail(CDL_ERR_UNSUPPORTED, "%s: the number of columns (%lld) must be a multiple of 8", op,
                 cols);
   if (y_row) CDL_CHECK(mx_check(op, "rowwise output", y_row, CDL_MX_ROWWISE, rows, cols));
   if (y_col) CDL_CHECK(mx_check(op, "colwise output", y_col, CDL_MX_COLWISE, rows, cols));
+  const bool fp4 = y_row && y_row->format == CDL_NVFP4;
+  if (y_col && (fp4 || y_col->format != CDL_MXFP8))
+    return fail(CDL_ERR_UNSUPPORTED,
+                "%s: a colwise output exists for MXFP8 only (the outputs are MXFP8 rowwise, MXFP8 "
+                "rowwise and colwise, or NVFP4 rowwise)", op);
   for (const cdl_tensor* v : {scale, bias}) {
     if (!v) continue;
     if (v->rank != 1 || v->shape[0] != cols || v->dtype != CDL_BF16 || v->stride[0] != 1 ||
@@ -498,7 +578,12 @@ static int32_t mx_rows_run(const char* op, const cdl_tensor* x, const cdl_tensor
   // algorithmic bytes: x read, one byte per element and output, one scale byte per 32
   const double bytes = 2.0 * rows * cols + ((y_row ? 1 : 0) + (y_col ? 1 : 0)) * (rows * cols * (1.0 + 1.0 / 32));
   ProfileScope ps(PROF_NORM_FWD, bytes, stream);
-  if (y_col) {
+  if (fp4) {
+    const long long want = (rows + 7) / 8;
+    const unsigned grid = static_cast<unsigned>(want < 16LL * sm_count() ? want : 16LL * sm_count());
+    if (norm) nvfp4_rows_kernel<true><<<grid, 256, 0, stream>>>(p);
+    else nvfp4_rows_kernel<false><<<grid, 256, 0, stream>>>(p);
+  } else if (y_col) {
     int dev = 0;
     CDL_CUDA(cudaGetDevice(&dev));
     const size_t tile_bytes = 32 * static_cast<size_t>(cols + 8) * 2;
@@ -573,10 +658,11 @@ int32_t mx_dequantize_execute(const cdl_mx_tensor* x, const cdl_tensor* y, cudaS
   const long long outer = colwise ? x->cols : x->rows, inner = colwise ? x->rows : x->cols;
   if (outer > INT32_MAX / 2 || inner > INT32_MAX / 2)
     return fail(CDL_ERR_UNSUPPORTED, "%s: shape too large", op);
-  const long long n = outer * (inner / mx::BLOCK);
+  const bool fp4 = x->format == CDL_NVFP4;
+  const long long n = outer * (inner / (fp4 ? 16 : mx::BLOCK));
   mx::mx_dequantize_kernel<<<static_cast<unsigned>((n + 255) / 256), 256, 0, stream>>>(
       static_cast<const uint8_t*>(x->values), static_cast<const uint8_t*>(x->scale_factors),
-      static_cast<int>(outer), static_cast<int>(inner), colwise ? 1 : 0, y->ptr,
+      static_cast<int>(outer), static_cast<int>(inner), colwise ? 1 : 0, fp4 ? 1 : 0, y->ptr,
       y->dtype == CDL_F32 ? 1 : 0, y->stride[0]);
   CDL_CUDA(cudaGetLastError());
   return CDL_OK;

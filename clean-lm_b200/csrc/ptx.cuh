@@ -401,6 +401,24 @@ __host__ __device__ constexpr uint32_t make_idesc_mxf8(int m, int n, uint32_t a_
   return (b_sf_byte << 4) | (static_cast<uint32_t>(n >> 3) << 17) | (1u << 23) |
          (static_cast<uint32_t>(m >> 4) << 24) | (a_sf_byte << 29);
 }
+// The NVFP4 form: FP4 E2M1 operands packed two per byte (K = 64 per instruction), four UE4M3
+// scales per row and instruction (blocks of 16): the whole 32-bit word of the scale column.
+__device__ __forceinline__ void umma_nvf4_ss(uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc,
+                                             uint32_t idesc, uint32_t sfa_tmem, uint32_t sfb_tmem,
+                                             uint32_t accumulate) {
+  asm volatile(
+      "{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %6, 0;\n\t"
+      "tcgen05.mma.cta_group::1.kind::mxf4nvf4.block_scale.block16 [%0], %1, %2, %3, [%4], [%5], p;\n\t}\n" ::"r"(
+          d_tmem),
+      "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(sfa_tmem), "r"(sfb_tmem), "r"(accumulate)
+      : "memory");
+}
+// Instruction descriptor of kind::mxf4nvf4: A / B format 1 (E2M1) in bits 7-9 / 10-12, both
+// K-major, UE4M3 scales (bit 23 clear), N >> 3 in bits 17-22, M >> 4 in bits 24-28.
+__host__ __device__ constexpr uint32_t make_idesc_nvf4(int m, int n) {
+  return (1u << 7) | (1u << 10) | (static_cast<uint32_t>(n >> 3) << 17) |
+         (static_cast<uint32_t>(m >> 4) << 24);
+}
 // Shared memory -> tensor memory copy of 32 rows x 16 bytes, replicated to the four lane
 // quadrants: the 512-byte scale-factor tile of 128 rows x 4 blocks lands in 4 columns with
 // row r on lane r % 32 of column r / 32.  Ordered with the MMAs of the issuing thread.

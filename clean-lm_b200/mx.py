@@ -16,9 +16,9 @@ import torch
 from . import _lib
 from ._lib import CdlMxTensor, check, lib, ref, tensor_arg
 
-MXFP8 = _lib.CDL_MXFP8
+MXFP8, NVFP4 = _lib.CDL_MXFP8, _lib.CDL_NVFP4
 ROWWISE, COLWISE = _lib.CDL_MX_ROWWISE, _lib.CDL_MX_COLWISE
-BLOCK = 32
+BLOCK = 32  # MXFP8; NVFP4 blocks hold 16 elements
 
 
 def _stream() -> ctypes.c_void_p:
@@ -34,8 +34,8 @@ def layout_bytes(rows: int, cols: int, dim: int, fmt: int = MXFP8):
 
 @dataclass
 class MxTensor:
-    """values: uint8 [rows, cols] (rowwise) or [cols, rows] (colwise); scale_factors: uint8, the
-    128 x 4 tiled layout, flat."""
+    """values: uint8 [rows, cols] (rowwise) or [cols, rows] (colwise), for NVFP4 with two elements
+    per byte along the last dimension; scale_factors: uint8, the 128 x 4 tiled layout, flat."""
 
     values: torch.Tensor
     scale_factors: torch.Tensor
@@ -45,13 +45,20 @@ class MxTensor:
     format: int = MXFP8
 
     @staticmethod
-    def empty(rows: int, cols: int, dim: int, device="cuda", zero_scales: bool = False) -> "MxTensor":
-        vb, sb = layout_bytes(rows, cols, dim)
+    def empty(rows: int, cols: int, dim: int, device="cuda", zero_scales: bool = False,
+              fmt: int = MXFP8) -> "MxTensor":
+        vb, sb = layout_bytes(rows, cols, dim, fmt)
         outer, inner = (rows, cols) if dim == ROWWISE else (cols, rows)
-        values = torch.empty(outer, inner, dtype=torch.uint8, device=device)
+        values = torch.empty(outer, inner // (2 if fmt == NVFP4 else 1), dtype=torch.uint8, device=device)
         assert values.numel() == vb
         make = torch.zeros if zero_scales else torch.empty
-        return MxTensor(values, make(sb, dtype=torch.uint8, device=device), dim, rows, cols)
+        return MxTensor(values, make(sb, dtype=torch.uint8, device=device), dim, rows, cols, fmt)
+
+    def transposed(self) -> "MxTensor":
+        """The same buffers seen as the transposed logical matrix: a rowwise [r, c] tensor is a
+        colwise [c, r] tensor (`into_transposed`, crates/cleandl/tests/matmul.rs:939-943)."""
+        return MxTensor(self.values, self.scale_factors, COLWISE if self.dim == ROWWISE else ROWWISE,
+                        self.cols, self.rows, self.format)
 
     def arg(self) -> CdlMxTensor:
         return CdlMxTensor(self.values.data_ptr(), self.scale_factors.data_ptr(), self.format, self.dim,
@@ -62,13 +69,14 @@ def _mx_arg(t: Optional[MxTensor]):
     return None if t is None else t.arg()
 
 
-def quantize(x: torch.Tensor, rowwise: bool = True, colwise: bool = False):
-    """bf16 [rows, cols] -> (rowwise MxTensor or None, colwise MxTensor or None)."""
+def quantize(x: torch.Tensor, rowwise: bool = True, colwise: bool = False, fmt: int = MXFP8):
+    """bf16 [rows, cols] -> (rowwise MxTensor or None, colwise MxTensor or None).  NVFP4 has the
+    rowwise form only; a colwise NVFP4 operand is `quantize(x.T.contiguous(), fmt=NVFP4)[0].transposed()`."""
     if not x.is_cuda:
         raise _lib.CdlError(-1, "operands must live in device memory (there is no CPU path)")
     rows, cols = x.shape
-    yr = MxTensor.empty(rows, cols, ROWWISE, x.device, zero_scales=True) if rowwise else None
-    yc = MxTensor.empty(rows, cols, COLWISE, x.device, zero_scales=True) if colwise else None
+    yr = MxTensor.empty(rows, cols, ROWWISE, x.device, zero_scales=True, fmt=fmt) if rowwise else None
+    yc = MxTensor.empty(rows, cols, COLWISE, x.device, zero_scales=True, fmt=fmt) if colwise else None
     tx, ar, ac = tensor_arg(x), _mx_arg(yr), _mx_arg(yc)
     check(lib.cdl_b200_mx_quantize(ref(tx), ref(ar), ref(ac), _stream()))
     return yr, yc
@@ -90,8 +98,10 @@ class NormMxOutputs:
 
 def norm_fwd_mx(x: torch.Tensor, scale: Optional[torch.Tensor] = None,
                 bias: Optional[torch.Tensor] = None, eps: float = 1e-6, colwise: bool = False,
-                save_stats: bool = False, out: Optional[NormMxOutputs] = None) -> NormMxOutputs:
-    """RMSNorm forward with `NormOutput::Mxfp8Rowwise` (or `...RowwiseAndColwise`) outputs.
+                save_stats: bool = False, out: Optional[NormMxOutputs] = None,
+                fmt: int = MXFP8) -> NormMxOutputs:
+    """RMSNorm forward with `NormOutput::Mxfp8Rowwise` (or `...RowwiseAndColwise`) outputs, or with
+    `NormOutput::Nvfp4Rowwise` (`fmt=NVFP4`).
     `out` reuses the buffers of an earlier call (the engine's pre-allocated outputs)."""
     if not x.is_cuda:
         raise _lib.CdlError(-1, "operands must live in device memory (there is no CPU path)")
@@ -101,8 +111,8 @@ def norm_fwd_mx(x: torch.Tensor, scale: Optional[torch.Tensor] = None,
     if out is not None:
         yr, yc, r_inv = out.y, out.y_col, out.r_inv
     else:
-        yr = MxTensor.empty(rows, cols, ROWWISE, x.device, zero_scales=True)
-        yc = MxTensor.empty(rows, cols, COLWISE, x.device, zero_scales=True) if colwise else None
+        yr = MxTensor.empty(rows, cols, ROWWISE, x.device, zero_scales=True, fmt=fmt)
+        yc = MxTensor.empty(rows, cols, COLWISE, x.device, zero_scales=True, fmt=fmt) if colwise else None
         r_inv = torch.empty(rows, dtype=torch.float32, device=x.device) if save_stats else None
     tx, ts, tb, tr = tensor_arg(x), tensor_arg(scale), tensor_arg(bias), tensor_arg(r_inv)
     ar, ac = _mx_arg(yr), _mx_arg(yc)

@@ -158,7 +158,11 @@ int32_t cdl_b200_rmsnorm_bwd_static(const cdl_tensor* x, const cdl_tensor* dy,
  * scale of block (o, b) is byte ((o / 128) * ceil(B / 4) + b / 4) * 512 + (o % 32) * 16 +
  * ((o % 128) / 32) * 4 + b % 4 of a buffer of round_up(outer, 128) * round_up(B, 4) bytes
  * (crates/cleandl/tests/common/mod.rs:124-129).  values must be 32-byte and scale_factors 16-byte
- * aligned.  NVFP4 (MxFormat::Nvfp4) is not implemented: CDL_ERR_UNSUPPORTED. */
+ * aligned.
+ * NVFP4 (MxFormat::Nvfp4, without a global scale factor): blocks of 16 FP4 E2M1 elements, two per
+ * byte along the block dimension (the even element in the low nibble), with one E4M3 scale;
+ * same scale layout with B = blocks of 16.  Implemented: rowwise quantisation / RMSNorm output,
+ * dequantisation, matmul operands. */
 typedef enum { CDL_MXFP8 = 0, CDL_NVFP4 = 1 } cdl_mx_format;
 typedef enum { CDL_MX_ROWWISE = 0, CDL_MX_COLWISE = 1 } cdl_mx_dim;
 typedef struct {
@@ -178,7 +182,9 @@ int32_t cdl_b200_mx_layout(int32_t format, int32_t dim, int64_t rows, int64_t co
  * to a power of two, element = x / scale rounded to nearest E4M3, saturating
  * (crates/cleandl-specialized-kernels/src/utils/block_scale.rs:24-55; the host quantiser of
  * crates/cleandl/tests/matmul.rs:885-952 gives the same bits).  Scale bytes of the padding are
- * not written. */
+ * not written.  NVFP4 (y_rowwise only): scale = amax / 6 rounded to nearest E4M3, element = x / scale
+ * rounded to nearest E2M1, ties to even, saturating; zeros when the scale rounds to zero
+ * (block_scale.rs:28-31, 55-66). */
 int32_t cdl_b200_mx_quantize(const cdl_tensor* x, const cdl_mx_tensor* y_rowwise,
                              const cdl_mx_tensor* y_colwise, cdl_stream stream);
 
@@ -189,7 +195,8 @@ int32_t cdl_b200_mx_dequantize(const cdl_mx_tensor* x, const cdl_tensor* y, cdl_
  * NULL) or ::Mxfp8RowwiseAndColwise (crates/cleandl/src/execgraph/ops/norm/mod.rs:33-62; kernel
  * crates/cleandl-specialized-kernels/src/kernels/norm/forward.rs:509-785).  Operands as for
  * cdl_b200_rmsnorm_fwd; the result is rounded to bf16 and then quantised as by
- * cdl_b200_mx_quantize.  The colwise output needs rows % 32 == 0 (norm/mod.rs validation). */
+ * cdl_b200_mx_quantize.  The colwise output needs rows % 32 == 0 (norm/mod.rs validation).
+ * An NVFP4 y_rowwise (and no y_colwise) gives NormOutput::Nvfp4Rowwise. */
 int32_t cdl_b200_rmsnorm_fwd_mx(const cdl_tensor* x, const cdl_tensor* scale, const cdl_tensor* bias,
                                 float eps, const cdl_mx_tensor* y_rowwise,
                                 const cdl_mx_tensor* y_colwise, const cdl_tensor* r_inv,
@@ -199,7 +206,8 @@ int32_t cdl_b200_rmsnorm_fwd_mx(const cdl_tensor* x, const cdl_tensor* scale, co
  * (crates/cleandl/src/execgraph/ops/matmul.rs:808-838, forwarded to cuBLASLt block scaling by the
  * reference; tests crates/cleandl/tests/matmul.rs:1041-1060).  A is rowwise [M, K], B is colwise
  * [K, N] (both K-contiguous), D is bf16 or f32 [M, N] with packed rows; accumulation is f32.
- * K % 32 == 0. */
+ * K % 32 == 0.  Both operands NVFP4 (InputKind::Mx(Nvfp4), tests :1063-1080) works the same way
+ * with K % 64 == 0; mixed formats are rejected like in the reference (:569-571). */
 int32_t cdl_b200_matmul_mx(const cdl_mx_tensor* a, const cdl_mx_tensor* b, const cdl_tensor* d,
                            float alpha, cdl_stream stream);
 

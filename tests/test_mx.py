@@ -82,8 +82,8 @@ def test_layout_through_the_c_abi(cdl):
                     cdl.mx.layout_bytes(rows, cols, dim)
                 continue
             assert cdl.mx.layout_bytes(rows, cols, dim) == (outer * inner, sf_rows * sf_cols)
-    with pytest.raises(cdl._lib.CdlError, match="not implemented"):
-        cdl.mx.layout_bytes(128, 128, ROW, fmt=cdl._lib.CDL_NVFP4)
+    with pytest.raises(cdl._lib.CdlError, match="unknown format"):
+        cdl.mx.layout_bytes(128, 128, ROW, fmt=7)
 
 
 def test_host_validation_needs_no_gpu(cdl):
@@ -110,9 +110,6 @@ def test_host_validation_needs_no_gpu(cdl):
     b = L.CdlMxTensor(512, 1024, L.CDL_MXFP8, L.CDL_MX_COLWISE, 96, 128)
     st = L.lib.cdl_b200_matmul_mx(ctypes.byref(a), ctypes.byref(b), ctypes.byref(d), 1.0, None)
     assert st == -1 and "contraction" in L.last_error()
-    a = L.CdlMxTensor(512, 1024, L.CDL_NVFP4, L.CDL_MX_ROWWISE, 128, 64)
-    st = L.lib.cdl_b200_matmul_mx(ctypes.byref(a), ctypes.byref(b), ctypes.byref(d), 1.0, None)
-    assert st == -2 and "MXFP8" in L.last_error()
 
 
 # ------------------------------------------------------------------------------ GPU parity
@@ -285,3 +282,99 @@ def test_matmul_mx_block_scaled_output(cdl, gpu_ok, m, k, n, dim):
         b2 = np.abs(got).astype(np.float64) @ np.abs(dc).astype(np.float64)
         out2 = cdl.mx.matmul_mx(d, qc, out_dtype=torch.float32)
         assert_all_close("chained", to_f32(out2), e2, oracle.matmul_tolerance(e2, b2, False))
+
+
+# ------------------------------------------------------------------------------ NVFP4
+def test_nvfp4_oracle_pins():
+    assert mx_ref.e2m1_decode(np.arange(16)).tolist() == [0, .5, 1, 1.5, 2, 3, 4, 6, -0., -.5, -1, -1.5, -2, -3, -4, -6]
+    # nearest with ties to the even code, saturating
+    assert mx_ref.e2m1_encode(np.array([0.25, 0.75, 1.25, 1.75, 2.5, 3.5, 5.0, 7.0, -0.3, 0.2])).tolist() == \
+        [0, 2, 2, 4, 4, 6, 6, 7, 9, 0]
+    rng = np.random.default_rng(3)
+    m = rng.standard_normal((64, 128)).astype(np.float32)
+    for dim in (ROW, COL):
+        v, s = mx_ref.quantize_nvfp4(m, dim)
+        outer, inner, sf_rows, sf_cols = mx_ref.layout(64, 128, dim, mx_ref.NVFP4)
+        assert v.shape == (outer, inner // 2) and s.shape == (sf_rows * sf_cols,)
+        d, es = mx_ref.dequantize_nvfp4(v, s, 64, 128, dim)
+        # the tolerance the reference's tests give an NVFP4 result (crates/cleandl/tests/norm.rs:144)
+        assert np.all(np.abs(d - m) <= 0.34 * np.abs(m) + 0.5 * es)
+
+
+def nv_valid_scales(t, scales_np):
+    outer, inner, _, _ = mx_ref.layout(t.rows, t.cols, t.dim, mx_ref.NVFP4)
+    blocks = inner // 16
+    o, b = np.meshgrid(np.arange(outer), np.arange(blocks), indexing="ij")
+    return scales_np[mx_ref.sf_index(o, b, blocks)]
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("rows,cols", [(1, 128), (37, 4096), (300, 2048), (128, 8192), (64, 144), (5, 1024)])
+def test_nvfp4_quantize_is_bit_exact(cdl, gpu_ok, rows, cols):
+    x = rand_bf16(rows, cols, 20, spread=1.0)
+    x[0, :16] = 0
+    yr, _ = cdl.mx.quantize(x.cuda(), rowwise=True, fmt=cdl.mx.NVFP4)
+    v_ref, s_ref = mx_ref.quantize_nvfp4(to_f32(x), ROW)
+    assert np.array_equal(yr.values.cpu().numpy(), v_ref)
+    assert np.array_equal(nv_valid_scales(yr, yr.scale_factors.cpu().numpy()), nv_valid_scales(yr, s_ref))
+    d_ref, _ = mx_ref.dequantize_nvfp4(v_ref, s_ref, rows, cols, ROW)
+    assert np.array_equal(to_f32(cdl.mx.dequantize(yr)), d_ref)
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("rows,cols", [(1, 128), (37, 4096), (300, 2048), (100, 7168), (5, 1024)])
+@pytest.mark.parametrize("affine", ["none", "scale_bias"])
+def test_norm_fwd_nvfp4(cdl, gpu_ok, rows, cols, affine):
+    """NormOutput::Nvfp4Rowwise: |got - y| <= 0.34 |y| + 0.5 * block scale (tests/norm.rs:144)."""
+    gen = torch.Generator().manual_seed(1)
+    x = (torch.randn(rows, cols, generator=gen) * 2.0 + 0.5).to(torch.bfloat16)
+    scale = (torch.rand(cols, generator=gen) + 0.5).to(torch.bfloat16) if affine != "none" else None
+    bias = torch.randn(cols, generator=gen).to(torch.bfloat16) if affine != "none" else None
+    out = cdl.mx.norm_fwd_mx(x.cuda(), None if scale is None else scale.cuda(),
+                             None if bias is None else bias.cuda(), 1e-6, save_stats=True,
+                             fmt=cdl.mx.NVFP4)
+    y_ref, r_ref = oracle.rmsnorm_fwd(to_f32(x), None if scale is None else to_f32(scale),
+                                      None if bias is None else to_f32(bias), 1e-6)
+    assert_all_close("r_inv", to_f32(out.r_inv), r_ref, oracle.abs_rel_tolerance(r_ref, 1e-6, 1e-4))
+    got, es = mx_ref.dequantize_nvfp4(out.y.values.cpu().numpy(), out.y.scale_factors.cpu().numpy(),
+                                      rows, cols, ROW)
+    assert_all_close("y", got, y_ref, 0.34 * np.abs(y_ref) + 0.5 * es + 1e-30)
+    v_ref, _ = mx_ref.quantize_nvfp4(oracle.bf16_round(y_ref.astype(np.float32)), ROW)
+    assert (out.y.values.cpu().numpy() == v_ref).mean() > 0.97
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("m,k,n", [(128, 256, 64), (128, 64, 256), (192, 320, 160), (512, 2048, 768),
+                                   (2048, 512, 4864)])
+@pytest.mark.parametrize("out", ["bf16", "f32"])
+def test_matmul_nvfp4(cdl, gpu_ok, m, k, n, out):
+    """The reference's nvfp4_inputs test (crates/cleandl/tests/matmul.rs:1063-1080)."""
+    gen = torch.Generator().manual_seed(90)
+    a = torch.randn(m, k, generator=gen).to(torch.bfloat16)
+    b = torch.randn(k, n, generator=gen).to(torch.bfloat16)
+    qa, _ = cdl.mx.quantize(a.cuda(), rowwise=True, fmt=cdl.mx.NVFP4)
+    qb = cdl.mx.quantize(b.cuda().T.contiguous(), rowwise=True, fmt=cdl.mx.NVFP4)[0].transposed()
+    assert (qb.dim, qb.rows, qb.cols) == (COL, k, n)
+    da, _ = mx_ref.dequantize_nvfp4(qa.values.cpu().numpy(), qa.scale_factors.cpu().numpy(), m, k, ROW)
+    db, _ = mx_ref.dequantize_nvfp4(qb.values.cpu().numpy(), qb.scale_factors.cpu().numpy(), k, n, COL)
+    d = cdl.mx.matmul_mx(qa, qb, out_dtype=torch.bfloat16 if out == "bf16" else torch.float32)
+    expected = da.astype(np.float64) @ db.astype(np.float64)
+    bound = np.abs(da).astype(np.float64) @ np.abs(db).astype(np.float64)
+    assert_all_close(f"nvfp4 {m}x{k}x{n} -> {out}", to_f32(d), expected,
+                     oracle.matmul_tolerance(expected, bound, out == "bf16"))
+
+
+def test_nvfp4_host_validation(cdl):
+    L = cdl._lib
+    a = L.CdlMxTensor(512, 1024, L.CDL_NVFP4, L.CDL_MX_ROWWISE, 128, 96)
+    b = L.CdlMxTensor(512, 1024, L.CDL_NVFP4, L.CDL_MX_COLWISE, 96, 128)
+    d = L.CdlTensor(ptr=2048, dtype=L.CDL_BF16, rank=2)
+    d.shape[0], d.shape[1], d.stride[0], d.stride[1] = 128, 128, 128, 1
+    st = L.lib.cdl_b200_matmul_mx(ctypes.byref(a), ctypes.byref(b), ctypes.byref(d), 1.0, None)
+    assert st == -2 and "multiple of 64" in L.last_error()
+    b = L.CdlMxTensor(512, 1024, L.CDL_MXFP8, L.CDL_MX_COLWISE, 96, 128)
+    st = L.lib.cdl_b200_matmul_mx(ctypes.byref(a), ctypes.byref(b), ctypes.byref(d), 1.0, None)
+    assert st == -2 and "mixed" in L.last_error()
+    assert cdl.mx.layout_bytes(128, 256, ROW, fmt=cdl.mx.NVFP4) == (128 * 128, 128 * 16)
+    with pytest.raises(cdl._lib.CdlError, match="block size 16"):
+        cdl.mx.layout_bytes(128, 40, ROW, fmt=cdl.mx.NVFP4)
