@@ -363,23 +363,37 @@ __global__ void __launch_bounds__(THREADS, 1)
       // and frees the columns.
       const bool owner = half == (acc == 0 ? 1 : 0);
       const bool backwards = owner && acc == 0;
-#pragma unroll 1
-      for (int i = 0; i < 4; ++i) {
-        const int ch = backwards ? 3 - i : i;
-        uint32_t r[32];
-        tmem_ld32(t_row + ch * 32, r);
-        tmem_wait_ld();
-        if (i == C::OVL_CHUNKS - 1 && owner) {
-          tc_fence_before();
-          __syncwarp();
-          if (lane == 0) mbar_arrive(&bars->overlap_free);
-        }
+      auto emit = [&](const uint32_t (&r)[32], int ch) {
         const int col0 = col_base + ch * 32;
         if (p.out_mx == 0) {
           if (row < p.M && col0 < p.N) store32(p, r, row, col0);
         } else if (row - lane < p.M && col0 < p.N) {  // whole warps: the block dimension is padded to 32
           store32_mx(p, r, row, col0, lane);
         }
+      };
+      int i = 0;
+      if (owner) {
+        // every shared chunk is in registers before the first store: the next tile's first MMA
+        // waits for this arrival, and a chunk's global stores would sit on that path
+        uint32_t r0[32], r1[32];
+        const int ch0 = backwards ? 3 : 0, ch1 = backwards ? 2 : 1;
+        tmem_ld32(t_row + ch0 * 32, r0);
+        if (C::OVL_CHUNKS == 2) tmem_ld32(t_row + ch1 * 32, r1);
+        tmem_wait_ld();
+        tc_fence_before();
+        __syncwarp();
+        if (lane == 0) mbar_arrive(&bars->overlap_free);
+        emit(r0, ch0);
+        if (C::OVL_CHUNKS == 2) emit(r1, ch1);
+        i = C::OVL_CHUNKS;
+      }
+#pragma unroll 1
+      for (; i < 4; ++i) {
+        const int ch = backwards ? 3 - i : i;
+        uint32_t r[32];
+        tmem_ld32(t_row + ch * 32, r);
+        tmem_wait_ld();
+        emit(r, ch);
       }
       tc_fence_before();
       __syncwarp();
