@@ -26,6 +26,9 @@
 
 #include <cuda_fp8.h>
 
+#include <stdlib.h>
+#include <string.h>
+
 #include <mutex>
 
 namespace cdl {
@@ -417,6 +420,261 @@ __global__ void __launch_bounds__(THREADS, 1)
   if (threadIdx.x == 0 && *abort_word != 0) atomicExch(p.status, *abort_word);
 }
 
+// ------------------------------------------------------------------------------------------
+// CTA-pair variant (cluster of two, tcgen05.mma.cta_group::2, 256 x 256 tiles).  The one-CTA
+// kernel above is bound by the L2 -> SM operand traffic (48 KiB per stage per SM, measured
+// 12.6 TB/s in aggregate); a pair splits B between its CTAs, so a stage is A (16 KiB) + half of B
+// (16 KiB) per SM.  Each CTA also brings the scale tiles it needs into its own shared memory: A's
+// for its own 128 rows and B's for all 256 columns (every CTA's tensor core multiplies its rows
+// with the whole B).  They come through a tensor map over the scale buffer ([tiles * 2][256]
+// bytes, a tile = two rows) because the cta_group::2 form of the load can credit the LEADER's
+// barrier; tcgen05.cp.cta_group::2 then moves them into both CTAs' tensor memory, each from its
+// own shared memory.  The rest is the protocol of the bf16 pair kernel: the leader issues every
+// MMA and commits to both CTAs' barriers, the peer's epilogue warps arrive remotely.
+template <int FP4>
+struct PairCfg {
+  static constexpr int SFT = Cfg<FP4>::SFT;
+  static constexpr int HALF_B_BYTES = B_BYTES / 2;
+  static constexpr int SF_OFF = A_BYTES + HALF_B_BYTES;
+  static constexpr int SF_BYTES = 3 * SFT * SF_TILE;
+  static constexpr int STAGE_BYTES = SF_OFF + (FP4 ? 6 : 2) * 1024;  // 34 / 38 KiB, 1024-aligned
+  static constexpr int STAGES = FP4 ? 5 : 6;
+  static constexpr int TX_BYTES = A_BYTES + HALF_B_BYTES + SF_BYTES;  // per CTA and stage
+  static constexpr size_t SMEM_BYTES = 1024 + STAGES * STAGE_BYTES + 256;
+  static_assert(SF_OFF + SF_BYTES <= STAGE_BYTES, "stage layout");
+  static_assert(SMEM_BYTES <= 232448, "exceeds the 227 KiB of shared memory a CTA can opt in to");
+};
+
+struct PairBarriers {
+  uint64_t full[6];
+  uint64_t empty[6];
+  uint64_t acc_full[2];
+  uint64_t acc_empty[2];
+  uint64_t overlap_free;
+  uint32_t tmem_base;
+  int abort_word;
+};
+
+template <int FP4>
+__global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(THREADS, 1)
+    gemm_mx_pair_kernel(const __grid_constant__ CUtensorMap tmap_a,
+                        const __grid_constant__ CUtensorMap tmap_b,
+                        const __grid_constant__ CUtensorMap tmap_sfa,
+                        const __grid_constant__ CUtensorMap tmap_sfb, const Params p) {
+  using C = Cfg<FP4>;
+  using PC = PairCfg<FP4>;
+  constexpr int STAGE_BYTES = PC::STAGE_BYTES;
+  constexpr int NSTAGES = PC::STAGES;
+  constexpr int SFT = C::SFT;
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) &
+                                             ~static_cast<uintptr_t>(1023));
+  PairBarriers* bars = reinterpret_cast<PairBarriers*>(smem + NSTAGES * STAGE_BYTES);
+  volatile int* abort_word = &bars->abort_word;
+
+  const int warp = threadIdx.x >> 5;
+  const int lane = threadIdx.x & 31;
+  const uint32_t rank = cluster_ctarank();
+  const int cluster_id = blockIdx.x >> 1;
+  const int num_clusters = gridDim.x >> 1;
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < NSTAGES; ++s) {
+      mbar_init(&bars->full[s], 1);
+      mbar_init(&bars->empty[s], 1);
+    }
+    for (int i = 0; i < 2; ++i) {
+      mbar_init(&bars->acc_full[i], 1);
+      mbar_init(&bars->acc_empty[i], 2 * EPI_WARPS);  // both CTAs' epilogue warps; the leader's copy is used
+    }
+    mbar_init(&bars->overlap_free, 8);  // the four owning warps of each CTA
+    bars->abort_word = 0;
+    fence_mbar_init();
+  }
+  if (warp == 1) {
+    tmem_alloc_pair(&bars->tmem_base, TMEM_COLS);
+    tmem_relinquish_pair();
+  }
+  if (warp == 0 && lane == 0) {
+    tma_prefetch_desc(&tmap_a);
+    tma_prefetch_desc(&tmap_b);
+    tma_prefetch_desc(&tmap_sfa);
+    tma_prefetch_desc(&tmap_sfb);
+  }
+  tc_fence_before();
+  __syncthreads();
+  cluster_sync_all();  // both CTAs' barriers exist before anything signals across the pair
+  tc_fence_after();
+  const uint32_t tmem_base = bars->tmem_base;
+
+  if (warp == 0) {
+    // ------------------------------------------------------------ producer (both CTAs)
+    if (elect_one()) {
+      uint32_t it = 0;
+      bool ok = true;
+      for (int tile = cluster_id; tile < p.num_tiles && ok; tile += num_clusters) {
+        int tm, tn;
+        tile_coords(p, tile, tm, tn);
+        const int m0 = tm * 2 * BM + static_cast<int>(rank) * BM;
+        const int n0 = tn * BN + static_cast<int>(rank) * (BN / 2);
+        // first scale-tile rows (a tile is two 256-byte rows of the scale tensor map)
+        const int sfa_row = 2 * (tm * 2 + static_cast<int>(rank)) * p.sf_k_tiles;
+        const int sfb_row = 2 * (tn * 2) * p.sf_k_tiles;
+        for (int kt = 0; kt < p.k_tiles; ++kt, ++it) {
+          const int s = it % NSTAGES;
+          const uint32_t ph = (it / NSTAGES) & 1;
+          if (!mbar_wait(&bars->empty[s], ph ^ 1, abort_word, 411)) {
+            ok = false;
+            break;
+          }
+          uint8_t* sa = smem + s * STAGE_BYTES;
+          uint8_t* sb = sa + A_BYTES;
+          uint8_t* ssf = sa + PC::SF_OFF;
+          // Bytes of both CTAs land on the leader's barrier.  Every load moves its whole box
+          // (rows beyond a tensor are filled with zeros), so the count is a constant.
+          if (rank == 0) mbar_arrive_expect_tx(&bars->full[s], 2 * PC::TX_BYTES);
+          const uint32_t full_leader = mapa_shared(smem_u32(&bars->full[s]), 0);
+          const int k0 = kt * BK;  // byte coordinate along K
+          tma_load_3d_pair(sa, &tmap_a, full_leader, k0, m0, 0);
+          tma_load_3d_pair(sb, &tmap_b, full_leader, k0, n0, 0);
+          const int sf_k = 2 * kt * SFT;
+          tma_load_3d_pair(ssf, &tmap_sfa, full_leader, 0, sfa_row + sf_k, 0);
+          tma_load_3d_pair(ssf + SFT * SF_TILE, &tmap_sfb, full_leader, 0, sfb_row + sf_k, 0);
+          tma_load_3d_pair(ssf + 2 * SFT * SF_TILE, &tmap_sfb, full_leader, 0,
+                           sfb_row + 2 * p.sf_k_tiles + sf_k, 0);
+        }
+      }
+    }
+  } else if (warp == 1) {
+    // ------------------------------------------------------------ MMA issuer (leader CTA only)
+    if (rank == 0 && elect_one()) {
+      uint32_t it = 0;
+      int t = 0;
+      bool ok = true;
+      const uint32_t sfa_t = tmem_base + C::SFA_COL, sfb_t = tmem_base + C::SFB_COL;
+      for (int tile = cluster_id; tile < p.num_tiles && ok; tile += num_clusters, ++t) {
+        const int acc = t & 1;
+        const uint32_t acc_ph = (t >> 1) & 1;
+        if (!mbar_wait(&bars->acc_empty[acc], acc_ph ^ 1, abort_word, 412)) break;
+        if (t > 0 && !mbar_wait(&bars->overlap_free, (t - 1) & 1, abort_word, 413)) break;
+        tc_fence_after();
+        const uint32_t d_tmem = tmem_base + acc * C::ACC1_COL;
+        for (int kt = 0; kt < p.k_tiles; ++kt, ++it) {
+          const int s = it % NSTAGES;
+          const uint32_t ph = (it / NSTAGES) & 1;
+          if (!mbar_wait(&bars->full[s], ph, abort_word, 414)) {
+            ok = false;
+            break;
+          }
+          tc_fence_after();
+          const uint32_t sa = smem_u32(smem + s * STAGE_BYTES);
+          const uint32_t sb = sa + A_BYTES;
+          const uint32_t ssf = sa + PC::SF_OFF;
+          const int kblocks = min(4, (p.K - kt * C::K_STAGE) / C::K_MMA);
+          const int sf_tiles = FP4 ? kblocks : 1;
+#pragma unroll
+          for (int j = 0; j < SFT; ++j) {
+            if (j < sf_tiles) {
+              tmem_cp_32x128b_warpx4_pair(sfa_t + 4 * j, smem_desc_rows16(ssf + j * SF_TILE));
+              tmem_cp_32x128b_warpx4_pair(sfb_t + 8 * j, smem_desc_rows16(ssf + (SFT + j) * SF_TILE));
+              tmem_cp_32x128b_warpx4_pair(sfb_t + 8 * j + 4,
+                                          smem_desc_rows16(ssf + (2 * SFT + j) * SF_TILE));
+            }
+          }
+#pragma unroll
+          for (int k = 0; k < 4; ++k) {
+            if (k < kblocks) {
+              const uint64_t da = smem_desc_sw128(sa + k * 32, 16, 1024);
+              const uint64_t db = smem_desc_sw128(sb + k * 32, 16, 1024);
+              if (FP4)
+                umma_nvf4_ss_pair(d_tmem, da, db, make_idesc_nvf4(2 * BM, BN), sfa_t + 4 * k,
+                                  sfb_t + 8 * k, (kt | k) != 0 ? 1u : 0u);
+              else
+                umma_mxf8_ss_pair(d_tmem, da, db, make_idesc_mxf8(2 * BM, BN, k, k), sfa_t, sfb_t,
+                                  (kt | k) != 0 ? 1u : 0u);
+            }
+          }
+          const uint32_t e = smem_u32(&bars->empty[s]);
+          umma_commit_pair(e);                  // own producer
+          umma_commit_pair(mapa_shared(e, 1));  // the peer's producer
+        }
+        if (ok) {
+          const uint32_t f = smem_u32(&bars->acc_full[acc]);
+          umma_commit_pair(f);
+          umma_commit_pair(mapa_shared(f, 1));
+        }
+      }
+    }
+  } else {
+    // ------------------------------------------------------------ epilogue (warps 2..9, both CTAs)
+    const int quad = warp & 3;
+    const int half = (warp - 2) >> 2;
+    const uint32_t ovl_leader = mapa_shared(smem_u32(&bars->overlap_free), 0);
+    int t = 0;
+    for (int tile = cluster_id; tile < p.num_tiles; tile += num_clusters, ++t) {
+      int tm, tn;
+      tile_coords(p, tile, tm, tn);
+      const int acc = t & 1;
+      const uint32_t acc_ph = (t >> 1) & 1;
+      if (!mbar_wait(&bars->acc_full[acc], acc_ph, abort_word, 415)) break;
+      tc_fence_after();
+      const uint32_t t_row = tmem_base + (static_cast<uint32_t>(quad * 32) << 16) + acc * C::ACC1_COL + half * 128;
+      const int row = tm * 2 * BM + static_cast<int>(rank) * BM + quad * 32 + lane;
+      const int col_base = tn * BN + half * 128;
+      const bool owner = half == (acc == 0 ? 1 : 0);
+      const bool backwards = owner && acc == 0;
+      auto emit = [&](const uint32_t (&r)[32], int ch) {
+        const int col0 = col_base + ch * 32;
+        if (p.out_mx == 0) {
+          if (row < p.M && col0 < p.N) store32(p, r, row, col0);
+        } else if (row - lane < p.M && col0 < p.N) {
+          store32_mx(p, r, row, col0, lane);
+        }
+      };
+      int i = 0;
+      if (owner) {
+        uint32_t r0[32], r1[32];
+        const int ch0 = backwards ? 3 : 0, ch1 = backwards ? 2 : 1;
+        tmem_ld32(t_row + ch0 * 32, r0);
+        if (C::OVL_CHUNKS == 2) tmem_ld32(t_row + ch1 * 32, r1);
+        tmem_wait_ld();
+        tc_fence_before();
+        __syncwarp();
+        if (lane == 0) mbar_arrive_cluster(ovl_leader);
+        emit(r0, ch0);
+        if (C::OVL_CHUNKS == 2) emit(r1, ch1);
+        i = C::OVL_CHUNKS;
+      }
+#pragma unroll 1
+      for (; i < 4; ++i) {
+        const int ch = backwards ? 3 - i : i;
+        uint32_t r[32];
+        tmem_ld32(t_row + ch * 32, r);
+        tmem_wait_ld();
+        emit(r, ch);
+      }
+      tc_fence_before();
+      __syncwarp();
+      if (lane == 0) mbar_arrive_cluster(mapa_shared(smem_u32(&bars->acc_empty[acc]), 0));
+    }
+  }
+
+  // ------------------------------------------------------------ tear-down
+  __syncwarp();
+  if (*abort_word != 0) {
+    const unsigned long long t0 = globaltimer_ns();
+    while (globaltimer_ns() - t0 < 200000ull) __nanosleep(1000);
+  }
+  tc_fence_before();
+  __syncthreads();
+  cluster_sync_all();  // the peer may still signal into this CTA's shared memory until here
+  if (warp == 1) {
+    tc_fence_after();
+    tmem_dealloc_pair(tmem_base, TMEM_COLS);
+  }
+  if (threadIdx.x == 0 && *abort_word != 0) atomicExch(p.status, *abort_word);
+}
+
 }  // namespace gemm_mx
 
 static int32_t matmul_mx_run(const char* op, const cdl_mx_tensor* a, const cdl_mx_tensor* b,
@@ -476,6 +734,14 @@ static int32_t matmul_mx_run(const char* op, const cdl_mx_tensor* a, const cdl_m
     if (attr_err == cudaSuccess)
       attr_err = cudaFuncSetAttribute(gemm_mx_kernel<1>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                       static_cast<int>(Cfg<1>::SMEM_BYTES));
+    if (attr_err == cudaSuccess)
+      attr_err = cudaFuncSetAttribute(gemm_mx_pair_kernel<0>,
+                                      cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                      static_cast<int>(PairCfg<0>::SMEM_BYTES));
+    if (attr_err == cudaSuccess)
+      attr_err = cudaFuncSetAttribute(gemm_mx_pair_kernel<1>,
+                                      cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                      static_cast<int>(PairCfg<1>::SMEM_BYTES));
   });
   if (attr_err != cudaSuccess)
     return fail(CDL_ERR_CUDA, "cudaFuncSetAttribute failed: %s", cudaGetErrorString(attr_err));
@@ -521,10 +787,41 @@ static int32_t matmul_mx_run(const char* op, const cdl_mx_tensor* a, const cdl_m
     const uint32_t box[3] = {BK, BN, 1};
     CDL_CHECK(encode_tmap(&tb, b->values, TMAP_U8, 3, dims, strides, box, true));
   }
-  const int grid = p.num_tiles < sm_count() ? p.num_tiles : sm_count();
   ProfileScope ps(PROF_GEMM, 2.0 * M * N * K, stream);
-  if (fp4) gemm_mx_kernel<1><<<grid, THREADS, Cfg<1>::SMEM_BYTES, stream>>>(ta, tb, p);
-  else gemm_mx_kernel<0><<<grid, THREADS, Cfg<0>::SMEM_BYTES, stream>>>(ta, tb, p);
+  const char* mode = getenv("CDL_B200_MX_GEMM");  // "single" forces the one-CTA kernel
+  if (M > BM && !(mode && strcmp(mode, "single") == 0)) {
+    // CTA pairs over 256 x 256 tiles
+    p.num_m_tiles = static_cast<int>((M + 2 * BM - 1) / (2 * BM));
+    p.num_tiles = p.num_m_tiles * p.num_n_tiles;
+    CUtensorMap tbh, tsa, tsb;
+    {
+      const uint64_t dims[3] = {static_cast<uint64_t>(k_bytes), static_cast<uint64_t>(N), 1};
+      const uint64_t strides[3] = {1, static_cast<uint64_t>(k_bytes), static_cast<uint64_t>(k_bytes) * N};
+      const uint32_t box[3] = {BK, BN / 2, 1};
+      CDL_CHECK(encode_tmap(&tbh, b->values, TMAP_U8, 3, dims, strides, box, true));
+    }
+    const uint32_t sft = fp4 ? 4 : 1;
+    auto sf_map = [&](CUtensorMap* out, const void* base, long long outer) -> int32_t {
+      // the scale buffer as rows of 256 bytes: tile i = rows 2i, 2i + 1
+      const uint64_t tiles = static_cast<uint64_t>((outer + 127) / 128) * p.sf_k_tiles;
+      const uint64_t dims[3] = {256, 2 * tiles, 1};
+      const uint64_t strides[3] = {1, 256, 512 * tiles};
+      const uint32_t box[3] = {256, 2 * sft, 1};
+      return encode_tmap(out, base, TMAP_U8, 3, dims, strides, box, false);
+    };
+    CDL_CHECK(sf_map(&tsa, a->scale_factors, M));
+    CDL_CHECK(sf_map(&tsb, b->scale_factors, N));
+    int grid = 2 * p.num_tiles < sm_count() ? 2 * p.num_tiles : sm_count();
+    grid &= ~1;
+    if (fp4)
+      gemm_mx_pair_kernel<1><<<grid, THREADS, PairCfg<1>::SMEM_BYTES, stream>>>(ta, tbh, tsa, tsb, p);
+    else
+      gemm_mx_pair_kernel<0><<<grid, THREADS, PairCfg<0>::SMEM_BYTES, stream>>>(ta, tbh, tsa, tsb, p);
+  } else {
+    const int grid = p.num_tiles < sm_count() ? p.num_tiles : sm_count();
+    if (fp4) gemm_mx_kernel<1><<<grid, THREADS, Cfg<1>::SMEM_BYTES, stream>>>(ta, tb, p);
+    else gemm_mx_kernel<0><<<grid, THREADS, Cfg<0>::SMEM_BYTES, stream>>>(ta, tb, p);
+  }
   CDL_CUDA(cudaGetLastError());
   return CDL_OK;
 }
