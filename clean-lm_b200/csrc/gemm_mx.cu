@@ -1,4 +1,5 @@
-// Matmul with block-scaled (MXFP8) operands: D = alpha * dequant(A) . dequant(B), f32 accumulate.
+// Matmul with block-scaled (MXFP8 or NVFP4) operands: D = alpha * dequant(A) . dequant(B), f32
+// accumulate; plain bf16 / f32 output or an MXFP8 block-scaled one.
 //
 // The reference forwards this case to cuBLASLt block scaling
 // (crates/cleandl/src/execgraph/ops/matmul.rs:808-838, InputKind::Mx; tests
@@ -6,6 +7,10 @@
 // crates/cleandl-specialized-kernels/src/kernels/matmul/tcgen05.rs.  A is rowwise [M, K], B is
 // colwise [K, N]: both value matrices are K-contiguous bytes, both scale tensors are in the
 // 128 x 4 tiled layout, which is what the hardware reads.
+//
+// Two kernels share the design below: a one-CTA kernel (128 x 256 tiles) and, further down, the
+// CTA-pair kernel (256 x 256 tiles) that is used whenever M > 128.  The text describes MXFP8;
+// Cfg<> lists what changes for NVFP4.
 //
 // Kernel: persistent, one CTA per SM, 128 x 256 output tiles, K in steps of 128 bytes (one
 // 128-byte swizzled row per operand row, four K = 32 instructions).  Per stage the producer warp

@@ -225,7 +225,15 @@ __device__ __forceinline__ void apply_norm8(const Params& p, const uint4& xq, in
       float v = f[j] * r;
       if (p.gamma != nullptr) v *= gm[j];
       if (p.beta != nullptr) v += bt[j];
-      f[j] = bf16_round(v);
+      f[j] = v;
+    }
+    // One packed conversion per pair and two unpacking moves: rounding with integer arithmetic
+    // costs four ALU operations per element, and the ALU pipe is what bounds these kernels.
+#pragma unroll
+    for (int j = 0; j < 8; j += 2) {
+      const uint32_t q = pack_bf16x2(f[j], f[j + 1]);
+      f[j] = bf16_lo(q);
+      f[j + 1] = bf16_hi(q);
     }
   }
 }
