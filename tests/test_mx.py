@@ -378,3 +378,44 @@ def test_nvfp4_host_validation(cdl):
     assert cdl.mx.layout_bytes(128, 256, ROW, fmt=cdl.mx.NVFP4) == (128 * 128, 128 * 16)
     with pytest.raises(cdl._lib.CdlError, match="block size 16"):
         cdl.mx.layout_bytes(128, 40, ROW, fmt=cdl.mx.NVFP4)
+
+
+@pytest.mark.gpu
+def test_mx_edge_shapes(cdl, gpu_ok):
+    """Empty shapes are a silent success; single rows, the smallest K and ragged N work."""
+    dev = "cuda"
+    # empty
+    x0 = torch.empty(0, 64, dtype=torch.bfloat16, device=dev)
+    yr, _ = cdl.mx.quantize(x0, rowwise=True)
+    assert yr.values.numel() == 0
+    out = cdl.mx.norm_fwd_mx(x0, save_stats=True)
+    assert out.y.values.numel() == 0 and out.r_inv.numel() == 0
+    qa = cdl.mx.MxTensor.empty(0, 64, ROW, dev)
+    qb = cdl.mx.MxTensor.empty(64, 16, COL, dev)
+    assert cdl.mx.matmul_mx(qa, qb).shape == (0, 16)
+    # one row, K = 32, N = 8; and 129 rows (a pair tile with one row in the second CTA)
+    gen = torch.Generator().manual_seed(7)
+    for m, k, n in [(1, 32, 8), (129, 64, 40), (257, 160, 264)]:
+        a = torch.randn(m, k, generator=gen).to(torch.bfloat16)
+        b = torch.randn(k, n, generator=gen).to(torch.bfloat16)
+        qa, _ = cdl.mx.quantize(a.cuda(), rowwise=True)
+        _, qb = cdl.mx.quantize(b.cuda(), rowwise=False, colwise=True)
+        da, _ = mx_ref.dequantize(qa.values.cpu().numpy(), qa.scale_factors.cpu().numpy(), m, k, ROW)
+        db, _ = mx_ref.dequantize(qb.values.cpu().numpy(), qb.scale_factors.cpu().numpy(), k, n, COL)
+        expected = da.astype(np.float64) @ db.astype(np.float64)
+        bound = np.abs(da).astype(np.float64) @ np.abs(db).astype(np.float64)
+        d = cdl.mx.matmul_mx(qa, qb, out_dtype=torch.float32)
+        assert_all_close(f"{m}x{k}x{n}", to_f32(d), expected, oracle.matmul_tolerance(expected, bound, False))
+    # the one-CTA kernel is still reachable and agrees bit for bit with the pair kernel
+    import os
+    a = torch.randn(512, 256, generator=gen).to(torch.bfloat16)
+    b = torch.randn(256, 384, generator=gen).to(torch.bfloat16)
+    qa, _ = cdl.mx.quantize(a.cuda(), rowwise=True)
+    _, qb = cdl.mx.quantize(b.cuda(), rowwise=False, colwise=True)
+    d_pair = cdl.mx.matmul_mx(qa, qb, out_dtype=torch.float32)
+    os.environ["CDL_B200_MX_GEMM"] = "single"
+    try:
+        d_single = cdl.mx.matmul_mx(qa, qb, out_dtype=torch.float32)
+    finally:
+        del os.environ["CDL_B200_MX_GEMM"]
+    assert torch.equal(d_pair, d_single)
