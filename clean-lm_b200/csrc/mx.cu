@@ -80,13 +80,6 @@ __device__ __forceinline__ uint32_t fp8x4(float a, float b, float c, float d) {
   const uint32_t hi = __nv_cvt_float2_to_fp8x2(make_float2(c, d), __NV_SATFINITE, __NV_E4M3);
   return lo | (hi << 16);
 }
-// Round to nearest even bf16, result as f32.  Integer arithmetic: conversion instructions run at
-// a fraction of the ALU rate and the fp8 conversion already needs one per two elements.
-__device__ __forceinline__ float bf16_round(float v) {
-  uint32_t u = __float_as_uint(v);
-  u += 0x7FFFu + ((u >> 16) & 1u);
-  return __uint_as_float(u & 0xFFFF0000u);
-}
 // Two bf16-representable floats -> packed bf16x2 (lo in the low half).
 __device__ __forceinline__ uint32_t pack_rounded(float lo, float hi) {
   return __byte_perm(__float_as_uint(lo), __float_as_uint(hi), 0x7632);
@@ -94,121 +87,6 @@ __device__ __forceinline__ uint32_t pack_rounded(float lo, float hi) {
 __device__ __forceinline__ void unpack8(const uint4& q, float (&f)[8]) {
   f[0] = bf16_lo(q.x); f[1] = bf16_hi(q.x); f[2] = bf16_lo(q.y); f[3] = bf16_hi(q.y);
   f[4] = bf16_lo(q.z); f[5] = bf16_hi(q.z); f[6] = bf16_lo(q.w); f[7] = bf16_hi(q.w);
-}
-
-// NORM: y = x * r * gamma + beta with r = rsqrt(mean x^2 + eps); otherwise y = x.
-// COL: the CTA has 32 warps and owns rows [32 * blockIdx.x, +32); otherwise any number of warps,
-// each striding over rows.
-template <bool NORM, bool COL>
-__global__ void __launch_bounds__(COL ? 1024 : 256, 1) mx_rows_kernel(const Params p) {
-  extern __shared__ __align__(16) uint8_t smem_raw[];
-  __nv_bfloat16* tile = reinterpret_cast<__nv_bfloat16*>(smem_raw);  // [32][TILE_LD] (COL only)
-  const int lane = threadIdx.x & 31;
-  const int warp = threadIdx.x >> 5;
-  const int warps = blockDim.x >> 5;
-  const int row_blocks = p.cols / BLOCK;  // blocks per row (rowwise)
-  const int col_blocks = p.rows / BLOCK;  // blocks per column (colwise)
-  const float inv_cols = 1.0f / static_cast<float>(p.cols);
-
-  const long long row_step = COL ? static_cast<long long>(gridDim.x) * 32
-                                 : static_cast<long long>(gridDim.x) * warps;
-  for (long long row0 = COL ? static_cast<long long>(blockIdx.x) * 32
-                            : static_cast<long long>(blockIdx.x) * warps;
-       row0 < p.rows; row0 += row_step) {
-    const long long row = row0 + warp;
-    const bool row_ok = row < p.rows;
-    const __nv_bfloat16* xr = p.x + row * p.ldx;
-    float r = 1.0f;
-    if (NORM && row_ok) {
-      float ss = 0.f;
-      for (int c = lane * 8; c < p.cols; c += 256) {
-        float f[8];
-        unpack8(*reinterpret_cast<const uint4*>(xr + c), f);
-#pragma unroll
-        for (int j = 0; j < 8; ++j) ss = fmaf(f[j], f[j], ss);
-      }
-#pragma unroll
-      for (int o = 16; o > 0; o >>= 1) ss += __shfl_xor_sync(0xffffffffu, ss, o);
-      r = rsqrtf(ss * inv_cols + p.eps);
-      if (lane == 0 && p.r_inv != nullptr) p.r_inv[row * p.r_inv_stride] = r;
-    }
-
-    for (int g0 = 0; g0 < p.cols; g0 += COL_GROUP) {
-      const int g_cols = min(COL_GROUP, p.cols - g0);
-      // ---- a warp's row: results of up to four stripes, rowwise output, staging for colwise
-      if (row_ok) {
-        for (int c0 = g0; c0 < g0 + g_cols; c0 += 256) {  // warp-uniform: the shuffles need all lanes
-          const int c = c0 + lane * 8;
-          const bool active = c < g0 + g_cols;
-          float f[8];
-#pragma unroll
-          for (int j = 0; j < 8; ++j) f[j] = 0.f;
-          if (active) {
-            unpack8(*reinterpret_cast<const uint4*>(xr + c), f);
-            if (NORM) {
-              float gm[8], bt[8];
-              if (p.gamma != nullptr) unpack8(*reinterpret_cast<const uint4*>(p.gamma + c), gm);
-              if (p.beta != nullptr) unpack8(*reinterpret_cast<const uint4*>(p.beta + c), bt);
-#pragma unroll
-              for (int j = 0; j < 8; ++j) {
-                float v = f[j] * r;
-                if (p.gamma != nullptr) v *= gm[j];
-                if (p.beta != nullptr) v += bt[j];
-                f[j] = bf16_round(v);
-              }
-            }
-            if (COL) {
-              uint4 q;
-              q.x = pack_bf16x2(f[0], f[1]); q.y = pack_bf16x2(f[2], f[3]);
-              q.z = pack_bf16x2(f[4], f[5]); q.w = pack_bf16x2(f[6], f[7]);
-              *reinterpret_cast<uint4*>(tile + warp * TILE_LD + (c - g0)) = q;
-            }
-          }
-          if (p.row_values != nullptr) {
-            // the four lanes of a 32-element block are all active or all idle (cols % 32 == 0)
-            float amax = 0.f;
-#pragma unroll
-            for (int j = 0; j < 8; ++j) amax = fmaxf(amax, fabsf(f[j]));
-            amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, 1));
-            amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, 2));
-            if (active) {
-              const uint32_t e = scale_exponent(amax);
-              const float ds = descale_of(e);
-              uint2 out;
-              out.x = fp8x4(f[0] * ds, f[1] * ds, f[2] * ds, f[3] * ds);
-              out.y = fp8x4(f[4] * ds, f[5] * ds, f[6] * ds, f[7] * ds);
-              *reinterpret_cast<uint2*>(p.row_values + row * p.cols + c) = out;
-              if ((lane & 3) == 0)
-                p.row_sf[sf_index(static_cast<int>(row), c / BLOCK, row_blocks)] = static_cast<uint8_t>(e);
-            }
-          }
-        }
-      }
-      if (COL) {
-        __syncthreads();
-        const int c = threadIdx.x;
-        if (c < g_cols) {
-          // rows % 32 == 0: all 32 staged rows exist
-          float v[32];
-          float amax = 0.f;
-#pragma unroll
-          for (int j = 0; j < 32; ++j) {
-            v[j] = __bfloat162float(tile[j * TILE_LD + c]);
-            amax = fmaxf(amax, fabsf(v[j]));
-          }
-          const uint32_t e = scale_exponent(amax);
-          const float ds = descale_of(e);
-          uint32_t w[8];
-#pragma unroll
-          for (int j = 0; j < 8; ++j)
-            w[j] = fp8x4(v[4 * j] * ds, v[4 * j + 1] * ds, v[4 * j + 2] * ds, v[4 * j + 3] * ds);
-          st_global_v8(p.col_values + static_cast<long long>(g0 + c) * p.rows + row0, w);
-          p.col_sf[sf_index(g0 + c, static_cast<int>(row0 / BLOCK), col_blocks)] = static_cast<uint8_t>(e);
-        }
-        __syncthreads();
-      }
-    }
-  }
 }
 
 // y of 8 consecutive elements: normalisation (NORM) and rounding to bf16.
@@ -260,6 +138,92 @@ __device__ __forceinline__ void quantize_row8(const Params& p, const float (&f)[
   if (active && (lane & 3) == 0)
     p.row_sf[sf_index(static_cast<int>(row), c / BLOCK, row_blocks)] =
         static_cast<uint8_t>(scale_exponent(amax));
+}
+
+// NORM: y = x * r * gamma + beta with r = rsqrt(mean x^2 + eps); otherwise y = x.
+// COL: the CTA has 32 warps and owns rows [32 * blockIdx.x, +32); otherwise any number of warps,
+// each striding over rows.
+template <bool NORM, bool COL>
+__global__ void __launch_bounds__(COL ? 1024 : 256, 1) mx_rows_kernel(const Params p) {
+  extern __shared__ __align__(16) uint8_t smem_raw[];
+  __nv_bfloat16* tile = reinterpret_cast<__nv_bfloat16*>(smem_raw);  // [32][TILE_LD] (COL only)
+  const int lane = threadIdx.x & 31;
+  const int warp = threadIdx.x >> 5;
+  const int warps = blockDim.x >> 5;
+  const int row_blocks = p.cols / BLOCK;  // blocks per row (rowwise)
+  const int col_blocks = p.rows / BLOCK;  // blocks per column (colwise)
+  const float inv_cols = 1.0f / static_cast<float>(p.cols);
+
+  const long long row_step = COL ? static_cast<long long>(gridDim.x) * 32
+                                 : static_cast<long long>(gridDim.x) * warps;
+  for (long long row0 = COL ? static_cast<long long>(blockIdx.x) * 32
+                            : static_cast<long long>(blockIdx.x) * warps;
+       row0 < p.rows; row0 += row_step) {
+    const long long row = row0 + warp;
+    const bool row_ok = row < p.rows;
+    const __nv_bfloat16* xr = p.x + row * p.ldx;
+    float r = 1.0f;
+    if (NORM && row_ok) {
+      float ss = 0.f;
+      for (int c = lane * 8; c < p.cols; c += 256) {
+        float f[8];
+        unpack8(*reinterpret_cast<const uint4*>(xr + c), f);
+#pragma unroll
+        for (int j = 0; j < 8; ++j) ss = fmaf(f[j], f[j], ss);
+      }
+#pragma unroll
+      for (int o = 16; o > 0; o >>= 1) ss += __shfl_xor_sync(0xffffffffu, ss, o);
+      r = rsqrtf(ss * inv_cols + p.eps);
+      if (lane == 0 && p.r_inv != nullptr) p.r_inv[row * p.r_inv_stride] = r;
+    }
+
+    for (int g0 = 0; g0 < p.cols; g0 += COL_GROUP) {
+      const int g_cols = min(COL_GROUP, p.cols - g0);
+      // ---- a warp's row: results of up to four stripes, rowwise output, staging for colwise
+      if (row_ok) {
+        for (int c0 = g0; c0 < g0 + g_cols; c0 += 256) {  // warp-uniform: the shuffles need all lanes
+          const int c = c0 + lane * 8;
+          const bool active = c < g0 + g_cols;
+          float f[8];
+#pragma unroll
+          for (int j = 0; j < 8; ++j) f[j] = 0.f;
+          if (active) {
+            apply_norm8<NORM>(p, *reinterpret_cast<const uint4*>(xr + c), c, r, f);
+            if (COL) {
+              uint4 q;
+              q.x = pack_rounded(f[0], f[1]); q.y = pack_rounded(f[2], f[3]);
+              q.z = pack_rounded(f[4], f[5]); q.w = pack_rounded(f[6], f[7]);
+              *reinterpret_cast<uint4*>(tile + warp * TILE_LD + (c - g0)) = q;
+            }
+          }
+          if (p.row_values != nullptr) quantize_row8(p, f, active, row, c, lane, row_blocks);
+        }
+      }
+      if (COL) {
+        __syncthreads();
+        const int c = threadIdx.x;
+        if (c < g_cols) {
+          // rows % 32 == 0: all 32 staged rows exist
+          float v[32];
+          float amax = 0.f;
+#pragma unroll
+          for (int j = 0; j < 32; ++j) {
+            v[j] = __bfloat162float(tile[j * TILE_LD + c]);
+            amax = fmaxf(amax, fabsf(v[j]));
+          }
+          const uint32_t e = scale_exponent(amax);
+          const float ds = descale_of(e);
+          uint32_t w[8];
+#pragma unroll
+          for (int j = 0; j < 8; ++j)
+            w[j] = fp8x4(v[4 * j] * ds, v[4 * j + 1] * ds, v[4 * j + 2] * ds, v[4 * j + 3] * ds);
+          st_global_v8(p.col_values + static_cast<long long>(g0 + c) * p.rows + row0, w);
+          p.col_sf[sf_index(g0 + c, static_cast<int>(row0 / BLOCK), col_blocks)] = static_cast<uint8_t>(e);
+        }
+        __syncthreads();
+      }
+    }
+  }
 }
 
 // Rowwise output only, rows of up to 256 * NCH columns: the row stays in registers between the

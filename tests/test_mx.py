@@ -129,7 +129,7 @@ def rand_bf16(rows, cols, seed, spread=2.0):
 
 @pytest.mark.gpu
 @pytest.mark.parametrize("rows,cols", [(1, 128), (37, 4096), (300, 2048), (128, 8192), (96, 512),
-                                        (64, 160), (256, 7168)])
+                                        (64, 160), (256, 7168), (4, 16384), (32, 12288)])
 def test_quantize_is_bit_exact(cdl, gpu_ok, rows, cols):
     x = rand_bf16(rows, cols, 10)
     x[0, :32] = 0  # an all-zero block
@@ -159,7 +159,7 @@ def test_quantize_strided_rows(cdl, gpu_ok):
 
 
 NORM_CASES = [(1, 128), (37, 4096), (300, 2048), (128, 8192), (100, 7168), (5, 1024), (96, 512),
-              (320, 1536), (16384, 2048)]
+              (320, 1536), (16384, 2048), (3, 16384)]
 
 
 @pytest.mark.gpu
