@@ -83,7 +83,7 @@ struct Params {
   void* d;
   long long ldd;
   int out_f32, wide;
-  // Block-scaled output (out_mx 1 = rowwise, 2 = colwise): MXFP8 values and scale tiles.
+  // Block-scaled output (out_mx 1): rowwise MXFP8 values and scale tiles.
   int out_mx;
   uint8_t* out_values;
   uint8_t* out_sf;
@@ -171,44 +171,26 @@ __device__ __forceinline__ uint32_t fp8x4(float a, float b, float c, float d) {
   return lo | (hi << 16);
 }
 
-// Block-scaled store of 32 consecutive columns of the warp's 32 rows (lane = row).  Rowwise: the
-// thread's 32 columns are one block of its row.  Colwise: a column's block is the 32 rows of the
-// warp, so the maximum is taken across lanes and the transposed value matrix receives 32
-// consecutive bytes per column.  Called by all lanes of a warp with a valid row range.
-__device__ __forceinline__ void store32_mx(const Params& p, const uint32_t (&r)[32], int row, int col0,
-                                           int lane) {
+// Block-scaled (rowwise MXFP8) store of 32 consecutive columns of one output row: they are one
+// block of the row.  A colwise output never reaches the kernel: the host runs it as the rowwise
+// output of the transposed product (matmul_mx_out_execute).
+__device__ __forceinline__ void store32_mx(const Params& p, const uint32_t (&r)[32], int row, int col0) {
+  if (row >= p.M) return;
   float v[32];
+  float amax = 0.f;
 #pragma unroll
-  for (int j = 0; j < 32; ++j) v[j] = p.alpha * __uint_as_float(r[j]);
-  if (p.out_mx == 1) {
-    if (row >= p.M) return;
-    float amax = 0.f;
-#pragma unroll
-    for (int j = 0; j < 32; ++j) amax = fmaxf(amax, fabsf(v[j]));
-    const uint32_t e = scale_exponent(amax);
-    const float ds = descale_of(e);
-    uint32_t w[8];
-#pragma unroll
-    for (int j = 0; j < 8; ++j)
-      w[j] = fp8x4(v[4 * j] * ds, v[4 * j + 1] * ds, v[4 * j + 2] * ds, v[4 * j + 3] * ds);
-    st_global_v8(p.out_values + static_cast<long long>(row) * p.N + col0, w);  // N % 32 == 0
-    p.out_sf[sf_index(row, col0 >> 5, p.N >> 5)] = static_cast<uint8_t>(e);
-  } else {
-    const int row0 = row - lane;  // M % 32 == 0: the warp's rows are one block of every column
-#pragma unroll
-    for (int j = 0; j < 32; ++j) {
-      if (col0 + j < p.N) {  // warp-uniform
-        float amax = fabsf(v[j]);
-#pragma unroll
-        for (int o = 16; o > 0; o >>= 1) amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, o));
-        const uint32_t e = scale_exponent(amax);
-        const uint32_t q = __nv_cvt_float2_to_fp8x2(make_float2(v[j] * descale_of(e), 0.f),
-                                                    __NV_SATFINITE, __NV_E4M3);
-        p.out_values[static_cast<long long>(col0 + j) * p.M + row] = static_cast<uint8_t>(q & 0xFFu);
-        if (lane == 0) p.out_sf[sf_index(col0 + j, row0 >> 5, p.M >> 5)] = static_cast<uint8_t>(e);
-      }
-    }
+  for (int j = 0; j < 32; ++j) {
+    v[j] = p.alpha * __uint_as_float(r[j]);
+    amax = fmaxf(amax, fabsf(v[j]));
   }
+  const uint32_t e = scale_exponent(amax);
+  const float ds = descale_of(e);
+  uint32_t w[8];
+#pragma unroll
+  for (int j = 0; j < 8; ++j)
+    w[j] = fp8x4(v[4 * j] * ds, v[4 * j + 1] * ds, v[4 * j + 2] * ds, v[4 * j + 3] * ds);
+  st_global_v8(p.out_values + static_cast<long long>(row) * p.N + col0, w);  // N % 32 == 0
+  p.out_sf[sf_index(row, col0 >> 5, p.N >> 5)] = static_cast<uint8_t>(e);
 }
 
 template <int FP4>
@@ -375,8 +357,8 @@ __global__ void __launch_bounds__(THREADS, 1)
         const int col0 = col_base + ch * 32;
         if (p.out_mx == 0) {
           if (row < p.M && col0 < p.N) store32(p, r, row, col0);
-        } else if (row - lane < p.M && col0 < p.N) {  // whole warps: the block dimension is padded to 32
-          store32_mx(p, r, row, col0, lane);
+        } else if (col0 < p.N) {
+          store32_mx(p, r, row, col0);
         }
       };
       int i = 0;
@@ -632,8 +614,8 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(THREADS, 1)
         const int col0 = col_base + ch * 32;
         if (p.out_mx == 0) {
           if (row < p.M && col0 < p.N) store32(p, r, row, col0);
-        } else if (row - lane < p.M && col0 < p.N) {
-          store32_mx(p, r, row, col0, lane);
+        } else if (col0 < p.N) {
+          store32_mx(p, r, row, col0);
         }
       };
       int i = 0;
@@ -709,7 +691,7 @@ static int32_t matmul_mx_run(const char* op, const cdl_mx_tensor* a, const cdl_m
   if (fp4 && d_mx)
     return fail(CDL_ERR_UNSUPPORTED, "%s: a block-scaled output with NVFP4 operands is not implemented", op);
   if (d_mx) {
-    if (d_mx->dim != CDL_MX_ROWWISE && d_mx->dim != CDL_MX_COLWISE)
+    if (d_mx->dim != CDL_MX_ROWWISE)  // (a colwise output arrives here transposed)
       return fail(CDL_ERR_INVALID, "%s: unknown block dimension of the output", op);
     if (d_mx->format != CDL_MXFP8)
       return fail(CDL_ERR_UNSUPPORTED, "%s: only MXFP8 block-scaled outputs are implemented", op);
@@ -765,7 +747,7 @@ static int32_t matmul_mx_run(const char* op, const cdl_mx_tensor* a, const cdl_m
   p.sfa = static_cast<const uint8_t*>(a->scale_factors);
   p.sfb = static_cast<const uint8_t*>(b->scale_factors);
   if (d_mx) {
-    p.out_mx = d_mx->dim == CDL_MX_ROWWISE ? 1 : 2;
+    p.out_mx = 1;
     p.out_values = static_cast<uint8_t*>(d_mx->values);
     p.out_sf = static_cast<uint8_t*>(d_mx->scale_factors);
   } else {
@@ -838,8 +820,23 @@ int32_t matmul_mx_execute(const cdl_mx_tensor* a, const cdl_mx_tensor* b, const 
 
 int32_t matmul_mx_out_execute(const cdl_mx_tensor* a, const cdl_mx_tensor* b, const cdl_mx_tensor* d,
                               float alpha, cudaStream_t stream) {
-  if (!d) return fail(CDL_ERR_INVALID, "matmul (mxfp8, block-scaled output): d is required");
-  return matmul_mx_run("matmul (mxfp8, block-scaled output)", a, b, nullptr, d, alpha, stream);
+  const char* op = "matmul (mxfp8, block-scaled output)";
+  if (!d) return fail(CDL_ERR_INVALID, "%s: d is required", op);
+  if (a && b && d->dim == CDL_MX_COLWISE && a->dim == CDL_MX_ROWWISE && b->dim == CDL_MX_COLWISE) {
+    // A colwise D is a rowwise D^T = B^T . A^T, and the buffers already are what that product
+    // needs: B's values are the rowwise [N, K] matrix, A's values are the colwise [K, M] one, D's
+    // values are the packed [N, M] transpose with blocks along M.  So the colwise output runs as
+    // the rowwise epilogue (a thread's 32 columns are one block) of the swapped problem.
+    cdl_mx_tensor at = *b, bt = *a, dt = *d;
+    at.dim = CDL_MX_ROWWISE; at.rows = b->cols; at.cols = b->rows;
+    bt.dim = CDL_MX_COLWISE; bt.rows = a->cols; bt.cols = a->rows;
+    dt.dim = CDL_MX_ROWWISE; dt.rows = d->cols; dt.cols = d->rows;
+    if (d->rows != a->rows || d->cols != b->cols)
+      return fail(CDL_ERR_INVALID, "%s: d must have shape [%lld, %lld]", op,
+                  static_cast<long long>(a->rows), static_cast<long long>(b->cols));
+    return matmul_mx_run(op, &at, &bt, nullptr, &dt, alpha, stream);
+  }
+  return matmul_mx_run(op, a, b, nullptr, d, alpha, stream);
 }
 
 }  // namespace cdl
