@@ -419,3 +419,38 @@ def test_mx_edge_shapes(cdl, gpu_ok):
     finally:
         del os.environ["CDL_B200_MX_GEMM"]
     assert torch.equal(d_pair, d_single)
+
+
+def test_oracle_against_torch_golden():
+    """tests/golden/mx.npz was produced by an independent torch implementation
+    (tests/golden/make_golden_mx.py): the oracle reproduces it bit for bit."""
+    from pathlib import Path
+
+    g = np.load(Path(__file__).resolve().parent / "golden" / "mx.npz")
+    m = g["m"]
+    rows, cols = m.shape
+    for dim, key in ((ROW, "row"), (COL, "col")):
+        v, s = mx_ref.quantize(m, dim)
+        assert np.array_equal(v, g[key + "_values"]) and np.array_equal(s, g[key + "_scales"])
+        assert np.array_equal(mx_ref.dequantize(v, s, rows, cols, dim)[0], g[key + "_deq"])
+    v, s = mx_ref.quantize_nvfp4(m, ROW)
+    assert np.array_equal(v, g["nv_values"]) and np.array_equal(s, g["nv_scales"])
+    assert np.array_equal(mx_ref.dequantize_nvfp4(v, s, rows, cols, ROW)[0], g["nv_deq"])
+
+
+@pytest.mark.gpu
+def test_gpu_against_torch_golden(cdl, gpu_ok):
+    """The same fixture against the CUDA quantisers (the committed bits, not only the oracle)."""
+    from pathlib import Path
+
+    g = np.load(Path(__file__).resolve().parent / "golden" / "mx.npz")
+    x = torch.from_numpy(g["m"]).to(torch.bfloat16).cuda()
+    yr, yc = cdl.mx.quantize(x, rowwise=True, colwise=True)
+    assert np.array_equal(yr.values.cpu().numpy(), g["row_values"])
+    assert np.array_equal(yc.values.cpu().numpy(), g["col_values"])
+    assert np.array_equal(valid_scales(yr, yr.scale_factors.cpu().numpy()), valid_scales(yr, g["row_scales"]))
+    assert np.array_equal(valid_scales(yc, yc.scale_factors.cpu().numpy()), valid_scales(yc, g["col_scales"]))
+    yn, _ = cdl.mx.quantize(x, rowwise=True, fmt=cdl.mx.NVFP4)
+    assert np.array_equal(yn.values.cpu().numpy(), g["nv_values"])
+    assert np.array_equal(nv_valid_scales(yn, yn.scale_factors.cpu().numpy()), nv_valid_scales(yn, g["nv_scales"]))
+    assert np.array_equal(to_f32(cdl.mx.dequantize(yn)), g["nv_deq"])
