@@ -8,9 +8,11 @@ Follows the host-side quantiser and checks of the reference's own tests:
   * UE8M0 decode                            crates/cleandl/tests/common/mod.rs:131-137
   * tolerances of a block-scaled output     crates/cleandl/tests/norm.rs:134-149,
                                             crates/cleandl/tests/matmul.rs:1100-1110
-Parity: the reference's tests draw their inputs from Rust random streams and hold no stored
-vectors for this format, so the oracle is pinned by the format's definition (the e4m3 table is
-checked against its 256 codes, the index against the closed form) rather than by golden bits.
+Parity unpinned against the reference itself: its tests draw their inputs from Rust random
+streams and hold no stored vectors for this format.  The oracle is pinned instead by the format's
+definition (the e4m3 table against its 256 codes, the index against the closed form), by torch's
+float8_e4m3fn cast, and bit for bit by tests/golden/mx.npz, which an independent torch
+implementation produced (tests/golden/make_golden_mx.py).
 
 MXFP8: blocks of 32 elements along the block dimension share one UE8M0 scale 2^(e - 127); values
 are FP8 E4M3 (bias 7, no infinities, 0x7F / 0xFF NaN, largest finite 448).
