@@ -29,6 +29,7 @@
 #include "ops.h"
 #include "ptx.cuh"
 
+#include <cuda_fp4.h>
 #include <cuda_fp8.h>
 
 #include <stdlib.h>
@@ -83,7 +84,7 @@ struct Params {
   void* d;
   long long ldd;
   int out_f32, wide;
-  // Block-scaled output (out_mx 1): rowwise MXFP8 values and scale tiles.
+  // Block-scaled output, rowwise: out_mx 1 = MXFP8, 2 = NVFP4 values and scale tiles.
   int out_mx;
   uint8_t* out_values;
   uint8_t* out_sf;
@@ -169,6 +170,43 @@ __device__ __forceinline__ uint32_t fp8x4(float a, float b, float c, float d) {
   const uint32_t lo = __nv_cvt_float2_to_fp8x2(make_float2(a, b), __NV_SATFINITE, __NV_E4M3);
   const uint32_t hi = __nv_cvt_float2_to_fp8x2(make_float2(c, d), __NV_SATFINITE, __NV_E4M3);
   return lo | (hi << 16);
+}
+
+// The NVFP4 form of the block-scaled store: the 32 columns are two blocks of 16; scale = amax / 6
+// rounded to nearest E4M3, elements x / scale rounded to nearest E2M1 (the quantiser of mx.cu).
+__device__ __forceinline__ void store32_nvfp4(const Params& p, const uint32_t (&r)[32], int row, int col0) {
+  if (row >= p.M) return;
+  uint32_t out[4];
+  uint32_t sf2 = 0;
+#pragma unroll
+  for (int h = 0; h < 2; ++h) {
+    float v[16];
+    float amax = 0.f;
+#pragma unroll
+    for (int j = 0; j < 16; ++j) {
+      v[j] = p.alpha * __uint_as_float(r[h * 16 + j]);
+      amax = fmaxf(amax, fabsf(v[j]));
+    }
+    const __nv_fp8_storage_t sbits = __nv_cvt_float_to_fp8(__fdiv_rn(amax, 6.0f), __NV_SATFINITE, __NV_E4M3);
+    const float sc = __half2float(__half(__nv_cvt_fp8_to_halfraw(sbits, __NV_E4M3)));
+    sf2 |= static_cast<uint32_t>(sbits) << (8 * h);
+#pragma unroll
+    for (int w = 0; w < 2; ++w) {
+      uint32_t word = 0;
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        const float a = sc != 0.f ? __fdiv_rn(v[w * 8 + 2 * j], sc) : 0.f;
+        const float b = sc != 0.f ? __fdiv_rn(v[w * 8 + 2 * j + 1], sc) : 0.f;
+        word |= static_cast<uint32_t>(__nv_cvt_float2_to_fp4x2(make_float2(a, b), __NV_E2M1, cudaRoundNearest))
+                << (8 * j);
+      }
+      out[h * 2 + w] = word;
+    }
+  }
+  // N % 32 == 0: 16 bytes of values, 16-byte aligned; the two scales are neighbours in a tile
+  *reinterpret_cast<uint4*>(p.out_values + (static_cast<long long>(row) * p.N + col0) / 2) =
+      make_uint4(out[0], out[1], out[2], out[3]);
+  *reinterpret_cast<uint16_t*>(p.out_sf + sf_index(row, col0 >> 4, p.N >> 4)) = static_cast<uint16_t>(sf2);
 }
 
 // Block-scaled (rowwise MXFP8) store of 32 consecutive columns of one output row: they are one
@@ -358,7 +396,8 @@ __global__ void __launch_bounds__(THREADS, 1)
         if (p.out_mx == 0) {
           if (row < p.M && col0 < p.N) store32(p, r, row, col0);
         } else if (col0 < p.N) {
-          store32_mx(p, r, row, col0);
+          if (p.out_mx == 2) store32_nvfp4(p, r, row, col0);
+          else store32_mx(p, r, row, col0);
         }
       };
       int i = 0;
@@ -615,7 +654,8 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(THREADS, 1)
         if (p.out_mx == 0) {
           if (row < p.M && col0 < p.N) store32(p, r, row, col0);
         } else if (col0 < p.N) {
-          store32_mx(p, r, row, col0);
+          if (p.out_mx == 2) store32_nvfp4(p, r, row, col0);
+          else store32_mx(p, r, row, col0);
         }
       };
       int i = 0;
@@ -688,14 +728,16 @@ static int32_t matmul_mx_run(const char* op, const cdl_mx_tensor* a, const cdl_m
   const bool fp4 = a->format == CDL_NVFP4;
   if (fp4 && K % 64 != 0)
     return fail(CDL_ERR_UNSUPPORTED, "%s: NVFP4 operands need K to be a multiple of 64 (got %lld)", op, K);
-  if (fp4 && d_mx)
-    return fail(CDL_ERR_UNSUPPORTED, "%s: a block-scaled output with NVFP4 operands is not implemented", op);
   if (d_mx) {
     if (d_mx->dim != CDL_MX_ROWWISE)  // (a colwise output arrives here transposed)
       return fail(CDL_ERR_INVALID, "%s: unknown block dimension of the output", op);
-    if (d_mx->format != CDL_MXFP8)
-      return fail(CDL_ERR_UNSUPPORTED, "%s: only MXFP8 block-scaled outputs are implemented", op);
+    if (d_mx->format != CDL_MXFP8 && d_mx->format != CDL_NVFP4)
+      return fail(CDL_ERR_INVALID, "%s: unknown format of the block-scaled output", op);
     CDL_CHECK(mx_check(op, "d", d_mx, d_mx->dim, M, N));
+    if (N % 32 != 0)
+      return fail(CDL_ERR_UNSUPPORTED,
+                  "%s: the block dimension of a block-scaled output must be a multiple of 32 (got %lld)",
+                  op, N);
   } else {
     if (d->rank != 2 || d->shape[0] != M || d->shape[1] != N)
       return fail(CDL_ERR_INVALID, "%s: d must have shape [%lld, %lld]", op, M, N);
@@ -747,7 +789,7 @@ static int32_t matmul_mx_run(const char* op, const cdl_mx_tensor* a, const cdl_m
   p.sfa = static_cast<const uint8_t*>(a->scale_factors);
   p.sfb = static_cast<const uint8_t*>(b->scale_factors);
   if (d_mx) {
-    p.out_mx = 1;
+    p.out_mx = d_mx->format == CDL_NVFP4 ? 2 : 1;
     p.out_values = static_cast<uint8_t*>(d_mx->values);
     p.out_sf = static_cast<uint8_t*>(d_mx->scale_factors);
   } else {

@@ -132,10 +132,10 @@ def matmul_mx(a: MxTensor, b: MxTensor, out_dtype: torch.dtype = torch.bfloat16,
 
 
 def matmul_mx_out(a: MxTensor, b: MxTensor, dim: int = ROWWISE, alpha: float = 1.0,
-                  out: Optional[MxTensor] = None) -> MxTensor:
-    """The same product with `MatmulOutput::BlockScaled { Mxfp8, dim }`: an MXFP8 [M, N] result."""
+                  out: Optional[MxTensor] = None, fmt: int = MXFP8) -> MxTensor:
+    """The same product with `MatmulOutput::BlockScaled { format, dim }`: a block-scaled [M, N] result."""
     if out is None:
-        out = MxTensor.empty(a.rows, b.cols, dim, a.values.device, zero_scales=True)
+        out = MxTensor.empty(a.rows, b.cols, dim, a.values.device, zero_scales=True, fmt=fmt)
     aa, ab, ad = a.arg(), b.arg(), out.arg()
     check(lib.cdl_b200_matmul_mx_out(ref(aa), ref(ab), ref(ad), alpha, _stream()))
     return out

@@ -213,9 +213,10 @@ int32_t cdl_b200_matmul_mx(const cdl_mx_tensor* a, const cdl_mx_tensor* b, const
 
 /* The same product with a block-scaled output: MatmulOutput::BlockScaled { Mxfp8, dim }
  * (crates/cleandl/src/execgraph/ops/matmul.rs:826-834; test crates/cleandl/tests/matmul.rs:
- * 1083-1115).  d is an MXFP8 tensor of logical shape [M, N], rowwise (N % 32 == 0) or colwise
- * (M % 32 == 0); the f32 accumulator times alpha is quantised block by block in the epilogue as
- * by cdl_b200_mx_quantize (without the intermediate rounding to bf16). */
+ * 1083-1115).  d is an MXFP8 or NVFP4 tensor of logical shape [M, N], rowwise (N % 32 == 0) or
+ * colwise (M % 32 == 0); the f32 accumulator times alpha is quantised block by block in the
+ * epilogue as by cdl_b200_mx_quantize (without the intermediate rounding to bf16).  Operands
+ * and output may have different formats. */
 int32_t cdl_b200_matmul_mx_out(const cdl_mx_tensor* a, const cdl_mx_tensor* b, const cdl_mx_tensor* d,
                                float alpha, cdl_stream stream);
 

@@ -454,3 +454,36 @@ def test_gpu_against_torch_golden(cdl, gpu_ok):
     assert np.array_equal(yn.values.cpu().numpy(), g["nv_values"])
     assert np.array_equal(nv_valid_scales(yn, yn.scale_factors.cpu().numpy()), nv_valid_scales(yn, g["nv_scales"]))
     assert np.array_equal(to_f32(cdl.mx.dequantize(yn)), g["nv_deq"])
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("dim", [ROW, COL])
+@pytest.mark.parametrize("in_fmt", ["mxfp8", "nvfp4"])
+def test_matmul_nvfp4_block_scaled_output(cdl, gpu_ok, dim, in_fmt):
+    """The (Nvfp4, Rowwise) case of the reference's block_scaled_outputs test
+    (crates/cleandl/tests/matmul.rs:1083-1115), with either operand format, and the colwise form:
+    |got - e| <= 0.25 |e| + 0.5 * block scale + 1e-4 * sum |a b|."""
+    m, k, n = 256, 128, 192
+    gen = torch.Generator().manual_seed(100)
+    a = torch.randn(m, k, generator=gen).to(torch.bfloat16)
+    b = torch.randn(k, n, generator=gen).to(torch.bfloat16)
+    if in_fmt == "nvfp4":
+        qa, _ = cdl.mx.quantize(a.cuda(), rowwise=True, fmt=cdl.mx.NVFP4)
+        qb = cdl.mx.quantize(b.cuda().T.contiguous(), rowwise=True, fmt=cdl.mx.NVFP4)[0].transposed()
+        da, _ = mx_ref.dequantize_nvfp4(qa.values.cpu().numpy(), qa.scale_factors.cpu().numpy(), m, k, ROW)
+        db, _ = mx_ref.dequantize_nvfp4(qb.values.cpu().numpy(), qb.scale_factors.cpu().numpy(), k, n, COL)
+    else:
+        qa, _ = cdl.mx.quantize(a.cuda(), rowwise=True)
+        _, qb = cdl.mx.quantize(b.cuda(), rowwise=False, colwise=True)
+        da, _ = mx_ref.dequantize(qa.values.cpu().numpy(), qa.scale_factors.cpu().numpy(), m, k, ROW)
+        db, _ = mx_ref.dequantize(qb.values.cpu().numpy(), qb.scale_factors.cpu().numpy(), k, n, COL)
+    expected = da.astype(np.float64) @ db.astype(np.float64)
+    bound = np.abs(da).astype(np.float64) @ np.abs(db).astype(np.float64)
+    d = cdl.mx.matmul_mx_out(qa, qb, dim=dim, fmt=cdl.mx.NVFP4)
+    assert (d.format, d.dim, d.rows, d.cols) == (cdl.mx.NVFP4, dim, m, n)
+    got, es = mx_ref.dequantize_nvfp4(d.values.cpu().numpy(), d.scale_factors.cpu().numpy(), m, n, dim)
+    assert_all_close(f"nvfp4 output dim {dim}", got, expected, 0.25 * np.abs(expected) + 0.5 * es + 1e-4 * bound)
+    plain = cdl.mx.matmul_mx(qa, qb, out_dtype=torch.float32)
+    v_ref, s_ref = mx_ref.quantize_nvfp4(to_f32(plain), dim)
+    assert np.array_equal(d.values.cpu().numpy(), v_ref)
+    assert np.array_equal(nv_valid_scales(d, d.scale_factors.cpu().numpy()), nv_valid_scales(d, s_ref))
