@@ -114,7 +114,7 @@ SIGNATURES = {
     "cdl_b200_mx_quantize": ([_T, _MX, _MX, _vp], ctypes.c_int32),
     "cdl_b200_mx_dequantize": ([_MX, _T, _vp], ctypes.c_int32),
     "cdl_b200_rmsnorm_fwd_mx": ([_T, _T, _T, ctypes.c_float, _MX, _MX, _T, _vp], ctypes.c_int32),
-    "cdl_b200_matmul_mx": ([_MX, _MX, _T, ctypes.c_float, _vp], ctypes.c_int32),
+    "cdl_b200_matmul_mx": ([_MX, _MX, _T, _T, ctypes.c_float, ctypes.c_float, _vp], ctypes.c_int32),
     "cdl_b200_matmul_mx_out": ([_MX, _MX, _MX, ctypes.c_float, _vp], ctypes.c_int32),
     "cdl_b200_attn_fwd": ([ctypes.POINTER(CdlAttnDesc), _T, _T, _T, _T, _T, _vp], ctypes.c_int32),
     "cdl_b200_attn_bwd": ([ctypes.POINTER(CdlAttnDesc), _T, _T, _T, _T, _T, _T, _T, _T, _T, _vp,

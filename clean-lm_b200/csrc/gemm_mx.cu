@@ -84,6 +84,11 @@ struct Params {
   void* d;
   long long ldd;
   int out_f32, wide;
+  // C operand (plain outputs only): c_mode 0 none, 1 bf16, 2 f32; v = alpha * acc + beta * C
+  int c_mode;
+  const void* c;
+  long long ldc;
+  float beta;
   // Block-scaled output, rowwise: out_mx 1 = MXFP8, 2 = NVFP4 values and scale tiles.
   int out_mx;
   uint8_t* out_values;
@@ -118,6 +123,40 @@ __device__ __forceinline__ void store32(const Params& p, const uint32_t (&r)[32]
 #pragma unroll
   for (int j = 0; j < 32; ++j) v[j] = p.alpha * __uint_as_float(r[j]);
   const bool full = col0 + 32 <= p.N;
+  if (p.c_mode == 1) {
+    const __nv_bfloat16* cp = static_cast<const __nv_bfloat16*>(p.c) + static_cast<long long>(row) * p.ldc + col0;
+    if (p.wide && full) {
+#pragma unroll
+      for (int g = 0; g < 2; ++g) {
+        uint32_t w[8];
+        ld_global_v8(cp + g * 16, w);
+#pragma unroll
+        for (int j = 0; j < 8; ++j) {
+          v[g * 16 + 2 * j] += p.beta * bf16_lo(w[j]);
+          v[g * 16 + 2 * j + 1] += p.beta * bf16_hi(w[j]);
+        }
+      }
+    } else {
+#pragma unroll
+      for (int j = 0; j < 32; ++j)
+        if (col0 + j < p.N) v[j] += p.beta * __bfloat162float(cp[j]);
+    }
+  } else if (p.c_mode == 2) {
+    const float* cp = static_cast<const float*>(p.c) + static_cast<long long>(row) * p.ldc + col0;
+    if (p.wide && full) {
+#pragma unroll
+      for (int g = 0; g < 4; ++g) {
+        uint32_t w[8];
+        ld_global_v8(cp + g * 8, w);
+#pragma unroll
+        for (int j = 0; j < 8; ++j) v[g * 8 + j] += p.beta * __uint_as_float(w[j]);
+      }
+    } else {
+#pragma unroll
+      for (int j = 0; j < 32; ++j)
+        if (col0 + j < p.N) v[j] += p.beta * cp[j];
+    }
+  }
   if (p.out_f32) {
     float* dp = static_cast<float*>(p.d) + static_cast<long long>(row) * p.ldd + col0;
     if (p.wide && full) {
@@ -705,8 +744,8 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(THREADS, 1)
 }  // namespace gemm_mx
 
 static int32_t matmul_mx_run(const char* op, const cdl_mx_tensor* a, const cdl_mx_tensor* b,
-                             const cdl_tensor* d, const cdl_mx_tensor* d_mx, float alpha,
-                             cudaStream_t stream) {
+                             const cdl_tensor* c, const cdl_tensor* d, const cdl_mx_tensor* d_mx,
+                             float alpha, float beta, cudaStream_t stream) {
   using namespace gemm_mx;
   if (!a || !b || (!d && !d_mx)) return fail(CDL_ERR_INVALID, "%s: a, b and d are required", op);
   if ((a->format != CDL_MXFP8 && a->format != CDL_NVFP4) || b->format != a->format)
@@ -747,6 +786,16 @@ static int32_t matmul_mx_run(const char* op, const cdl_mx_tensor* a, const cdl_m
       return fail(CDL_ERR_UNSUPPORTED, "%s: d must have contiguous rows", op);
     if ((reinterpret_cast<uintptr_t>(d->ptr) & (dtype_size(d->dtype) - 1)) != 0)
       return fail(CDL_ERR_INVALID, "%s: d is not aligned to its element size", op);
+    if (c) {
+      if (c->rank != 2 || c->shape[0] != M || c->shape[1] != N)
+        return fail(CDL_ERR_INVALID, "%s: c must have shape [%lld, %lld]", op, M, N);
+      if (c->dtype != CDL_BF16 && c->dtype != CDL_F32)
+        return fail(CDL_ERR_UNSUPPORTED, "%s: c must be f32 or bf16", op);
+      if (N > 1 && c->stride[1] != 1)
+        return fail(CDL_ERR_UNSUPPORTED, "%s: c must have contiguous rows", op);
+      if ((reinterpret_cast<uintptr_t>(c->ptr) & (dtype_size(c->dtype) - 1)) != 0)
+        return fail(CDL_ERR_INVALID, "%s: c is not aligned to its element size", op);
+    }
   }
   if (M == 0 || N == 0) return CDL_OK;
   if (K == 0) return fail(CDL_ERR_INVALID, "%s: K is zero", op);
@@ -798,6 +847,14 @@ static int32_t matmul_mx_run(const char* op, const cdl_mx_tensor* a, const cdl_m
     p.out_f32 = d->dtype == CDL_F32;
     p.wide = (reinterpret_cast<uintptr_t>(d->ptr) & 31) == 0 &&
              (M == 1 || (d->stride[0] * dtype_size(d->dtype)) % 32 == 0);
+    if (c && beta != 0.f) {
+      p.c_mode = c->dtype == CDL_BF16 ? 1 : 2;
+      p.c = c->ptr;
+      p.ldc = c->stride[0];
+      p.beta = beta;
+      p.wide = p.wide && (reinterpret_cast<uintptr_t>(c->ptr) & 31) == 0 &&
+               (M == 1 || (c->stride[0] * dtype_size(c->dtype)) % 32 == 0);
+    }
   }
   p.alpha = alpha;
   p.status = device_status_ptr();
@@ -855,14 +912,14 @@ static int32_t matmul_mx_run(const char* op, const cdl_mx_tensor* a, const cdl_m
   return CDL_OK;
 }
 
-int32_t matmul_mx_execute(const cdl_mx_tensor* a, const cdl_mx_tensor* b, const cdl_tensor* d,
-                          float alpha, cudaStream_t stream) {
-  return matmul_mx_run("matmul (mxfp8)", a, b, d, nullptr, alpha, stream);
+int32_t matmul_mx_execute(const cdl_mx_tensor* a, const cdl_mx_tensor* b, const cdl_tensor* c,
+                          const cdl_tensor* d, float alpha, float beta, cudaStream_t stream) {
+  return matmul_mx_run("matmul (block-scaled operands)", a, b, c, d, nullptr, alpha, beta, stream);
 }
 
 int32_t matmul_mx_out_execute(const cdl_mx_tensor* a, const cdl_mx_tensor* b, const cdl_mx_tensor* d,
                               float alpha, cudaStream_t stream) {
-  const char* op = "matmul (mxfp8, block-scaled output)";
+  const char* op = "matmul (block-scaled operands and output)";
   if (!d) return fail(CDL_ERR_INVALID, "%s: d is required", op);
   if (a && b && d->dim == CDL_MX_COLWISE && a->dim == CDL_MX_ROWWISE && b->dim == CDL_MX_COLWISE) {
     // A colwise D is a rowwise D^T = B^T . A^T, and the buffers already are what that product
@@ -876,18 +933,18 @@ int32_t matmul_mx_out_execute(const cdl_mx_tensor* a, const cdl_mx_tensor* b, co
     if (d->rows != a->rows || d->cols != b->cols)
       return fail(CDL_ERR_INVALID, "%s: d must have shape [%lld, %lld]", op,
                   static_cast<long long>(a->rows), static_cast<long long>(b->cols));
-    return matmul_mx_run(op, &at, &bt, nullptr, &dt, alpha, stream);
+    return matmul_mx_run(op, &at, &bt, nullptr, nullptr, &dt, alpha, 0.f, stream);
   }
-  return matmul_mx_run(op, a, b, nullptr, d, alpha, stream);
+  return matmul_mx_run(op, a, b, nullptr, nullptr, d, alpha, 0.f, stream);
 }
 
 }  // namespace cdl
 
 extern "C" {
 
-int32_t cdl_b200_matmul_mx(const cdl_mx_tensor* a, const cdl_mx_tensor* b, const cdl_tensor* d,
-                           float alpha, cdl_stream stream) {
-  return cdl::matmul_mx_execute(a, b, d, alpha, static_cast<cudaStream_t>(stream));
+int32_t cdl_b200_matmul_mx(const cdl_mx_tensor* a, const cdl_mx_tensor* b, const cdl_tensor* c,
+                           const cdl_tensor* d, float alpha, float beta, cdl_stream stream) {
+  return cdl::matmul_mx_execute(a, b, c, d, alpha, beta, static_cast<cudaStream_t>(stream));
 }
 
 int32_t cdl_b200_matmul_mx_out(const cdl_mx_tensor* a, const cdl_mx_tensor* b, const cdl_mx_tensor* d,

@@ -62,8 +62,8 @@ int32_t mx_dequantize_execute(const cdl_mx_tensor* x, const cdl_tensor* y, cudaS
 int32_t rmsnorm_fwd_mx_execute(const cdl_tensor* x, const cdl_tensor* scale, const cdl_tensor* bias,
                                float eps, const cdl_mx_tensor* y_row, const cdl_mx_tensor* y_col,
                                const cdl_tensor* r_inv, cudaStream_t stream);
-int32_t matmul_mx_execute(const cdl_mx_tensor* a, const cdl_mx_tensor* b, const cdl_tensor* d,
-                          float alpha, cudaStream_t stream);
+int32_t matmul_mx_execute(const cdl_mx_tensor* a, const cdl_mx_tensor* b, const cdl_tensor* c,
+                          const cdl_tensor* d, float alpha, float beta, cudaStream_t stream);
 int32_t matmul_mx_out_execute(const cdl_mx_tensor* a, const cdl_mx_tensor* b, const cdl_mx_tensor* d,
                               float alpha, cudaStream_t stream);
 

@@ -122,12 +122,14 @@ def norm_fwd_mx(x: torch.Tensor, scale: Optional[torch.Tensor] = None,
 
 
 def matmul_mx(a: MxTensor, b: MxTensor, out_dtype: torch.dtype = torch.bfloat16, alpha: float = 1.0,
-              out: Optional[torch.Tensor] = None) -> torch.Tensor:
-    """D = alpha * A . B for a rowwise A [M, K] and a colwise B [K, N]."""
+              out: Optional[torch.Tensor] = None, c: Optional[torch.Tensor] = None,
+              beta: float = 0.0) -> torch.Tensor:
+    """D = alpha * A . B + beta * C for a rowwise A [M, K] and a colwise B [K, N]; `c` may be `out`
+    (accumulation in place)."""
     if out is None:
         out = torch.empty(a.rows, b.cols, dtype=out_dtype, device=a.values.device)
-    aa, ab, td = a.arg(), b.arg(), tensor_arg(out)
-    check(lib.cdl_b200_matmul_mx(ref(aa), ref(ab), ref(td), alpha, _stream()))
+    aa, ab, tc, td = a.arg(), b.arg(), tensor_arg(c), tensor_arg(out)
+    check(lib.cdl_b200_matmul_mx(ref(aa), ref(ab), ref(tc), ref(td), alpha, beta, _stream()))
     return out
 
 

@@ -202,14 +202,15 @@ int32_t cdl_b200_rmsnorm_fwd_mx(const cdl_tensor* x, const cdl_tensor* scale, co
                                 const cdl_mx_tensor* y_colwise, const cdl_tensor* r_inv,
                                 cdl_stream stream);
 
-/* D = alpha * A . B with block-scaled operands: Matmul with InputKind::Mx(Mxfp8)
+/* D = alpha * A . B + beta * C with block-scaled operands: Matmul with InputKind::Mx(Mxfp8)
  * (crates/cleandl/src/execgraph/ops/matmul.rs:808-838, forwarded to cuBLASLt block scaling by the
  * reference; tests crates/cleandl/tests/matmul.rs:1041-1060).  A is rowwise [M, K], B is colwise
- * [K, N] (both K-contiguous), D is bf16 or f32 [M, N] with packed rows; accumulation is f32.
+ * [K, N] (both K-contiguous), D and C (nullable; needs beta != 0 to matter; may be D itself) are
+ * bf16 or f32 [M, N] with contiguous rows; accumulation is f32.
  * K % 32 == 0.  Both operands NVFP4 (InputKind::Mx(Nvfp4), tests :1063-1080) works the same way
  * with K % 64 == 0; mixed formats are rejected like in the reference (:569-571). */
-int32_t cdl_b200_matmul_mx(const cdl_mx_tensor* a, const cdl_mx_tensor* b, const cdl_tensor* d,
-                           float alpha, cdl_stream stream);
+int32_t cdl_b200_matmul_mx(const cdl_mx_tensor* a, const cdl_mx_tensor* b, const cdl_tensor* c,
+                           const cdl_tensor* d, float alpha, float beta, cdl_stream stream);
 
 /* The same product with a block-scaled output: MatmulOutput::BlockScaled { Mxfp8, dim }
  * (crates/cleandl/src/execgraph/ops/matmul.rs:826-834; test crates/cleandl/tests/matmul.rs:

@@ -104,11 +104,11 @@ def test_host_validation_needs_no_gpu(cdl):
     b = L.CdlMxTensor(512, 1024, L.CDL_MXFP8, L.CDL_MX_COLWISE, 64, 128)
     d = L.CdlTensor(ptr=2048, dtype=L.CDL_BF16, rank=2)
     d.shape[0], d.shape[1], d.stride[0], d.stride[1] = 128, 128, 128, 1
-    st = L.lib.cdl_b200_matmul_mx(ctypes.byref(a), ctypes.byref(b), ctypes.byref(d), 1.0, None)
+    st = L.lib.cdl_b200_matmul_mx(ctypes.byref(a), ctypes.byref(b), None, ctypes.byref(d), 1.0, 0.0, None)
     assert st == -1 and "contraction" in L.last_error()
     a = L.CdlMxTensor(512, 1024, L.CDL_MXFP8, L.CDL_MX_ROWWISE, 128, 64)
     b = L.CdlMxTensor(512, 1024, L.CDL_MXFP8, L.CDL_MX_COLWISE, 96, 128)
-    st = L.lib.cdl_b200_matmul_mx(ctypes.byref(a), ctypes.byref(b), ctypes.byref(d), 1.0, None)
+    st = L.lib.cdl_b200_matmul_mx(ctypes.byref(a), ctypes.byref(b), None, ctypes.byref(d), 1.0, 0.0, None)
     assert st == -1 and "contraction" in L.last_error()
 
 
@@ -370,10 +370,10 @@ def test_nvfp4_host_validation(cdl):
     b = L.CdlMxTensor(512, 1024, L.CDL_NVFP4, L.CDL_MX_COLWISE, 96, 128)
     d = L.CdlTensor(ptr=2048, dtype=L.CDL_BF16, rank=2)
     d.shape[0], d.shape[1], d.stride[0], d.stride[1] = 128, 128, 128, 1
-    st = L.lib.cdl_b200_matmul_mx(ctypes.byref(a), ctypes.byref(b), ctypes.byref(d), 1.0, None)
+    st = L.lib.cdl_b200_matmul_mx(ctypes.byref(a), ctypes.byref(b), None, ctypes.byref(d), 1.0, 0.0, None)
     assert st == -2 and "multiple of 64" in L.last_error()
     b = L.CdlMxTensor(512, 1024, L.CDL_MXFP8, L.CDL_MX_COLWISE, 96, 128)
-    st = L.lib.cdl_b200_matmul_mx(ctypes.byref(a), ctypes.byref(b), ctypes.byref(d), 1.0, None)
+    st = L.lib.cdl_b200_matmul_mx(ctypes.byref(a), ctypes.byref(b), None, ctypes.byref(d), 1.0, 0.0, None)
     assert st == -2 and "mixed" in L.last_error()
     assert cdl.mx.layout_bytes(128, 256, ROW, fmt=cdl.mx.NVFP4) == (128 * 128, 128 * 16)
     with pytest.raises(cdl._lib.CdlError, match="block size 16"):
@@ -487,3 +487,43 @@ def test_matmul_nvfp4_block_scaled_output(cdl, gpu_ok, dim, in_fmt):
     v_ref, s_ref = mx_ref.quantize_nvfp4(to_f32(plain), dim)
     assert np.array_equal(d.values.cpu().numpy(), v_ref)
     assert np.array_equal(nv_valid_scales(d, d.scale_factors.cpu().numpy()), nv_valid_scales(d, s_ref))
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("fmt", ["mxfp8", "nvfp4"])
+def test_matmul_mx_with_c(cdl, gpu_ok, fmt):
+    """alpha / beta / C with block-scaled operands, C bf16 and f32, and accumulation in place (the
+    weight-gradient form D (f32) += A . B), after the reference's accumulate_c test
+    (crates/cleandl/tests/matmul.rs:690-726)."""
+    m, k, n = 384, 256, 320
+    gen = torch.Generator().manual_seed(110)
+    a = torch.randn(m, k, generator=gen).to(torch.bfloat16)
+    b = torch.randn(k, n, generator=gen).to(torch.bfloat16)
+    if fmt == "nvfp4":
+        qa, _ = cdl.mx.quantize(a.cuda(), rowwise=True, fmt=cdl.mx.NVFP4)
+        qb = cdl.mx.quantize(b.cuda().T.contiguous(), rowwise=True, fmt=cdl.mx.NVFP4)[0].transposed()
+        da, _ = mx_ref.dequantize_nvfp4(qa.values.cpu().numpy(), qa.scale_factors.cpu().numpy(), m, k, ROW)
+        db, _ = mx_ref.dequantize_nvfp4(qb.values.cpu().numpy(), qb.scale_factors.cpu().numpy(), k, n, COL)
+    else:
+        qa, _ = cdl.mx.quantize(a.cuda(), rowwise=True)
+        _, qb = cdl.mx.quantize(b.cuda(), rowwise=False, colwise=True)
+        da, _ = mx_ref.dequantize(qa.values.cpu().numpy(), qa.scale_factors.cpu().numpy(), m, k, ROW)
+        db, _ = mx_ref.dequantize(qb.values.cpu().numpy(), qb.scale_factors.cpu().numpy(), k, n, COL)
+    prod = da.astype(np.float64) @ db.astype(np.float64)
+    bound = np.abs(da).astype(np.float64) @ np.abs(db).astype(np.float64)
+    for c_dtype, out_dtype in ((torch.bfloat16, torch.bfloat16), (torch.float32, torch.float32),
+                               (torch.bfloat16, torch.float32)):
+        c = torch.randn(m, n, generator=gen).to(c_dtype)
+        d = cdl.mx.matmul_mx(qa, qb, out_dtype=out_dtype, alpha=0.5, c=c.cuda(), beta=-2.0)
+        expected = 0.5 * prod - 2.0 * c.double().numpy()
+        tol = oracle.matmul_tolerance(expected, 0.5 * bound + 2.0 * np.abs(c.double().numpy()),
+                                      out_dtype == torch.bfloat16)
+        assert_all_close(f"{fmt} c {c_dtype} -> {out_dtype}", to_f32(d), expected, tol)
+    # in place, twice: D = C0 + 2 A.B
+    acc = torch.randn(m, n, generator=gen)
+    d = acc.cuda().clone()
+    for _ in range(2):
+        cdl.mx.matmul_mx(qa, qb, out=d, c=d, beta=1.0)
+    expected = acc.double().numpy() + 2.0 * prod
+    assert_all_close("in place", to_f32(d), expected,
+                     oracle.matmul_tolerance(expected, 2.0 * bound + np.abs(acc.double().numpy()), False))
