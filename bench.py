@@ -485,6 +485,54 @@ def run_kernel(args) -> None:
                       "steps": args.steps, "warmup": args.warmup}))
 
 
+# ------------------------------------------------------------------ block with MXFP8 products
+def run_block_mx(args) -> None:
+    """The block of benchmark configuration 4 with every matrix product on MXFP8 operands
+    (clean-lm_b200/sky1_mx.py), one GPU, inputs resident.  Not the headline metric: the numerics are
+    those of MXFP8; the line exists to measure the block-scaled operators end to end."""
+    import torch
+
+    import cleanlm_b200 as cdl
+
+    torch.cuda.set_device(0)
+    cfg = cdl.sky1.Sky1Config()
+    blk = cdl.sky1_mx.Sky1BlockMX(cfg, cdl.sky1.init_params(cfg, 3))
+    gen = torch.Generator(device="cuda").manual_seed(3)
+    x = torch.randn(cfg.tokens, cfg.hidden, device="cuda", generator=gen).to(torch.bfloat16)
+    dy = torch.randn(cfg.tokens, cfg.hidden, device="cuda", generator=gen).to(torch.bfloat16)
+    out, dx = torch.empty_like(x), torch.empty_like(x)
+
+    def step():
+        blk.forward(x, out)
+        blk.zero_grads()
+        blk.backward(dy, dx)
+
+    for _ in range(max(args.warmup, 3)):
+        step()
+    torch.cuda.synchronize()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    cdl._lib.profile_start(128 * args.steps + 64)
+    e0.record()
+    for _ in range(args.steps):
+        step()
+    e1.record()
+    torch.cuda.synchronize()
+    records = cdl._lib.profile_stop(128 * args.steps + 64)
+    ms = e0.elapsed_time(e1) / args.steps
+    by_kind = {}
+    for kind, t, _ in records:
+        by_kind[kind] = by_kind.get(kind, 0.0) + t
+    assert cdl._lib.device_status() == 0
+    print(json.dumps({
+        "metric": "sky1_block_mxfp8_fwd_bwd_tokens_per_s", "value": cfg.tokens / (ms * 1e-3),
+        "unit": "tokens/s", "n_gpus": 1, "steps": args.steps, "warmup": max(args.warmup, 3),
+        "ms_per_step": ms, "higher_is_better": True, "dtype": "mxfp8 products, bf16 elsewhere",
+        "data": "synthetic",
+        "config": {"workload": "sky-1 block fwd+bwd (config 4) with MXFP8 matrix products; weights "
+                               "quantised once outside the timed region",
+                   "kernel_ms_per_step": {k: round(v / args.steps, 4) for k, v in by_kind.items()}}}))
+
+
 # ------------------------------------------------------------------ full LM step (config 5)
 def run_lm(args) -> None:
     """24-layer sky-1-style LM training step (benchmark configuration 5): global batch 64 x 2048
@@ -588,12 +636,16 @@ def main() -> None:
     ap.add_argument("--batch", type=int, default=8)
     ap.add_argument("--seq", type=int, default=2048)
     ap.add_argument("--heads", type=int, default=16)
-    ap.add_argument("--workload", default="block", choices=["block", "lm"],
-                    help="block = benchmark configuration 4 (the headline metric); lm = the 24-layer training step")
+    ap.add_argument("--workload", default="block", choices=["block", "lm", "block_mx"],
+                    help="block = benchmark configuration 4 (the headline metric); lm = the 24-layer "
+                         "training step; block_mx = the block with MXFP8 matrix products (one GPU)")
     ap.add_argument("--layers", type=int, default=24)
     args = ap.parse_args()
     if args.workload == "lm":
         run_lm(args)
+        return
+    if args.workload == "block_mx":
+        run_block_mx(args)
         return
     if args.kernel:
         args.warmup = max(args.warmup, 3)

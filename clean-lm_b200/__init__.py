@@ -13,5 +13,6 @@ from . import ops  # noqa: F401
 from . import sky1  # noqa: F401
 from . import checkpoint  # noqa: F401
 from . import mx  # noqa: F401
+from . import sky1_mx  # noqa: F401
 
-__all__ = ["_lib", "ops", "sky1", "checkpoint", "mx"]
+__all__ = ["_lib", "ops", "sky1", "checkpoint", "mx", "sky1_mx"]

@@ -69,14 +69,19 @@ def _mx_arg(t: Optional[MxTensor]):
     return None if t is None else t.arg()
 
 
-def quantize(x: torch.Tensor, rowwise: bool = True, colwise: bool = False, fmt: int = MXFP8):
+def quantize(x: torch.Tensor, rowwise: bool = True, colwise: bool = False, fmt: int = MXFP8,
+             out=None):
     """bf16 [rows, cols] -> (rowwise MxTensor or None, colwise MxTensor or None).  NVFP4 has the
-    rowwise form only; a colwise NVFP4 operand is `quantize(x.T.contiguous(), fmt=NVFP4)[0].transposed()`."""
+    rowwise form only; a colwise NVFP4 operand is `quantize(x.T.contiguous(), fmt=NVFP4)[0].transposed()`.
+    `out` = (rowwise, colwise) of an earlier call reuses those buffers."""
     if not x.is_cuda:
         raise _lib.CdlError(-1, "operands must live in device memory (there is no CPU path)")
     rows, cols = x.shape
-    yr = MxTensor.empty(rows, cols, ROWWISE, x.device, zero_scales=True, fmt=fmt) if rowwise else None
-    yc = MxTensor.empty(rows, cols, COLWISE, x.device, zero_scales=True, fmt=fmt) if colwise else None
+    if out is not None:
+        yr, yc = out
+    else:
+        yr = MxTensor.empty(rows, cols, ROWWISE, x.device, zero_scales=True, fmt=fmt) if rowwise else None
+        yc = MxTensor.empty(rows, cols, COLWISE, x.device, zero_scales=True, fmt=fmt) if colwise else None
     tx, ar, ac = tensor_arg(x), _mx_arg(yr), _mx_arg(yc)
     check(lib.cdl_b200_mx_quantize(ref(tx), ref(ar), ref(ac), _stream()))
     return yr, yc

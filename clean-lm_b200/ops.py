@@ -98,12 +98,13 @@ def norm_bwd_scratch_bytes(rows: int, cols: int) -> int:
     return n.value
 
 
-def norm_bwd(x, dy, scale, r_inv, dscale, residual_dy=None, scratch=None) -> torch.Tensor:
+def norm_bwd(x, dy, scale, r_inv, dscale, residual_dy=None, scratch=None, dx=None) -> torch.Tensor:
     """dx of RMSNorm; `dscale` (f32 [cols]) is accumulated in place."""
     _require_cuda(x, dy, scale, r_inv, dscale, residual_dy)
     if x.dim() != 2:
         raise _lib.CdlError(-1, "norm_bwd: x must be a 2D tensor")
-    dx = torch.empty(x.shape, dtype=torch.bfloat16, device=x.device)
+    if dx is None:
+        dx = torch.empty(x.shape, dtype=torch.bfloat16, device=x.device)
     need = norm_bwd_scratch_bytes(x.shape[0], x.shape[1])
     if scratch is None:
         scratch = torch.empty(max(need, 16), dtype=torch.uint8, device=x.device)
@@ -151,7 +152,9 @@ def _attn_desc(opts: AttentionOpts) -> CdlAttnDesc:
     return d
 
 
-def attention_fwd(q, k, v, opts: AttentionOpts | None = None, lse: bool = True) -> AttentionFwdOutputs:
+def attention_fwd(q, k, v, opts: AttentionOpts | None = None, lse: bool = True,
+                  out=None) -> AttentionFwdOutputs:
+    """`out` (dense layout only) receives the result in place of a new tensor."""
     opts = opts or AttentionOpts()
     _require_cuda(q, k, v)
     if opts.packed:
@@ -169,7 +172,8 @@ def attention_fwd(q, k, v, opts: AttentionOpts | None = None, lse: bool = True) 
         return AttentionFwdOutputs(out, lse_t)
     if q.dim() != 4:
         raise _lib.CdlError(-1, "attention: q must be [batch, seqlen, heads, head_dim]")
-    out = torch.empty(q.shape, dtype=q.dtype, device=q.device)
+    if out is None:
+        out = torch.empty(q.shape, dtype=q.dtype, device=q.device)
     lse_t = (torch.empty(q.shape[0], q.shape[2], q.shape[1], dtype=torch.float32, device=q.device)
              if lse else None)
     desc = _attn_desc(opts)
