@@ -54,6 +54,7 @@ struct Params {
   uint8_t* row_sf;
   uint8_t* col_values;  // [cols, rows]; nullable
   uint8_t* col_sf;
+  int panel_cols;  // tile kernel: columns a CTA owns (blockIdx.y selects the panel); cols if one panel
 };
 
 __device__ __forceinline__ long long sf_index(int outer, int block, int blocks) {
@@ -282,7 +283,11 @@ template <bool NORM>
 __global__ void __launch_bounds__(1024, 1) mx_rowcol_tile_kernel(const Params p) {
   extern __shared__ __align__(16) uint8_t smem_raw[];
   __nv_bfloat16* tile = reinterpret_cast<__nv_bfloat16*>(smem_raw);
-  const int ld = p.cols + 8;
+  // Without the normalisation nothing couples the columns of a row, so wide matrices are cut
+  // into panels of panel_cols columns (blockIdx.y); with it there is one panel, the whole row.
+  const int pc0 = blockIdx.y * p.panel_cols;
+  const int pcols = min(p.panel_cols, p.cols - pc0);
+  const int ld = p.panel_cols + 8;
   const int lane = threadIdx.x & 31;
   const int warp = threadIdx.x >> 5;
   const int row_blocks = p.cols / BLOCK;
@@ -291,10 +296,10 @@ __global__ void __launch_bounds__(1024, 1) mx_rowcol_tile_kernel(const Params p)
   for (long long row0 = static_cast<long long>(blockIdx.x) * 32; row0 < p.rows;
        row0 += static_cast<long long>(gridDim.x) * 32) {
     const long long row = row0 + warp;  // rows % 32 == 0: always a real row
-    const __nv_bfloat16* xr = p.x + row * p.ldx;
+    const __nv_bfloat16* xr = p.x + row * p.ldx + pc0;
     __nv_bfloat16* trow = tile + warp * ld;
     float ss = 0.f;
-    for (int c = lane * 8; c < p.cols; c += 256) {
+    for (int c = lane * 8; c < pcols; c += 256) {
       const uint4 q = ld_nc_v4(xr + c);
       *reinterpret_cast<uint4*>(trow + c) = q;
       if (NORM) {
@@ -311,14 +316,14 @@ __global__ void __launch_bounds__(1024, 1) mx_rowcol_tile_kernel(const Params p)
       r = rsqrtf(ss * inv_cols + p.eps);
       if (lane == 0 && p.r_inv != nullptr) p.r_inv[row * p.r_inv_stride] = r;
     }
-    for (int c0 = 0; c0 < p.cols; c0 += 256) {  // warp-uniform
+    for (int c0 = 0; c0 < pcols; c0 += 256) {  // warp-uniform
       const int c = c0 + lane * 8;
-      const bool active = c < p.cols;
+      const bool active = c < pcols;
       float f[8];
 #pragma unroll
       for (int j = 0; j < 8; ++j) f[j] = 0.f;
       if (active) {
-        apply_norm8<NORM>(p, *reinterpret_cast<const uint4*>(trow + c), c, r, f);
+        apply_norm8<NORM>(p, *reinterpret_cast<const uint4*>(trow + c), pc0 + c, r, f);
         if (NORM) {
           uint4 q;
           q.x = pack_rounded(f[0], f[1]); q.y = pack_rounded(f[2], f[3]);
@@ -326,10 +331,10 @@ __global__ void __launch_bounds__(1024, 1) mx_rowcol_tile_kernel(const Params p)
           *reinterpret_cast<uint4*>(trow + c) = q;
         }
       }
-      if (p.row_values != nullptr) quantize_row8(p, f, active, row, c, lane, row_blocks);
+      if (p.row_values != nullptr) quantize_row8(p, f, active, row, pc0 + c, lane, row_blocks);
     }
     __syncthreads();
-    for (int c = threadIdx.x; c < p.cols; c += 1024) {
+    for (int c = threadIdx.x; c < pcols; c += 1024) {
       float v[32];
       float amax = 0.f;
 #pragma unroll
@@ -343,8 +348,8 @@ __global__ void __launch_bounds__(1024, 1) mx_rowcol_tile_kernel(const Params p)
 #pragma unroll
       for (int j = 0; j < 8; ++j)
         w[j] = fp8x4(v[4 * j] * ds, v[4 * j + 1] * ds, v[4 * j + 2] * ds, v[4 * j + 3] * ds);
-      st_global_v8(p.col_values + static_cast<long long>(c) * p.rows + row0, w);
-      p.col_sf[sf_index(c, static_cast<int>(row0 / BLOCK), col_blocks)] = static_cast<uint8_t>(e);
+      st_global_v8(p.col_values + static_cast<long long>(pc0 + c) * p.rows + row0, w);
+      p.col_sf[sf_index(pc0 + c, static_cast<int>(row0 / BLOCK), col_blocks)] = static_cast<uint8_t>(e);
     }
     __syncthreads();
   }
@@ -575,8 +580,14 @@ static int32_t mx_rows_run(const char* op, const cdl_tensor* x, const cdl_tensor
       return fail(CDL_ERR_CUDA, "cudaFuncSetAttribute failed: %s", cudaGetErrorString(err));
     const unsigned grid = static_cast<unsigned>(rows / 32);
     if (whole_rows) {
+      p.panel_cols = static_cast<int>(cols);
       if (norm) mx_rowcol_tile_kernel<true><<<grid, 1024, tile_bytes, stream>>>(p);
       else mx_rowcol_tile_kernel<false><<<grid, 1024, tile_bytes, stream>>>(p);
+    } else if (!norm) {
+      // plain quantisation of wide rows: panels of 2048 columns (a multiple of the 256-column stripe)
+      p.panel_cols = 2048;
+      const dim3 g2(grid, static_cast<unsigned>((cols + 2047) / 2048));
+      mx_rowcol_tile_kernel<false><<<g2, 1024, 32 * (2048 + 8) * 2, stream>>>(p);
     } else {
       if (norm) mx_rows_kernel<true, true><<<grid, 1024, COL_SMEM_BYTES, stream>>>(p);
       else mx_rows_kernel<false, true><<<grid, 1024, COL_SMEM_BYTES, stream>>>(p);
