@@ -109,6 +109,22 @@ class ClockSampler:
         self.samples = []
         self.proc = None
         self.t_begin = None  # samples read before mark() are dropped
+        self.nvml = None
+        # NVML read-only queries from a thread (a sample every few ms); nvidia-smi as a fallback
+        # (it manages two or three samples in a 100 ms region).
+        try:
+            import pynvml
+
+            pynvml.nvmlInit()
+            self.nvml = pynvml
+            self.handle = pynvml.nvmlDeviceGetHandleByIndex(self._physical_index(index))
+            self.max_sm = pynvml.nvmlDeviceGetMaxClockInfo(self.handle, pynvml.NVML_CLOCK_SM)
+            self.stop_flag = False
+            self.thread = threading.Thread(target=self._poll, daemon=True)
+            self.thread.start()
+            return
+        except Exception:
+            self.nvml = None
         try:
             self.proc = subprocess.Popen(
                 ["nvidia-smi", f"--query-gpu={self.FIELDS}", "--format=csv,noheader,nounits",
@@ -118,6 +134,38 @@ class ClockSampler:
             self.thread.start()
         except OSError:
             self.proc = None
+
+    @staticmethod
+    def _physical_index(index: int) -> int:
+        vis = os.environ.get("CUDA_VISIBLE_DEVICES")
+        if vis:
+            ids = [v.strip() for v in vis.split(",") if v.strip()]
+            if index < len(ids) and ids[index].isdigit():
+                return int(ids[index])
+        return index
+
+    def _poll(self):
+        n = self.nvml
+        bits = (("hw_slowdown", n.nvmlClocksEventReasonHwSlowdown if hasattr(n, "nvmlClocksEventReasonHwSlowdown")
+                 else n.nvmlClocksThrottleReasonHwSlowdown),
+                ("hw_thermal_slowdown", getattr(n, "nvmlClocksEventReasonHwThermalSlowdown",
+                                                getattr(n, "nvmlClocksThrottleReasonHwThermalSlowdown", 0))),
+                ("sw_thermal_slowdown", getattr(n, "nvmlClocksEventReasonSwThermalSlowdown",
+                                                getattr(n, "nvmlClocksThrottleReasonSwThermalSlowdown", 0))),
+                ("sw_power_cap", getattr(n, "nvmlClocksEventReasonSwPowerCap",
+                                         getattr(n, "nvmlClocksThrottleReasonSwPowerCap", 0))))
+        reasons_fn = getattr(n, "nvmlDeviceGetCurrentClocksEventReasons",
+                             getattr(n, "nvmlDeviceGetCurrentClocksThrottleReasons", None))
+        while not self.stop_flag:
+            try:
+                sm = n.nvmlDeviceGetClockInfo(self.handle, n.NVML_CLOCK_SM)
+                mask = reasons_fn(self.handle) if reasons_fn else 0
+            except Exception:
+                break
+            if self.t_begin is not None:
+                self.samples.append([str(sm), str(self.max_sm)] +
+                                    ["Active" if mask & bit else "Not Active" for _, bit in bits])
+            time.sleep(0.002)
 
     def _read(self):
         for line in self.proc.stdout:
@@ -130,13 +178,17 @@ class ClockSampler:
         self.t_begin = time.time()
 
     def stop(self) -> dict:
-        if self.proc is None:
+        if self.nvml is not None:
+            self.stop_flag = True
+            self.thread.join(timeout=2)
+        elif self.proc is None:
             return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
-        self.proc.terminate()
-        try:
-            self.proc.wait(timeout=5)
-        except subprocess.TimeoutExpired:
-            self.proc.kill()
+        else:
+            self.proc.terminate()
+            try:
+                self.proc.wait(timeout=5)
+            except subprocess.TimeoutExpired:
+                self.proc.kill()
         if not self.samples:
             return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["no samples"]}
         sm = [int(s[0]) for s in self.samples]
