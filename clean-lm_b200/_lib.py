@@ -105,6 +105,7 @@ SIGNATURES = {
     "cdl_b200_matmul_swiglu_dgrad": ([_T, _T, _T, _T, _T, _T, _vp], ctypes.c_int32),
     "cdl_b200_matmul_scratch_bytes": ([_T, _T, _T, ctypes.POINTER(_sz)], ctypes.c_int32),
     "cdl_b200_rmsnorm_fwd": ([_T, _T, _T, ctypes.c_float, _T, _T, _vp], ctypes.c_int32),
+    "cdl_b200_layernorm_fwd": ([_T, _T, _T, ctypes.c_float, _T, _T, _T, _vp], ctypes.c_int32),
     "cdl_b200_rmsnorm_bwd": ([_T, _T, _T, _T, _T, _T, _T, _vp, _sz, _vp], ctypes.c_int32),
     "cdl_b200_rmsnorm_bwd_static": ([_T, _T, _T, _T, _T, _T, _T, _vp], ctypes.c_int32),
     "cdl_b200_rmsnorm_bwd_scratch_bytes": ([ctypes.c_int64, ctypes.c_int64, ctypes.POINTER(_sz)],

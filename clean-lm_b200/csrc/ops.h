@@ -16,6 +16,9 @@ int32_t matmul_execute_epi(const cdl_tensor* a, const cdl_tensor* b, const cdl_t
 int32_t rmsnorm_fwd_execute(const cdl_tensor* x, const cdl_tensor* scale, const cdl_tensor* bias,
                             float eps, const cdl_tensor* y, const cdl_tensor* r_inv,
                             cudaStream_t stream);
+int32_t layernorm_fwd_execute(const cdl_tensor* x, const cdl_tensor* scale, const cdl_tensor* bias,
+                              float eps, const cdl_tensor* y, const cdl_tensor* mean,
+                              const cdl_tensor* r_inv, cudaStream_t stream);
 size_t rmsnorm_bwd_scratch_bytes(long long rows, long long cols);
 int32_t rmsnorm_bwd_execute(const cdl_tensor* x, const cdl_tensor* dy, const cdl_tensor* res,
                             const cdl_tensor* scale, const cdl_tensor* r_inv, const cdl_tensor* dx,

@@ -106,6 +106,83 @@ __global__ void __launch_bounds__(FWD_THREADS, NCH <= 8 ? 4 : 1)
   }
 }
 
+// LayerNorm forward (NormType::LayerNorm of the reference, crates/cleandl/src/execgraph/ops/norm/
+// mod.rs:23-30; reference tests/norm.rs:97-130): mean_i = mean_j x_ij, r_i = rsqrt(mean_j
+// (x_ij - mean_i)^2 + eps), y_ij = bf16((x_ij - mean_i) * r_i * scale_j + bias_j); optional mean
+// and r_inv outputs.  Same shape as the RMSNorm forward: a warp per row, the row in registers, the
+// variance taken around the mean in a second pass over the registers (no E[x^2] - mean^2).
+template <int NCH>
+__global__ void __launch_bounds__(FWD_THREADS, NCH <= 4 ? 4 : NCH <= 8 ? 3 : 1)
+    layernorm_fwd_kernel(const __nv_bfloat16* __restrict__ x, long long ldx,
+                         const __nv_bfloat16* __restrict__ scale,
+                         const __nv_bfloat16* __restrict__ bias, __nv_bfloat16* __restrict__ y,
+                         long long ldy, float* __restrict__ mean_out, long long mean_stride,
+                         float* __restrict__ r_inv, long long r_inv_stride, int rows, int cols,
+                         float eps) {
+  const int lane = threadIdx.x & 31;
+  const int warps_per_block = FWD_THREADS / 32;
+  const long long warp_global = static_cast<long long>(blockIdx.x) * warps_per_block + (threadIdx.x >> 5);
+  const long long warp_stride = static_cast<long long>(gridDim.x) * warps_per_block;
+  const float inv_cols = 1.0f / static_cast<float>(cols);
+  for (long long row = warp_global; row < rows; row += warp_stride) {
+    const __nv_bfloat16* xr = x + row * ldx;
+    uint4 v[NCH];
+#pragma unroll
+    for (int c = 0; c < NCH; ++c) {
+      const int col = c * 256 + lane * 8;
+      v[c] = col < cols ? ld_nc_v4(xr + col) : make_uint4(0, 0, 0, 0);
+    }
+    float sum = 0.f;
+#pragma unroll
+    for (int c = 0; c < NCH; ++c) {
+      float f[8];
+      unpack8(v[c], f);
+#pragma unroll
+      for (int j = 0; j < 8; ++j) sum += f[j];
+    }
+    const float mean = warp_sum(sum) * inv_cols;
+    float ss = 0.f;
+#pragma unroll
+    for (int c = 0; c < NCH; ++c) {
+      if (c * 256 + lane * 8 < cols) {
+        float f[8];
+        unpack8(v[c], f);
+#pragma unroll
+        for (int j = 0; j < 8; ++j) ss = fmaf(f[j] - mean, f[j] - mean, ss);
+      }
+    }
+    const float r = rsqrtf(warp_sum(ss) * inv_cols + eps);
+    if (lane == 0) {
+      if (mean_out != nullptr) mean_out[row * mean_stride] = mean;
+      if (r_inv != nullptr) r_inv[row * r_inv_stride] = r;
+    }
+    __nv_bfloat16* yr = y + row * ldy;
+#pragma unroll
+    for (int c = 0; c < NCH; ++c) {
+      const int col = c * 256 + lane * 8;
+      if (col < cols) {
+        float f[8];
+        unpack8(v[c], f);
+#pragma unroll
+        for (int j = 0; j < 8; ++j) f[j] = (f[j] - mean) * r;
+        if (scale != nullptr) {
+          float sc[8];
+          unpack8(__ldg(reinterpret_cast<const uint4*>(scale + col)), sc);
+#pragma unroll
+          for (int j = 0; j < 8; ++j) f[j] *= sc[j];
+        }
+        if (bias != nullptr) {
+          float b[8];
+          unpack8(__ldg(reinterpret_cast<const uint4*>(bias + col)), b);
+#pragma unroll
+          for (int j = 0; j < 8; ++j) f[j] += b[j];
+        }
+        st_cs_v4(yr + col, pack8(f));
+      }
+    }
+  }
+}
+
 // Pipelined forward: one persistent CTA per SM; warp 8 streams whole rows into a shared-memory
 // ring with 1-D bulk copies (up to 128 KiB in flight per SM, independent of how fast the rows
 // are consumed), warps 0-7 each take every 8th row of the CTA's slice out of the ring, reduce
@@ -629,6 +706,54 @@ int32_t rmsnorm_fwd_execute(const cdl_tensor* x, const cdl_tensor* scale, const 
   return CDL_OK;
 }
 
+template <int NCH>
+static void launch_layernorm(const cdl_tensor* x, const cdl_tensor* scale, const cdl_tensor* bias,
+                             float eps, const cdl_tensor* y, const cdl_tensor* mean,
+                             const cdl_tensor* r_inv, int rows, int cols, cudaStream_t stream) {
+  using namespace norm;
+  const int warps = FWD_THREADS / 32;
+  const long long want = (static_cast<long long>(rows) + warps - 1) / warps;
+  const int grid = static_cast<int>(want > (1 << 24) ? (1 << 24) : want);
+  layernorm_fwd_kernel<NCH><<<grid, FWD_THREADS, 0, stream>>>(
+      static_cast<const __nv_bfloat16*>(x->ptr), x->stride[0],
+      scale ? static_cast<const __nv_bfloat16*>(scale->ptr) : nullptr,
+      bias ? static_cast<const __nv_bfloat16*>(bias->ptr) : nullptr,
+      static_cast<__nv_bfloat16*>(y->ptr), y->stride[0],
+      mean ? static_cast<float*>(mean->ptr) : nullptr, mean ? mean->stride[0] : 0,
+      r_inv ? static_cast<float*>(r_inv->ptr) : nullptr, r_inv ? r_inv->stride[0] : 0, rows, cols, eps);
+}
+
+int32_t layernorm_fwd_execute(const cdl_tensor* x, const cdl_tensor* scale, const cdl_tensor* bias,
+                              float eps, const cdl_tensor* y, const cdl_tensor* mean,
+                              const cdl_tensor* r_inv, cudaStream_t stream) {
+  using namespace norm;
+  const char* op = "norm_fwd (layer norm)";
+  if (!x || !y) return fail(CDL_ERR_INVALID, "%s: x and y are required", op);
+  if (x->rank != 2) return fail(CDL_ERR_INVALID, "%s: x must be a 2D tensor", op);
+  const long long rows = x->shape[0], cols = x->shape[1];
+  if (cols % 8 != 0 || cols > 8192)
+    return fail(CDL_ERR_UNSUPPORTED,
+                "%s: cols must be a multiple of 8 and at most 8192 (got %lld)", op, cols);
+  CDL_CHECK(check_rows(op, "x", x, rows, cols));
+  CDL_CHECK(check_rows(op, "y", y, rows, cols));
+  if (scale) CDL_CHECK(check_vec(op, "scale", scale, cols, CDL_BF16, true));
+  if (bias) CDL_CHECK(check_vec(op, "bias", bias, cols, CDL_BF16, true));
+  if (mean) CDL_CHECK(check_vec(op, "mean", mean, rows, CDL_F32, false));
+  if (r_inv) CDL_CHECK(check_vec(op, "r_inv", r_inv, rows, CDL_F32, false));
+  if (rows == 0 || cols == 0) return CDL_OK;
+  if (rows > INT32_MAX) return fail(CDL_ERR_UNSUPPORTED, "%s: too many rows", op);
+  const int r = static_cast<int>(rows), c = static_cast<int>(cols);
+  ProfileScope ps(PROF_NORM_FWD, 4.0 * rows * cols + 2.0 * cols + 8.0 * rows, stream);
+  if (c <= 256) launch_layernorm<1>(x, scale, bias, eps, y, mean, r_inv, r, c, stream);
+  else if (c <= 512) launch_layernorm<2>(x, scale, bias, eps, y, mean, r_inv, r, c, stream);
+  else if (c <= 1024) launch_layernorm<4>(x, scale, bias, eps, y, mean, r_inv, r, c, stream);
+  else if (c <= 2048) launch_layernorm<8>(x, scale, bias, eps, y, mean, r_inv, r, c, stream);
+  else if (c <= 4096) launch_layernorm<16>(x, scale, bias, eps, y, mean, r_inv, r, c, stream);
+  else launch_layernorm<32>(x, scale, bias, eps, y, mean, r_inv, r, c, stream);
+  CDL_CUDA(cudaGetLastError());
+  return CDL_OK;
+}
+
 size_t rmsnorm_bwd_scratch_bytes(long long rows, long long cols) {
   (void)rows;
   return static_cast<size_t>(norm::MAX_PARTIALS) * static_cast<size_t>(cols) * sizeof(float);
@@ -765,6 +890,13 @@ int32_t cdl_b200_rmsnorm_fwd(const cdl_tensor* x, const cdl_tensor* scale, const
                              cdl_stream stream) {
   return cdl::rmsnorm_fwd_execute(x, scale, bias, eps, y, r_inv,
                                   static_cast<cudaStream_t>(stream));
+}
+
+int32_t cdl_b200_layernorm_fwd(const cdl_tensor* x, const cdl_tensor* scale, const cdl_tensor* bias,
+                               float eps, const cdl_tensor* y, const cdl_tensor* mean,
+                               const cdl_tensor* r_inv, cdl_stream stream) {
+  return cdl::layernorm_fwd_execute(x, scale, bias, eps, y, mean, r_inv,
+                                    static_cast<cudaStream_t>(stream));
 }
 
 int32_t cdl_b200_rmsnorm_bwd(const cdl_tensor* x, const cdl_tensor* dy,

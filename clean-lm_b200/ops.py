@@ -66,18 +66,21 @@ def matmul(a: torch.Tensor, b: torch.Tensor, opts: MatmulOpts | None = None,
 # --------------------------------------------------------------------------- norm
 @dataclass
 class NormFwdOpts:
-    """`NormFwdOpts` of the reference (ops/norm/mod.rs:87-111); RMSNorm with bf16 output only."""
+    """`NormFwdOpts` of the reference (ops/norm/mod.rs:87-111); bf16 output (the block-scaled outputs
+    are in `mx.norm_fwd_mx`).  `norm_type`: "rms" (`NormType::RmsNorm`) or "layer" (`LayerNorm`)."""
 
     scale: Optional[torch.Tensor] = None
     bias: Optional[torch.Tensor] = None
     eps: float = 1e-6
     save_stats: bool = False
+    norm_type: str = "rms"
 
 
 @dataclass
 class NormFwdOutputs:
     y: torch.Tensor
-    r_inv: Optional[torch.Tensor]  # per-row reciprocal RMS (f32), with save_stats
+    r_inv: Optional[torch.Tensor]  # per-row reciprocal RMS / standard deviation (f32), with save_stats
+    mean: Optional[torch.Tensor] = None  # per-row mean (f32): layer norm with save_stats
 
 
 def norm_fwd(x: torch.Tensor, opts: NormFwdOpts | None = None) -> NormFwdOutputs:
@@ -88,6 +91,14 @@ def norm_fwd(x: torch.Tensor, opts: NormFwdOpts | None = None) -> NormFwdOutputs
     y = torch.empty(x.shape, dtype=torch.bfloat16, device=x.device)
     r_inv = torch.empty(x.shape[0], dtype=torch.float32, device=x.device) if opts.save_stats else None
     tx, ts, tb, ty, tr = (tensor_arg(t) for t in (x, opts.scale, opts.bias, y, r_inv))
+    if opts.norm_type == "layer":
+        mean = torch.empty(x.shape[0], dtype=torch.float32, device=x.device) if opts.save_stats else None
+        tm = tensor_arg(mean)
+        check(lib.cdl_b200_layernorm_fwd(ref(tx), ref(ts), ref(tb), opts.eps, ref(ty), ref(tm), ref(tr),
+                                         _stream()))
+        return NormFwdOutputs(y, r_inv, mean)
+    if opts.norm_type != "rms":
+        raise _lib.CdlError(-1, f"norm_fwd: unknown norm type '{opts.norm_type}'")
     check(lib.cdl_b200_rmsnorm_fwd(ref(tx), ref(ts), ref(tb), opts.eps, ref(ty), ref(tr), _stream()))
     return NormFwdOutputs(y, r_inv)
 

@@ -112,6 +112,14 @@ int32_t cdl_b200_rmsnorm_fwd(const cdl_tensor* x, const cdl_tensor* scale, const
                              float eps, const cdl_tensor* y, const cdl_tensor* r_inv,
                              cdl_stream stream);
 
+/* LayerNorm forward: NormFwd with NormType::LayerNorm (ops/norm/mod.rs:23-30; tests
+ * crates/cleandl/tests/norm.rs:97-130): y = bf16((x - mean) * r_inv * scale + bias) with
+ * mean = mean_j x, r_inv = rsqrt(mean_j (x - mean)^2 + eps).  Operands as for the RMSNorm forward;
+ * mean and r_inv (f32 [rows], nullable) are the saved statistics. */
+int32_t cdl_b200_layernorm_fwd(const cdl_tensor* x, const cdl_tensor* scale, const cdl_tensor* bias,
+                               float eps, const cdl_tensor* y, const cdl_tensor* mean,
+                               const cdl_tensor* r_inv, cdl_stream stream);
+
 /* ---- RMSNorm backward ------------------------------------------------------------------
  * The reference tree holds only the call sites (crates/sky-1/src/training/model/decoder.rs:
  * 599-607, 684-692): dx = rmsnorm_backward(x, dy, residual_dy, scale, r_inv; dscale +=).

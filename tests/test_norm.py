@@ -122,3 +122,35 @@ def test_bwd_config2_determinism(cdl, gpu_ok):
     dx_ref, ds_ref = oracle.rmsnorm_bwd(to_f32(x), to_f32(dy), to_f32(w), None, 1e-6)
     assert np.abs(to_f32(dx1) - dx_ref).max() / np.abs(dx_ref).max() <= 1e-2
     assert np.abs(to_f32(ds1) - ds_ref).max() / np.abs(ds_ref).max() <= 1e-2
+
+
+def layernorm_reference(x, scale, bias, eps):
+    """The reference's test oracle for NormType::LayerNorm (crates/cleandl/tests/norm.rs:97-130), f64."""
+    x = x.astype(np.float64)
+    mean = x.mean(axis=1, keepdims=True)
+    var = ((x - mean) ** 2).mean(axis=1, keepdims=True)
+    r = 1.0 / np.sqrt(var + eps)
+    y = (x - mean) * r
+    if scale is not None:
+        y = y * scale.astype(np.float64)
+    if bias is not None:
+        y = y + bias.astype(np.float64)
+    return y, mean[:, 0], r[:, 0]
+
+
+@pytest.mark.parametrize("rows,cols", CASES)
+@pytest.mark.parametrize("affine", ["none", "scale_bias"])
+def test_layernorm_fwd_cases(cdl, gpu_ok, rows, cols, affine):
+    """NormType::LayerNorm: y within 1e-5 + 2^-7 |e|, mean and r_inv within 1e-5 / 1e-6 + 1e-4 |e|
+    (crates/cleandl/tests/norm.rs:261-268, 295-315)."""
+    x, scale, bias = make_inputs(rows, cols, 1)
+    s = scale if affine != "none" else None
+    b = bias if affine != "none" else None
+    out = cdl.ops.norm_fwd(x.cuda(), cdl.ops.NormFwdOpts(
+        scale=None if s is None else s.cuda(), bias=None if b is None else b.cuda(), eps=1e-6,
+        save_stats=True, norm_type="layer"))
+    y_ref, m_ref, r_ref = layernorm_reference(to_f32(x), None if s is None else to_f32(s),
+                                              None if b is None else to_f32(b), 1e-6)
+    assert_all_close("y", to_f32(out.y), y_ref, oracle.abs_rel_tolerance(y_ref, 1e-5, 2.0 ** -7))
+    assert_all_close("mean", to_f32(out.mean), m_ref, oracle.abs_rel_tolerance(m_ref, 1e-5, 1e-4))
+    assert_all_close("r_inv", to_f32(out.r_inv), r_ref, oracle.abs_rel_tolerance(r_ref, 1e-6, 1e-4))
