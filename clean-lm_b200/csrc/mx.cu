@@ -274,6 +274,121 @@ __global__ void __launch_bounds__(256, NCH <= 4 ? 4 : NCH <= 8 ? 2 : 1) mx_row_c
   }
 }
 
+#ifndef CDL_MX_FULL_MINB
+#define CDL_MX_FULL_MINB 3
+#endif
+// Packed bf16 pairs: |a| and max per half (exact: a maximum picks one of its operands).
+__device__ __forceinline__ uint32_t abs_max_bf16x2(uint32_t a, uint32_t b) {
+  const __nv_bfloat162 m = __hmax2(__habs2(*reinterpret_cast<const __nv_bfloat162*>(&a)),
+                                   __habs2(*reinterpret_cast<const __nv_bfloat162*>(&b)));
+  return *reinterpret_cast<const uint32_t*>(&m);
+}
+__device__ __forceinline__ uint32_t max_bf16x2(uint32_t a, uint32_t b) {
+  const __nv_bfloat162 m = __hmax2(*reinterpret_cast<const __nv_bfloat162*>(&a),
+                                   *reinterpret_cast<const __nv_bfloat162*>(&b));
+  return *reinterpret_cast<const uint32_t*>(&m);
+}
+
+// y of a lane's 8 elements as four packed bf16 pairs: x * r (* gamma, f32 from shared memory in
+// stage_gamma's layout: gamma2 points at the lane's first float4).
+__device__ __forceinline__ void norm_packed8(const uint4& xq, float r, const float4* gamma2,
+                                             uint32_t (&q)[4]) {
+  float f[8];
+  unpack8(xq, f);
+  if (gamma2 != nullptr) {
+    const float4 g0 = gamma2[0], g1 = gamma2[32];
+    f[0] = f[0] * r * g0.x; f[1] = f[1] * r * g0.y; f[2] = f[2] * r * g0.z; f[3] = f[3] * r * g0.w;
+    f[4] = f[4] * r * g1.x; f[5] = f[5] * r * g1.y; f[6] = f[6] * r * g1.z; f[7] = f[7] * r * g1.w;
+  } else {
+#pragma unroll
+    for (int j = 0; j < 8; ++j) f[j] *= r;
+  }
+#pragma unroll
+  for (int j = 0; j < 4; ++j) q[j] = pack_bf16x2(f[2 * j], f[2 * j + 1]);
+}
+// Rowwise quantisation of a lane's 8 packed bf16 values, a quarter of a 32-element block (all
+// four lanes of a block call): returns the 8 E4M3 bytes, e = the block's scale exponent.
+__device__ __forceinline__ uint2 quantize_packed8(const uint32_t (&q)[4], uint32_t& e) {
+  uint32_t m = max_bf16x2(abs_max_bf16x2(q[0], q[1]), abs_max_bf16x2(q[2], q[3]));
+  m = max_bf16x2(m, __shfl_xor_sync(0xffffffffu, m, 1));
+  m = max_bf16x2(m, __shfl_xor_sync(0xffffffffu, m, 2));
+  m = max_bf16x2(m, __byte_perm(m, 0, 0x1032));  // both halves: the block's amax
+  e = scale_exponent(__uint_as_float(m & 0xFFFF0000u));
+  const float ds = descale_of(e);
+  uint2 o;
+  o.x = fp8x4(bf16_lo(q[0]) * ds, bf16_hi(q[0]) * ds, bf16_lo(q[1]) * ds, bf16_hi(q[1]) * ds);
+  o.y = fp8x4(bf16_lo(q[2]) * ds, bf16_hi(q[2]) * ds, bf16_lo(q[3]) * ds, bf16_hi(q[3]) * ds);
+  return o;
+}
+// The scale vector as f32 in shared memory (all threads of the CTA call; ends with a barrier;
+// cols % 256 == 0).  Per 256-column stripe 64 float4: the first four values of lane l's eight
+// columns at [l], the last four at [32 + l], so that a warp's 128-bit loads touch consecutive
+// words (lane-interleaved halves at [2 l], [2 l + 1] would be two-way bank conflicts).
+__device__ __forceinline__ void stage_gamma(const __nv_bfloat16* gamma, int cols, float4* s_gamma) {
+  for (int c = threadIdx.x * 8; c < cols; c += blockDim.x * 8) {
+    float g[8];
+    unpack8(*reinterpret_cast<const uint4*>(gamma + c), g);
+    const int at = (c >> 8) * 64 + ((c & 255) >> 3);
+    s_gamma[at] = make_float4(g[0], g[1], g[2], g[3]);
+    s_gamma[at + 32] = make_float4(g[4], g[5], g[6], g[7]);
+  }
+  __syncthreads();
+}
+
+// Rowwise output only, cols == 256 * NCH exactly and no bias (a model's hidden dimension): the
+// trimmed form of mx_row_cached_kernel.  What bounds these kernels is the ALU pipe, so this one
+// spends as few of its operations per element as the arithmetic allows: the scale vector sits in
+// shared memory as f32 (no unpacking per row), the block maximum is taken on the packed bf16
+// results (half the operations, and no unpacking before it), no lane is ever idle (no selects),
+// and the row's pointers and the row part of the scale index are computed once per row, every
+// stripe at a constant offset from them.
+template <bool NORM, int NCH>
+__global__ void __launch_bounds__(256, NCH <= 8 ? CDL_MX_FULL_MINB : 1) mx_row_full_kernel(const Params p) {
+  extern __shared__ __align__(16) uint8_t smem_raw[];
+  float4* s_gamma = reinterpret_cast<float4*>(smem_raw);  // [cols] f32 (NORM with a scale vector)
+  constexpr int COLS = NCH * 256;
+  const int lane = threadIdx.x & 31;
+  const bool has_gamma = NORM && p.gamma != nullptr;
+  if (has_gamma) stage_gamma(p.gamma, COLS, s_gamma);
+  // Block of (stripe s, lane): b = 8 s + lane / 4, so b / 4 = 2 s + lane / 16, b % 4 = lane / 4 % 4.
+  const int sf_lane = (lane >> 4) * 512 + ((lane >> 2) & 3);
+  const long long warp_global = static_cast<long long>(blockIdx.x) * 8 + (threadIdx.x >> 5);
+  const long long warp_stride = static_cast<long long>(gridDim.x) * 8;
+  for (long long row = warp_global; row < p.rows; row += warp_stride) {
+    const uint4* xr = reinterpret_cast<const uint4*>(p.x + row * p.ldx) + lane;
+    uint4 xv[NCH];
+#pragma unroll
+    for (int s = 0; s < NCH; ++s) xv[s] = ld_nc_v4(xr + s * 32);
+    float r = 1.0f;
+    if (NORM) {
+      float ss = 0.f;
+#pragma unroll
+      for (int s = 0; s < NCH; ++s) {
+        float f[8];
+        unpack8(xv[s], f);
+#pragma unroll
+        for (int j = 0; j < 8; ++j) ss = fmaf(f[j], f[j], ss);
+      }
+#pragma unroll
+      for (int o = 16; o > 0; o >>= 1) ss += __shfl_xor_sync(0xffffffffu, ss, o);
+      r = rsqrtf(ss * (1.0f / COLS) + p.eps);
+      if (lane == 0 && p.r_inv != nullptr) p.r_inv[row * p.r_inv_stride] = r;
+    }
+    uint2* out = reinterpret_cast<uint2*>(p.row_values + row * COLS) + lane;
+    uint8_t* sf = p.row_sf + (row >> 7) * (NCH * 2 * 512) + (row & 31) * 16 + ((row & 127) >> 5) * 4 +
+                  sf_lane;
+#pragma unroll
+    for (int s = 0; s < NCH; ++s) {
+      uint32_t q[4] = {xv[s].x, xv[s].y, xv[s].z, xv[s].w};
+      if (NORM) norm_packed8(xv[s], r, has_gamma ? s_gamma + s * 64 + lane : nullptr, q);
+      uint32_t e;
+      const uint2 o = quantize_packed8(q, e);
+      out[s * 32] = o;
+      if ((lane & 3) == 0) sf[s * 1024] = static_cast<uint8_t>(e);
+    }
+  }
+}
+
 // Rowwise and colwise outputs, rows short enough for 32 of them to sit in shared memory
 // (TILE [32][cols + 8] bf16): a CTA of 32 warps owns 32 rows.  A warp loads its row into the
 // tile while it sums the squares, replaces it by the bf16 result (writing the rowwise output on
@@ -353,6 +468,211 @@ __global__ void __launch_bounds__(1024, 1) mx_rowcol_tile_kernel(const Params p)
     }
     __syncthreads();
   }
+}
+
+// Colwise quantisation of columns pc0 + 2 c2 and pc0 + 2 c2 + 1 of a staged tile of 32 rows
+// (ld bf16 per row): one 32-bit load brings a pair, the maximum over the rows runs on the pairs,
+// and each column leaves as one 32-byte sector of the transposed output.
+__device__ __forceinline__ void quantize_column_pair(const Params& p, const __nv_bfloat16* tile, int ld,
+                                                     int c2, int pc0, long long row0, int col_blocks) {
+  const uint32_t* tp = reinterpret_cast<const uint32_t*>(tile) + c2;
+  const int ldw = ld >> 1;
+  uint32_t w[32];
+#pragma unroll
+  for (int j = 0; j < 32; ++j) w[j] = tp[j * ldw];
+  uint32_t m = abs_max_bf16x2(w[0], w[1]);
+#pragma unroll
+  for (int j = 2; j < 32; j += 2) m = max_bf16x2(m, abs_max_bf16x2(w[j], w[j + 1]));
+  const uint32_t e_lo = scale_exponent(__uint_as_float(m << 16));
+  const uint32_t e_hi = scale_exponent(__uint_as_float(m & 0xFFFF0000u));
+  const float ds_lo = descale_of(e_lo), ds_hi = descale_of(e_hi);
+  uint32_t o_lo[8], o_hi[8];
+#pragma unroll
+  for (int j = 0; j < 8; ++j) {
+    o_lo[j] = fp8x4(bf16_lo(w[4 * j]) * ds_lo, bf16_lo(w[4 * j + 1]) * ds_lo,
+                    bf16_lo(w[4 * j + 2]) * ds_lo, bf16_lo(w[4 * j + 3]) * ds_lo);
+    o_hi[j] = fp8x4(bf16_hi(w[4 * j]) * ds_hi, bf16_hi(w[4 * j + 1]) * ds_hi,
+                    bf16_hi(w[4 * j + 2]) * ds_hi, bf16_hi(w[4 * j + 3]) * ds_hi);
+  }
+  const int col = pc0 + 2 * c2;
+  uint8_t* dst = p.col_values + static_cast<long long>(col) * p.rows + row0;
+  st_global_v8(dst, o_lo);
+  st_global_v8(dst + p.rows, o_hi);
+  // col is even: the next column's scale sits 16 bytes on (same 128-column tile)
+  uint8_t* csf = p.col_sf + sf_index(col, static_cast<int>(row0 / BLOCK), col_blocks);
+  csf[0] = static_cast<uint8_t>(e_lo);
+  csf[16] = static_cast<uint8_t>(e_hi);
+}
+
+// mx_rowcol_tile_kernel for panels whose width is a multiple of 256 and no bias, trimmed like
+// mx_row_full_kernel (packed block maxima, f32 scale vector in shared memory behind the tile, no
+// idle lanes, index arithmetic hoisted out of the stripes).  The colwise phase takes two columns
+// per thread: one 32-bit shared-memory load brings a bf16 pair, the maximum over the 32 rows runs
+// on the pairs, and each column still leaves as one 32-byte sector.
+template <bool NORM>
+__global__ void __launch_bounds__(1024, 1) mx_rowcol_full_kernel(const Params p) {
+  extern __shared__ __align__(16) uint8_t smem_raw[];
+  __nv_bfloat16* tile = reinterpret_cast<__nv_bfloat16*>(smem_raw);
+  const int ld = p.panel_cols + 8;
+  float4* s_gamma = reinterpret_cast<float4*>(smem_raw + static_cast<size_t>(64) * ld);
+  const int pc0 = blockIdx.y * p.panel_cols;
+  const int pcols = min(p.panel_cols, p.cols - pc0);
+  const int lane = threadIdx.x & 31;
+  const int warp = threadIdx.x >> 5;
+  const int row_tiles = (p.cols / BLOCK + 3) >> 2;
+  const int col_blocks = p.rows / BLOCK;
+  const float inv_cols = 1.0f / static_cast<float>(p.cols);
+  const bool has_gamma = NORM && p.gamma != nullptr;
+  if (has_gamma) stage_gamma(p.gamma, p.cols, s_gamma);  // with NORM the panel is the whole row
+  // Block of (stripe at column c0, lane): b = (pc0 + c0) / 32 + lane / 4, the first term a multiple of 8.
+  const int sf_lane = (lane >> 4) * 512 + ((lane >> 2) & 3);
+  const bool rowwise = p.row_values != nullptr;
+  for (long long row0 = static_cast<long long>(blockIdx.x) * 32; row0 < p.rows;
+       row0 += static_cast<long long>(gridDim.x) * 32) {
+    const long long row = row0 + warp;  // rows % 32 == 0: always a real row
+    const __nv_bfloat16* xr = p.x + row * p.ldx + pc0;
+    __nv_bfloat16* trow = tile + warp * ld;
+    float ss = 0.f;
+    for (int c = lane * 8; c < pcols; c += 256) {
+      const uint4 q = ld_nc_v4(xr + c);
+      *reinterpret_cast<uint4*>(trow + c) = q;
+      if (NORM) {
+        float f[8];
+        unpack8(q, f);
+#pragma unroll
+        for (int j = 0; j < 8; ++j) ss = fmaf(f[j], f[j], ss);
+      }
+    }
+    float r = 1.0f;
+    if (NORM) {
+#pragma unroll
+      for (int o = 16; o > 0; o >>= 1) ss += __shfl_xor_sync(0xffffffffu, ss, o);
+      r = rsqrtf(ss * inv_cols + p.eps);
+      if (lane == 0 && p.r_inv != nullptr) p.r_inv[row * p.r_inv_stride] = r;
+    }
+    if (NORM || rowwise) {
+      uint8_t* out = rowwise ? p.row_values + row * p.cols + pc0 + lane * 8 : nullptr;
+      uint8_t* sf = rowwise ? p.row_sf + ((row >> 7) * row_tiles + (pc0 >> 7)) * 512 +
+                                  (row & 31) * 16 + ((row & 127) >> 5) * 4 + sf_lane
+                            : nullptr;
+      for (int c0 = 0; c0 < pcols; c0 += 256) {
+        const int c = c0 + lane * 8;
+        const uint4 xq = *reinterpret_cast<const uint4*>(trow + c);
+        uint32_t q[4] = {xq.x, xq.y, xq.z, xq.w};
+        if (NORM) {
+          norm_packed8(xq, r, has_gamma ? s_gamma + (c0 >> 2) + lane : nullptr, q);
+          *reinterpret_cast<uint4*>(trow + c) = make_uint4(q[0], q[1], q[2], q[3]);
+        }
+        if (rowwise) {  // CTA-uniform: the shuffles see whole warps
+          uint32_t e;
+          const uint2 o = quantize_packed8(q, e);
+          *reinterpret_cast<uint2*>(out + c0) = o;
+          if ((lane & 3) == 0) sf[(c0 >> 7) * 512] = static_cast<uint8_t>(e);
+        }
+      }
+    }
+    __syncthreads();
+    for (int c2 = threadIdx.x; c2 < pcols / 2; c2 += 1024)
+      quantize_column_pair(p, tile, ld, c2, pc0, row0, col_blocks);
+    __syncthreads();
+  }
+}
+
+__device__ __forceinline__ void st_shared_cluster_f32(uint32_t cluster_addr, float v) {
+  asm volatile("st.shared::cluster.f32 [%0], %1;" ::"r"(cluster_addr), "f"(v) : "memory");
+}
+
+// Rowwise and colwise outputs by panels of W = panel_cols columns (512 or 1024, cols % W == 0,
+// no bias): CTA (blockIdx.x, blockIdx.y) owns rows [32 y, +32) x columns [W x, +W) with W / 2
+// threads, so that several CTAs share an SM and one's loads run under another's arithmetic (the
+// whole-row kernels above hold one CTA per SM and leave half of the issue slots idle), and the
+// last wave of CTAs is short.  With NORM the CTAs of a row of panels form a cluster (at most 8):
+// each sums the squares of its part of the 32 rows, writes the 32 partial sums into every
+// member's shared memory, and after one cluster barrier all of them add the parts in rank order,
+// so that every member normalises with the same bits.
+template <bool NORM>
+__global__ void __launch_bounds__(512, 2) mx_rowcol_panel_kernel(const Params p) {
+  extern __shared__ __align__(16) uint8_t smem_raw[];
+  const int W = p.panel_cols;
+  const int ld = W + 8;
+  __nv_bfloat16* tile = reinterpret_cast<__nv_bfloat16*>(smem_raw);
+  float4* s_gamma = reinterpret_cast<float4*>(smem_raw + static_cast<size_t>(64) * ld);  // [W] f32
+  float* s_ss = reinterpret_cast<float*>(s_gamma + W / 4);                               // [8][32]
+  const int pc0 = blockIdx.x * W;
+  const long long row0 = static_cast<long long>(blockIdx.y) * 32;
+  const int lane = threadIdx.x & 31;
+  const int warp = threadIdx.x >> 5;
+  const int warps = blockDim.x >> 5;
+  const int row_tiles = (p.cols / BLOCK + 3) >> 2;
+  const int col_blocks = p.rows / BLOCK;
+  const bool has_gamma = NORM && p.gamma != nullptr;
+  const bool rowwise = p.row_values != nullptr;
+  const uint32_t rank = NORM ? cluster_ctarank() : 0;
+  const uint32_t members = NORM ? gridDim.x : 1;
+  if (has_gamma) stage_gamma(p.gamma + pc0, W, s_gamma);
+  // A member's shared memory may be written only once that member runs: every CTA of the cluster
+  // passes this barrier before the first remote store.
+  if (NORM) cluster_sync_all();
+
+  for (int rr = warp; rr < 32; rr += warps) {
+    const __nv_bfloat16* xr = p.x + (row0 + rr) * p.ldx + pc0;
+    __nv_bfloat16* trow = tile + rr * ld;
+    float ss = 0.f;
+    for (int c = lane * 8; c < W; c += 256) {
+      const uint4 q = ld_nc_v4(xr + c);
+      *reinterpret_cast<uint4*>(trow + c) = q;
+      if (NORM) {
+        float f[8];
+        unpack8(q, f);
+#pragma unroll
+        for (int j = 0; j < 8; ++j) ss = fmaf(f[j], f[j], ss);
+      }
+    }
+    if (NORM) {
+#pragma unroll
+      for (int o = 16; o > 0; o >>= 1) ss += __shfl_xor_sync(0xffffffffu, ss, o);
+      if (lane < members)
+        st_shared_cluster_f32(mapa_shared(smem_u32(s_ss + rank * 32 + rr), lane), ss);
+    }
+  }
+  if (NORM) cluster_sync_all();  // every member's partial sums have landed; nothing remote after this
+
+  const int sf_lane = (lane >> 4) * 512 + ((lane >> 2) & 3);
+  if (NORM || rowwise) {
+    for (int rr = warp; rr < 32; rr += warps) {
+      const long long row = row0 + rr;
+      __nv_bfloat16* trow = tile + rr * ld;
+      float r = 1.0f;
+      if (NORM) {
+        float ss = 0.f;
+        for (uint32_t k = 0; k < members; ++k) ss += s_ss[k * 32 + rr];
+        r = rsqrtf(ss * (1.0f / static_cast<float>(p.cols)) + p.eps);
+        if (rank == 0 && lane == 0 && p.r_inv != nullptr) p.r_inv[row * p.r_inv_stride] = r;
+      }
+      uint8_t* out = rowwise ? p.row_values + row * p.cols + pc0 + lane * 8 : nullptr;
+      uint8_t* sf = rowwise ? p.row_sf + ((row >> 7) * row_tiles + (pc0 >> 7)) * 512 +
+                                  (row & 31) * 16 + ((row & 127) >> 5) * 4 + sf_lane
+                            : nullptr;
+      for (int c0 = 0; c0 < W; c0 += 256) {
+        const int c = c0 + lane * 8;
+        const uint4 xq = *reinterpret_cast<const uint4*>(trow + c);
+        uint32_t q[4] = {xq.x, xq.y, xq.z, xq.w};
+        if (NORM) {
+          norm_packed8(xq, r, has_gamma ? s_gamma + (c0 >> 2) + lane : nullptr, q);
+          *reinterpret_cast<uint4*>(trow + c) = make_uint4(q[0], q[1], q[2], q[3]);
+        }
+        if (rowwise) {  // CTA-uniform: the shuffles see whole warps
+          uint32_t e;
+          const uint2 o = quantize_packed8(q, e);
+          *reinterpret_cast<uint2*>(out + c0) = o;
+          if ((lane & 3) == 0) sf[(c0 >> 7) * 512] = static_cast<uint8_t>(e);
+        }
+      }
+    }
+  }
+  __syncthreads();
+  for (int c2 = threadIdx.x; c2 < W / 2; c2 += blockDim.x)
+    quantize_column_pair(p, tile, ld, c2, pc0, row0, col_blocks);
 }
 
 // NVFP4 rowwise output (NormOutput::Nvfp4Rowwise, no global scale): blocks of 16 elements, scale
@@ -564,30 +884,65 @@ static int32_t mx_rows_run(const char* op, const cdl_tensor* x, const cdl_tensor
     int dev = 0;
     CDL_CUDA(cudaGetDevice(&dev));
     const size_t tile_bytes = 32 * static_cast<size_t>(cols + 8) * 2;
+    const size_t gamma_bytes = norm && scale ? static_cast<size_t>(cols) * 4 : 0;
     const bool whole_rows = tile_bytes <= 227 * 1024;
+    // panels a multiple of 256 columns wide and no bias: the trimmed kernel
+    const bool full = cols % 256 == 0 && !(norm && bias) &&
+                      (!whole_rows || tile_bytes + gamma_bytes <= 227 * 1024);
     static std::once_flag once[64];
     cudaError_t err = cudaSuccess;
     std::call_once(once[dev & 63], [&] {
-      const void* fns[4] = {reinterpret_cast<const void*>(&mx_rows_kernel<true, true>),
+      const void* fns[8] = {reinterpret_cast<const void*>(&mx_rows_kernel<true, true>),
                             reinterpret_cast<const void*>(&mx_rows_kernel<false, true>),
                             reinterpret_cast<const void*>(&mx_rowcol_tile_kernel<true>),
-                            reinterpret_cast<const void*>(&mx_rowcol_tile_kernel<false>)};
-      for (int i = 0; i < 4 && err == cudaSuccess; ++i)
+                            reinterpret_cast<const void*>(&mx_rowcol_tile_kernel<false>),
+                            reinterpret_cast<const void*>(&mx_rowcol_full_kernel<true>),
+                            reinterpret_cast<const void*>(&mx_rowcol_full_kernel<false>),
+                            reinterpret_cast<const void*>(&mx_rowcol_panel_kernel<true>),
+                            reinterpret_cast<const void*>(&mx_rowcol_panel_kernel<false>)};
+      for (int i = 0; i < 8 && err == cudaSuccess; ++i)
         err = cudaFuncSetAttribute(fns[i], cudaFuncAttributeMaxDynamicSharedMemorySize,
                                    i < 2 ? static_cast<int>(COL_SMEM_BYTES) : 227 * 1024);
     });
     if (err != cudaSuccess)
       return fail(CDL_ERR_CUDA, "cudaFuncSetAttribute failed: %s", cudaGetErrorString(err));
     const unsigned grid = static_cast<unsigned>(rows / 32);
-    if (whole_rows) {
+    // Panels of 1024 (else 512) columns when they tile the row: every plain quantisation, and the
+    // normalisation of rows too long for 32 of them to sit in one CTA's shared memory (the panels
+    // of a row then form a cluster, which holds at most 8 CTAs; rows that fit measured the same
+    // either way and stay with the whole-row kernel).
+    const int panel = cols % 1024 == 0 ? 1024 : cols % 512 == 0 ? 512 : 0;
+    const bool use_panels = panel != 0 && rows / 32 <= 65535 &&
+                            (!norm || (!bias && cols / panel <= 8 && !(whole_rows && full)));
+    if (use_panels) {
+      p.panel_cols = panel;
+      const size_t smem = 64 * static_cast<size_t>(panel + 8) + static_cast<size_t>(panel) * 4 + 8 * 32 * 4;
+      cudaLaunchConfig_t cfg{};
+      cfg.gridDim = dim3(static_cast<unsigned>(cols / panel), grid);
+      cfg.blockDim = dim3(static_cast<unsigned>(panel / 2));
+      cfg.dynamicSmemBytes = smem;
+      cfg.stream = stream;
+      cudaLaunchAttribute attr{};
+      attr.id = cudaLaunchAttributeClusterDimension;
+      attr.val.clusterDim.x = norm ? static_cast<unsigned>(cols / panel) : 1;
+      attr.val.clusterDim.y = 1;
+      attr.val.clusterDim.z = 1;
+      cfg.attrs = &attr;
+      cfg.numAttrs = 1;
+      if (norm) CDL_CUDA(cudaLaunchKernelEx(&cfg, mx_rowcol_panel_kernel<true>, p));
+      else CDL_CUDA(cudaLaunchKernelEx(&cfg, mx_rowcol_panel_kernel<false>, p));
+    } else if (whole_rows) {
       p.panel_cols = static_cast<int>(cols);
-      if (norm) mx_rowcol_tile_kernel<true><<<grid, 1024, tile_bytes, stream>>>(p);
+      if (full && norm) mx_rowcol_full_kernel<true><<<grid, 1024, tile_bytes + gamma_bytes, stream>>>(p);
+      else if (full) mx_rowcol_full_kernel<false><<<grid, 1024, tile_bytes, stream>>>(p);
+      else if (norm) mx_rowcol_tile_kernel<true><<<grid, 1024, tile_bytes, stream>>>(p);
       else mx_rowcol_tile_kernel<false><<<grid, 1024, tile_bytes, stream>>>(p);
     } else if (!norm) {
       // plain quantisation of wide rows: panels of 2048 columns (a multiple of the 256-column stripe)
       p.panel_cols = 2048;
       const dim3 g2(grid, static_cast<unsigned>((cols + 2047) / 2048));
-      mx_rowcol_tile_kernel<false><<<g2, 1024, 32 * (2048 + 8) * 2, stream>>>(p);
+      if (full) mx_rowcol_full_kernel<false><<<g2, 1024, 32 * (2048 + 8) * 2, stream>>>(p);
+      else mx_rowcol_tile_kernel<false><<<g2, 1024, 32 * (2048 + 8) * 2, stream>>>(p);
     } else {
       if (norm) mx_rows_kernel<true, true><<<grid, 1024, COL_SMEM_BYTES, stream>>>(p);
       else mx_rows_kernel<false, true><<<grid, 1024, COL_SMEM_BYTES, stream>>>(p);
@@ -600,6 +955,26 @@ static int32_t mx_rows_run(const char* op, const cdl_tensor* x, const cdl_tensor
     if (norm) mx_row_cached_kernel<true, NCH><<<grid, 256, 0, stream>>>(p);              \
     else mx_row_cached_kernel<false, NCH><<<grid, 256, 0, stream>>>(p);                  \
   } while (0)
+    // cols == 256 * NCH exactly, no bias, up to 4096 columns: the trimmed kernel (scale vector
+    // as f32 in shared memory, at most 16 KiB)
+    const bool full = cols % 256 == 0 && cols <= 4096 && (cols / 256 & (cols / 256 - 1)) == 0 &&
+                      !(norm && bias);
+    const size_t gamma_bytes = norm && scale ? static_cast<size_t>(cols) * 4 : 0;
+#define CDL_MX_FULL(NCH)                                                                 \
+  do {                                                                                   \
+    if (norm) mx_row_full_kernel<true, NCH><<<grid, 256, gamma_bytes, stream>>>(p);      \
+    else mx_row_full_kernel<false, NCH><<<grid, 256, 0, stream>>>(p);                    \
+  } while (0)
+    if (full) {
+      switch (cols / 256) {
+        case 1: CDL_MX_FULL(1); break;
+        case 2: CDL_MX_FULL(2); break;
+        case 4: CDL_MX_FULL(4); break;
+        case 8: CDL_MX_FULL(8); break;
+        default: CDL_MX_FULL(16); break;
+      }
+    } else
+#undef CDL_MX_FULL
     if (cols <= 256) CDL_MX_ROW(1);
     else if (cols <= 512) CDL_MX_ROW(2);
     else if (cols <= 1024) CDL_MX_ROW(4);

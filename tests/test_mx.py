@@ -129,7 +129,8 @@ def rand_bf16(rows, cols, seed, spread=2.0):
 
 @pytest.mark.gpu
 @pytest.mark.parametrize("rows,cols", [(1, 128), (37, 4096), (300, 2048), (128, 8192), (96, 512),
-                                        (64, 160), (256, 7168), (4, 16384), (32, 12288)])
+                                        (64, 160), (256, 7168), (4, 16384), (32, 12288), (8, 256),
+                                        (64, 768), (160, 1280), (32, 2304)])
 def test_quantize_is_bit_exact(cdl, gpu_ok, rows, cols):
     x = rand_bf16(rows, cols, 10)
     x[0, :32] = 0  # an all-zero block
@@ -148,6 +149,17 @@ def test_quantize_is_bit_exact(cdl, gpu_ok, rows, cols):
 
 
 @pytest.mark.gpu
+@pytest.mark.parametrize("rows,cols", [(64, 512), (96, 4352), (32, 72)])
+def test_quantize_colwise_only_is_bit_exact(cdl, gpu_ok, rows, cols):
+    x = rand_bf16(rows, cols, 12)
+    yr, yc = cdl.mx.quantize(x.cuda(), rowwise=False, colwise=True)
+    assert yr is None
+    v_ref, s_ref = mx_ref.quantize(to_f32(x), COL)
+    assert np.array_equal(yc.values.cpu().numpy(), v_ref)
+    assert np.array_equal(valid_scales(yc, yc.scale_factors.cpu().numpy()), valid_scales(yc, s_ref))
+
+
+@pytest.mark.gpu
 def test_quantize_strided_rows(cdl, gpu_ok):
     big = rand_bf16(64, 1024, 11).cuda()
     x = big[:, 256:768]
@@ -159,7 +171,8 @@ def test_quantize_strided_rows(cdl, gpu_ok):
 
 
 NORM_CASES = [(1, 128), (37, 4096), (300, 2048), (128, 8192), (100, 7168), (5, 1024), (96, 512),
-              (320, 1536), (16384, 2048), (3, 16384)]
+              (320, 1536), (16384, 2048), (3, 16384), (64, 256), (40, 768), (64, 4096),
+              (32, 6144), (64, 5120), (32, 3584)]
 
 
 @pytest.mark.gpu
