@@ -21,8 +21,10 @@ NVFP4 (no global scale factor, as in the reference's NormOutput::Nvfp4Rowwise): 
 elements share one E4M3 scale; values are FP4 E2M1 (magnitudes 0, 0.5, 1, 1.5, 2, 3, 4, 6), two per
 byte, the even element in the low nibble.  The quantiser here is the device's: scale = amax / 6
 rounded to nearest E4M3 (the reference's kernel, crates/cleandl-specialized-kernels/src/utils/
-block_scale.rs:28-31, 55-66), elements x / scale rounded to nearest E2M1 with ties to even and
-saturation, all zero when the scale rounds to zero.  The reference's HOST test quantiser
+block_scale.rs:28-31, 55-66), elements x * (1 / scale) rounded to nearest E2M1 with ties to even
+and saturation, all zero when the scale rounds to zero; the reciprocal and the product are
+correctly rounded f32 operations (the reference multiplies by an approximate bf16 reciprocal),
+which keeps the bits reproducible on any IEEE machine.  The reference's HOST test quantiser
 (tests/matmul.rs:922-935) floors the scale at 2^-9 and breaks ties toward the smaller magnitude;
 both lie within the tolerance its tests allow an NVFP4 result (0.34 |y| + 0.5 scale).
 """
@@ -177,8 +179,8 @@ def quantize_nvfp4(m: np.ndarray, dim: int):
     sbits = e4m3_encode((amax / np.float32(6.0)).astype(np.float32))
     scale = e4m3_decode(sbits)  # float32
     with np.errstate(divide="ignore", invalid="ignore"):
-        q = (blk / scale[:, :, None]).astype(np.float32)
-    q = np.where(scale[:, :, None] == 0, np.float32(0), q)
+        inv = np.where(scale == 0, np.float32(0), np.float32(1) / scale).astype(np.float32)
+    q = (blk * inv[:, :, None]).astype(np.float32)
     codes = e2m1_encode(q).reshape(outer, inner)
     values = (codes[:, 0::2] | (codes[:, 1::2] << 4)).astype(np.uint8)
     scales = np.zeros(sf_rows * sf_cols, dtype=np.uint8)

@@ -61,7 +61,8 @@ def nvfp4(m):
     amax = blk.abs().amax(dim=2)
     s8 = (amax / 6.0).to(torch.float32).clamp(max=448.0).to(torch.float8_e4m3fn)  # satfinite
     scale = s8.to(torch.float32)
-    q = torch.where(scale.unsqueeze(2) == 0, torch.zeros_like(blk), blk / scale.unsqueeze(2))
+    inv = torch.where(scale == 0, torch.zeros_like(scale), 1.0 / scale)  # correctly rounded f32
+    q = blk * inv.unsqueeze(2)
     codes = e2m1_codes(q.to(torch.float32)).view(outer, inner)
     values = (codes[:, 0::2] | (codes[:, 1::2] << 4)).contiguous()
     sf = torch.zeros(((outer + 127) // 128 * 128) * ((inner // 16 + 3) // 4 * 4), dtype=torch.uint8)
