@@ -212,7 +212,7 @@ __device__ __forceinline__ uint32_t fp8x4(float a, float b, float c, float d) {
 }
 
 // The NVFP4 form of the block-scaled store: the 32 columns are two blocks of 16; scale = amax / 6
-// rounded to nearest E4M3, elements x / scale rounded to nearest E2M1 (the quantiser of mx.cu).
+// rounded to nearest E4M3, elements x * (1 / scale) rounded to nearest E2M1 (the quantiser of mx.cu).
 __device__ __forceinline__ void store32_nvfp4(const Params& p, const uint32_t (&r)[32], int row, int col0) {
   if (row >= p.M) return;
   uint32_t out[4];
@@ -228,14 +228,15 @@ __device__ __forceinline__ void store32_nvfp4(const Params& p, const uint32_t (&
     }
     const __nv_fp8_storage_t sbits = __nv_cvt_float_to_fp8(__fdiv_rn(amax, 6.0f), __NV_SATFINITE, __NV_E4M3);
     const float sc = __half2float(__half(__nv_cvt_fp8_to_halfraw(sbits, __NV_E4M3)));
+    const float inv = sc != 0.f ? __frcp_rn(sc) : 0.f;  // a zero scale stores zeros
     sf2 |= static_cast<uint32_t>(sbits) << (8 * h);
 #pragma unroll
     for (int w = 0; w < 2; ++w) {
       uint32_t word = 0;
 #pragma unroll
       for (int j = 0; j < 4; ++j) {
-        const float a = sc != 0.f ? __fdiv_rn(v[w * 8 + 2 * j], sc) : 0.f;
-        const float b = sc != 0.f ? __fdiv_rn(v[w * 8 + 2 * j + 1], sc) : 0.f;
+        const float a = __fmul_rn(v[w * 8 + 2 * j], inv);
+        const float b = __fmul_rn(v[w * 8 + 2 * j + 1], inv);
         word |= static_cast<uint32_t>(__nv_cvt_float2_to_fp4x2(make_float2(a, b), __NV_E2M1, cudaRoundNearest))
                 << (8 * j);
       }

@@ -676,10 +676,11 @@ __global__ void __launch_bounds__(512, 2) mx_rowcol_panel_kernel(const Params p)
 }
 
 // NVFP4 rowwise output (NormOutput::Nvfp4Rowwise, no global scale): blocks of 16 elements, scale
-// = amax / 6 rounded to nearest E4M3, elements x / scale rounded to nearest E2M1 (ties to even,
-// saturating), two per byte; a block whose scale rounds to zero stores zeros
-// (crates/cleandl-specialized-kernels/src/utils/block_scale.rs:28-31, 55-66, with an exact
-// division where the reference multiplies by an approximate reciprocal).  A lane's 8 elements are
+// = amax / 6 rounded to nearest E4M3, elements x * (1 / scale) rounded to nearest E2M1 (ties to
+// even, saturating), two per byte; a block whose scale rounds to zero stores zeros
+// (crates/cleandl-specialized-kernels/src/utils/block_scale.rs:28-31, 55-66; the reciprocal and
+// the product are correctly rounded f32 operations where the reference takes an approximate
+// bf16 reciprocal, so that a host restatement reproduces the bits).  A lane's 8 elements are
 // half a block: one shuffle.  x is read twice (the second time from cache).
 template <bool NORM>
 __global__ void __launch_bounds__(256, 2) nvfp4_rows_kernel(const Params p) {
@@ -719,11 +720,12 @@ __global__ void __launch_bounds__(256, 2) nvfp4_rows_kernel(const Params p) {
         const __nv_fp8_storage_t sbits =
             __nv_cvt_float_to_fp8(__fdiv_rn(amax, 6.0f), __NV_SATFINITE, __NV_E4M3);
         const float sc = __half2float(__half(__nv_cvt_fp8_to_halfraw(sbits, __NV_E4M3)));
+        const float inv = sc != 0.f ? __frcp_rn(sc) : 0.f;  // a zero scale stores zeros
         uint32_t out = 0;
 #pragma unroll
         for (int j = 0; j < 4; ++j) {
-          const float a = sc != 0.f ? __fdiv_rn(f[2 * j], sc) : 0.f;
-          const float b = sc != 0.f ? __fdiv_rn(f[2 * j + 1], sc) : 0.f;
+          const float a = __fmul_rn(f[2 * j], inv);
+          const float b = __fmul_rn(f[2 * j + 1], inv);
           out |= static_cast<uint32_t>(__nv_cvt_float2_to_fp4x2(make_float2(a, b), __NV_E2M1, cudaRoundNearest))
                  << (8 * j);
         }
@@ -731,6 +733,69 @@ __global__ void __launch_bounds__(256, 2) nvfp4_rows_kernel(const Params p) {
         if ((lane & 1) == 0)
           p.row_sf[sf_index(static_cast<int>(row), c / 16, row_blocks)] = sbits;
       }
+    }
+  }
+}
+
+// nvfp4_rows_kernel for cols == 256 * NCH exactly and no bias, trimmed like mx_row_full_kernel:
+// the row stays in registers (x is read once), the scale vector sits in shared memory as f32, the
+// block maximum is taken on the packed bf16 results, index arithmetic is per row.
+template <bool NORM, int NCH>
+__global__ void __launch_bounds__(256, NCH <= 8 ? CDL_MX_FULL_MINB : 1) nvfp4_row_full_kernel(const Params p) {
+  extern __shared__ __align__(16) uint8_t smem_raw[];
+  float4* s_gamma = reinterpret_cast<float4*>(smem_raw);
+  constexpr int COLS = NCH * 256;
+  const int lane = threadIdx.x & 31;
+  const bool has_gamma = NORM && p.gamma != nullptr;
+  if (has_gamma) stage_gamma(p.gamma, COLS, s_gamma);
+  // Block of (stripe s, lane): b = 16 s + lane / 2, so b / 4 = 4 s + lane / 8, b % 4 = lane / 2 % 4.
+  const int sf_lane = (lane >> 3) * 512 + ((lane >> 1) & 3);
+  const long long warp_global = static_cast<long long>(blockIdx.x) * 8 + (threadIdx.x >> 5);
+  const long long warp_stride = static_cast<long long>(gridDim.x) * 8;
+  for (long long row = warp_global; row < p.rows; row += warp_stride) {
+    const uint4* xr = reinterpret_cast<const uint4*>(p.x + row * p.ldx) + lane;
+    uint4 xv[NCH];
+#pragma unroll
+    for (int s = 0; s < NCH; ++s) xv[s] = ld_nc_v4(xr + s * 32);
+    float r = 1.0f;
+    if (NORM) {
+      float ss = 0.f;
+#pragma unroll
+      for (int s = 0; s < NCH; ++s) {
+        float f[8];
+        unpack8(xv[s], f);
+#pragma unroll
+        for (int j = 0; j < 8; ++j) ss = fmaf(f[j], f[j], ss);
+      }
+#pragma unroll
+      for (int o = 16; o > 0; o >>= 1) ss += __shfl_xor_sync(0xffffffffu, ss, o);
+      r = rsqrtf(ss * (1.0f / COLS) + p.eps);
+      if (lane == 0 && p.r_inv != nullptr) p.r_inv[row * p.r_inv_stride] = r;
+    }
+    uint32_t* out = reinterpret_cast<uint32_t*>(p.row_values + row * (COLS / 2)) + lane;
+    uint8_t* sf = p.row_sf + (row >> 7) * (NCH * 4 * 512) + (row & 31) * 16 + ((row & 127) >> 5) * 4 +
+                  sf_lane;
+#pragma unroll
+    for (int s = 0; s < NCH; ++s) {
+      uint32_t q[4] = {xv[s].x, xv[s].y, xv[s].z, xv[s].w};
+      if (NORM) norm_packed8(xv[s], r, has_gamma ? s_gamma + s * 64 + lane : nullptr, q);
+      uint32_t m = max_bf16x2(abs_max_bf16x2(q[0], q[1]), abs_max_bf16x2(q[2], q[3]));
+      m = max_bf16x2(m, __shfl_xor_sync(0xffffffffu, m, 1));  // a block of 16 is two lanes
+      m = max_bf16x2(m, __byte_perm(m, 0, 0x1032));
+      const float amax = __uint_as_float(m & 0xFFFF0000u);
+      const __nv_fp8_storage_t sbits =
+          __nv_cvt_float_to_fp8(__fdiv_rn(amax, 6.0f), __NV_SATFINITE, __NV_E4M3);
+      const float sc = __half2float(__half(__nv_cvt_fp8_to_halfraw(sbits, __NV_E4M3)));
+      const float inv = sc != 0.f ? __frcp_rn(sc) : 0.f;  // a zero scale stores zeros
+      uint32_t word = 0;
+#pragma unroll
+      for (int j = 0; j < 4; ++j)
+        word |= static_cast<uint32_t>(__nv_cvt_float2_to_fp4x2(
+                    make_float2(__fmul_rn(bf16_lo(q[j]), inv), __fmul_rn(bf16_hi(q[j]), inv)), __NV_E2M1,
+                    cudaRoundNearest))
+                << (8 * j);
+      out[s * 32] = word;
+      if ((lane & 1) == 0) sf[s * 2048] = sbits;
     }
   }
 }
@@ -878,8 +943,25 @@ static int32_t mx_rows_run(const char* op, const cdl_tensor* x, const cdl_tensor
   if (fp4) {
     const long long want = (rows + 7) / 8;
     const unsigned grid = static_cast<unsigned>(want < 16LL * sm_count() ? want : 16LL * sm_count());
-    if (norm) nvfp4_rows_kernel<true><<<grid, 256, 0, stream>>>(p);
+    const long long nch = cols / 256;
+    const bool full = cols % 256 == 0 && cols <= 4096 && (nch & (nch - 1)) == 0 && !(norm && bias);
+    const size_t gamma_bytes = norm && scale ? static_cast<size_t>(cols) * 4 : 0;
+#define CDL_FP4_FULL(NCH)                                                                  \
+  do {                                                                                     \
+    if (norm) nvfp4_row_full_kernel<true, NCH><<<grid, 256, gamma_bytes, stream>>>(p);     \
+    else nvfp4_row_full_kernel<false, NCH><<<grid, 256, 0, stream>>>(p);                   \
+  } while (0)
+    if (full) {
+      switch (nch) {
+        case 1: CDL_FP4_FULL(1); break;
+        case 2: CDL_FP4_FULL(2); break;
+        case 4: CDL_FP4_FULL(4); break;
+        case 8: CDL_FP4_FULL(8); break;
+        default: CDL_FP4_FULL(16); break;
+      }
+    } else if (norm) nvfp4_rows_kernel<true><<<grid, 256, 0, stream>>>(p);
     else nvfp4_rows_kernel<false><<<grid, 256, 0, stream>>>(p);
+#undef CDL_FP4_FULL
   } else if (y_col) {
     int dev = 0;
     CDL_CUDA(cudaGetDevice(&dev));

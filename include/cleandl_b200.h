@@ -190,9 +190,9 @@ int32_t cdl_b200_mx_layout(int32_t format, int32_t dim, int64_t rows, int64_t co
  * to a power of two, element = x / scale rounded to nearest E4M3, saturating
  * (crates/cleandl-specialized-kernels/src/utils/block_scale.rs:24-55; the host quantiser of
  * crates/cleandl/tests/matmul.rs:885-952 gives the same bits).  Scale bytes of the padding are
- * not written.  NVFP4 (y_rowwise only): scale = amax / 6 rounded to nearest E4M3, element = x / scale
- * rounded to nearest E2M1, ties to even, saturating; zeros when the scale rounds to zero
- * (block_scale.rs:28-31, 55-66). */
+ * not written.  NVFP4 (y_rowwise only): scale = amax / 6 rounded to nearest E4M3, element =
+ * x * (1 / scale), reciprocal and product correctly rounded in f32, rounded to nearest E2M1, ties
+ * to even, saturating; zeros when the scale rounds to zero (block_scale.rs:28-31, 55-66). */
 int32_t cdl_b200_mx_quantize(const cdl_tensor* x, const cdl_mx_tensor* y_rowwise,
                              const cdl_mx_tensor* y_colwise, cdl_stream stream);
 
