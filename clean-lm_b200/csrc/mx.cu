@@ -24,6 +24,19 @@
 // consecutive rows (one warp each): the bf16 results of 1024 columns go through shared memory and
 // one thread per column quantises the 32 rows of its block and stores one 32-byte sector of the
 // transposed output.  NVFP4 (NormOutput::Nvfp4Rowwise): rowwise only, see nvfp4_rows_kernel.
+//
+// Kernels, from the general to the common case (the host picks in mx_rows_run):
+//   mx_rows_kernel            any shape; with the colwise output 1024 columns at a time through
+//                             shared memory (rows too long for the kernels below, or a bias)
+//   mx_row_cached_kernel      rowwise only, cols <= 8192: the row stays in registers
+//   mx_rowcol_tile_kernel     both outputs, 32 whole rows (or 2048-column panels) in shared memory
+//   mx_row_full_kernel,       cols % 256 == 0 and no bias: the same two schemes trimmed of every
+//   mx_rowcol_full_kernel     operation the arithmetic does not need (these kernels are bound by
+//                             the ALU pipe, not by HBM)
+//   mx_rowcol_panel_kernel    both outputs by 512- / 1024-column panels, several CTAs per SM; with
+//                             the normalisation the panels of a row are a cluster that shares the
+//                             row sums through distributed shared memory (rows up to 8192)
+//   nvfp4_rows_kernel, nvfp4_row_full_kernel   the NVFP4 rowwise output, general and trimmed
 #include "host.h"
 #include "ops.h"
 #include "ptx.cuh"
