@@ -44,8 +44,8 @@ def attention(q, k, v, causal=True):
     v = v.repeat_interleave(h // hk, dim=2)
     s = torch.einsum("bqhd,bkhd->bhqk", q, k) / math.sqrt(d)
     if causal:
-        i = torch.arange(sq)[:, None]
-        j = torch.arange(sk)[None, :]
+        i = torch.arange(sq, device=q.device)[:, None]
+        j = torch.arange(sk, device=q.device)[None, :]
         s = s.masked_fill(j > i + sk - sq, float("-inf"))
     p = torch.softmax(s, dim=-1)
     return torch.einsum("bhqk,bkhd->bqhd", p, v)

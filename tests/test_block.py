@@ -1,6 +1,7 @@
 """GPU parity of the sky-1 decoder block (forward + backward) against the float64 restatement of
-the reference's dataflow (oracle/block_ref.py), on reduced dimensions the CPU finishes in seconds,
-and of the elementwise kernels it uses.  Bound: the acceptance bound of 2e-2 of the largest magnitude for bf16
+the reference's dataflow (oracle/block_ref.py), on reduced dimensions the CPU finishes in seconds
+(and once at the full size of benchmark configuration 4, with the same restatement run in f32 on
+the device), and of the elementwise kernels it uses.  Bound: the acceptance bound of 2e-2 of the largest magnitude for bf16
 tensors produced by chains of bf16 GEMMs; gradients likewise."""
 import numpy as np
 import pytest
@@ -88,6 +89,41 @@ def test_block_forward_backward_vs_oracle(cdl, gpu_ok, dims):
         got = blk.grads[n].double().cpu() - g0[n].double()
         err = ((got - g_ref[n]).abs().max() / g_ref[n].abs().max()).item()
         assert err <= 2e-2, (n, err)
+
+
+def test_block_config4_full_size_vs_f32_on_device(cdl, gpu_ok):
+    """Benchmark configuration 4 at its full size (8 x 2048 tokens, hidden 2048, 16 heads, ffn
+    5632): the f64 oracle on the host would take minutes, so the same restatement runs in f32 on
+    the device (torch, TF32 off) and the bounds are those of the small cases."""
+    sky1 = cdl.sky1
+    cfg = sky1.Sky1Config()
+    assert (cfg.batch, cfg.seqlen, cfg.hidden, cfg.heads, cfg.ffn) == (8, 2048, 2048, 16, 5632)
+    params = sky1.init_params(cfg, seed=3)
+    gen = torch.Generator().manual_seed(3)
+    x = torch.randn(cfg.tokens, cfg.hidden, generator=gen).to(torch.bfloat16).cuda()
+    dy = torch.randn(cfg.tokens, cfg.hidden, generator=gen).to(torch.bfloat16).cuda()
+    blk = sky1.Sky1Block(cfg, params)
+    for g in blk.grads.values():
+        g.zero_()
+    out = blk.forward(x)
+    dx = blk.backward(dy)
+    torch.cuda.synchronize()
+
+    assert not torch.backends.cuda.matmul.allow_tf32
+    c = dict(heads=cfg.heads, kv_heads=cfg.kv_heads, head_dim=cfg.head_dim, eps=cfg.eps)
+    table = block_ref.rope_table(cfg.seqlen, cfg.head_dim).cuda()
+    shape3 = (cfg.batch, cfg.seqlen, cfg.hidden)
+    out_ref, dx_ref, g_ref = block_ref.block_forward_backward(
+        x.view(shape3), {k: v.cuda() for k, v in params.items()}, dy.view(shape3), c, table,
+        dtype=torch.float32)
+
+    def err(got, ref):
+        return ((got.float() - ref.float()).abs().max() / ref.float().abs().max()).item()
+
+    assert err(out, out_ref.reshape(cfg.tokens, -1)) <= 2e-2
+    assert err(dx, dx_ref.reshape(cfg.tokens, -1)) <= 2e-2
+    for n in sky1.PARAM_NAMES:
+        assert err(blk.grads[n], g_ref[n]) <= 2e-2, n
 
 
 def test_block_rejects_bad_arguments(cdl, gpu_ok):
