@@ -18,6 +18,7 @@
 // forward (A row-major, B row-major), dgrad (B transposed view) and wgrad (A transposed view)
 // without copies.  M/N/K tails rely on TMA zero fill for loads and on predicated stores.
 #include "host.h"
+#include "ops.h"
 #include "ptx.cuh"
 
 #include <stdlib.h>
@@ -750,11 +751,12 @@ int32_t matmul_execute_epi(const cdl_tensor* a, const cdl_tensor* b, const cdl_t
     return fail(CDL_ERR_INVALID,
                 "matmul operands must all have rank 2 or all rank 3 (got rank %d, %d, %d)",
                 a->rank, b->rank, d->rank);
-  if (a->dtype != CDL_BF16 || b->dtype != CDL_BF16)
-    return fail(a->dtype == CDL_F32 && b->dtype == CDL_F32 ? CDL_ERR_UNSUPPORTED : CDL_ERR_INVALID,
-                "matmul inputs must be f32 or bf16 and of one type; this library implements bf16 "
-                "(got %s x %s)",
+  const bool f32_inputs = a->dtype == CDL_F32 && b->dtype == CDL_F32;
+  if (!f32_inputs && (a->dtype != CDL_BF16 || b->dtype != CDL_BF16))
+    return fail(CDL_ERR_INVALID, "matmul inputs must be f32 or bf16 and of one type (got %s x %s)",
                 dtype_name(a->dtype), dtype_name(b->dtype));
+  if (f32_inputs && epi_mode != 0)
+    return fail(CDL_ERR_UNSUPPORTED, "matmul (fused SwiGLU): inputs must be bf16");
   if (d->dtype != CDL_BF16 && d->dtype != CDL_F32)
     return fail(CDL_ERR_INVALID, "matmul output must be f32 or bf16");
   const int r = a->rank;
@@ -784,9 +786,17 @@ int32_t matmul_execute_epi(const cdl_tensor* a, const cdl_tensor* b, const cdl_t
   if (M > INT32_MAX || N > INT32_MAX || K > INT32_MAX || batch > 65535)
     return fail(CDL_ERR_UNSUPPORTED, "matmul dimension too large");
 
+  // f32 inputs, and bf16 operands TMA cannot describe (unaligned pointer or leading dimension):
+  // the general CUDA-core kernel (gemm_general.cu).  Operands without any contiguous dimension
+  // stay rejected, as in the reference.
+  if (f32_inputs) return matmul_general_execute(a, b, c, d, alpha, beta, stream);
   OperandLayout la, lb;
-  CDL_CHECK(analyze_operand("a", a, true, &la));
-  CDL_CHECK(analyze_operand("b", b, false, &lb));
+  for (int which = 0; which < 2; ++which) {
+    const int32_t rc = which == 0 ? analyze_operand("a", a, true, &la) : analyze_operand("b", b, false, &lb);
+    if (rc == CDL_ERR_UNSUPPORTED && epi_mode == 0)
+      return matmul_general_execute(a, b, c, d, alpha, beta, stream);
+    CDL_CHECK(rc);
+  }
 
   // Kernel choice: CTA pairs (256 x 256 tiles) whenever the problem has more than one 128-row
   // slab; CDL_B200_GEMM=1cta / 2cta overrides it (benchmarking aid).

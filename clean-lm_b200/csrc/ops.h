@@ -7,6 +7,9 @@ namespace cdl {
 
 int32_t matmul_execute(const cdl_tensor* a, const cdl_tensor* b, const cdl_tensor* c,
                        const cdl_tensor* d, float alpha, float beta, cudaStream_t stream);
+// gemm_general.cu: any strides, bf16 or f32 inputs, CUDA cores (operands already validated).
+int32_t matmul_general_execute(const cdl_tensor* a, const cdl_tensor* b, const cdl_tensor* c,
+                               const cdl_tensor* d, float alpha, float beta, cudaStream_t stream);
 // epi_mode 1: d = product, out2 = SiLU(product) * aux0.  epi_mode 2: d = SiLU(aux0) * product,
 // out2 = product * aux1 * dSiLU(aux0).
 int32_t matmul_execute_epi(const cdl_tensor* a, const cdl_tensor* b, const cdl_tensor* c,

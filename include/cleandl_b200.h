@@ -75,12 +75,14 @@ int32_t cdl_b200_profile_stop(cdl_profile_record* out, int32_t capacity, int32_t
 /* ---- Matmul: D = alpha * A . B + beta * C ----------------------------------------------
  * Replaces MatmulExecutor::execute (crates/cleandl/src/execgraph/ops/matmul.rs:1092-1183),
  * which forwards to cuBLASLt.  A is [M,K] or [batch,M,K]; B is [K,N] or [batch,K,N]; C
- * (nullable; needs beta != 0 to matter) and D are [M,N] / [batch,M,N].  A and B are bf16
- * views with one contiguous dimension (a transposed view is free, matmul.rs:128-157); D and C
- * are bf16 or f32; accumulation is f32.  forward = (A row-major, B row-major), dgrad =
- * (A row-major, B transposed view), wgrad = (A transposed view, B row-major, D = C f32, beta 1).
- * Unlike cuBLASLt, A's and B's base address and non-unit strides must be 16-byte aligned (TMA);
- * other layouts return CDL_ERR_UNSUPPORTED.  K == 0 is an error ("K is zero", matmul.rs tests
+ * (nullable; needs beta != 0 to matter) and D are [M,N] / [batch,M,N].  A and B are views with
+ * one contiguous dimension (a transposed view is free, matmul.rs:128-157), both bf16 or both
+ * f32; D and C are bf16 or f32; accumulation is f32.  forward = (A row-major, B row-major),
+ * dgrad = (A row-major, B transposed view), wgrad = (A transposed view, B row-major, D = C f32,
+ * beta 1).  bf16 operands whose base address and non-unit strides are 16-byte aligned take the
+ * tensor-core kernels; other layouts (tests/matmul.rs:604-630) and f32 inputs
+ * (tests/matmul.rs:243-265; full f32 products, where cuBLASLt uses TF32) take a general
+ * CUDA-core kernel that is correct but slow.  K == 0 is an error ("K is zero", matmul.rs tests
  * :825-843).  D may alias C. */
 int32_t cdl_b200_matmul(const cdl_tensor* a, const cdl_tensor* b, const cdl_tensor* c,
                         const cdl_tensor* d, float alpha, float beta, void* scratch,

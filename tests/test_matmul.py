@@ -2,7 +2,8 @@
 
 Cases follow crates/cleandl/tests/matmul.rs: shapes and output types (:212-240), transposed views
 (:268-310), sliced views (:313-339), batched (:666-687), batched + transposed + C with alpha/beta
-(:632-663), accumulate into C (:690-725), K = 0 (:825-843), rejection messages (:355-468), with the
+(:632-663), accumulate into C (:690-725), unaligned operands (:604-630), f32 inputs (:243-265),
+K = 0 (:825-843), rejection messages (:355-468), with the
 tolerance of :199-202.  The acceptance bound of this build (max relative error 2e-2 against an
 f32-accumulated reference) is checked as well.
 """
@@ -106,6 +107,44 @@ def test_unaligned_output_rows(cdl, gpu_ok):
     run_case(cdl, a, b, torch.float32)
 
 
+@pytest.mark.parametrize("m,k,n", [(37, 64, 65), (40, 72, 1), (16, 24, 8), (200, 333, 129)])
+def test_unaligned_operands(cdl, gpu_ok, m, k, n):
+    """The reference's unaligned_operands test (crates/cleandl/tests/matmul.rs:604-630): A starts 3
+    elements into rows of k + 3 elements (pointer and leading dimension off the 16-byte grid), B
+    is the transposed view of an [n, k] matrix.  TMA cannot describe these; the general kernel
+    computes them."""
+    gen = torch.Generator().manual_seed(110)
+    a = rand_bf16(gen, m, k + 3)[:, 3:]
+    b = rand_bf16(gen, n, k).T
+    run_case(cdl, a, b, torch.bfloat16)
+    run_case(cdl, a, b, torch.float32)
+    c = torch.randn(m, n, generator=gen)
+    run_case(cdl, a, b, torch.float32, c=c, alpha=0.5, beta=2.0)
+
+
+def test_unaligned_batched(cdl, gpu_ok):
+    gen = torch.Generator().manual_seed(111)
+    a = rand_bf16(gen, 3, 50, 45)[:, :, 1:41]     # [3, 50, 40], row stride 45
+    b = rand_bf16(gen, 3, 33, 40).transpose(1, 2)  # [3, 40, 33], K contiguous
+    run_case(cdl, a, b, torch.bfloat16)
+
+
+@pytest.mark.parametrize("shape", [(96, 200, 136), (130, 64, 70)])
+def test_f32_inputs(cdl, gpu_ok, shape):
+    """The reference's f32_tf32_matmul test (tests/matmul.rs:243-265): f32 x f32 -> f32 within the
+    TF32 tolerance 2e-3 * sum |a b| + 1e-5 (the products here are full f32)."""
+    m, k, n = shape
+    gen = torch.Generator().manual_seed(10)
+    a = torch.rand(m, k, generator=gen) * 2 - 1
+    b = torch.rand(k, n, generator=gen) * 2 - 1
+    d = cdl.ops.matmul(a.cuda(), b.cuda(), cdl.ops.MatmulOpts(out=torch.float32))
+    expected, bound = oracle.matmul(to_f32(a), to_f32(b), None, 1.0, 0.0)
+    assert_all_close("f32 inputs", to_f32(d), expected, 2e-3 * bound + 1e-5)
+    dt = cdl.ops.matmul(a.T.contiguous().cuda().T, b.cuda(), cdl.ops.MatmulOpts(out=torch.bfloat16))
+    assert_all_close("f32 inputs, transposed a, bf16 out", to_f32(dt), expected,
+                     oracle.matmul_tolerance(expected, bound, True))
+
+
 def test_deterministic(cdl, gpu_ok):
     gen = torch.Generator().manual_seed(8)
     a, b = rand_bf16(gen, 1024, 2048).cuda(), rand_bf16(gen, 2048, 1536).cuda()
@@ -154,10 +193,15 @@ def test_empty_and_errors(cdl, gpu_ok):
     with pytest.raises(cdl._lib.CdlError, match="contiguous"):
         cdl.ops.matmul(torch.zeros(16, 32, dtype=torch.bfloat16, device=dev)[::2, ::2],
                        torch.zeros(16, 8, dtype=torch.bfloat16, device=dev))
-    # A leading dimension TMA cannot describe (65 elements): rejected, not mis-computed.
-    with pytest.raises(cdl._lib.CdlError, match="16-byte"):
-        cdl.ops.matmul(torch.zeros(37, 65, dtype=torch.bfloat16, device=dev)[:, :64],
-                       torch.zeros(64, 8, dtype=torch.bfloat16, device=dev))
+    # The fused epilogues exist on the tensor-memory path only: unaligned operands are rejected there.
+    L = cdl._lib
+    a65 = torch.zeros(37, 65, dtype=torch.bfloat16, device=dev)[:, :64]
+    b8 = torch.zeros(64, 8, dtype=torch.bfloat16, device=dev)
+    up = torch.zeros(37, 8, dtype=torch.bfloat16, device=dev)
+    gate, act = torch.empty_like(up), torch.empty_like(up)
+    args = [L.tensor_arg(t) for t in (a65, b8, up, gate, act)]
+    with pytest.raises(L.CdlError, match="16-byte"):
+        L.check(L.lib.cdl_b200_matmul_swiglu_gate(*(L.ref(t) for t in args), None))
 
 
 @pytest.mark.parametrize("m,n,k", [(300, 264, 136), (128, 72, 64), (1024, 512, 256)])
