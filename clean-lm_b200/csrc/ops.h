@@ -16,6 +16,10 @@ int32_t matmul_execute_epi(const cdl_tensor* a, const cdl_tensor* b, const cdl_t
                            const cdl_tensor* d, float alpha, float beta, int epi_mode,
                            const cdl_tensor* aux0, const cdl_tensor* aux1, const cdl_tensor* out2,
                            cudaStream_t stream);
+// norm_general.cu: any float types, strides and column counts (layer = 0 RmsNorm, 1 LayerNorm).
+int32_t norm_general_execute(int layer, const cdl_tensor* x, const cdl_tensor* scale,
+                             const cdl_tensor* bias, float eps, const cdl_tensor* y,
+                             const cdl_tensor* mean, const cdl_tensor* r_inv, cudaStream_t stream);
 int32_t rmsnorm_fwd_execute(const cdl_tensor* x, const cdl_tensor* scale, const cdl_tensor* bias,
                             float eps, const cdl_tensor* y, const cdl_tensor* r_inv,
                             cudaStream_t stream);

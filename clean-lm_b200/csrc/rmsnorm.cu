@@ -14,6 +14,7 @@
 // single-pass over HBM.  Row reductions are five shuffle steps; no shared memory or block
 // barrier is on the critical path.
 #include "host.h"
+#include "ops.h"
 #include "ptx.cuh"
 
 #include <stdlib.h>
@@ -595,6 +596,25 @@ static int32_t check_vec(const char* op, const char* name, const cdl_tensor* t, 
   return CDL_OK;
 }
 
+// Whether the vectorised kernels take these operands; everything else goes to the general kernel
+// (norm_general.cu), which also reports the invalid ones.
+static bool fast_rows(const cdl_tensor* t, long long rows, long long cols) {
+  return t->rank == 2 && t->shape[0] == rows && t->shape[1] == cols && t->dtype == CDL_BF16 &&
+         (cols <= 1 || t->stride[1] == 1) && (reinterpret_cast<uintptr_t>(t->ptr) & 15) == 0 &&
+         (rows <= 1 || t->stride[0] % 8 == 0);
+}
+static bool fast_vec(const cdl_tensor* t, long long n) {
+  return t->rank == 1 && t->shape[0] == n && t->dtype == CDL_BF16 && t->stride[0] == 1 &&
+         (reinterpret_cast<uintptr_t>(t->ptr) & 15) == 0;
+}
+static bool fast_norm_operands(const cdl_tensor* x, const cdl_tensor* scale, const cdl_tensor* bias,
+                               const cdl_tensor* y) {
+  if (x->rank != 2) return false;
+  const long long rows = x->shape[0], cols = x->shape[1];
+  return cols % 8 == 0 && cols <= 8192 && fast_rows(x, rows, cols) && fast_rows(y, rows, cols) &&
+         (!scale || fast_vec(scale, cols)) && (!bias || fast_vec(bias, cols));
+}
+
 template <int NCH>
 static void launch_fwd(const cdl_tensor* x, const cdl_tensor* scale, const cdl_tensor* bias,
                        float eps, const cdl_tensor* y, const cdl_tensor* r_inv, int rows, int cols,
@@ -682,15 +702,9 @@ int32_t rmsnorm_fwd_execute(const cdl_tensor* x, const cdl_tensor* scale, const 
   using namespace norm;
   const char* op = "norm_fwd";
   if (!x || !y) return fail(CDL_ERR_INVALID, "%s: x and y are required", op);
-  if (x->rank != 2) return fail(CDL_ERR_INVALID, "%s: x must be a 2D tensor", op);
+  if (!fast_norm_operands(x, scale, bias, y))
+    return norm_general_execute(0, x, scale, bias, eps, y, nullptr, r_inv, stream);
   const long long rows = x->shape[0], cols = x->shape[1];
-  if (cols % 8 != 0 || cols > 8192)
-    return fail(CDL_ERR_UNSUPPORTED,
-                "%s: cols must be a multiple of 8 and at most 8192 (got %lld)", op, cols);
-  CDL_CHECK(check_rows(op, "x", x, rows, cols));
-  CDL_CHECK(check_rows(op, "y", y, rows, cols));
-  if (scale) CDL_CHECK(check_vec(op, "scale", scale, cols, CDL_BF16, true));
-  if (bias) CDL_CHECK(check_vec(op, "bias", bias, cols, CDL_BF16, true));
   if (r_inv) CDL_CHECK(check_vec(op, "r_inv", r_inv, rows, CDL_F32, false));
   if (rows == 0 || cols == 0) return CDL_OK;
   if (rows > INT32_MAX) return fail(CDL_ERR_UNSUPPORTED, "%s: too many rows", op);
@@ -729,15 +743,9 @@ int32_t layernorm_fwd_execute(const cdl_tensor* x, const cdl_tensor* scale, cons
   using namespace norm;
   const char* op = "norm_fwd (layer norm)";
   if (!x || !y) return fail(CDL_ERR_INVALID, "%s: x and y are required", op);
-  if (x->rank != 2) return fail(CDL_ERR_INVALID, "%s: x must be a 2D tensor", op);
+  if (!fast_norm_operands(x, scale, bias, y))
+    return norm_general_execute(1, x, scale, bias, eps, y, mean, r_inv, stream);
   const long long rows = x->shape[0], cols = x->shape[1];
-  if (cols % 8 != 0 || cols > 8192)
-    return fail(CDL_ERR_UNSUPPORTED,
-                "%s: cols must be a multiple of 8 and at most 8192 (got %lld)", op, cols);
-  CDL_CHECK(check_rows(op, "x", x, rows, cols));
-  CDL_CHECK(check_rows(op, "y", y, rows, cols));
-  if (scale) CDL_CHECK(check_vec(op, "scale", scale, cols, CDL_BF16, true));
-  if (bias) CDL_CHECK(check_vec(op, "bias", bias, cols, CDL_BF16, true));
   if (mean) CDL_CHECK(check_vec(op, "mean", mean, rows, CDL_F32, false));
   if (r_inv) CDL_CHECK(check_vec(op, "r_inv", r_inv, rows, CDL_F32, false));
   if (rows == 0 || cols == 0) return CDL_OK;

@@ -66,14 +66,16 @@ def matmul(a: torch.Tensor, b: torch.Tensor, opts: MatmulOpts | None = None,
 # --------------------------------------------------------------------------- norm
 @dataclass
 class NormFwdOpts:
-    """`NormFwdOpts` of the reference (ops/norm/mod.rs:87-111); bf16 output (the block-scaled outputs
-    are in `mx.norm_fwd_mx`).  `norm_type`: "rms" (`NormType::RmsNorm`) or "layer" (`LayerNorm`)."""
+    """`NormFwdOpts` of the reference (ops/norm/mod.rs:87-111); `out` is the element type of
+    `NormOutput::Plain` (bf16 or f32; the block-scaled outputs are in `mx.norm_fwd_mx`).
+    `norm_type`: "rms" (`NormType::RmsNorm`) or "layer" (`LayerNorm`)."""
 
     scale: Optional[torch.Tensor] = None
     bias: Optional[torch.Tensor] = None
     eps: float = 1e-6
     save_stats: bool = False
     norm_type: str = "rms"
+    out: torch.dtype = torch.bfloat16
 
 
 @dataclass
@@ -88,7 +90,7 @@ def norm_fwd(x: torch.Tensor, opts: NormFwdOpts | None = None) -> NormFwdOutputs
     _require_cuda(x, opts.scale, opts.bias)
     if x.dim() != 2:
         raise _lib.CdlError(-1, "norm_fwd: x must be a 2D tensor")
-    y = torch.empty(x.shape, dtype=torch.bfloat16, device=x.device)
+    y = torch.empty(x.shape, dtype=opts.out, device=x.device)
     r_inv = torch.empty(x.shape[0], dtype=torch.float32, device=x.device) if opts.save_stats else None
     tx, ts, tb, ty, tr = (tensor_arg(t) for t in (x, opts.scale, opts.bias, y, r_inv))
     if opts.norm_type == "layer":

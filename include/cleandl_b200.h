@@ -108,8 +108,12 @@ int32_t cdl_b200_matmul_scratch_bytes(const cdl_tensor* a, const cdl_tensor* b,
  * Replaces SpecializedExecutor::execute (crates/cleandl/src/execgraph/ops/norm/specialized.rs:
  * 116-200) and the kernel it launches (crates/cleandl-specialized-kernels/src/kernels/norm/
  * forward.rs:509-785):  r_i = rsqrt(mean_j x_ij^2 + eps);  y_ij = bf16(x_ij * r_i * scale_j + bias_j).
- * x, y: bf16 [rows, cols], packed rows; scale, bias: bf16 [cols], nullable; r_inv: f32 [rows],
- * nullable (the op's save_stats).  cols % 8 == 0. */
+ * x, y: [rows, cols]; scale, bias: [cols], nullable; r_inv: f32 [rows], nullable (the op's
+ * save_stats).  bf16 operands with packed, 16-byte aligned rows, cols % 8 == 0 and cols <= 8192
+ * (the domain of the reference's specialized kernel, specialized.rs:24-73) take the vectorised
+ * kernels; everything else the reference's fallback accepts (f32 or bf16 x, y, scale and bias in
+ * any combination, any column count and strides; crates/cleandl/tests/norm.rs:414-470) takes a
+ * general kernel: y = (f32 or bf16)(x * r_i * scale_j + bias_j) computed in f32. */
 int32_t cdl_b200_rmsnorm_fwd(const cdl_tensor* x, const cdl_tensor* scale, const cdl_tensor* bias,
                              float eps, const cdl_tensor* y, const cdl_tensor* r_inv,
                              cdl_stream stream);

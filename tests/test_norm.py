@@ -76,13 +76,18 @@ def test_fwd_empty_and_errors(cdl, gpu_ok):
     assert out.y.shape == (0, 128)
     with pytest.raises(cdl._lib.CdlError, match="2D"):
         cdl.ops.norm_fwd(torch.zeros(2, 4, 128, dtype=torch.bfloat16, device=dev))
-    with pytest.raises(cdl._lib.CdlError, match="multiple of 8"):
-        cdl.ops.norm_fwd(torch.zeros(4, 16, dtype=torch.bfloat16, device=dev)[:, :12].contiguous())
     with pytest.raises(cdl._lib.CdlError, match=r"shape \[128\]"):
         cdl.ops.norm_fwd(torch.zeros(4, 128, dtype=torch.bfloat16, device=dev),
                          cdl.ops.NormFwdOpts(scale=torch.zeros(64, dtype=torch.bfloat16, device=dev)))
-    with pytest.raises(cdl._lib.CdlError, match="bf16"):
-        cdl.ops.norm_fwd(torch.zeros(4, 128, dtype=torch.float32, device=dev))
+    with pytest.raises(cdl._lib.CdlError, match="f32 or bf16"):
+        cdl.ops.norm_fwd(torch.zeros(4, 128, dtype=torch.float16, device=dev))
+    with pytest.raises(cdl._lib.CdlError, match=r"r_inv must be f32 \[4\]"):
+        L = cdl._lib
+        x = torch.zeros(4, 100, dtype=torch.float32, device=dev)
+        y, bad = torch.empty_like(x), torch.zeros(5, dtype=torch.float32, device=dev)
+        args = [L.tensor_arg(t) for t in (x, None, None, y, bad)]
+        L.check(L.lib.cdl_b200_rmsnorm_fwd(L.ref(args[0]), None, None, 1e-6, L.ref(args[3]),
+                                           L.ref(args[4]), None))
 
 
 @pytest.mark.parametrize("rows,cols", [(1, 128), (37, 2048), (300, 1536), (1000, 2048), (64, 136),
@@ -154,3 +159,50 @@ def test_layernorm_fwd_cases(cdl, gpu_ok, rows, cols, affine):
     assert_all_close("y", to_f32(out.y), y_ref, oracle.abs_rel_tolerance(y_ref, 1e-5, 2.0 ** -7))
     assert_all_close("mean", to_f32(out.mean), m_ref, oracle.abs_rel_tolerance(m_ref, 1e-5, 1e-4))
     assert_all_close("r_inv", to_f32(out.r_inv), r_ref, oracle.abs_rel_tolerance(r_ref, 1e-6, 1e-4))
+
+
+F32, BF16 = torch.float32, torch.bfloat16
+
+
+def _general_case(cdl, rows, cols, norm_type, x_ty, out_ty, scale_ty, bias_ty, seed=2, eps=1e-6,
+                  col_stride=1):
+    gen = torch.Generator().manual_seed(seed)
+    x = (torch.randn(rows, cols * col_stride, generator=gen) * 2.0 + 0.5).to(x_ty)[:, ::col_stride]
+    scale = None if scale_ty is None else (torch.rand(cols, generator=gen) + 0.5).to(scale_ty)
+    bias = None if bias_ty is None else torch.randn(cols, generator=gen).to(bias_ty)
+    xd = torch.empty(0, dtype=x_ty).set_(x.untyped_storage()).cuda().as_strided(
+        x.shape, x.stride(), x.storage_offset())
+    out = cdl.ops.norm_fwd(xd, cdl.ops.NormFwdOpts(
+        scale=None if scale is None else scale.cuda(), bias=None if bias is None else bias.cuda(),
+        eps=eps, save_stats=True, norm_type=norm_type, out=out_ty))
+    assert out.y.dtype == out_ty
+    xs, ss, bs = to_f32(x), None if scale is None else to_f32(scale), None if bias is None else to_f32(bias)
+    if norm_type == "layer":
+        y_ref, m_ref, r_ref = layernorm_reference(xs, ss, bs, eps)
+        assert_all_close("mean", to_f32(out.mean), m_ref, oracle.abs_rel_tolerance(m_ref, 1e-5, 1e-4))
+    else:
+        y_ref, r_ref = oracle.rmsnorm_fwd(xs, ss, bs, eps)
+    rel = 2.0 ** -7 if out_ty == BF16 else 1e-4
+    assert_all_close("y", to_f32(out.y), y_ref, oracle.abs_rel_tolerance(y_ref, 1e-5, rel))
+    assert_all_close("r_inv", to_f32(out.r_inv), r_ref, oracle.abs_rel_tolerance(r_ref, 1e-6, 1e-4))
+
+
+@pytest.mark.parametrize("norm_type", ["rms", "layer"])
+@pytest.mark.parametrize("x_ty,out_ty", [(F32, F32), (F32, BF16), (BF16, F32), (BF16, BF16)])
+@pytest.mark.parametrize("scale_ty,bias_ty", [(None, None), (F32, BF16), (BF16, F32)])
+def test_general_path_type_matrix(cdl, gpu_ok, norm_type, x_ty, out_ty, scale_ty, bias_ty):
+    """The type matrix of the reference's fallback_configurations test
+    (crates/cleandl/tests/norm.rs:414-437) on its [77, 1000] shape: every combination of f32 / bf16
+    input, output, scale and bias, both norm types; f32 outputs within 1e-5 + 1e-4 |e| (:266-268)."""
+    _general_case(cdl, 77, 1000, norm_type, x_ty, out_ty, scale_ty, bias_ty)
+
+
+@pytest.mark.parametrize("norm_type", ["rms", "layer"])
+def test_general_path_shapes(cdl, gpu_ok, norm_type):
+    """Long rows (tests/norm.rs:438-446), a column count past the vectorised kernels' 8192 (:471-475),
+    one that is not a multiple of 8, eps 1e-3 on [50, 3000] (:454-462), strided columns."""
+    _general_case(cdl, 9, 20000, norm_type, F32, F32, F32, None)
+    _general_case(cdl, 31, 8200, norm_type, BF16, BF16, None, None)
+    _general_case(cdl, 50, 3000, norm_type, BF16, BF16, BF16, None, eps=1e-3)
+    _general_case(cdl, 13, 100, norm_type, BF16, BF16, BF16, BF16)
+    _general_case(cdl, 20, 96, norm_type, BF16, F32, None, None, col_stride=2)

@@ -75,7 +75,7 @@ def test_error_messages_stay_in_their_thread(cdl, gpu_ok):
         start.wait()
         for _ in range(200):
             try:
-                cdl.ops.norm_fwd(x[:, :100])  # 100 of 2048 columns: not a supported layout
+                cdl.ops.norm_fwd(x, cdl.ops.NormFwdOpts(scale=w[:64]))  # a scale of the wrong length
                 errors.append("the invalid call was accepted")
             except cdl._lib.CdlError as e:
                 seen.append(str(e))
