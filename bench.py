@@ -12,9 +12,14 @@ Printed line (rank 0): `value` = tokens/s with inputs resident in HBM, timed wit
 exactly K steps, max over ranks; `e2e` = the same through the public API with the step's token ids
 copied from pinned host memory and the step's result (the gradient of the first norm gain, 8 KiB)
 read back every step; `roofline` = the GEMM kernel (the dominant one) timed per launch by the
-library's event profiler inside the timed region; `cpu_baseline` = the CPU oracle of the same block
-on a bounded sample.  `--impl reference` times only that CPU path (the reference has no other host
-implementation of these operators and cannot be built here).
+library's event profiler in a separate pass over the same steps (the timed passes run without
+it); `cpu_baseline` = the CPU oracle of the same block on a bounded sample.  The same line carries,
+under `kernels` (and as flat `k_*` scalars in `config`), every kernel-level target at its stated
+shape -- GEMM 8192^3, RMSNorm forward / backward on [16384, 2048], causal attention forward /
+backward at B 8, H 16, S 2048 -- next to the library stand-ins for the reference's own route
+(torch.matmul = cuBLASLt, torch SDPA), and under `lm_step` a short run of the 24-layer training
+step (configuration 5).  `--impl reference` times only the CPU path (the reference has no other
+host implementation of these operators and cannot be built here).
 """
 from __future__ import annotations
 
@@ -71,10 +76,19 @@ def cpu_block_tokens_per_s(seqlen: int, repeats: int = 1):
     return seqlen / best, torch.get_num_threads()
 
 
+WORKLOAD = ("sky-1 block fwd+bwd (config 4): hidden 2048, 16x128 heads, RoPE, pre-RMSNorm, SwiGLU 5632, "
+            "batch 8 x seq 2048 per GPU, seed 3")
+L2_NOTE = "per-step working set (~1 GB of activations) exceeds the 126 MB L2"
+
+
 def run_reference(args) -> None:
     rank = int(os.environ.get("RANK", "0"))
     if rank != 0:
         return
+    import torch
+
+    # torchrun pins every rank to one OpenMP thread; the CPU arm uses all host cores it can get.
+    torch.set_num_threads(max(1, os.cpu_count() or 1))
     seqlen = 512
     for _ in range(args.warmup):
         cpu_block_tokens_per_s(seqlen)
@@ -90,8 +104,7 @@ def run_reference(args) -> None:
         "n_gpus": args.gpus, "steps": args.steps, "warmup": args.warmup,
         "ms_per_step": 1e3 * dt / args.steps, "higher_is_better": True, "scaling": "weak",
         "vs_baseline": None, "dtype": "f64", "data": "synthetic",
-        "config": {"workload": "sky-1 block fwd+bwd, hidden 2048, 16x128 heads, ffn 5632 (config 4)",
-                   "sample": sample},
+        "config": {"workload": WORKLOAD, "parallelism": f"dp{args.gpus}", "l2": L2_NOTE},
         "cpu_baseline": {"value": value, "unit": "tokens/s", "cores": threads, "kind": "port",
                          "sample": sample},
         "e2e": {"value": value, "unit": "tokens/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
@@ -298,17 +311,32 @@ def run_ours(args) -> None:
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
         return float(t.item())
 
+    def timed(step_fn, indexed: bool):
+        """W warm-up steps, then exactly K steps between a barrier + synchronize on both sides,
+        CUDA events on the launching stream; returns the max over ranks of the elapsed ms."""
+        for i in range(args.warmup):
+            step_fn(i) if indexed else step_fn()
+        barrier()
+        a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        a.record()
+        for i in range(args.steps):
+            step_fn(args.warmup + i) if indexed else step_fn()
+        if world > 1:
+            torch.cuda.current_stream().wait_event(reduced)
+        b.record()
+        barrier()
+        return max_over_ranks(a.elapsed_time(b))
+
     with torch.cuda.stream(main):
         reduced.record()
         tokens_dev.copy_(tokens_host[0])
-        # ---- device-resident number
+        # ---- device-resident number (no per-launch profiling inside the timed region)
         sampler = ClockSampler(local) if rank == 0 else None
         for _ in range(args.warmup):
             step_resident()
         barrier()
         if sampler:
             sampler.mark()
-        L.profile_start(64 * args.steps + 64)
         e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
         e0.record()
         for _ in range(args.steps):
@@ -317,24 +345,39 @@ def run_ours(args) -> None:
             torch.cuda.current_stream().wait_event(reduced)
         e1.record()
         barrier()
-        records = L.profile_stop(64 * args.steps + 64)
         clocks = sampler.stop() if sampler else None
         ms_resident = max_over_ranks(e0.elapsed_time(e1))
 
         # ---- end to end: host token ids in, result read back, every step
-        for i in range(args.warmup):
-            step_e2e(i)
+        ms_e2e = timed(step_e2e, indexed=True)
+
+        # ---- the same steps once more with the library's per-launch event pairs: per-kernel times
         barrier()
-        t0, t1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-        t0.record()
-        for i in range(args.steps):
-            step_e2e(args.warmup + i)
-        t1.record()
+        L.profile_start(64 * args.steps + 64)
+        p0, p1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        p0.record()
+        for _ in range(args.steps):
+            step_resident()
+        if world > 1:
+            torch.cuda.current_stream().wait_event(reduced)
+        p1.record()
         barrier()
-        ms_e2e = max_over_ranks(t0.elapsed_time(t1))
+        records = L.profile_stop(64 * args.steps + 64)
+        ms_profiled = p0.elapsed_time(p1)
     status = L.device_status()
     if status != 0:
         raise RuntimeError(f"a kernel reported status {status} (bounded wait ran out)")
+
+    # ---- every kernel-level target at its stated shape + the library stand-ins (rank 0)
+    kernels = None
+    if rank == 0 and not args.no_kernels:
+        kernels = kernel_targets(torch, cdl, dev)
+    barrier()
+    # ---- configuration 5: a short run of the 24-layer training step on all ranks
+    lm = None
+    if not args.no_lm:
+        lm = lm_short_run(torch, dist, cdl, dev, world, rank, barrier, max_over_ranks)
+    barrier()
 
     if rank == 0:
         peaks = measured_peaks()
@@ -350,60 +393,282 @@ def run_ours(args) -> None:
         # kernels launched per step: 15 GEMM (SwiGLU fused into two of them), 4 norm fwd,
         # 2 x 2 norm bwd, 1 attn fwd, 3 attn bwd, 2 rope, 1 embedding
         launches_per_step = 15 + 4 + 4 + 1 + 3 + 2 + 1
-        # DRAM traffic of the average GEMM launch: the minimum bytes of each of the block's 15
-        # GEMMs (operands read once, outputs written once, accumulated outputs read and written,
-        # fused-epilogue operands included) scaled by the ratio measured with Nsight Compute on
-        # 8192 x 8192 x 2048 (dram read + write = 191.5 MB against a minimum of 201.3 MB; see
-        # profiles/gemm_bf16_8192x8192x2048.md).
+        # DRAM traffic of the average GEMM launch.  The block's shapes are too large to capture
+        # under Nsight Compute, so: the minimum bytes of each of the 15 GEMMs (operands read once,
+        # outputs written once, accumulated outputs read and written, fused-epilogue operands
+        # included) times the measured-to-minimum ratio of the committed capture of the same
+        # KIND of launch -- forward / dgrad shapes: profiles/gemm_bf16_pair_8192x8192x2048.md;
+        # weight-gradient shapes: profiles/gemm_bf16_pair_wgrad_2048x5632x16384.md.
         Hd, QKV, F = cfg.hidden, cfg.qkv_dim, cfg.ffn
-        gemm_bytes = [
+        plain_bytes = [
             2 * (T * Hd + Hd * QKV + T * QKV),              # qkv
             2 * (T * Hd + Hd * Hd + 2 * T * Hd),            # o + residual
             2 * (T * Hd + Hd * F + T * F),                  # up
             2 * (T * Hd + Hd * F + 3 * T * F),              # gate (+ up in, act out)
             2 * (T * F + F * Hd + 2 * T * Hd),              # down + residual
-            2 * (T * F + T * Hd) + 8 * F * Hd,              # dW down (f32 read + write)
             2 * (T * Hd + F * Hd + 4 * T * F),              # d_act fused: gate, up in; d_up, d_gate out
-            2 * (T * Hd + T * F) + 8 * Hd * F,              # dW up
             2 * (T * F + Hd * F + T * Hd),                  # dh2
-            2 * (T * Hd + T * F) + 8 * Hd * F,              # dW gate
             2 * (T * F + Hd * F + 2 * T * Hd),              # dh2 += (C read)
-            2 * (T * Hd + T * Hd) + 8 * Hd * Hd,            # dW o
             2 * (T * Hd + Hd * Hd + T * Hd),                # d_attn
-            2 * (T * Hd + T * QKV) + 8 * Hd * QKV,          # dW qkv
             2 * (T * QKV + Hd * QKV + T * Hd),              # dh1
         ]
-        gemm_traffic = sum(gemm_bytes) / len(gemm_bytes) * (191.5 / 201.3)
+        wgrad_bytes = [
+            2 * (T * F + T * Hd) + 8 * F * Hd,              # dW down (f32 read + write)
+            2 * (T * Hd + T * F) + 8 * Hd * F,              # dW up
+            2 * (T * Hd + T * F) + 8 * Hd * F,              # dW gate
+            2 * (T * Hd + T * Hd) + 8 * Hd * Hd,            # dW o
+            2 * (T * Hd + T * QKV) + 8 * Hd * QKV,          # dW qkv
+        ]
+        gemm_traffic = (sum(plain_bytes) * TRAFFIC_RATIO_PLAIN + sum(wgrad_bytes) * TRAFFIC_RATIO_WGRAD) / 15
+        # Which cuBLAS figure bounds the kernel: the burst one unless the clocks sampled during the
+        # timed region had settled well below the maximum (a seconds-long, power-capped region).
+        sm, sm_max = (clocks or {}).get("sm_mhz"), (clocks or {}).get("sm_max_mhz")
+        settled = bool(sm and sm_max and sm < 0.9 * sm_max)
+        peak = peaks["bf16"] if settled else peaks["bf16_burst"]
         # CPU baseline on rank 0 at N = 1 only (torchrun pins ranks to one OpenMP thread).
         cpu_value, cpu_threads = cpu_block_tokens_per_s(512, repeats=2) if world == 1 else (None, None)
+        config = {"workload": WORKLOAD, "parallelism": f"dp{world}", "l2": L2_NOTE,
+                  "tflops_per_gpu": cfg.flops_fwd_bwd() * args.steps / (ms_resident * 1e-3) / 1e12,
+                  "ms_per_step_with_event_profiler": ms_profiled / args.steps,
+                  "kernel_ms_per_step": kernel_ms}
+        for kname, ms in kernel_ms.items():
+            config[f"ms_{kname}"] = ms
+        if kernels:
+            for name, rec in kernels.items():
+                for key in ("ms", "achieved", "frac"):
+                    if key in rec:
+                        config[f"k_{name}_{key}"] = rec[key]
+        if lm:
+            for key, val in lm.items():
+                config[f"lm_{key}"] = val
         line = {
             "metric": METRIC, "value": args.steps * T * world / (ms_resident * 1e-3),
             "unit": "tokens/s", "n_gpus": world, "steps": args.steps, "warmup": args.warmup,
             "ms_per_step": ms_resident / args.steps, "higher_is_better": True, "scaling": "weak",
             "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
-            "config": {"workload": "sky-1 block fwd+bwd (config 4): hidden 2048, 16x128 heads, RoPE, "
-                                   "pre-RMSNorm, SwiGLU 5632, batch 8 x seq 2048 per GPU, seed 3",
-                       "parallelism": f"dp{world}",
-                       "l2": "per-step working set (~1 GB of activations) exceeds the 126 MB L2",
-                       "tflops_per_gpu": cfg.flops_fwd_bwd() * args.steps / (ms_resident * 1e-3) / 1e12,
-                       "kernel_ms_per_step": kernel_ms},
+            "config": config,
             "e2e": {"value": args.steps * T * world / (ms_e2e * 1e-3), "unit": "tokens/s",
                     "h2d_bytes_per_step": T * 4, "d2h_bytes_per_step": cfg.hidden * 4,
                     "ms_per_step": ms_e2e / args.steps},
-            "gpu_launches": launches_per_step * args.steps * 2,
+            # resident, end-to-end and profiled passes, warm-up included
+            "gpu_launches": launches_per_step * (args.steps + args.warmup) * 2 + launches_per_step * args.steps,
             "clocks": clocks,
-            "roofline": {"bound": "tensor", "achieved": achieved, "peak": peaks["bf16"],
-                         "unit": "TFLOP/s", "frac": (achieved / peaks["bf16"]) if achieved else None,
+            "roofline": {"bound": "tensor", "achieved": achieved, "peak": peak,
+                         "unit": "TFLOP/s", "frac": (achieved / peak) if achieved else None,
+                         "frac_of_burst": (achieved / peaks["bf16_burst"]) if achieved else None,
+                         "frac_of_sustained": (achieved / peaks["bf16"]) if achieved else None,
                          "traffic": gemm_traffic, "traffic_unit": "bytes per launch (mean of the 15 GEMMs)",
-                         "kernel": "gemm_bf16_pair_kernel",
-                         "launches": gemm[0], "peak_source": peaks["source"] + " (sustained cuBLAS bf16)"},
+                         "traffic_source": f"minimum bytes x {TRAFFIC_RATIO_PLAIN} (forward / dgrad shapes, "
+                                           f"profiles/gemm_bf16_pair_8192x8192x2048.md) and x {TRAFFIC_RATIO_WGRAD} "
+                                           "(weight-gradient shapes, profiles/gemm_bf16_pair_wgrad_2048x5632x16384.md)",
+                         "kernel": "gemm_bf16_pair_kernel", "launches": gemm[0],
+                         "timed": "per-launch CUDA events in a separate pass over the same steps",
+                         "peak_source": peaks["source"] + (" sustained" if settled else " burst") +
+                                        " cuBLAS bf16 (chosen by the SM clock sampled in the timed region)"},
             "cpu_baseline": None if cpu_value is None else {
                 "value": cpu_value, "unit": "tokens/s", "cores": cpu_threads, "kind": "port",
                 "sample": "batch 1 x seq 512 of the same block, float64 oracle, best of 2 passes"},
+            "kernels": kernels,
+            "lm_step": lm,
         }
         print(json.dumps(line))
     if world > 1:
         dist.destroy_process_group()
+
+
+# DRAM bytes measured with Nsight Compute over the minimum bytes, per kind of GEMM launch (see the
+# two profiles named where these are used).
+TRAFFIC_RATIO_PLAIN = 1.14
+TRAFFIC_RATIO_WGRAD = 2.19
+
+
+def graph_time_ms(torch, fns, steps: int, replays: int = 3) -> float:
+    """`steps` launches (round-robin over fns) captured into one CUDA graph and replayed back to
+    back; best of `replays` replays, per launch."""
+    for i in range(max(3, len(fns))):
+        fns[i % len(fns)]()
+    torch.cuda.synchronize()
+    graph = torch.cuda.CUDAGraph()
+    with torch.cuda.graph(graph):
+        for i in range(steps):
+            fns[i % len(fns)]()
+    graph.replay()
+    torch.cuda.synchronize()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    best = None
+    for _ in range(replays):
+        e0.record()
+        graph.replay()
+        e1.record()
+        torch.cuda.synchronize()
+        ms = e0.elapsed_time(e1) / steps
+        best = ms if best is None else min(best, ms)
+    return best
+
+
+def eager_time_ms(torch, fn, steps: int) -> float:
+    """Plain launches timed with one CUDA event pair around `steps` of them (library routines that
+    cannot be captured into a graph, e.g. an autograd backward)."""
+    for _ in range(3):
+        fn()
+    torch.cuda.synchronize()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for _ in range(steps):
+        fn()
+    e1.record()
+    torch.cuda.synchronize()
+    return e0.elapsed_time(e1) / steps
+
+
+def kernel_targets(torch, cdl, dev) -> dict:
+    """Times every kernel-level target at its stated shape (back-to-back launches from a CUDA
+    graph, inputs rotated where one launch's data would fit in L2) and the library routines the
+    reference itself would call for the same operator: torch.matmul (cuBLASLt, what
+    crates/cleandl/src/execgraph/ops/matmul.rs:1160-1182 runs) and torch's fused attention."""
+    import torch.nn.functional as Fnn
+
+    peaks = measured_peaks()
+    gen = torch.Generator(device=dev).manual_seed(0)
+    rnd = lambda *shape: torch.randn(*shape, device=dev, generator=gen).to(torch.bfloat16)
+    out = {}
+
+    def rec(name, ms, work, unit, peak, note=None):
+        ach = work / (ms * 1e-3) / (1e12 if unit == "TFLOP/s" else 1e9)
+        r = {"ms": round(ms, 5), "achieved": round(ach, 2), "unit": unit, "frac": round(ach / peak, 4),
+             "peak": peak}
+        if note:
+            r["note"] = note
+        out[name] = r
+
+    burst, hbm = peaks["bf16_burst"], peaks["hbm"]
+    # ---- GEMM 8192^3 and the block's five forward shapes: ours and cuBLASLt through torch.matmul
+    shapes = {"gemm_8192": (8192, 8192, 8192), "gemm_qkv": (16384, 6144, 2048), "gemm_o": (16384, 2048, 2048),
+              "gemm_up": (16384, 5632, 2048), "gemm_down": (16384, 2048, 5632)}
+    for name, (m, n, k) in shapes.items():
+        a, b = rnd(m, k), rnd(k, n)
+        d = torch.empty(m, n, device=dev, dtype=torch.bfloat16)
+        steps = 10 if name == "gemm_8192" else 20
+        rec(name, graph_time_ms(torch, [lambda: cdl.ops.matmul(a, b, out=d)], steps), 2.0 * m * n * k,
+            "TFLOP/s", burst)
+        rec(name + "_cublaslt", graph_time_ms(torch, [lambda: torch.matmul(a, b, out=d)], steps),
+            2.0 * m * n * k, "TFLOP/s", burst, "library stand-in: torch.matmul")
+        del a, b, d
+    # weight-gradient form of the widest weight: D (f32) += A^T B
+    m, n, k = 2048, 5632, 16384
+    a, b = rnd(k, m), rnd(k, n)
+    d = torch.zeros(m, n, device=dev, dtype=torch.float32)
+    wopts = cdl.ops.MatmulOpts(out=torch.float32, c=d, beta=1.0)
+    rec("gemm_wgrad_up", graph_time_ms(torch, [lambda: cdl.ops.matmul(a.T, b, wopts, out=d)], 20),
+        2.0 * m * n * k, "TFLOP/s", burst)
+    dbf = torch.empty(m, n, device=dev, dtype=torch.bfloat16)
+    rec("gemm_wgrad_up_cublaslt", graph_time_ms(torch, [lambda: torch.matmul(a.T, b, out=dbf)], 20),
+        2.0 * m * n * k, "TFLOP/s", burst, "library stand-in: torch.matmul (bf16 out, no f32 accumulate)")
+    del a, b, d, dbf
+    # ---- RMSNorm forward / backward on x[16384, 2048]
+    rows, cols = 16384, 2048
+    nbuf = 3  # 3 x 67 MB per tensor: successive launches do not find their input in L2
+    xs = [rnd(rows, cols) for _ in range(nbuf)]
+    dys = [rnd(rows, cols) for _ in range(nbuf)]
+    ress = [rnd(rows, cols) for _ in range(nbuf)]
+    w = (1 + 0.02 * torch.randn(cols, device=dev, generator=gen)).to(torch.bfloat16)
+    o = cdl.ops.NormFwdOpts(scale=w, save_stats=True)
+    ys = [torch.empty_like(x) for x in xs]
+    r_inv = cdl.ops.norm_fwd(xs[0], o).r_inv
+    L = cdl._lib
+
+    def norm_fwd_into(x, y):
+        tx, ts, ty, tr = (L.tensor_arg(t) for t in (x, w, y, r_inv))
+        L.check(L.lib.cdl_b200_rmsnorm_fwd(L.ref(tx), L.ref(ts), None, 1e-6, L.ref(ty), L.ref(tr),
+                                           torch.cuda.current_stream().cuda_stream))
+
+    rec("rmsnorm_fwd", graph_time_ms(torch, [(lambda x=x, y=y: norm_fwd_into(x, y)) for x, y in zip(xs, ys)], 30),
+        4.0 * rows * cols + 2 * cols + 4 * rows, "GB/s", hbm)
+    ds = torch.zeros(cols, device=dev)
+    scr = torch.empty(cdl.ops.norm_bwd_scratch_bytes(rows, cols), dtype=torch.uint8, device=dev)
+    rec("rmsnorm_bwd", graph_time_ms(torch, [(lambda x=x, dy=dy, y=y: cdl.ops.norm_bwd(x, dy, w, r_inv, ds, scratch=scr, dx=y))
+                                             for x, dy, y in zip(xs, dys, ys)], 30),
+        6.0 * rows * cols + 6 * cols + 4 * rows, "GB/s", hbm)
+    rec("rmsnorm_bwd_residual",
+        graph_time_ms(torch, [(lambda x=x, dy=dy, rs=rs, y=y: cdl.ops.norm_bwd(x, dy, w, r_inv, ds, scratch=scr,
+                                                                             residual_dy=rs, dx=y))
+                              for x, dy, rs, y in zip(xs, dys, ress, ys)], 30),
+        8.0 * rows * cols + 6 * cols + 4 * rows, "GB/s", hbm, "the form the block uses")
+    del xs, dys, ress, ys
+    # ---- causal attention forward / backward, B 8, H 16, S 2048, D 128
+    bsz, s_, h = 8, 2048, 16
+    q, kx, v, do = (rnd(bsz, s_, h, 128) for _ in range(4))
+    fwd = cdl.ops.attention_fwd(q, kx, v)
+    f_fwd = 4.0 * bsz * h * s_ * s_ * 128 / 2
+    rec("attn_fwd", graph_time_ms(torch, [lambda: cdl.ops.attention_fwd(q, kx, v, out=fwd.out)], 20), f_fwd,
+        "TFLOP/s", burst)
+    scr = torch.empty(cdl.ops.attention_bwd_scratch_bytes(q, kx), dtype=torch.uint8, device=dev)
+    dq, dk, dv = (torch.empty_like(q) for _ in range(3))
+    rec("attn_bwd", graph_time_ms(torch, [lambda: cdl.ops.attention_bwd(q, kx, v, fwd.out, do, fwd.lse, scratch=scr,
+                                                                        dq=dq, dk=dk, dv=dv)], 20),
+        2.5 * f_fwd, "TFLOP/s", burst, "2.5 x forward FLOP convention; three launches")
+    try:
+        qt, kt, vt = (t.transpose(1, 2).detach().requires_grad_(True) for t in (q, kx, v))
+        dot = do.transpose(1, 2)
+        ms_f = eager_time_ms(torch, lambda: Fnn.scaled_dot_product_attention(qt, kt, vt, is_causal=True), 20)
+        rec("attn_fwd_torch_sdpa", ms_f, f_fwd, "TFLOP/s", burst, "library stand-in: torch SDPA")
+        o_ref = Fnn.scaled_dot_product_attention(qt, kt, vt, is_causal=True)
+        ms_b = eager_time_ms(
+            torch, lambda: torch.autograd.grad(o_ref, (qt, kt, vt), dot, retain_graph=True), 20)
+        rec("attn_bwd_torch_sdpa", ms_b, 2.5 * f_fwd, "TFLOP/s", burst, "library stand-in: torch SDPA backward")
+    except Exception as exc:  # a stand-in that cannot run is reported, not fatal
+        out["attn_torch_sdpa"] = {"unavailable": str(exc)[:200]}
+    torch.cuda.synchronize()
+    assert L.device_status() == 0
+    return out
+
+
+def lm_short_run(torch, dist, cdl, dev, world, rank, barrier, max_over_ranks, warmup=2, steps=3):
+    """Configuration 5 inside the default run: the 24-layer LM, global batch 64 x 2048 uniform
+    random tokens split over the ranks (strong scaling), microbatches of 8 x 2048, AdamW; 2 warm-up
+    and 3 timed optimizer steps with the token ids copied from pinned host memory and the loss read
+    back every step."""
+    blk = cdl.sky1.Sky1Config()
+    cfg = cdl.sky1.Sky1LMConfig(block=blk, layers=24, vocab=VOCAB)
+    model = cdl.sky1.Sky1LM(cfg, seed=4, device=dev, init_on_device=True)
+    seqs_per_rank = max(1, 64 // world)
+    mb = max(1, seqs_per_rank // blk.batch)
+    global_tokens = mb * blk.tokens * world
+    gen = torch.Generator().manual_seed(4 + 1000 * rank)
+    n = warmup + steps
+    data = torch.randint(0, VOCAB, (n, mb, blk.batch, blk.seqlen + 1), generator=gen, dtype=torch.int32)
+    tok = data[..., :-1].reshape(n, mb, -1).contiguous().pin_memory()
+    tgt = data[..., 1:].reshape(n, mb, -1).contiguous().pin_memory()
+    d_tok = torch.empty(mb, blk.tokens, dtype=torch.int32, device=dev)
+    d_tgt = torch.empty_like(d_tok)
+    losses = []
+
+    def step(i):
+        d_tok.copy_(tok[i], non_blocking=True)
+        d_tgt.copy_(tgt[i], non_blocking=True)
+        loss = model.train_step(d_tok, d_tgt, global_tokens=global_tokens)
+        if world > 1:
+            dist.all_reduce(loss)
+        losses.append(loss.item())
+
+    for i in range(warmup):
+        step(i)
+    barrier()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for i in range(steps):
+        step(warmup + i)
+    e1.record()
+    barrier()
+    ms = max_over_ranks(e0.elapsed_time(e1))
+    assert cdl._lib.device_status() == 0
+    flops = (cfg.layers * blk.flops_fwd_bwd() + 3 * 2.0 * blk.tokens * blk.hidden * VOCAB) * mb
+    del model
+    torch.cuda.empty_cache()
+    return {"tokens_per_s": steps * global_tokens / (ms * 1e-3), "ms_per_step": ms / steps,
+            "tflops_per_gpu": flops * steps / (ms * 1e-3) / 1e12, "loss_first": losses[0],
+            "loss_last": losses[-1], "steps": steps, "warmup": warmup, "microbatches_per_rank": mb,
+            "scaling": "strong", "params": cfg.param_count()}
 
 
 # ------------------------------------------------------------------ single-kernel mode
@@ -692,6 +957,10 @@ def main() -> None:
                     help="block = benchmark configuration 4 (the headline metric); lm = the 24-layer "
                          "training step; block_mx = the block with MXFP8 matrix products (one GPU)")
     ap.add_argument("--layers", type=int, default=24)
+    ap.add_argument("--no-kernels", action="store_true",
+                    help="block workload: skip the per-kernel targets and library stand-ins")
+    ap.add_argument("--no-lm", action="store_true",
+                    help="block workload: skip the short run of the 24-layer training step")
     args = ap.parse_args()
     if args.workload == "lm":
         run_lm(args)

@@ -45,7 +45,26 @@ class CdlAdamwParams(ctypes.Structure):
 class CdlSky1Config(ctypes.Structure):
     _fields_ = [(n, ctypes.c_int32) for n in
                 ("batch", "seqlen", "hidden", "heads", "kv_heads", "head_dim", "ffn")] + [
-                    ("eps", ctypes.c_float)]
+                    ("eps", ctypes.c_float), ("flags", ctypes.c_int32)]
+
+
+CDL_SKY1_DETERMINISTIC = 1
+
+
+class CdlMatmulOptions(ctypes.Structure):
+    """cdl_matmul_options: variant (GEMM_AUTO / GEMM_ONE_CTA / GEMM_CTA_PAIR), deterministic."""
+
+    _fields_ = [("variant", ctypes.c_int32), ("deterministic", ctypes.c_int32)]
+
+
+class CdlNormOptions(ctypes.Structure):
+    """cdl_norm_options: variant (NORM_AUTO / NORM_WARP_PER_ROW / NORM_PIPELINED)."""
+
+    _fields_ = [("variant", ctypes.c_int32)]
+
+
+GEMM_AUTO, GEMM_ONE_CTA, GEMM_CTA_PAIR = 0, 1, 2
+NORM_AUTO, NORM_WARP_PER_ROW, NORM_PIPELINED = 0, 1, 2
 
 
 class CdlSky1Ragged(ctypes.Structure):
@@ -87,6 +106,8 @@ lib = ctypes.CDLL(str(LIB_PATH))
 
 _T = ctypes.POINTER(CdlTensor)
 _MX = ctypes.POINTER(CdlMxTensor)
+_MO = ctypes.POINTER(CdlMatmulOptions)
+_NO = ctypes.POINTER(CdlNormOptions)
 _vp = ctypes.c_void_p
 _sz = ctypes.c_size_t
 
@@ -101,10 +122,16 @@ SIGNATURES = {
     "cdl_b200_embedding_fwd": ([_T, _T, _T, _vp], ctypes.c_int32),
     "cdl_b200_matmul": ([_T, _T, _T, _T, ctypes.c_float, ctypes.c_float, _vp, _sz, _vp],
                         ctypes.c_int32),
+    "cdl_b200_matmul_opt": ([_T, _T, _T, _T, ctypes.c_float, ctypes.c_float, _MO, _vp, _sz, _vp],
+                            ctypes.c_int32),
+    "cdl_b200_matmul_candidates": ([_T, _T, _T, _MO, ctypes.c_int32, ctypes.POINTER(ctypes.c_int32)],
+                                   ctypes.c_int32),
     "cdl_b200_matmul_swiglu_gate": ([_T, _T, _T, _T, _T, _vp], ctypes.c_int32),
     "cdl_b200_matmul_swiglu_dgrad": ([_T, _T, _T, _T, _T, _T, _vp], ctypes.c_int32),
     "cdl_b200_matmul_scratch_bytes": ([_T, _T, _T, ctypes.POINTER(_sz)], ctypes.c_int32),
     "cdl_b200_rmsnorm_fwd": ([_T, _T, _T, ctypes.c_float, _T, _T, _vp], ctypes.c_int32),
+    "cdl_b200_rmsnorm_fwd_opt": ([_T, _T, _T, ctypes.c_float, _T, _T, _NO, _vp], ctypes.c_int32),
+    "cdl_b200_rmsnorm_bwd_opt": ([_T, _T, _T, _T, _T, _T, _T, _NO, _vp, _sz, _vp], ctypes.c_int32),
     "cdl_b200_layernorm_fwd": ([_T, _T, _T, ctypes.c_float, _T, _T, _T, _vp], ctypes.c_int32),
     "cdl_b200_rmsnorm_bwd": ([_T, _T, _T, _T, _T, _T, _T, _vp, _sz, _vp], ctypes.c_int32),
     "cdl_b200_rmsnorm_bwd_static": ([_T, _T, _T, _T, _T, _T, _T, _vp], ctypes.c_int32),
@@ -116,6 +143,8 @@ SIGNATURES = {
     "cdl_b200_mx_dequantize": ([_MX, _T, _vp], ctypes.c_int32),
     "cdl_b200_rmsnorm_fwd_mx": ([_T, _T, _T, ctypes.c_float, _MX, _MX, _T, _vp], ctypes.c_int32),
     "cdl_b200_matmul_mx": ([_MX, _MX, _T, _T, ctypes.c_float, ctypes.c_float, _vp], ctypes.c_int32),
+    "cdl_b200_matmul_mx_opt": ([_MX, _MX, _T, _T, ctypes.c_float, ctypes.c_float, _MO, _vp],
+                               ctypes.c_int32),
     "cdl_b200_matmul_mx_out": ([_MX, _MX, _MX, ctypes.c_float, _vp], ctypes.c_int32),
     "cdl_b200_attn_fwd": ([ctypes.POINTER(CdlAttnDesc), _T, _T, _T, _T, _T, _vp], ctypes.c_int32),
     "cdl_b200_attn_bwd": ([ctypes.POINTER(CdlAttnDesc), _T, _T, _T, _T, _T, _T, _T, _T, _T, _vp,

@@ -63,6 +63,9 @@ constexpr size_t Q_SMEM_BYTES = (4 + QK_STAGES) * TILE_BYTES + 256;
 static_assert(KV_SMEM_BYTES <= 232448 && Q_SMEM_BYTES <= 232448,
               "exceeds the 227 KiB of shared memory a CTA can opt in to");
 
+// Status code (device status word) of a packed sequence longer than max_seqlen_q / max_seqlen_k.
+constexpr int STATUS_SEQ_EXCEEDS_BOUND = 921;
+
 struct Params {
   int B, H, Hkv, Sq, Sk, Sq_pad;
   int causal;
@@ -174,7 +177,7 @@ __global__ void __launch_bounds__(256)
   int len = Sq;
   if (cu_q != nullptr) {
     const int base = cu_q[b];
-    len = cu_q[b + 1] - base;
+    len = min(cu_q[b + 1] - base, Sq);  // a sequence longer than the bound is cut there
     grow = static_cast<long long>(base) + row;
     gb = 0;
   }
@@ -220,6 +223,13 @@ __global__ void __launch_bounds__(THREADS, 1)
     k_base = p_in.cu_k[blockIdx.z];
     p.Sk = p_in.cu_k[blockIdx.z + 1] - k_base;
     bt = 0;
+    // The grids and the statistics scratch are sized with the caller's bounds: a longer sequence
+    // is cut at the bound (nothing beyond the scratch is touched) and reported.
+    if (p.Sq > p_in.Sq || p.Sk > p_in.Sk) {
+      if (threadIdx.x == 0) atomicExch(p.status, STATUS_SEQ_EXCEEDS_BOUND);
+      p.Sq = min(p.Sq, p_in.Sq);
+      p.Sk = min(p.Sk, p_in.Sk);
+    }
   }
   // Shared memory is used to the last kilobytes, so there is no room for manual alignment slack:
   // the 1024-byte alignment the swizzled tiles need is requested from the compiler and verified.
@@ -614,6 +624,11 @@ __global__ void __launch_bounds__(THREADS, 1)
     k_base = p_in.cu_k[blockIdx.z];
     p.Sk = p_in.cu_k[blockIdx.z + 1] - k_base;
     bt = 0;
+    if (p.Sq > p_in.Sq || p.Sk > p_in.Sk) {
+      if (threadIdx.x == 0) atomicExch(p.status, STATUS_SEQ_EXCEEDS_BOUND);
+      p.Sq = min(p.Sq, p_in.Sq);
+      p.Sk = min(p.Sk, p_in.Sk);
+    }
   }
   if ((smem_u32(smem) & 1023u) != 0) {
     if (threadIdx.x == 0) atomicExch(p.status, 902);

@@ -39,12 +39,13 @@ constexpr int STAGE_BYTES = A_BYTES + B_BYTES;
 constexpr int THREADS = 320;  // warp 0 TMA, warp 1 MMA, warps 2-9 epilogue (two per TMEM lane quadrant)
 constexpr int EPI_WARPS = 8;
 constexpr int TMEM_COLS = 512;
-constexpr int RASTER_W = 8;  // N tiles per raster panel
+constexpr int RASTER_W = 8;  // N tiles per raster panel (upper bound; see Params::raster_w)
 constexpr size_t SMEM_BYTES = 1024 + STAGES * STAGE_BYTES + 256;
 
 struct Params {
   int M, N, K, batch;
   int num_m_tiles, num_n_tiles, num_tiles, k_blocks;
+  int raster_w;        // N tiles per raster panel, 1 .. RASTER_W
   int a_mn, b_mn;      // 1 = operand is MN-major (M or N contiguous)
   int out_f32, c_mode; // c_mode: 0 none, 1 bf16, 2 f32
   void* d;
@@ -79,10 +80,10 @@ __device__ __forceinline__ void tile_coords(const Params& p, int tile, int& b, i
   const int per_batch = p.num_m_tiles * p.num_n_tiles;
   b = tile / per_batch;
   int r = tile - b * per_batch;
-  const int panel_tiles = RASTER_W * p.num_m_tiles;
+  const int panel_tiles = p.raster_w * p.num_m_tiles;
   const int panel = r / panel_tiles;
-  const int first_n = panel * RASTER_W;
-  const int width = min(RASTER_W, p.num_n_tiles - first_n);
+  const int first_n = panel * p.raster_w;
+  const int width = min(p.raster_w, p.num_n_tiles - first_n);
   r -= panel * panel_tiles;
   m = r / width;
   n = first_n + (r - m * width);
@@ -731,21 +732,20 @@ static int32_t check_epi_operand(const char* name, const cdl_tensor* t, long lon
   return CDL_OK;
 }
 
-int32_t matmul_execute_epi(const cdl_tensor* a, const cdl_tensor* b, const cdl_tensor* c,
-                           const cdl_tensor* d, float alpha, float beta, int epi_mode,
-                           const cdl_tensor* aux0, const cdl_tensor* aux1, const cdl_tensor* out2,
-                           cudaStream_t stream);
-
 int32_t matmul_execute(const cdl_tensor* a, const cdl_tensor* b, const cdl_tensor* c,
-                       const cdl_tensor* d, float alpha, float beta, cudaStream_t stream) {
-  return matmul_execute_epi(a, b, c, d, alpha, beta, 0, nullptr, nullptr, nullptr, stream);
+                       const cdl_tensor* d, float alpha, float beta, cudaStream_t stream,
+                       const cdl_matmul_options* opts) {
+  return matmul_execute_epi(a, b, c, d, alpha, beta, 0, nullptr, nullptr, nullptr, stream, opts);
 }
 
 int32_t matmul_execute_epi(const cdl_tensor* a, const cdl_tensor* b, const cdl_tensor* c,
                            const cdl_tensor* d, float alpha, float beta, int epi_mode,
                            const cdl_tensor* aux0, const cdl_tensor* aux1, const cdl_tensor* out2,
-                           cudaStream_t stream) {
+                           cudaStream_t stream, const cdl_matmul_options* opts) {
   using namespace gemm;
+  const int variant = opts ? opts->variant : CDL_GEMM_AUTO;
+  if (variant < CDL_GEMM_AUTO || variant > CDL_GEMM_CTA_PAIR)
+    return fail(CDL_ERR_INVALID, "matmul: unknown kernel variant %d", variant);
   if (!a || !b || !d) return fail(CDL_ERR_INVALID, "matmul: a, b and d are required");
   if (a->rank != b->rank || (a->rank != 2 && a->rank != 3) || d->rank != a->rank)
     return fail(CDL_ERR_INVALID,
@@ -799,12 +799,8 @@ int32_t matmul_execute_epi(const cdl_tensor* a, const cdl_tensor* b, const cdl_t
   }
 
   // Kernel choice: CTA pairs (256 x 256 tiles) whenever the problem has more than one 128-row
-  // slab; CDL_B200_GEMM=1cta / 2cta overrides it (benchmarking aid).
-  bool use_pair = M > BM;
-  if (const char* env = getenv("CDL_B200_GEMM")) {
-    if (strcmp(env, "1cta") == 0) use_pair = false;
-    else if (strcmp(env, "2cta") == 0) use_pair = true;
-  }
+  // slab, unless the caller's options name a variant.
+  const bool use_pair = variant == CDL_GEMM_AUTO ? M > BM : variant == CDL_GEMM_CTA_PAIR;
   const int tile_m = use_pair ? PAIR_M : BM;
   const uint32_t b_box_rows = use_pair ? BN / 2 : BN;
 
@@ -842,6 +838,20 @@ int32_t matmul_execute_epi(const cdl_tensor* a, const cdl_tensor* b, const cdl_t
   if (tiles > INT32_MAX) return fail(CDL_ERR_UNSUPPORTED, "matmul: too many tiles");
   p.num_tiles = static_cast<int>(tiles);
   p.k_blocks = static_cast<int>((K + BK - 1) / BK);
+  {
+    // Raster panels: all M tiles of `raster_w` N tiles run together, so the panel's B columns
+    // (raster_w * 256 * K elements) and, when it fits next to them, all of A are served from L2
+    // while the panel lasts.  With a long K (the weight-gradient shapes: K = tokens) eight B
+    // column panels plus A exceed the L2's 126 MB and both get evicted and re-read from HBM, so
+    // the panel is narrowed until A and the panel's B fit a budget of 96 MB.
+    const double a_bytes = 2.0 * static_cast<double>(M) * K;
+    const double b_panel = 2.0 * BN * static_cast<double>(K);
+    const double budget = 96.0 * 1024 * 1024;
+    int w = RASTER_W;
+    if (a_bytes <= 0.75 * budget)
+      while (w > 2 && a_bytes + w * b_panel > budget) --w;
+    p.raster_w = w;
+  }
   p.a_mn = la.mn_major;
   p.b_mn = lb.mn_major;
   p.out_f32 = d->dtype == CDL_F32;
@@ -931,11 +941,10 @@ int32_t matmul_execute_epi(const cdl_tensor* a, const cdl_tensor* b, const cdl_t
   // K slicing for the accumulate-in-place form (D = C, f32, beta = 1: the weight-gradient GEMM,
   // whose output is small and whose K is long).  Slices add into D with atomics, which removes
   // the tile-count quantisation (e.g. 192 tiles on 74 CTA pairs = 2.6 waves) at the price of an
-  // unordered f32 sum; CDL_B200_DETERMINISTIC=1 turns it off.
+  // unordered f32 sum; the caller's `deterministic` option turns it off.
   if (use_pair && use_c && p.out_f32 && c->dtype == CDL_F32 && c->ptr == d->ptr && beta == 1.0f &&
       p.ldc == p.ldd && p.c_batch == p.d_batch) {
-    const char* det = getenv("CDL_B200_DETERMINISTIC");
-    if (!(det && det[0] == '1')) {
+    if (!(opts && opts->deterministic != 0)) {
       const int nc = max_clusters[dev & 63];
       int best_s = 1;
       double best_cost = 1e30;
@@ -980,6 +989,47 @@ int32_t cdl_b200_matmul(const cdl_tensor* a, const cdl_tensor* b, const cdl_tens
   (void)scratch;
   (void)scratch_bytes;
   return cdl::matmul_execute(a, b, c, d, alpha, beta, static_cast<cudaStream_t>(stream));
+}
+
+int32_t cdl_b200_matmul_opt(const cdl_tensor* a, const cdl_tensor* b, const cdl_tensor* c,
+                            const cdl_tensor* d, float alpha, float beta,
+                            const cdl_matmul_options* options, void* scratch, size_t scratch_bytes,
+                            cdl_stream stream) {
+  (void)scratch;
+  (void)scratch_bytes;
+  return cdl::matmul_execute(a, b, c, d, alpha, beta, static_cast<cudaStream_t>(stream), options);
+}
+
+int32_t cdl_b200_matmul_candidates(const cdl_tensor* a, const cdl_tensor* b, const cdl_tensor* d,
+                                   cdl_matmul_options* out, int32_t capacity, int32_t* count) {
+  using namespace cdl;
+  if (!a || !b || !d || !count || (capacity > 0 && !out))
+    return fail(CDL_ERR_INVALID, "matmul_candidates: a, b, d, count (and out) are required");
+  cdl_matmul_options list[4];
+  int n = 0;
+  const bool tensor_core = a->dtype == CDL_BF16 && b->dtype == CDL_BF16 && a->rank >= 2 &&
+                           a->rank == b->rank && [&] {
+                             gemm::OperandLayout la, lb;
+                             const bool ok = gemm::analyze_operand("a", a, true, &la) == CDL_OK &&
+                                             gemm::analyze_operand("b", b, false, &lb) == CDL_OK;
+                             last_error().clear();
+                             return ok;
+                           }();
+  if (!tensor_core) {
+    list[n++] = {CDL_GEMM_AUTO, 0};
+  } else {
+    const long long M = a->shape[a->rank - 2];
+    const bool accumulates = d->dtype == CDL_F32;  // the weight-gradient form may slice K
+    const int first = M > gemm::BM ? CDL_GEMM_CTA_PAIR : CDL_GEMM_ONE_CTA;
+    const int second = first == CDL_GEMM_CTA_PAIR ? CDL_GEMM_ONE_CTA : CDL_GEMM_CTA_PAIR;
+    list[n++] = {first, 0};
+    if (accumulates && first == CDL_GEMM_CTA_PAIR) list[n++] = {first, 1};
+    list[n++] = {second, 0};
+    if (accumulates && second == CDL_GEMM_CTA_PAIR) list[n++] = {second, 1};
+  }
+  *count = n;
+  for (int i = 0; i < n && i < capacity; ++i) out[i] = list[i];
+  return CDL_OK;
 }
 
 int32_t cdl_b200_matmul_swiglu_gate(const cdl_tensor* a, const cdl_tensor* b, const cdl_tensor* up,

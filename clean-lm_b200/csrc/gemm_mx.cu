@@ -746,9 +746,13 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(THREADS, 1)
 
 static int32_t matmul_mx_run(const char* op, const cdl_mx_tensor* a, const cdl_mx_tensor* b,
                              const cdl_tensor* c, const cdl_tensor* d, const cdl_mx_tensor* d_mx,
-                             float alpha, float beta, cudaStream_t stream) {
+                             float alpha, float beta, cudaStream_t stream,
+                             const cdl_matmul_options* opts = nullptr) {
   using namespace gemm_mx;
   if (!a || !b || (!d && !d_mx)) return fail(CDL_ERR_INVALID, "%s: a, b and d are required", op);
+  const int variant = opts ? opts->variant : CDL_GEMM_AUTO;
+  if (variant < CDL_GEMM_AUTO || variant > CDL_GEMM_CTA_PAIR)
+    return fail(CDL_ERR_INVALID, "%s: unknown kernel variant %d", op, variant);
   if ((a->format != CDL_MXFP8 && a->format != CDL_NVFP4) || b->format != a->format)
     return fail(CDL_ERR_UNSUPPORTED,
                 "%s: both operands must be MXFP8, or both NVFP4 (mixed block-scaled formats are not "
@@ -875,8 +879,7 @@ static int32_t matmul_mx_run(const char* op, const cdl_mx_tensor* a, const cdl_m
     CDL_CHECK(encode_tmap(&tb, b->values, TMAP_U8, 3, dims, strides, box, true));
   }
   ProfileScope ps(PROF_GEMM, 2.0 * M * N * K, stream);
-  const char* mode = getenv("CDL_B200_MX_GEMM");  // "single" forces the one-CTA kernel
-  if (M > BM && !(mode && strcmp(mode, "single") == 0)) {
+  if (variant == CDL_GEMM_AUTO ? M > BM : variant == CDL_GEMM_CTA_PAIR) {
     // CTA pairs over 256 x 256 tiles
     p.num_m_tiles = static_cast<int>((M + 2 * BM - 1) / (2 * BM));
     p.num_tiles = p.num_m_tiles * p.num_n_tiles;
@@ -914,8 +917,10 @@ static int32_t matmul_mx_run(const char* op, const cdl_mx_tensor* a, const cdl_m
 }
 
 int32_t matmul_mx_execute(const cdl_mx_tensor* a, const cdl_mx_tensor* b, const cdl_tensor* c,
-                          const cdl_tensor* d, float alpha, float beta, cudaStream_t stream) {
-  return matmul_mx_run("matmul (block-scaled operands)", a, b, c, d, nullptr, alpha, beta, stream);
+                          const cdl_tensor* d, float alpha, float beta, cudaStream_t stream,
+                          const cdl_matmul_options* opts) {
+  return matmul_mx_run("matmul (block-scaled operands)", a, b, c, d, nullptr, alpha, beta, stream,
+                       opts);
 }
 
 int32_t matmul_mx_out_execute(const cdl_mx_tensor* a, const cdl_mx_tensor* b, const cdl_mx_tensor* d,
@@ -946,6 +951,12 @@ extern "C" {
 int32_t cdl_b200_matmul_mx(const cdl_mx_tensor* a, const cdl_mx_tensor* b, const cdl_tensor* c,
                            const cdl_tensor* d, float alpha, float beta, cdl_stream stream) {
   return cdl::matmul_mx_execute(a, b, c, d, alpha, beta, static_cast<cudaStream_t>(stream));
+}
+
+int32_t cdl_b200_matmul_mx_opt(const cdl_mx_tensor* a, const cdl_mx_tensor* b, const cdl_tensor* c,
+                               const cdl_tensor* d, float alpha, float beta,
+                               const cdl_matmul_options* options, cdl_stream stream) {
+  return cdl::matmul_mx_execute(a, b, c, d, alpha, beta, static_cast<cudaStream_t>(stream), options);
 }
 
 int32_t cdl_b200_matmul_mx_out(const cdl_mx_tensor* a, const cdl_mx_tensor* b, const cdl_mx_tensor* d,

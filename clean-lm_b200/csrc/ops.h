@@ -6,7 +6,8 @@
 namespace cdl {
 
 int32_t matmul_execute(const cdl_tensor* a, const cdl_tensor* b, const cdl_tensor* c,
-                       const cdl_tensor* d, float alpha, float beta, cudaStream_t stream);
+                       const cdl_tensor* d, float alpha, float beta, cudaStream_t stream,
+                       const cdl_matmul_options* opts = nullptr);
 // gemm_general.cu: any strides, bf16 or f32 inputs, CUDA cores (operands already validated).
 int32_t matmul_general_execute(const cdl_tensor* a, const cdl_tensor* b, const cdl_tensor* c,
                                const cdl_tensor* d, float alpha, float beta, cudaStream_t stream);
@@ -15,14 +16,14 @@ int32_t matmul_general_execute(const cdl_tensor* a, const cdl_tensor* b, const c
 int32_t matmul_execute_epi(const cdl_tensor* a, const cdl_tensor* b, const cdl_tensor* c,
                            const cdl_tensor* d, float alpha, float beta, int epi_mode,
                            const cdl_tensor* aux0, const cdl_tensor* aux1, const cdl_tensor* out2,
-                           cudaStream_t stream);
+                           cudaStream_t stream, const cdl_matmul_options* opts = nullptr);
 // norm_general.cu: any float types, strides and column counts (layer = 0 RmsNorm, 1 LayerNorm).
 int32_t norm_general_execute(int layer, const cdl_tensor* x, const cdl_tensor* scale,
                              const cdl_tensor* bias, float eps, const cdl_tensor* y,
                              const cdl_tensor* mean, const cdl_tensor* r_inv, cudaStream_t stream);
 int32_t rmsnorm_fwd_execute(const cdl_tensor* x, const cdl_tensor* scale, const cdl_tensor* bias,
                             float eps, const cdl_tensor* y, const cdl_tensor* r_inv,
-                            cudaStream_t stream);
+                            cudaStream_t stream, const cdl_norm_options* opts = nullptr);
 int32_t layernorm_fwd_execute(const cdl_tensor* x, const cdl_tensor* scale, const cdl_tensor* bias,
                               float eps, const cdl_tensor* y, const cdl_tensor* mean,
                               const cdl_tensor* r_inv, cudaStream_t stream);
@@ -30,7 +31,7 @@ size_t rmsnorm_bwd_scratch_bytes(long long rows, long long cols);
 int32_t rmsnorm_bwd_execute(const cdl_tensor* x, const cdl_tensor* dy, const cdl_tensor* res,
                             const cdl_tensor* scale, const cdl_tensor* r_inv, const cdl_tensor* dx,
                             const cdl_tensor* dscale, void* scratch, size_t scratch_bytes,
-                            cudaStream_t stream);
+                            cudaStream_t stream, const cdl_norm_options* opts = nullptr);
 int32_t attn_fwd_execute(const cdl_attn_desc* desc, const cdl_tensor* q, const cdl_tensor* k,
                          const cdl_tensor* v, const cdl_tensor* o, const cdl_tensor* lse,
                          cudaStream_t stream);
@@ -73,7 +74,8 @@ int32_t rmsnorm_fwd_mx_execute(const cdl_tensor* x, const cdl_tensor* scale, con
                                float eps, const cdl_mx_tensor* y_row, const cdl_mx_tensor* y_col,
                                const cdl_tensor* r_inv, cudaStream_t stream);
 int32_t matmul_mx_execute(const cdl_mx_tensor* a, const cdl_mx_tensor* b, const cdl_tensor* c,
-                          const cdl_tensor* d, float alpha, float beta, cudaStream_t stream);
+                          const cdl_tensor* d, float alpha, float beta, cudaStream_t stream,
+                          const cdl_matmul_options* opts = nullptr);
 int32_t matmul_mx_out_execute(const cdl_mx_tensor* a, const cdl_mx_tensor* b, const cdl_mx_tensor* d,
                               float alpha, cudaStream_t stream);
 

@@ -618,11 +618,12 @@ static bool fast_norm_operands(const cdl_tensor* x, const cdl_tensor* scale, con
 template <int NCH>
 static void launch_fwd(const cdl_tensor* x, const cdl_tensor* scale, const cdl_tensor* bias,
                        float eps, const cdl_tensor* y, const cdl_tensor* r_inv, int rows, int cols,
-                       cudaStream_t stream) {
-  const char* mode = getenv("CDL_B200_NORM");
+                       int variant, cudaStream_t stream) {
   int* status = device_status_ptr();
   if constexpr (NCH <= 8) {
-  if (status != nullptr && rows >= 2 * sm_count() && mode && strcmp(mode, "pipe") == 0) {
+  // The pipelined forward measured slower than the warp-per-row one, so only an explicit request
+  // selects it.
+  if (status != nullptr && rows >= 2 * sm_count() && variant == CDL_NORM_PIPELINED) {
     const int row_bytes = cols * 2;
     int stages = PIPE_RING_BYTES / row_bytes;
     if (stages > 64) stages = 64;
@@ -698,10 +699,13 @@ static void launch_bwd_pipe(const cdl_tensor* x, const cdl_tensor* dy, const cdl
 
 int32_t rmsnorm_fwd_execute(const cdl_tensor* x, const cdl_tensor* scale, const cdl_tensor* bias,
                             float eps, const cdl_tensor* y, const cdl_tensor* r_inv,
-                            cudaStream_t stream) {
+                            cudaStream_t stream, const cdl_norm_options* opts) {
   using namespace norm;
   const char* op = "norm_fwd";
   if (!x || !y) return fail(CDL_ERR_INVALID, "%s: x and y are required", op);
+  const int variant = opts ? opts->variant : CDL_NORM_AUTO;
+  if (variant < CDL_NORM_AUTO || variant > CDL_NORM_PIPELINED)
+    return fail(CDL_ERR_INVALID, "%s: unknown kernel variant %d", op, variant);
   if (!fast_norm_operands(x, scale, bias, y))
     return norm_general_execute(0, x, scale, bias, eps, y, nullptr, r_inv, stream);
   const long long rows = x->shape[0], cols = x->shape[1];
@@ -710,12 +714,12 @@ int32_t rmsnorm_fwd_execute(const cdl_tensor* x, const cdl_tensor* scale, const 
   if (rows > INT32_MAX) return fail(CDL_ERR_UNSUPPORTED, "%s: too many rows", op);
   const int r = static_cast<int>(rows), c = static_cast<int>(cols);
   ProfileScope ps(PROF_NORM_FWD, 4.0 * rows * cols + 2.0 * cols + (r_inv ? 4.0 * rows : 0.0), stream);
-  if (c <= 256) launch_fwd<1>(x, scale, bias, eps, y, r_inv, r, c, stream);
-  else if (c <= 512) launch_fwd<2>(x, scale, bias, eps, y, r_inv, r, c, stream);
-  else if (c <= 1024) launch_fwd<4>(x, scale, bias, eps, y, r_inv, r, c, stream);
-  else if (c <= 2048) launch_fwd<8>(x, scale, bias, eps, y, r_inv, r, c, stream);
-  else if (c <= 4096) launch_fwd<16>(x, scale, bias, eps, y, r_inv, r, c, stream);
-  else launch_fwd<32>(x, scale, bias, eps, y, r_inv, r, c, stream);
+  if (c <= 256) launch_fwd<1>(x, scale, bias, eps, y, r_inv, r, c, variant, stream);
+  else if (c <= 512) launch_fwd<2>(x, scale, bias, eps, y, r_inv, r, c, variant, stream);
+  else if (c <= 1024) launch_fwd<4>(x, scale, bias, eps, y, r_inv, r, c, variant, stream);
+  else if (c <= 2048) launch_fwd<8>(x, scale, bias, eps, y, r_inv, r, c, variant, stream);
+  else if (c <= 4096) launch_fwd<16>(x, scale, bias, eps, y, r_inv, r, c, variant, stream);
+  else launch_fwd<32>(x, scale, bias, eps, y, r_inv, r, c, variant, stream);
   CDL_CUDA(cudaGetLastError());
   return CDL_OK;
 }
@@ -770,9 +774,12 @@ size_t rmsnorm_bwd_scratch_bytes(long long rows, long long cols) {
 int32_t rmsnorm_bwd_execute(const cdl_tensor* x, const cdl_tensor* dy, const cdl_tensor* res,
                             const cdl_tensor* scale, const cdl_tensor* r_inv, const cdl_tensor* dx,
                             const cdl_tensor* dscale, void* scratch, size_t scratch_bytes,
-                            cudaStream_t stream) {
+                            cudaStream_t stream, const cdl_norm_options* opts) {
   using namespace norm;
   const char* op = "norm_bwd";
+  const int variant = opts ? opts->variant : CDL_NORM_AUTO;
+  if (variant < CDL_NORM_AUTO || variant > CDL_NORM_PIPELINED)
+    return fail(CDL_ERR_INVALID, "%s: unknown kernel variant %d", op, variant);
   if (!x || !dy || !scale || !r_inv || !dx || !dscale)
     return fail(CDL_ERR_INVALID, "%s: x, dy, scale, r_inv, dx and dscale are required", op);
   if (x->rank != 2) return fail(CDL_ERR_INVALID, "%s: x must be a 2D tensor", op);
@@ -801,13 +808,11 @@ int32_t rmsnorm_bwd_execute(const cdl_tensor* x, const cdl_tensor* dy, const cdl
   const int need = (r + warps - 1) / warps;
   if (grid > need) grid = need;
   int num_partials = grid;
-  const char* mode = getenv("CDL_B200_NORM");
   // Measured back to back at [16384, 2048]: without a residual gradient the warp-per-row kernel
   // is faster (47 us against 55 us); with one, the pipelined kernel is (60 us against 72 us: the
   // third row does not fit the other kernel's registers next to the dscale accumulators).
   const bool pipe = c <= 2048 && r >= 2 * sm_count() &&
-                    (mode ? strcmp(mode, "pipe") == 0 || (res != nullptr && strcmp(mode, "simple") != 0)
-                          : res != nullptr);
+                    (variant == CDL_NORM_AUTO ? res != nullptr : variant == CDL_NORM_PIPELINED);
   ProfileScope ps(PROF_NORM_BWD, (res ? 8.0 : 6.0) * rows * cols + 6.0 * cols + 4.0 * rows, stream);
   if (pipe) {
     num_partials = sm_count();
@@ -900,6 +905,14 @@ int32_t cdl_b200_rmsnorm_fwd(const cdl_tensor* x, const cdl_tensor* scale, const
                                   static_cast<cudaStream_t>(stream));
 }
 
+int32_t cdl_b200_rmsnorm_fwd_opt(const cdl_tensor* x, const cdl_tensor* scale,
+                                 const cdl_tensor* bias, float eps, const cdl_tensor* y,
+                                 const cdl_tensor* r_inv, const cdl_norm_options* options,
+                                 cdl_stream stream) {
+  return cdl::rmsnorm_fwd_execute(x, scale, bias, eps, y, r_inv, static_cast<cudaStream_t>(stream),
+                                  options);
+}
+
 int32_t cdl_b200_layernorm_fwd(const cdl_tensor* x, const cdl_tensor* scale, const cdl_tensor* bias,
                                float eps, const cdl_tensor* y, const cdl_tensor* mean,
                                const cdl_tensor* r_inv, cdl_stream stream) {
@@ -914,6 +927,15 @@ int32_t cdl_b200_rmsnorm_bwd(const cdl_tensor* x, const cdl_tensor* dy,
                              cdl_stream stream) {
   return cdl::rmsnorm_bwd_execute(x, dy, residual_dy, scale, r_inv, dx, dscale, scratch,
                                   scratch_bytes, static_cast<cudaStream_t>(stream));
+}
+
+int32_t cdl_b200_rmsnorm_bwd_opt(const cdl_tensor* x, const cdl_tensor* dy,
+                                 const cdl_tensor* residual_dy, const cdl_tensor* scale,
+                                 const cdl_tensor* r_inv, const cdl_tensor* dx,
+                                 const cdl_tensor* dscale, const cdl_norm_options* options,
+                                 void* scratch, size_t scratch_bytes, cdl_stream stream) {
+  return cdl::rmsnorm_bwd_execute(x, dy, residual_dy, scale, r_inv, dx, dscale, scratch,
+                                  scratch_bytes, static_cast<cudaStream_t>(stream), options);
 }
 
 int32_t cdl_b200_rmsnorm_bwd_static(const cdl_tensor* x, const cdl_tensor* dy,

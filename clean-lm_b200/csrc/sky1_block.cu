@@ -288,22 +288,26 @@ int32_t sky1_block_bwd(const cdl_sky1_config* cfg, const cdl_sky1_weights* wt, c
   const cdl_tensor woT = transposed(wo), wqkvT = transposed(wqkv);
 
   if (phase < 0 || phase > 2) return fail(CDL_ERR_INVALID, "sky1_block_bwd: phase must be 0, 1 or 2");
+  // Weight-gradient products: the caller chooses between K slices that meet through f32 atomics
+  // (default) and a fixed summation order.
+  const cdl_matmul_options wg_opts{CDL_GEMM_AUTO, (cfg->flags & CDL_SKY1_DETERMINISTIC) ? 1 : 0};
+  const cdl_matmul_options* wg = &wg_opts;
   if (phase != 2) {
   // FFN
-  CDL_CHECK(matmul_execute(&actT, &tdy, &gwdown, &gwdown, 1.f, 1.f, st));          // dWdown += act^T dy
+  CDL_CHECK(matmul_execute(&actT, &tdy, &gwdown, &gwdown, 1.f, 1.f, st, wg));          // dWdown += act^T dy
   // d_act = dy Wdown^T never reaches memory: the epilogue turns it into d_up and d_gate
   CDL_CHECK(matmul_execute_epi(&tdy, &wdownT, nullptr, &tdact, 1.f, 0.f, 2, &tgate, &tup, &tdgate, st));
   CDL_CHECK(rmsnorm_fwd_execute(&to, &g2, nullptr, cfg->eps, &th, &tr, st));        // recompute h2, r2
-  CDL_CHECK(matmul_execute(&hT, &tdact, &gwup, &gwup, 1.f, 1.f, st));               // dWup += h2^T d_up
+  CDL_CHECK(matmul_execute(&hT, &tdact, &gwup, &gwup, 1.f, 1.f, st, wg));               // dWup += h2^T d_up
   CDL_CHECK(matmul_execute(&tdact, &wupT, nullptr, &tdh, 1.f, 0.f, st));            // dh2 = d_up Wup^T
-  CDL_CHECK(matmul_execute(&hT, &tdgate, &gwgate, &gwgate, 1.f, 1.f, st));          // dWgate += h2^T d_gate
+  CDL_CHECK(matmul_execute(&hT, &tdgate, &gwgate, &gwgate, 1.f, 1.f, st, wg));          // dWgate += h2^T d_gate
   CDL_CHECK(matmul_execute(&tdgate, &wgateT, &tdh, &tdh, 1.f, 1.f, st));            // dh2 += d_gate Wgate^T
   CDL_CHECK(rmsnorm_bwd_execute(&to, &tdh, &tdy, &g2, &tr, &tdo, &dg2, b.norm_scratch,
                                 b.norm_scratch_bytes, st));                         // d_o (+ dy)
   }
   if (phase == 1) return CDL_OK;
   // attention
-  CDL_CHECK(matmul_execute(&attnT, &tdo, &gwo, &gwo, 1.f, 1.f, st));                // dWo += attn^T d_o
+  CDL_CHECK(matmul_execute(&attnT, &tdo, &gwo, &gwo, 1.f, 1.f, st, wg));                // dWo += attn^T d_o
   CDL_CHECK(matmul_execute(&tdo, &woT, nullptr, &tdattn, 1.f, 0.f, st));            // d_attn = d_o Wo^T
   const cdl_tensor rv = rope_view(b.dqkv, d);
   if (d.rg) {
@@ -333,7 +337,7 @@ int32_t sky1_block_bwd(const cdl_sky1_config* cfg, const cdl_sky1_weights* wt, c
     CDL_CHECK(rope_execute(&rv, &cs, static_cast<int32_t>(d.H + d.Hkv), static_cast<int32_t>(d.S), 1, st));
   }
   CDL_CHECK(rmsnorm_fwd_execute(&tx, &g1, nullptr, cfg->eps, &th, &tr, st));        // recompute h1, r1
-  CDL_CHECK(matmul_execute(&hT, &tdqkv, &gwqkv, &gwqkv, 1.f, 1.f, st));             // dWqkv += h1^T d_qkv
+  CDL_CHECK(matmul_execute(&hT, &tdqkv, &gwqkv, &gwqkv, 1.f, 1.f, st, wg));             // dWqkv += h1^T d_qkv
   CDL_CHECK(matmul_execute(&tdqkv, &wqkvT, nullptr, &tdh, 1.f, 0.f, st));           // dh1 = d_qkv Wqkv^T
   CDL_CHECK(rmsnorm_bwd_execute(&tx, &tdh, &tdo, &g1, &tr, &tdx, &dg1, b.norm_scratch,
                                 b.norm_scratch_bytes, st));                         // dx (+ d_o)

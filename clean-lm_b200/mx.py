@@ -128,12 +128,20 @@ def norm_fwd_mx(x: torch.Tensor, scale: Optional[torch.Tensor] = None,
 
 def matmul_mx(a: MxTensor, b: MxTensor, out_dtype: torch.dtype = torch.bfloat16, alpha: float = 1.0,
               out: Optional[torch.Tensor] = None, c: Optional[torch.Tensor] = None,
-              beta: float = 0.0) -> torch.Tensor:
+              beta: float = 0.0, variant: int = 0) -> torch.Tensor:
     """D = alpha * A . B + beta * C for a rowwise A [M, K] and a colwise B [K, N]; `c` may be `out`
-    (accumulation in place)."""
+    (accumulation in place).  `variant`: cdl_gemm_variant (0 = the library's heuristic)."""
     if out is None:
         out = torch.empty(a.rows, b.cols, dtype=out_dtype, device=a.values.device)
     aa, ab, tc, td = a.arg(), b.arg(), tensor_arg(c), tensor_arg(out)
+    if variant != 0:
+        import ctypes
+
+        from ._lib import CdlMatmulOptions
+        mo = CdlMatmulOptions(int(variant), 0)
+        check(lib.cdl_b200_matmul_mx_opt(ref(aa), ref(ab), ref(tc), ref(td), alpha, beta,
+                                         ctypes.byref(mo), _stream()))
+        return out
     check(lib.cdl_b200_matmul_mx(ref(aa), ref(ab), ref(tc), ref(td), alpha, beta, _stream()))
     return out
 

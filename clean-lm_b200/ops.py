@@ -41,6 +41,9 @@ class MatmulOpts:
     c: Optional[torch.Tensor] = None  # needs a nonzero beta to have an effect
     alpha: float = 1.0
     beta: float = 0.0
+    # Kernel choice, the argument an engine's tuner would vary per graph node (cdl_matmul_options):
+    variant: int = _lib.GEMM_AUTO
+    deterministic: bool = False  # fixed f32 summation order for the accumulate-in-place form
 
 
 def matmul(a: torch.Tensor, b: torch.Tensor, opts: MatmulOpts | None = None,
@@ -58,9 +61,24 @@ def matmul(a: torch.Tensor, b: torch.Tensor, opts: MatmulOpts | None = None,
     if out is None:
         out = torch.empty(*a.shape[:-1], b.shape[-1], dtype=opts.out, device=a.device)
     ta, tb, tc, td = tensor_arg(a), tensor_arg(b), tensor_arg(opts.c), tensor_arg(out)
-    check(lib.cdl_b200_matmul(ref(ta), ref(tb), ref(tc), ref(td), opts.alpha, opts.beta, None, 0,
-                              _stream()))
+    if opts.variant == _lib.GEMM_AUTO and not opts.deterministic:
+        check(lib.cdl_b200_matmul(ref(ta), ref(tb), ref(tc), ref(td), opts.alpha, opts.beta, None, 0,
+                                  _stream()))
+    else:
+        mo = _lib.CdlMatmulOptions(int(opts.variant), 1 if opts.deterministic else 0)
+        check(lib.cdl_b200_matmul_opt(ref(ta), ref(tb), ref(tc), ref(td), opts.alpha, opts.beta,
+                                      ctypes.byref(mo), None, 0, _stream()))
     return out
+
+
+def matmul_candidates(a: torch.Tensor, b: torch.Tensor, out: torch.Tensor) -> list:
+    """[(variant, deterministic), ...] valid for this problem, the heuristic default first
+    (what an Executor would hand the tuner, op.rs:301-318)."""
+    buf = (_lib.CdlMatmulOptions * 8)()
+    n = ctypes.c_int32(0)
+    ta, tb, td = tensor_arg(a), tensor_arg(b), tensor_arg(out)
+    check(lib.cdl_b200_matmul_candidates(ref(ta), ref(tb), ref(td), buf, 8, ctypes.byref(n)))
+    return [(buf[i].variant, bool(buf[i].deterministic)) for i in range(n.value)]
 
 
 # --------------------------------------------------------------------------- norm
@@ -76,6 +94,7 @@ class NormFwdOpts:
     save_stats: bool = False
     norm_type: str = "rms"
     out: torch.dtype = torch.bfloat16
+    variant: int = _lib.NORM_AUTO  # cdl_norm_options.variant (RMSNorm only)
 
 
 @dataclass
@@ -101,6 +120,11 @@ def norm_fwd(x: torch.Tensor, opts: NormFwdOpts | None = None) -> NormFwdOutputs
         return NormFwdOutputs(y, r_inv, mean)
     if opts.norm_type != "rms":
         raise _lib.CdlError(-1, f"norm_fwd: unknown norm type '{opts.norm_type}'")
+    if opts.variant != _lib.NORM_AUTO:
+        no = _lib.CdlNormOptions(int(opts.variant))
+        check(lib.cdl_b200_rmsnorm_fwd_opt(ref(tx), ref(ts), ref(tb), opts.eps, ref(ty), ref(tr),
+                                           ctypes.byref(no), _stream()))
+        return NormFwdOutputs(y, r_inv)
     check(lib.cdl_b200_rmsnorm_fwd(ref(tx), ref(ts), ref(tb), opts.eps, ref(ty), ref(tr), _stream()))
     return NormFwdOutputs(y, r_inv)
 
@@ -111,8 +135,10 @@ def norm_bwd_scratch_bytes(rows: int, cols: int) -> int:
     return n.value
 
 
-def norm_bwd(x, dy, scale, r_inv, dscale, residual_dy=None, scratch=None, dx=None) -> torch.Tensor:
-    """dx of RMSNorm; `dscale` (f32 [cols]) is accumulated in place."""
+def norm_bwd(x, dy, scale, r_inv, dscale, residual_dy=None, scratch=None, dx=None,
+             variant: int = _lib.NORM_AUTO) -> torch.Tensor:
+    """dx of RMSNorm; `dscale` (f32 [cols]) is accumulated in place.  `variant` selects the
+    kernel form (cdl_norm_options.variant)."""
     _require_cuda(x, dy, scale, r_inv, dscale, residual_dy)
     if x.dim() != 2:
         raise _lib.CdlError(-1, "norm_bwd: x must be a 2D tensor")
@@ -122,6 +148,12 @@ def norm_bwd(x, dy, scale, r_inv, dscale, residual_dy=None, scratch=None, dx=Non
     if scratch is None:
         scratch = torch.empty(max(need, 16), dtype=torch.uint8, device=x.device)
     args = [tensor_arg(t) for t in (x, dy, residual_dy, scale, r_inv, dx, dscale)]
+    if variant != _lib.NORM_AUTO:
+        no = _lib.CdlNormOptions(int(variant))
+        check(lib.cdl_b200_rmsnorm_bwd_opt(*(ref(a) for a in args), ctypes.byref(no),
+                                           ctypes.c_void_p(scratch.data_ptr()),
+                                           scratch.numel() * scratch.element_size(), _stream()))
+        return dx
     check(lib.cdl_b200_rmsnorm_bwd(*(ref(a) for a in args), ctypes.c_void_p(scratch.data_ptr()),
                                    scratch.numel() * scratch.element_size(), _stream()))
     return dx

@@ -30,6 +30,7 @@ class Sky1Config:
     ffn: int = 5632
     eps: float = 1e-6
     rope_base: float = 10000.0
+    deterministic: bool = False  # weight-gradient GEMMs with a fixed summation order
 
     @property
     def tokens(self) -> int:
@@ -50,7 +51,8 @@ class Sky1Config:
 
     def c_struct(self) -> _lib.CdlSky1Config:
         return _lib.CdlSky1Config(self.batch, self.seqlen, self.hidden, self.heads, self.kv_heads,
-                                  self.head_dim, self.ffn, self.eps)
+                                  self.head_dim, self.ffn, self.eps,
+                                  _lib.CDL_SKY1_DETERMINISTIC if self.deterministic else 0)
 
     def flops_fwd_bwd(self) -> float:
         """Algorithmic FLOP of one block forward + backward: 3 x the five GEMMs' 2MNK plus causal
@@ -228,7 +230,10 @@ class Sky1LM:
     """
 
     def __init__(self, cfg: Sky1LMConfig, seed: int = 4, device="cuda", std: float = 0.02,
-                 process_group=None):
+                 process_group=None, init_on_device: bool = False):
+        """`init_on_device` draws the initial weights with the device's generator (seconds for the
+        24-layer model) instead of the host's; both are N(0, std) from `seed`, but not the same
+        values."""
         import torch.distributed as dist
 
         self.cfg, self.device = cfg, torch.device(device)
@@ -251,13 +256,16 @@ class Sky1LM:
         self.v = torch.zeros(off, **f32)
         self.grads = torch.zeros(off, **f32)
         self.replica = torch.empty(off, dtype=torch.bfloat16, device=self.device)
-        gen = torch.Generator().manual_seed(seed)
-        init = {}  # drawn in name order, so the values do not depend on the flat layout
+        init_dev = self.device if init_on_device else torch.device("cpu")
+        gen = torch.Generator(device=init_dev).manual_seed(seed)
+        # drawn in name order, so the values do not depend on the flat layout
         for name, shape, _ in sorted(layout, key=lambda t: t[0]):
-            init[name] = (torch.ones(shape) if "norm" in name else torch.randn(shape, generator=gen) * std)
-        for name, shape, _ in layout:
             o, n = self.offsets[name]
-            self.master[o:o + n].copy_(init[name].reshape(-1))
+            if "norm" in name:
+                self.master[o:o + n].fill_(1.0)
+            else:
+                self.master[o:o + n].copy_(
+                    (torch.randn(shape, generator=gen, device=init_dev) * std).reshape(-1))
         self.replica.copy_(self.master)
         # contiguous runs with one weight-decay setting -> one AdamW launch each
         self.segments = []

@@ -72,6 +72,36 @@ typedef struct {
 int32_t cdl_b200_profile_start(int32_t max_records);
 int32_t cdl_b200_profile_stop(cdl_profile_record* out, int32_t capacity, int32_t* count);
 
+/* ---- Per-call kernel choices -------------------------------------------------------------
+ * The reference's executors hand the engine's tuner a list of candidate implementations with the
+ * heuristic default first (crates/cleandl/src/execgraph/op.rs:301-318; the matmul's list is built
+ * in crates/cleandl/src/execgraph/ops/matmul.rs:667-729), and the tuner times each one per graph
+ * node.  The `*_opt` entry points below take that choice as an argument (NULL = the library's own
+ * heuristic, i.e. what the plain entry points do), and the `*_candidates` calls enumerate the
+ * valid choices for a problem, default first.  Nothing in the library reads an environment
+ * variable. */
+typedef enum {
+  CDL_GEMM_AUTO = 0,    /* heuristic: CTA pairs whenever M > 128 */
+  CDL_GEMM_ONE_CTA = 1, /* 128 x 256 tiles, one CTA per tile */
+  CDL_GEMM_CTA_PAIR = 2 /* 256 x 256 tiles, tcgen05.mma.cta_group::2 over a cluster of two CTAs */
+} cdl_gemm_variant;
+typedef struct {
+  int32_t variant;       /* cdl_gemm_variant */
+  int32_t deterministic; /* != 0: fixed f32 summation order.  The accumulate-in-place form
+                          * (D = C in f32, beta = 1: the weight-gradient GEMM) otherwise cuts K into
+                          * slices that add into D with red.global.add, so its low-order bits can
+                          * differ from run to run. */
+} cdl_matmul_options;
+typedef enum {
+  CDL_NORM_AUTO = 0,         /* heuristic (measured per form, see cdl_b200_rmsnorm_bwd) */
+  CDL_NORM_WARP_PER_ROW = 1, /* rows streamed straight from global memory into registers */
+  CDL_NORM_PIPELINED = 2     /* persistent CTAs, rows staged through a shared-memory ring of bulk
+                              * copies; cols <= 2048 and rows >= 2 per SM, else the other form */
+} cdl_norm_variant;
+typedef struct {
+  int32_t variant; /* cdl_norm_variant */
+} cdl_norm_options;
+
 /* ---- Matmul: D = alpha * A . B + beta * C ----------------------------------------------
  * Replaces MatmulExecutor::execute (crates/cleandl/src/execgraph/ops/matmul.rs:1092-1183),
  * which forwards to cuBLASLt.  A is [M,K] or [batch,M,K]; B is [K,N] or [batch,K,N]; C
@@ -87,6 +117,20 @@ int32_t cdl_b200_profile_stop(cdl_profile_record* out, int32_t capacity, int32_t
 int32_t cdl_b200_matmul(const cdl_tensor* a, const cdl_tensor* b, const cdl_tensor* c,
                         const cdl_tensor* d, float alpha, float beta, void* scratch,
                         size_t scratch_bytes, cdl_stream stream);
+/* The same product with the kernel choice made by the caller (NULL options = cdl_b200_matmul).
+ * By default the weight-gradient form (D = C in f32, beta = 1, M > 128) is NOT bit-reproducible
+ * from run to run (K slices meet in D through f32 atomics; every result is within the f32
+ * summation bound of every other); options->deterministic != 0 gives a fixed order at the cost
+ * of idle SMs on small outputs.  All other forms are always bit-reproducible. */
+int32_t cdl_b200_matmul_opt(const cdl_tensor* a, const cdl_tensor* b, const cdl_tensor* c,
+                            const cdl_tensor* d, float alpha, float beta,
+                            const cdl_matmul_options* options, void* scratch, size_t scratch_bytes,
+                            cdl_stream stream);
+/* Writes the valid choices for this problem to out[0 .. *count), the heuristic default first (the
+ * order Executor candidates have, op.rs:301-318); at most `capacity` entries, *count = how many
+ * exist.  Problems that take the general CUDA-core kernel have the single candidate AUTO. */
+int32_t cdl_b200_matmul_candidates(const cdl_tensor* a, const cdl_tensor* b, const cdl_tensor* d,
+                                   cdl_matmul_options* out, int32_t capacity, int32_t* count);
 /* GEMM with the SwiGLU activation fused into its epilogue, the counterparts of the reference's
  * sky_matmul_swiglu_gate_train_fwd and sky_matmul_swiglu_down_train_dgrad kernels
  * (crates/cleandl/rust-kernels/src/sky_matmul/tcgen05_bf16.rs:879-942, 944-1031, entry points
@@ -117,6 +161,11 @@ int32_t cdl_b200_matmul_scratch_bytes(const cdl_tensor* a, const cdl_tensor* b,
 int32_t cdl_b200_rmsnorm_fwd(const cdl_tensor* x, const cdl_tensor* scale, const cdl_tensor* bias,
                              float eps, const cdl_tensor* y, const cdl_tensor* r_inv,
                              cdl_stream stream);
+/* The same with the kernel form chosen by the caller (NULL options = the call above). */
+int32_t cdl_b200_rmsnorm_fwd_opt(const cdl_tensor* x, const cdl_tensor* scale,
+                                 const cdl_tensor* bias, float eps, const cdl_tensor* y,
+                                 const cdl_tensor* r_inv, const cdl_norm_options* options,
+                                 cdl_stream stream);
 
 /* LayerNorm forward: NormFwd with NormType::LayerNorm (ops/norm/mod.rs:23-30; tests
  * crates/cleandl/tests/norm.rs:97-130): y = bf16((x - mean) * r_inv * scale + bias) with
@@ -139,6 +188,14 @@ int32_t cdl_b200_rmsnorm_bwd(const cdl_tensor* x, const cdl_tensor* dy,
                              const cdl_tensor* dscale, void* scratch, size_t scratch_bytes,
                              cdl_stream stream);
 int32_t cdl_b200_rmsnorm_bwd_scratch_bytes(int64_t rows, int64_t cols, size_t* bytes_out);
+/* The same with the kernel form chosen by the caller (NULL options = the heuristic: pipelined when
+ * a residual gradient is fused in, warp-per-row otherwise).  Both forms sum dscale in a fixed
+ * order and are bit-reproducible. */
+int32_t cdl_b200_rmsnorm_bwd_opt(const cdl_tensor* x, const cdl_tensor* dy,
+                                 const cdl_tensor* residual_dy, const cdl_tensor* scale,
+                                 const cdl_tensor* r_inv, const cdl_tensor* dx,
+                                 const cdl_tensor* dscale, const cdl_norm_options* options,
+                                 void* scratch, size_t scratch_bytes, cdl_stream stream);
 
 /* RMSNorm backward for callers that cannot supply scratch.  (No counterpart in the reference: its
  * engine always hands an executor a scratch slice.)  Some hosts of this library may not allocate
@@ -151,8 +208,10 @@ int32_t cdl_b200_rmsnorm_bwd_scratch_bytes(int64_t rows, int64_t cols, size_t* b
  *   - cols <= 2048 (what the built-in array can hold); larger problems return
  *     CDL_ERR_UNSUPPORTED and should use cdl_b200_rmsnorm_bwd;
  *   - it calls no cudaMalloc / cudaFree or any other allocating routine;
- *   - the first call on each device looks up the array's device address (once, under a lock);
- *     make that first call before starting any stream capture;
+ *   - the first call on each device looks up the array's device address (once, under a lock), and
+ *     the first call per device and per column class (<= 256, 512, 1024, 2048 columns) also sets
+ *     the kernel's shared-memory attribute; make those first calls before starting any stream
+ *     capture;
  *   - all calls on a device share the one array: calls that may overlap on the GPU (different
  *     streams) race on it and must be serialised by the caller.  Nothing needs clearing between
  *     calls, each call overwrites what it later reads. */
@@ -225,6 +284,11 @@ int32_t cdl_b200_rmsnorm_fwd_mx(const cdl_tensor* x, const cdl_tensor* scale, co
  * with K % 64 == 0; mixed formats are rejected like in the reference (:569-571). */
 int32_t cdl_b200_matmul_mx(const cdl_mx_tensor* a, const cdl_mx_tensor* b, const cdl_tensor* c,
                            const cdl_tensor* d, float alpha, float beta, cdl_stream stream);
+/* The same with the kernel variant chosen by the caller (NULL options = the call above; the
+ * block-scaled kernels are always bit-reproducible, `deterministic` is ignored). */
+int32_t cdl_b200_matmul_mx_opt(const cdl_mx_tensor* a, const cdl_mx_tensor* b, const cdl_tensor* c,
+                               const cdl_tensor* d, float alpha, float beta,
+                               const cdl_matmul_options* options, cdl_stream stream);
 
 /* The same product with a block-scaled output: MatmulOutput::BlockScaled { Mxfp8, dim }
  * (crates/cleandl/src/execgraph/ops/matmul.rs:826-834; test crates/cleandl/tests/matmul.rs:
@@ -296,12 +360,12 @@ int32_t cdl_b200_attn_bwd_packed_scratch_bytes(int64_t batch, int64_t max_seqlen
  * backward != 0 applies the inverse rotation (the gradient). */
 int32_t cdl_b200_rope(const cdl_tensor* x, const cdl_tensor* cos_sin, int32_t rot_heads,
                       int32_t seqlen, int32_t backward, cdl_stream stream);
-/* act = SiLU(gate) * up, packed bf16 tensors of equal size. */
 /* RoPE over a ragged batch: token t of sequence b (rows cu_seqlens[b] .. cu_seqlens[b + 1]) has
  * position t - cu_seqlens[b]; the table has one row per position; rows after the last sequence are
  * left untouched. */
 int32_t cdl_b200_rope_ragged(const cdl_tensor* x, const cdl_tensor* cos_sin, int32_t rot_heads,
                              const cdl_tensor* cu_seqlens, int32_t backward, cdl_stream stream);
+/* act = SiLU(gate) * up, packed bf16 tensors of equal size. */
 int32_t cdl_b200_swiglu_fwd(const cdl_tensor* gate, const cdl_tensor* up, const cdl_tensor* act,
                             cdl_stream stream);
 /* d_up = d_act * SiLU(gate);  d_gate = d_act * up * dSiLU(gate).  d_up may alias d_act. */
@@ -350,9 +414,14 @@ int32_t cdl_b200_adamw(float* master, void* replica_bf16, float* grad, float* m,
  * SwiGLU FFN with fused residual.  All tensors are packed row-major device buffers; tokens
  * T = batch * seqlen.  Weights are bf16 stored [in, out] (decoder.rs:166-173); gradients are
  * f32 and ACCUMULATED (parameter.rs:69-74).  head_dim must be 128. */
+typedef enum {
+  CDL_SKY1_DETERMINISTIC = 1 /* weight-gradient GEMMs with a fixed summation order
+                              * (cdl_matmul_options.deterministic for every product of the block) */
+} cdl_sky1_flags;
 typedef struct {
   int32_t batch, seqlen, hidden, heads, kv_heads, head_dim, ffn;
   float eps;
+  int32_t flags; /* bit set of cdl_sky1_flags; 0 = defaults */
 } cdl_sky1_config;
 typedef struct { /* bf16 */
   const void* norm1; /* [hidden] */

@@ -54,3 +54,46 @@ def test_host_validation_needs_no_gpu(cdl):
     x = L.CdlTensor(ptr=256, dtype=L.CDL_BF16, rank=3)
     st = L.lib.cdl_b200_rmsnorm_fwd(ctypes.byref(x), None, None, 1e-6, ctypes.byref(x), None, None)
     assert st == -1 and "2D" in L.last_error()
+
+
+def test_candidates_need_no_gpu_and_put_the_heuristic_first(cdl):
+    """cdl_b200_matmul_candidates only inspects shapes and layouts (what the reference's
+    Executor::candidates does, op.rs:301-318)."""
+    L = cdl._lib
+
+    def t(ptr, rows, cols, dtype=None, transposed=False):
+        x = L.CdlTensor(ptr=ptr, dtype=L.CDL_BF16 if dtype is None else dtype, rank=2)
+        x.shape[0], x.shape[1] = rows, cols
+        x.stride[0], x.stride[1] = (1, rows) if transposed else (cols, 1)
+        return x
+
+    buf = (L.CdlMatmulOptions * 8)()
+    n = ctypes.c_int32(0)
+    a, b, d = t(4096, 1024, 512), t(8192, 512, 256), t(1 << 20, 1024, 256)
+    L.check(L.lib.cdl_b200_matmul_candidates(ctypes.byref(a), ctypes.byref(b), ctypes.byref(d), buf, 8,
+                                             ctypes.byref(n)))
+    assert [(buf[i].variant, buf[i].deterministic) for i in range(n.value)] == [
+        (L.GEMM_CTA_PAIR, 0), (L.GEMM_ONE_CTA, 0)]
+    # the weight-gradient form (f32 output) adds the fixed-order variant of the pair kernel
+    a, d = t(4096, 512, 1024, transposed=True), t(1 << 20, 512, 256, dtype=L.CDL_F32)
+    b = t(8192, 1024, 256)
+    L.check(L.lib.cdl_b200_matmul_candidates(ctypes.byref(a), ctypes.byref(b), ctypes.byref(d), buf, 8,
+                                             ctypes.byref(n)))
+    assert [(buf[i].variant, buf[i].deterministic) for i in range(n.value)] == [
+        (L.GEMM_CTA_PAIR, 0), (L.GEMM_CTA_PAIR, 1), (L.GEMM_ONE_CTA, 0)]
+    # one 128-row slab: the one-CTA kernel is the default; unaligned operands: the general kernel
+    a, d = t(4096, 64, 512), t(1 << 20, 64, 256)
+    b = t(8192, 512, 256)
+    L.check(L.lib.cdl_b200_matmul_candidates(ctypes.byref(a), ctypes.byref(b), ctypes.byref(d), buf, 8,
+                                             ctypes.byref(n)))
+    assert buf[0].variant == L.GEMM_ONE_CTA
+    a = t(4098, 64, 512)
+    L.check(L.lib.cdl_b200_matmul_candidates(ctypes.byref(a), ctypes.byref(b), ctypes.byref(d), buf, 8,
+                                             ctypes.byref(n)))
+    assert n.value == 1 and buf[0].variant == L.GEMM_AUTO
+    # an unknown variant is rejected before any CUDA call
+    mo = L.CdlMatmulOptions(7, 0)
+    a = t(4096, 64, 512)
+    st = L.lib.cdl_b200_matmul_opt(ctypes.byref(a), ctypes.byref(b), None, ctypes.byref(d), 1.0, 0.0,
+                                   ctypes.byref(mo), None, 0, None)
+    assert st == -1 and "variant" in L.last_error()

@@ -5,6 +5,8 @@ atol * max|expected| + rtol * |expected| (:541-556) with (1e-2, 1e-2) for the bf
 (1e-4, 1e-3) for LSE and (2e-2, 2e-2) for bf16 gradients (:781-804); cases over masks, GQA and
 Sq != Sk (:836-866), fused-QKV slicing (:589-613), backward (:984-1032), rejections (:1035-1105).
 """
+import ctypes
+
 import numpy as np
 import pytest
 import torch
@@ -268,6 +270,32 @@ def test_packed_equals_dense_for_equal_lengths(cdl, gpu_ok):
     assert torch.equal(pdq.view(b, s, h, 128), ddq)
     assert torch.equal(pdk.view(b, s, h, 128), ddk)
     assert torch.equal(pdv.view(b, s, h, 128), ddv)
+
+
+def test_packed_sequence_longer_than_the_bound_is_cut_and_reported(cdl, gpu_ok):
+    """max_seqlen_q / max_seqlen_k size the grids and the backward's statistics scratch.  A
+    sequence longer than the bound must not make the backward read or write beyond that scratch:
+    it is cut at the bound and the device status word reports code 921.  The sequences within the
+    bound still get their exact gradients."""
+    sq = [128, 300]
+    q, k, v, do, cu_q, cu_k = make_packed(sq, sq, 2, 2)
+    qd, kd, vd, dod = q.cuda(), k.cuda(), v.cuda(), do.cuda()
+    ok = cdl.ops.AttentionOpts(causal=True, cu_seqlens_q=cu_q.cuda(), cu_seqlens_k=cu_k.cuda(),
+                               max_seqlen_q=300, max_seqlen_k=300)
+    fwd = cdl.ops.attention_fwd(qd, kd, vd, ok)
+    ref_dq, ref_dk, ref_dv = cdl.ops.attention_bwd(qd, kd, vd, fwd.out, dod, fwd.lse, ok)
+    assert cdl._lib.device_status() == 0
+    low = cdl.ops.AttentionOpts(causal=True, cu_seqlens_q=cu_q.cuda(), cu_seqlens_k=cu_k.cuda(),
+                                max_seqlen_q=128, max_seqlen_k=128)
+    # scratch sized exactly by the (too small) bound, followed by a guard region
+    n = ctypes.c_size_t(0)
+    cdl._lib.check(cdl._lib.lib.cdl_b200_attn_bwd_packed_scratch_bytes(2, 128, 2, ctypes.byref(n)))
+    buf = torch.full((n.value + 4096,), 0x5A, dtype=torch.uint8, device="cuda")
+    dq, dk, dv = cdl.ops.attention_bwd(qd, kd, vd, fwd.out, dod, fwd.lse, low, scratch=buf[:n.value])
+    assert cdl._lib.device_status() == 921
+    assert bool((buf[n.value:] == 0x5A).all()), "the backward wrote beyond its scratch"
+    s0 = slice(0, 128)  # the sequence that fits the bound
+    assert torch.equal(dq[s0], ref_dq[s0]) and torch.equal(dk[s0], ref_dk[s0]) and torch.equal(dv[s0], ref_dv[s0])
 
 
 def test_packed_rejections(cdl, gpu_ok):

@@ -126,6 +126,49 @@ def test_block_config4_full_size_vs_f32_on_device(cdl, gpu_ok):
         assert err(blk.grads[n], g_ref[n]) <= 2e-2, n
 
 
+def test_block_backward_in_two_phases_equals_whole_backward(cdl, gpu_ok):
+    """The data-parallel step runs the backward as phase 1 (FFN half) then phase 2 (attention half)
+    so that the FFN gradients can be reduced early.  With the fixed-summation-order option the two
+    halves must reproduce the one-call backward bit for bit: dx and all seven weight gradients.
+    (Without the option the weight gradients agree within the f32 summation bound, checked too.)"""
+    sky1 = cdl.sky1
+    dims = dict(batch=2, seqlen=512, hidden=512, heads=4, kv_heads=4, head_dim=128, ffn=1024)
+    gen = torch.Generator().manual_seed(9)
+    results = {}
+    for det in (True, False):
+        cfg = sky1.Sky1Config(deterministic=det, **dims)
+        params = sky1.init_params(cfg, seed=9, std=0.05)
+        x = torch.randn(cfg.tokens, cfg.hidden, generator=torch.Generator().manual_seed(10)).to(torch.bfloat16).cuda()
+        dy = torch.randn(cfg.tokens, cfg.hidden, generator=torch.Generator().manual_seed(11)).to(torch.bfloat16).cuda()
+        for split in (False, True):
+            blk = sky1.Sky1Block(cfg, params)
+            for g in blk.grads.values():
+                g.zero_()
+            blk.forward(x)
+            dx = torch.empty_like(x)
+            if split:
+                blk.backward(dy, dx, phase=1)
+                ffn_after_phase1 = {n: blk.grads[n].clone() for n in ("wdown", "wup", "wgate", "norm2")}
+                blk.backward(dy, dx, phase=2)
+                # phase 2 must not touch the gradients phase 1 declared final
+                for n, g in ffn_after_phase1.items():
+                    assert torch.equal(g, blk.grads[n]), n
+            else:
+                blk.backward(dy, dx)
+            torch.cuda.synchronize()
+            results[(det, split)] = (dx.clone(), {n: g.clone() for n, g in blk.grads.items()})
+    dx_a, g_a = results[(True, False)]
+    dx_b, g_b = results[(True, True)]
+    assert torch.equal(dx_a, dx_b)
+    for n in sky1.PARAM_NAMES:
+        assert torch.equal(g_a[n], g_b[n]), n
+    dx_c, g_c = results[(False, True)]
+    assert torch.equal(dx_a, dx_c)  # activations never depend on the K-slice order
+    for n in sky1.PARAM_NAMES:
+        scale = g_a[n].abs().max().item()
+        assert (g_a[n] - g_c[n]).abs().max().item() <= 1e-5 * scale + 1e-7, n
+
+
 def test_block_rejects_bad_arguments(cdl, gpu_ok):
     sky1 = cdl.sky1
     cfg = sky1.Sky1Config(batch=1, seqlen=128, hidden=256, heads=2, kv_heads=2, head_dim=64, ffn=256)

@@ -1,8 +1,9 @@
-"""Data-parallel recipe on CPU with gloo, world size 2: every rank scales its loss by
+"""The data-parallel RECIPE on CPU with gloo, world size 2: every rank scales its loss by
 1 / GLOBAL token count, gradients are summed with all_reduce, and the result equals the gradient
-of the mean loss over the whole batch on one rank.  This is the host-side logic of the N > 1 path
-(bench.py, Sky1LM._reduce); the arithmetic is the torch restatement (oracle/lm_ref.py), so no GPU
-is needed."""
+of the mean loss over the whole batch on one rank.  This checks the recipe the N > 1 path follows,
+with the torch restatement's arithmetic (oracle/lm_ref.py), so it needs no GPU; the product's own
+data-parallel code (Sky1LM._reduce, the communication stream, the split backward) is checked on
+GPUs by tests/test_dp_nccl.py and tests/test_block.py."""
 import os
 import socket
 import sys
@@ -65,7 +66,7 @@ def _worker(rank, world, port, out):
     dist.destroy_process_group()
 
 
-def test_two_rank_gradient_sum_equals_global_mean_gradient(tmp_path):
+def test_recipe_two_rank_gradient_sum_equals_global_mean_gradient(tmp_path):
     out = str(tmp_path / "dp.pt")
     mp.spawn(_worker, args=(2, _free_port(), out), nprocs=2, join=True)
     got = torch.load(out)

@@ -153,6 +153,35 @@ def test_deterministic(cdl, gpu_ok):
     assert torch.equal(d1, d2)
 
 
+def test_weight_gradient_form_summation_order_option(cdl, gpu_ok):
+    """D (f32) += A^T . B with a long contraction: by default the K slices meet in D through f32
+    atomics, so two runs agree only within the f32 summation bound; with the `deterministic`
+    option (cdl_matmul_options) two runs are bit-equal.  Both agree with the oracle, and every
+    candidate the library enumerates for the problem gives a result within tolerance."""
+    gen = torch.Generator().manual_seed(12)
+    x, dy = rand_bf16(gen, 8192, 512).cuda(), rand_bf16(gen, 8192, 768).cuda()
+    w0 = torch.randn(512, 768, generator=gen).cuda()
+    expected, bound = oracle.matmul(to_f32(x.T), to_f32(dy), to_f32(w0), 1.0, 1.0)
+    tol = oracle.matmul_tolerance(expected, bound, False)
+
+    def run(**kw):
+        w = w0.clone()
+        cdl.ops.matmul(x.T, dy, cdl.ops.MatmulOpts(out=torch.float32, c=w, beta=1.0, **kw), out=w)
+        return w
+
+    d1, d2 = run(deterministic=True), run(deterministic=True)
+    assert torch.equal(d1, d2)
+    assert_all_close("deterministic wgrad", to_f32(d1), expected, tol)
+    f1, f2 = run(), run()
+    assert_all_close("sliced wgrad", to_f32(f1), expected, tol)
+    assert (f1 - f2).abs().max().item() <= 1e-5 * float(np.abs(bound).max())
+    cands = cdl.ops.matmul_candidates(x.T, dy, w0)
+    assert cands[0] == (cdl._lib.GEMM_CTA_PAIR, False) and len(cands) >= 3
+    for variant, det in cands:
+        assert_all_close(f"candidate {variant} {det}", to_f32(run(variant=variant, deterministic=det)),
+                         expected, tol)
+
+
 def test_large_vs_f32_accumulated(cdl, gpu_ok):
     """A block-sized forward GEMM against a float32-accumulated torch product on the same GPU
     (the f64 oracle would take minutes at this size)."""

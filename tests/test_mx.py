@@ -420,17 +420,12 @@ def test_mx_edge_shapes(cdl, gpu_ok):
         d = cdl.mx.matmul_mx(qa, qb, out_dtype=torch.float32)
         assert_all_close(f"{m}x{k}x{n}", to_f32(d), expected, oracle.matmul_tolerance(expected, bound, False))
     # the one-CTA kernel is still reachable and agrees bit for bit with the pair kernel
-    import os
     a = torch.randn(512, 256, generator=gen).to(torch.bfloat16)
     b = torch.randn(256, 384, generator=gen).to(torch.bfloat16)
     qa, _ = cdl.mx.quantize(a.cuda(), rowwise=True)
     _, qb = cdl.mx.quantize(b.cuda(), rowwise=False, colwise=True)
     d_pair = cdl.mx.matmul_mx(qa, qb, out_dtype=torch.float32)
-    os.environ["CDL_B200_MX_GEMM"] = "single"
-    try:
-        d_single = cdl.mx.matmul_mx(qa, qb, out_dtype=torch.float32)
-    finally:
-        del os.environ["CDL_B200_MX_GEMM"]
+    d_single = cdl.mx.matmul_mx(qa, qb, out_dtype=torch.float32, variant=cdl._lib.GEMM_ONE_CTA)
     assert torch.equal(d_pair, d_single)
 
 
