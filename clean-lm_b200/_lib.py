@@ -2,9 +2,12 @@
 from __future__ import annotations
 
 import ctypes
+import os
 from pathlib import Path
 
-LIB_PATH = Path(__file__).resolve().parent / "libcleandl_b200.so"
+# The in-tree build; CLEANDL_B200_LIB names another build of the same sources (a variant made by
+# build.py with other tunable macros) for side-by-side measurements.
+LIB_PATH = Path(os.environ.get("CLEANDL_B200_LIB") or Path(__file__).resolve().parent / "libcleandl_b200.so")
 
 CDL_BF16, CDL_F32, CDL_I32 = 0, 1, 2
 
@@ -29,7 +32,11 @@ class CdlTensor(ctypes.Structure):
 
 
 class CdlAttnDesc(ctypes.Structure):
-    _fields_ = [("softmax_scale", ctypes.c_float), ("causal", ctypes.c_int32)]
+    _fields_ = [("softmax_scale", ctypes.c_float), ("causal", ctypes.c_int32),
+                ("variant", ctypes.c_int32)]
+
+
+ATTN_AUTO, ATTN_ONE_SHOT, ATTN_PERSISTENT = 0, 1, 2
 
 
 class CdlProfileRecord(ctypes.Structure):
@@ -126,6 +133,7 @@ SIGNATURES = {
                             ctypes.c_int32),
     "cdl_b200_matmul_candidates": ([_T, _T, _T, _MO, ctypes.c_int32, ctypes.POINTER(ctypes.c_int32)],
                                    ctypes.c_int32),
+    "cdl_b200_matmul_rope": ([_T, _T, _T, ctypes.c_int32, ctypes.c_int32, _T, _T, _vp], ctypes.c_int32),
     "cdl_b200_matmul_swiglu_gate": ([_T, _T, _T, _T, _T, _vp], ctypes.c_int32),
     "cdl_b200_matmul_swiglu_dgrad": ([_T, _T, _T, _T, _T, _T, _vp], ctypes.c_int32),
     "cdl_b200_matmul_scratch_bytes": ([_T, _T, _T, ctypes.POINTER(_sz)], ctypes.c_int32),

@@ -41,10 +41,22 @@ def _stale(out: Path, deps: list[Path]) -> bool:
     return any(d.stat().st_mtime > t for d in deps)
 
 
-def build(verbose: bool = False, force: bool = False) -> Path:
-    """Compiles every csrc/*.cu and links the shared library. Returns its path."""
+def build(verbose: bool = False, force: bool = False, defines: list[str] | None = None,
+          out: Path | None = None) -> Path:
+    """Compiles every csrc/*.cu and links the shared library. Returns its path.
+
+    `defines` (e.g. ["CDL_ATTN_POLY_MASK=0x1111u"]) and `out` build a variant with other values of
+    the tunable macros into another file (with its own object directory), for side-by-side timing;
+    the package loads the variant when CLEANDL_B200_LIB names it."""
     nvcc = _nvcc()
-    OBJ_DIR.mkdir(exist_ok=True)
+    global OBJ_DIR, LIB_PATH
+    flags = list(NVCC_FLAGS)
+    if defines or out:
+        out = Path(out or PKG_DIR / "libcleandl_b200_variant.so").resolve()
+        OBJ_DIR, LIB_PATH = out.parent / (out.stem + "_obj"), out
+        flags += [f"-D{d}" for d in (defines or [])]
+        force = True
+    OBJ_DIR.mkdir(parents=True, exist_ok=True)
     sources = sorted(CSRC.glob("*.cu"))
     headers = sorted(CSRC.glob("*.h")) + sorted(CSRC.glob("*.cuh")) + [
         PKG_DIR.parent / "include" / "cleandl_b200.h"
@@ -53,7 +65,7 @@ def build(verbose: bool = False, force: bool = False) -> Path:
     def compile_one(src: Path) -> Path:
         obj = OBJ_DIR / (src.stem + ".o")
         if force or _stale(obj, [src] + headers):
-            cmd = [nvcc, *NVCC_FLAGS, "-c", str(src), "-o", str(obj)]
+            cmd = [nvcc, *flags, "-c", str(src), "-o", str(obj)]
             if verbose:
                 cmd.insert(1, "-Xptxas=-v")
             r = subprocess.run(cmd, capture_output=True, text=True)
@@ -74,4 +86,7 @@ def build(verbose: bool = False, force: bool = False) -> Path:
 
 
 if __name__ == "__main__":
-    print(build(verbose="-v" in sys.argv, force="-f" in sys.argv))
+    args = sys.argv[1:]
+    out = args[args.index("-o") + 1] if "-o" in args else None
+    print(build(verbose="-v" in args, force="-f" in args, out=out,
+                defines=[a[2:] for a in args if a.startswith("-D")]))

@@ -18,6 +18,7 @@
 // softmax overlaps the other tile's MMAs.  TMEM: S0/P0 [0,128) S1/P1 [128,256) O0 [256,384)
 // O1 [384,512).
 #include "host.h"
+#include "ops.h"
 #include "ptx.cuh"
 
 #include <math.h>
@@ -105,6 +106,7 @@ __global__ void __launch_bounds__(THREADS, 1)
   Params p = p_in;
   int q_base = 0, k_base = 0, bt = b;
   if (p_in.cu_q != nullptr) {
+    grid_dep_wait();  // the sequence offsets may come from the previous kernel of the stream
     q_base = p_in.cu_q[b];
     p.Sq = p_in.cu_q[b + 1] - q_base;
     k_base = p_in.cu_k[b];
@@ -144,6 +146,8 @@ __global__ void __launch_bounds__(THREADS, 1)
   __syncthreads();
   tc_fence_after();
   const uint32_t tmem_base = bars->tmem_base;
+  grid_dep_wait();  // the set-up above overlaps the previous kernel's tail; global memory from here on
+  grid_dep_launch();
   // The control warps need few registers; hand theirs to the softmax warp groups, which hold a
   // whole 128-column row of scores per thread.
 
@@ -504,6 +508,16 @@ int32_t attn_fwd_execute(const cdl_attn_desc* desc, const cdl_tensor* q, const c
   p.status = device_status_ptr();
   if (!p.status) return fail(CDL_ERR_CUDA, "cannot resolve the device status word");
 
+  const int variant = desc->variant;
+  if (variant < CDL_ATTN_AUTO || variant > CDL_ATTN_PERSISTENT)
+    return fail(CDL_ERR_INVALID, "%s: unknown kernel variant %d", op, variant);
+  if (variant != CDL_ATTN_ONE_SHOT) {
+    ProfileScope ps(PROF_ATTN_FWD, 4.0 * B * H * Sq * Sk * D * (p.causal ? 0.5 : 1.0), stream);
+    return attn_fwd_persistent_launch(q, k, v, B, H, Hkv, Sq, Sk, p.causal != 0, p.scale_log2, p.o, p.o_sb,
+                                p.o_ss, p.o_sh, p.lse, p.lse_sb, p.lse_sh, p.lse_ss, nullptr, nullptr,
+                                Sk > 0, stream);
+  }
+
   CUtensorMap tq, tk, tv;
   if (Sk > 0) {
     CDL_CHECK(attn_encode_tmap(&tq, q));
@@ -521,7 +535,7 @@ int32_t attn_fwd_execute(const cdl_attn_desc* desc, const cdl_tensor* q, const c
             static_cast<unsigned>(B));
   // FLOP by the flash-attention convention: 4 B H Sq Sk D, halved for the causal mask.
   ProfileScope ps(PROF_ATTN_FWD, 4.0 * B * H * Sq * Sk * D * (p.causal ? 0.5 : 1.0), stream);
-  attn_fwd_kernel<<<grid, THREADS, SMEM_BYTES, stream>>>(tq, tk, tv, p);
+  CDL_CUDA(launch_pdl(attn_fwd_kernel, grid, dim3(THREADS), SMEM_BYTES, stream, tq, tk, tv, p));
   CDL_CUDA(cudaGetLastError());
   return CDL_OK;
 }
@@ -615,6 +629,17 @@ int32_t attn_fwd_packed_execute(const cdl_attn_desc* desc, const cdl_tensor* q, 
   p.status = device_status_ptr();
   if (!p.status) return fail(CDL_ERR_CUDA, "cannot resolve the device status word");
 
+  const int variant = desc->variant;
+  if (variant < CDL_ATTN_AUTO || variant > CDL_ATTN_PERSISTENT)
+    return fail(CDL_ERR_INVALID, "%s: unknown kernel variant %d", op, variant);
+  if (variant != CDL_ATTN_ONE_SHOT) {
+    const double mq = static_cast<double>(Tq) / B, mk = static_cast<double>(Tk) / B;
+    ProfileScope ps(PROF_ATTN_FWD, 4.0 * B * H * mq * mk * D * (p.causal ? 0.5 : 1.0), stream);
+    return attn_fwd_persistent_launch(&q4, &k4, &v4, B, H, Hkv, max_q, max_k, p.causal != 0, p.scale_log2, p.o,
+                                0, p.o_ss, p.o_sh, p.lse, 0, p.lse_sh, p.lse_ss, p.cu_q, p.cu_k, Tk > 0,
+                                stream);
+  }
+
   CUtensorMap tq, tk, tv;
   if (Tk > 0) {
     CDL_CHECK(attn_encode_tmap(&tq, &q4));
@@ -632,7 +657,7 @@ int32_t attn_fwd_packed_execute(const cdl_attn_desc* desc, const cdl_tensor* q, 
   // sequence had the mean length.
   const double mean_q = static_cast<double>(Tq) / B, mean_k = static_cast<double>(Tk) / B;
   ProfileScope ps(PROF_ATTN_FWD, 4.0 * B * H * mean_q * mean_k * D * (p.causal ? 0.5 : 1.0), stream);
-  attn_fwd_kernel<<<grid, THREADS, SMEM_BYTES, stream>>>(tq, tk, tv, p);
+  CDL_CUDA(launch_pdl(attn_fwd_kernel, grid, dim3(THREADS), SMEM_BYTES, stream, tq, tk, tv, p));
   CDL_CUDA(cudaGetLastError());
   return CDL_OK;
 }

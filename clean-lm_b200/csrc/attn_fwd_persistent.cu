@@ -1,0 +1,736 @@
+// Flash attention forward, persistent form: one CTA per SM walks work items of 256 query rows
+// (two 128-row tiles) of one (batch, head), longest first.
+//
+// Operator semantics as in attn_fwd.cu (AttentionFwd of the reference, crates/cleandl/src/execgraph/
+// ops/attention/mod.rs:353-363, 807-850; exec.rs:358-416).  The tile program is the one of
+// attn_fwd.cu (S = Q K^T into tensor memory, one softmax thread per row, P written back over S as
+// bf16, O += P V with A = P from tensor memory, the two tiles alternating on the tensor core);
+// what differs:
+//
+//   * Persistent CTAs.  Work items are ordered by the number of key blocks they see and dealt to
+//     the CTAs in a boustrophedon (within 3 % of a dynamic longest-first schedule for the shapes
+//     measured), so barrier set-up, the tensor-memory allocation and the first loads are paid
+//     once per SM instead of once per 256 rows, and the next item's Q, K and V arrive while the
+//     current item's last blocks are computed.
+//   * Exponentials on two pipes.  The 2 x 16384 exponentials of a step take 2048 clk of the MUFU
+//     pipe alone (16 per clk per SM), about as long as the step's four products.  A fixed share of
+//     every row's exponentials is evaluated on the FMA pipe with packed f32x2 arithmetic
+//     (exp2_poly2); scaling, row sums and the bf16 conversion are packed, the row maximum uses
+//     three-input max.
+//   * Lazy rescale.  O and the row sum are rescaled only when a row's maximum has grown by more
+//     than 2^8 since the value the exponentials are taken against (rare after a tile's first
+//     blocks), so the wait for the previous P V and the pass over O leave the common path.
+//     (Taking the exponentials speculatively against the old maximum, with the block's maximum
+//     computed alongside, was measured too: 7 % slower at B=8 S=2048, the re-take after a grown
+//     maximum costs more than the separate pass over the scores it saves.)
+//   * The MMA warp stays converged (one elected lane polls, issues and commits) and every wait
+//     sleeps in mbarrier.try_wait with a time hint instead of spinning next to the softmax warps
+//     of its scheduler partition.
+//
+// A CTA-pair version (tcgen05.mma.cta_group::2, M = 256 over two SMs, which issues at the full
+// 64 clk per K step where the one-CTA forms take ~112 / ~82) was built and measured first: correct,
+// but each key block then carries two cross-CTA hand-overs on its dependent chain (S ready ->
+// peer's softmax, peer's P ready -> leader's MMA warp), together 1100-1600 clk against the ~530
+// the faster products save, so the step took 4450-5000 clk and the one-CTA form is used.
+//
+// TMEM: S0/P0 [0,128) S1/P1 [128,256) O0 [256,384) O1 [384,512).
+#include "host.h"
+#include "ops.h"
+#include "ptx.cuh"
+
+#include <math.h>
+#include <string.h>
+
+#include <mutex>
+
+namespace cdl {
+namespace attn_fwd_ps {
+
+constexpr int D = 128;
+constexpr int BQ = 128;                    // rows per tile
+constexpr int BKV = 128;                   // keys per block
+constexpr int ROWS_PER_ITEM = 2 * BQ;      // two tiles
+constexpr int TILE_BYTES = 128 * 128 * 2;  // a 128 x 128 bf16 tile as two [128 rows][64 d] panels
+constexpr int PANEL_BYTES = TILE_BYTES / 2;
+constexpr int KV_STAGES = 2;
+constexpr int THREADS = 384;  // warp 0 TMA, warp 1 MMA, warps 2-3 idle, warps 4-11 softmax
+constexpr int TMEM_COLS = 512;
+constexpr float RESCALE_THRESHOLD = 8.0f;  // log2 units
+constexpr size_t SMEM_BYTES = 1024 + 2 * TILE_BYTES + 2 * KV_STAGES * TILE_BYTES + 512;
+static_assert(SMEM_BYTES <= 232448, "exceeds the 227 KiB of shared memory a CTA can opt in to");
+
+// Which of the 16 column pairs of every 32-column chunk take the polynomial instead of MUFU.
+#ifndef CDL_ATTN_POLY_MASK
+#define CDL_ATTN_POLY_MASK 0x4924u
+#endif
+constexpr uint32_t POLY_MASK = CDL_ATTN_POLY_MASK;
+
+// Timeline probe (builds with -DCDL_ATTN_PROBE only): CTA 0 stamps clock64 at the hand-over
+// points of its first 64 key blocks; cdl_attn_probe_read copies the stamps out.  Slots: 0-5 MMA
+// lane (P ready seen / P V issued / next Q K^T issued, per tile), 8-13 and 16-21 first softmax
+// thread of tile 0 / 1 (S seen, S in registers, max done, -, P stored, arrived), 24-31 arrival of
+// lane 0 of each of the 8 softmax warps.
+#ifdef CDL_ATTN_PROBE
+__device__ long long g_probe_items[16 * 16];  // [item of CTA 0][slot]
+#define CDL_PROBE_ITEM(k, slot)                                                            \
+  do {                                                                                     \
+    if (blockIdx.x == 0 && (k) < 16) g_probe_items[(k) * 16 + (slot)] = clock64();         \
+  } while (0)
+__device__ long long g_probe[64 * 32];
+#define CDL_PROBE(it, slot)                                                            \
+  do {                                                                                 \
+    if (blockIdx.x == 0 && (it) < 64u) g_probe[(it) * 32 + (slot)] = clock64();        \
+  } while (0)
+#else
+#define CDL_PROBE(it, slot) \
+  do {                      \
+  } while (0)
+#define CDL_PROBE_ITEM(k, slot) \
+  do {                          \
+  } while (0)
+#endif
+
+struct Params {
+  int B, H, Hkv, Sq, Sk;
+  int causal;
+  float scale_log2;  // softmax_scale * log2(e)
+  __nv_bfloat16* o;
+  long long o_sb, o_ss, o_sh;  // element strides of O [B, Sq, H, D]
+  float* lse;                  // [B, H, Sq] or nullptr
+  long long lse_sb, lse_sh, lse_ss;
+  const int* cu_q;  // packed layout (see attn_fwd.cu); nullptr: dense
+  const int* cu_k;
+  int num_q_blocks;  // ceil(Sq / 256)
+  int total_items;   // num_q_blocks * H * B
+  int* status;
+};
+
+struct Barriers {
+  uint64_t q_full[2], q_empty[2];
+  uint64_t k_full[KV_STAGES], k_empty[KV_STAGES], v_full[KV_STAGES], v_empty[KV_STAGES];
+  uint64_t s_full[2], p_ready[2], o_done[2];
+  uint32_t tmem_base;
+  int abort_word;
+};
+
+__device__ __forceinline__ float ex2(float x) {
+  float y;
+  asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+  return y;
+}
+
+// ---- packed f32x2 arithmetic (one issue slot for two lanes of work)
+__device__ __forceinline__ uint64_t pack2(float lo, float hi) {
+  uint64_t r;
+  asm("mov.b64 %0, {%1, %2};" : "=l"(r) : "f"(lo), "f"(hi));
+  return r;
+}
+__device__ __forceinline__ void unpack2(uint64_t v, float& lo, float& hi) {
+  asm("mov.b64 {%0, %1}, %2;" : "=f"(lo), "=f"(hi) : "l"(v));
+}
+__device__ __forceinline__ uint64_t fma2(uint64_t a, uint64_t b, uint64_t c) {
+  uint64_t d;
+  asm("fma.rn.f32x2 %0, %1, %2, %3;" : "=l"(d) : "l"(a), "l"(b), "l"(c));
+  return d;
+}
+__device__ __forceinline__ uint64_t add2(uint64_t a, uint64_t b) {
+  uint64_t d;
+  asm("add.rn.f32x2 %0, %1, %2;" : "=l"(d) : "l"(a), "l"(b));
+  return d;
+}
+__device__ __forceinline__ uint64_t sub2(uint64_t a, uint64_t b) {
+  uint64_t d;
+  asm("sub.rn.f32x2 %0, %1, %2;" : "=l"(d) : "l"(a), "l"(b));
+  return d;
+}
+__device__ __forceinline__ float max3(float a, float b, float c) {
+  float d;
+  asm("max.f32 %0, %1, %2, %3;" : "=f"(d) : "f"(a), "f"(b), "f"(c));
+  return d;
+}
+__device__ __forceinline__ uint32_t cvt_bf16x2(float lo, float hi) {
+  uint32_t r;
+  asm("cvt.rn.bf16x2.f32 %0, %1, %2;" : "=r"(r) : "f"(hi), "f"(lo));
+  return r;
+}
+// 2^x for two arguments <= 0 on the FMA / integer pipes (the scheme of exp2_poly in ptx.cuh):
+// n = round(x) read from the low mantissa bits of x + 1.5 * 2^23, a degree-3 polynomial for
+// 2^(x - n) on [-0.5, 0.5], n added to the exponent field.  Relative error 1.4e-4; arguments
+// below -126 (including -inf) give 2^-126.
+__device__ __forceinline__ void exp2_poly2(uint64_t x, float& r0, float& r1) {
+  float x0, x1;
+  unpack2(x, x0, x1);
+  const uint64_t xc = pack2(fmaxf(x0, -126.0f), fmaxf(x1, -126.0f));
+  const uint64_t magic = pack2(12582912.0f, 12582912.0f);
+  const uint64_t t = add2(xc, magic);
+  const uint64_t f = sub2(xc, sub2(t, magic));
+  uint64_t r = fma2(f, pack2(0.0551716685f, 0.0551716685f), pack2(0.2426111251f, 0.2426111251f));
+  r = fma2(r, f, pack2(0.6932609677f, 0.6932609677f));
+  r = fma2(r, f, pack2(0.9999280572f, 0.9999280572f));
+  float t0, t1, p0, p1;
+  unpack2(t, t0, t1);
+  unpack2(r, p0, p1);
+  r0 = __int_as_float(__float_as_int(p0) + (__float_as_int(t0) << 23));
+  r1 = __int_as_float(__float_as_int(p1) + (__float_as_int(t1) << 23));
+}
+
+// Number of 128-key blocks tile rows [r0, r0 + 128) need; 0 when the tile has no valid row.
+__device__ __forceinline__ int kv_blocks_for_tile(int Sq, int Sk, int causal, int r0) {
+  if (r0 >= Sq) return 0;
+  int max_key = Sk - 1;
+  if (causal) {
+    const int r_last = min(r0 + BQ - 1, Sq - 1);
+    max_key = min(max_key, r_last + Sk - Sq);
+  }
+  return max_key < 0 ? 0 : max_key / BKV + 1;
+}
+
+// The k-th work item of CTA `cid` out of `nc`: items are ordered longest first (last query block
+// first) and dealt in a boustrophedon, so every CTA gets a similar mix of long and short items.
+// Negative when the CTA has no k-th item (and then no later one either).
+__device__ __forceinline__ int item_of(int k, int cid, int nc, int total) {
+  if (static_cast<long long>(k) * nc >= total) return -1;
+  const int idx = k * nc + ((k & 1) ? nc - 1 - cid : cid);
+  return idx < total ? idx : -1;
+}
+
+// Per-sequence view of an item: head, lengths, row bases and block counts of the two tiles.
+struct View {
+  int h, b, Sq, Sk, q_base, k_base, bt, m0, n[2], n_max;
+};
+__device__ __forceinline__ View view_of(const Params& p, int idx) {
+  View v;
+  const int bh = p.H * p.B;
+  const int qb = p.num_q_blocks - 1 - idx / bh;
+  const int r = idx % bh;
+  v.h = r % p.H;
+  v.b = r / p.H;
+  v.Sq = p.Sq;
+  v.Sk = p.Sk;
+  v.q_base = 0;
+  v.k_base = 0;
+  v.bt = v.b;
+  if (p.cu_q != nullptr) {
+    // Packed layout: every sequence has its own lengths and its rows start at q_base / k_base of a
+    // single "batch" (bt = 0).  Rows a tile loads beyond its sequence belong to the next one (or
+    // are zero beyond the tensor): their scores are masked like keys beyond Sk, their outputs are
+    // not stored.
+    v.q_base = p.cu_q[v.b];
+    v.Sq = min(p.cu_q[v.b + 1] - v.q_base, p.Sq);
+    v.k_base = p.cu_k[v.b];
+    v.Sk = p.cu_k[v.b + 1] - v.k_base;
+    v.bt = 0;
+  }
+  v.m0 = qb * ROWS_PER_ITEM;
+  v.n[0] = kv_blocks_for_tile(v.Sq, v.Sk, p.causal, v.m0);
+  v.n[1] = kv_blocks_for_tile(v.Sq, v.Sk, p.causal, v.m0 + BQ);
+  v.n_max = max(v.n[0], v.n[1]);
+  return v;
+}
+
+__global__ void __launch_bounds__(THREADS, 1)
+    attn_fwd_persistent_kernel(const __grid_constant__ CUtensorMap tmap_q,
+                               const __grid_constant__ CUtensorMap tmap_k,
+                               const __grid_constant__ CUtensorMap tmap_v, const Params p_in) {
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) &
+                                             ~static_cast<uintptr_t>(1023));
+  uint8_t* s_q = smem;                               // 2 tiles
+  uint8_t* s_k = smem + 2 * TILE_BYTES;              // KV_STAGES tiles
+  uint8_t* s_v = s_k + KV_STAGES * TILE_BYTES;       // KV_STAGES tiles
+  Barriers* bars = reinterpret_cast<Barriers*>(s_v + KV_STAGES * TILE_BYTES);
+  volatile int* abort_word = &bars->abort_word;
+
+  const int warp = threadIdx.x >> 5;
+  const int lane = threadIdx.x & 31;
+  const int cid = blockIdx.x;
+  const int nc = gridDim.x;
+
+  if (threadIdx.x == 0) {
+    for (int i = 0; i < 2; ++i) {
+      mbar_init(&bars->q_full[i], 1);
+      mbar_init(&bars->q_empty[i], 1);
+      mbar_init(&bars->s_full[i], 1);
+      mbar_init(&bars->p_ready[i], 4);  // one arrival per softmax warp of the tile
+      mbar_init(&bars->o_done[i], 1);
+    }
+    for (int i = 0; i < KV_STAGES; ++i) {
+      mbar_init(&bars->k_full[i], 1);
+      mbar_init(&bars->k_empty[i], 1);
+      mbar_init(&bars->v_full[i], 1);
+      mbar_init(&bars->v_empty[i], 1);
+    }
+    bars->abort_word = 0;
+    fence_mbar_init();
+  }
+  if (warp == 1) {
+    tmem_alloc(&bars->tmem_base, TMEM_COLS);
+    tmem_relinquish();
+  }
+  if (warp == 0 && lane == 0) {
+    tma_prefetch_desc(&tmap_q);
+    tma_prefetch_desc(&tmap_k);
+    tma_prefetch_desc(&tmap_v);
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = bars->tmem_base;
+  grid_dep_wait();  // the set-up above overlaps the previous kernel's tail; global memory from here on
+  grid_dep_launch();
+
+  if (warp == 0) {
+    // ------------------------------------------------------------ TMA producer
+    setmaxnreg_dec<56>();
+    if (elect_one()) {
+      uint32_t kv_cnt = 0, q_cnt[2] = {0, 0};
+      bool ok = true;
+      for (int k = 0; ok; ++k) {
+        const int idx = item_of(k, cid, nc, p_in.total_items);
+        if (idx < 0) break;
+        const View v = view_of(p_in, idx);
+        const int kvh = v.h / (p_in.H / p_in.Hkv);
+        for (int t = 0; t < 2 && ok; ++t) {
+          if (v.n[t] == 0) continue;
+          // Q_t of the previous item is free once its last Q K^T has run
+          ok = mbar_wait(&bars->q_empty[t], (q_cnt[t] & 1) ^ 1, abort_word, 121);
+          if (!ok) break;
+          ++q_cnt[t];
+          mbar_arrive_expect_tx(&bars->q_full[t], TILE_BYTES);
+#pragma unroll
+          for (int dh = 0; dh < 2; ++dh)
+            tma_load_4d(s_q + t * TILE_BYTES + dh * PANEL_BYTES, &tmap_q, &bars->q_full[t], dh * 64,
+                        v.q_base + v.m0 + t * BQ, v.h, v.bt);
+        }
+        // The next item's Q can only be loaded once this item's last Q K^T has run; bring it into
+        // L2 now, so that load is short when its turn comes.
+        {
+          const int nidx = item_of(k + 1, cid, nc, p_in.total_items);
+          if (nidx >= 0) {
+            const View nv = view_of(p_in, nidx);
+            for (int t = 0; t < 2; ++t)
+              if (nv.n[t] > 0)
+                for (int dh = 0; dh < 2; ++dh)
+                  tma_prefetch_4d(&tmap_q, dh * 64, nv.q_base + nv.m0 + t * BQ, nv.h, nv.bt);
+          }
+        }
+        for (int j = 0; j < v.n_max && ok; ++j, ++kv_cnt) {
+          const int s = kv_cnt % KV_STAGES;
+          const uint32_t ph = (kv_cnt / KV_STAGES) & 1;
+          ok = mbar_wait(&bars->k_empty[s], ph ^ 1, abort_word, 122);
+          if (!ok) break;
+          mbar_arrive_expect_tx(&bars->k_full[s], TILE_BYTES);
+#pragma unroll
+          for (int dh = 0; dh < 2; ++dh)
+            tma_load_4d(s_k + s * TILE_BYTES + dh * PANEL_BYTES, &tmap_k, &bars->k_full[s], dh * 64,
+                        v.k_base + j * BKV, kvh, v.bt);
+          ok = mbar_wait(&bars->v_empty[s], ph ^ 1, abort_word, 123);
+          if (!ok) break;
+          mbar_arrive_expect_tx(&bars->v_full[s], TILE_BYTES);
+#pragma unroll
+          for (int dh = 0; dh < 2; ++dh)
+            tma_load_4d(s_v + s * TILE_BYTES + dh * PANEL_BYTES, &tmap_v, &bars->v_full[s], dh * 64,
+                        v.k_base + j * BKV, kvh, v.bt);
+        }
+      }
+    }
+  } else if (warp == 1) {
+    // ------------------------------------------------------------ MMA issuer
+    setmaxnreg_dec<56>();
+    {
+      // The whole warp walks the loop (so the address arithmetic is warp-uniform work) and one
+      // elected lane polls the barriers, issues and commits.
+      const bool el = elect_one();
+      const int el_lane = __ffs(__ballot_sync(0xffffffffu, el)) - 1;
+      auto wait_all = [&](uint64_t* bar, uint32_t parity, int code) -> bool {
+        int r = 1;
+        if (el) r = mbar_wait(bar, parity, abort_word, code) ? 1 : 0;
+        return __shfl_sync(0xffffffffu, r, el_lane) != 0;
+      };
+      const uint32_t idesc_qk = make_idesc_bf16(BQ, BKV, 0, 0);
+      const uint32_t idesc_pv = make_idesc_bf16(BQ, D, 0, 1);
+      // A descriptor costs one 32-bit add: low word per operand, constant high word (SBO 1024,
+      // version 1, 128-byte swizzle).
+      constexpr uint32_t DESC_HI = (1024u >> 4) | (1u << 14) | (2u << 29);
+      auto lo_of = [](uint32_t addr, uint32_t lbo) { return ((addr & 0x3FFFFu) >> 4) | ((lbo >> 4) << 16); };
+      auto desc = [&](uint32_t lo, uint32_t off) {
+        return (static_cast<uint64_t>(DESC_HI) << 32) | (lo + (off >> 4));
+      };
+      const uint32_t q_lo = lo_of(smem_u32(s_q), 16), k_lo = lo_of(smem_u32(s_k), 16);
+      const uint32_t v_lo = lo_of(smem_u32(s_v), PANEL_BYTES);
+      // S_t = Q_t K_j^T: 8 products of K = 16 over the two 64-wide d panels.
+      auto issue_qk = [&](int t, int stage) {
+        const uint32_t qa = q_lo + t * (TILE_BYTES >> 4), ka = k_lo + stage * (TILE_BYTES >> 4);
+        const uint32_t d = tmem_base + t * 128;
+        if (el) {
+#pragma unroll
+          for (int k = 0; k < D / 16; ++k) {
+            const uint32_t off = (k >> 2) * PANEL_BYTES + (k & 3) * 32;
+            umma_ss(d, desc(qa, off), desc(ka, off), idesc_qk, k != 0);
+          }
+          umma_commit(&bars->s_full[t]);
+        }
+        __syncwarp();
+      };
+      // O_t (+)= P_t V_j: A = P (bf16 pairs in TMEM), B = V, MN-major.
+      auto issue_pv = [&](int t, int stage, bool accumulate) {
+        const uint32_t va = v_lo + stage * (TILE_BYTES >> 4);
+        const uint32_t d = tmem_base + 256 + t * 128, a = tmem_base + t * 128;
+        const uint32_t acc = accumulate ? 1u : 0u;
+        if (el) {
+#pragma unroll
+          for (int k = 0; k < BKV / 16; ++k)
+            umma_ts(d, a + k * 8, desc(va, k * 2048), idesc_pv, k != 0 ? 1u : acc);
+          umma_commit(&bars->o_done[t]);
+        }
+        __syncwarp();
+      };
+      uint32_t kv_cnt = 0, q_cnt[2] = {0, 0}, p_cnt[2] = {0, 0};
+      bool ok = true;
+      for (int k = 0; ok; ++k) {
+        const int idx = item_of(k, cid, nc, p_in.total_items);
+        if (idx < 0) break;
+        const View v = view_of(p_in, idx);
+        if (v.n_max == 0) continue;
+        if (el) CDL_PROBE_ITEM(k, 0);  // MMA lane: item begins (slot 1: first Q K^T issued; 2: item ends)
+        // first key block of the item
+        {
+          const int s = kv_cnt % KV_STAGES;
+          const uint32_t ph = (kv_cnt / KV_STAGES) & 1;
+          for (int t = 0; t < 2 && ok; ++t) {
+            if (v.n[t] == 0) continue;
+            ok = wait_all(&bars->q_full[t], q_cnt[t] & 1, 221) && wait_all(&bars->k_full[s], ph, 222);
+            if (!ok) break;
+            ++q_cnt[t];
+            tc_fence_after();
+            issue_qk(t, s);
+            if (v.n[t] == 1 && el) umma_commit(&bars->q_empty[t]);
+          }
+          if (ok && el) umma_commit(&bars->k_empty[s]);
+          if (el) CDL_PROBE_ITEM(k, 1);
+          __syncwarp();
+        }
+        for (int j = 0; j < v.n_max && ok; ++j) {
+          const int s = (kv_cnt + j) % KV_STAGES, sn = (kv_cnt + j + 1) % KV_STAGES;
+          const uint32_t ph = ((kv_cnt + j) / KV_STAGES) & 1, phn = ((kv_cnt + j + 1) / KV_STAGES) & 1;
+          for (int t = 0; t < 2 && ok; ++t) {
+            if (j < v.n[t]) {
+              ok = wait_all(&bars->p_ready[t], p_cnt[t] & 1, 223) && wait_all(&bars->v_full[s], ph, 224);
+              if (!ok) break;
+              if (el) CDL_PROBE(kv_cnt + j, 3 * t);
+              tc_fence_after();
+              issue_pv(t, s, j > 0);
+              ++p_cnt[t];
+              if (el) CDL_PROBE(kv_cnt + j, 3 * t + 1);
+            }
+            if (j + 1 < v.n[t]) {
+              ok = wait_all(&bars->k_full[sn], phn, 225);
+              if (!ok) break;
+              tc_fence_after();
+              issue_qk(t, sn);
+              if (el) CDL_PROBE(kv_cnt + j, 3 * t + 2);
+              if (j + 2 == v.n[t] && el) umma_commit(&bars->q_empty[t]);  // the last reader of Q_t
+            }
+          }
+          if (!ok) break;
+          if (el) {
+            umma_commit(&bars->v_empty[s]);
+            if (j + 1 < v.n_max) umma_commit(&bars->k_empty[sn]);
+          }
+          __syncwarp();
+        }
+        kv_cnt += v.n_max;
+        if (el) CDL_PROBE_ITEM(k, 2);
+      }
+    }
+  } else if (warp < 4) {
+    setmaxnreg_dec<56>();
+  } else {
+    // ------------------------------------------------------------ softmax + epilogue
+    setmaxnreg_inc<224>();
+    const int t = (warp - 4) >> 2;  // query tile of this warp group
+    const int quad = warp & 3;      // TMEM lane quadrant
+    const int row_in_tile = quad * 32 + lane;
+    const uint32_t lane_addr = static_cast<uint32_t>(quad * 32) << 16;
+    const uint32_t t_s = tmem_base + lane_addr + t * 128;
+    const uint32_t t_o = tmem_base + lane_addr + 256 + t * 128;
+    const uint64_t scale2 = pack2(p_in.scale_log2, p_in.scale_log2);
+    const bool probe_thread = quad == 0 && lane == 0;
+    uint32_t s_cnt = 0, o_cnt = 0;  // phases of s_full[t] / o_done[t] this thread has passed
+    bool ok = true;
+
+    for (int k = 0; ok; ++k) {
+      const int idx = item_of(k, cid, nc, p_in.total_items);
+      if (idx < 0) break;
+      const View v = view_of(p_in, idx);
+      const int n_t = v.n[t];
+      const int tile_row0 = v.m0 + t * BQ;
+      const int row = tile_row0 + row_in_tile;
+      const bool row_ok = row < v.Sq;
+      // Last key this row may see.
+      const int key_limit = p_in.causal ? min(v.Sk - 1, row + v.Sk - v.Sq) : v.Sk - 1;
+      const int warp_first_row = tile_row0 + quad * 32;
+
+      float m_used = -INFINITY;  // max the exponentials are taken against (scaled, log2 domain)
+      float l = 0.f;
+      if (probe_thread) CDL_PROBE_ITEM(k, 4 + 4 * t);  // softmax: item begins (+1: last P handed over, +2: O final seen, +3: epilogue done)
+      for (int j = 0; j < n_t; ++j) {
+        if (!mbar_wait(&bars->s_full[t], s_cnt & 1, abort_word, 321)) {
+          ok = false;
+          break;
+        }
+        ++s_cnt;
+        if (probe_thread) CDL_PROBE(s_cnt - 1, 8 + 8 * t);
+        tc_fence_after();
+        uint32_t sr[4][32];
+#pragma unroll
+        for (int c = 0; c < 4; ++c) tmem_ld32(t_s + c * 32, sr[c]);
+        tmem_wait_ld();
+        if (probe_thread) CDL_PROBE(s_cnt - 1, 9 + 8 * t);
+        const int key0 = j * BKV;
+        // Warp-uniform: does any row of this warp see a masked key in this block?
+        const int warp_limit = p_in.causal ? warp_first_row + v.Sk - v.Sq : v.Sk - 1;
+        const bool need_mask = key0 + BKV - 1 > min(warp_limit, v.Sk - 1);
+        if (need_mask) {
+#pragma unroll
+          for (int c = 0; c < 4; ++c)
+#pragma unroll
+            for (int i = 0; i < 32; ++i)
+              if (key0 + c * 32 + i > key_limit) sr[c][i] = 0xff800000u;  // -inf
+        }
+        // Row max over the raw scores (four chains of three-input max), scaled afterwards: scale > 0.
+        auto row_max = [&]() -> float {
+          float mxa[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
+#pragma unroll
+          for (int c = 0; c < 4; ++c)
+#pragma unroll
+            for (int i = 0; i < 32; i += 8) {
+              mxa[0] = max3(mxa[0], __uint_as_float(sr[c][i]), __uint_as_float(sr[c][i + 1]));
+              mxa[1] = max3(mxa[1], __uint_as_float(sr[c][i + 2]), __uint_as_float(sr[c][i + 3]));
+              mxa[2] = max3(mxa[2], __uint_as_float(sr[c][i + 4]), __uint_as_float(sr[c][i + 5]));
+              mxa[3] = max3(mxa[3], __uint_as_float(sr[c][i + 6]), __uint_as_float(sr[c][i + 7]));
+            }
+          return fmaxf(fmaxf(mxa[0], mxa[1]), fmaxf(mxa[2], mxa[3])) * p_in.scale_log2;
+        };
+        // P = 2^(S * scale - m_eff) for the whole row: stored to TMEM chunk by chunk, the row sum
+        // returned.
+        auto exp_store = [&](float m_eff) -> float {
+          const uint64_t neg_m2 = pack2(-m_eff, -m_eff);
+          uint64_t sum2[2] = {0ull, 0ull};
+#pragma unroll
+          for (int c = 0; c < 4; ++c) {
+            uint32_t pk[16];
+#pragma unroll
+            for (int i = 0; i < 16; ++i) {
+              const float r0 = __uint_as_float(sr[c][2 * i]), r1 = __uint_as_float(sr[c][2 * i + 1]);
+              const uint64_t x = fma2(pack2(r0, r1), scale2, neg_m2);
+              float p0, p1;
+              if ((POLY_MASK >> i) & 1u) {
+                exp2_poly2(x, p0, p1);
+              } else {
+                float x0, x1;
+                unpack2(x, x0, x1);
+                p0 = ex2(x0);
+                p1 = ex2(x1);
+              }
+              sum2[i & 1] = add2(sum2[i & 1], pack2(p0, p1));
+              pk[i] = cvt_bf16x2(p0, p1);
+            }
+            tmem_st16(t_s + c * 16, pk);
+          }
+          float s0, s1, s2, s3;
+          unpack2(sum2[0], s0, s1);
+          unpack2(sum2[1], s2, s3);
+          return (s0 + s1) + (s2 + s3);
+        };
+        // Moves the reference maximum of the rows that grew to `mx` and rescales O and l for them
+        // (lazy rescale: only when a maximum grew by more than the threshold).
+        auto rescale = [&](float mx, bool grow) -> bool {
+          if (j > 0) {
+            // o_done has completed o_cnt + j phases once P V of block j - 1 is done
+            if (!mbar_wait(&bars->o_done[t], (o_cnt + j - 1) & 1, abort_word, 322)) return false;
+            tc_fence_after();
+            const float f = grow ? (m_used == -INFINITY ? 0.f : ex2(m_used - mx)) : 1.f;
+#pragma unroll
+            for (int c = 0; c < 4; ++c) {
+              uint32_t orow[32];
+              tmem_ld32(t_o + c * 32, orow);
+              tmem_wait_ld();
+#pragma unroll
+              for (int i = 0; i < 32; ++i) orow[i] = __float_as_uint(__uint_as_float(orow[i]) * f);
+              tmem_st32(t_o + c * 32, orow);
+            }
+            l *= f;
+          }
+          if (grow) m_used = mx;
+          return true;
+        };
+        const float mx = row_max();
+        const bool grow = mx > m_used + RESCALE_THRESHOLD || (m_used == -INFINITY && mx > -INFINITY);
+        if (__any_sync(0xffffffffu, grow) && !rescale(mx, grow)) {
+          ok = false;
+          break;
+        }
+        if (probe_thread) CDL_PROBE(s_cnt - 1, 10 + 8 * t);
+        const float sum = exp_store(m_used == -INFINITY ? 0.f : m_used);
+        l += sum;
+        tmem_wait_st();
+        if (probe_thread) CDL_PROBE(s_cnt - 1, 12 + 8 * t);
+        tc_fence_before();
+        // One arrival per warp: 128 arrivals on one barrier word are serialised (measured: about
+        // 500 clk between the last thread's arrive and the waiter's wake-up, against ~100 for four).
+        __syncwarp();
+        if (lane == 0) mbar_arrive(&bars->p_ready[t]);
+        if (probe_thread) CDL_PROBE(s_cnt - 1, 13 + 8 * t);
+        if (lane == 0) CDL_PROBE(s_cnt - 1, 24 + 4 * t + quad);
+      }
+      if (!ok) break;
+      if (probe_thread) CDL_PROBE_ITEM(k, 5 + 4 * t);
+
+      if (n_t > 0) {
+        if (!mbar_wait(&bars->o_done[t], (o_cnt + n_t - 1) & 1, abort_word, 323)) {
+          ok = false;
+          break;
+        }
+        o_cnt += n_t;
+        tc_fence_after();
+      }
+      if (probe_thread) CDL_PROBE_ITEM(k, 6 + 4 * t);
+      // A row that saw no key at all: the polynomial's 2^-126 floor must not pass for a sum.
+      if (m_used == -INFINITY) l = 0.f;
+      if (tile_row0 < v.Sq) {
+        const float inv_l = l > 0.f ? 1.f / l : 0.f;
+        __nv_bfloat16* orow_ptr =
+            p_in.o + v.bt * p_in.o_sb + static_cast<long long>(v.q_base + row) * p_in.o_ss + v.h * p_in.o_sh;
+#pragma unroll
+        for (int c = 0; c < 4; ++c) {
+          uint32_t orow[32];
+          if (n_t > 0) {
+            tmem_ld32(t_o + c * 32, orow);
+            tmem_wait_ld();
+          } else {
+#pragma unroll
+            for (int i = 0; i < 32; ++i) orow[i] = 0u;
+          }
+          if (row_ok) {
+#pragma unroll
+            for (int g = 0; g < 4; ++g) {
+              uint4 q;
+              q.x = cvt_bf16x2(__uint_as_float(orow[g * 8 + 0]) * inv_l, __uint_as_float(orow[g * 8 + 1]) * inv_l);
+              q.y = cvt_bf16x2(__uint_as_float(orow[g * 8 + 2]) * inv_l, __uint_as_float(orow[g * 8 + 3]) * inv_l);
+              q.z = cvt_bf16x2(__uint_as_float(orow[g * 8 + 4]) * inv_l, __uint_as_float(orow[g * 8 + 5]) * inv_l);
+              q.w = cvt_bf16x2(__uint_as_float(orow[g * 8 + 6]) * inv_l, __uint_as_float(orow[g * 8 + 7]) * inv_l);
+              *reinterpret_cast<uint4*>(orow_ptr + c * 32 + g * 8) = q;
+            }
+          }
+        }
+        if (row_ok && p_in.lse != nullptr) {
+          const float lse = l > 0.f ? (m_used + log2f(l)) * 0.6931471805599453f : -INFINITY;
+          p_in.lse[v.bt * p_in.lse_sb + v.h * p_in.lse_sh +
+                   static_cast<long long>(v.q_base + row) * p_in.lse_ss] = lse;
+        }
+      }
+      // The O columns are read: the next item's first P V (which overwrites them) is ordered after
+      // this through the p_ready arrival of that item's first block.
+      tc_fence_before();
+      if (probe_thread) CDL_PROBE_ITEM(k, 7 + 4 * t);
+    }
+  }
+
+  // ------------------------------------------------------------ tear-down
+  __syncwarp();
+  if (*abort_word != 0) {
+    const unsigned long long t0 = globaltimer_ns();
+    while (globaltimer_ns() - t0 < 200000ull) __nanosleep(1000);
+  }
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 1) {
+    tc_fence_after();
+    tmem_dealloc(tmem_base, TMEM_COLS);
+  }
+  if (threadIdx.x == 0 && *abort_word != 0) atomicExch(p_in.status, *abort_word);
+}
+
+}  // namespace attn_fwd_ps
+
+int32_t attn_encode_tmap_rows(CUtensorMap* out, const cdl_tensor* t, uint32_t box_rows);
+
+// Launches the persistent kernel for operands the caller has validated (q, k, v are
+// [B, S, heads, 128] views; the packed layout passes single-batch views and the cu_seqlens
+// pointers).
+int32_t attn_fwd_persistent_launch(const cdl_tensor* q, const cdl_tensor* k, const cdl_tensor* v,
+                                   long long B, long long H, long long Hkv, long long Sq, long long Sk,
+                                   bool causal, float scale_log2, __nv_bfloat16* o, long long o_sb,
+                                   long long o_ss, long long o_sh, float* lse, long long lse_sb,
+                                   long long lse_sh, long long lse_ss, const int* cu_q,
+                                   const int* cu_k, bool any_keys, cudaStream_t stream) {
+  using namespace attn_fwd_ps;
+  Params p;
+  p.B = static_cast<int>(B);
+  p.H = static_cast<int>(H);
+  p.Hkv = static_cast<int>(Hkv);
+  p.Sq = static_cast<int>(Sq);
+  p.Sk = static_cast<int>(Sk);
+  p.causal = causal ? 1 : 0;
+  p.scale_log2 = scale_log2;
+  p.o = o;
+  p.o_sb = o_sb;
+  p.o_ss = o_ss;
+  p.o_sh = o_sh;
+  p.lse = lse;
+  p.lse_sb = lse_sb;
+  p.lse_sh = lse_sh;
+  p.lse_ss = lse_ss;
+  p.cu_q = cu_q;
+  p.cu_k = cu_k;
+  p.num_q_blocks = static_cast<int>((Sq + ROWS_PER_ITEM - 1) / ROWS_PER_ITEM);
+  const long long items = static_cast<long long>(p.num_q_blocks) * H * B;
+  if (items > INT32_MAX) return fail(CDL_ERR_UNSUPPORTED, "attention_fwd: too many work items");
+  p.total_items = static_cast<int>(items);
+  p.status = device_status_ptr();
+  if (!p.status) return fail(CDL_ERR_CUDA, "cannot resolve the device status word");
+
+  CUtensorMap tq, tk, tv;
+  if (any_keys) {
+    CDL_CHECK(attn_encode_tmap_rows(&tq, q, 128));
+    CDL_CHECK(attn_encode_tmap_rows(&tk, k, 128));
+    CDL_CHECK(attn_encode_tmap_rows(&tv, v, 128));
+  } else {
+    // No keys at all: the kernel never touches the maps (every tile has zero blocks).
+    memset(&tq, 0, sizeof tq);
+    tk = tq;
+    tv = tq;
+  }
+
+  static std::once_flag attr_once[64];
+  int dev = 0;
+  CDL_CUDA(cudaGetDevice(&dev));
+  cudaError_t attr_err = cudaSuccess;
+  std::call_once(attr_once[dev & 63], [&] {
+    attr_err = cudaFuncSetAttribute(attn_fwd_persistent_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                    static_cast<int>(SMEM_BYTES));
+  });
+  if (attr_err != cudaSuccess)
+    return fail(CDL_ERR_CUDA, "cudaFuncSetAttribute failed: %s", cudaGetErrorString(attr_err));
+  const int grid = items < sm_count() ? static_cast<int>(items) : sm_count();
+  CDL_CUDA(launch_pdl(attn_fwd_persistent_kernel, dim3(grid), dim3(THREADS), SMEM_BYTES, stream, tq, tk, tv, p));
+  CDL_CUDA(cudaGetLastError());
+  return CDL_OK;
+}
+
+}  // namespace cdl
+
+#ifdef CDL_ATTN_PROBE
+extern "C" int32_t cdl_attn_probe_items_read(long long* out) {
+  return cudaMemcpyFromSymbol(out, cdl::attn_fwd_ps::g_probe_items, sizeof(cdl::attn_fwd_ps::g_probe_items)) ==
+                 cudaSuccess
+             ? 0
+             : -3;
+}
+extern "C" int32_t cdl_attn_probe_read(long long* out) {
+  return cudaMemcpyFromSymbol(out, cdl::attn_fwd_ps::g_probe, sizeof(cdl::attn_fwd_ps::g_probe)) == cudaSuccess
+             ? 0
+             : -3;
+}
+#endif

@@ -29,6 +29,8 @@ __global__ void __launch_bounds__(256)
     rope_kernel(__nv_bfloat16* __restrict__ x, long long token_stride, long long head_stride,
                 const float* __restrict__ cos_sin, long long tokens, int seqlen, int rot_heads,
                 int half_dim, float sign, const int* __restrict__ cu_seqlens, int num_seqs) {
+  grid_dep_wait();
+  grid_dep_launch();
   const int groups = half_dim / 8;  // 8-element groups per half
   const long long idx = static_cast<long long>(blockIdx.x) * 256 + threadIdx.x;
   const long long total = tokens * rot_heads * groups;
@@ -164,11 +166,11 @@ int32_t rope_ragged_execute(const cdl_tensor* x, const cdl_tensor* cos_sin, int3
   const long long total = tokens * rot_heads * (d / 16);
   if (total == 0) return CDL_OK;
   ProfileScope ps(PROF_ELEMENTWISE, static_cast<double>(total) * 64, stream);
-  elem::rope_kernel<<<static_cast<unsigned>((total + 255) / 256), 256, 0, stream>>>(
+  CDL_CUDA(launch_pdl(elem::rope_kernel, dim3(static_cast<unsigned>((total + 255) / 256)), dim3(256), 0, stream,
       static_cast<__nv_bfloat16*>(x->ptr), x->stride[0], x->stride[1],
       static_cast<const float*>(cos_sin->ptr), tokens, seqlen, rot_heads, static_cast<int>(d / 2),
       backward ? -1.0f : 1.0f, cu_seqlens ? static_cast<const int*>(cu_seqlens->ptr) : nullptr,
-      cu_seqlens ? static_cast<int>(cu_seqlens->shape[0] - 1) : 0);
+      cu_seqlens ? static_cast<int>(cu_seqlens->shape[0] - 1) : 0));
   CDL_CUDA(cudaGetLastError());
   return CDL_OK;
 }

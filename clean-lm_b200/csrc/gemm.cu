@@ -40,6 +40,10 @@ constexpr int THREADS = 320;  // warp 0 TMA, warp 1 MMA, warps 2-9 epilogue (two
 constexpr int EPI_WARPS = 8;
 constexpr int TMEM_COLS = 512;
 constexpr int RASTER_W = 8;  // N tiles per raster panel (upper bound; see Params::raster_w)
+// L2 budget for A plus one raster panel of B (see the raster_w computation on the host).
+#ifndef CDL_GEMM_RASTER_BUDGET_MB
+#define CDL_GEMM_RASTER_BUDGET_MB 96
+#endif
 constexpr size_t SMEM_BYTES = 1024 + STAGES * STAGE_BYTES + 256;
 
 struct Params {
@@ -64,6 +68,14 @@ struct Params {
   const __nv_bfloat16* aux1;
   __nv_bfloat16* out2;
   long long ld_aux0, ld_aux1, ld_out2;
+  // Epilogue mode 3, rotate-half RoPE on the heads (128 columns each) below rope_cols:
+  //   d[r, h 128 + i]      = x[i] cos(pos, i) - x[i + 64] sin(pos, i)
+  //   d[r, h 128 + i + 64] = x[i + 64] cos(pos, i) + x[i] sin(pos, i)        (i < 64)
+  // with x the product's row, pos = r % rope_seqlen, or r - cu_seqlens[b] for the sequence b that
+  // holds row r of a ragged batch; the table is f32 [positions, 128] = cos | sin.
+  const float* rope_table;
+  const int* rope_cu;  // cu_seqlens of a ragged batch (device), or nullptr
+  int rope_seqlen, rope_cols, rope_nseq;
   int* status;
 };
 
@@ -340,6 +352,71 @@ __device__ __forceinline__ void store_tile_rows(const Params& p, uint32_t t_row,
   }
 }
 
+// Epilogue of mode 3 for the calling warp: its 128 columns are one head.  The rotation pairs column
+// i with column i + 64, so the 32-column chunks are drained in pairs (0, 2) and (1, 3); heads at or
+// beyond rope_cols (the value heads of a fused qkv projection) are stored unrotated.
+__device__ __forceinline__ void store_tile_rows_rope(const Params& p, uint32_t t_row, int row,
+                                                     int col_base) {
+  if (col_base >= p.N) return;  // warp-uniform
+  const bool row_ok = row < p.M;
+  const bool rotate = col_base < p.rope_cols;  // warp-uniform
+  int pos = 0;
+  if (row_ok && rotate) {
+    if (p.rope_cu != nullptr) {
+      // ragged batch: the position restarts at every sequence; rows after the last sequence keep
+      // position 0 (they are padding)
+      int lo_i = 0, hi_i = p.rope_nseq;  // largest b with cu[b] <= row
+      while (hi_i - lo_i > 1) {
+        const int mid = (lo_i + hi_i) >> 1;
+        if (p.rope_cu[mid] <= row) lo_i = mid;
+        else hi_i = mid;
+      }
+      pos = row < p.rope_cu[p.rope_nseq] ? min(row - p.rope_cu[lo_i], p.rope_seqlen - 1) : 0;
+    } else {
+      pos = row % p.rope_seqlen;
+    }
+  }
+  const float* cs = p.rope_table + static_cast<long long>(pos) * 128;
+  __nv_bfloat16* dp = static_cast<__nv_bfloat16*>(p.d) + static_cast<long long>(row) * p.ldd + col_base;
+#pragma unroll 1
+  for (int pr = 0; pr < 2; ++pr) {
+    uint32_t lo[32], hi[32];
+    tmem_ld32(t_row + pr * 32, lo);
+    tmem_ld32(t_row + (pr + 2) * 32, hi);
+    tmem_wait_ld();
+    if (!row_ok) continue;
+    uint32_t olo[16], ohi[16];
+#pragma unroll
+    for (int g = 0; g < 8; ++g) {
+      float c[4] = {1.f, 1.f, 1.f, 1.f}, sn[4] = {0.f, 0.f, 0.f, 0.f};
+      if (rotate) {
+        const float4 cv = __ldg(reinterpret_cast<const float4*>(cs + pr * 32 + g * 4));
+        const float4 sv = __ldg(reinterpret_cast<const float4*>(cs + 64 + pr * 32 + g * 4));
+        c[0] = cv.x; c[1] = cv.y; c[2] = cv.z; c[3] = cv.w;
+        sn[0] = sv.x; sn[1] = sv.y; sn[2] = sv.z; sn[3] = sv.w;
+      }
+      float rl[4], rh[4];
+#pragma unroll
+      for (int e = 0; e < 4; ++e) {
+        const float l = p.alpha * __uint_as_float(lo[g * 4 + e]), h = p.alpha * __uint_as_float(hi[g * 4 + e]);
+        rl[e] = l * c[e] - h * sn[e];
+        rh[e] = h * c[e] + l * sn[e];
+      }
+      olo[g * 2] = pack_bf16x2(rl[0], rl[1]);
+      olo[g * 2 + 1] = pack_bf16x2(rl[2], rl[3]);
+      ohi[g * 2] = pack_bf16x2(rh[0], rh[1]);
+      ohi[g * 2 + 1] = pack_bf16x2(rh[2], rh[3]);
+    }
+#pragma unroll
+    for (int g = 0; g < 4; ++g) {
+      *reinterpret_cast<uint4*>(dp + pr * 32 + g * 8) =
+          make_uint4(olo[g * 4], olo[g * 4 + 1], olo[g * 4 + 2], olo[g * 4 + 3]);
+      *reinterpret_cast<uint4*>(dp + (pr + 2) * 32 + g * 8) =
+          make_uint4(ohi[g * 4], ohi[g * 4 + 1], ohi[g * 4 + 2], ohi[g * 4 + 3]);
+    }
+  }
+}
+
 __global__ void __launch_bounds__(THREADS, 1)
     gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmap_a,
                      const __grid_constant__ CUtensorMap tmap_b, const Params p) {
@@ -376,6 +453,10 @@ __global__ void __launch_bounds__(THREADS, 1)
   __syncthreads();
   tc_fence_after();
   const uint32_t tmem_base = bars->tmem_base;
+  // Everything above overlaps the tail of the previous kernel of the stream; operands are read
+  // (and outputs written) only from here on.
+  grid_dep_wait();
+  grid_dep_launch();
 
   if (warp == 0) {
     // ------------------------------------------------------------ TMA producer
@@ -462,8 +543,9 @@ __global__ void __launch_bounds__(THREADS, 1)
       const uint32_t acc_ph = (t >> 1) & 1;
       if (!mbar_wait(&bars->acc_full[acc], acc_ph, abort_word, 301)) break;
       tc_fence_after();
-      store_tile_rows(p, tmem_base + (static_cast<uint32_t>(quad * 32) << 16) + acc * BN + half * (BN / 2),
-                      b, tm * BM + quad * 32 + lane, tn * BN + half * (BN / 2));
+      const uint32_t t_row = tmem_base + (static_cast<uint32_t>(quad * 32) << 16) + acc * BN + half * (BN / 2);
+      if (p.epi_mode == 3) store_tile_rows_rope(p, t_row, tm * BM + quad * 32 + lane, tn * BN + half * (BN / 2));
+      else store_tile_rows(p, t_row, b, tm * BM + quad * 32 + lane, tn * BN + half * (BN / 2));
       tc_fence_before();
       __syncwarp();
       if (lane == 0) mbar_arrive(&bars->acc_empty[acc]);
@@ -557,6 +639,8 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(THREADS, 1)
   cluster_sync_all();  // both CTAs' barriers exist before anything signals across the pair
   tc_fence_after();
   const uint32_t tmem_base = bars->tmem_base;
+  grid_dep_wait();  // set-up above overlaps the previous kernel's tail; global memory from here on
+  grid_dep_launch();
 
   if (warp == 0) {
     // ------------------------------------------------------------ TMA producer (both CTAs)
@@ -656,9 +740,10 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(THREADS, 1)
       const uint32_t acc_ph = (t >> 1) & 1;
       if (!mbar_wait(&bars->acc_full[acc], acc_ph, abort_word, 311)) break;
       tc_fence_after();
-      store_tile_rows(p, tmem_base + (static_cast<uint32_t>(quad * 32) << 16) + acc * BN + half * (BN / 2),
-                      b, tm * PAIR_M + static_cast<int>(rank) * BM + quad * 32 + lane,
-                      tn * BN + half * (BN / 2));
+      const uint32_t t_row = tmem_base + (static_cast<uint32_t>(quad * 32) << 16) + acc * BN + half * (BN / 2);
+      const int row = tm * PAIR_M + static_cast<int>(rank) * BM + quad * 32 + lane;
+      if (p.epi_mode == 3) store_tile_rows_rope(p, t_row, row, tn * BN + half * (BN / 2));
+      else store_tile_rows(p, t_row, b, row, tn * BN + half * (BN / 2));
       tc_fence_before();
       __syncwarp();
       if (lane == 0) mbar_arrive_cluster(mapa_shared(smem_u32(&bars->acc_empty[acc]), 0));
@@ -735,13 +820,13 @@ static int32_t check_epi_operand(const char* name, const cdl_tensor* t, long lon
 int32_t matmul_execute(const cdl_tensor* a, const cdl_tensor* b, const cdl_tensor* c,
                        const cdl_tensor* d, float alpha, float beta, cudaStream_t stream,
                        const cdl_matmul_options* opts) {
-  return matmul_execute_epi(a, b, c, d, alpha, beta, 0, nullptr, nullptr, nullptr, stream, opts);
+  return matmul_execute_epi(a, b, c, d, alpha, beta, 0, nullptr, nullptr, nullptr, stream, opts, nullptr);
 }
 
 int32_t matmul_execute_epi(const cdl_tensor* a, const cdl_tensor* b, const cdl_tensor* c,
                            const cdl_tensor* d, float alpha, float beta, int epi_mode,
                            const cdl_tensor* aux0, const cdl_tensor* aux1, const cdl_tensor* out2,
-                           cudaStream_t stream, const cdl_matmul_options* opts) {
+                           cudaStream_t stream, const cdl_matmul_options* opts, const RopeEpilogue* rope) {
   using namespace gemm;
   const int variant = opts ? opts->variant : CDL_GEMM_AUTO;
   if (variant < CDL_GEMM_AUTO || variant > CDL_GEMM_CTA_PAIR)
@@ -846,7 +931,7 @@ int32_t matmul_execute_epi(const cdl_tensor* a, const cdl_tensor* b, const cdl_t
     // the panel is narrowed until A and the panel's B fit a budget of 96 MB.
     const double a_bytes = 2.0 * static_cast<double>(M) * K;
     const double b_panel = 2.0 * BN * static_cast<double>(K);
-    const double budget = 96.0 * 1024 * 1024;
+    const double budget = static_cast<double>(CDL_GEMM_RASTER_BUDGET_MB) * 1024 * 1024;
     int w = RASTER_W;
     if (a_bytes <= 0.75 * budget)
       while (w > 2 && a_bytes + w * b_panel > budget) --w;
@@ -876,7 +961,25 @@ int32_t matmul_execute_epi(const cdl_tensor* a, const cdl_tensor* b, const cdl_t
   p.aux0 = p.aux1 = nullptr;
   p.out2 = nullptr;
   p.ld_aux0 = p.ld_aux1 = p.ld_out2 = 0;
-  if (epi_mode != 0) {
+  p.rope_table = nullptr;
+  p.rope_cu = nullptr;
+  p.rope_seqlen = p.rope_cols = p.rope_nseq = 0;
+  if (epi_mode == 3) {
+    if (!rope || !rope->table || rope->seqlen <= 0 || rope->rot_cols < 0 || rope->rot_cols % 128 != 0 ||
+        rope->rot_cols > N || (rope->cu_seqlens != nullptr && rope->num_seqs <= 0))
+      return fail(CDL_ERR_INVALID, "matmul (RoPE epilogue): table, seqlen > 0 and rot_cols (a multiple of 128, "
+                  "at most N) are required");
+    if (r != 2 || use_c || d->dtype != CDL_BF16 || N % 128 != 0 || !p.d_vec ||
+        (reinterpret_cast<uintptr_t>(rope->table) & 15) != 0)
+      return fail(CDL_ERR_INVALID, "matmul (RoPE epilogue): rank 2, no C operand, bf16 output with 16-byte "
+                  "aligned rows, N %% 128 == 0 and a 16-byte aligned table are required");
+    p.epi_mode = 3;
+    p.rope_table = rope->table;
+    p.rope_cu = rope->cu_seqlens;
+    p.rope_seqlen = rope->seqlen;
+    p.rope_cols = rope->rot_cols;
+    p.rope_nseq = rope->num_seqs;
+  } else if (epi_mode != 0) {
     if (r != 2 || use_c || d->dtype != CDL_BF16 || N % 8 != 0 || !p.d_vec)
       return fail(CDL_ERR_INVALID,
                   "matmul (fused SwiGLU): rank 2, no C operand, bf16 output with 16-byte aligned rows "
@@ -901,7 +1004,7 @@ int32_t matmul_execute_epi(const cdl_tensor* a, const cdl_tensor* b, const cdl_t
     };
     bool w = al32(p.d, p.ldd, p.d_batch, dtype_size(d->dtype));
     if (use_c) w = w && al32(p.c, p.ldc, p.c_batch, dtype_size(c->dtype));
-    if (p.epi_mode != 0) {
+    if (p.epi_mode == 1 || p.epi_mode == 2) {
       w = w && al32(p.aux0, p.ld_aux0, 0, 2) && al32(p.out2, p.ld_out2, 0, 2);
       if (p.epi_mode == 2) w = w && al32(p.aux1, p.ld_aux1, 0, 2);
     }
@@ -970,10 +1073,11 @@ int32_t matmul_execute_epi(const cdl_tensor* a, const cdl_tensor* b, const cdl_t
   if (use_pair) {
     const long long units = static_cast<long long>(p.num_tiles) * p.split_k;
     const int clusters = units < max_clusters[dev & 63] ? static_cast<int>(units) : max_clusters[dev & 63];
-    gemm_bf16_pair_kernel<<<2 * clusters, THREADS, PAIR_SMEM_BYTES, stream>>>(tm_a, tm_b, p);
+    CDL_CUDA(launch_pdl(gemm_bf16_pair_kernel, dim3(2 * clusters), dim3(THREADS), PAIR_SMEM_BYTES, stream,
+                        tm_a, tm_b, p));
   } else {
     const int grid = p.num_tiles < sm_count() ? p.num_tiles : sm_count();
-    gemm_bf16_kernel<<<grid, THREADS, SMEM_BYTES, stream>>>(tm_a, tm_b, p);
+    CDL_CUDA(launch_pdl(gemm_bf16_kernel, dim3(grid), dim3(THREADS), SMEM_BYTES, stream, tm_a, tm_b, p));
   }
   CDL_CUDA(cudaGetLastError());
   return CDL_OK;
@@ -1036,14 +1140,33 @@ int32_t cdl_b200_matmul_swiglu_gate(const cdl_tensor* a, const cdl_tensor* b, co
                                     const cdl_tensor* gate_out, const cdl_tensor* act_out,
                                     cdl_stream stream) {
   return cdl::matmul_execute_epi(a, b, nullptr, gate_out, 1.0f, 0.0f, 1, up, nullptr, act_out,
-                                 static_cast<cudaStream_t>(stream));
+                                 static_cast<cudaStream_t>(stream), nullptr, nullptr);
+}
+
+int32_t cdl_b200_matmul_rope(const cdl_tensor* a, const cdl_tensor* b, const cdl_tensor* cos_sin,
+                             int32_t rot_heads, int32_t seqlen, const cdl_tensor* cu_seqlens,
+                             const cdl_tensor* d, cdl_stream stream) {
+  using namespace cdl;
+  const char* op = "matmul (RoPE epilogue)";
+  if (!cos_sin || cos_sin->rank != 2 || cos_sin->dtype != CDL_F32 || cos_sin->shape[1] != 128 ||
+      cos_sin->stride[1] != 1 || cos_sin->stride[0] != 128 || seqlen <= 0 || cos_sin->shape[0] < seqlen)
+    return fail(CDL_ERR_INVALID, "%s: cos_sin must be packed f32 [>= seqlen, 128] (head_dim 128)", op);
+  if (rot_heads < 0) return fail(CDL_ERR_INVALID, "%s: rot_heads must not be negative", op);
+  if (cu_seqlens && (cu_seqlens->rank != 1 || cu_seqlens->dtype != CDL_I32 || cu_seqlens->stride[0] != 1 ||
+                     cu_seqlens->shape[0] < 2))
+    return fail(CDL_ERR_INVALID, "%s: cu_seqlens must be a packed i32 vector of num_seqs + 1 entries", op);
+  RopeEpilogue rope{static_cast<const float*>(cos_sin->ptr), seqlen, rot_heads * 128,
+                    cu_seqlens ? static_cast<const int*>(cu_seqlens->ptr) : nullptr,
+                    cu_seqlens ? static_cast<int>(cu_seqlens->shape[0] - 1) : 0};
+  return matmul_execute_epi(a, b, nullptr, d, 1.0f, 0.0f, 3, nullptr, nullptr, nullptr,
+                            static_cast<cudaStream_t>(stream), nullptr, &rope);
 }
 
 int32_t cdl_b200_matmul_swiglu_dgrad(const cdl_tensor* a, const cdl_tensor* b, const cdl_tensor* gate,
                                      const cdl_tensor* up, const cdl_tensor* d_up_out,
                                      const cdl_tensor* d_gate_out, cdl_stream stream) {
   return cdl::matmul_execute_epi(a, b, nullptr, d_up_out, 1.0f, 0.0f, 2, gate, up, d_gate_out,
-                                 static_cast<cudaStream_t>(stream));
+                                 static_cast<cudaStream_t>(stream), nullptr, nullptr);
 }
 
 int32_t cdl_b200_matmul_scratch_bytes(const cdl_tensor* a, const cdl_tensor* b,

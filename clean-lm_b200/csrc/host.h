@@ -8,6 +8,7 @@
 #include <stdio.h>
 
 #include <string>
+#include <utility>
 
 #include "../../include/cleandl_b200.h"
 
@@ -50,6 +51,28 @@ constexpr int32_t TMAP_U8 = 100;
 int32_t encode_tmap(CUtensorMap* out, const void* base, int32_t dtype, int rank,
                     const uint64_t* dims, const uint64_t* strides_bytes, const uint32_t* box,
                     bool swizzle128);
+
+// Launches `kernel` with the programmatic-serialization attribute (see grid_dep_wait in ptx.cuh):
+// the kernel may begin before the previous kernel of the stream has finished and MUST call
+// grid_dep_wait() before its first access to global memory.  CDL_PDL=0 builds launch normally.
+#ifndef CDL_PDL
+#define CDL_PDL 1
+#endif
+template <typename... KArgs, typename... Args>
+inline cudaError_t launch_pdl(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem,
+                              cudaStream_t stream, Args&&... args) {
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = grid;
+  cfg.blockDim = block;
+  cfg.dynamicSmemBytes = smem;
+  cfg.stream = stream;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[0].val.programmaticStreamSerializationAllowed = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = CDL_PDL ? 1 : 0;
+  return cudaLaunchKernelEx(&cfg, kernel, static_cast<KArgs>(args)...);
+}
 
 // Opt-in per-launch timing (cdl_b200_profile_start / _stop).  When enabled, a launcher brackets
 // its kernel with two pre-created CUDA events on the launching stream; when disabled the scope

@@ -1,6 +1,8 @@
 // Internal C++ entry points of the operators (one per exec-graph node of the reference); the
 // extern "C" functions and the sky-1 block are thin layers over these.
 #pragma once
+#include <cuda_bf16.h>
+
 #include "host.h"
 
 namespace cdl {
@@ -11,12 +13,23 @@ int32_t matmul_execute(const cdl_tensor* a, const cdl_tensor* b, const cdl_tenso
 // gemm_general.cu: any strides, bf16 or f32 inputs, CUDA cores (operands already validated).
 int32_t matmul_general_execute(const cdl_tensor* a, const cdl_tensor* b, const cdl_tensor* c,
                                const cdl_tensor* d, float alpha, float beta, cudaStream_t stream);
+// Arguments of the RoPE epilogue (epi_mode 3): rotate-half RoPE on the heads (128 columns each)
+// below rot_cols of the product; position = row % seqlen, or the row's offset inside its sequence
+// of a ragged batch (cu_seqlens: num_seqs + 1 device entries).
+struct RopeEpilogue {
+  const float* table;  // f32 [positions, 128] = cos | sin
+  int seqlen;          // dense: sequence length; ragged: rows of the table
+  int rot_cols;
+  const int* cu_seqlens;
+  int num_seqs;
+};
 // epi_mode 1: d = product, out2 = SiLU(product) * aux0.  epi_mode 2: d = SiLU(aux0) * product,
-// out2 = product * aux1 * dSiLU(aux0).
+// out2 = product * aux1 * dSiLU(aux0).  epi_mode 3: d = RoPE(product), see RopeEpilogue.
 int32_t matmul_execute_epi(const cdl_tensor* a, const cdl_tensor* b, const cdl_tensor* c,
                            const cdl_tensor* d, float alpha, float beta, int epi_mode,
                            const cdl_tensor* aux0, const cdl_tensor* aux1, const cdl_tensor* out2,
-                           cudaStream_t stream, const cdl_matmul_options* opts = nullptr);
+                           cudaStream_t stream, const cdl_matmul_options* opts = nullptr,
+                           const RopeEpilogue* rope = nullptr);
 // norm_general.cu: any float types, strides and column counts (layer = 0 RmsNorm, 1 LayerNorm).
 int32_t norm_general_execute(int layer, const cdl_tensor* x, const cdl_tensor* scale,
                              const cdl_tensor* bias, float eps, const cdl_tensor* y,
@@ -35,6 +48,13 @@ int32_t rmsnorm_bwd_execute(const cdl_tensor* x, const cdl_tensor* dy, const cdl
 int32_t attn_fwd_execute(const cdl_attn_desc* desc, const cdl_tensor* q, const cdl_tensor* k,
                          const cdl_tensor* v, const cdl_tensor* o, const cdl_tensor* lse,
                          cudaStream_t stream);
+// attn_fwd_persistent.cu: the persistent forward for validated operands ([B, S, heads, 128] views).
+int32_t attn_fwd_persistent_launch(const cdl_tensor* q, const cdl_tensor* k, const cdl_tensor* v,
+                             long long B, long long H, long long Hkv, long long Sq, long long Sk,
+                             bool causal, float scale_log2, __nv_bfloat16* o, long long o_sb,
+                             long long o_ss, long long o_sh, float* lse, long long lse_sb,
+                             long long lse_sh, long long lse_ss, const int* cu_q, const int* cu_k,
+                             bool any_keys, cudaStream_t stream);
 size_t attn_bwd_scratch_bytes(long long B, long long Sq, long long H);
 int32_t attn_bwd_execute(const cdl_attn_desc* desc, const cdl_tensor* q, const cdl_tensor* k,
                          const cdl_tensor* v, const cdl_tensor* o, const cdl_tensor* d_o,

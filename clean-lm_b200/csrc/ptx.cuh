@@ -26,6 +26,17 @@ __device__ __forceinline__ unsigned long long globaltimer_ns() {
   return t;
 }
 
+// Programmatic dependent launch.  A kernel launched with the programmatic-serialization attribute
+// may start while its predecessor in the stream still runs: everything before grid_dep_wait() (the
+// set-up that touches no global memory: barrier init, tensor-memory allocation, descriptor
+// prefetch) overlaps the predecessor's tail; grid_dep_wait() returns once the predecessor grid has
+// completed and its writes are visible.  grid_dep_launch() lets the successor's CTAs be scheduled
+// as soon as this grid's CTAs free their SMs.  Both are no-ops for a normal launch.
+__device__ __forceinline__ void grid_dep_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+__device__ __forceinline__ void grid_dep_launch() {
+  asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+}
+
 __device__ __forceinline__ bool elect_one() {
   uint32_t pred;
   asm volatile(
@@ -71,6 +82,26 @@ __device__ __forceinline__ bool mbar_try_wait(uint64_t* bar, uint32_t parity) {
   return ok != 0;
 }
 
+// The same test with a suspend-time hint: the thread may sleep in hardware for up to `hint_ns`
+// and is woken when the phase completes, so a waiting thread does not compete for issue slots
+// with the warps that share its scheduler partition.
+__device__ __forceinline__ bool mbar_try_wait_hint(uint64_t* bar, uint32_t parity, uint32_t hint_ns) {
+  uint32_t ok;
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2, %3;\n\t"
+      "selp.u32 %0, 1, 0, p;\n\t}\n"
+      : "=r"(ok)
+      : "r"(smem_u32(bar)), "r"(parity), "r"(hint_ns)
+      : "memory");
+  return ok != 0;
+}
+
+// Suspend-time hint of the polling loop below, in nanoseconds (0: plain try_wait).
+#ifndef CDL_MBAR_HINT_NS
+#define CDL_MBAR_HINT_NS 20000
+#endif
+
 // Bounded wait.  `abort_word` is a CTA-shared int: non-zero means some role gave up; every
 // other waiter then returns at once.  Returns true when the phase completed.
 __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, volatile int* abort_word,
@@ -79,8 +110,9 @@ __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, volati
   unsigned long long t0 = globaltimer_ns();
   uint32_t spins = 0;
   while (true) {
-    if (mbar_try_wait(bar, parity)) return true;
-    if ((++spins & 63u) == 0) {
+    if (CDL_MBAR_HINT_NS ? mbar_try_wait_hint(bar, parity, CDL_MBAR_HINT_NS) : mbar_try_wait(bar, parity))
+      return true;
+    if ((++spins & (CDL_MBAR_HINT_NS ? 7u : 63u)) == 0) {
       if (*abort_word != 0) return false;
       if (globaltimer_ns() - t0 > WAIT_LIMIT_NS) {
         *abort_word = code;
@@ -113,6 +145,13 @@ __device__ __forceinline__ void tma_load_4d(void* smem_dst, const CUtensorMap* m
       " [%0], [%1, {%3, %4, %5, %6}], [%2];" ::"r"(smem_u32(smem_dst)),
       "l"(reinterpret_cast<uint64_t>(m)), "r"(smem_u32(bar)), "r"(c0), "r"(c1), "r"(c2), "r"(c3)
       : "memory");
+}
+// Prefetch of a 4-D box into L2 (no shared-memory destination, no completion to wait for).
+__device__ __forceinline__ void tma_prefetch_4d(const CUtensorMap* m, int c0, int c1, int c2, int c3) {
+  asm volatile("cp.async.bulk.prefetch.tensor.4d.L2.global.tile [%0, {%1, %2, %3, %4}];" ::"l"(
+                   reinterpret_cast<uint64_t>(m)),
+               "r"(c0), "r"(c1), "r"(c2), "r"(c3)
+               : "memory");
 }
 __device__ __forceinline__ void tma_store_4d(const CUtensorMap* m, const void* smem_src, int c0,
                                              int c1, int c2, int c3) {

@@ -60,6 +60,8 @@ __global__ void __launch_bounds__(FWD_THREADS, NCH <= 8 ? 4 : 1)
   const long long warp_global = static_cast<long long>(blockIdx.x) * warps_per_block + (threadIdx.x >> 5);
   const long long warp_stride = static_cast<long long>(gridDim.x) * warps_per_block;
   const float inv_cols = 1.0f / static_cast<float>(cols);
+  grid_dep_wait();
+  grid_dep_launch();
 
   for (long long row = warp_global; row < rows; row += warp_stride) {
     const __nv_bfloat16* xr = x + row * ldx;
@@ -125,6 +127,8 @@ __global__ void __launch_bounds__(FWD_THREADS, NCH <= 4 ? 4 : NCH <= 8 ? 3 : 1)
   const long long warp_global = static_cast<long long>(blockIdx.x) * warps_per_block + (threadIdx.x >> 5);
   const long long warp_stride = static_cast<long long>(gridDim.x) * warps_per_block;
   const float inv_cols = 1.0f / static_cast<float>(cols);
+  grid_dep_wait();
+  grid_dep_launch();
   for (long long row = warp_global; row < rows; row += warp_stride) {
     const __nv_bfloat16* xr = x + row * ldx;
     uint4 v[NCH];
@@ -219,6 +223,8 @@ __global__ void __launch_bounds__(PIPE_THREADS, 1)
     fence_mbar_init();
   }
   __syncthreads();
+  grid_dep_wait();
+  grid_dep_launch();
   if (warp == PIPE_CONSUMERS) {
     if (lane == 0) {
       for (int i = 0; i < n; ++i) {
@@ -312,6 +318,8 @@ __global__ void __launch_bounds__(BWD_THREADS, BWD_BLOCKS_PER_SM)
   float acc[DSCALE ? NCH * 8 : 1];
 #pragma unroll
   for (int i = 0; i < (DSCALE ? NCH * 8 : 1); ++i) acc[i] = 0.f;
+  grid_dep_wait();
+  grid_dep_launch();
 
   for (long long row = warp_global; row < rows; row += warp_stride) {
     const __nv_bfloat16* xr = x + row * ldx;
@@ -422,6 +430,8 @@ __global__ void __launch_bounds__(PIPE_THREADS, 1)
     *abort_word = 0;
     fence_mbar_init();
   }
+  grid_dep_wait();
+  grid_dep_launch();
   for (int i = threadIdx.x * 8; i < cols; i += PIPE_THREADS * 8)
     *reinterpret_cast<uint4*>(s_scale + i * 2) = __ldg(reinterpret_cast<const uint4*>(scale + i));
   __syncthreads();
@@ -535,6 +545,8 @@ __global__ void __launch_bounds__(128)
                        const float* __restrict__ r_inv, long long r_inv_stride,
                        float* __restrict__ partials, int rows, int cols) {
   const int col = blockIdx.x * 128 + threadIdx.x;
+  grid_dep_wait();
+  grid_dep_launch();
   if (col >= cols) return;
   float acc = 0.f;
   for (long long row = blockIdx.y; row < rows; row += gridDim.y)
@@ -553,6 +565,8 @@ __global__ void __launch_bounds__(256)
   const int cx = threadIdx.x & 31, rg = threadIdx.x >> 5;
   const int col = blockIdx.x * 32 + cx;
   float s0 = 0.f, s1 = 0.f;
+  grid_dep_wait();
+  grid_dep_launch();
   if (col < cols) {
     int b = rg;
     for (; b + 8 < num_partials; b += 16) {
@@ -635,7 +649,7 @@ static void launch_fwd(const cdl_tensor* x, const cdl_tensor* scale, const cdl_t
       cudaFuncSetAttribute(rmsnorm_fwd_pipe_kernel<NCH>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                            PIPE_RING_BYTES + 2 * 64 * static_cast<int>(sizeof(uint64_t)) + 16);
     });
-    rmsnorm_fwd_pipe_kernel<NCH><<<sm_count(), PIPE_THREADS, smem, stream>>>(
+    launch_pdl(rmsnorm_fwd_pipe_kernel<NCH>, dim3(sm_count()), dim3(PIPE_THREADS), smem, stream,
         static_cast<const __nv_bfloat16*>(x->ptr), x->stride[0],
         scale ? static_cast<const __nv_bfloat16*>(scale->ptr) : nullptr,
         bias ? static_cast<const __nv_bfloat16*>(bias->ptr) : nullptr,
@@ -648,7 +662,7 @@ static void launch_fwd(const cdl_tensor* x, const cdl_tensor* scale, const cdl_t
   const int warps = FWD_THREADS / 32;
   const long long want = (static_cast<long long>(rows) + warps - 1) / warps;
   const int grid = static_cast<int>(want < 1 ? 1 : (want > (1 << 24) ? (1 << 24) : want));
-  rmsnorm_fwd_kernel<NCH><<<grid, FWD_THREADS, 0, stream>>>(
+  launch_pdl(rmsnorm_fwd_kernel<NCH>, dim3(grid), dim3(FWD_THREADS), 0, stream,
       static_cast<const __nv_bfloat16*>(x->ptr), x->stride[0],
       scale ? static_cast<const __nv_bfloat16*>(scale->ptr) : nullptr,
       bias ? static_cast<const __nv_bfloat16*>(bias->ptr) : nullptr,
@@ -662,7 +676,7 @@ static void launch_bwd(const cdl_tensor* x, const cdl_tensor* dy, const cdl_tens
                        const cdl_tensor* scale, const cdl_tensor* r_inv, const cdl_tensor* dx,
                        float* partials, int grid, int rows, int cols, cudaStream_t stream) {
   const size_t smem = DSCALE ? static_cast<size_t>(cols) * sizeof(float) : 0;
-  rmsnorm_bwd_kernel<NCH, DSCALE><<<grid, BWD_THREADS, smem, stream>>>(
+  launch_pdl(rmsnorm_bwd_kernel<NCH, DSCALE>, dim3(grid), dim3(BWD_THREADS), smem, stream,
       static_cast<const __nv_bfloat16*>(x->ptr), x->stride[0],
       static_cast<const __nv_bfloat16*>(dy->ptr), dy->stride[0],
       res ? static_cast<const __nv_bfloat16*>(res->ptr) : nullptr, res ? res->stride[0] : 0,
@@ -686,7 +700,7 @@ static void launch_bwd_pipe(const cdl_tensor* x, const cdl_tensor* dy, const cdl
     cudaFuncSetAttribute(rmsnorm_bwd_pipe_kernel<NCH>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                          160 * 1024 + 4096 + 2 * 64 * static_cast<int>(sizeof(uint64_t)) + 16);
   });
-  rmsnorm_bwd_pipe_kernel<NCH><<<sm_count(), PIPE_THREADS, smem, stream>>>(
+  launch_pdl(rmsnorm_bwd_pipe_kernel<NCH>, dim3(sm_count()), dim3(PIPE_THREADS), smem, stream,
       static_cast<const __nv_bfloat16*>(x->ptr), x->stride[0],
       static_cast<const __nv_bfloat16*>(dy->ptr), dy->stride[0],
       res ? static_cast<const __nv_bfloat16*>(res->ptr) : nullptr, res ? res->stride[0] : 0,
@@ -732,7 +746,7 @@ static void launch_layernorm(const cdl_tensor* x, const cdl_tensor* scale, const
   const int warps = FWD_THREADS / 32;
   const long long want = (static_cast<long long>(rows) + warps - 1) / warps;
   const int grid = static_cast<int>(want > (1 << 24) ? (1 << 24) : want);
-  layernorm_fwd_kernel<NCH><<<grid, FWD_THREADS, 0, stream>>>(
+  launch_pdl(layernorm_fwd_kernel<NCH>, dim3(grid), dim3(FWD_THREADS), 0, stream,
       static_cast<const __nv_bfloat16*>(x->ptr), x->stride[0],
       scale ? static_cast<const __nv_bfloat16*>(scale->ptr) : nullptr,
       bias ? static_cast<const __nv_bfloat16*>(bias->ptr) : nullptr,
@@ -831,14 +845,15 @@ int32_t rmsnorm_bwd_execute(const cdl_tensor* x, const cdl_tensor* dy, const cdl
     else launch_bwd<32, false>(x, dy, res, scale, r_inv, dx, nullptr, grid, r, c, stream);
     num_partials = r < 256 ? r : 256;
     dim3 g((c + 127) / 128, num_partials);
-    dscale_cols_kernel<<<g, 128, 0, stream>>>(
+    launch_pdl(dscale_cols_kernel, g, dim3(128), 0, stream,
         static_cast<const __nv_bfloat16*>(x->ptr), x->stride[0],
         static_cast<const __nv_bfloat16*>(dy->ptr), dy->stride[0],
         static_cast<const float*>(r_inv->ptr), r_inv->stride[0], partials, r, c);
   }
   CDL_CUDA(cudaGetLastError());
-  dscale_finalize_kernel<<<(c + 31) / 32, 256, 0, stream>>>(
-      partials, num_partials, c, static_cast<float*>(dscale->ptr), dscale->stride[0]);
+  launch_pdl(dscale_finalize_kernel, dim3((c + 31) / 32), dim3(256), 0, stream,
+             static_cast<const float*>(partials), num_partials, c, static_cast<float*>(dscale->ptr),
+             static_cast<long long>(dscale->stride[0]));
   CDL_CUDA(cudaGetLastError());
   return CDL_OK;
 }

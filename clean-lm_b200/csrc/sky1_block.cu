@@ -213,16 +213,16 @@ int32_t sky1_block_fwd(const cdl_sky1_config* cfg, const cdl_sky1_weights* wt, c
   const cdl_tensor wdown = view2(wt->wdown, CDL_BF16, d.F, d.Hd);
   const cdl_tensor tout = view2(out, CDL_BF16, d.T, d.Hd);
   const long long table_rows = d.rg ? d.rg->max_seqlen : d.S;
-  const cdl_tensor cs = view2(rope_cos_sin, CDL_F32, table_rows, d.D);
   const cdl_attn_desc ad{0.0f, 1};
 
   CDL_CHECK(rmsnorm_fwd_execute(&tx, &g1, nullptr, cfg->eps, &th, nullptr, st));
-  CDL_CHECK(matmul_execute(&th, &wqkv, nullptr, &tqkv, 1.f, 0.f, st));
-  const cdl_tensor rv = rope_view(sv->qkv, d);
+  // qkv = h1 Wqkv with RoPE on the q and k heads applied in the GEMM's epilogue
+  const RopeEpilogue rope{rope_cos_sin, static_cast<int>(table_rows), static_cast<int>((d.H + d.Hkv) * d.D),
+                          d.rg ? d.rg->cu_seqlens : nullptr, d.rg ? d.rg->num_seqs : 0};
+  CDL_CHECK(matmul_execute_epi(&th, &wqkv, nullptr, &tqkv, 1.f, 0.f, 3, nullptr, nullptr, nullptr, st, nullptr,
+                               &rope));
   if (d.rg) {
     const cdl_tensor cu = cu_view(d);
-    CDL_CHECK(rope_ragged_execute(&rv, &cs, static_cast<int32_t>(d.H + d.Hkv),
-                                  static_cast<int32_t>(table_rows), &cu, 0, st));
     const cdl_tensor q = head_view_packed(sv->qkv, d, 0, d.H), k = head_view_packed(sv->qkv, d, d.H, d.Hkv),
                      v = head_view_packed(sv->qkv, d, d.H + d.Hkv, d.Hkv);
     const cdl_tensor ao = attn_view_packed(sv->attn, d), lse = lse_view_packed(sv->lse, d);
@@ -232,7 +232,6 @@ int32_t sky1_block_fwd(const cdl_sky1_config* cfg, const cdl_sky1_weights* wt, c
     CDL_CHECK(attn_fwd_packed_execute(&ad, &q, &k, &v, &cu, &cu, d.rg->max_seqlen, d.rg->max_seqlen,
                                       &ao, &lse, st));
   } else {
-    CDL_CHECK(rope_execute(&rv, &cs, static_cast<int32_t>(d.H + d.Hkv), static_cast<int32_t>(d.S), 0, st));
     const cdl_tensor q = head_view(sv->qkv, d, 0, d.H), k = head_view(sv->qkv, d, d.H, d.Hkv),
                      v = head_view(sv->qkv, d, d.H + d.Hkv, d.Hkv);
     const cdl_tensor ao = attn_view(sv->attn, d), lse = lse_view(sv->lse, d);

@@ -176,6 +176,7 @@ class AttentionOpts:
     cu_seqlens_k: Optional[torch.Tensor] = None
     max_seqlen_q: Optional[int] = None
     max_seqlen_k: Optional[int] = None
+    variant: int = _lib.ATTN_AUTO  # cdl_attn_desc.variant: the forward kernel (a tuner's choice)
 
     @property
     def packed(self) -> bool:
@@ -194,6 +195,7 @@ def _attn_desc(opts: AttentionOpts) -> CdlAttnDesc:
     d = CdlAttnDesc()
     d.softmax_scale = float(opts.softmax_scale) if opts.softmax_scale is not None else 0.0
     d.causal = 1 if opts.causal else 0
+    d.variant = int(opts.variant)
     return d
 
 

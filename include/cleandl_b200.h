@@ -144,6 +144,15 @@ int32_t cdl_b200_matmul_swiglu_gate(const cdl_tensor* a, const cdl_tensor* b, co
 int32_t cdl_b200_matmul_swiglu_dgrad(const cdl_tensor* a, const cdl_tensor* b, const cdl_tensor* gate,
                                      const cdl_tensor* up, const cdl_tensor* d_up_out,
                                      const cdl_tensor* d_gate_out, cdl_stream stream);
+/* D = RoPE(A . B): the product (bf16 [M, N], N % 128 == 0, 16-byte aligned rows) with rotate-half
+ * RoPE applied in the epilogue to heads [0, rot_heads) of 128 columns of every row -- the fused
+ * QKV projection of the sky-1 block followed by its RoPE on the q and k heads
+ * (crates/sky-1/src/training/model/decoder.rs:350-378) in one kernel, without the extra pass over
+ * the qkv tensor.  cos_sin, seqlen, cu_seqlens (nullable: ragged batch) as for cdl_b200_rope /
+ * cdl_b200_rope_ragged; the row index is the token index. */
+int32_t cdl_b200_matmul_rope(const cdl_tensor* a, const cdl_tensor* b, const cdl_tensor* cos_sin,
+                             int32_t rot_heads, int32_t seqlen, const cdl_tensor* cu_seqlens,
+                             const cdl_tensor* d, cdl_stream stream);
 /* Scratch the call above needs for these operands (Executor::scratch_bytes, op.rs:132-135). */
 int32_t cdl_b200_matmul_scratch_bytes(const cdl_tensor* a, const cdl_tensor* b,
                                       const cdl_tensor* d, size_t* bytes_out);
@@ -306,9 +315,17 @@ int32_t cdl_b200_matmul_mx_out(const cdl_mx_tensor* a, const cdl_mx_tensor* b, c
  * fused QKV buffer are fine); o like q; lse f32 [B,H,Sq] (natural log; -inf for rows with no
  * visible key).  The causal mask is aligned to the bottom right: query i sees keys
  * j <= i + Sk - Sq (attention/mod.rs:24-31).  D = 128, H % Hkv == 0. */
+typedef enum {
+  CDL_ATTN_AUTO = 0,      /* the library's choice (the persistent kernel) */
+  CDL_ATTN_ONE_SHOT = 1,  /* forward: one short-lived CTA per 256 query rows */
+  CDL_ATTN_PERSISTENT = 2 /* forward: one CTA per SM walks the 256-row work items, longest first;
+                           * part of the exponentials on the FMA pipe */
+} cdl_attn_variant;
 typedef struct {
   float softmax_scale; /* <= 0 selects 1/sqrt(D) (exec.rs:198-200) */
   int32_t causal;      /* 0 = AttentionMask::None, 1 = AttentionMask::Causal */
+  int32_t variant;     /* cdl_attn_variant: a tuner's per-node choice for the forward (see "Per-call
+                        * kernel choices"); the backward ignores it.  0 = default. */
 } cdl_attn_desc;
 
 int32_t cdl_b200_attn_fwd(const cdl_attn_desc* desc, const cdl_tensor* q, const cdl_tensor* k,

@@ -47,14 +47,40 @@ FWD_CASES = [
     (2, 256, 320, 4, 2, False),    # dense (no mask), GQA
     (1, 1, 1, 1, 1, True),
     (1, 640, 640, 1, 1, True),
+    (3, 1100, 1100, 2, 2, True),   # five 256-row work items per head
+    (1, 1536, 700, 1, 1, True),    # sq > sk over several work items: the first of them see no key
+    (2, 520, 1300, 2, 1, False),   # dense, ragged in both directions
 ]
 
 
+@pytest.mark.parametrize("variant", [1, 2], ids=["one_shot", "persistent"])
 @pytest.mark.parametrize("b,sq,sk,hq,hk,causal", FWD_CASES)
-def test_fwd_cases(cdl, gpu_ok, b, sq, sk, hq, hk, causal):
+def test_fwd_cases(cdl, gpu_ok, b, sq, sk, hq, hk, causal, variant):
+    """Both forward kernels (cdl_attn_desc.variant: what a tuner enumerates) on every case."""
     q, k, v, _ = make(b, sq, sk, hq, hk)
-    out = cdl.ops.attention_fwd(q.cuda(), k.cuda(), v.cuda(), cdl.ops.AttentionOpts(causal=causal))
+    out = cdl.ops.attention_fwd(q.cuda(), k.cuda(), v.cuda(),
+                                cdl.ops.AttentionOpts(causal=causal, variant=variant))
     check_fwd(out, q, k, v, causal)
+
+
+def test_fwd_many_items_per_cluster(cdl, gpu_ok):
+    """More work items than SMs (the persistent kernel walks several items per CTA: rings,
+    barriers and tensor memory live across items): 4 x 40 heads x 4 query blocks = 640 items.  Run twice (bit-equal) and checked on three (batch, head) slices against the oracle
+    and everywhere against the one-CTA kernel."""
+    gen = torch.Generator().manual_seed(31)
+    q, k, v = (torch.randn(4, 1024, 40, 128, generator=gen).to(torch.bfloat16).cuda() for _ in range(3))
+    o1 = cdl.ops.attention_fwd(q, k, v)
+    o2 = cdl.ops.attention_fwd(q, k, v)
+    assert torch.equal(o1.out, o2.out) and torch.equal(o1.lse, o2.lse)
+    ref = cdl.ops.attention_fwd(q, k, v, cdl.ops.AttentionOpts(variant=cdl._lib.ATTN_ONE_SHOT))
+    assert (o1.out.float() - ref.out.float()).abs().max().item() <= 2e-2 * ref.out.float().abs().max().item()
+    assert (o1.lse - ref.lse).abs().max().item() <= 2e-3
+    for bi, hi in ((0, 0), (3, 39), (2, 17)):
+        sl = (slice(bi, bi + 1), slice(None), slice(hi, hi + 1))
+        r = oracle.attention(to_f32(q[sl]), to_f32(k[sl]), to_f32(v[sl]), None, causal=True)
+        assert_all_close("out", to_f32(o1.out[sl]), r["out"], oracle.attention_tolerance(r["out"], 1e-2, 1e-2))
+        assert_all_close("lse", to_f32(o1.lse[bi:bi + 1, hi:hi + 1]), r["lse"],
+                         oracle.attention_tolerance(r["lse"], 1e-4, 1e-3))
 
 
 def test_fwd_fused_qkv_views_and_scale(cdl, gpu_ok):

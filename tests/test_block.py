@@ -35,6 +35,53 @@ def test_rope_forward_backward(cdl, gpu_ok):
         assert torch.equal(dev[:, 4:].cpu(), x[:, 4:])  # heads beyond rot_heads are untouched
 
 
+@pytest.mark.parametrize("ragged", [False, True])
+def test_matmul_with_rope_epilogue(cdl, gpu_ok, ragged):
+    """cdl_b200_matmul_rope: the fused QKV projection with RoPE on the q and k heads applied in the
+    GEMM's epilogue (the call sites it fuses: decoder.rs:350-378), against the f64 product rotated
+    by the oracle; heads beyond rot_heads (v) must equal the plain product bit for bit."""
+    L = cdl._lib
+    gen = torch.Generator().manual_seed(12)
+    bsz, s, hidden, heads, rot = 2, 200, 256, 5, 3   # tokens 400: a partial 256-row tile
+    tokens = bsz * s
+    x = torch.randn(tokens, hidden, generator=gen).to(torch.bfloat16)
+    w = (torch.randn(hidden, heads * 128, generator=gen) * 0.1).to(torch.bfloat16)
+    if ragged:
+        lens = [130, 1, 200, 40]  # 371 tokens, then 29 rows of padding
+        cu = torch.tensor([0] + list(np.cumsum(lens)), dtype=torch.int32)
+        table = block_ref.rope_table(max(lens), 128)
+        seqlen = max(lens)
+    else:
+        cu, table, seqlen = None, block_ref.rope_table(s, 128), s
+    d = torch.empty(tokens, heads * 128, dtype=torch.bfloat16, device="cuda")
+    dev = [x.cuda(), w.cuda(), table.cuda(), cu.cuda() if ragged else None]  # kept alive for the call
+    args = [L.tensor_arg(t) for t in dev[:3]]
+    tcu = L.tensor_arg(dev[3]) if ragged else None
+    td = L.tensor_arg(d)
+    L.check(L.lib.cdl_b200_matmul_rope(L.ref(args[0]), L.ref(args[1]), L.ref(args[2]), rot, seqlen,
+                                       L.ref(tcu), L.ref(td), None))
+    torch.cuda.synchronize()
+    prod = (x.double() @ w.double()).view(tokens, heads, 128)
+    ref = prod.clone()
+    if ragged:
+        for b in range(len(lens)):
+            r0, r1 = int(cu[b]), int(cu[b + 1])
+            ref[r0:r1, :rot] = block_ref.rope(prod[None, r0:r1, :rot], table.double())[0]
+    else:
+        ref[:, :rot] = block_ref.rope(prod.view(bsz, s, heads, 128)[:, :, :rot], table.double()).reshape(tokens, rot, 128)
+    got = d.cpu().double().view(tokens, heads, 128)
+    tol = 2.0 ** -8 * ref.abs() + 1e-5 * (x.double().abs() @ w.double().abs()).view(tokens, heads, 128) * 2 + 1e-6
+    assert ((got - ref).abs() <= tol).all(), ((got - ref).abs() / tol).max()
+    plain = cdl.ops.matmul(x.cuda(), w.cuda()).view(tokens, heads, 128)
+    assert torch.equal(plain[:, rot:], d.view(tokens, heads, 128)[:, rot:])
+    with pytest.raises(cdl._lib.CdlError, match="RoPE epilogue"):
+        d2 = torch.empty(tokens, 200, dtype=torch.bfloat16, device="cuda")
+        w2_dev = w.cuda()[:, :200].contiguous()
+        w2 = L.tensor_arg(w2_dev)
+        td2 = L.tensor_arg(d2)
+        L.check(L.lib.cdl_b200_matmul_rope(L.ref(args[0]), L.ref(w2), L.ref(args[2]), 1, seqlen, None, L.ref(td2), None))
+
+
 def test_swiglu_forward_backward(cdl, gpu_ok):
     L = cdl._lib
     gen = torch.Generator().manual_seed(1)
