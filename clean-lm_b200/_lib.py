@@ -163,6 +163,11 @@ SIGNATURES = {
     "cdl_b200_attn_bwd_packed": ([ctypes.POINTER(CdlAttnDesc), _T, _T, _T, _T, _T, _T, _T, _T,
                                   ctypes.c_int64, ctypes.c_int64, _T, _T, _T, _vp, _sz, _vp],
                                  ctypes.c_int32),
+    "cdl_b200_attn_bwd_rope": ([ctypes.POINTER(CdlAttnDesc), _T, _T, _T, _T, _T, _T, _T, _T, _T, _T, _vp,
+                                _sz, _vp], ctypes.c_int32),
+    "cdl_b200_attn_bwd_packed_rope": ([ctypes.POINTER(CdlAttnDesc), _T, _T, _T, _T, _T, _T, _T, _T,
+                                       ctypes.c_int64, ctypes.c_int64, _T, _T, _T, _T, _vp, _sz, _vp],
+                                      ctypes.c_int32),
     "cdl_b200_attn_bwd_packed_scratch_bytes": ([ctypes.c_int64, ctypes.c_int64, ctypes.c_int64,
                                                 ctypes.POINTER(_sz)], ctypes.c_int32),
     "cdl_b200_rope": ([_T, _T, ctypes.c_int32, ctypes.c_int32, ctypes.c_int32, _vp], ctypes.c_int32),

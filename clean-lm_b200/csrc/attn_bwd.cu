@@ -81,6 +81,12 @@ struct Params {
   // with (Sq_pad pads that bound).  nullptr: dense layout.
   const int* cu_q;
   const int* cu_k;
+  // Rotary embedding folded into the dQ / dK stores: f32 [rope_rows, 128] = cos(64) | sin(64) per
+  // position (the position of a row is its index in its sequence), or nullptr.  q and k are then
+  // the rotated tensors the forward consumed and dQ / dK come out as gradients of the tensors
+  // before the rotation.
+  const float* rope;
+  int rope_rows;
   int* status;
 };
 
@@ -132,6 +138,44 @@ __device__ __forceinline__ void exp2_row64(const float (&x)[64], float (&y)[64])
 
 __device__ __forceinline__ void compute_bar_sync() {
   asm volatile("bar.sync 1, 256;" ::: "memory");
+}
+
+// Inverse rotary rotation of one staged dQ / dK row, in place of the transposed-rotation kernel
+// that would otherwise re-read the tensor: thread (wg, r) holds columns [64 wg, 64 wg + 64) of row
+// r, staged as bf16 in two 128-byte-swizzled panels of [128 rows][64 columns]; the rotation pairs
+// column i with column i + 64, i.e. with the same chunk of the other panel.  With x the staged
+// (bf16-rounded) values, out_lo = x_lo cos + x_hi sin and out_hi = x_hi cos - x_lo sin, evaluated
+// in f32 exactly as the stand-alone kernel does on the stored bf16 tensor.  The caller has
+// synchronised the compute threads after staging and synchronises again before the rows are
+// overwritten (this function only reads).
+__device__ __forceinline__ void rope_inverse_row(const uint8_t* stage, int wg, int r, const float* cs,
+                                                 uint4 (&out)[8]) {
+  const uint8_t* own = stage + wg * PANEL_BYTES + r * 128;
+  const uint8_t* other = stage + (1 - wg) * PANEL_BYTES + r * 128;
+  const float sign = wg == 0 ? 1.0f : -1.0f;
+#pragma unroll
+  for (int c = 0; c < 8; ++c) {
+    const int off = (c ^ (r & 7)) << 4;
+    const uint4 a = *reinterpret_cast<const uint4*>(own + off);
+    const uint4 b = *reinterpret_cast<const uint4*>(other + off);
+    const float4 c0 = __ldg(reinterpret_cast<const float4*>(cs + c * 8));
+    const float4 c1 = __ldg(reinterpret_cast<const float4*>(cs + c * 8 + 4));
+    const float4 s0 = __ldg(reinterpret_cast<const float4*>(cs + 64 + c * 8));
+    const float4 s1 = __ldg(reinterpret_cast<const float4*>(cs + 64 + c * 8 + 4));
+    const float cv[8] = {c0.x, c0.y, c0.z, c0.w, c1.x, c1.y, c1.z, c1.w};
+    const float sv[8] = {s0.x, s0.y, s0.z, s0.w, s1.x, s1.y, s1.z, s1.w};
+    const uint32_t aw[4] = {a.x, a.y, a.z, a.w}, bw[4] = {b.x, b.y, b.z, b.w};
+    uint32_t ow[4];
+#pragma unroll
+    for (int e = 0; e < 4; ++e) {
+      const float x0 = __uint_as_float(aw[e] << 16), x1 = __uint_as_float(aw[e] & 0xffff0000u);
+      const float y0 = __uint_as_float(bw[e] << 16), y1 = __uint_as_float(bw[e] & 0xffff0000u);
+      const float r0 = x0 * cv[2 * e] + y0 * (sv[2 * e] * sign);
+      const float r1 = x1 * cv[2 * e + 1] + y1 * (sv[2 * e + 1] * sign);
+      ow[e] = pack_bf16x2(r0, r1);
+    }
+    out[c] = make_uint4(ow[0], ow[1], ow[2], ow[3]);
+  }
 }
 
 // The issuing thread builds a descriptor with one 32-bit add: the low word (start address and
@@ -555,6 +599,7 @@ __global__ void __launch_bounds__(THREADS, 1)
         uint8_t* stage = s_q + which * TILE_BYTES;
         uint8_t* stage_row = stage + wg * PANEL_BYTES + r * 128;
         const uint32_t col = (which == 0 ? KV_COL_DV : KV_COL_DK) + wg * 64;
+        const bool rotate = which == 1 && p.rope != nullptr;
 #pragma unroll
         for (int half = 0; half < 2; ++half) {
           uint32_t a[32];
@@ -573,10 +618,24 @@ __global__ void __launch_bounds__(THREADS, 1)
             q.y = pack_bf16x2(__uint_as_float(a[g * 8 + 2]) * sc, __uint_as_float(a[g * 8 + 3]) * sc);
             q.z = pack_bf16x2(__uint_as_float(a[g * 8 + 4]) * sc, __uint_as_float(a[g * 8 + 5]) * sc);
             q.w = pack_bf16x2(__uint_as_float(a[g * 8 + 6]) * sc, __uint_as_float(a[g * 8 + 7]) * sc);
-            if (staged)
+            if (staged || rotate)
               *reinterpret_cast<uint4*>(stage_row + (((half * 4 + g) ^ (r & 7)) << 4)) = q;
             else if (row_ok)
               *reinterpret_cast<uint4*>(dst + half * 32 + g * 8) = q;
+          }
+        }
+        if (rotate) {
+          // dK of the keys before the rotary rotation: the staged rows are rotated back in place
+          uint4 rot[8];
+          compute_bar_sync();
+          rope_inverse_row(stage, wg, r, p.rope + static_cast<long long>(min(key, p.rope_rows - 1)) * 128, rot);
+          compute_bar_sync();
+#pragma unroll
+          for (int c = 0; c < 8; ++c) {
+            if (staged)
+              *reinterpret_cast<uint4*>(stage_row + ((c ^ (r & 7)) << 4)) = rot[c];
+            else if (row_ok)
+              *reinterpret_cast<uint4*>(dst + c * 8) = rot[c];
           }
         }
         if (staged) {
@@ -866,6 +925,7 @@ __global__ void __launch_bounds__(THREADS, 1)
       const bool staged = p.cu_q == nullptr || q0 + BQ <= p.Sq;
       __nv_bfloat16* dst = p.dq + bt * p.dq_sb + static_cast<long long>(q_base + row) * p.dq_ss + h * p.dq_sh + wg * 64;
       uint8_t* stage_row = s_k + wg * PANEL_BYTES + r * 128;
+      const bool rotate = p.rope != nullptr;
 #pragma unroll
       for (int half = 0; half < 2; ++half) {
         uint32_t a[32];
@@ -884,10 +944,24 @@ __global__ void __launch_bounds__(THREADS, 1)
           q.y = pack_bf16x2(__uint_as_float(a[g * 8 + 2]) * sc, __uint_as_float(a[g * 8 + 3]) * sc);
           q.z = pack_bf16x2(__uint_as_float(a[g * 8 + 4]) * sc, __uint_as_float(a[g * 8 + 5]) * sc);
           q.w = pack_bf16x2(__uint_as_float(a[g * 8 + 6]) * sc, __uint_as_float(a[g * 8 + 7]) * sc);
-          if (staged)
+          if (staged || rotate)
             *reinterpret_cast<uint4*>(stage_row + (((half * 4 + g) ^ (r & 7)) << 4)) = q;
           else if (row < p.Sq)
             *reinterpret_cast<uint4*>(dst + half * 32 + g * 8) = q;
+        }
+      }
+      if (rotate) {
+        // dQ of the queries before the rotary rotation (see rope_inverse_row)
+        uint4 rot[8];
+        compute_bar_sync();
+        rope_inverse_row(s_k, wg, r, p.rope + static_cast<long long>(min(row, p.rope_rows - 1)) * 128, rot);
+        compute_bar_sync();
+#pragma unroll
+        for (int c = 0; c < 8; ++c) {
+          if (staged)
+            *reinterpret_cast<uint4*>(stage_row + ((c ^ (r & 7)) << 4)) = rot[c];
+          else if (row < p.Sq)
+            *reinterpret_cast<uint4*>(dst + c * 8) = rot[c];
         }
       }
       if (staged) {
@@ -997,11 +1071,27 @@ static int32_t bwd_run(const attn_bwd::Params& p, const cdl_tensor* q, const cdl
   return CDL_OK;
 }
 
+// The rotary table of the fused inverse rotation: f32 [rows, 128] contiguous, one row per position.
+static int32_t check_rope_table(const char* op, const cdl_tensor* t, long long min_rows, attn_bwd::Params* p) {
+  p->rope = nullptr;
+  p->rope_rows = 0;
+  if (t == nullptr) return CDL_OK;
+  if (t->rank != 2 || t->dtype != CDL_F32 || t->shape[1] != 128 || t->stride[1] != 1 || t->stride[0] != 128 ||
+      t->ptr == nullptr || (reinterpret_cast<uintptr_t>(t->ptr) & 15) != 0)
+    return fail(CDL_ERR_INVALID, "%s: the rotary table must be contiguous f32 [positions, 128], 16-byte aligned", op);
+  if (t->shape[0] < min_rows)
+    return fail(CDL_ERR_INVALID, "%s: the rotary table has %lld positions, the longest sequence %lld", op,
+                static_cast<long long>(t->shape[0]), min_rows);
+  p->rope = static_cast<const float*>(t->ptr);
+  p->rope_rows = static_cast<int>(t->shape[0]);
+  return CDL_OK;
+}
+
 int32_t attn_bwd_execute(const cdl_attn_desc* desc, const cdl_tensor* q, const cdl_tensor* k,
                          const cdl_tensor* v, const cdl_tensor* o, const cdl_tensor* d_o,
                          const cdl_tensor* lse, const cdl_tensor* dq, const cdl_tensor* dk,
                          const cdl_tensor* dv, void* scratch, size_t scratch_bytes,
-                         cudaStream_t stream) {
+                         cudaStream_t stream, const cdl_tensor* rope_table) {
   using namespace attn_bwd;
   const char* op = "attention_bwd";
   if (!desc || !q || !k || !v || !o || !d_o || !lse || !dq || !dk || !dv)
@@ -1062,6 +1152,7 @@ int32_t attn_bwd_execute(const cdl_attn_desc* desc, const cdl_tensor* q, const c
 
   p.cu_q = nullptr;
   p.cu_k = nullptr;
+  CDL_CHECK(check_rope_table(op, rope_table, Sq > Sk ? Sq : Sk, &p));
   // 14 B H Sq Sk D with the recomputed S and dP of the dQ kernel; reported as the conventional
   // 10 B H Sq Sk D (2.5 x forward), halved for the causal mask.
   return bwd_run(p, q, k, v, o, d_o, static_cast<const float*>(lse->ptr), lse->stride[0],
@@ -1078,7 +1169,8 @@ int32_t attn_bwd_packed_execute(const cdl_attn_desc* desc, const cdl_tensor* q, 
                                 const cdl_tensor* lse, const cdl_tensor* cu_q, const cdl_tensor* cu_k,
                                 long long max_q, long long max_k, const cdl_tensor* dq,
                                 const cdl_tensor* dk, const cdl_tensor* dv, void* scratch,
-                                size_t scratch_bytes, cudaStream_t stream) {
+                                size_t scratch_bytes, cudaStream_t stream,
+                                const cdl_tensor* rope_table) {
   using namespace attn_bwd;
   const char* op = "attention_bwd (packed)";
   if (!desc || !q || !k || !v || !o || !d_o || !lse || !dq || !dk || !dv || !cu_q || !cu_k)
@@ -1138,6 +1230,7 @@ int32_t attn_bwd_packed_execute(const cdl_attn_desc* desc, const cdl_tensor* q, 
   p.dv_sb = 0; p.dv_ss = dv->stride[0]; p.dv_sh = dv->stride[1];
   p.cu_q = static_cast<const int*>(cu_q->ptr);
   p.cu_k = static_cast<const int*>(cu_k->ptr);
+  CDL_CHECK(check_rope_table(op, rope_table, max_q > max_k ? max_q : max_k, &p));
   p.status = device_status_ptr();
   if (!p.status) return fail(CDL_ERR_CUDA, "cannot resolve the device status word");
   const double mean_q = static_cast<double>(Tq) / B, mean_k = static_cast<double>(Tk) / B;
@@ -1158,7 +1251,7 @@ int32_t cdl_b200_attn_bwd_packed(const cdl_attn_desc* desc, const cdl_tensor* q,
                                  cdl_stream stream) {
   return cdl::attn_bwd_packed_execute(desc, q, k, v, o, d_out, lse, cu_seqlens_q, cu_seqlens_k,
                                       max_seqlen_q, max_seqlen_k, dq, dk, dv, scratch, scratch_bytes,
-                                      static_cast<cudaStream_t>(stream));
+                                      static_cast<cudaStream_t>(stream), nullptr);
 }
 
 int32_t cdl_b200_attn_bwd_packed_scratch_bytes(int64_t batch, int64_t max_seqlen_q, int64_t heads,
@@ -1175,7 +1268,31 @@ int32_t cdl_b200_attn_bwd(const cdl_attn_desc* desc, const cdl_tensor* q, const 
                           const cdl_tensor* dv, void* scratch, size_t scratch_bytes,
                           cdl_stream stream) {
   return cdl::attn_bwd_execute(desc, q, k, v, o, d_out, lse, dq, dk, dv, scratch, scratch_bytes,
-                               static_cast<cudaStream_t>(stream));
+                               static_cast<cudaStream_t>(stream), nullptr);
+}
+
+int32_t cdl_b200_attn_bwd_rope(const cdl_attn_desc* desc, const cdl_tensor* q, const cdl_tensor* k,
+                               const cdl_tensor* v, const cdl_tensor* o, const cdl_tensor* d_out,
+                               const cdl_tensor* lse, const cdl_tensor* cos_sin, const cdl_tensor* dq,
+                               const cdl_tensor* dk, const cdl_tensor* dv, void* scratch,
+                               size_t scratch_bytes, cdl_stream stream) {
+  if (!cos_sin) return cdl::fail(CDL_ERR_INVALID, "attention_bwd: the rotary table is required");
+  return cdl::attn_bwd_execute(desc, q, k, v, o, d_out, lse, dq, dk, dv, scratch, scratch_bytes,
+                               static_cast<cudaStream_t>(stream), cos_sin);
+}
+
+int32_t cdl_b200_attn_bwd_packed_rope(const cdl_attn_desc* desc, const cdl_tensor* q,
+                                      const cdl_tensor* k, const cdl_tensor* v, const cdl_tensor* o,
+                                      const cdl_tensor* d_out, const cdl_tensor* lse,
+                                      const cdl_tensor* cu_seqlens_q, const cdl_tensor* cu_seqlens_k,
+                                      int64_t max_seqlen_q, int64_t max_seqlen_k,
+                                      const cdl_tensor* cos_sin, const cdl_tensor* dq,
+                                      const cdl_tensor* dk, const cdl_tensor* dv, void* scratch,
+                                      size_t scratch_bytes, cdl_stream stream) {
+  if (!cos_sin) return cdl::fail(CDL_ERR_INVALID, "attention_bwd (packed): the rotary table is required");
+  return cdl::attn_bwd_packed_execute(desc, q, k, v, o, d_out, lse, cu_seqlens_q, cu_seqlens_k,
+                                      max_seqlen_q, max_seqlen_k, dq, dk, dv, scratch, scratch_bytes,
+                                      static_cast<cudaStream_t>(stream), cos_sin);
 }
 
 int32_t cdl_b200_attn_bwd_scratch_bytes(const cdl_tensor* q, const cdl_tensor* k,

@@ -12,6 +12,12 @@
 //     measured), so barrier set-up, the tensor-memory allocation and the first loads are paid
 //     once per SM instead of once per 256 rows, and the next item's Q, K and V arrive while the
 //     current item's last blocks are computed.
+//   * One issuing warp per tile, each a stream across items.  A tile whose item is finished has
+//     its next item's first S = Q K^T issued at once, so the softmax warps find it when their
+//     output is stored, while the other tile still works on its last blocks (under causal
+//     masking the upper tile of an item always has one block less).  With one issuing warp that
+//     walked item by item the tensor pipe drained and refilled at every item: ~7000 clk per item
+//     against ~3700 per key block.
 //   * Exponentials on two pipes.  The 2 x 16384 exponentials of a step take 2048 clk of the MUFU
 //     pipe alone (16 per clk per SM), about as long as the step's four products.  A fixed share of
 //     every row's exponentials is evaluated on the FMA pipe with packed f32x2 arithmetic
@@ -23,7 +29,7 @@
 //     (Taking the exponentials speculatively against the old maximum, with the block's maximum
 //     computed alongside, was measured too: 7 % slower at B=8 S=2048, the re-take after a grown
 //     maximum costs more than the separate pass over the scores it saves.)
-//   * The MMA warp stays converged (one elected lane polls, issues and commits) and every wait
+//   * The MMA warps stay converged (one elected lane polls, issues and commits) and every wait
 //     sleeps in mbarrier.try_wait with a time hint instead of spinning next to the softmax warps
 //     of its scheduler partition.
 //
@@ -53,7 +59,7 @@ constexpr int ROWS_PER_ITEM = 2 * BQ;      // two tiles
 constexpr int TILE_BYTES = 128 * 128 * 2;  // a 128 x 128 bf16 tile as two [128 rows][64 d] panels
 constexpr int PANEL_BYTES = TILE_BYTES / 2;
 constexpr int KV_STAGES = 2;
-constexpr int THREADS = 384;  // warp 0 TMA, warp 1 MMA, warps 2-3 idle, warps 4-11 softmax
+constexpr int THREADS = 384;  // warp 0 TMA, warps 1-2 MMA (one per tile), warp 3 idle, warps 4-11 softmax
 constexpr int TMEM_COLS = 512;
 constexpr float RESCALE_THRESHOLD = 8.0f;  // log2 units
 constexpr size_t SMEM_BYTES = 1024 + 2 * TILE_BYTES + 2 * KV_STAGES * TILE_BYTES + 512;
@@ -64,12 +70,22 @@ static_assert(SMEM_BYTES <= 232448, "exceeds the 227 KiB of shared memory a CTA 
 #define CDL_ATTN_POLY_MASK 0x4924u
 #endif
 constexpr uint32_t POLY_MASK = CDL_ATTN_POLY_MASK;
+// Registers per thread after the roles split: the loader / issuer warp group gives up what the
+// two softmax warp groups take (LOW_REGS + 2 HIGH_REGS = 3 x 168, the launch allocation).
+#ifndef CDL_ATTN_LOW_REGS
+#define CDL_ATTN_LOW_REGS 88
+#endif
+constexpr int LOW_REGS = CDL_ATTN_LOW_REGS;
+constexpr int HIGH_REGS = (3 * 168 - LOW_REGS) / 2;
+static_assert(LOW_REGS % 8 == 0 && HIGH_REGS % 8 == 0, "setmaxnreg takes multiples of 8");
 
 // Timeline probe (builds with -DCDL_ATTN_PROBE only): CTA 0 stamps clock64 at the hand-over
 // points of its first 64 key blocks; cdl_attn_probe_read copies the stamps out.  Slots: 0-5 MMA
 // lane (P ready seen / P V issued / next Q K^T issued, per tile), 8-13 and 16-21 first softmax
-// thread of tile 0 / 1 (S seen, S in registers, max done, -, P stored, arrived), 24-31 arrival of
-// lane 0 of each of the 8 softmax warps.
+// thread of tile 0 / 1 (S seen, S in registers, max done, MMA lane past the P barrier, P stored,
+// arrived), 6-7 MMA lane begins to wait for P, 24-31 MMA lane around tile 0's products (before
+// P V, after its 8 issues, after its commit, before the wait for K, before Q K^T, after its 8
+// issues, after its commit, end of the step).
 #ifdef CDL_ATTN_PROBE
 __device__ long long g_probe_items[16 * 16];  // [item of CTA 0][slot]
 #define CDL_PROBE_ITEM(k, slot)                                                            \
@@ -196,7 +212,7 @@ __device__ __forceinline__ int item_of(int k, int cid, int nc, int total) {
 
 // Per-sequence view of an item: head, lengths, row bases and block counts of the two tiles.
 struct View {
-  int h, b, Sq, Sk, q_base, k_base, bt, m0, n[2], n_max;
+  int h, b, Sq, Sk, q_base, k_base, bt, m0, n0, n1, n_max;  // n0 / n1: key blocks of the two tiles
 };
 __device__ __forceinline__ View view_of(const Params& p, int idx) {
   View v;
@@ -222,9 +238,9 @@ __device__ __forceinline__ View view_of(const Params& p, int idx) {
     v.bt = 0;
   }
   v.m0 = qb * ROWS_PER_ITEM;
-  v.n[0] = kv_blocks_for_tile(v.Sq, v.Sk, p.causal, v.m0);
-  v.n[1] = kv_blocks_for_tile(v.Sq, v.Sk, p.causal, v.m0 + BQ);
-  v.n_max = max(v.n[0], v.n[1]);
+  v.n0 = kv_blocks_for_tile(v.Sq, v.Sk, p.causal, v.m0);
+  v.n1 = kv_blocks_for_tile(v.Sq, v.Sk, p.causal, v.m0 + BQ);
+  v.n_max = max(v.n0, v.n1);
   return v;
 }
 
@@ -281,7 +297,7 @@ __global__ void __launch_bounds__(THREADS, 1)
 
   if (warp == 0) {
     // ------------------------------------------------------------ TMA producer
-    setmaxnreg_dec<56>();
+    setmaxnreg_dec<LOW_REGS>();
     if (elect_one()) {
       uint32_t kv_cnt = 0, q_cnt[2] = {0, 0};
       bool ok = true;
@@ -290,30 +306,21 @@ __global__ void __launch_bounds__(THREADS, 1)
         if (idx < 0) break;
         const View v = view_of(p_in, idx);
         const int kvh = v.h / (p_in.H / p_in.Hkv);
-        for (int t = 0; t < 2 && ok; ++t) {
-          if (v.n[t] == 0) continue;
-          // Q_t of the previous item is free once its last Q K^T has run
+        // Q_t of the previous item is free once its last Q K^T has run.  Tile 0 finishes an item
+        // first, so its Q and the first K go ahead of tile 1's Q.
+        auto load_q = [&](int t) {
+          if ((t == 0 ? v.n0 : v.n1) == 0 || !ok) return;
           ok = mbar_wait(&bars->q_empty[t], (q_cnt[t] & 1) ^ 1, abort_word, 121);
-          if (!ok) break;
+          if (!ok) return;
           ++q_cnt[t];
           mbar_arrive_expect_tx(&bars->q_full[t], TILE_BYTES);
 #pragma unroll
           for (int dh = 0; dh < 2; ++dh)
             tma_load_4d(s_q + t * TILE_BYTES + dh * PANEL_BYTES, &tmap_q, &bars->q_full[t], dh * 64,
                         v.q_base + v.m0 + t * BQ, v.h, v.bt);
-        }
-        // The next item's Q can only be loaded once this item's last Q K^T has run; bring it into
-        // L2 now, so that load is short when its turn comes.
-        {
-          const int nidx = item_of(k + 1, cid, nc, p_in.total_items);
-          if (nidx >= 0) {
-            const View nv = view_of(p_in, nidx);
-            for (int t = 0; t < 2; ++t)
-              if (nv.n[t] > 0)
-                for (int dh = 0; dh < 2; ++dh)
-                  tma_prefetch_4d(&tmap_q, dh * 64, nv.q_base + nv.m0 + t * BQ, nv.h, nv.bt);
-          }
-        }
+        };
+        load_q(0);
+        if (v.n_max == 0) load_q(1);
         for (int j = 0; j < v.n_max && ok; ++j, ++kv_cnt) {
           const int s = kv_cnt % KV_STAGES;
           const uint32_t ph = (kv_cnt / KV_STAGES) & 1;
@@ -324,6 +331,8 @@ __global__ void __launch_bounds__(THREADS, 1)
           for (int dh = 0; dh < 2; ++dh)
             tma_load_4d(s_k + s * TILE_BYTES + dh * PANEL_BYTES, &tmap_k, &bars->k_full[s], dh * 64,
                         v.k_base + j * BKV, kvh, v.bt);
+          if (j == 0) load_q(1);
+          if (!ok) break;
           ok = mbar_wait(&bars->v_empty[s], ph ^ 1, abort_word, 123);
           if (!ok) break;
           mbar_arrive_expect_tx(&bars->v_full[s], TILE_BYTES);
@@ -336,17 +345,20 @@ __global__ void __launch_bounds__(THREADS, 1)
     }
   } else if (warp == 1) {
     // ------------------------------------------------------------ MMA issuer
-    setmaxnreg_dec<56>();
-    {
-      // The whole warp walks the loop (so the address arithmetic is warp-uniform work) and one
-      // elected lane polls the barriers, issues and commits.
-      const bool el = elect_one();
-      const int el_lane = __ffs(__ballot_sync(0xffffffffu, el)) - 1;
-      auto wait_all = [&](uint64_t* bar, uint32_t parity, int code) -> bool {
-        int r = 1;
-        if (el) r = mbar_wait(bar, parity, abort_word, code) ? 1 : 0;
-        return __shfl_sync(0xffffffffu, r, el_lane) != 0;
-      };
+    // The ring slots (key blocks of the CTA's items, in order) are the steps of one loop.  In step
+    // r each tile that uses slot r gets O += P V for it and then S = Q K^T for the tile's next
+    // block, also when that block is the first of the next item: a tile whose item is finished
+    // (under causal masking the upper tile has one block less) has its next S under way while the
+    // other tile works on its last block and the softmax warps store the finished output.  The
+    // fixed order P V (0), Q K^T (0), P V (1), Q K^T (1) keeps the two tiles in opposite phase:
+    // one tile's softmax runs while the other's products do.
+    // The issuing lane shares its scheduler partition with two softmax warps that always have
+    // an instruction ready, so its scalar code runs at a few clocks per dependent instruction and
+    // sits on the critical path between "P ready" and the products: one lane runs the loop alone
+    // (no warp-wide broadcasts), the per-tile state lives in scalars (indexed arrays would go to
+    // local memory), and a K or V slot one tile has waited for is not waited for again by the other.
+    setmaxnreg_dec<LOW_REGS>();
+    if (elect_one()) {
       const uint32_t idesc_qk = make_idesc_bf16(BQ, BKV, 0, 0);
       const uint32_t idesc_pv = make_idesc_bf16(BQ, D, 0, 1);
       // A descriptor costs one 32-bit add: low word per operand, constant high word (SBO 1024,
@@ -359,95 +371,143 @@ __global__ void __launch_bounds__(THREADS, 1)
       const uint32_t q_lo = lo_of(smem_u32(s_q), 16), k_lo = lo_of(smem_u32(s_k), 16);
       const uint32_t v_lo = lo_of(smem_u32(s_v), PANEL_BYTES);
       // S_t = Q_t K_j^T: 8 products of K = 16 over the two 64-wide d panels.
-      auto issue_qk = [&](int t, int stage) {
+      auto issue_qk = [&](const int t, uint32_t stage, int r) {
         const uint32_t qa = q_lo + t * (TILE_BYTES >> 4), ka = k_lo + stage * (TILE_BYTES >> 4);
         const uint32_t d = tmem_base + t * 128;
-        if (el) {
+        if (t == 0 && r >= 0) CDL_PROBE(r, 28);
 #pragma unroll
-          for (int k = 0; k < D / 16; ++k) {
-            const uint32_t off = (k >> 2) * PANEL_BYTES + (k & 3) * 32;
-            umma_ss(d, desc(qa, off), desc(ka, off), idesc_qk, k != 0);
-          }
-          umma_commit(&bars->s_full[t]);
+        for (int k = 0; k < D / 16; ++k) {
+          const uint32_t off = (k >> 2) * PANEL_BYTES + (k & 3) * 32;
+          umma_ss(d, desc(qa, off), desc(ka, off), idesc_qk, k != 0);
         }
-        __syncwarp();
+        if (t == 0 && r >= 0) CDL_PROBE(r, 29);
+        umma_commit(&bars->s_full[t]);
+        if (t == 0 && r >= 0) CDL_PROBE(r, 30);
       };
       // O_t (+)= P_t V_j: A = P (bf16 pairs in TMEM), B = V, MN-major.
-      auto issue_pv = [&](int t, int stage, bool accumulate) {
+      auto issue_pv = [&](const int t, uint32_t stage, bool accumulate, int r) {
         const uint32_t va = v_lo + stage * (TILE_BYTES >> 4);
         const uint32_t d = tmem_base + 256 + t * 128, a = tmem_base + t * 128;
         const uint32_t acc = accumulate ? 1u : 0u;
-        if (el) {
+        if (t == 0) CDL_PROBE(r, 24);
 #pragma unroll
-          for (int k = 0; k < BKV / 16; ++k)
-            umma_ts(d, a + k * 8, desc(va, k * 2048), idesc_pv, k != 0 ? 1u : acc);
-          umma_commit(&bars->o_done[t]);
-        }
-        __syncwarp();
+        for (int k = 0; k < BKV / 16; ++k)
+          umma_ts(d, a + k * 8, desc(va, k * 2048), idesc_pv, k != 0 ? 1u : acc);
+        if (t == 0) CDL_PROBE(r, 25);
+        umma_commit(&bars->o_done[t]);
+        if (t == 0) CDL_PROBE(r, 26);
       };
-      uint32_t kv_cnt = 0, q_cnt[2] = {0, 0}, p_cnt[2] = {0, 0};
-      bool ok = true;
-      for (int k = 0; ok; ++k) {
-        const int idx = item_of(k, cid, nc, p_in.total_items);
-        if (idx < 0) break;
-        const View v = view_of(p_in, idx);
-        if (v.n_max == 0) continue;
-        if (el) CDL_PROBE_ITEM(k, 0);  // MMA lane: item begins (slot 1: first Q K^T issued; 2: item ends)
-        // first key block of the item
-        {
-          const int s = kv_cnt % KV_STAGES;
-          const uint32_t ph = (kv_cnt / KV_STAGES) & 1;
-          for (int t = 0; t < 2 && ok; ++t) {
-            if (v.n[t] == 0) continue;
-            ok = wait_all(&bars->q_full[t], q_cnt[t] & 1, 221) && wait_all(&bars->k_full[s], ph, 222);
-            if (!ok) break;
-            ++q_cnt[t];
+      // Per tile: the block its next Q K^T is for (item ordinal k, block j of n, ring slot; n == 0
+      // once the tile has no further block) and the block whose S has been issued and whose P V
+      // is due (pend, pend_slot, acc: not the first block of its item).
+      struct Tile {
+        int k, j, n;
+        uint32_t slot, next_base, pend_slot, q_cnt, p_cnt;
+        bool pend, acc;
+      };
+      Tile T0{-1, 0, 0, 0u, 0u, 0u, 0u, 0u, false, false};
+      Tile T1 = T0;
+      // Moves a tile's cursor to the first block of the next item the tile takes part in.
+      auto next_item = [&](Tile& T, const int t) {
+        while (true) {
+          ++T.k;
+          const int idx = item_of(T.k, cid, nc, p_in.total_items);
+          if (idx < 0) {
+            T.n = 0;
+            T.slot = T.next_base;
+            return;
+          }
+          const View v = view_of(p_in, idx);
+          const uint32_t base = T.next_base;
+          T.next_base = base + v.n_max;
+          const int n_t = t == 0 ? v.n0 : v.n1;
+          if (n_t > 0) {
+            T.j = 0;
+            T.n = n_t;
+            T.slot = base;
+            return;
+          }
+        }
+      };
+      next_item(T0, 0);
+      next_item(T1, 1);
+      // Ring slots this lane has seen filled, per stage (slot + 1 of the latest one).
+      uint32_t k_seen0 = 0, k_seen1 = 0, v_seen0 = 0, v_seen1 = 0;
+      // One tile's part of step r: P V for slot r if the tile has it, then S = Q K^T of the tile's
+      // next block.  A block two slots ahead (the tile skipped a slot that only the other tile
+      // uses) is started only if its operands are there already, so that this step's other
+      // products do not wait for it; otherwise it is started in the next step.
+      auto turn = [&](Tile& T, const int t, const int r) -> bool {
+        if (T.pend && static_cast<int>(T.pend_slot) == r) {
+          const uint32_t st = static_cast<uint32_t>(r) % KV_STAGES;
+          if (t == 0) CDL_PROBE(r, 6); else CDL_PROBE(r, 7);
+          if (!mbar_wait(&bars->p_ready[t], T.p_cnt & 1, abort_word, 223)) return false;
+          ++T.p_cnt;
+          if (t == 0) CDL_PROBE(r, 11); else CDL_PROBE(r, 19);
+          if ((st ? v_seen1 : v_seen0) <= static_cast<uint32_t>(r)) {
+            if (!mbar_wait(&bars->v_full[st], (static_cast<uint32_t>(r) / KV_STAGES) & 1, abort_word, 224))
+              return false;
+            if (st) v_seen1 = r + 1; else v_seen0 = r + 1;
+          }
+          CDL_PROBE(r, 3 * t);
+          tc_fence_after();
+          issue_pv(t, st, T.acc, r);
+          T.pend = false;
+          CDL_PROBE(r, 3 * t + 1);
+        }
+        if (!T.pend && T.n > 0 && static_cast<int>(T.slot) <= r + 2) {
+          const uint32_t s = T.slot;
+          const uint32_t sst = s % KV_STAGES, sph = (s / KV_STAGES) & 1;
+          const bool first = T.j == 0;
+          const bool k_known = (sst ? k_seen1 : k_seen0) > s;
+          bool go = true;
+          if (static_cast<int>(s) == r + 2)
+            go = (k_known || mbar_test(&bars->k_full[sst], sph)) &&
+                 (!first || mbar_test(&bars->q_full[t], T.q_cnt & 1));
+          if (go) {
+            if (first) {
+              if (!mbar_wait(&bars->q_full[t], T.q_cnt & 1, abort_word, 221)) return false;
+              ++T.q_cnt;
+            }
+            if (t == 0 && r >= 0) CDL_PROBE(r, 27);
+            if (!k_known) {
+              if (!mbar_wait(&bars->k_full[sst], sph, abort_word, 222)) return false;
+              if (sst) k_seen1 = s + 1; else k_seen0 = s + 1;
+            }
             tc_fence_after();
-            issue_qk(t, s);
-            if (v.n[t] == 1 && el) umma_commit(&bars->q_empty[t]);
-          }
-          if (ok && el) umma_commit(&bars->k_empty[s]);
-          if (el) CDL_PROBE_ITEM(k, 1);
-          __syncwarp();
-        }
-        for (int j = 0; j < v.n_max && ok; ++j) {
-          const int s = (kv_cnt + j) % KV_STAGES, sn = (kv_cnt + j + 1) % KV_STAGES;
-          const uint32_t ph = ((kv_cnt + j) / KV_STAGES) & 1, phn = ((kv_cnt + j + 1) / KV_STAGES) & 1;
-          for (int t = 0; t < 2 && ok; ++t) {
-            if (j < v.n[t]) {
-              ok = wait_all(&bars->p_ready[t], p_cnt[t] & 1, 223) && wait_all(&bars->v_full[s], ph, 224);
-              if (!ok) break;
-              if (el) CDL_PROBE(kv_cnt + j, 3 * t);
-              tc_fence_after();
-              issue_pv(t, s, j > 0);
-              ++p_cnt[t];
-              if (el) CDL_PROBE(kv_cnt + j, 3 * t + 1);
-            }
-            if (j + 1 < v.n[t]) {
-              ok = wait_all(&bars->k_full[sn], phn, 225);
-              if (!ok) break;
-              tc_fence_after();
-              issue_qk(t, sn);
-              if (el) CDL_PROBE(kv_cnt + j, 3 * t + 2);
-              if (j + 2 == v.n[t] && el) umma_commit(&bars->q_empty[t]);  // the last reader of Q_t
+            issue_qk(t, sst, r);
+            if (r >= 0) CDL_PROBE(r, 3 * t + 2);
+            T.pend = true;
+            T.pend_slot = s;
+            T.acc = !first;
+            if (T.j + 1 == T.n) {
+              umma_commit(&bars->q_empty[t]);  // the last reader of Q_t
+              next_item(T, t);
+            } else {
+              ++T.j;
+              ++T.slot;
             }
           }
-          if (!ok) break;
-          if (el) {
-            umma_commit(&bars->v_empty[s]);
-            if (j + 1 < v.n_max) umma_commit(&bars->k_empty[sn]);
-          }
-          __syncwarp();
         }
-        kv_cnt += v.n_max;
-        if (el) CDL_PROBE_ITEM(k, 2);
+        return true;
+      };
+      // r = -1 is the prologue (the first Q K^T of each tile); the loop ends when both tiles have
+      // neither a block to start nor a P V due.
+      for (int r = -1; T0.pend || T1.pend || T0.n > 0 || T1.n > 0; ++r) {
+        if (!turn(T0, 0, r) || !turn(T1, 1, r)) break;
+        // Every P V that reads V of slot r and every Q K^T that reads K of slot r + 1 has been
+        // issued (a Q K^T is issued one or two steps before its slot's step).
+        if (r >= 0) umma_commit(&bars->v_empty[static_cast<uint32_t>(r) % KV_STAGES]);
+        umma_commit(&bars->k_empty[static_cast<uint32_t>(r + 1) % KV_STAGES]);
+        if (r >= 0) CDL_PROBE(r, 31);
       }
     }
+    __syncwarp();
   } else if (warp < 4) {
-    setmaxnreg_dec<56>();
+    setmaxnreg_dec<LOW_REGS>();
   } else {
     // ------------------------------------------------------------ softmax + epilogue
-    setmaxnreg_inc<224>();
+    setmaxnreg_inc<HIGH_REGS>();
     const int t = (warp - 4) >> 2;  // query tile of this warp group
     const int quad = warp & 3;      // TMEM lane quadrant
     const int row_in_tile = quad * 32 + lane;
@@ -463,7 +523,7 @@ __global__ void __launch_bounds__(THREADS, 1)
       const int idx = item_of(k, cid, nc, p_in.total_items);
       if (idx < 0) break;
       const View v = view_of(p_in, idx);
-      const int n_t = v.n[t];
+      const int n_t = t == 0 ? v.n0 : v.n1;
       const int tile_row0 = v.m0 + t * BQ;
       const int row = tile_row0 + row_in_tile;
       const bool row_ok = row < v.Sq;
@@ -582,7 +642,6 @@ __global__ void __launch_bounds__(THREADS, 1)
         __syncwarp();
         if (lane == 0) mbar_arrive(&bars->p_ready[t]);
         if (probe_thread) CDL_PROBE(s_cnt - 1, 13 + 8 * t);
-        if (lane == 0) CDL_PROBE(s_cnt - 1, 24 + 4 * t + quad);
       }
       if (!ok) break;
       if (probe_thread) CDL_PROBE_ITEM(k, 5 + 4 * t);

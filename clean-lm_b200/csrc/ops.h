@@ -60,7 +60,7 @@ int32_t attn_bwd_execute(const cdl_attn_desc* desc, const cdl_tensor* q, const c
                          const cdl_tensor* v, const cdl_tensor* o, const cdl_tensor* d_o,
                          const cdl_tensor* lse, const cdl_tensor* dq, const cdl_tensor* dk,
                          const cdl_tensor* dv, void* scratch, size_t scratch_bytes,
-                         cudaStream_t stream);
+                         cudaStream_t stream, const cdl_tensor* rope_table = nullptr);
 int32_t attn_fwd_packed_execute(const cdl_attn_desc* desc, const cdl_tensor* q, const cdl_tensor* k,
                                 const cdl_tensor* v, const cdl_tensor* cu_q, const cdl_tensor* cu_k,
                                 long long max_q, long long max_k, const cdl_tensor* o,
@@ -71,7 +71,8 @@ int32_t attn_bwd_packed_execute(const cdl_attn_desc* desc, const cdl_tensor* q, 
                                 const cdl_tensor* lse, const cdl_tensor* cu_q, const cdl_tensor* cu_k,
                                 long long max_q, long long max_k, const cdl_tensor* dq,
                                 const cdl_tensor* dk, const cdl_tensor* dv, void* scratch,
-                                size_t scratch_bytes, cudaStream_t stream);
+                                size_t scratch_bytes, cudaStream_t stream,
+                                const cdl_tensor* rope_table = nullptr);
 int32_t rope_execute(const cdl_tensor* x, const cdl_tensor* cos_sin, int32_t rot_heads,
                      int32_t seqlen, int32_t backward, cudaStream_t stream);
 int32_t rope_ragged_execute(const cdl_tensor* x, const cdl_tensor* cos_sin, int32_t rot_heads,

@@ -152,15 +152,6 @@ cdl_tensor attn_view(const void* p, const Dims& d) {
   t.stride[0] = d.S * d.H * d.D; t.stride[1] = d.H * d.D; t.stride[2] = d.D; t.stride[3] = 1;
   return t;
 }
-cdl_tensor rope_view(const void* qkv, const Dims& d) {
-  cdl_tensor t{};
-  t.ptr = const_cast<void*>(qkv);
-  t.dtype = CDL_BF16;
-  t.rank = 3;
-  t.shape[0] = d.T; t.shape[1] = d.H + 2 * d.Hkv; t.shape[2] = d.D;
-  t.stride[0] = d.QKV; t.stride[1] = d.D; t.stride[2] = 1;
-  return t;
-}
 cdl_tensor lse_view(const float* p, const Dims& d) {
   cdl_tensor t{};
   t.ptr = const_cast<float*>(p);
@@ -308,7 +299,8 @@ int32_t sky1_block_bwd(const cdl_sky1_config* cfg, const cdl_sky1_weights* wt, c
   // attention
   CDL_CHECK(matmul_execute(&attnT, &tdo, &gwo, &gwo, 1.f, 1.f, st, wg));                // dWo += attn^T d_o
   CDL_CHECK(matmul_execute(&tdo, &woT, nullptr, &tdattn, 1.f, 0.f, st));            // d_attn = d_o Wo^T
-  const cdl_tensor rv = rope_view(b.dqkv, d);
+  // d_q and d_k leave the attention backward already rotated back (the transpose of the rotary
+  // embedding runs in its store epilogues)
   if (d.rg) {
     const cdl_tensor cu = cu_view(d);
     // Rows after the last sequence get no gradient from the attention kernels: clear the buffer
@@ -322,9 +314,7 @@ int32_t sky1_block_bwd(const cdl_sky1_config* cfg, const cdl_sky1_weights* wt, c
                      lse = lse_view_packed(sv->lse, d);
     CDL_CHECK(attn_bwd_packed_execute(&ad, &q, &k, &v, &ao, &dao, &lse, &cu, &cu, d.rg->max_seqlen,
                                       d.rg->max_seqlen, &dq, &dk, &dv, b.attn_scratch,
-                                      b.attn_scratch_bytes, st));
-    CDL_CHECK(rope_ragged_execute(&rv, &cs, static_cast<int32_t>(d.H + d.Hkv),
-                                  static_cast<int32_t>(d.rg->max_seqlen), &cu, 1, st));
+                                      b.attn_scratch_bytes, st, &cs));
   } else {
     const cdl_tensor q = head_view(sv->qkv, d, 0, d.H), k = head_view(sv->qkv, d, d.H, d.Hkv),
                      v = head_view(sv->qkv, d, d.H + d.Hkv, d.Hkv);
@@ -332,8 +322,7 @@ int32_t sky1_block_bwd(const cdl_sky1_config* cfg, const cdl_sky1_weights* wt, c
                      dv = head_view(b.dqkv, d, d.H + d.Hkv, d.Hkv);
     const cdl_tensor ao = attn_view(sv->attn, d), dao = attn_view(b.dattn, d), lse = lse_view(sv->lse, d);
     CDL_CHECK(attn_bwd_execute(&ad, &q, &k, &v, &ao, &dao, &lse, &dq, &dk, &dv, b.attn_scratch,
-                               b.attn_scratch_bytes, st));
-    CDL_CHECK(rope_execute(&rv, &cs, static_cast<int32_t>(d.H + d.Hkv), static_cast<int32_t>(d.S), 1, st));
+                               b.attn_scratch_bytes, st, &cs));
   }
   CDL_CHECK(rmsnorm_fwd_execute(&tx, &g1, nullptr, cfg->eps, &th, &tr, st));        // recompute h1, r1
   CDL_CHECK(matmul_execute(&hT, &tdqkv, &gwqkv, &gwqkv, 1.f, 1.f, st, wg));             // dWqkv += h1^T d_qkv

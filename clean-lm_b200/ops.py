@@ -237,10 +237,16 @@ def attention_bwd_scratch_bytes(q, k) -> int:
 
 
 def attention_bwd(q, k, v, out, d_out, lse, opts: AttentionOpts | None = None, scratch=None,
-                  dq=None, dk=None, dv=None):
-    """Returns (dq, dk, dv) in the input dtype (ops/attention/mod.rs:915-919)."""
+                  dq=None, dk=None, dv=None, rope_table=None):
+    """Returns (dq, dk, dv) in the input dtype (ops/attention/mod.rs:915-919).
+
+    With ``rope_table`` (f32 [positions, 128] = cos | sin) q and k are taken as rotated by the
+    rotary embedding and dq, dk are the gradients of the tensors before the rotation: the
+    transposed rotation runs in the kernels' store epilogues instead of as a call of its own."""
     opts = opts or AttentionOpts()
     _require_cuda(q, k, v, out, d_out, lse)
+    if rope_table is not None:
+        _require_cuda(rope_table)
     dq = torch.empty(q.shape, dtype=q.dtype, device=q.device) if dq is None else dq
     dk = torch.empty(k.shape, dtype=k.dtype, device=k.device) if dk is None else dk
     dv = torch.empty(v.shape, dtype=v.dtype, device=v.device) if dv is None else dv
@@ -257,17 +263,20 @@ def attention_bwd(q, k, v, out, d_out, lse, opts: AttentionOpts | None = None, s
         desc = _attn_desc(opts)
         a = [tensor_arg(t) for t in (q, k, v, out, d_out, lse, opts.cu_seqlens_q, opts.cu_seqlens_k)]
         b = [tensor_arg(t) for t in (dq, dk, dv)]
-        check(lib.cdl_b200_attn_bwd_packed(ctypes.byref(desc), *(ref(x) for x in a), max_q,
-                                           int(opts.max_seqlen_k or 0), *(ref(x) for x in b),
-                                           ctypes.c_void_p(scratch.data_ptr()),
-                                           scratch.numel() * scratch.element_size(), _stream()))
+        if rope_table is not None:
+            b.insert(0, tensor_arg(rope_table))
+        fn = lib.cdl_b200_attn_bwd_packed if rope_table is None else lib.cdl_b200_attn_bwd_packed_rope
+        check(fn(ctypes.byref(desc), *(ref(x) for x in a), max_q, int(opts.max_seqlen_k or 0),
+                 *(ref(x) for x in b), ctypes.c_void_p(scratch.data_ptr()),
+                 scratch.numel() * scratch.element_size(), _stream()))
         return dq, dk, dv
     need = attention_bwd_scratch_bytes(q, k)
     if scratch is None:
         scratch = torch.empty(max(need, 16), dtype=torch.uint8, device=q.device)
     desc = _attn_desc(opts)
-    args = [tensor_arg(t) for t in (q, k, v, out, d_out, lse, dq, dk, dv)]
-    check(lib.cdl_b200_attn_bwd(ctypes.byref(desc), *(ref(a) for a in args),
-                                ctypes.c_void_p(scratch.data_ptr()),
-                                scratch.numel() * scratch.element_size(), _stream()))
+    tensors = (q, k, v, out, d_out, lse) + (() if rope_table is None else (rope_table,)) + (dq, dk, dv)
+    args = [tensor_arg(t) for t in tensors]
+    fn = lib.cdl_b200_attn_bwd if rope_table is None else lib.cdl_b200_attn_bwd_rope
+    check(fn(ctypes.byref(desc), *(ref(a) for a in args), ctypes.c_void_p(scratch.data_ptr()),
+             scratch.numel() * scratch.element_size(), _stream()))
     return dq, dk, dv

@@ -365,6 +365,31 @@ int32_t cdl_b200_attn_bwd_packed(const cdl_attn_desc* desc, const cdl_tensor* q,
 int32_t cdl_b200_attn_bwd_packed_scratch_bytes(int64_t batch, int64_t max_seqlen_q, int64_t heads,
                                                size_t* bytes_out);
 
+/* The backward with the rotary embedding's transpose folded into the dQ and dK stores.  q and k are
+ * the rotated tensors the forward consumed (as cdl_b200_matmul_rope or cdl_b200_rope produce
+ * them); dq and dk come out as the gradients of q and k BEFORE the rotation, so the separate
+ * backward call of cdl_b200_rope (one more read and write of both tensors) goes away.  cos_sin is
+ * the table of cdl_b200_rope: f32 [positions, 128] = cos(64) | sin(64), at least as many positions
+ * as the longest sequence; a row's position is its index in its sequence.  Every head of q and k
+ * is rotated, as at the reference's call sites (crates/sky-1/src/training/model/decoder.rs:
+ * 363-378 forward, :645-655 backward).
+ * The values are those of the two-call form up to one bf16 rounding of f32 arithmetic on the same
+ * bf16-rounded dQ / dK.  No counterpart in the reference, whose backward graph holds a separate
+ * RoPE node. */
+int32_t cdl_b200_attn_bwd_rope(const cdl_attn_desc* desc, const cdl_tensor* q, const cdl_tensor* k,
+                               const cdl_tensor* v, const cdl_tensor* o, const cdl_tensor* d_out,
+                               const cdl_tensor* lse, const cdl_tensor* cos_sin, const cdl_tensor* dq,
+                               const cdl_tensor* dk, const cdl_tensor* dv, void* scratch,
+                               size_t scratch_bytes, cdl_stream stream);
+int32_t cdl_b200_attn_bwd_packed_rope(const cdl_attn_desc* desc, const cdl_tensor* q,
+                                      const cdl_tensor* k, const cdl_tensor* v, const cdl_tensor* o,
+                                      const cdl_tensor* d_out, const cdl_tensor* lse,
+                                      const cdl_tensor* cu_seqlens_q, const cdl_tensor* cu_seqlens_k,
+                                      int64_t max_seqlen_q, int64_t max_seqlen_k,
+                                      const cdl_tensor* cos_sin, const cdl_tensor* dq,
+                                      const cdl_tensor* dk, const cdl_tensor* dv, void* scratch,
+                                      size_t scratch_bytes, cdl_stream stream);
+
 /* ---- Elementwise glue of the sky-1 block -----------------------------------------------
  * The reference's kernels for these lived in its legacy `cleandl::operators` module, which is
  * absent from its tree; the call sites are crates/sky-1/src/training/model/decoder.rs:363-378

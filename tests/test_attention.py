@@ -324,6 +324,74 @@ def test_packed_sequence_longer_than_the_bound_is_cut_and_reported(cdl, gpu_ok):
     assert torch.equal(dq[s0], ref_dq[s0]) and torch.equal(dk[s0], ref_dk[s0]) and torch.equal(dv[s0], ref_dv[s0])
 
 
+def _rope_table(positions, d=128):
+    inv = 10000.0 ** (-torch.arange(0, d // 2, dtype=torch.float64) * 2 / d)
+    ang = torch.arange(positions, dtype=torch.float64)[:, None] * inv[None]
+    return torch.cat([ang.cos(), ang.sin()], 1).float()
+
+
+def _assert_same_up_to_one_rounding(name, got, ref):
+    """Both sides apply the same f32 arithmetic to the same bf16 values; the compiler may contract
+    the two kernels' multiply-adds differently, so single results may differ by one bf16 step."""
+    g, r = got.float(), ref.float()
+    step = torch.maximum(g.abs(), r.abs()) * 2.0 ** -7 + 1e-30
+    assert bool(((g - r).abs() <= step).all()), f"{name}: more than one bf16 step apart"
+    assert (got == ref).float().mean().item() > 0.99, f"{name}: too many elements differ"
+
+
+@pytest.mark.parametrize("b,s,hq,hk", [(2, 384, 2, 2), (1, 200, 4, 2), (2, 130, 2, 1)])
+def test_bwd_with_rope_equals_bwd_then_inverse_rope(cdl, gpu_ok, b, s, hq, hk):
+    """cdl_b200_attn_bwd_rope: dq and dk with the transposed rotary rotation applied in the store
+    epilogues equal the plain backward followed by cdl_b200_rope(backward = 1); dv is untouched."""
+    L = cdl._lib
+    q, k, v, do = make(b, s, s, hq, hk, seed=21)
+    qd, kd, vd, dod = q.cuda(), k.cuda(), v.cuda(), do.cuda()
+    table = _rope_table(s).cuda()
+    opts = cdl.ops.AttentionOpts(causal=True)
+    fwd = cdl.ops.attention_fwd(qd, kd, vd, opts)
+    dq, dk, dv = cdl.ops.attention_bwd(qd, kd, vd, fwd.out, dod, fwd.lse, opts)
+    keep = []
+    for t, heads in ((dq, hq), (dk, hk)):
+        flat = t.view(b * s, heads, 128)
+        tx, tt = L.tensor_arg(flat), L.tensor_arg(table)
+        keep += [tx, tt]
+        L.check(L.lib.cdl_b200_rope(L.ref(tx), L.ref(tt), heads, s, 1, None))
+    fq, fk, fv = cdl.ops.attention_bwd(qd, kd, vd, fwd.out, dod, fwd.lse, opts, rope_table=table)
+    torch.cuda.synchronize()
+    assert L.device_status() == 0
+    _assert_same_up_to_one_rounding("dq", fq, dq)
+    _assert_same_up_to_one_rounding("dk", fk, dk)
+    assert torch.equal(fv, dv)
+
+
+def test_packed_bwd_with_rope_equals_bwd_then_inverse_rope(cdl, gpu_ok):
+    L = cdl._lib
+    lens = [128, 300, 77]
+    q, k, v, do, cu_q, cu_k = make_packed(lens, lens, 4, 2)
+    qd, kd, vd, dod, cu = q.cuda(), k.cuda(), v.cuda(), do.cuda(), cu_q.cuda()
+    table = _rope_table(max(lens)).cuda()
+    opts = cdl.ops.AttentionOpts(causal=True, cu_seqlens_q=cu, cu_seqlens_k=cu, max_seqlen_q=max(lens),
+                                 max_seqlen_k=max(lens))
+    fwd = cdl.ops.attention_fwd(qd, kd, vd, opts)
+    mark = lambda t: torch.full_like(t, 7.0)
+    dq, dk, dv = cdl.ops.attention_bwd(qd, kd, vd, fwd.out, dod, fwd.lse, opts, dq=mark(qd), dk=mark(kd), dv=mark(vd))
+    keep = []
+    for t, heads in ((dq, 4), (dk, 2)):
+        tx, tt, tc = L.tensor_arg(t), L.tensor_arg(table), L.tensor_arg(cu)
+        keep += [tx, tt, tc]
+        L.check(L.lib.cdl_b200_rope_ragged(L.ref(tx), L.ref(tt), heads, L.ref(tc), 1, None))
+    fq, fk, fv = cdl.ops.attention_bwd(qd, kd, vd, fwd.out, dod, fwd.lse, opts, dq=mark(qd), dk=mark(kd),
+                                       dv=mark(vd), rope_table=table)
+    torch.cuda.synchronize()
+    assert L.device_status() == 0
+    _assert_same_up_to_one_rounding("dq", fq, dq)
+    _assert_same_up_to_one_rounding("dk", fk, dk)
+    assert torch.equal(fv, dv)
+    # a table shorter than the longest sequence is refused
+    with pytest.raises(L.CdlError, match="positions"):
+        cdl.ops.attention_bwd(qd, kd, vd, fwd.out, dod, fwd.lse, opts, rope_table=table[:100].contiguous())
+
+
 def test_packed_rejections(cdl, gpu_ok):
     z = lambda *s: torch.zeros(*s, dtype=torch.bfloat16, device="cuda")
     cu = torch.tensor([0, 8], dtype=torch.int32, device="cuda")
