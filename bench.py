@@ -113,6 +113,18 @@ def run_reference(args) -> None:
 
 
 # ------------------------------------------------------------------ clocks sampler
+def init_nccl(dist, dev, max_ctas: int) -> None:
+    """One NCCL communicator per rank.  `max_ctas` > 0 bounds the CTAs NCCL's kernels may take
+    (ncclConfig_t.maxCTAs): the all-reduces run next to persistent GEMMs that are scheduled for
+    the whole machine, and every SM NCCL holds delays the GEMM CTAs that would run there."""
+    opts = None
+    if max_ctas > 0:
+        opts = dist.ProcessGroupNCCL.Options()
+        opts.config.max_ctas = max_ctas
+        opts.config.min_ctas = 1
+    dist.init_process_group("nccl", device_id=dev, pg_options=opts)
+
+
 class ClockSampler:
     FIELDS = ("clocks.sm,clocks.max.sm,clocks_event_reasons.hw_slowdown,"
               "clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,"
@@ -224,7 +236,7 @@ def run_ours(args) -> None:
     torch.cuda.set_device(local)
     dev = torch.device("cuda", local)
     if world > 1:
-        dist.init_process_group("nccl", device_id=dev)
+        init_nccl(dist, dev, args.nccl_max_ctas)
     L = cdl._lib
     L.check(L.lib.cdl_b200_device_ok(local))
 
@@ -240,8 +252,15 @@ def run_ours(args) -> None:
     for n in order:
         grads[n] = bucket[off:off + sizes[n]].view(shapes[n])
         off += sizes[n]
-    ffn_elems = sum(sizes[n] for n in order[:4])
     blk = cdl.sky1.Sky1Block(cfg, params, device=dev, grads=grads)
+    # One slice of the bucket per group of gradients the backward completes together, in the
+    # backward's order: each slice's all-reduce starts as soon as its weight gradients are done.
+    slices, off = [], 0
+    for group in blk.GRAD_GROUPS:
+        n = sum(sizes[g] for g in group)
+        slices.append((off, off + n))
+        off += n
+    assert off == bucket.numel() and [g for grp in blk.GRAD_GROUPS for g in grp] == list(order)
 
     gen = torch.Generator().manual_seed(SEED + 1000 * rank)
     emb = (torch.randn(VOCAB, cfg.hidden, generator=gen) * 0.02).to(torch.bfloat16).to(dev)
@@ -256,8 +275,7 @@ def run_ours(args) -> None:
 
     main = torch.cuda.Stream(device=dev)
     comm = torch.cuda.Stream(device=dev)
-    ffn_ready = torch.cuda.Event()
-    all_ready = torch.cuda.Event()
+    group_done = [torch.cuda.Event() for _ in slices]
     reduced = torch.cuda.Event()
 
     def embed():
@@ -274,16 +292,11 @@ def run_ours(args) -> None:
         # The previous step's all-reduce must have drained before gradients are touched again.
         torch.cuda.current_stream().wait_event(reduced)
         bucket.zero_()
-        blk.backward(dy, dx, phase=1)
-        ffn_ready.record()
+        blk.backward(dy, dx, events=group_done)
         with torch.cuda.stream(comm):
-            comm.wait_event(ffn_ready)
-            dist.all_reduce(bucket[:ffn_elems])
-        blk.backward(dy, dx, phase=2)
-        all_ready.record()
-        with torch.cuda.stream(comm):
-            comm.wait_event(all_ready)
-            dist.all_reduce(bucket[ffn_elems:])
+            for ev, (lo, hi) in zip(group_done, slices):
+                comm.wait_event(ev)
+                dist.all_reduce(bucket[lo:hi])
             reduced.record()
 
     def step_resident():
@@ -710,7 +723,7 @@ def run_kernel(args) -> None:
         xs = [rnd(rows, cols) for _ in range(nbuf)]
         w = (1 + 0.02 * torch.randn(cols, device=dev, generator=gen)).to(torch.bfloat16)
         if k == "norm_fwd":
-            o = cdl.ops.NormFwdOpts(scale=w, save_stats=True)
+            o = cdl.ops.NormFwdOpts(scale=w, save_stats=True, variant=args.variant)
             fns = [(lambda x=x: cdl.ops.norm_fwd(x, o)) for x in xs]
             work = 4.0 * rows * cols + 2 * cols + 4 * rows
         else:
@@ -719,11 +732,13 @@ def run_kernel(args) -> None:
             ds = torch.zeros(cols, device=dev)
             scr = torch.empty(cdl.ops.norm_bwd_scratch_bytes(rows, cols), dtype=torch.uint8, device=dev)
             ress = [rnd(rows, cols) for _ in range(nbuf)] if args.residual else [None] * nbuf
-            fns = [(lambda x=x, dy=dy, rs=rs: cdl.ops.norm_bwd(x, dy, w, r_inv, ds, scratch=scr, residual_dy=rs))
+            fns = [(lambda x=x, dy=dy, rs=rs: cdl.ops.norm_bwd(x, dy, w, r_inv, ds, scratch=scr, residual_dy=rs,
+                                                                  variant=args.variant))
                    for x, dy, rs in zip(xs, dys, ress)]
             work = (8.0 if args.residual else 6.0) * rows * cols + 6 * cols + 4 * rows
         unit, peak = "GB/s", peaks["hbm"]
-        desc = f"{k} x[{rows},{cols}] bf16" + (" + residual gradient" if k == "norm_bwd" and args.residual else "")
+        desc = (f"{k} x[{rows},{cols}] bf16" + (" + residual gradient" if k == "norm_bwd" and args.residual else "")
+                + (f" variant {args.variant}" if args.variant else ""))
     elif k == "gemm_mx":
         # D[m, n] = A[m, k] . B[k, n] with MXFP8 operands (quantised once, outside the timing)
         m, n, kk = args.m, args.n, args.k
@@ -874,7 +889,7 @@ def run_lm(args) -> None:
     torch.cuda.set_device(local)
     dev = torch.device("cuda", local)
     if world > 1:
-        dist.init_process_group("nccl", device_id=dev)
+        init_nccl(dist, dev, args.nccl_max_ctas)
     blk = cdl.sky1.Sky1Config()
     cfg = cdl.sky1.Sky1LMConfig(block=blk, layers=args.layers, vocab=VOCAB)
     model = cdl.sky1.Sky1LM(cfg, seed=4, device=dev)
@@ -966,6 +981,8 @@ def main() -> None:
                     help="block = benchmark configuration 4 (the headline metric); lm = the 24-layer "
                          "training step; block_mx = the block with MXFP8 matrix products (one GPU)")
     ap.add_argument("--layers", type=int, default=24)
+    ap.add_argument("--nccl-max-ctas", type=int, default=0,
+                    help="N > 1: upper bound on the CTAs of NCCL's kernels (0: NCCL's default)")
     ap.add_argument("--no-kernels", action="store_true",
                     help="block workload: skip the per-kernel targets and library stand-ins")
     ap.add_argument("--no-lm", action="store_true",

@@ -79,6 +79,10 @@ class CdlSky1Ragged(ctypes.Structure):
                 ("max_seqlen", ctypes.c_int32)]
 
 
+class CdlSky1GradEvents(ctypes.Structure):
+    _fields_ = [(n, ctypes.c_void_p) for n in ("wdown", "wup", "wgate_norm2", "wo", "wqkv_norm1")]
+
+
 class CdlMxTensor(ctypes.Structure):
     _fields_ = [("values", ctypes.c_void_p), ("scale_factors", ctypes.c_void_p),
                 ("format", ctypes.c_int32), ("dim", ctypes.c_int32),
@@ -199,6 +203,11 @@ SIGNATURES = {
                                  _vp, ctypes.POINTER(CdlSky1Saved), _vp,
                                  ctypes.POINTER(CdlSky1Grads), _vp, _vp, _sz, ctypes.c_int32, _vp],
                                 ctypes.c_int32),
+    "cdl_b200_sky1_block_bwd_events": ([ctypes.POINTER(CdlSky1Config), ctypes.POINTER(CdlSky1Weights),
+                                        _vp, _vp, ctypes.POINTER(CdlSky1Ragged),
+                                        ctypes.POINTER(CdlSky1Saved), _vp, ctypes.POINTER(CdlSky1Grads),
+                                        _vp, _vp, _sz, ctypes.POINTER(CdlSky1GradEvents), _vp],
+                               ctypes.c_int32),
 }
 
 for _name, (_args, _res) in SIGNATURES.items():

@@ -63,6 +63,10 @@ constexpr size_t Q_SMEM_BYTES = (4 + QK_STAGES) * TILE_BYTES + 256;
 static_assert(KV_SMEM_BYTES <= 232448 && Q_SMEM_BYTES <= 232448,
               "exceeds the 227 KiB of shared memory a CTA can opt in to");
 
+// Registers per thread of the dK/dV kernel's roles (control warps / compute warps; 168 at launch,
+// LOW + 2 HIGH = 3 x 168): with 56 the issuing lane spills.
+constexpr int KV_LOW_REGS = 72, KV_HIGH_REGS = 216;
+
 // Status code (device status word) of a packed sequence longer than max_seqlen_q / max_seqlen_k.
 constexpr int STATUS_SEQ_EXCEEDS_BOUND = 921;
 
@@ -345,7 +349,7 @@ __global__ void __launch_bounds__(THREADS, 1)
 
   if (warp == 0) {
     // ------------------------------------------------------------ TMA producer
-    setmaxnreg_dec<56>();
+    setmaxnreg_dec<KV_LOW_REGS>();
     if (elect_one() && iters > 0) {
       mbar_arrive_expect_tx(&bars->kv_full, 2 * TILE_BYTES);
 #pragma unroll
@@ -377,7 +381,7 @@ __global__ void __launch_bounds__(THREADS, 1)
     // Issue order: dV(it), S^T(it+1), dK(it), dP^T(it+1): the products of the next query block
     // that do not depend on this block's dS^T are issued before the one that does, so the
     // compute warps always find their next input ready.
-    setmaxnreg_dec<56>();
+    setmaxnreg_dec<KV_LOW_REGS>();
     if (elect_one() && iters > 0) {
       const uint32_t idesc_kk = make_idesc_bf16(128, 128, 0, 0);  // both operands K-major
       const uint32_t idesc_kmn = make_idesc_bf16(128, 128, 0, 1); // A K-major / TMEM, B MN-major
@@ -447,12 +451,12 @@ __global__ void __launch_bounds__(THREADS, 1)
       if (ok) umma_commit(&bars->dk_done);
     }
   } else if (warp < 4) {
-    setmaxnreg_dec<56>();
+    setmaxnreg_dec<KV_LOW_REGS>();
   } else {
     // ------------------------------------------------------------ compute warps (4..11)
     // Per iteration: dS^T(it) from dP^T(it) and the P^T kept in registers, then P^T(it+1), which
     // overlaps the dK product of this block.
-    setmaxnreg_inc<224>();
+    setmaxnreg_inc<KV_HIGH_REGS>();
     const int ct = threadIdx.x - 128;  // 0..255
     const int wg = (warp - 4) >> 2;    // column (query) half this thread works on
     const int quad = warp & 3;

@@ -47,6 +47,29 @@ __device__ __forceinline__ uint4 pack8(const float (&f)[8]) {
   return q;
 }
 
+// Adds (or, for the first warp, stores) a warp's per-lane dscale sums into the CTA's row in shared
+// memory: 128-bit accesses, so a lane's 8 consecutive floats cost two conflict-free transactions.
+template <int NCH>
+__device__ __forceinline__ void fold_dscale(float* s_part, const float (&acc)[NCH * 8], int cols, int lane,
+                                            bool first) {
+#pragma unroll
+  for (int c = 0; c < NCH; ++c) {
+    const int col = c * 256 + lane * 8;
+    if (col < cols) {
+      float4* dst = reinterpret_cast<float4*>(s_part + col);
+      float4 lo = make_float4(acc[c * 8 + 0], acc[c * 8 + 1], acc[c * 8 + 2], acc[c * 8 + 3]);
+      float4 hi = make_float4(acc[c * 8 + 4], acc[c * 8 + 5], acc[c * 8 + 6], acc[c * 8 + 7]);
+      if (!first) {
+        const float4 a = dst[0], b = dst[1];
+        lo.x += a.x; lo.y += a.y; lo.z += a.z; lo.w += a.w;
+        hi.x += b.x; hi.y += b.y; hi.z += b.z; hi.w += b.w;
+      }
+      dst[0] = lo;
+      dst[1] = hi;
+    }
+  }
+}
+
 // NCH = number of 256-column stripes a row spans (cols <= 256 * NCH).
 template <int NCH>
 __global__ void __launch_bounds__(FWD_THREADS, NCH <= 8 ? 4 : 1)
@@ -249,6 +272,9 @@ __global__ void __launch_bounds__(PIPE_THREADS, 1)
     for (int i = warp; i < n; i += PIPE_CONSUMERS) {
       const int s = i % stages;
       const uint32_t ph = (i / stages) & 1;
+      // (see the backward's consumer: the previous use of the stage must have been released
+      // before a parity wait on `full` is unambiguous)
+      if (i >= stages && !mbar_wait(&empty[s], ph ^ 1, abort_word, 703)) break;
       if (!mbar_wait(&full[s], ph, abort_word, 702)) break;
       const uint8_t* src = ring + static_cast<size_t>(s) * row_bytes;
       uint4 v[NCH];
@@ -374,22 +400,10 @@ __global__ void __launch_bounds__(BWD_THREADS, BWD_BLOCKS_PER_SM)
     }
   }
 
-  if (DSCALE) {
+  if constexpr (DSCALE) {
     // Fold the block's warps one after another (fixed order: deterministic).
     for (int w = 0; w < warps_per_block; ++w) {
-      if (warp == w) {
-#pragma unroll
-        for (int c = 0; c < NCH; ++c) {
-          const int col = c * 256 + lane * 8;
-          if (col < cols) {
-#pragma unroll
-            for (int j = 0; j < 8; ++j) {
-              if (w == 0) s_part[col + j] = acc[c * 8 + j];
-              else s_part[col + j] += acc[c * 8 + j];
-            }
-          }
-        }
-      }
+      if (warp == w) fold_dscale<NCH>(s_part, acc, cols, lane, w == 0);
       __syncthreads();
     }
     float* out = partials + static_cast<long long>(blockIdx.x) * cols;
@@ -401,8 +415,16 @@ __global__ void __launch_bounds__(BWD_THREADS, BWD_BLOCKS_PER_SM)
 // residual) rows of the CTA's slice into a shared-memory ring with bulk copies; warps 0-7 take
 // every 8th row, keep their partial dscale sums in registers, and the CTA writes one partial
 // row at the end (folded through the ring's memory once the pipeline has drained).
+// The backward's ring is fed by two producer warps (one lane each): the lane that issues a row's
+// copies spends ~800 clk per row on the barrier wait, the expect-tx arrival and three bulk copies
+// (measured: the kernel's time per row followed that lane, not the memory system), more than the
+// ~550 clk a row may take at the measured copy bandwidth.  Producer p takes the rows i with
+// i % 2 == p; with an even number of stages it also owns the stages s with s % 2 == p.
+constexpr int BWD_PIPE_PRODUCERS = 2;
+constexpr int BWD_PIPE_THREADS = (PIPE_CONSUMERS + BWD_PIPE_PRODUCERS) * 32;
+
 template <int NCH>
-__global__ void __launch_bounds__(PIPE_THREADS, 1)
+__global__ void __launch_bounds__(BWD_PIPE_THREADS, 1)
     rmsnorm_bwd_pipe_kernel(const __nv_bfloat16* __restrict__ x, long long ldx,
                             const __nv_bfloat16* __restrict__ dy, long long lddy,
                             const __nv_bfloat16* __restrict__ res, long long ldres,
@@ -422,17 +444,31 @@ __global__ void __launch_bounds__(PIPE_THREADS, 1)
   const int row_begin = min(rows, static_cast<int>(blockIdx.x) * per);
   const int row_end = min(rows, row_begin + per);
   const int n = row_end - row_begin;
-  if (threadIdx.x == 0) {
-    for (int s = 0; s < stages; ++s) {
+  const int producer = (warp >= PIPE_CONSUMERS && lane == 0) ? warp - PIPE_CONSUMERS : -1;
+  auto load_row = [&](int i, int s) {
+    uint8_t* dst = ring + static_cast<size_t>(s) * stage_bytes;
+    const long long row = row_begin + i;
+    mbar_arrive_expect_tx(&full[s], stage_bytes);
+    bulk_load_1d(dst, x + row * ldx, row_bytes, &full[s]);
+    bulk_load_1d(dst + row_bytes, dy + row * lddy, row_bytes, &full[s]);
+    if (ntens == 3) bulk_load_1d(dst + 2 * row_bytes, res + row * ldres, row_bytes, &full[s]);
+  };
+  // Each producer lane sets up the barriers of its own stages and fills them once before the CTA
+  // synchronises: the first rows are on their way while the other warps fetch the scale.
+  if (threadIdx.x == 0) *abort_word = 0;
+  if (producer >= 0) {
+    for (int s = producer; s < stages; s += BWD_PIPE_PRODUCERS) {
       mbar_init(&full[s], 1);
       mbar_init(&empty[s], 1);
     }
-    *abort_word = 0;
     fence_mbar_init();
   }
   grid_dep_wait();
   grid_dep_launch();
-  for (int i = threadIdx.x * 8; i < cols; i += PIPE_THREADS * 8)
+  const int first_round = min(n, stages);
+  if (producer >= 0)
+    for (int i = producer; i < first_round; i += BWD_PIPE_PRODUCERS) load_row(i, i);
+  for (int i = threadIdx.x * 8; i < cols; i += BWD_PIPE_THREADS * 8)
     *reinterpret_cast<uint4*>(s_scale + i * 2) = __ldg(reinterpret_cast<const uint4*>(scale + i));
   __syncthreads();
 
@@ -440,18 +476,20 @@ __global__ void __launch_bounds__(PIPE_THREADS, 1)
 #pragma unroll
   for (int i = 0; i < NCH * 8; ++i) acc[i] = 0.f;
 
-  if (warp == PIPE_CONSUMERS) {
-    if (lane == 0) {
-      for (int i = 0; i < n; ++i) {
-        const int s = i % stages;
-        const uint32_t ph = ((i / stages) & 1) ^ 1;
+  if (warp >= PIPE_CONSUMERS) {
+    if (producer >= 0) {
+      // stage and phase advance without divisions: the stage steps by 2 and wraps (stages is even)
+      int s = producer;
+      uint32_t ph = 0;  // phase of `empty` that frees the stage for its second use
+      for (int i = first_round + ((first_round ^ producer) & 1); i < n; i += BWD_PIPE_PRODUCERS) {
+        // first_round == stages here (n > stages), so row i goes to stage i % stages
         if (!mbar_wait(&empty[s], ph, abort_word, 711)) break;
-        uint8_t* dst = ring + static_cast<size_t>(s) * stage_bytes;
-        const long long row = row_begin + i;
-        mbar_arrive_expect_tx(&full[s], stage_bytes);
-        bulk_load_1d(dst, x + row * ldx, row_bytes, &full[s]);
-        bulk_load_1d(dst + row_bytes, dy + row * lddy, row_bytes, &full[s]);
-        if (ntens == 3) bulk_load_1d(dst + 2 * row_bytes, res + row * ldres, row_bytes, &full[s]);
+        load_row(i, s);
+        s += BWD_PIPE_PRODUCERS;
+        if (s >= stages) {
+          s -= stages;
+          ph ^= 1;
+        }
       }
     }
   } else {
@@ -459,10 +497,16 @@ __global__ void __launch_bounds__(PIPE_THREADS, 1)
     for (int i = warp; i < n; i += PIPE_CONSUMERS) {
       const int s = i % stages;
       const uint32_t ph = (i / stages) & 1;
+      const long long row = row_begin + i;
+      const float r = r_inv[row * r_inv_stride];  // on its way while the row's tiles land
+      // The consumer warps run independently, so this warp can reach the stage's next use before
+      // another warp has taken the previous one (or before that one's copies have landed): a
+      // parity wait on `full` would then pass on the phase before last.  The stage's previous
+      // use has been released (`empty`) only after its data arrived and was read, and that
+      // release cannot be two phases behind (this warp's previous row was loaded after it).
+      if (i >= stages && !mbar_wait(&empty[s], ph ^ 1, abort_word, 713)) break;
       if (!mbar_wait(&full[s], ph, abort_word, 712)) break;
       const uint8_t* src = ring + static_cast<size_t>(s) * stage_bytes;
-      const long long row = row_begin + i;
-      const float r = r_inv[row * r_inv_stride];
       uint4 vx[NCH], vd[NCH];
 #pragma unroll
       for (int c = 0; c < NCH; ++c) {
@@ -517,23 +561,11 @@ __global__ void __launch_bounds__(PIPE_THREADS, 1)
   __syncthreads();
   float* s_part = reinterpret_cast<float*>(ring);
   for (int w = 0; w < PIPE_CONSUMERS; ++w) {
-    if (warp == w) {
-#pragma unroll
-      for (int c = 0; c < NCH; ++c) {
-        const int col = c * 256 + lane * 8;
-        if (col < cols) {
-#pragma unroll
-          for (int j = 0; j < 8; ++j) {
-            if (w == 0) s_part[col + j] = acc[c * 8 + j];
-            else s_part[col + j] += acc[c * 8 + j];
-          }
-        }
-      }
-    }
+    if (warp == w) fold_dscale<NCH>(s_part, acc, cols, lane, w == 0);
     __syncthreads();
   }
   float* out = partials + static_cast<long long>(blockIdx.x) * cols;
-  for (int i = threadIdx.x; i < cols; i += PIPE_THREADS) out[i] = s_part[i];
+  for (int i = threadIdx.x; i < cols; i += BWD_PIPE_THREADS) out[i] = s_part[i];
   if (threadIdx.x == 0 && *abort_word != 0) atomicExch(status, *abort_word);
 }
 
@@ -555,32 +587,38 @@ __global__ void __launch_bounds__(128)
   partials[static_cast<long long>(blockIdx.y) * cols + col] = acc;
 }
 
-// dscale[j] += sum_b partials[b][j], summed in a fixed order.  A CTA owns 32 columns; its 8
-// warps each sum every 8th partial row (coalesced 128-byte reads), then the 8 sums are folded
-// through shared memory in warp order.
-__global__ void __launch_bounds__(256)
+// dscale[j] += sum_b partials[b][j], summed in a fixed order.  The partial rows were written a
+// moment ago (L2 hits), so the kernel is bound by load round trips, not bandwidth: a CTA owns 16
+// columns and spreads the rows over 32 groups of threads, each thread keeps four loads in flight,
+// and the 32 group sums are folded through shared memory in group order.  (With 8 groups and two
+// loads in flight the 444 partial rows of a [16384, 2048] backward took ~8 us of a 48 us call.)
+constexpr int FIN_COLS = 16, FIN_GROUPS = 32;
+__global__ void __launch_bounds__(FIN_COLS * FIN_GROUPS)
     dscale_finalize_kernel(const float* __restrict__ partials, int num_partials, int cols,
                            float* __restrict__ dscale, long long dscale_stride) {
-  __shared__ float s_sum[8][32];
-  const int cx = threadIdx.x & 31, rg = threadIdx.x >> 5;
-  const int col = blockIdx.x * 32 + cx;
-  float s0 = 0.f, s1 = 0.f;
+  __shared__ float s_sum[FIN_GROUPS][FIN_COLS];
+  const int cx = threadIdx.x % FIN_COLS, rg = threadIdx.x / FIN_COLS;
+  const int col = blockIdx.x * FIN_COLS + cx;
+  float s0 = 0.f, s1 = 0.f, s2 = 0.f, s3 = 0.f;
   grid_dep_wait();
   grid_dep_launch();
   if (col < cols) {
+    const float* p = partials + col;
     int b = rg;
-    for (; b + 8 < num_partials; b += 16) {
-      s0 += partials[static_cast<long long>(b) * cols + col];
-      s1 += partials[static_cast<long long>(b + 8) * cols + col];
+    for (; b + 3 * FIN_GROUPS < num_partials; b += 4 * FIN_GROUPS) {
+      s0 += p[static_cast<long long>(b) * cols];
+      s1 += p[static_cast<long long>(b + FIN_GROUPS) * cols];
+      s2 += p[static_cast<long long>(b + 2 * FIN_GROUPS) * cols];
+      s3 += p[static_cast<long long>(b + 3 * FIN_GROUPS) * cols];
     }
-    if (b < num_partials) s0 += partials[static_cast<long long>(b) * cols + col];
+    for (; b < num_partials; b += FIN_GROUPS) s0 += p[static_cast<long long>(b) * cols];
   }
-  s_sum[rg][cx] = s0 + s1;
+  s_sum[rg][cx] = (s0 + s1) + (s2 + s3);
   __syncthreads();
   if (rg == 0 && col < cols) {
     float t = 0.f;
 #pragma unroll
-    for (int w = 0; w < 8; ++w) t += s_sum[w][cx];
+    for (int w = 0; w < FIN_GROUPS; ++w) t += s_sum[w][cx];
     dscale[col * dscale_stride] += t;
   }
 }
@@ -692,6 +730,7 @@ static void launch_bwd_pipe(const cdl_tensor* x, const cdl_tensor* dy, const cdl
   const int stage_bytes = (res ? 3 : 2) * row_bytes;
   int stages = (160 * 1024) / stage_bytes;
   if (stages > 64) stages = 64;
+  stages &= ~1;  // even: each of the two producer lanes owns every other stage
   const size_t smem = static_cast<size_t>(stages) * stage_bytes + row_bytes + 2 * stages * sizeof(uint64_t) + 16;
   static std::once_flag once[64];
   int dev = 0;
@@ -700,7 +739,7 @@ static void launch_bwd_pipe(const cdl_tensor* x, const cdl_tensor* dy, const cdl
     cudaFuncSetAttribute(rmsnorm_bwd_pipe_kernel<NCH>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                          160 * 1024 + 4096 + 2 * 64 * static_cast<int>(sizeof(uint64_t)) + 16);
   });
-  launch_pdl(rmsnorm_bwd_pipe_kernel<NCH>, dim3(sm_count()), dim3(PIPE_THREADS), smem, stream,
+  launch_pdl(rmsnorm_bwd_pipe_kernel<NCH>, dim3(sm_count()), dim3(BWD_PIPE_THREADS), smem, stream,
       static_cast<const __nv_bfloat16*>(x->ptr), x->stride[0],
       static_cast<const __nv_bfloat16*>(dy->ptr), dy->stride[0],
       res ? static_cast<const __nv_bfloat16*>(res->ptr) : nullptr, res ? res->stride[0] : 0,
@@ -822,11 +861,12 @@ int32_t rmsnorm_bwd_execute(const cdl_tensor* x, const cdl_tensor* dy, const cdl
   const int need = (r + warps - 1) / warps;
   if (grid > need) grid = need;
   int num_partials = grid;
-  // Measured back to back at [16384, 2048]: without a residual gradient the warp-per-row kernel
-  // is faster (47 us against 55 us); with one, the pipelined kernel is (60 us against 72 us: the
-  // third row does not fit the other kernel's registers next to the dscale accumulators).
+  // Measured back to back at [16384, 2048] with two producer lanes feeding the ring: the pipelined
+  // kernel takes 44.5 us without and 52.5 us with a residual gradient, the warp-per-row kernel
+  // 45 us and 81 us (the third row does not fit its registers next to the dscale accumulators);
+  // at 65536 rows 139 / 171 us against 147 us for the warp-per-row form without residual.
   const bool pipe = c <= 2048 && r >= 2 * sm_count() &&
-                    (variant == CDL_NORM_AUTO ? res != nullptr : variant == CDL_NORM_PIPELINED);
+                    (variant == CDL_NORM_AUTO || variant == CDL_NORM_PIPELINED);
   ProfileScope ps(PROF_NORM_BWD, (res ? 8.0 : 6.0) * rows * cols + 6.0 * cols + 4.0 * rows, stream);
   if (pipe) {
     num_partials = sm_count();
@@ -851,7 +891,7 @@ int32_t rmsnorm_bwd_execute(const cdl_tensor* x, const cdl_tensor* dy, const cdl
         static_cast<const float*>(r_inv->ptr), r_inv->stride[0], partials, r, c);
   }
   CDL_CUDA(cudaGetLastError());
-  launch_pdl(dscale_finalize_kernel, dim3((c + 31) / 32), dim3(256), 0, stream,
+  launch_pdl(dscale_finalize_kernel, dim3((c + FIN_COLS - 1) / FIN_COLS), dim3(FIN_COLS * FIN_GROUPS), 0, stream,
              static_cast<const float*>(partials), num_partials, c, static_cast<float*>(dscale->ptr),
              static_cast<long long>(dscale->stride[0]));
   CDL_CUDA(cudaGetLastError());

@@ -240,7 +240,8 @@ int32_t sky1_block_fwd(const cdl_sky1_config* cfg, const cdl_sky1_weights* wt, c
 int32_t sky1_block_bwd(const cdl_sky1_config* cfg, const cdl_sky1_weights* wt, const void* x,
                        const float* rope_cos_sin, const cdl_sky1_saved* sv, const void* dy,
                        const cdl_sky1_grads* gr, void* dx, void* workspace, size_t workspace_bytes,
-                       int32_t phase, const cdl_sky1_ragged* rg, cudaStream_t st) {
+                       int32_t phase, const cdl_sky1_ragged* rg, cudaStream_t st,
+                       const cdl_sky1_grad_events* ev) {
   Dims d;
   CDL_CHECK(read_config(cfg, &d));
   CDL_CHECK(read_ragged(rg, &d));
@@ -282,22 +283,32 @@ int32_t sky1_block_bwd(const cdl_sky1_config* cfg, const cdl_sky1_weights* wt, c
   // (default) and a fixed summation order.
   const cdl_matmul_options wg_opts{CDL_GEMM_AUTO, (cfg->flags & CDL_SKY1_DETERMINISTIC) ? 1 : 0};
   const cdl_matmul_options* wg = &wg_opts;
+  // A data-parallel caller's events: recorded as soon as the kernels that complete a group of
+  // weight gradients are enqueued, so that group's all-reduce can start while the rest runs.
+  auto mark = [&](void* e) -> int32_t {
+    if (ev && e) CDL_CUDA(cudaEventRecord(static_cast<cudaEvent_t>(e), st));
+    return CDL_OK;
+  };
   if (phase != 2) {
   // FFN
   CDL_CHECK(matmul_execute(&actT, &tdy, &gwdown, &gwdown, 1.f, 1.f, st, wg));          // dWdown += act^T dy
+  CDL_CHECK(mark(ev ? ev->wdown : nullptr));
   // d_act = dy Wdown^T never reaches memory: the epilogue turns it into d_up and d_gate
   CDL_CHECK(matmul_execute_epi(&tdy, &wdownT, nullptr, &tdact, 1.f, 0.f, 2, &tgate, &tup, &tdgate, st));
   CDL_CHECK(rmsnorm_fwd_execute(&to, &g2, nullptr, cfg->eps, &th, &tr, st));        // recompute h2, r2
   CDL_CHECK(matmul_execute(&hT, &tdact, &gwup, &gwup, 1.f, 1.f, st, wg));               // dWup += h2^T d_up
+  CDL_CHECK(mark(ev ? ev->wup : nullptr));
   CDL_CHECK(matmul_execute(&tdact, &wupT, nullptr, &tdh, 1.f, 0.f, st));            // dh2 = d_up Wup^T
   CDL_CHECK(matmul_execute(&hT, &tdgate, &gwgate, &gwgate, 1.f, 1.f, st, wg));          // dWgate += h2^T d_gate
   CDL_CHECK(matmul_execute(&tdgate, &wgateT, &tdh, &tdh, 1.f, 1.f, st));            // dh2 += d_gate Wgate^T
   CDL_CHECK(rmsnorm_bwd_execute(&to, &tdh, &tdy, &g2, &tr, &tdo, &dg2, b.norm_scratch,
                                 b.norm_scratch_bytes, st));                         // d_o (+ dy)
+  CDL_CHECK(mark(ev ? ev->wgate_norm2 : nullptr));
   }
   if (phase == 1) return CDL_OK;
   // attention
   CDL_CHECK(matmul_execute(&attnT, &tdo, &gwo, &gwo, 1.f, 1.f, st, wg));                // dWo += attn^T d_o
+  CDL_CHECK(mark(ev ? ev->wo : nullptr));
   CDL_CHECK(matmul_execute(&tdo, &woT, nullptr, &tdattn, 1.f, 0.f, st));            // d_attn = d_o Wo^T
   // d_q and d_k leave the attention backward already rotated back (the transpose of the rotary
   // embedding runs in its store epilogues)
@@ -329,6 +340,7 @@ int32_t sky1_block_bwd(const cdl_sky1_config* cfg, const cdl_sky1_weights* wt, c
   CDL_CHECK(matmul_execute(&tdqkv, &wqkvT, nullptr, &tdh, 1.f, 0.f, st));           // dh1 = d_qkv Wqkv^T
   CDL_CHECK(rmsnorm_bwd_execute(&tx, &tdh, &tdo, &g1, &tr, &tdx, &dg1, b.norm_scratch,
                                 b.norm_scratch_bytes, st));                         // dx (+ d_o)
+  CDL_CHECK(mark(ev ? ev->wqkv_norm1 : nullptr));
   return CDL_OK;
 }
 
@@ -365,7 +377,7 @@ int32_t cdl_b200_sky1_block_bwd_ragged(const cdl_sky1_config* cfg, const cdl_sky
                                        cdl_stream stream) {
   if (!ragged) return cdl::fail(CDL_ERR_INVALID, "sky1_block_bwd_ragged: the ragged descriptor is required");
   return cdl::sky1_block_bwd(cfg, weights, x, rope_cos_sin, saved, dy, grads, dx, workspace,
-                             workspace_bytes, phase, ragged, static_cast<cudaStream_t>(stream));
+                             workspace_bytes, phase, ragged, static_cast<cudaStream_t>(stream), nullptr);
 }
 
 int32_t cdl_b200_sky1_block_workspace_bytes(const cdl_sky1_config* cfg, size_t* fwd_bytes,
@@ -391,7 +403,17 @@ int32_t cdl_b200_sky1_block_bwd(const cdl_sky1_config* cfg, const cdl_sky1_weigh
                                 const cdl_sky1_grads* grads, void* dx, void* workspace,
                                 size_t workspace_bytes, int32_t phase, cdl_stream stream) {
   return cdl::sky1_block_bwd(cfg, weights, x, rope_cos_sin, saved, dy, grads, dx, workspace,
-                             workspace_bytes, phase, nullptr, static_cast<cudaStream_t>(stream));
+                             workspace_bytes, phase, nullptr, static_cast<cudaStream_t>(stream), nullptr);
+}
+
+int32_t cdl_b200_sky1_block_bwd_events(const cdl_sky1_config* cfg, const cdl_sky1_weights* weights,
+                                       const void* x, const float* rope_cos_sin,
+                                       const cdl_sky1_ragged* ragged, const cdl_sky1_saved* saved,
+                                       const void* dy, const cdl_sky1_grads* grads, void* dx,
+                                       void* workspace, size_t workspace_bytes,
+                                       const cdl_sky1_grad_events* events, cdl_stream stream) {
+  return cdl::sky1_block_bwd(cfg, weights, x, rope_cos_sin, saved, dy, grads, dx, workspace,
+                             workspace_bytes, 0, ragged, static_cast<cudaStream_t>(stream), events);
 }
 
 }  // extern "C"

@@ -170,14 +170,35 @@ class Sky1Block:
         self._x = x
         return out
 
-    def backward(self, dy: torch.Tensor, dx: torch.Tensor | None = None, phase: int = 0) -> torch.Tensor:
+    #: gradient groups in the order the backward completes them (cdl_sky1_grad_events)
+    GRAD_GROUPS = (("wdown",), ("wup",), ("wgate", "norm2"), ("wo",), ("wqkv", "norm1"))
+
+    def backward(self, dy: torch.Tensor, dx: torch.Tensor | None = None, phase: int = 0,
+                 events=None) -> torch.Tensor:
         """dy: gradient of the forward's output. Accumulates into self.grads; returns dx.
-        phase 1 / 2 run the FFN half / the attention half (see cdl_b200_sky1_block_bwd)."""
+        phase 1 / 2 run the FFN half / the attention half (see cdl_b200_sky1_block_bwd).
+        `events`: five torch.cuda.Event, one per entry of GRAD_GROUPS, each recorded on the
+        current stream as soon as that group's gradients are complete (whole backward only)."""
         if self._x is None:
             raise _lib.CdlError(-1, "backward called before forward")
         if dy.dtype != torch.bfloat16 or dy.numel() != self._x.numel() or not dy.is_contiguous():
             raise _lib.CdlError(-1, "dy must be a contiguous bf16 tensor shaped like x")
         dx = torch.empty_like(dy) if dx is None else dx
+        if events is not None:
+            if phase != 0 or len(events) != len(self.GRAD_GROUPS):
+                raise _lib.CdlError(-1, "events: five events and the whole backward (phase 0)")
+            handles = []
+            for e in events:
+                if not e.cuda_event:  # torch creates the CUDA event at its first record
+                    e.record()
+                handles.append(e.cuda_event)
+            ev_c = _lib.CdlSky1GradEvents(*handles)
+            check(lib.cdl_b200_sky1_block_bwd_events(
+                ctypes.byref(self._cfg_c), ctypes.byref(self._w_c), self._x.data_ptr(),
+                self.table.data_ptr(), ctypes.byref(self._rg_c) if self._rg_c is not None else None,
+                ctypes.byref(self._s_c), dy.data_ptr(), ctypes.byref(self._g_c), dx.data_ptr(),
+                self.workspace.data_ptr(), self.workspace.numel(), ctypes.byref(ev_c), self._stream()))
+            return dx
         if self._rg_c is not None:
             check(lib.cdl_b200_sky1_block_bwd_ragged(
                 ctypes.byref(self._cfg_c), ctypes.byref(self._w_c), self._x.data_ptr(),

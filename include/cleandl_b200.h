@@ -534,6 +534,24 @@ int32_t cdl_b200_sky1_block_bwd(const cdl_sky1_config* cfg, const cdl_sky1_weigh
                                 const cdl_sky1_grads* grads, void* dx, void* workspace,
                                 size_t workspace_bytes, int32_t phase, cdl_stream stream);
 
+/* The whole backward with one CUDA event per group of weight gradients, for a data-parallel
+ * caller that reduces gradients while the backward still runs (finer than the two phases above and
+ * without returning to the host in between).  Each handle is a cudaEvent_t or NULL; the library
+ * records it on `stream` right after the last kernel that writes the group is enqueued, in this
+ * order: wdown; wup; wgate and norm2; wo; wqkv and norm1 (the last one also marks the end of the
+ * backward).  The caller lets its communication stream wait for an event and starts that group's
+ * all-reduce.  `ragged` may be NULL (dense batch).  No counterpart in the reference, whose
+ * data-parallel reduction runs after the backward graph (crates/sky-1/src/training). */
+typedef struct {
+  void *wdown, *wup, *wgate_norm2, *wo, *wqkv_norm1;
+} cdl_sky1_grad_events;
+int32_t cdl_b200_sky1_block_bwd_events(const cdl_sky1_config* cfg, const cdl_sky1_weights* weights,
+                                       const void* x, const float* rope_cos_sin,
+                                       const cdl_sky1_ragged* ragged, const cdl_sky1_saved* saved,
+                                       const void* dy, const cdl_sky1_grads* grads, void* dx,
+                                       void* workspace, size_t workspace_bytes,
+                                       const cdl_sky1_grad_events* events, cdl_stream stream);
+
 #ifdef __cplusplus
 }
 #endif

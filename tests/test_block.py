@@ -173,6 +173,45 @@ def test_block_config4_full_size_vs_f32_on_device(cdl, gpu_ok):
         assert err(blk.grads[n], g_ref[n]) <= 2e-2, n
 
 
+def test_block_backward_records_an_event_per_gradient_group(cdl, gpu_ok):
+    """cdl_b200_sky1_block_bwd_events: the whole backward with one event per group of weight
+    gradients.  A second stream that waits for a group's event and copies that group's gradients
+    must see their final values (that is what a data-parallel caller's all-reduce relies on), and
+    dx and the gradients equal the plain backward's bit for bit (fixed summation order)."""
+    sky1 = cdl.sky1
+    cfg = sky1.Sky1Config(deterministic=True, batch=2, seqlen=512, hidden=512, heads=4, kv_heads=4,
+                          head_dim=128, ffn=1024)
+    params = sky1.init_params(cfg, seed=12, std=0.05)
+    x = torch.randn(cfg.tokens, cfg.hidden, generator=torch.Generator().manual_seed(13)).to(torch.bfloat16).cuda()
+    dy = torch.randn(cfg.tokens, cfg.hidden, generator=torch.Generator().manual_seed(14)).to(torch.bfloat16).cuda()
+    ref = sky1.Sky1Block(cfg, params)
+    ref.zero_grads()
+    ref.forward(x)
+    dx_ref = ref.backward(dy)
+    blk = sky1.Sky1Block(cfg, params)
+    blk.zero_grads()
+    blk.forward(x)
+    events = [torch.cuda.Event() for _ in blk.GRAD_GROUPS]
+    side = torch.cuda.Stream()
+    torch.cuda.synchronize()
+    dx = blk.backward(dy, events=events)
+    early = {}
+    with torch.cuda.stream(side):
+        for ev, group in zip(events, blk.GRAD_GROUPS):
+            side.wait_event(ev)
+            for n in group:
+                early[n] = blk.grads[n].clone()
+    torch.cuda.synchronize()
+    assert cdl._lib.device_status() == 0
+    assert torch.equal(dx, dx_ref)
+    assert sorted(early) == sorted(sky1.PARAM_NAMES)
+    for n in sky1.PARAM_NAMES:
+        assert torch.equal(blk.grads[n], ref.grads[n]), n
+        assert torch.equal(early[n], ref.grads[n]), f"{n}: not final when its event fired"
+    with pytest.raises(cdl._lib.CdlError, match="events"):
+        blk.backward(dy, events=events[:3])
+
+
 def test_block_backward_in_two_phases_equals_whole_backward(cdl, gpu_ok):
     """The data-parallel step runs the backward as phase 1 (FFN half) then phase 2 (attention half)
     so that the FFN gradients can be reduced early.  With the fixed-summation-order option the two

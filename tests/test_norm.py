@@ -93,7 +93,8 @@ def test_fwd_empty_and_errors(cdl, gpu_ok):
 @pytest.mark.parametrize("rows,cols", [(1, 128), (37, 2048), (300, 1536), (1000, 2048), (64, 136),
                                        (50, 4096), (33, 8192)])
 @pytest.mark.parametrize("residual", [False, True])
-def test_bwd_cases(cdl, gpu_ok, rows, cols, residual):
+@pytest.mark.parametrize("variant", [1, 2], ids=["warp_per_row", "pipelined"])
+def test_bwd_cases(cdl, gpu_ok, rows, cols, residual, variant):
     gen = torch.Generator().manual_seed(3)
     x = torch.randn(rows, cols, generator=gen).to(torch.bfloat16)
     dy = torch.randn(rows, cols, generator=gen).to(torch.bfloat16)
@@ -103,7 +104,7 @@ def test_bwd_cases(cdl, gpu_ok, rows, cols, residual):
     fwd = cdl.ops.norm_fwd(x.cuda(), cdl.ops.NormFwdOpts(scale=w.cuda(), save_stats=True))
     dscale = dscale0.cuda().clone()
     dx = cdl.ops.norm_bwd(x.cuda(), dy.cuda(), w.cuda(), fwd.r_inv, dscale,
-                          residual_dy=None if res is None else res.cuda())
+                          residual_dy=None if res is None else res.cuda(), variant=variant)
     dx_ref, ds_ref = oracle.rmsnorm_bwd(to_f32(x), to_f32(dy), to_f32(w),
                                         None if res is None else to_f32(res), 1e-6,
                                         dscale_init=to_f32(dscale0))
@@ -127,6 +128,43 @@ def test_bwd_config2_determinism(cdl, gpu_ok):
     dx_ref, ds_ref = oracle.rmsnorm_bwd(to_f32(x), to_f32(dy), to_f32(w), None, 1e-6)
     assert np.abs(to_f32(dx1) - dx_ref).max() / np.abs(dx_ref).max() <= 1e-2
     assert np.abs(to_f32(ds1) - ds_ref).max() / np.abs(ds_ref).max() <= 1e-2
+
+
+def test_bwd_many_launches_back_to_back(cdl, gpu_ok):
+    """Thirty launches of the pipelined backward replayed from one CUDA graph on alternating
+    buffers, 443 rows per CTA.  The consumer warps of its shared-memory ring run independently; a
+    warp that reached a stage's next use before the previous use was taken once passed the parity
+    wait on a stale phase (garbage rows, then a stalled ring: status 711 / 712).  Every launch must
+    reproduce the single-launch result bit for bit and leave the status word clear."""
+    rows, cols, nb, launches = 65536, 2048, 2, 30
+    gen = torch.Generator(device="cuda").manual_seed(5)
+    rnd = lambda: torch.randn(rows, cols, device="cuda", generator=gen).to(torch.bfloat16)
+    xs, dys, rss = [rnd() for _ in range(nb)], [rnd() for _ in range(nb)], [rnd() for _ in range(nb)]
+    w = (1 + 0.02 * torch.randn(cols, device="cuda", generator=gen)).to(torch.bfloat16)
+    r_invs = [cdl.ops.norm_fwd(x, cdl.ops.NormFwdOpts(scale=w, save_stats=True)).r_inv for x in xs]
+    scr = torch.empty(cdl.ops.norm_bwd_scratch_bytes(rows, cols), dtype=torch.uint8, device="cuda")
+    want = []
+    for j in range(nb):
+        ds = torch.zeros(cols, device="cuda")
+        want.append((cdl.ops.norm_bwd(xs[j], dys[j], w, r_invs[j], ds, residual_dy=rss[j], scratch=scr), ds))
+    torch.cuda.synchronize()
+    dxs = [torch.empty_like(xs[0]) for _ in range(nb)]
+    dss = [torch.zeros(cols, device="cuda") for _ in range(launches)]
+    side = torch.cuda.Stream()
+    with torch.cuda.stream(side):
+        graph = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(graph, stream=side):
+            for i in range(launches):
+                j = i % nb
+                cdl.ops.norm_bwd(xs[j], dys[j], w, r_invs[j], dss[i], residual_dy=rss[j], scratch=scr, dx=dxs[j])
+        for _ in range(3):
+            graph.replay()
+    torch.cuda.synchronize()
+    assert cdl._lib.device_status() == 0
+    for j in range(nb):
+        assert torch.equal(dxs[j], want[j][0])
+    for i in range(launches):
+        assert torch.equal(dss[i], want[i % nb][1] * 3), i  # three replays accumulate into dscale
 
 
 def layernorm_reference(x, scale, bias, eps):
