@@ -5,8 +5,9 @@ Workload (benchmark configuration 4): hidden 2048, 16 heads x 128, RoPE, pre-RMS
 batch 8 x seq 2048 per GPU, weights ~ N(0, 0.02) bf16, tokens uniform over a 32768-token vocabulary,
 seed 3.  One step = token embedding lookup -> block forward -> block backward (weight gradients
 accumulated in f32) for one batch; at N > 1 every rank runs its own batch (weak scaling, data
-parallel) and the weight gradients are all-reduced with NCCL, the FFN bucket overlapping the
-attention half of the backward.
+parallel) and the weight gradients are all-reduced with NCCL in five slices of one flat f32 bucket,
+each slice as soon as the backward has completed it (an event per gradient group), on a second
+stream; the last slice drains under the next step's forward.
 
 Printed line (rank 0): `value` = tokens/s with inputs resident in HBM, timed with CUDA events over
 exactly K steps, max over ranks; `e2e` = the same through the public API with the step's token ids

@@ -76,6 +76,9 @@ struct Params {
   const float* rope_table;
   const int* rope_cu;  // cu_seqlens of a ragged batch (device), or nullptr
   int rope_seqlen, rope_cols, rope_nseq;
+  // Pair kernel: counter of the work units handed out beyond every cluster's first one (zero
+  // between launches; one counter per device and stream).
+  unsigned int* sched_counter;
   int* status;
 };
 
@@ -582,11 +585,23 @@ constexpr int PAIR_STAGE_BYTES = 2 * A_BYTES;  // A 128 x 64 and half of B 128 x
 constexpr int PAIR_M = 2 * BM;
 constexpr size_t PAIR_SMEM_BYTES = 1024 + PAIR_STAGES * PAIR_STAGE_BYTES + 256;
 
+// Work units are handed out at run time: a cluster's first unit is its index, every further one
+// comes from a global counter, so a cluster that finds its SMs late (another kernel, e.g. a
+// collective, holds them) takes less work instead of holding its fixed share back to the end.
+// The leader's producer thread draws the unit for step t and publishes it in slot t % SCHED_SLOTS
+// of both CTAs' rings: locally with a store and an arrival on sched_full, in the peer with one
+// st.async that carries the value and completes the peer's sched_full (armed by the peer's
+// producer thread with expect-tx).  No role can be SCHED_SLOTS units ahead of another (6 stages of
+// operands and 2 accumulators bound the distance), so slots are reused without a release barrier.
+constexpr int SCHED_SLOTS = 16;
+constexpr uint32_t SCHED_DONE = 0xffffffffu;
 struct PairBarriers {
   uint64_t full[PAIR_STAGES];
   uint64_t empty[PAIR_STAGES];
   uint64_t acc_full[2];
   uint64_t acc_empty[2];
+  uint64_t sched_full[SCHED_SLOTS];
+  uint32_t unit_ring[SCHED_SLOTS];
   uint32_t tmem_base;
   int abort_word;
 };
@@ -623,8 +638,12 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(THREADS, 1)
       mbar_init(&bars->acc_full[i], 1);
       mbar_init(&bars->acc_empty[i], 2 * EPI_WARPS);  // epilogue warps of both CTAs (leader's copy is used)
     }
+    for (int i = 0; i < SCHED_SLOTS; ++i) mbar_init(&bars->sched_full[i], 1);
     bars->abort_word = 0;
     fence_mbar_init();
+    // the peer's slots wait for the leader's 4-byte st.async
+    if (rank != 0)
+      for (int i = 0; i < SCHED_SLOTS; ++i) mbar_arrive_expect_tx(&bars->sched_full[i], 4);
   }
   if (warp == 1) {
     tmem_alloc_pair(&bars->tmem_base, TMEM_COLS);
@@ -647,7 +666,39 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(THREADS, 1)
     if (elect_one()) {
       uint32_t it = 0;
       bool ok = true;
-      for (int unit = cluster_id; unit < num_units && ok; unit += num_clusters) {
+      // The leader's producer also hands out the units (see PairBarriers).  Every cluster with a
+      // valid first unit draws from the counter after each unit it takes, until a draw runs past
+      // the last unit; the launch's last draw puts the counter back to zero.
+      const int fetchers = num_clusters < num_units ? num_clusters : num_units;
+      const unsigned total_draws = static_cast<unsigned>((num_units > num_clusters ? num_units - num_clusters : 0) + fetchers);
+      uint32_t unit_u = cluster_id < num_units ? static_cast<uint32_t>(cluster_id) : SCHED_DONE;
+      unsigned drawn = 0;  // the draw for the next step, under way while this step's tiles load
+      for (int t = 0; ok; ++t) {
+        const int slot = t % SCHED_SLOTS;
+        if (rank == 0) {
+          if (t > 0) {
+            if (p.sched_counter != nullptr) {
+              unit_u = static_cast<unsigned>(num_clusters) + drawn < static_cast<unsigned>(num_units)
+                           ? static_cast<uint32_t>(num_clusters) + drawn
+                           : SCHED_DONE;
+              if (drawn + 1 == total_draws) atomicExch(p.sched_counter, 0u);
+            } else {  // fixed round-robin assignment
+              const long long u = static_cast<long long>(cluster_id) + static_cast<long long>(t) * num_clusters;
+              unit_u = u < num_units ? static_cast<uint32_t>(u) : SCHED_DONE;
+            }
+          }
+          bars->unit_ring[slot] = unit_u;
+          mbar_arrive(&bars->sched_full[slot]);
+          st_async_u32(mapa_shared(smem_u32(&bars->unit_ring[slot]), 1), unit_u,
+                       mapa_shared(smem_u32(&bars->sched_full[slot]), 1));
+          if (unit_u != SCHED_DONE && p.sched_counter != nullptr) drawn = atomicAdd(p.sched_counter, 1u);
+        } else {
+          if (!mbar_wait(&bars->sched_full[slot], (t / SCHED_SLOTS) & 1, abort_word, 112)) break;
+          unit_u = bars->unit_ring[slot];
+          mbar_arrive_expect_tx(&bars->sched_full[slot], 4);  // armed again for step t + SCHED_SLOTS
+        }
+        if (unit_u == SCHED_DONE) break;
+        const int unit = static_cast<int>(unit_u);
         int tile, kb0, kb1, b, tm, tn;
         unit_range(unit, tile, kb0, kb1);
         tile_coords(p, tile, b, tm, tn);
@@ -692,7 +743,12 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(THREADS, 1)
       uint32_t it = 0;
       int t = 0;
       bool ok = true;
-      for (int unit = cluster_id; unit < num_units && ok; unit += num_clusters, ++t) {
+      for (; ok; ++t) {
+        const int slot = t % SCHED_SLOTS;
+        if (!mbar_wait(&bars->sched_full[slot], (t / SCHED_SLOTS) & 1, abort_word, 213)) break;
+        const uint32_t unit_u = bars->unit_ring[slot];
+        if (unit_u == SCHED_DONE) break;
+        const int unit = static_cast<int>(unit_u);
         int tile, kb0, kb1;
         unit_range(unit, tile, kb0, kb1);
         const int acc = t & 1;
@@ -732,7 +788,12 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(THREADS, 1)
     const int quad = warp & 3;
     const int half = (warp - 2) >> 2;
     int t = 0;
-    for (int unit = cluster_id; unit < num_units; unit += num_clusters, ++t) {
+    for (;; ++t) {
+      const int slot = t % SCHED_SLOTS;
+      if (!mbar_wait(&bars->sched_full[slot], (t / SCHED_SLOTS) & 1, abort_word, 312)) break;
+      const uint32_t unit_u = bars->unit_ring[slot];
+      if (unit_u == SCHED_DONE) break;
+      const int unit = static_cast<int>(unit_u);
       int tile, kb0, kb1, b, tm, tn;
       unit_range(unit, tile, kb0, kb1);
       tile_coords(p, tile, b, tm, tn);
@@ -764,6 +825,45 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(THREADS, 1)
     tmem_dealloc_pair(tmem_base, TMEM_COLS);
   }
   if (threadIdx.x == 0 && *abort_word != 0) atomicExch(p.status, *abort_word);
+}
+
+// Unit counters of the pair kernel's run-time scheduling: one per device and stream, zero between
+// launches (the kernel puts its counter back).  Launches on one stream run one after the other,
+// so they can share a counter; launches on different streams may overlap and must not.  Inside
+// the library's device image: nothing is allocated.  A launch that gets no counter (more than
+// SCHED_STREAMS streams on a device) runs with the fixed round-robin assignment.
+#ifndef CDL_GEMM_DYNAMIC
+#define CDL_GEMM_DYNAMIC 1
+#endif
+constexpr int SCHED_STREAMS = 256;
+__device__ unsigned int g_sched_counters[SCHED_STREAMS];
+
+static unsigned int* sched_counter_for(int dev, cudaStream_t stream) {
+#if CDL_GEMM_DYNAMIC
+  static std::mutex mu;
+  static unsigned int* base[64] = {};
+  static cudaStream_t owner[64][SCHED_STREAMS];
+  static int used[64] = {};
+  if (dev < 0 || dev >= 64) return nullptr;
+  std::lock_guard<std::mutex> lock(mu);
+  if (base[dev] == nullptr) {
+    void* ptr = nullptr;
+    if (cudaGetSymbolAddress(&ptr, g_sched_counters) != cudaSuccess) {
+      (void)cudaGetLastError();
+      return nullptr;
+    }
+    base[dev] = static_cast<unsigned int*>(ptr);
+  }
+  for (int i = 0; i < used[dev]; ++i)
+    if (owner[dev][i] == stream) return base[dev] + i;
+  if (used[dev] == SCHED_STREAMS) return nullptr;
+  owner[dev][used[dev]] = stream;
+  return base[dev] + used[dev]++;
+#else
+  (void)dev;
+  (void)stream;
+  return nullptr;
+#endif
 }
 
 // Splits a [rows, cols] (or batched) bf16 view into major-ness and leading dimension.
@@ -956,6 +1056,7 @@ int32_t matmul_execute_epi(const cdl_tensor* a, const cdl_tensor* b, const cdl_t
   p.alpha = alpha;
   p.beta = use_c ? beta : 0.0f;
   p.split_k = 1;
+  p.sched_counter = nullptr;
   p.atomic_out = 0;
   p.epi_mode = 0;
   p.aux0 = p.aux1 = nullptr;
@@ -1073,6 +1174,7 @@ int32_t matmul_execute_epi(const cdl_tensor* a, const cdl_tensor* b, const cdl_t
   if (use_pair) {
     const long long units = static_cast<long long>(p.num_tiles) * p.split_k;
     const int clusters = units < max_clusters[dev & 63] ? static_cast<int>(units) : max_clusters[dev & 63];
+    p.sched_counter = units > clusters ? sched_counter_for(dev, stream) : nullptr;
     CDL_CUDA(launch_pdl(gemm_bf16_pair_kernel, dim3(2 * clusters), dim3(THREADS), PAIR_SMEM_BYTES, stream,
                         tm_a, tm_b, p));
   } else {

@@ -322,6 +322,13 @@ __device__ __forceinline__ uint32_t mapa_shared(uint32_t addr, uint32_t rank) {
   asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(r) : "r"(addr), "r"(rank));
   return r;
 }
+// A 32-bit store into another CTA's shared memory that completes 4 bytes of the transaction
+// count of an mbarrier of that CTA: value and signal travel together, no fence on either side.
+__device__ __forceinline__ void st_async_u32(uint32_t cluster_addr, uint32_t value, uint32_t cluster_mbar) {
+  asm volatile("st.async.weak.shared::cluster.mbarrier::complete_tx::bytes.u32 [%0], %1, [%2];" ::"r"(cluster_addr),
+               "r"(value), "r"(cluster_mbar)
+               : "memory");
+}
 __device__ __forceinline__ void mbar_arrive_cluster(uint32_t cluster_addr) {
   // CTA-scope release (the default): the cluster-scope form measured 1000-1700 clk per arrive on
   // B200.  What is handed over through these barriers lives in tensor memory or was written by
