@@ -622,9 +622,28 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(THREADS, 1)
   const int num_clusters = gridDim.x >> 1;
   // Work unit = (tile, K slice); slices exist only in the accumulate-in-place form.
   const int num_units = p.num_tiles * p.split_k;
+  // Unit numbering with K slices: tiles are taken in chunks of one wave (as many tiles as the
+  // grid has clusters); within a chunk all tiles of K slice 0 come first, then all of slice 1, ...
+  // The clusters that run at the same time then work on neighbouring tiles of ONE slice and share
+  // its A and B panels through L2, and the chunk's slices follow each other while the chunk's
+  // part of D (19 MB at 74 tiles) is still in L2.  Weight gradient 2048 x 5632 x 16384 (251 MB of
+  // operands, 46 MB of f32 output read and written): numbered tile by tile (a wave = three slices
+  // of ~25 tiles, which share nothing) 693 MB read + 42 MB written; slice by slice over all tiles
+  // 525 + 75 MB (every slice pass brings all of D back).
   auto unit_range = [&](int unit, int& tile, int& kb0, int& kb1) {
-    tile = unit / p.split_k;
-    const int slice = unit - tile * p.split_k;
+    int slice;
+    if (p.split_k == 1) {
+      tile = unit;
+      slice = 0;
+    } else {
+      const int per_chunk = num_clusters * p.split_k;
+      const int chunk = unit / per_chunk;
+      const int r = unit - chunk * per_chunk;
+      const int first = chunk * num_clusters;
+      const int in_chunk = p.num_tiles - first < num_clusters ? p.num_tiles - first : num_clusters;
+      slice = r / in_chunk;
+      tile = first + (r - slice * in_chunk);
+    }
     kb0 = static_cast<int>(static_cast<long long>(slice) * p.k_blocks / p.split_k);
     kb1 = static_cast<int>(static_cast<long long>(slice + 1) * p.k_blocks / p.split_k);
   };
@@ -1166,6 +1185,15 @@ int32_t matmul_execute_epi(const cdl_tensor* a, const cdl_tensor* b, const cdl_t
         p.split_k = best_s;
         p.atomic_out = 1;
         p.c_mode = 0;  // D already holds C; the slices only add
+        // Only one K slice of the operands is live at a time (units are numbered slice by slice
+        // within a chunk of tiles): the raster panel may be as wide as that slice allows.
+        const double a_slice = 2.0 * static_cast<double>(M) * K / best_s;
+        const double b_panel_slice = 2.0 * BN * static_cast<double>(K) / best_s;
+        const double budget = static_cast<double>(CDL_GEMM_RASTER_BUDGET_MB) * 1024 * 1024;
+        int w = RASTER_W;
+        if (a_slice <= 0.75 * budget)
+          while (w > 2 && a_slice + w * b_panel_slice > budget) --w;
+        p.raster_w = w;
       }
     }
   }
