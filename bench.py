@@ -493,8 +493,8 @@ def run_ours(args) -> None:
 
 # DRAM bytes measured with Nsight Compute over the minimum bytes, per kind of GEMM launch (see the
 # two profiles named where these are used).
-TRAFFIC_RATIO_PLAIN = 1.14
-TRAFFIC_RATIO_WGRAD = 2.19
+TRAFFIC_RATIO_PLAIN = 1.10
+TRAFFIC_RATIO_WGRAD = 1.86
 
 
 def graph_time_ms(torch, fns, steps: int, replays: int = 3) -> float:
