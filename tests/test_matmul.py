@@ -153,6 +153,31 @@ def test_deterministic(cdl, gpu_ok):
     assert torch.equal(d1, d2)
 
 
+def test_pair_kernel_on_several_streams_at_once(cdl, gpu_ok):
+    """The CTA-pair kernel draws its work units from a counter that belongs to the launching
+    stream.  Products with many more tiles than the device has clusters, enqueued on four streams
+    so that they overlap on the device, each repeated back to back on its stream, must all equal
+    the product computed alone (bit for bit: bf16 output, no K slices), and the next launch on a
+    stream must find its counter at zero again."""
+    gen = torch.Generator(device="cuda").manual_seed(17)
+    m, k, n = 4096, 512, 4096  # 256 tiles of 256 x 256 on 74 clusters
+    streams = [torch.cuda.Stream() for _ in range(4)]
+    ab = [(torch.randn(m, k, device="cuda", generator=gen).to(torch.bfloat16),
+           torch.randn(k, n, device="cuda", generator=gen).to(torch.bfloat16)) for _ in streams]
+    want = [cdl.ops.matmul(a, b) for a, b in ab]
+    torch.cuda.synchronize()
+    got = [[None] * 6 for _ in streams]
+    for rep in range(6):
+        for i, st in enumerate(streams):
+            with torch.cuda.stream(st):
+                got[i][rep] = cdl.ops.matmul(*ab[i])
+    torch.cuda.synchronize()
+    assert cdl._lib.device_status() == 0
+    for i in range(len(streams)):
+        for rep in range(6):
+            assert torch.equal(got[i][rep], want[i]), (i, rep)
+
+
 def test_weight_gradient_form_summation_order_option(cdl, gpu_ok):
     """D (f32) += A^T . B with a long contraction: by default the K slices meet in D through f32
     atomics, so two runs agree only within the f32 summation bound; with the `deterministic`
