@@ -405,9 +405,10 @@ def run_ours(args) -> None:
         gemm = by_kind.get("gemm", [0, 0.0, 0.0])
         achieved = gemm[2] / (gemm[1] * 1e-3) / 1e12 if gemm[1] > 0 else None
         kernel_ms = {k: round(v[1] / args.steps, 4) for k, v in by_kind.items()}
-        # kernels launched per step: 15 GEMM (SwiGLU fused into two of them), 4 norm fwd,
-        # 2 x 2 norm bwd, 1 attn fwd, 3 attn bwd, 2 rope, 1 embedding
-        launches_per_step = 15 + 4 + 4 + 1 + 3 + 2 + 1
+        # kernels launched per step: 15 GEMM (SwiGLU fused into two of them, RoPE into the QKV
+        # projection), 4 norm fwd, 2 x 2 norm bwd, 1 attn fwd, 3 attn bwd (the inverse RoPE in
+        # their store epilogues), 1 embedding
+        launches_per_step = 15 + 4 + 4 + 1 + 3 + 1
         # DRAM traffic of the average GEMM launch.  The block's shapes are too large to capture
         # under Nsight Compute, so: the minimum bytes of each of the 15 GEMMs (operands read once,
         # outputs written once, accumulated outputs read and written, fused-epilogue operands
