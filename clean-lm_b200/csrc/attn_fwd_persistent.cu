@@ -7,11 +7,11 @@
 // bf16, O += P V with A = P from tensor memory, the two tiles alternating on the tensor core);
 // what differs:
 //
-//   * Persistent CTAs.  Work items are ordered by the number of key blocks they see and dealt to
-//     the CTAs in a boustrophedon (within 3 % of a dynamic longest-first schedule for the shapes
-//     measured), so barrier set-up, the tensor-memory allocation and the first loads are paid
-//     once per SM instead of once per 256 rows, and the next item's Q, K and V arrive while the
-//     current item's last blocks are computed.
+//   * Persistent CTAs.  Work items are ordered by the number of key blocks they see and handed
+//     out at run time, longest first (a counter per stream; see fixed_item_of), so barrier
+//     set-up, the tensor-memory allocation and the first loads are paid once per SM instead of
+//     once per 256 rows, and the next item's Q, K and V arrive while the current item's last
+//     blocks are computed.
 //   * One issuing warp per tile, each a stream across items.  A tile whose item is finished has
 //     its next item's first S = Q K^T issued at once, so the softmax warps find it when their
 //     output is stored, while the other tile still works on its last blocks (under causal
@@ -59,6 +59,7 @@ constexpr int ROWS_PER_ITEM = 2 * BQ;      // two tiles
 constexpr int TILE_BYTES = 128 * 128 * 2;  // a 128 x 128 bf16 tile as two [128 rows][64 d] panels
 constexpr int PANEL_BYTES = TILE_BYTES / 2;
 constexpr int KV_STAGES = 2;
+constexpr int ITEM_SLOTS = 16;
 constexpr int THREADS = 384;  // warp 0 TMA, warps 1-2 MMA (one per tile), warp 3 idle, warps 4-11 softmax
 constexpr int TMEM_COLS = 512;
 constexpr float RESCALE_THRESHOLD = 8.0f;  // log2 units
@@ -118,6 +119,7 @@ struct Params {
   const int* cu_k;
   int num_q_blocks;  // ceil(Sq / 256)
   int total_items;   // num_q_blocks * H * B
+  unsigned int* item_counter;  // items handed out beyond every CTA's first one (zero between launches), or nullptr
   int* status;
 };
 
@@ -125,6 +127,8 @@ struct Barriers {
   uint64_t q_full[2], q_empty[2];
   uint64_t k_full[KV_STAGES], k_empty[KV_STAGES], v_full[KV_STAGES], v_empty[KV_STAGES];
   uint64_t s_full[2], p_ready[2], o_done[2];
+  uint64_t item_full[ITEM_SLOTS], item_read[ITEM_SLOTS];
+  int item_ring[ITEM_SLOTS];
   uint32_t tmem_base;
   int abort_word;
 };
@@ -201,10 +205,17 @@ __device__ __forceinline__ int kv_blocks_for_tile(int Sq, int Sk, int causal, in
   return max_key < 0 ? 0 : max_key / BKV + 1;
 }
 
-// The k-th work item of CTA `cid` out of `nc`: items are ordered longest first (last query block
-// first) and dealt in a boustrophedon, so every CTA gets a similar mix of long and short items.
-// Negative when the CTA has no k-th item (and then no later one either).
-__device__ __forceinline__ int item_of(int k, int cid, int nc, int total) {
+// Work items are ordered longest first (last query block first).  A CTA's first item is its
+// index; every further one is drawn from a counter at run time by the producer lane, which
+// publishes the k-th item of the CTA in slot k % ITEM_SLOTS of a ring in shared memory (-1: no
+// further item).  The MMA lane (once per tile) and the softmax warps read the slot after its
+// barrier and report that on item_read; the producer refills a slot only when all ten readers
+// have (items without key blocks pass through no other barrier, so nothing else would bound how
+// far the producer runs ahead).  Handing items out at run
+// time is the longest-first schedule itself, and a CTA that finds its SM late (another kernel
+// holds it, e.g. a collective of a data-parallel step) takes fewer items instead of keeping a
+// fixed share back to the end.  Without a counter (fixed assignment): a boustrophedon deal.
+__device__ __forceinline__ int fixed_item_of(int k, int cid, int nc, int total) {
   if (static_cast<long long>(k) * nc >= total) return -1;
   const int idx = k * nc + ((k & 1) ? nc - 1 - cid : cid);
   return idx < total ? idx : -1;
@@ -270,6 +281,10 @@ __global__ void __launch_bounds__(THREADS, 1)
       mbar_init(&bars->p_ready[i], 4);  // one arrival per softmax warp of the tile
       mbar_init(&bars->o_done[i], 1);
     }
+    for (int i = 0; i < ITEM_SLOTS; ++i) {
+      mbar_init(&bars->item_full[i], 1);
+      mbar_init(&bars->item_read[i], 10);  // the eight softmax warps and the MMA lane's two tile cursors
+    }
     for (int i = 0; i < KV_STAGES; ++i) {
       mbar_init(&bars->k_full[i], 1);
       mbar_init(&bars->k_empty[i], 1);
@@ -301,8 +316,28 @@ __global__ void __launch_bounds__(THREADS, 1)
     if (elect_one()) {
       uint32_t kv_cnt = 0, q_cnt[2] = {0, 0};
       bool ok = true;
+      // Every CTA draws after each item it takes, until a draw runs past the last item; the
+      // launch's last draw puts the counter back to zero.
+      const int total = p_in.total_items;
+      const unsigned total_draws = static_cast<unsigned>((total > nc ? total - nc : 0) + (nc < total ? nc : total));
+      int idx = cid < total ? cid : -1;
+      unsigned drawn = 0;  // the draw for the next item
       for (int k = 0; ok; ++k) {
-        const int idx = item_of(k, cid, nc, p_in.total_items);
+        if (k > 0) {
+          if (p_in.item_counter != nullptr) {
+            idx = static_cast<unsigned>(nc) + drawn < static_cast<unsigned>(total) ? static_cast<int>(nc + drawn) : -1;
+            if (drawn + 1 == total_draws) atomicExch(p_in.item_counter, 0u);
+          } else {
+            idx = fixed_item_of(k, cid, nc, total);
+          }
+        }
+        if (k >= ITEM_SLOTS &&
+            !mbar_wait(&bars->item_read[k % ITEM_SLOTS], ((k / ITEM_SLOTS) - 1) & 1, abort_word, 124)) {
+          ok = false;
+          break;
+        }
+        bars->item_ring[k % ITEM_SLOTS] = idx;
+        mbar_arrive(&bars->item_full[k % ITEM_SLOTS]);
         if (idx < 0) break;
         const View v = view_of(p_in, idx);
         const int kvh = v.h / (p_in.H / p_in.Hkv);
@@ -341,6 +376,10 @@ __global__ void __launch_bounds__(THREADS, 1)
             tma_load_4d(s_v + s * TILE_BYTES + dh * PANEL_BYTES, &tmap_v, &bars->v_full[s], dh * 64,
                         v.k_base + j * BKV, kvh, v.bt);
         }
+        // The next item is drawn only now, when this item's last loads are on their way (two key
+        // blocks before its products end): items differ in length, and an item reserved earlier
+        // would be held back by a CTA that is busy while others run dry.
+        if (ok && p_in.item_counter != nullptr) drawn = atomicAdd(p_in.item_counter, 1u);
       }
     }
   } else if (warp == 1) {
@@ -404,15 +443,40 @@ __global__ void __launch_bounds__(THREADS, 1)
         int k, j, n;
         uint32_t slot, next_base, pend_slot, q_cnt, p_cnt;
         bool pend, acc;
+        bool open;  // the tile's next item has not been published yet (n == 0, slot >= next_base)
       };
-      Tile T0{-1, 0, 0, 0u, 0u, 0u, 0u, 0u, false, false};
+      Tile T0{-1, 0, 0, 0u, 0u, 0u, 0u, 0u, false, false, true};
       Tile T1 = T0;
-      // Moves a tile's cursor to the first block of the next item the tile takes part in.
-      auto next_item = [&](Tile& T, const int t) {
+      // Moves a tile's cursor to the first block of the next item the tile takes part in.  The
+      // items come from the producer's ring; one that is not published yet is waited for only
+      // when step r needs the answer, i.e. when the tile's next block could be at slot r + 1 or
+      // earlier.  (By then the producer can have published it: all it waits for before that is
+      // the release of slots that steps before r have released.  Waiting earlier could stall the
+      // other tile's products, which the producer may need in order to get there.)
+      auto next_item = [&](Tile& T, const int t, const int r) {
         while (true) {
-          ++T.k;
-          const int idx = item_of(T.k, cid, nc, p_in.total_items);
+          const int k = T.k + 1;
+          uint64_t* bar = &bars->item_full[k % ITEM_SLOTS];
+          const uint32_t par = (k / ITEM_SLOTS) & 1;
+          if (!mbar_test(bar, par)) {
+            if (static_cast<int>(T.next_base) > r + 1) {
+              T.open = true;
+              T.n = 0;
+              T.slot = T.next_base;
+              return;
+            }
+            if (!mbar_wait(bar, par, abort_word, 225)) {  // the abort word ends every other wait too
+              T.open = false;
+              T.n = 0;
+              T.slot = T.next_base;
+              return;
+            }
+          }
+          T.k = k;
+          const int idx = bars->item_ring[k % ITEM_SLOTS];
+          mbar_arrive(&bars->item_read[k % ITEM_SLOTS]);
           if (idx < 0) {
+            T.open = false;
             T.n = 0;
             T.slot = T.next_base;
             return;
@@ -422,6 +486,7 @@ __global__ void __launch_bounds__(THREADS, 1)
           T.next_base = base + v.n_max;
           const int n_t = t == 0 ? v.n0 : v.n1;
           if (n_t > 0) {
+            T.open = false;
             T.j = 0;
             T.n = n_t;
             T.slot = base;
@@ -429,8 +494,8 @@ __global__ void __launch_bounds__(THREADS, 1)
           }
         }
       };
-      next_item(T0, 0);
-      next_item(T1, 1);
+      next_item(T0, 0, -1);
+      next_item(T1, 1, -1);
       // Ring slots this lane has seen filled, per stage (slot + 1 of the latest one).
       uint32_t k_seen0 = 0, k_seen1 = 0, v_seen0 = 0, v_seen1 = 0;
       // One tile's part of step r: P V for slot r if the tile has it, then S = Q K^T of the tile's
@@ -438,6 +503,7 @@ __global__ void __launch_bounds__(THREADS, 1)
       // uses) is started only if its operands are there already, so that this step's other
       // products do not wait for it; otherwise it is started in the next step.
       auto turn = [&](Tile& T, const int t, const int r) -> bool {
+        if (T.open && !T.pend) next_item(T, t, r);
         if (T.pend && static_cast<int>(T.pend_slot) == r) {
           const uint32_t st = static_cast<uint32_t>(r) % KV_STAGES;
           if (t == 0) CDL_PROBE(r, 6); else CDL_PROBE(r, 7);
@@ -454,6 +520,7 @@ __global__ void __launch_bounds__(THREADS, 1)
           issue_pv(t, st, T.acc, r);
           T.pend = false;
           CDL_PROBE(r, 3 * t + 1);
+          if (T.open) next_item(T, t, r);
         }
         if (!T.pend && T.n > 0 && static_cast<int>(T.slot) <= r + 2) {
           const uint32_t s = T.slot;
@@ -482,7 +549,7 @@ __global__ void __launch_bounds__(THREADS, 1)
             T.acc = !first;
             if (T.j + 1 == T.n) {
               umma_commit(&bars->q_empty[t]);  // the last reader of Q_t
-              next_item(T, t);
+              next_item(T, t, r);
             } else {
               ++T.j;
               ++T.slot;
@@ -493,7 +560,7 @@ __global__ void __launch_bounds__(THREADS, 1)
       };
       // r = -1 is the prologue (the first Q K^T of each tile); the loop ends when both tiles have
       // neither a block to start nor a P V due.
-      for (int r = -1; T0.pend || T1.pend || T0.n > 0 || T1.n > 0; ++r) {
+      for (int r = -1; T0.pend || T1.pend || T0.n > 0 || T1.n > 0 || T0.open || T1.open; ++r) {
         if (!turn(T0, 0, r) || !turn(T1, 1, r)) break;
         // Every P V that reads V of slot r and every Q K^T that reads K of slot r + 1 has been
         // issued (a Q K^T is issued one or two steps before its slot's step).
@@ -520,7 +587,10 @@ __global__ void __launch_bounds__(THREADS, 1)
     bool ok = true;
 
     for (int k = 0; ok; ++k) {
-      const int idx = item_of(k, cid, nc, p_in.total_items);
+      if (!mbar_wait(&bars->item_full[k % ITEM_SLOTS], (k / ITEM_SLOTS) & 1, abort_word, 324)) break;
+      const int idx = bars->item_ring[k % ITEM_SLOTS];
+      __syncwarp();
+      if (lane == 0) mbar_arrive(&bars->item_read[k % ITEM_SLOTS]);
       if (idx < 0) break;
       const View v = view_of(p_in, idx);
       const int n_t = t == 0 ? v.n0 : v.n1;
@@ -747,6 +817,7 @@ int32_t attn_fwd_persistent_launch(const cdl_tensor* q, const cdl_tensor* k, con
   const long long items = static_cast<long long>(p.num_q_blocks) * H * B;
   if (items > INT32_MAX) return fail(CDL_ERR_UNSUPPORTED, "attention_fwd: too many work items");
   p.total_items = static_cast<int>(items);
+  p.item_counter = nullptr;
   p.status = device_status_ptr();
   if (!p.status) return fail(CDL_ERR_CUDA, "cannot resolve the device status word");
 
@@ -773,6 +844,7 @@ int32_t attn_fwd_persistent_launch(const cdl_tensor* q, const cdl_tensor* k, con
   if (attr_err != cudaSuccess)
     return fail(CDL_ERR_CUDA, "cudaFuncSetAttribute failed: %s", cudaGetErrorString(attr_err));
   const int grid = items < sm_count() ? static_cast<int>(items) : sm_count();
+  if (items > grid) p.item_counter = sched_counter_for(1, dev, stream);
   CDL_CUDA(launch_pdl(attn_fwd_persistent_kernel, dim3(grid), dim3(THREADS), SMEM_BYTES, stream, tq, tk, tv, p));
   CDL_CUDA(cudaGetLastError());
   return CDL_OK;

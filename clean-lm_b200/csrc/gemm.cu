@@ -846,45 +846,6 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(THREADS, 1)
   if (threadIdx.x == 0 && *abort_word != 0) atomicExch(p.status, *abort_word);
 }
 
-// Unit counters of the pair kernel's run-time scheduling: one per device and stream, zero between
-// launches (the kernel puts its counter back).  Launches on one stream run one after the other,
-// so they can share a counter; launches on different streams may overlap and must not.  Inside
-// the library's device image: nothing is allocated.  A launch that gets no counter (more than
-// SCHED_STREAMS streams on a device) runs with the fixed round-robin assignment.
-#ifndef CDL_GEMM_DYNAMIC
-#define CDL_GEMM_DYNAMIC 1
-#endif
-constexpr int SCHED_STREAMS = 256;
-__device__ unsigned int g_sched_counters[SCHED_STREAMS];
-
-static unsigned int* sched_counter_for(int dev, cudaStream_t stream) {
-#if CDL_GEMM_DYNAMIC
-  static std::mutex mu;
-  static unsigned int* base[64] = {};
-  static cudaStream_t owner[64][SCHED_STREAMS];
-  static int used[64] = {};
-  if (dev < 0 || dev >= 64) return nullptr;
-  std::lock_guard<std::mutex> lock(mu);
-  if (base[dev] == nullptr) {
-    void* ptr = nullptr;
-    if (cudaGetSymbolAddress(&ptr, g_sched_counters) != cudaSuccess) {
-      (void)cudaGetLastError();
-      return nullptr;
-    }
-    base[dev] = static_cast<unsigned int*>(ptr);
-  }
-  for (int i = 0; i < used[dev]; ++i)
-    if (owner[dev][i] == stream) return base[dev] + i;
-  if (used[dev] == SCHED_STREAMS) return nullptr;
-  owner[dev][used[dev]] = stream;
-  return base[dev] + used[dev]++;
-#else
-  (void)dev;
-  (void)stream;
-  return nullptr;
-#endif
-}
-
 // Splits a [rows, cols] (or batched) bf16 view into major-ness and leading dimension.
 struct OperandLayout {
   int mn_major;     // 1 when the non-contraction dimension is the contiguous one
@@ -1202,7 +1163,7 @@ int32_t matmul_execute_epi(const cdl_tensor* a, const cdl_tensor* b, const cdl_t
   if (use_pair) {
     const long long units = static_cast<long long>(p.num_tiles) * p.split_k;
     const int clusters = units < max_clusters[dev & 63] ? static_cast<int>(units) : max_clusters[dev & 63];
-    p.sched_counter = units > clusters ? sched_counter_for(dev, stream) : nullptr;
+    p.sched_counter = units > clusters ? sched_counter_for(0, dev, stream) : nullptr;
     CDL_CUDA(launch_pdl(gemm_bf16_pair_kernel, dim3(2 * clusters), dim3(THREADS), PAIR_SMEM_BYTES, stream,
                         tm_a, tm_b, p));
   } else {

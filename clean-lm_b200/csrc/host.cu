@@ -56,6 +56,52 @@ int sm_count() {
   return counts[dev];
 }
 
+// Work counters of the kernels that hand out their work at run time (the CTA-pair GEMM's units,
+// kind 0; the persistent attention forward's items, kind 1): one per kind, device and stream, zero
+// between launches (the kernel's last draw puts its counter back).  Launches on one stream run
+// one after the other, so they can share a counter; launches on different streams may overlap and
+// must not.  Inside the library's device image: nothing is allocated.  A launch that gets no
+// counter (more than SCHED_STREAMS streams on a device) runs with its fixed assignment.
+#ifndef CDL_DYNAMIC_WORK
+#define CDL_DYNAMIC_WORK 1
+#endif
+constexpr int SCHED_KINDS = 2;
+constexpr int SCHED_STREAMS = 256;
+__device__ unsigned int g_sched_counters[SCHED_KINDS * SCHED_STREAMS];
+
+unsigned int* sched_counter_for(int kind, int dev, cudaStream_t stream) {
+#if CDL_DYNAMIC_WORK
+  static std::mutex mu;
+  static unsigned int* base[kMaxDevices] = {};
+  static cudaStream_t owner[kMaxDevices][SCHED_STREAMS];
+  static int used[kMaxDevices] = {};
+  if (dev < 0 || dev >= kMaxDevices || kind < 0 || kind >= SCHED_KINDS) return nullptr;
+  std::lock_guard<std::mutex> lock(mu);
+  if (base[dev] == nullptr) {
+    void* ptr = nullptr;
+    if (cudaGetSymbolAddress(&ptr, g_sched_counters) != cudaSuccess) {
+      (void)cudaGetLastError();
+      return nullptr;
+    }
+    base[dev] = static_cast<unsigned int*>(ptr);
+  }
+  int slot = -1;
+  for (int i = 0; i < used[dev]; ++i)
+    if (owner[dev][i] == stream) slot = i;
+  if (slot < 0) {
+    if (used[dev] == SCHED_STREAMS) return nullptr;
+    slot = used[dev]++;
+    owner[dev][slot] = stream;
+  }
+  return base[dev] + kind * SCHED_STREAMS + slot;
+#else
+  (void)kind;
+  (void)dev;
+  (void)stream;
+  return nullptr;
+#endif
+}
+
 using EncodeTiledFn = CUresult (*)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*,
                                    const cuuint64_t*, const cuuint64_t*, const cuuint32_t*,
                                    const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,

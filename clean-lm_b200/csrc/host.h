@@ -74,6 +74,9 @@ inline cudaError_t launch_pdl(void (*kernel)(KArgs...), dim3 grid, dim3 block, s
   return cudaLaunchKernelEx(&cfg, kernel, static_cast<KArgs>(args)...);
 }
 
+// Device counter for a kernel that hands out its work at run time (see host.cu); nullptr: none.
+unsigned int* sched_counter_for(int kind, int dev, cudaStream_t stream);
+
 // Opt-in per-launch timing (cdl_b200_profile_start / _stop).  When enabled, a launcher brackets
 // its kernel with two pre-created CUDA events on the launching stream; when disabled the scope
 // costs one relaxed atomic load.
