@@ -392,6 +392,29 @@ def test_packed_bwd_with_rope_equals_bwd_then_inverse_rope(cdl, gpu_ok):
         cdl.ops.attention_bwd(qd, kd, vd, fwd.out, dod, fwd.lse, opts, rope_table=table[:100].contiguous())
 
 
+def test_forward_on_several_streams_at_once(cdl, gpu_ok):
+    """The persistent forward hands its work items out through a counter that belongs to the
+    launching stream.  Calls with many more items than SMs, enqueued on three streams so that they
+    overlap on the device and repeated back to back on each stream, must all reproduce the call
+    made alone bit for bit, and every launch must leave its counter at zero for the next one."""
+    streams = [torch.cuda.Stream() for _ in range(3)]
+    inputs = [tuple(t.cuda() for t in make(4, 2048, 2048, 16, 16, seed=40 + i)[:3]) for i in range(3)]  # 512 items each
+    opts = cdl.ops.AttentionOpts(causal=True)
+    want = [cdl.ops.attention_fwd(q, k, v, opts) for q, k, v in inputs]
+    torch.cuda.synchronize()
+    got = [[None] * 5 for _ in streams]
+    for rep in range(5):
+        for i, st in enumerate(streams):
+            with torch.cuda.stream(st):
+                got[i][rep] = cdl.ops.attention_fwd(*inputs[i], opts)
+    torch.cuda.synchronize()
+    assert cdl._lib.device_status() == 0
+    for i in range(len(streams)):
+        for rep in range(5):
+            assert torch.equal(got[i][rep].out, want[i].out), (i, rep)
+            assert torch.equal(got[i][rep].lse, want[i].lse), (i, rep)
+
+
 def test_packed_rejections(cdl, gpu_ok):
     z = lambda *s: torch.zeros(*s, dtype=torch.bfloat16, device="cuda")
     cu = torch.tensor([0, 8], dtype=torch.int32, device="cuda")
