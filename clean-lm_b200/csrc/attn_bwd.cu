@@ -67,6 +67,14 @@ static_assert(KV_SMEM_BYTES <= 232448 && Q_SMEM_BYTES <= 232448,
 // LOW + 2 HIGH = 3 x 168): with 56 the issuing lane spills.
 constexpr int KV_LOW_REGS = 72, KV_HIGH_REGS = 216;
 
+// Bytes of Q, dO, K, V a chunk of the CTA order may span (see cta_coords).  Measured at B 8 / 2,
+// S 2048, B 1 S 8192 and B 4 S 4096 against the old order (all blocks of one head, then the next
+// head): 16 MB 0.555 / 0.145 / 0.789 / 0.880 ms against 0.561 / 0.166 / 0.825 / 0.897; 8 MB 0.561 /
+// 0.162 / 0.837 / 0.900; 48 MB 0.575 / 0.154 / 0.81-0.84 (too many CTAs of one length in step).
+#ifndef CDL_ATTN_BWD_CHUNK_MB
+#define CDL_ATTN_BWD_CHUNK_MB 16
+#endif
+
 // Status code (device status word) of a packed sequence longer than max_seqlen_q / max_seqlen_k.
 constexpr int STATUS_SEQ_EXCEEDS_BOUND = 921;
 
@@ -91,6 +99,9 @@ struct Params {
   // before the rotation.
   const float* rope;
   int rope_rows;
+  // CTA order (see cta_coords): number of blocks along the sequence, heads x batch, heads per chunk
+  int kv_blocks, kv_heads_total, kv_chunk;  // dK/dV kernel
+  int q_blocks, q_heads_total, q_chunk;     // dQ kernel
   int* status;
 };
 
@@ -254,6 +265,23 @@ __global__ void __launch_bounds__(256)
 
 
 // ---------------------------------------------------------------- dK / dV kernel
+// Order of the one-shot CTAs.  A CTA's length is the number of blocks its own block sees, which
+// under the causal mask runs from all of them down to one, and the hardware places CTAs in index
+// order as SMs free up: the grid is one-dimensional and counts, within a chunk of `chunk` (head,
+// batch) pairs, the longest block of every pair first, then the second longest, ...; so the
+// launch ends on its shortest CTAs instead of on a full-length one, and a chunk's Q, dO, K, V
+// (sized to stay in L2) are re-read from L2 by the CTAs that follow.  `rank` is the block's place in
+// the order longest-first, `hb` the (head, batch) pair.
+__device__ __forceinline__ void cta_coords(int linear, int blocks, int heads_total, int chunk, int& rank, int& hb) {
+  const int per_chunk = chunk * blocks;
+  const int c = linear / per_chunk;
+  const int r = linear - c * per_chunk;
+  const int first = c * chunk;
+  const int in_chunk = heads_total - first < chunk ? heads_total - first : chunk;
+  rank = r / in_chunk;
+  hb = first + (r - rank * in_chunk);
+}
+
 __global__ void __launch_bounds__(THREADS, 1)
     attn_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap tmap_q,
                          const __grid_constant__ CUtensorMap tmap_k,
@@ -266,13 +294,16 @@ __global__ void __launch_bounds__(THREADS, 1)
   // the next one: keys beyond Sk are masked, queries beyond Sq carry lse2 = +inf (P = 0), and
   // neither is stored.
   Params p = p_in;
-  int q_base = 0, k_base = 0, bt = blockIdx.z;
+  int cta_rank, cta_hb;
+  cta_coords(static_cast<int>(blockIdx.x), p_in.kv_blocks, p_in.kv_heads_total, p_in.kv_chunk, cta_rank, cta_hb);
+  const int cta_b = cta_hb / p_in.Hkv;
+  int q_base = 0, k_base = 0, bt = cta_b;
   if (p_in.cu_q != nullptr) {
     grid_dep_wait();  // the sequence offsets may come from the previous kernel of the stream
-    q_base = p_in.cu_q[blockIdx.z];
-    p.Sq = p_in.cu_q[blockIdx.z + 1] - q_base;
-    k_base = p_in.cu_k[blockIdx.z];
-    p.Sk = p_in.cu_k[blockIdx.z + 1] - k_base;
+    q_base = p_in.cu_q[cta_b];
+    p.Sq = p_in.cu_q[cta_b + 1] - q_base;
+    k_base = p_in.cu_k[cta_b];
+    p.Sk = p_in.cu_k[cta_b + 1] - k_base;
     bt = 0;
     // The grids and the statistics scratch are sized with the caller's bounds: a longer sequence
     // is cut at the bound (nothing beyond the scratch is touched) and reported.
@@ -300,9 +331,9 @@ __global__ void __launch_bounds__(THREADS, 1)
 
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
-  const int n_blk = blockIdx.x;
-  const int kvh = blockIdx.y;
-  const int b = blockIdx.z;
+  const int n_blk = cta_rank;  // key block 0 is seen by every query block: the longest CTA
+  const int kvh = cta_hb % p_in.Hkv;
+  const int b = cta_b;
   const int key0 = n_blk * BKV;
   const int group = p.H / p.Hkv;
   const int shift = p.Sk - p.Sq;  // query i sees keys <= i + shift
@@ -689,13 +720,16 @@ __global__ void __launch_bounds__(THREADS, 1)
                        const __grid_constant__ CUtensorMap tmap_dq, const Params p_in) {
   extern __shared__ __align__(1024) uint8_t smem[];
   Params p = p_in;  // per-sequence view, as in the dK/dV kernel
-  int q_base = 0, k_base = 0, bt = blockIdx.z;
+  int cta_rank, cta_hb;
+  cta_coords(static_cast<int>(blockIdx.x), p_in.q_blocks, p_in.q_heads_total, p_in.q_chunk, cta_rank, cta_hb);
+  const int cta_b = cta_hb / p_in.H;
+  int q_base = 0, k_base = 0, bt = cta_b;
   if (p_in.cu_q != nullptr) {
     grid_dep_wait();  // the sequence offsets may come from the previous kernel of the stream
-    q_base = p_in.cu_q[blockIdx.z];
-    p.Sq = p_in.cu_q[blockIdx.z + 1] - q_base;
-    k_base = p_in.cu_k[blockIdx.z];
-    p.Sk = p_in.cu_k[blockIdx.z + 1] - k_base;
+    q_base = p_in.cu_q[cta_b];
+    p.Sq = p_in.cu_q[cta_b + 1] - q_base;
+    k_base = p_in.cu_k[cta_b];
+    p.Sk = p_in.cu_k[cta_b + 1] - k_base;
     bt = 0;
     if (p.Sq > p_in.Sq || p.Sk > p_in.Sk) {
       if (threadIdx.x == 0) atomicExch(p.status, STATUS_SEQ_EXCEEDS_BOUND);
@@ -716,9 +750,9 @@ __global__ void __launch_bounds__(THREADS, 1)
 
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
-  const int q_block = gridDim.x - 1 - blockIdx.x;  // most keys first
-  const int h = blockIdx.y;
-  const int b = blockIdx.z;
+  const int q_block = p_in.q_blocks - 1 - cta_rank;  // the last query block sees the most keys
+  const int h = cta_hb % p_in.H;
+  const int b = cta_b;
   const int kvh = h / (p.H / p.Hkv);
   const int q0 = q_block * BQ;
   const int n_kv = dq_kv_blocks(p, q0);
@@ -1006,11 +1040,12 @@ size_t attn_bwd_scratch_bytes(long long B, long long Sq, long long H) {
 
 // Launches preprocess, dK/dV and dQ for a filled-in Params (p.Sq / p.Sk: the lengths the grids
 // are sized with; q .. d_o: [B, S, H, D] views; lse strides as (batch, head, row)).
-static int32_t bwd_run(const attn_bwd::Params& p, const cdl_tensor* q, const cdl_tensor* k,
+static int32_t bwd_run(const attn_bwd::Params& p_const, const cdl_tensor* q, const cdl_tensor* k,
                        const cdl_tensor* v, const cdl_tensor* o, const cdl_tensor* d_o,
                        const float* lse, long long lse_sb, long long lse_sh, long long lse_ss,
                        const cdl_tensor* dq, const cdl_tensor* dk, const cdl_tensor* dv,
                        double work, cudaStream_t stream) {
+  attn_bwd::Params p = p_const;  // the CTA-order fields are filled in below
   using namespace attn_bwd;
   static std::once_flag attr_once[64];
   int dev = 0;
@@ -1060,15 +1095,26 @@ static int32_t bwd_run(const attn_bwd::Params& p, const cdl_tensor* q, const cdl
     tdk = tk;
     tdv = tk;
   }
+  // (head, batch) pairs per chunk of the CTA order: their Q, dO, K and V should stay in L2
+  auto chunk_of = [&](long long heads_total) {
+    const double per_head = 4.0 * 2.0 * D * static_cast<double>(Sq > Sk ? Sq : Sk);
+    long long c = static_cast<long long>(static_cast<double>(CDL_ATTN_BWD_CHUNK_MB) * 1024 * 1024 / per_head);
+    if (c < 1) c = 1;
+    return static_cast<int>(c < heads_total ? c : heads_total);
+  };
+  p.kv_blocks = static_cast<int>((Sk + BKV - 1) / BKV);
+  p.kv_heads_total = static_cast<int>(Hkv * B);
+  p.kv_chunk = chunk_of(Hkv * B);
+  p.q_blocks = static_cast<int>((Sq + BQ - 1) / BQ);
+  p.q_heads_total = static_cast<int>(H * B);
+  p.q_chunk = chunk_of(H * B);
   if (have_k) {
-    dim3 grid(static_cast<unsigned>((Sk + BKV - 1) / BKV), static_cast<unsigned>(Hkv),
-              static_cast<unsigned>(B));
+    dim3 grid(static_cast<unsigned>(static_cast<long long>(p.kv_blocks) * p.kv_heads_total));
     CDL_CUDA(launch_pdl(attn_bwd_dkdv_kernel, grid, dim3(THREADS), KV_SMEM_BYTES, stream, tq, tk, tv, tdo, tdk, tdv, p));
     CDL_CUDA(cudaGetLastError());
   }
   if (have_q) {
-    dim3 grid(static_cast<unsigned>((Sq + BQ - 1) / BQ), static_cast<unsigned>(H),
-              static_cast<unsigned>(B));
+    dim3 grid(static_cast<unsigned>(static_cast<long long>(p.q_blocks) * p.q_heads_total));
     CDL_CUDA(launch_pdl(attn_bwd_dq_kernel, grid, dim3(THREADS), Q_SMEM_BYTES, stream, tq, tk, tv, tdo, tdq, p));
     CDL_CUDA(cudaGetLastError());
   }
