@@ -9,9 +9,9 @@ The global batch is the same whatever the number of ranks: rank r of N takes seq
 one-rank curve up to the order of the f32 gradient sums -- that is the check of the product's
 data-parallel reduction (Sky1LM._reduce) at full size.
 
-    python tests/lm_curve_config5.py --steps 50 --torch-bf16-steps 50 --torch-f32-steps 3 --out gpurun_out/lm_curve_n1.json
+    python tests/lm_curve_config5.py --steps 50 --torch-bf16-steps 50 --torch-f32-steps 3 --out lm_curve_n1.json
     python -m torch.distributed.run --nnodes=1 --nproc-per-node 8 --master-addr 127.0.0.1 \\
-        --master-port 29511 tests/lm_curve_config5.py --steps 50 --out gpurun_out/lm_curve_n8.json
+        --master-port 29511 tests/lm_curve_config5.py --steps 50 --out lm_curve_n8.json
 
 The torch arms are the checker (oracle/lm_ref.py): `f32` = full f32 products on bf16-rounded
 weights; `bf16` = the same graph under torch.autocast(bfloat16), i.e. bf16 matrix products with f32
