@@ -133,20 +133,64 @@ __device__ __forceinline__ float ex2(float x) {
 #define CDL_POLY_OF_16 6
 #endif
 constexpr int POLY_OF_16 = CDL_POLY_OF_16;
-template <int C>
-__device__ __forceinline__ float exp2_mixed(float x) {
-  if constexpr ((C & 15) < POLY_OF_16) return exp2_poly(x);
-  else return ex2(x);
+// Two polynomial exponentials at once with packed f32x2 arithmetic (one issue slot for two lanes
+// of work; the scheme of exp2_poly in ptx.cuh).
+__device__ __forceinline__ void exp2_poly_pair(float x0, float x1, float& r0, float& r1) {
+  auto pack2 = [](float lo, float hi) {
+    uint64_t r;
+    asm("mov.b64 %0, {%1, %2};" : "=l"(r) : "f"(lo), "f"(hi));
+    return r;
+  };
+  auto unpack2 = [](uint64_t v, float& lo, float& hi) { asm("mov.b64 {%0, %1}, %2;" : "=f"(lo), "=f"(hi) : "l"(v)); };
+  auto fma2 = [](uint64_t a, uint64_t b, uint64_t c) {
+    uint64_t d;
+    asm("fma.rn.f32x2 %0, %1, %2, %3;" : "=l"(d) : "l"(a), "l"(b), "l"(c));
+    return d;
+  };
+  auto add2 = [](uint64_t a, uint64_t b) {
+    uint64_t d;
+    asm("add.rn.f32x2 %0, %1, %2;" : "=l"(d) : "l"(a), "l"(b));
+    return d;
+  };
+  auto sub2 = [](uint64_t a, uint64_t b) {
+    uint64_t d;
+    asm("sub.rn.f32x2 %0, %1, %2;" : "=l"(d) : "l"(a), "l"(b));
+    return d;
+  };
+  const uint64_t xc = pack2(fmaxf(x0, -126.0f), fmaxf(x1, -126.0f));
+  const uint64_t magic = pack2(12582912.0f, 12582912.0f);
+  const uint64_t t = add2(xc, magic);
+  const uint64_t f = sub2(xc, sub2(t, magic));
+  uint64_t r = fma2(f, pack2(0.0551716685f, 0.0551716685f), pack2(0.2426111251f, 0.2426111251f));
+  r = fma2(r, f, pack2(0.6932609677f, 0.6932609677f));
+  r = fma2(r, f, pack2(0.9999280572f, 0.9999280572f));
+  float t0, t1, p0, p1;
+  unpack2(t, t0, t1);
+  unpack2(r, p0, p1);
+  r0 = __int_as_float(__float_as_int(p0) + (__float_as_int(t0) << 23));
+  r1 = __int_as_float(__float_as_int(p1) + (__float_as_int(t1) << 23));
 }
 
+// Columns C and C + 1 (C even): the first POLY_OF_16 (even) of every 16 take the polynomial.
 template <int C>
 __device__ __forceinline__ void exp2_row_step(const float (&x)[64], float (&y)[64]) {
   if constexpr (C < 64) {
-    y[C] = exp2_mixed<C>(x[C]);
-    exp2_row_step<C + 1>(x, y);
+#ifndef CDL_ATTN_BWD_SCALAR_POLY
+    if constexpr ((C & 15) < POLY_OF_16) {
+      exp2_poly_pair(x[C], x[C + 1], y[C], y[C + 1]);
+    } else {
+      y[C] = ex2(x[C]);
+      y[C + 1] = ex2(x[C + 1]);
+    }
+#else
+    y[C] = (C & 15) < POLY_OF_16 ? exp2_poly(x[C]) : ex2(x[C]);
+    y[C + 1] = ((C + 1) & 15) < POLY_OF_16 ? exp2_poly(x[C + 1]) : ex2(x[C + 1]);
+#endif
+    exp2_row_step<C + 2>(x, y);
   }
 }
-// y[c] = 2^x[c] for a thread's 64 elements, the two pipes interleaved element by element.
+static_assert(POLY_OF_16 % 2 == 0, "the polynomial takes column pairs");
+
 __device__ __forceinline__ void exp2_row64(const float (&x)[64], float (&y)[64]) {
   exp2_row_step<0>(x, y);
 }
