@@ -126,6 +126,30 @@ __device__ __forceinline__ float ex2(float x) {
   asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
   return y;
 }
+// Packed f32x2 arithmetic: one issue slot for two lanes of work.
+__device__ __forceinline__ uint64_t pk2(float lo, float hi) {
+  uint64_t r;
+  asm("mov.b64 %0, {%1, %2};" : "=l"(r) : "f"(lo), "f"(hi));
+  return r;
+}
+__device__ __forceinline__ void upk2(uint64_t v, float& lo, float& hi) {
+  asm("mov.b64 {%0, %1}, %2;" : "=f"(lo), "=f"(hi) : "l"(v));
+}
+__device__ __forceinline__ uint64_t fma_x2(uint64_t a, uint64_t b, uint64_t c) {
+  uint64_t d;
+  asm("fma.rn.f32x2 %0, %1, %2, %3;" : "=l"(d) : "l"(a), "l"(b), "l"(c));
+  return d;
+}
+__device__ __forceinline__ uint64_t sub_x2(uint64_t a, uint64_t b) {
+  uint64_t d;
+  asm("sub.rn.f32x2 %0, %1, %2;" : "=l"(d) : "l"(a), "l"(b));
+  return d;
+}
+__device__ __forceinline__ uint64_t mul_x2(uint64_t a, uint64_t b) {
+  uint64_t d;
+  asm("mul.rn.f32x2 %0, %1, %2;" : "=l"(d) : "l"(a), "l"(b));
+  return d;
+}
 
 // Of every 16 exponentials, this many go to the polynomial: it balances the MUFU pipe against the
 // FMA pipe for the instruction mix of the P phases (one FMA per element plus six per polynomial).
@@ -548,7 +572,7 @@ __global__ void __launch_bounds__(THREADS, 1)
       return ct < 128 ? p.lse2[base + ct] : p.delta[base + ct - 128];
     };
     auto store_stat = [&](int stage, float v) {
-      if (ct < 128) s_lse[stage * 128 + ct] = v;
+      if (ct < 128) s_lse[stage * 128 + ct] = -v;  // negated: it is the addend of a packed FMA
       else s_delta[stage * 128 + ct - 128] = v;
     };
     float pr[64];
@@ -566,13 +590,17 @@ __global__ void __launch_bounds__(THREADS, 1)
         tmem_ld32(tmem_base + lane_addr + KV_COL_S + wg * 64 + 32, sr[1]);
         tmem_wait_ld();
         float x[64];
+        const uint64_t scale2 = pk2(p.scale_log2, p.scale_log2);
 #pragma unroll
         for (int c4 = 0; c4 < 16; ++c4) {
-          const float4 l4 = lse_s[c4];
-          x[c4 * 4 + 0] = fmaf(__uint_as_float(sr[(c4 * 4 + 0) >> 5][(c4 * 4 + 0) & 31]), p.scale_log2, -l4.x);
-          x[c4 * 4 + 1] = fmaf(__uint_as_float(sr[(c4 * 4 + 1) >> 5][(c4 * 4 + 1) & 31]), p.scale_log2, -l4.y);
-          x[c4 * 4 + 2] = fmaf(__uint_as_float(sr[(c4 * 4 + 2) >> 5][(c4 * 4 + 2) & 31]), p.scale_log2, -l4.z);
-          x[c4 * 4 + 3] = fmaf(__uint_as_float(sr[(c4 * 4 + 3) >> 5][(c4 * 4 + 3) & 31]), p.scale_log2, -l4.w);
+          const float4 l4 = lse_s[c4];  // the statistics are stored negated (store_stat)
+          const int c = c4 * 4;
+          upk2(fma_x2(pk2(__uint_as_float(sr[c >> 5][c & 31]), __uint_as_float(sr[c >> 5][(c & 31) + 1])), scale2,
+                      pk2(l4.x, l4.y)),
+               x[c], x[c + 1]);
+          upk2(fma_x2(pk2(__uint_as_float(sr[c >> 5][(c & 31) + 2]), __uint_as_float(sr[c >> 5][(c & 31) + 3])), scale2,
+                      pk2(l4.z, l4.w)),
+               x[c + 2], x[c + 3]);
         }
         exp2_row64(x, pr);
         if (need_mask) {  // warp-uniform; only blocks on the diagonal or at the end of the keys
@@ -627,9 +655,13 @@ __global__ void __launch_bounds__(THREADS, 1)
           const float dl[8] = {d0.x, d0.y, d0.z, d0.w, d1.x, d1.y, d1.z, d1.w};
           float d[8];
 #pragma unroll
-          for (int j = 0; j < 8; ++j) {
+          for (int j = 0; j < 8; j += 2) {
             const int c = ch * 8 + j;
-            d[j] = pr[c] * (__uint_as_float(dr[c >> 5][c & 31]) - dl[j]);  // scale: dK epilogue
+            // (scale: dK epilogue)
+            upk2(mul_x2(pk2(pr[c], pr[c + 1]),
+                        sub_x2(pk2(__uint_as_float(dr[c >> 5][c & 31]), __uint_as_float(dr[c >> 5][(c & 31) + 1])),
+                               pk2(dl[j], dl[j + 1]))),
+                 d[j], d[j + 1]);
           }
           pk[ch * 4 + 0] = pack_bf16x2(d[0], d[1]);
           pk[ch * 4 + 1] = pack_bf16x2(d[2], d[3]);
@@ -963,7 +995,11 @@ __global__ void __launch_bounds__(THREADS, 1)
         tmem_wait_ld();
         float x[64];
 #pragma unroll
-        for (int c = 0; c < 64; ++c) x[c] = fmaf(__uint_as_float(sr[c >> 5][c & 31]), p.scale_log2, -lse2);
+        const uint64_t scale2 = pk2(p.scale_log2, p.scale_log2), neg_lse2 = pk2(-lse2, -lse2);
+#pragma unroll
+        for (int c = 0; c < 64; c += 2)
+          upk2(fma_x2(pk2(__uint_as_float(sr[c >> 5][c & 31]), __uint_as_float(sr[c >> 5][(c & 31) + 1])), scale2, neg_lse2),
+               x[c], x[c + 1]);
         exp2_row64(x, pr);
         if (need_mask) {  // warp-uniform
 #pragma unroll
@@ -980,10 +1016,16 @@ __global__ void __launch_bounds__(THREADS, 1)
         tmem_ld32(tmem_base + lane_addr + Q_COL_DP + wg * 64 + 32, dr[1]);
         tmem_wait_ld();
 #pragma unroll
+        const uint64_t delta2 = pk2(delta, delta);
+#pragma unroll
         for (int c = 0; c < 32; ++c) {
           // without the softmax scale: it is applied once, when dQ leaves tensor memory
-          const float d0 = pr[2 * c] * (__uint_as_float(dr[(2 * c) >> 5][(2 * c) & 31]) - delta);
-          const float d1 = pr[2 * c + 1] * (__uint_as_float(dr[(2 * c + 1) >> 5][(2 * c + 1) & 31]) - delta);
+          float d0, d1;
+          upk2(mul_x2(pk2(pr[2 * c], pr[2 * c + 1]),
+                      sub_x2(pk2(__uint_as_float(dr[(2 * c) >> 5][(2 * c) & 31]),
+                                 __uint_as_float(dr[(2 * c) >> 5][((2 * c) & 31) + 1])),
+                             delta2)),
+               d0, d1);
           pk[c] = pack_bf16x2(d0, d1);
         }
       }
