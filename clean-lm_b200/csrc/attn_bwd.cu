@@ -108,7 +108,7 @@ struct Params {
 struct KvBarriers {
   uint64_t kv_full;
   uint64_t q_full[2], q_empty[2], do_full[2], do_empty[2];
-  uint64_t s_full, dp_full, p_ready, ds_ready, dk_done;
+  uint64_t s_full, dp_full, p_ready, ds_ready, dv_done, dk_done;
   uint32_t tmem_base;
   int abort_word;
 };
@@ -425,6 +425,7 @@ __global__ void __launch_bounds__(THREADS, 1)
     // serialised (measured in the forward kernel: ~500 clk for 128 of them).
     mbar_init(&bars->p_ready, 8);
     mbar_init(&bars->ds_ready, 8);
+    mbar_init(&bars->dv_done, 1);
     mbar_init(&bars->dk_done, 1);
     bars->abort_word = 0;
     fence_mbar_init();
@@ -534,6 +535,7 @@ __global__ void __launch_bounds__(THREADS, 1)
         for (int k = 0; k < 8; ++k)
           umma_ts(d_dv, d_s + acol(k), desc_at(df, koff_mn(k)), idesc_kmn, k != 0 ? 1u : acc);
         umma_commit(&bars->do_empty[s]);  // dP^T(it) and dV(it) were the readers of this dO stage
+        if (!has_next) umma_commit(&bars->dv_done);  // dV is final: its rows leave while dK finishes
         // S^T of the next query block; it overwrites P^T, which dV (issued above) reads first.
         if (has_next) issue_s(s ^ 1);
         // dK += dS^T Q  (A = dS^T from TMEM, written over dP^T)
@@ -691,13 +693,13 @@ __global__ void __launch_bounds__(THREADS, 1)
 
     // ---- epilogue: dV and dK rows of this key block
     if (ok && iters > 0) {
-      ok = mbar_wait(&bars->dk_done, 0, abort_word, 324);
+      ok = mbar_wait(&bars->dv_done, 0, abort_word, 325);
       tc_fence_after();
     }
     if (ok) {
       // The tiles go out through shared memory and one TMA store per 64-column panel: a thread
-      // owns a row, so direct stores would touch 32 rows per instruction.  The Q stages are free
-      // (every product has completed); the panel layout is the loads' 128-byte swizzle.  A store
+      // owns a row, so direct stores would touch 32 rows per instruction.  The staging tiles are
+      // operand stages whose readers have completed; the panel layout is the loads' 128-byte swizzle.  A store
       // clips rows beyond the tensor, not rows of the next packed sequence: a partial block of a
       // packed sequence stores its rows directly.
       const bool staged = p.cu_k == nullptr || key0 + BKV <= p.Sk;
@@ -707,7 +709,13 @@ __global__ void __launch_bounds__(THREADS, 1)
 #pragma unroll
       for (int which = 0; which < 2; ++which) {
         __nv_bfloat16* dst = which == 0 ? dv_row : dk_row;
-        uint8_t* stage = s_q + which * TILE_BYTES;
+        // dV is staged in a dO stage (dV's own products were their last readers) while the last
+        // dK product may still read Q; dK, once that product is done, in a Q stage.
+        if (which == 1 && iters > 0) {
+          if (!mbar_wait(&bars->dk_done, 0, abort_word, 324)) break;
+          tc_fence_after();
+        }
+        uint8_t* stage = which == 0 ? s_do : s_q;
         uint8_t* stage_row = stage + wg * PANEL_BYTES + r * 128;
         const uint32_t col = (which == 0 ? KV_COL_DV : KV_COL_DK) + wg * 64;
         const bool rotate = which == 1 && p.rope != nullptr;
