@@ -731,6 +731,9 @@ __global__ void __launch_bounds__(THREADS, 1)
         const float inv_l = l > 0.f ? 1.f / l : 0.f;
         __nv_bfloat16* orow_ptr =
             p_in.o + v.bt * p_in.o_sb + static_cast<long long>(v.q_base + row) * p_in.o_ss + v.h * p_in.o_sh;
+        // every row of the tensor starts on a 32-byte boundary (warp-uniform)
+        const bool wide_rows = ((reinterpret_cast<uintptr_t>(p_in.o) | static_cast<uintptr_t>(p_in.o_sb * 2) |
+                                 static_cast<uintptr_t>(p_in.o_ss * 2) | static_cast<uintptr_t>(p_in.o_sh * 2)) & 31) == 0;
 #pragma unroll
         for (int c = 0; c < 4; ++c) {
           uint32_t orow[32];
@@ -742,14 +745,24 @@ __global__ void __launch_bounds__(THREADS, 1)
             for (int i = 0; i < 32; ++i) orow[i] = 0u;
           }
           if (row_ok) {
+            uint32_t w[16];
 #pragma unroll
-            for (int g = 0; g < 4; ++g) {
-              uint4 q;
-              q.x = cvt_bf16x2(__uint_as_float(orow[g * 8 + 0]) * inv_l, __uint_as_float(orow[g * 8 + 1]) * inv_l);
-              q.y = cvt_bf16x2(__uint_as_float(orow[g * 8 + 2]) * inv_l, __uint_as_float(orow[g * 8 + 3]) * inv_l);
-              q.z = cvt_bf16x2(__uint_as_float(orow[g * 8 + 4]) * inv_l, __uint_as_float(orow[g * 8 + 5]) * inv_l);
-              q.w = cvt_bf16x2(__uint_as_float(orow[g * 8 + 6]) * inv_l, __uint_as_float(orow[g * 8 + 7]) * inv_l);
-              *reinterpret_cast<uint4*>(orow_ptr + c * 32 + g * 8) = q;
+            for (int i = 0; i < 16; ++i)
+              w[i] = cvt_bf16x2(__uint_as_float(orow[2 * i]) * inv_l, __uint_as_float(orow[2 * i + 1]) * inv_l);
+            // A thread owns a row, so a warp's store instruction touches 32 rows: with 256-bit
+            // stores (whole 32-byte sectors) it issues half as many of them.
+            if (wide_rows) {
+#pragma unroll
+              for (int g = 0; g < 2; ++g) {
+                const uint32_t v8[8] = {w[g * 8 + 0], w[g * 8 + 1], w[g * 8 + 2], w[g * 8 + 3],
+                                        w[g * 8 + 4], w[g * 8 + 5], w[g * 8 + 6], w[g * 8 + 7]};
+                st_global_v8(orow_ptr + c * 32 + g * 16, v8);
+              }
+            } else {
+#pragma unroll
+              for (int g = 0; g < 4; ++g)
+                *reinterpret_cast<uint4*>(orow_ptr + c * 32 + g * 8) =
+                    make_uint4(w[g * 4 + 0], w[g * 4 + 1], w[g * 4 + 2], w[g * 4 + 3]);
             }
           }
         }
