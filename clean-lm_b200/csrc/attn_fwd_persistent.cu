@@ -63,7 +63,7 @@ constexpr int ITEM_SLOTS = 16;
 constexpr int THREADS = 384;  // warp 0 TMA, warps 1-2 MMA (one per tile), warp 3 idle, warps 4-11 softmax
 constexpr int TMEM_COLS = 512;
 constexpr float RESCALE_THRESHOLD = 8.0f;  // log2 units
-constexpr size_t SMEM_BYTES = 1024 + 2 * TILE_BYTES + 2 * KV_STAGES * TILE_BYTES + 512;
+constexpr size_t SMEM_BYTES = 1024 + 2 * TILE_BYTES + 2 * KV_STAGES * TILE_BYTES + TILE_BYTES + 512;  // Q, K/V stages, O staging, barriers
 static_assert(SMEM_BYTES <= 232448, "exceeds the 227 KiB of shared memory a CTA can opt in to");
 
 // Which of the 16 column pairs of every 32-column chunk take the polynomial instead of MUFU.
@@ -119,6 +119,7 @@ struct Params {
   const int* cu_k;
   int num_q_blocks;  // ceil(Sq / 256)
   int total_items;   // num_q_blocks * H * B
+  int o_tma;  // 1: finished tiles leave through the staging tile and TMA stores
   unsigned int* item_counter;  // items handed out beyond every CTA's first one (zero between launches), or nullptr
   int* status;
 };
@@ -128,6 +129,8 @@ struct Barriers {
   uint64_t k_full[KV_STAGES], k_empty[KV_STAGES], v_full[KV_STAGES], v_empty[KV_STAGES];
   uint64_t s_full[2], p_ready[2], o_done[2];
   uint64_t item_full[ITEM_SLOTS], item_read[ITEM_SLOTS];
+  uint64_t stage_free;     // the O staging tile: one release per use, users take tickets
+  uint32_t stage_ticket;
   int item_ring[ITEM_SLOTS];
   uint32_t tmem_base;
   int abort_word;
@@ -258,14 +261,16 @@ __device__ __forceinline__ View view_of(const Params& p, int idx) {
 __global__ void __launch_bounds__(THREADS, 1)
     attn_fwd_persistent_kernel(const __grid_constant__ CUtensorMap tmap_q,
                                const __grid_constant__ CUtensorMap tmap_k,
-                               const __grid_constant__ CUtensorMap tmap_v, const Params p_in) {
+                               const __grid_constant__ CUtensorMap tmap_v,
+                               const __grid_constant__ CUtensorMap tmap_o, const Params p_in) {
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) &
                                              ~static_cast<uintptr_t>(1023));
   uint8_t* s_q = smem;                               // 2 tiles
   uint8_t* s_k = smem + 2 * TILE_BYTES;              // KV_STAGES tiles
   uint8_t* s_v = s_k + KV_STAGES * TILE_BYTES;       // KV_STAGES tiles
-  Barriers* bars = reinterpret_cast<Barriers*>(s_v + KV_STAGES * TILE_BYTES);
+  uint8_t* s_o = s_v + KV_STAGES * TILE_BYTES;       // 1 tile: staging of a finished O tile
+  Barriers* bars = reinterpret_cast<Barriers*>(s_o + TILE_BYTES);
   volatile int* abort_word = &bars->abort_word;
 
   const int warp = threadIdx.x >> 5;
@@ -291,6 +296,8 @@ __global__ void __launch_bounds__(THREADS, 1)
       mbar_init(&bars->v_full[i], 1);
       mbar_init(&bars->v_empty[i], 1);
     }
+    mbar_init(&bars->stage_free, 1);
+    bars->stage_ticket = 0;
     bars->abort_word = 0;
     fence_mbar_init();
   }
@@ -729,6 +736,22 @@ __global__ void __launch_bounds__(THREADS, 1)
       if (m_used == -INFINITY) l = 0.f;
       if (tile_row0 < v.Sq) {
         const float inv_l = l > 0.f ? 1.f / l : 0.f;
+        // A whole tile leaves through a staging tile in shared memory (the loads' 128-byte swizzle,
+        // two [128 rows][64 columns] panels) and two TMA stores: a thread owns a row, so its own
+        // stores touch 32 rows per instruction and cost the softmax warps ~2 300 clk per tile and
+        // item.  The staging tile is shared by the two tiles of the CTA (tickets; a use is
+        // released when the store has read it).  A store clips rows beyond the tensor, not rows of
+        // the next packed sequence: a partial tile of a packed sequence stores its rows directly.
+        const bool staged = p_in.o_tma != 0 && (p_in.cu_q == nullptr || tile_row0 + BQ <= v.Sq);
+        const bool tile_leader = quad == 0 && lane == 0;
+        auto tile_bar = [&]() { asm volatile("bar.sync %0, 128;" ::"r"(2 + t) : "memory"); };
+        if (staged) {
+          if (tile_leader) {
+            const uint32_t ticket = atomicAdd(&bars->stage_ticket, 1u);
+            if (!mbar_wait(&bars->stage_free, (ticket & 1u) ^ 1u, abort_word, 326)) ok = false;
+          }
+          tile_bar();
+        }
         __nv_bfloat16* orow_ptr =
             p_in.o + v.bt * p_in.o_sb + static_cast<long long>(v.q_base + row) * p_in.o_ss + v.h * p_in.o_sh;
         // every row of the tensor starts on a 32-byte boundary (warp-uniform)
@@ -744,13 +767,18 @@ __global__ void __launch_bounds__(THREADS, 1)
 #pragma unroll
             for (int i = 0; i < 32; ++i) orow[i] = 0u;
           }
-          if (row_ok) {
-            uint32_t w[16];
+          uint32_t w[16];
 #pragma unroll
-            for (int i = 0; i < 16; ++i)
-              w[i] = cvt_bf16x2(__uint_as_float(orow[2 * i]) * inv_l, __uint_as_float(orow[2 * i + 1]) * inv_l);
-            // A thread owns a row, so a warp's store instruction touches 32 rows: with 256-bit
-            // stores (whole 32-byte sectors) it issues half as many of them.
+          for (int i = 0; i < 16; ++i)
+            w[i] = cvt_bf16x2(__uint_as_float(orow[2 * i]) * inv_l, __uint_as_float(orow[2 * i + 1]) * inv_l);
+          if (staged) {
+            uint8_t* panel_row = s_o + (c >> 1) * PANEL_BYTES + row_in_tile * 128;
+#pragma unroll
+            for (int g = 0; g < 4; ++g)
+              *reinterpret_cast<uint4*>(panel_row + ((((c & 1) * 4 + g) ^ (row_in_tile & 7)) << 4)) =
+                  make_uint4(w[g * 4 + 0], w[g * 4 + 1], w[g * 4 + 2], w[g * 4 + 3]);
+          } else if (row_ok) {
+            // 256-bit stores (whole 32-byte sectors) where the rows allow them
             if (wide_rows) {
 #pragma unroll
               for (int g = 0; g < 2; ++g) {
@@ -764,6 +792,17 @@ __global__ void __launch_bounds__(THREADS, 1)
                 *reinterpret_cast<uint4*>(orow_ptr + c * 32 + g * 8) =
                     make_uint4(w[g * 4 + 0], w[g * 4 + 1], w[g * 4 + 2], w[g * 4 + 3]);
             }
+          }
+        }
+        if (staged) {
+          fence_proxy_async_smem();
+          tile_bar();
+          if (tile_leader) {
+            tma_store_4d(&tmap_o, s_o, 0, v.q_base + tile_row0, v.h, v.bt);
+            tma_store_4d(&tmap_o, s_o + PANEL_BYTES, 64, v.q_base + tile_row0, v.h, v.bt);
+            tma_store_commit();
+            tma_store_wait_read<0>();
+            mbar_arrive(&bars->stage_free);
           }
         }
         if (row_ok && p_in.lse != nullptr) {
@@ -834,6 +873,22 @@ int32_t attn_fwd_persistent_launch(const cdl_tensor* q, const cdl_tensor* k, con
   p.status = device_status_ptr();
   if (!p.status) return fail(CDL_ERR_CUDA, "cannot resolve the device status word");
 
+  // O as a tensor of q's shape for the TMA stores of finished tiles; rows that TMA cannot
+  // describe (strides off the 16-byte grid) are stored by the threads directly.
+  CUtensorMap to;
+  {
+    cdl_tensor ot = *q;
+    ot.ptr = o;
+    ot.stride[0] = o_sb;
+    ot.stride[1] = o_ss;
+    ot.stride[2] = o_sh;
+    ot.stride[3] = 1;
+    const bool describable = (reinterpret_cast<uintptr_t>(o) & 15) == 0 && o_ss % 8 == 0 && o_sh % 8 == 0 &&
+                             (q->shape[0] <= 1 || o_sb % 8 == 0);
+    p.o_tma = 0;
+    if (describable && attn_encode_tmap_rows(&to, &ot, 128) == CDL_OK) p.o_tma = 1;
+    if (!p.o_tma) memset(&to, 0, sizeof to);
+  }
   CUtensorMap tq, tk, tv;
   if (any_keys) {
     CDL_CHECK(attn_encode_tmap_rows(&tq, q, 128));
@@ -858,7 +913,7 @@ int32_t attn_fwd_persistent_launch(const cdl_tensor* q, const cdl_tensor* k, con
     return fail(CDL_ERR_CUDA, "cudaFuncSetAttribute failed: %s", cudaGetErrorString(attr_err));
   const int grid = items < sm_count() ? static_cast<int>(items) : sm_count();
   if (items > grid) p.item_counter = sched_counter_for(1, dev, stream);
-  CDL_CUDA(launch_pdl(attn_fwd_persistent_kernel, dim3(grid), dim3(THREADS), SMEM_BYTES, stream, tq, tk, tv, p));
+  CDL_CUDA(launch_pdl(attn_fwd_persistent_kernel, dim3(grid), dim3(THREADS), SMEM_BYTES, stream, tq, tk, tv, to, p));
   CDL_CUDA(cudaGetLastError());
   return CDL_OK;
 }
