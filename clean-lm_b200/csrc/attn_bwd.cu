@@ -75,6 +75,12 @@ constexpr int KV_LOW_REGS = 72, KV_HIGH_REGS = 216;
 #define CDL_ATTN_BWD_CHUNK_MB 16
 #endif
 
+// 1: the dK/dV kernel runs as one CTA per SM over many key blocks when there are more key blocks
+// than SMs; 0: always one CTA per key block.
+#ifndef CDL_ATTN_BWD_PERSISTENT
+#define CDL_ATTN_BWD_PERSISTENT 1
+#endif
+
 // Status code (device status word) of a packed sequence longer than max_seqlen_q / max_seqlen_k.
 constexpr int STATUS_SEQ_EXCEEDS_BOUND = 921;
 
@@ -102,6 +108,7 @@ struct Params {
   // CTA order (see cta_coords): number of blocks along the sequence, heads x batch, heads per chunk
   int kv_blocks, kv_heads_total, kv_chunk;  // dK/dV kernel
   int q_blocks, q_heads_total, q_chunk;     // dQ kernel
+  int variant;  // cdl_attn_variant of the call (read on the host only)
   int* status;
 };
 
@@ -787,6 +794,585 @@ __global__ void __launch_bounds__(THREADS, 1)
   if (threadIdx.x == 0 && *abort_word != 0) atomicExch(p.status, *abort_word);
 }
 
+// ---------------------------------------------------------------- dK / dV kernel, persistent form
+// The same tile program as attn_bwd_dkdv_kernel, run by one CTA per SM over many (key block, kv
+// head, batch) items, so that what a one-shot CTA pays per item -- its launch, the tensor-memory
+// allocation, the first operand loads and the first two products before any compute warp has
+// work -- happens under the previous item's last query block and store epilogue:
+//   * items are numbered in the order of cta_coords (longest first inside an L2-sized chunk); a
+//     CTA's first item is its index, later ones are drawn from a counter by the producer lane
+//     and published through a small ring in shared memory (-1: no further item);
+//   * all barrier phases count query blocks (or items) across items;
+//   * K is free for the next item's load once the item's last S^T has run, V once its last dP^T
+//     has (k_free / v_free, committed by the issuing lane one query block before the item ends),
+//     and the next item's first Q / dO go to the stage the last query block does not use;
+//   * the issuing lane starts S^T and dP^T of the next item's first query block right behind the
+//     last dK product; dV and dK leave tensor memory (staged in the dO / Q stage of the item's
+//     last query block, which the storing thread releases when the TMA stores have read it)
+//     before the compute warps write the next item's first P^T, and the products that overwrite
+//     the accumulators wait for that P^T / dS^T -- so the accumulators need no barrier of
+//     their own.
+constexpr int KVP_SLOTS = 4;
+struct KvpBarriers {
+  uint64_t kv_full, k_free, v_free;
+  uint64_t q_full[2], q_empty[2], do_full[2], do_empty[2];
+  uint64_t s_full, dp_full, p_ready, ds_ready, dv_done, dk_done;
+  uint64_t item_full[KVP_SLOTS], item_read[KVP_SLOTS];
+  int item_ring[KVP_SLOTS];
+  uint32_t tmem_base;
+  int abort_word;
+};
+constexpr size_t KVP_SMEM_BYTES = 6 * TILE_BYTES + 2 * 2 * 128 * sizeof(float) + sizeof(KvpBarriers);
+static_assert(KVP_SMEM_BYTES <= 232448, "exceeds the 227 KiB of shared memory a CTA can opt in to");
+
+// One item: key block `key0` of kv head `kvh` of sequence `b`, walked over `iters` query blocks
+// (query block m_start + it % m_count of head kvh * group + it / m_count).
+struct KvItem {
+  int b, kvh, bt, key0, q_base, k_base, Sq, Sk, shift, m_start, m_count, iters;
+  bool exceeds;  // a packed sequence longer than the bound the launch was sized with
+};
+__device__ __forceinline__ KvItem kv_item_of(const Params& p, int idx) {
+  KvItem v;
+  int rank, hb;
+  cta_coords(idx, p.kv_blocks, p.kv_heads_total, p.kv_chunk, rank, hb);
+  v.b = hb / p.Hkv;
+  v.kvh = hb - v.b * p.Hkv;
+  v.bt = v.b;
+  v.q_base = 0;
+  v.k_base = 0;
+  v.Sq = p.Sq;
+  v.Sk = p.Sk;
+  v.exceeds = false;
+  if (p.cu_q != nullptr) {
+    v.q_base = p.cu_q[v.b];
+    v.Sq = p.cu_q[v.b + 1] - v.q_base;
+    v.k_base = p.cu_k[v.b];
+    v.Sk = p.cu_k[v.b + 1] - v.k_base;
+    v.bt = 0;
+    if (v.Sq > p.Sq || v.Sk > p.Sk) {
+      v.exceeds = true;
+      v.Sq = min(v.Sq, p.Sq);
+      v.Sk = min(v.Sk, p.Sk);
+    }
+  }
+  v.key0 = rank * BKV;
+  v.shift = v.Sk - v.Sq;
+  const int num_q_blocks = (v.Sq + BQ - 1) / BQ;
+  v.m_start = p.causal ? max(0, v.key0 - v.shift) / BQ : 0;
+  v.m_count = max(0, num_q_blocks - v.m_start);
+  v.iters = v.key0 < v.Sk ? v.m_count * (p.H / p.Hkv) : 0;
+  return v;
+}
+// Items of a CTA when no counter is available: a boustrophedon deal of the longest-first order.
+__device__ __forceinline__ int kvp_fixed_item(int k, int cid, int nc, int total) {
+  if (static_cast<long long>(k) * nc >= total) return -1;
+  const int idx = k * nc + ((k & 1) ? nc - 1 - cid : cid);
+  return idx < total ? idx : -1;
+}
+
+__global__ void __launch_bounds__(THREADS, 1)
+    attn_bwd_dkdv_persistent_kernel(const __grid_constant__ CUtensorMap tmap_q,
+                                    const __grid_constant__ CUtensorMap tmap_k,
+                                    const __grid_constant__ CUtensorMap tmap_v,
+                                    const __grid_constant__ CUtensorMap tmap_do,
+                                    const __grid_constant__ CUtensorMap tmap_dk,
+                                    const __grid_constant__ CUtensorMap tmap_dv, const Params p,
+                                    unsigned int* item_counter) {
+  extern __shared__ __align__(1024) uint8_t smem[];
+  if ((smem_u32(smem) & 1023u) != 0) {
+    if (threadIdx.x == 0) atomicExch(p.status, 901);
+    return;
+  }
+  uint8_t* s_k = smem;
+  uint8_t* s_v = smem + TILE_BYTES;
+  uint8_t* s_q = smem + 2 * TILE_BYTES;   // 2 stages
+  uint8_t* s_do = smem + 4 * TILE_BYTES;  // 2 stages
+  float* s_lse = reinterpret_cast<float*>(smem + 6 * TILE_BYTES);  // [2][128]
+  float* s_delta = s_lse + 2 * 128;                                // [2][128]
+  KvpBarriers* bars = reinterpret_cast<KvpBarriers*>(s_delta + 2 * 128);
+  volatile int* abort_word = &bars->abort_word;
+
+  const int warp = threadIdx.x >> 5;
+  const int lane = threadIdx.x & 31;
+  const int group = p.H / p.Hkv;
+  const int total = p.kv_blocks * p.kv_heads_total;
+  const int nc = static_cast<int>(gridDim.x), cid = static_cast<int>(blockIdx.x);
+
+  if (threadIdx.x == 0) {
+    mbar_init(&bars->kv_full, 1);
+    mbar_init(&bars->k_free, 1);
+    mbar_init(&bars->v_free, 1);
+    for (int i = 0; i < 2; ++i) {
+      mbar_init(&bars->q_full[i], 1);
+      mbar_init(&bars->q_empty[i], 1);
+      mbar_init(&bars->do_full[i], 1);
+      mbar_init(&bars->do_empty[i], 1);
+    }
+    mbar_init(&bars->s_full, 1);
+    mbar_init(&bars->dp_full, 1);
+    mbar_init(&bars->p_ready, 8);  // one arrival per compute warp
+    mbar_init(&bars->ds_ready, 8);
+    mbar_init(&bars->dv_done, 1);
+    mbar_init(&bars->dk_done, 1);
+    for (int i = 0; i < KVP_SLOTS; ++i) {
+      mbar_init(&bars->item_full[i], 1);
+      mbar_init(&bars->item_read[i], 9);  // the issuing lane and the eight compute warps
+    }
+    bars->abort_word = 0;
+    fence_mbar_init();
+  }
+  if (warp == 1) {
+    tmem_alloc(&bars->tmem_base, TMEM_COLS);
+    tmem_relinquish();
+  }
+  if (warp == 0 && lane == 0) {
+    tma_prefetch_desc(&tmap_q);
+    tma_prefetch_desc(&tmap_k);
+    tma_prefetch_desc(&tmap_v);
+    tma_prefetch_desc(&tmap_do);
+    tma_prefetch_desc(&tmap_dk);
+    tma_prefetch_desc(&tmap_dv);
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = bars->tmem_base;
+  grid_dep_wait();  // the set-up above overlaps the previous kernel's tail; global memory from here on
+  grid_dep_launch();
+
+  if (warp == 0) {
+    // ------------------------------------------------------------ TMA producer (and item hand-out)
+    setmaxnreg_dec<KV_LOW_REGS>();
+    if (elect_one()) {
+      // Every CTA draws after each item it takes, until a draw runs past the last item; the
+      // launch's last draw puts the counter back to zero.
+      const unsigned total_draws = static_cast<unsigned>((total > nc ? total - nc : 0) + (nc < total ? nc : total));
+      int idx = cid < total ? cid : -1;
+      unsigned drawn = 0;
+      uint32_t g = 0, kvn = 0;  // query blocks / non-empty items so far
+      bool ok = true;
+      for (int k = 0; ok; ++k) {
+        if (k > 0) {
+          if (item_counter != nullptr) {
+            idx = static_cast<unsigned>(nc) + drawn < static_cast<unsigned>(total) ? static_cast<int>(nc + drawn) : -1;
+            if (drawn + 1 == total_draws) atomicExch(item_counter, 0u);
+          } else {
+            idx = kvp_fixed_item(k, cid, nc, total);
+          }
+        }
+        if (k >= KVP_SLOTS &&
+            !mbar_wait(&bars->item_read[k % KVP_SLOTS], ((k / KVP_SLOTS) - 1) & 1, abort_word, 124)) {
+          ok = false;
+          break;
+        }
+        bars->item_ring[k % KVP_SLOTS] = idx;
+        mbar_arrive(&bars->item_full[k % KVP_SLOTS]);
+        if (idx < 0) break;
+        const KvItem v = kv_item_of(p, idx);
+        if (v.exceeds) atomicExch(p.status, STATUS_SEQ_EXCEEDS_BOUND);
+        if (v.iters > 0) {
+          ok = mbar_wait(&bars->k_free, (kvn & 1) ^ 1, abort_word, 125) &&
+               mbar_wait(&bars->v_free, (kvn & 1) ^ 1, abort_word, 126);
+          if (!ok) break;
+          ++kvn;
+          mbar_arrive_expect_tx(&bars->kv_full, 2 * TILE_BYTES);
+#pragma unroll
+          for (int dh = 0; dh < 2; ++dh) {
+            tma_load_4d(s_k + dh * PANEL_BYTES, &tmap_k, &bars->kv_full, dh * 64, v.k_base + v.key0, v.kvh, v.bt);
+            tma_load_4d(s_v + dh * PANEL_BYTES, &tmap_v, &bars->kv_full, dh * 64, v.k_base + v.key0, v.kvh, v.bt);
+          }
+          int h = v.kvh * group, m = v.m_start;
+          for (int it = 0; it < v.iters; ++it, ++g) {
+            const int q0 = m * BQ;
+            const int s = g & 1;
+            const uint32_t ph = ((g >> 1) & 1) ^ 1;
+            if (!mbar_wait(&bars->q_empty[s], ph, abort_word, 121)) { ok = false; break; }
+            mbar_arrive_expect_tx(&bars->q_full[s], TILE_BYTES);
+#pragma unroll
+            for (int dh = 0; dh < 2; ++dh)
+              tma_load_4d(s_q + s * TILE_BYTES + dh * PANEL_BYTES, &tmap_q, &bars->q_full[s], dh * 64,
+                          v.q_base + q0, h, v.bt);
+            if (!mbar_wait(&bars->do_empty[s], ph, abort_word, 122)) { ok = false; break; }
+            mbar_arrive_expect_tx(&bars->do_full[s], TILE_BYTES);
+#pragma unroll
+            for (int dh = 0; dh < 2; ++dh)
+              tma_load_4d(s_do + s * TILE_BYTES + dh * PANEL_BYTES, &tmap_do, &bars->do_full[s],
+                          dh * 64, v.q_base + q0, h, v.bt);
+            if (++m == v.m_start + v.m_count) {
+              m = v.m_start;
+              ++h;
+            }
+          }
+        }
+        // The next item is drawn when this item's last loads are on their way.
+        if (ok && item_counter != nullptr) drawn = atomicAdd(item_counter, 1u);
+      }
+    }
+  } else if (warp == 1) {
+    // ------------------------------------------------------------ MMA issuer
+    // Issue order inside an item: dV(it), S^T(it+1), dK(it), dP^T(it+1); behind the last dK of an
+    // item come S^T(0) and dP^T(0) of the next one.
+    setmaxnreg_dec<KV_LOW_REGS>();
+    if (elect_one()) {
+      const uint32_t idesc_kk = make_idesc_bf16(128, 128, 0, 0);  // both operands K-major
+      const uint32_t idesc_kmn = make_idesc_bf16(128, 128, 0, 1); // A K-major / TMEM, B MN-major
+      const uint32_t k_lo = desc_lo(smem_u32(s_k), 16), v_lo = desc_lo(smem_u32(s_v), 16);
+      const uint32_t q_lo = desc_lo(smem_u32(s_q), 16), do_lo = desc_lo(smem_u32(s_do), 16);
+      const uint32_t q_mn_lo = desc_lo(smem_u32(s_q), PANEL_BYTES), do_mn_lo = desc_lo(smem_u32(s_do), PANEL_BYTES);
+      const uint32_t d_s = tmem_base + KV_COL_S, d_dp = tmem_base + KV_COL_DP;
+      const uint32_t d_dv = tmem_base + KV_COL_DV, d_dk = tmem_base + KV_COL_DK;
+      auto issue_s = [&](uint32_t stage) {  // S^T = K Q^T
+        const uint32_t qa = q_lo + stage * (TILE_BYTES >> 4);
+#pragma unroll
+        for (int k = 0; k < 8; ++k)
+          umma_ss(d_s, desc_at(k_lo, koff_k(k)), desc_at(qa, koff_k(k)), idesc_kk, k != 0);
+        umma_commit(&bars->s_full);
+      };
+      auto issue_dp = [&](uint32_t stage) {  // dP^T = V dO^T
+        const uint32_t da = do_lo + stage * (TILE_BYTES >> 4);
+#pragma unroll
+        for (int k = 0; k < 8; ++k)
+          umma_ss(d_dp, desc_at(v_lo, koff_k(k)), desc_at(da, koff_k(k)), idesc_kk, k != 0);
+        umma_commit(&bars->dp_full);
+      };
+      uint32_t g = 0, kvn = 0;
+      bool ok = true;
+      for (int k = 0; ok; ++k) {
+        if (!mbar_wait(&bars->item_full[k % KVP_SLOTS], (k / KVP_SLOTS) & 1, abort_word, 224)) break;
+        const int idx = bars->item_ring[k % KVP_SLOTS];
+        mbar_arrive(&bars->item_read[k % KVP_SLOTS]);
+        if (idx < 0) break;
+        const int iters = kv_item_of(p, idx).iters;
+        if (iters == 0) continue;
+        {
+          const uint32_t s0 = g & 1, par0 = (g >> 1) & 1;
+          ok = mbar_wait(&bars->kv_full, kvn & 1, abort_word, 221) &&
+               mbar_wait(&bars->q_full[s0], par0, abort_word, 222);
+          if (!ok) break;
+          tc_fence_after();
+          issue_s(s0);
+          if (iters == 1) umma_commit(&bars->k_free);
+          ok = mbar_wait(&bars->do_full[s0], par0, abort_word, 223);
+          if (!ok) break;
+          tc_fence_after();
+          issue_dp(s0);
+          if (iters == 1) umma_commit(&bars->v_free);
+        }
+        for (int it = 0; it < iters; ++it, ++g) {
+          const uint32_t s = g & 1;
+          const uint32_t ph = g & 1;
+          const bool has_next = it + 1 < iters;
+          if (has_next) {  // Q and dO of the next block: loaded an iteration ago as a rule
+            const uint32_t ph_next = ((g + 1) >> 1) & 1;
+            ok = mbar_wait(&bars->q_full[s ^ 1], ph_next, abort_word, 227) &&
+                 mbar_wait(&bars->do_full[s ^ 1], ph_next, abort_word, 228);
+            if (!ok) break;
+          }
+          const uint32_t acc = it > 0 ? 1u : 0u;
+          const uint32_t qf = q_mn_lo + s * (TILE_BYTES >> 4), df = do_mn_lo + s * (TILE_BYTES >> 4);
+          // dV += P^T dO  (A = P^T from TMEM).  The first one of an item overwrites the previous
+          // item's dV, which the compute warps have read before they wrote this P^T.
+          ok = mbar_wait(&bars->p_ready, ph, abort_word, 225);
+          if (!ok) break;
+          tc_fence_after();
+#pragma unroll
+          for (int kk = 0; kk < 8; ++kk)
+            umma_ts(d_dv, d_s + acol(kk), desc_at(df, koff_mn(kk)), idesc_kmn, kk != 0 ? 1u : acc);
+          // dP^T(it) and dV(it) were the readers of this dO stage; after the item's last query
+          // block the stage carries dV out and the storing thread releases it.
+          if (has_next) {
+            umma_commit(&bars->do_empty[s]);
+            issue_s(s ^ 1);  // overwrites P^T, which dV (issued above) reads first
+            if (it + 2 == iters) umma_commit(&bars->k_free);
+          } else {
+            umma_commit(&bars->dv_done);
+          }
+          // dK += dS^T Q  (A = dS^T from TMEM, written over dP^T)
+          ok = mbar_wait(&bars->ds_ready, ph, abort_word, 226);
+          if (!ok) break;
+          tc_fence_after();
+#pragma unroll
+          for (int kk = 0; kk < 8; ++kk)
+            umma_ts(d_dk, d_dp + acol(kk), desc_at(qf, koff_mn(kk)), idesc_kmn, kk != 0 ? 1u : acc);
+          if (has_next) {
+            umma_commit(&bars->q_empty[s]);
+            issue_dp(s ^ 1);  // overwrites dS^T, which dK (issued above) reads first
+            if (it + 2 == iters) umma_commit(&bars->v_free);
+          } else {
+            umma_commit(&bars->dk_done);
+          }
+        }
+        ++kvn;
+      }
+    }
+  } else if (warp < 4) {
+    setmaxnreg_dec<KV_LOW_REGS>();
+  } else {
+    // ------------------------------------------------------------ compute warps (4..11)
+    setmaxnreg_inc<KV_HIGH_REGS>();
+    const int ct = threadIdx.x - 128;  // 0..255
+    const int wg = (warp - 4) >> 2;    // column (query) half this thread works on
+    const int quad = warp & 3;
+    const int r = quad * 32 + lane;    // key row inside the block == TMEM lane
+    const uint32_t lane_addr = static_cast<uint32_t>(quad * 32) << 16;
+    bool ok = true;
+
+    // Row statistics of query block `it` of an item: threads 0..127 fetch LSE2, 128..255 delta.
+    auto fetch_stat = [&](const KvItem& v, int it) -> float {
+      const int hh = it / v.m_count;
+      const long long base = (static_cast<long long>(v.b) * p.H + v.kvh * group + hh) * p.Sq_pad +
+                             (v.m_start + it - hh * v.m_count) * BQ;
+      return ct < 128 ? p.lse2[base + ct] : p.delta[base + ct - 128];
+    };
+    auto store_stat = [&](uint32_t stage, float x) {
+      if (ct < 128) s_lse[stage * 128 + ct] = -x;  // negated: it is the addend of a packed FMA
+      else s_delta[stage * 128 + ct - 128] = x;
+    };
+    auto read_item = [&](int k) -> int {
+      if (!mbar_wait(&bars->item_full[k % KVP_SLOTS], (k / KVP_SLOTS) & 1, abort_word, 326)) return -2;
+      const int idx = bars->item_ring[k % KVP_SLOTS];
+      __syncwarp();
+      if (lane == 0) mbar_arrive(&bars->item_read[k % KVP_SLOTS]);
+      return idx;
+    };
+    float pr[64];
+    uint32_t g = 0, kvn = 0;
+
+    // P^T = exp2(S^T * scale_log2 - lse2) of running query block gi -> registers (f32) and TMEM (bf16)
+    auto p_phase = [&](const KvItem& v, int it, uint32_t gi) -> bool {
+      const int q0 = (v.m_start + it % v.m_count) * BQ;
+      const int key = v.key0 + r;
+      const float4* lse_s = reinterpret_cast<const float4*>(s_lse + (gi & 1) * 128 + wg * 64);
+      const bool need_mask = (p.causal && v.key0 + BKV - 1 > q0 + v.shift) || v.key0 + BKV > v.Sk;
+      if (!mbar_wait(&bars->s_full, gi & 1, abort_word, 321)) return false;
+      tc_fence_after();
+      {
+        uint32_t sr[2][32];
+        tmem_ld32(tmem_base + lane_addr + KV_COL_S + wg * 64, sr[0]);
+        tmem_ld32(tmem_base + lane_addr + KV_COL_S + wg * 64 + 32, sr[1]);
+        tmem_wait_ld();
+        float x[64];
+        const uint64_t scale2 = pk2(p.scale_log2, p.scale_log2);
+#pragma unroll
+        for (int c4 = 0; c4 < 16; ++c4) {
+          const float4 l4 = lse_s[c4];  // the statistics are stored negated (store_stat)
+          const int c = c4 * 4;
+          upk2(fma_x2(pk2(__uint_as_float(sr[c >> 5][c & 31]), __uint_as_float(sr[c >> 5][(c & 31) + 1])), scale2,
+                      pk2(l4.x, l4.y)),
+               x[c], x[c + 1]);
+          upk2(fma_x2(pk2(__uint_as_float(sr[c >> 5][(c & 31) + 2]), __uint_as_float(sr[c >> 5][(c & 31) + 3])), scale2,
+                      pk2(l4.z, l4.w)),
+               x[c + 2], x[c + 3]);
+        }
+        exp2_row64(x, pr);
+        if (need_mask) {  // warp-uniform; only blocks on the diagonal or at the end of the keys
+#pragma unroll
+          for (int c = 0; c < 64; ++c) {
+            const int qrow = q0 + wg * 64 + c;
+            if (key >= v.Sk || (p.causal && key > qrow + v.shift)) pr[c] = 0.f;
+          }
+        }
+      }
+      {
+        // P^T (bf16 pairs) goes over the first 32 of the 64 S^T columns this thread has read
+        uint32_t pk[32];
+#pragma unroll
+        for (int c = 0; c < 32; ++c) pk[c] = pack_bf16x2(pr[2 * c], pr[2 * c + 1]);
+        tmem_st32(tmem_base + lane_addr + KV_COL_S + wg * 64, pk);
+        tmem_wait_st();
+      }
+      tc_fence_before();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(&bars->p_ready);
+      return true;
+    };
+
+    int idx = read_item(0);
+    KvItem v;
+    float st0 = 0.f, st1 = 0.f;  // statistics of the item's first two query blocks
+    if (idx >= 0) {
+      v = kv_item_of(p, idx);
+      if (v.iters > 0) st0 = fetch_stat(v, 0);
+      if (v.iters > 1) st1 = fetch_stat(v, 1);
+    }
+    for (int k = 0; idx >= 0 && ok; ++k) {
+      const int iters = v.iters;
+      const int key = v.key0 + r;
+      if (iters > 0) {
+        store_stat(g & 1, st0);
+        if (iters > 1) store_stat((g + 1) & 1, st1);
+        compute_bar_sync();
+        ok = p_phase(v, 0, g);
+        float stat_next = 0.f;
+        for (int it = 0; it < iters && ok; ++it) {
+          const uint32_t gi = g + it;
+          const uint32_t ph = gi & 1;
+          if (it + 2 < iters) stat_next = fetch_stat(v, it + 2);  // lands while this iteration computes
+
+          // ---- dS^T / scale = P^T o (dP^T - delta)  -> TMEM (bf16) over the dP^T columns
+          if (!mbar_wait(&bars->dp_full, ph, abort_word, 322)) { ok = false; break; }
+          tc_fence_after();
+          {
+            const float4* delta_s = reinterpret_cast<const float4*>(s_delta + (gi & 1) * 128 + wg * 64);
+            uint32_t dr[2][32];
+            tmem_ld32(tmem_base + lane_addr + KV_COL_DP + wg * 64, dr[0]);
+            tmem_ld32(tmem_base + lane_addr + KV_COL_DP + wg * 64 + 32, dr[1]);
+            tmem_wait_ld();
+            uint32_t pk[32];
+#pragma unroll
+            for (int ch = 0; ch < 8; ++ch) {
+              const float4 d0 = delta_s[ch * 2], d1 = delta_s[ch * 2 + 1];
+              const float dl[8] = {d0.x, d0.y, d0.z, d0.w, d1.x, d1.y, d1.z, d1.w};
+              float d[8];
+#pragma unroll
+              for (int j = 0; j < 8; j += 2) {
+                const int c = ch * 8 + j;
+                upk2(mul_x2(pk2(pr[c], pr[c + 1]),
+                            sub_x2(pk2(__uint_as_float(dr[c >> 5][c & 31]), __uint_as_float(dr[c >> 5][(c & 31) + 1])),
+                                   pk2(dl[j], dl[j + 1]))),
+                     d[j], d[j + 1]);
+              }
+              pk[ch * 4 + 0] = pack_bf16x2(d[0], d[1]);
+              pk[ch * 4 + 1] = pack_bf16x2(d[2], d[3]);
+              pk[ch * 4 + 2] = pack_bf16x2(d[4], d[5]);
+              pk[ch * 4 + 3] = pack_bf16x2(d[6], d[7]);
+            }
+            tmem_st32(tmem_base + lane_addr + KV_COL_DP + wg * 64, pk);
+            tmem_wait_st();
+          }
+          tc_fence_before();
+          __syncwarp();
+          if (lane == 0) mbar_arrive(&bars->ds_ready);
+
+          // ---- P^T of the next query block (overlaps the dK product of this one)
+          if (it + 1 < iters && !p_phase(v, it + 1, gi + 1)) { ok = false; break; }
+
+          // Statistics of query block it + 2 replace those of query block it.
+          compute_bar_sync();
+          if (it + 2 < iters) store_stat(gi & 1, stat_next);
+          compute_bar_sync();
+        }
+        if (!ok) break;
+      }
+
+      // The next item and the statistics of its first query blocks: fetched before the stores so
+      // that they have landed when the epilogue is through.
+      const int idx_next = read_item(k + 1);
+      KvItem vn = v;
+      if (idx_next >= 0) {
+        vn = kv_item_of(p, idx_next);
+        if (vn.iters > 0) st0 = fetch_stat(vn, 0);
+        if (vn.iters > 1) st1 = fetch_stat(vn, 1);
+      }
+
+      __nv_bfloat16* dv_row = p.dv + v.bt * p.dv_sb + static_cast<long long>(v.k_base + key) * p.dv_ss + v.kvh * p.dv_sh + wg * 64;
+      __nv_bfloat16* dk_row = p.dk + v.bt * p.dk_sb + static_cast<long long>(v.k_base + key) * p.dk_ss + v.kvh * p.dk_sh + wg * 64;
+      if (iters == 0) {
+        // Keys no query sees (a sequence without queries): their gradients are zero.
+        if (key < v.Sk) {
+#pragma unroll
+          for (int c = 0; c < 8; ++c) {
+            *reinterpret_cast<uint4*>(dv_row + c * 8) = make_uint4(0u, 0u, 0u, 0u);
+            *reinterpret_cast<uint4*>(dk_row + c * 8) = make_uint4(0u, 0u, 0u, 0u);
+          }
+        }
+      } else {
+        // ---- epilogue: dV and dK rows of this key block leave through the dO / Q stage of the
+        // item's last query block (the loads' 128-byte swizzle) and one TMA store per 64-column
+        // panel.  A store clips rows beyond the tensor, not rows of the next packed sequence: a
+        // partial block of a packed sequence stores its rows directly.
+        const uint32_t s_last = (g + iters - 1) & 1;
+        const bool staged = p.cu_k == nullptr || v.key0 + BKV <= v.Sk;
+        const bool row_ok = key < v.Sk;
+#pragma unroll
+        for (int which = 0; which < 2; ++which) {
+          __nv_bfloat16* dst = which == 0 ? dv_row : dk_row;
+          // dV is complete one product before dK and is staged while that product runs.
+          if (!mbar_wait(which == 0 ? &bars->dv_done : &bars->dk_done, kvn & 1, abort_word, 324 + which)) {
+            ok = false;
+            break;
+          }
+          tc_fence_after();
+          uint8_t* stage = (which == 0 ? s_do : s_q) + s_last * TILE_BYTES;
+          uint8_t* stage_row = stage + wg * PANEL_BYTES + r * 128;
+          const uint32_t col = (which == 0 ? KV_COL_DV : KV_COL_DK) + wg * 64;
+          const bool rotate = which == 1 && p.rope != nullptr;
+#pragma unroll
+          for (int half = 0; half < 2; ++half) {
+            uint32_t a[32];
+            tmem_ld32(tmem_base + lane_addr + col + half * 32, a);
+            tmem_wait_ld();
+            const float sc = which == 0 ? 1.0f : p.scale;  // dS^T was accumulated without the scale
+#pragma unroll
+            for (int gq = 0; gq < 4; ++gq) {
+              uint4 q;
+              q.x = pack_bf16x2(__uint_as_float(a[gq * 8 + 0]) * sc, __uint_as_float(a[gq * 8 + 1]) * sc);
+              q.y = pack_bf16x2(__uint_as_float(a[gq * 8 + 2]) * sc, __uint_as_float(a[gq * 8 + 3]) * sc);
+              q.z = pack_bf16x2(__uint_as_float(a[gq * 8 + 4]) * sc, __uint_as_float(a[gq * 8 + 5]) * sc);
+              q.w = pack_bf16x2(__uint_as_float(a[gq * 8 + 6]) * sc, __uint_as_float(a[gq * 8 + 7]) * sc);
+              if (staged || rotate)
+                *reinterpret_cast<uint4*>(stage_row + (((half * 4 + gq) ^ (r & 7)) << 4)) = q;
+              else if (row_ok)
+                *reinterpret_cast<uint4*>(dst + half * 32 + gq * 8) = q;
+            }
+          }
+          if (rotate) {
+            // dK of the keys before the rotary rotation: the staged rows are rotated back in place
+            uint4 rot[8];
+            compute_bar_sync();
+            rope_inverse_row(stage, wg, r, p.rope + static_cast<long long>(min(key, p.rope_rows - 1)) * 128, rot);
+            compute_bar_sync();
+#pragma unroll
+            for (int c = 0; c < 8; ++c) {
+              if (staged)
+                *reinterpret_cast<uint4*>(stage_row + ((c ^ (r & 7)) << 4)) = rot[c];
+              else if (row_ok)
+                *reinterpret_cast<uint4*>(dst + c * 8) = rot[c];
+            }
+          }
+          if (staged) fence_proxy_async_smem();
+          compute_bar_sync();  // every thread is through with the stage (and with the accumulator)
+          if (staged && ct == 0) {
+            const CUtensorMap* tm = which == 0 ? &tmap_dv : &tmap_dk;
+            tma_store_4d(tm, stage, 0, v.k_base + v.key0, v.kvh, v.bt);
+            tma_store_4d(tm, stage + PANEL_BYTES, 64, v.k_base + v.key0, v.kvh, v.bt);
+            tma_store_commit();
+          }
+        }
+        if (!ok) break;
+        // The two stages go back to the producer when the stores have read them.
+        if (ct == 0) {
+          if (staged) tma_store_wait_read<1>();
+          mbar_arrive(&bars->do_empty[s_last]);
+          if (staged) tma_store_wait_read<0>();
+          mbar_arrive(&bars->q_empty[s_last]);
+        }
+        // The accumulators are read: the next item's first dV / dK products, which overwrite
+        // them, are ordered after this through that item's first p_ready / ds_ready arrivals.
+        tc_fence_before();
+        g += iters;
+        ++kvn;
+      }
+      v = vn;
+      idx = idx_next;
+    }
+  }
+
+  // ------------------------------------------------------------ tear-down
+  __syncwarp();
+  if (*abort_word != 0) {
+    const unsigned long long t0 = globaltimer_ns();
+    while (globaltimer_ns() - t0 < 200000ull) __nanosleep(1000);
+  }
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 1) {
+    tc_fence_after();
+    tmem_dealloc(tmem_base, TMEM_COLS);
+  }
+  if (threadIdx.x == 0 && *abort_word != 0) atomicExch(p.status, *abort_word);
+}
+
 // ---------------------------------------------------------------- dQ kernel
 // Number of 128-key blocks the query rows [q0, q0 + 128) see.
 __device__ __forceinline__ int dq_kv_blocks(const Params& p, int q0) {
@@ -1002,7 +1588,6 @@ __global__ void __launch_bounds__(THREADS, 1)
         tmem_ld32(tmem_base + lane_addr + Q_COL_S + s * 128 + wg * 64 + 32, sr[1]);
         tmem_wait_ld();
         float x[64];
-#pragma unroll
         const uint64_t scale2 = pk2(p.scale_log2, p.scale_log2), neg_lse2 = pk2(-lse2, -lse2);
 #pragma unroll
         for (int c = 0; c < 64; c += 2)
@@ -1023,7 +1608,6 @@ __global__ void __launch_bounds__(THREADS, 1)
         tmem_ld32(tmem_base + lane_addr + Q_COL_DP + wg * 64, dr[0]);
         tmem_ld32(tmem_base + lane_addr + Q_COL_DP + wg * 64 + 32, dr[1]);
         tmem_wait_ld();
-#pragma unroll
         const uint64_t delta2 = pk2(delta, delta);
 #pragma unroll
         for (int c = 0; c < 32; ++c) {
@@ -1149,6 +1733,9 @@ static int32_t bwd_run(const attn_bwd::Params& p_const, const cdl_tensor* q, con
     attr_err = cudaFuncSetAttribute(attn_bwd_dkdv_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                     static_cast<int>(KV_SMEM_BYTES));
     if (attr_err == cudaSuccess)
+      attr_err = cudaFuncSetAttribute(attn_bwd_dkdv_persistent_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                      static_cast<int>(KVP_SMEM_BYTES));
+    if (attr_err == cudaSuccess)
       attr_err = cudaFuncSetAttribute(attn_bwd_dq_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                       static_cast<int>(Q_SMEM_BYTES));
   });
@@ -1203,8 +1790,20 @@ static int32_t bwd_run(const attn_bwd::Params& p_const, const cdl_tensor* q, con
   p.q_heads_total = static_cast<int>(H * B);
   p.q_chunk = chunk_of(H * B);
   if (have_k) {
-    dim3 grid(static_cast<unsigned>(static_cast<long long>(p.kv_blocks) * p.kv_heads_total));
-    CDL_CUDA(launch_pdl(attn_bwd_dkdv_kernel, grid, dim3(THREADS), KV_SMEM_BYTES, stream, tq, tk, tv, tdo, tdk, tdv, p));
+    const long long items = static_cast<long long>(p.kv_blocks) * p.kv_heads_total;
+    // More items than SMs: one CTA per SM takes them one after the other (items handed out at
+    // run time from a counter of this stream; without one, a fixed deal).
+    const bool persistent = p.variant == CDL_ATTN_PERSISTENT ||
+                            (p.variant == CDL_ATTN_AUTO && CDL_ATTN_BWD_PERSISTENT && items > sm_count());
+    if (persistent && items < (1ll << 30)) {
+      const long long ctas = items < sm_count() ? items : sm_count();
+      unsigned int* counter = items > ctas ? sched_counter_for(2, dev, stream) : nullptr;
+      CDL_CUDA(launch_pdl(attn_bwd_dkdv_persistent_kernel, dim3(static_cast<unsigned>(ctas)), dim3(THREADS),
+                          KVP_SMEM_BYTES, stream, tq, tk, tv, tdo, tdk, tdv, p, counter));
+    } else {
+      dim3 grid(static_cast<unsigned>(items));
+      CDL_CUDA(launch_pdl(attn_bwd_dkdv_kernel, grid, dim3(THREADS), KV_SMEM_BYTES, stream, tq, tk, tv, tdo, tdk, tdv, p));
+    }
     CDL_CUDA(cudaGetLastError());
   }
   if (have_q) {
@@ -1244,6 +1843,8 @@ int32_t attn_bwd_execute(const cdl_attn_desc* desc, const cdl_tensor* q, const c
     return fail(CDL_ERR_INVALID, "%s: q and k must be [batch, seqlen, heads, head_dim]", op);
   const long long B = q->shape[0], Sq = q->shape[1], H = q->shape[2], Dh = q->shape[3];
   const long long Sk = k->shape[1], Hkv = k->shape[2];
+  if (desc->variant < CDL_ATTN_AUTO || desc->variant > CDL_ATTN_PERSISTENT)
+    return fail(CDL_ERR_INVALID, "%s: unknown kernel variant %d", op, desc->variant);
   if (Dh != D)
     return fail(CDL_ERR_UNSUPPORTED, "%s: head dimension %lld is not implemented (only 128)", op, Dh);
   if (Hkv <= 0 || H % Hkv != 0)
@@ -1281,6 +1882,7 @@ int32_t attn_bwd_execute(const cdl_attn_desc* desc, const cdl_tensor* q, const c
   p.Sk = static_cast<int>(Sk);
   p.Sq_pad = static_cast<int>(Sq_pad);
   p.causal = desc->causal != 0;
+  p.variant = desc->variant;
   p.scale = desc->softmax_scale > 0.f ? desc->softmax_scale : 1.0f / sqrtf(static_cast<float>(D));
   p.scale_log2 = p.scale * 1.4426950408889634f;
   p.lse2 = lse2;
@@ -1324,6 +1926,8 @@ int32_t attn_bwd_packed_execute(const cdl_attn_desc* desc, const cdl_tensor* q, 
   const long long Tq = q->shape[0], H = q->shape[1], Dh = q->shape[2];
   const long long Tk = k->shape[0], Hkv = k->shape[1];
   const long long B = cu_q->rank == 1 ? cu_q->shape[0] - 1 : -1;
+  if (desc->variant < CDL_ATTN_AUTO || desc->variant > CDL_ATTN_PERSISTENT)
+    return fail(CDL_ERR_INVALID, "%s: unknown kernel variant %d", op, desc->variant);
   if (Dh != D)
     return fail(CDL_ERR_UNSUPPORTED, "%s: head dimension %lld is not implemented (only 128)", op, Dh);
   if (Hkv <= 0 || H % Hkv != 0)
@@ -1362,6 +1966,7 @@ int32_t attn_bwd_packed_execute(const cdl_attn_desc* desc, const cdl_tensor* q, 
   p.Sk = static_cast<int>(max_k);
   p.Sq_pad = static_cast<int>(Sq_pad);
   p.causal = desc->causal != 0;
+  p.variant = desc->variant;
   p.scale = desc->softmax_scale > 0.f ? desc->softmax_scale : 1.0f / sqrtf(static_cast<float>(D));
   p.scale_log2 = p.scale * 1.4426950408889634f;
   p.lse2 = static_cast<float*>(scratch);

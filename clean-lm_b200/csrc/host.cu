@@ -57,7 +57,8 @@ int sm_count() {
 }
 
 // Work counters of the kernels that hand out their work at run time (the CTA-pair GEMM's units,
-// kind 0; the persistent attention forward's items, kind 1): one per kind, device and stream, zero
+// kind 0; the persistent attention forward's items, kind 1; the persistent attention backward
+// kernels' items, kinds 2 and 3): one per kind, device and stream, zero
 // between launches (the kernel's last draw puts its counter back).  Launches on one stream run
 // one after the other, so they can share a counter; launches on different streams may overlap and
 // must not.  Inside the library's device image: nothing is allocated.  A launch that gets no
@@ -65,7 +66,7 @@ int sm_count() {
 #ifndef CDL_DYNAMIC_WORK
 #define CDL_DYNAMIC_WORK 1
 #endif
-constexpr int SCHED_KINDS = 2;
+constexpr int SCHED_KINDS = 4;
 constexpr int SCHED_STREAMS = 256;
 __device__ unsigned int g_sched_counters[SCHED_KINDS * SCHED_STREAMS];
 

@@ -317,15 +317,18 @@ int32_t cdl_b200_matmul_mx_out(const cdl_mx_tensor* a, const cdl_mx_tensor* b, c
  * j <= i + Sk - Sq (attention/mod.rs:24-31).  D = 128, H % Hkv == 0. */
 typedef enum {
   CDL_ATTN_AUTO = 0,      /* the library's choice (the persistent kernel) */
-  CDL_ATTN_ONE_SHOT = 1,  /* forward: one short-lived CTA per 256 query rows */
+  CDL_ATTN_ONE_SHOT = 1,  /* forward: one short-lived CTA per 256 query rows; backward: one
+                           * short-lived CTA per 128-key block (dK, dV) */
   CDL_ATTN_PERSISTENT = 2 /* forward: one CTA per SM walks the 256-row work items, longest first;
-                           * part of the exponentials on the FMA pipe */
+                           * part of the exponentials on the FMA pipe; backward: one CTA per SM
+                           * walks the key blocks (dK, dV), longest first.  The automatic choice
+                           * of the backward is this form when there are more key blocks than SMs. */
 } cdl_attn_variant;
 typedef struct {
   float softmax_scale; /* <= 0 selects 1/sqrt(D) (exec.rs:198-200) */
   int32_t causal;      /* 0 = AttentionMask::None, 1 = AttentionMask::Causal */
-  int32_t variant;     /* cdl_attn_variant: a tuner's per-node choice for the forward (see "Per-call
-                        * kernel choices"); the backward ignores it.  0 = default. */
+  int32_t variant;     /* cdl_attn_variant: a tuner's per-node choice (see "Per-call kernel
+                        * choices").  0 = default. */
 } cdl_attn_desc;
 
 int32_t cdl_b200_attn_fwd(const cdl_attn_desc* desc, const cdl_tensor* q, const cdl_tensor* k,

@@ -139,9 +139,9 @@ def test_fwd_rejections(cdl, gpu_ok):
     assert out.out.shape == (0, 8, 2, 128)
 
 
-def check_bwd(cdl, q, k, v, do, causal, scale=None):
+def check_bwd(cdl, q, k, v, do, causal, scale=None, variant=0):
     dq_, dk_, dv_, ddo = q.cuda(), k.cuda(), v.cuda(), do.cuda()
-    opts = cdl.ops.AttentionOpts(softmax_scale=scale, causal=causal)
+    opts = cdl.ops.AttentionOpts(softmax_scale=scale, causal=causal, variant=variant)
     fwd = cdl.ops.attention_fwd(dq_, dk_, dv_, opts)
     dq, dk, dv = cdl.ops.attention_bwd(dq_, dk_, dv_, fwd.out, ddo, fwd.lse, opts)
     ref = oracle.attention(to_f32(q), to_f32(k), to_f32(v), to_f32(do), scale=scale, causal=causal)
@@ -162,10 +162,55 @@ BWD_CASES = [
 ]
 
 
+@pytest.mark.parametrize("variant", [1, 2], ids=["one_shot", "persistent"])
 @pytest.mark.parametrize("b,sq,sk,hq,hk,causal", BWD_CASES)
-def test_bwd_cases(cdl, gpu_ok, b, sq, sk, hq, hk, causal):
+def test_bwd_cases(cdl, gpu_ok, b, sq, sk, hq, hk, causal, variant):
     q, k, v, do = make(b, sq, sk, hq, hk)
-    check_bwd(cdl, q, k, v, do, causal)
+    check_bwd(cdl, q, k, v, do, causal, variant=variant)
+
+
+@pytest.mark.parametrize("b,s,hq,hk,causal", [(6, 1024, 8, 4, True), (3, 1100, 8, 8, False),
+                                              (20, 300, 8, 8, True)])
+def test_bwd_persistent_equals_one_shot(cdl, gpu_ok, b, s, hq, hk, causal):
+    """More key blocks than SMs, so every CTA of the persistent dK/dV kernel takes several items
+    (among them one-block items, whose hand-over to the next item is the shortest): the two forms
+    run the same arithmetic in the same order and must agree bit for bit; one (batch, head)
+    against the oracle."""
+    q, k, v, do = (t.cuda() for t in make(b, s, s, hq, hk, seed=19))
+    fwd = cdl.ops.attention_fwd(q, k, v, cdl.ops.AttentionOpts(causal=causal))
+    res = {}
+    for variant in (1, 2):
+        opts = cdl.ops.AttentionOpts(causal=causal, variant=variant)
+        for rep in range(2):     # twice: the second launch finds the work counter as the first left it
+            res[variant] = cdl.ops.attention_bwd(q, k, v, fwd.out, do, fwd.lse, opts)
+    for name, a, c in zip(("dq", "dk", "dv"), res[1], res[2]):
+        assert torch.equal(a, c), name
+    sl = (slice(b - 1, b), slice(None))
+    g = hq // hk
+    r = oracle.attention(to_f32(q[sl][:, :, :g]), to_f32(k[sl][:, :, :1]), to_f32(v[sl][:, :, :1]),
+                         to_f32(do[sl][:, :, :g]), causal=causal)
+    for name, got in (("dk", res[2][1]), ("dv", res[2][2])):
+        assert_all_close(name, to_f32(got[sl][:, :, :1]), r[name], oracle.attention_tolerance(r[name], 2e-2, 2e-2))
+
+
+def test_bwd_on_several_streams_at_once(cdl, gpu_ok):
+    """Persistent backward launches on different streams draw from different work counters."""
+    q, k, v, do = (t.cuda() for t in make(4, 1024, 1024, 8, 8, seed=23))
+    fwd = cdl.ops.attention_fwd(q, k, v)
+    opts = cdl.ops.AttentionOpts(variant=2)
+    ref = cdl.ops.attention_bwd(q, k, v, fwd.out, do, fwd.lse, opts)
+    torch.cuda.synchronize()
+    streams = [torch.cuda.Stream() for _ in range(3)]
+    outs = []
+    for rep in range(2):
+        for st in streams:
+            st.wait_stream(torch.cuda.current_stream())
+            with torch.cuda.stream(st):
+                outs.append(cdl.ops.attention_bwd(q, k, v, fwd.out, do, fwd.lse, opts))
+    torch.cuda.synchronize()
+    for got in outs:
+        for a, c in zip(got, ref):
+            assert torch.equal(a, c)
 
 
 def test_bwd_fused_qkv_views(cdl, gpu_ok):
@@ -244,10 +289,11 @@ PACKED_CASES = [
 ]
 
 
+@pytest.mark.parametrize("variant", [1, 2], ids=["one_shot", "persistent"])
 @pytest.mark.parametrize("sq,sk,hq,hk,causal,bound", PACKED_CASES)
-def test_packed_fwd_bwd(cdl, gpu_ok, sq, sk, hq, hk, causal, bound):
+def test_packed_fwd_bwd(cdl, gpu_ok, sq, sk, hq, hk, causal, bound, variant):
     q, k, v, do, cu_q, cu_k = make_packed(sq, sk, hq, hk)
-    opts = cdl.ops.AttentionOpts(causal=causal, cu_seqlens_q=cu_q.cuda(), cu_seqlens_k=cu_k.cuda(),
+    opts = cdl.ops.AttentionOpts(causal=causal, variant=variant, cu_seqlens_q=cu_q.cuda(), cu_seqlens_k=cu_k.cuda(),
                                  max_seqlen_q=max(sq) if bound else None,
                                  max_seqlen_k=max(sk) if bound else None)
     qd, kd, vd, dod = q.cuda(), k.cuda(), v.cuda(), do.cuda()
@@ -339,15 +385,16 @@ def _assert_same_up_to_one_rounding(name, got, ref):
     assert (got == ref).float().mean().item() > 0.99, f"{name}: too many elements differ"
 
 
+@pytest.mark.parametrize("variant", [1, 2], ids=["one_shot", "persistent"])
 @pytest.mark.parametrize("b,s,hq,hk", [(2, 384, 2, 2), (1, 200, 4, 2), (2, 130, 2, 1)])
-def test_bwd_with_rope_equals_bwd_then_inverse_rope(cdl, gpu_ok, b, s, hq, hk):
+def test_bwd_with_rope_equals_bwd_then_inverse_rope(cdl, gpu_ok, b, s, hq, hk, variant):
     """cdl_b200_attn_bwd_rope: dq and dk with the transposed rotary rotation applied in the store
     epilogues equal the plain backward followed by cdl_b200_rope(backward = 1); dv is untouched."""
     L = cdl._lib
     q, k, v, do = make(b, s, s, hq, hk, seed=21)
     qd, kd, vd, dod = q.cuda(), k.cuda(), v.cuda(), do.cuda()
     table = _rope_table(s).cuda()
-    opts = cdl.ops.AttentionOpts(causal=True)
+    opts = cdl.ops.AttentionOpts(causal=True, variant=variant)
     fwd = cdl.ops.attention_fwd(qd, kd, vd, opts)
     dq, dk, dv = cdl.ops.attention_bwd(qd, kd, vd, fwd.out, dod, fwd.lse, opts)
     keep = []
@@ -364,14 +411,15 @@ def test_bwd_with_rope_equals_bwd_then_inverse_rope(cdl, gpu_ok, b, s, hq, hk):
     assert torch.equal(fv, dv)
 
 
-def test_packed_bwd_with_rope_equals_bwd_then_inverse_rope(cdl, gpu_ok):
+@pytest.mark.parametrize("variant", [1, 2], ids=["one_shot", "persistent"])
+def test_packed_bwd_with_rope_equals_bwd_then_inverse_rope(cdl, gpu_ok, variant):
     L = cdl._lib
     lens = [128, 300, 77]
     q, k, v, do, cu_q, cu_k = make_packed(lens, lens, 4, 2)
     qd, kd, vd, dod, cu = q.cuda(), k.cuda(), v.cuda(), do.cuda(), cu_q.cuda()
     table = _rope_table(max(lens)).cuda()
-    opts = cdl.ops.AttentionOpts(causal=True, cu_seqlens_q=cu, cu_seqlens_k=cu, max_seqlen_q=max(lens),
-                                 max_seqlen_k=max(lens))
+    opts = cdl.ops.AttentionOpts(causal=True, variant=variant, cu_seqlens_q=cu, cu_seqlens_k=cu,
+                                 max_seqlen_q=max(lens), max_seqlen_k=max(lens))
     fwd = cdl.ops.attention_fwd(qd, kd, vd, opts)
     mark = lambda t: torch.full_like(t, 7.0)
     dq, dk, dv = cdl.ops.attention_bwd(qd, kd, vd, fwd.out, dod, fwd.lse, opts, dq=mark(qd), dk=mark(kd), dv=mark(vd))
