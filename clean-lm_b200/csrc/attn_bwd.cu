@@ -75,8 +75,8 @@ constexpr int KV_LOW_REGS = 72, KV_HIGH_REGS = 216;
 #define CDL_ATTN_BWD_CHUNK_MB 16
 #endif
 
-// 1: the dK/dV kernel runs as one CTA per SM over many key blocks when there are more key blocks
-// than SMs; 0: always one CTA per key block.
+// 1: the dK/dV and dQ kernels run as one CTA per SM over many key / query blocks when there are
+// more blocks than SMs; 0: always one CTA per block.
 #ifndef CDL_ATTN_BWD_PERSISTENT
 #define CDL_ATTN_BWD_PERSISTENT 1
 #endif
@@ -1708,6 +1708,480 @@ __global__ void __launch_bounds__(THREADS, 1)
   if (threadIdx.x == 0 && *abort_word != 0) atomicExch(p.status, *abort_word);
 }
 
+// ---------------------------------------------------------------- dQ kernel, persistent form
+// attn_bwd_dq_kernel's tile program run by one CTA per SM over many (query block, head, batch)
+// items, handed out like the items of the persistent dK/dV kernel.  All barrier phases count key
+// blocks (or items) across items; the K / V stages keep cycling.  Q is free for the next item's
+// load once the item's last S has run, dO once its last dP has (q_free / do_free, committed one
+// key block before the item ends); S and dP of the next item's first key block are issued right
+// behind the item's last dQ product; dQ leaves through the K stage of the item's last key block,
+// which the storing thread gives back to the producer when the TMA stores have read it.  The next
+// item's first dQ product, which overwrites the accumulator, waits for that item's first dS, which
+// the compute warps write after they have read the accumulator.
+struct QpBarriers {
+  uint64_t qdo_full, q_free, do_free;
+  uint64_t k_full[QK_STAGES], k_empty[QK_STAGES], v_full[2], v_empty[2];
+  uint64_t s_full[2], dp_full, ds_ready, dq_done;
+  uint64_t item_full[KVP_SLOTS], item_read[KVP_SLOTS];
+  int item_ring[KVP_SLOTS];
+  uint32_t tmem_base;
+  int abort_word;
+};
+constexpr size_t QP_SMEM_BYTES = (4 + QK_STAGES) * TILE_BYTES + sizeof(QpBarriers);
+static_assert(QP_SMEM_BYTES <= 232448, "exceeds the 227 KiB of shared memory a CTA can opt in to");
+
+// One item: query rows [q0, q0 + 128) of head h of sequence b, walked over n_kv key blocks.
+struct QItem {
+  int b, h, kvh, bt, q0, q_base, k_base, Sq, Sk, n_kv;
+  bool exceeds;
+};
+__device__ __forceinline__ QItem q_item_of(const Params& p, int idx) {
+  QItem v;
+  int rank, hb;
+  cta_coords(idx, p.q_blocks, p.q_heads_total, p.q_chunk, rank, hb);
+  v.b = hb / p.H;
+  v.h = hb - v.b * p.H;
+  v.kvh = v.h / (p.H / p.Hkv);
+  v.bt = v.b;
+  v.q_base = 0;
+  v.k_base = 0;
+  v.Sq = p.Sq;
+  v.Sk = p.Sk;
+  v.exceeds = false;
+  if (p.cu_q != nullptr) {
+    v.q_base = p.cu_q[v.b];
+    v.Sq = p.cu_q[v.b + 1] - v.q_base;
+    v.k_base = p.cu_k[v.b];
+    v.Sk = p.cu_k[v.b + 1] - v.k_base;
+    v.bt = 0;
+    if (v.Sq > p.Sq || v.Sk > p.Sk) {
+      v.exceeds = true;
+      v.Sq = min(v.Sq, p.Sq);
+      v.Sk = min(v.Sk, p.Sk);
+    }
+  }
+  v.q0 = (p.q_blocks - 1 - rank) * BQ;  // the last query block sees the most keys
+  v.n_kv = 0;
+  if (v.q0 < v.Sq) {
+    int max_key = v.Sk - 1;
+    if (p.causal) max_key = min(max_key, min(v.q0 + BQ - 1, v.Sq - 1) + v.Sk - v.Sq);
+    v.n_kv = max_key < 0 ? 0 : max_key / BKV + 1;
+  }
+  return v;
+}
+
+__global__ void __launch_bounds__(THREADS, 1)
+    attn_bwd_dq_persistent_kernel(const __grid_constant__ CUtensorMap tmap_q,
+                                  const __grid_constant__ CUtensorMap tmap_k,
+                                  const __grid_constant__ CUtensorMap tmap_v,
+                                  const __grid_constant__ CUtensorMap tmap_do,
+                                  const __grid_constant__ CUtensorMap tmap_dq, const Params p,
+                                  unsigned int* item_counter) {
+  extern __shared__ __align__(1024) uint8_t smem[];
+  if ((smem_u32(smem) & 1023u) != 0) {
+    if (threadIdx.x == 0) atomicExch(p.status, 902);
+    return;
+  }
+  uint8_t* s_q = smem;
+  uint8_t* s_do = smem + TILE_BYTES;
+  uint8_t* s_k = smem + 2 * TILE_BYTES;                 // QK_STAGES stages
+  uint8_t* s_v = s_k + QK_STAGES * TILE_BYTES;          // 2 stages
+  QpBarriers* bars = reinterpret_cast<QpBarriers*>(s_v + 2 * TILE_BYTES);
+  volatile int* abort_word = &bars->abort_word;
+
+  const int warp = threadIdx.x >> 5;
+  const int lane = threadIdx.x & 31;
+  const int total = p.q_blocks * p.q_heads_total;
+  const int nc = static_cast<int>(gridDim.x), cid = static_cast<int>(blockIdx.x);
+
+  if (threadIdx.x == 0) {
+    mbar_init(&bars->qdo_full, 1);
+    mbar_init(&bars->q_free, 1);
+    mbar_init(&bars->do_free, 1);
+    for (int i = 0; i < QK_STAGES; ++i) {
+      mbar_init(&bars->k_full[i], 1);
+      mbar_init(&bars->k_empty[i], 1);
+    }
+    for (int i = 0; i < 2; ++i) {
+      mbar_init(&bars->v_full[i], 1);
+      mbar_init(&bars->v_empty[i], 1);
+      mbar_init(&bars->s_full[i], 1);
+    }
+    mbar_init(&bars->dp_full, 1);
+    mbar_init(&bars->ds_ready, 8);  // one arrival per compute warp
+    mbar_init(&bars->dq_done, 1);
+    for (int i = 0; i < KVP_SLOTS; ++i) {
+      mbar_init(&bars->item_full[i], 1);
+      mbar_init(&bars->item_read[i], 9);  // the issuing lane and the eight compute warps
+    }
+    bars->abort_word = 0;
+    fence_mbar_init();
+  }
+  if (warp == 1) {
+    tmem_alloc(&bars->tmem_base, TMEM_COLS);
+    tmem_relinquish();
+  }
+  if (warp == 0 && lane == 0) {
+    tma_prefetch_desc(&tmap_q);
+    tma_prefetch_desc(&tmap_k);
+    tma_prefetch_desc(&tmap_v);
+    tma_prefetch_desc(&tmap_do);
+    tma_prefetch_desc(&tmap_dq);
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = bars->tmem_base;
+  grid_dep_wait();  // the set-up above overlaps the previous kernel's tail; global memory from here on
+  grid_dep_launch();
+
+  if (warp == 0) {
+    // ------------------------------------------------------------ TMA producer (and item hand-out)
+    setmaxnreg_dec<KV_LOW_REGS>();
+    if (elect_one()) {
+      const unsigned total_draws = static_cast<unsigned>((total > nc ? total - nc : 0) + (nc < total ? nc : total));
+      int idx = cid < total ? cid : -1;
+      unsigned drawn = 0;
+      uint32_t g = 0, qn = 0;        // key blocks / non-empty items so far
+      uint32_t sk = 0, kpar = 0;     // K stage of key block g and the parity of its use
+      bool ok = true;
+      for (int k = 0; ok; ++k) {
+        if (k > 0) {
+          if (item_counter != nullptr) {
+            idx = static_cast<unsigned>(nc) + drawn < static_cast<unsigned>(total) ? static_cast<int>(nc + drawn) : -1;
+            if (drawn + 1 == total_draws) atomicExch(item_counter, 0u);
+          } else {
+            idx = kvp_fixed_item(k, cid, nc, total);
+          }
+        }
+        if (k >= KVP_SLOTS &&
+            !mbar_wait(&bars->item_read[k % KVP_SLOTS], ((k / KVP_SLOTS) - 1) & 1, abort_word, 134)) {
+          ok = false;
+          break;
+        }
+        bars->item_ring[k % KVP_SLOTS] = idx;
+        mbar_arrive(&bars->item_full[k % KVP_SLOTS]);
+        if (idx < 0) break;
+        const QItem v = q_item_of(p, idx);
+        if (v.exceeds) atomicExch(p.status, STATUS_SEQ_EXCEEDS_BOUND);
+        if (v.n_kv > 0) {
+          ok = mbar_wait(&bars->q_free, (qn & 1) ^ 1, abort_word, 135) &&
+               mbar_wait(&bars->do_free, (qn & 1) ^ 1, abort_word, 136);
+          if (!ok) break;
+          ++qn;
+          mbar_arrive_expect_tx(&bars->qdo_full, 2 * TILE_BYTES);
+#pragma unroll
+          for (int dh = 0; dh < 2; ++dh) {
+            tma_load_4d(s_q + dh * PANEL_BYTES, &tmap_q, &bars->qdo_full, dh * 64, v.q_base + v.q0, v.h, v.bt);
+            tma_load_4d(s_do + dh * PANEL_BYTES, &tmap_do, &bars->qdo_full, dh * 64, v.q_base + v.q0, v.h, v.bt);
+          }
+          for (int j = 0; j < v.n_kv; ++j, ++g) {
+            if (!mbar_wait(&bars->k_empty[sk], kpar ^ 1, abort_word, 131)) { ok = false; break; }
+            mbar_arrive_expect_tx(&bars->k_full[sk], TILE_BYTES);
+#pragma unroll
+            for (int dh = 0; dh < 2; ++dh)
+              tma_load_4d(s_k + sk * TILE_BYTES + dh * PANEL_BYTES, &tmap_k, &bars->k_full[sk], dh * 64,
+                          v.k_base + j * BKV, v.kvh, v.bt);
+            const uint32_t s = g & 1;
+            if (!mbar_wait(&bars->v_empty[s], ((g >> 1) & 1) ^ 1, abort_word, 132)) { ok = false; break; }
+            mbar_arrive_expect_tx(&bars->v_full[s], TILE_BYTES);
+#pragma unroll
+            for (int dh = 0; dh < 2; ++dh)
+              tma_load_4d(s_v + s * TILE_BYTES + dh * PANEL_BYTES, &tmap_v, &bars->v_full[s], dh * 64,
+                          v.k_base + j * BKV, v.kvh, v.bt);
+            if (++sk == QK_STAGES) {
+              sk = 0;
+              kpar ^= 1;
+            }
+          }
+        }
+        // The next item is drawn when this item's last loads are on their way.
+        if (ok && item_counter != nullptr) drawn = atomicAdd(item_counter, 1u);
+      }
+    }
+  } else if (warp == 1) {
+    // ------------------------------------------------------------ MMA issuer
+    // Issue order inside an item: S(j+1) [other S buffer], then after dS(j) has arrived dP(j+1)
+    // and dQ(j); behind the last dQ of an item come S(0) and dP(0) of the next one.
+    setmaxnreg_dec<KV_LOW_REGS>();
+    if (elect_one()) {
+      const uint32_t idesc_kk = make_idesc_bf16(128, 128, 0, 0);
+      const uint32_t idesc_kmn = make_idesc_bf16(128, 128, 0, 1);
+      const uint32_t q_lo = desc_lo(smem_u32(s_q), 16), do_lo = desc_lo(smem_u32(s_do), 16);
+      const uint32_t k_lo = desc_lo(smem_u32(s_k), 16), v_lo = desc_lo(smem_u32(s_v), 16);
+      const uint32_t k_mn_lo = desc_lo(smem_u32(s_k), PANEL_BYTES);
+      const uint32_t d_s = tmem_base + Q_COL_S, d_dp = tmem_base + Q_COL_DP, d_dq = tmem_base + Q_COL_DQ;
+      auto issue_s = [&](uint32_t buf, uint32_t stage) {  // S = Q K_j^T
+        const uint32_t ka = k_lo + stage * (TILE_BYTES >> 4);
+        const uint32_t d = d_s + buf * 128;
+#pragma unroll
+        for (int k = 0; k < 8; ++k)
+          umma_ss(d, desc_at(q_lo, koff_k(k)), desc_at(ka, koff_k(k)), idesc_kk, k != 0);
+        umma_commit(&bars->s_full[buf]);
+      };
+      auto issue_dp = [&](uint32_t stage) {  // dP = dO V_j^T
+        const uint32_t va = v_lo + stage * (TILE_BYTES >> 4);
+#pragma unroll
+        for (int k = 0; k < 8; ++k)
+          umma_ss(d_dp, desc_at(do_lo, koff_k(k)), desc_at(va, koff_k(k)), idesc_kk, k != 0);
+        umma_commit(&bars->dp_full);
+        umma_commit(&bars->v_empty[stage]);
+      };
+      uint32_t g = 0, qn = 0, sk = 0, kpar = 0;
+      bool ok = true;
+      for (int k = 0; ok; ++k) {
+        if (!mbar_wait(&bars->item_full[k % KVP_SLOTS], (k / KVP_SLOTS) & 1, abort_word, 237)) break;
+        const int idx = bars->item_ring[k % KVP_SLOTS];
+        mbar_arrive(&bars->item_read[k % KVP_SLOTS]);
+        if (idx < 0) break;
+        const int n_kv = q_item_of(p, idx).n_kv;
+        if (n_kv == 0) continue;
+        ok = mbar_wait(&bars->qdo_full, qn & 1, abort_word, 231) &&
+             mbar_wait(&bars->k_full[sk], kpar, abort_word, 232);
+        if (!ok) break;
+        tc_fence_after();
+        issue_s(g & 1, sk);
+        if (n_kv == 1) umma_commit(&bars->q_free);
+        ok = mbar_wait(&bars->v_full[g & 1], (g >> 1) & 1, abort_word, 233);
+        if (!ok) break;
+        tc_fence_after();
+        issue_dp(g & 1);
+        if (n_kv == 1) umma_commit(&bars->do_free);
+        for (int j = 0; j < n_kv; ++j, ++g) {
+          const uint32_t s = g & 1;  // S buffer and V stage
+          const uint32_t sk1 = sk + 1 == QK_STAGES ? 0 : sk + 1;
+          const uint32_t kpar1 = sk1 == 0 ? kpar ^ 1 : kpar;
+          const bool has_next = j + 1 < n_kv;
+          if (has_next) {
+            // K and V of the next block (loaded a block ago as a rule).  S buffer s ^ 1 held
+            // dS of the block before, whose reader dQ was issued before this point.
+            ok = mbar_wait(&bars->k_full[sk1], kpar1, abort_word, 234) &&
+                 mbar_wait(&bars->v_full[s ^ 1], ((g + 1) >> 1) & 1, abort_word, 236);
+            if (!ok) break;
+            tc_fence_after();
+            issue_s(s ^ 1, sk1);
+            if (j + 2 == n_kv) umma_commit(&bars->q_free);
+          }
+          ok = mbar_wait(&bars->ds_ready, g & 1, abort_word, 235);
+          if (!ok) break;
+          tc_fence_after();
+          if (has_next) {
+            issue_dp(s ^ 1);
+            if (j + 2 == n_kv) umma_commit(&bars->do_free);
+          }
+          // dQ += dS K_j : A = dS (bf16 pairs in columns [0,32) and [64,96) of the S buffer),
+          // B = K_j MN-major.  The first one of an item overwrites the previous item's dQ, which
+          // the compute warps have read before they wrote this dS.
+          const uint32_t kf = k_mn_lo + sk * (TILE_BYTES >> 4);
+          const uint32_t a_ds = d_s + s * 128;
+          const uint32_t acc = j > 0 ? 1u : 0u;
+#pragma unroll
+          for (int kk = 0; kk < 8; ++kk)
+            umma_ts(d_dq, a_ds + acol(kk), desc_at(kf, koff_mn(kk)), idesc_kmn, kk != 0 ? 1u : acc);
+          // After the item's last key block its K stage carries dQ out; the storing thread
+          // releases it.
+          if (has_next) umma_commit(&bars->k_empty[sk]);
+          else umma_commit(&bars->dq_done);
+          sk = sk1;
+          kpar = kpar1;
+        }
+        ++qn;
+      }
+    }
+  } else if (warp < 4) {
+    setmaxnreg_dec<KV_LOW_REGS>();
+  } else {
+    // ------------------------------------------------------------ compute warps (4..11)
+    setmaxnreg_inc<KV_HIGH_REGS>();
+    const int ct = threadIdx.x - 128;
+    const int wg = (warp - 4) >> 2;  // key-column half this thread works on
+    const int quad = warp & 3;
+    const int r = quad * 32 + lane;  // query row inside the block == TMEM lane
+    const uint32_t lane_addr = static_cast<uint32_t>(quad * 32) << 16;
+    bool ok = true;
+    auto read_item = [&](int k) -> int {
+      if (!mbar_wait(&bars->item_full[k % KVP_SLOTS], (k / KVP_SLOTS) & 1, abort_word, 336)) return -2;
+      const int idx = bars->item_ring[k % KVP_SLOTS];
+      __syncwarp();
+      if (lane == 0) mbar_arrive(&bars->item_read[k % KVP_SLOTS]);
+      return idx;
+    };
+    auto stat_index = [&](const QItem& v) {
+      return (static_cast<long long>(v.b) * p.H + v.h) * p.Sq_pad + v.q0 + r;
+    };
+    uint32_t g = 0, qn = 0;
+    int idx = read_item(0);
+    QItem v;
+    float lse2 = 0.f, delta = 0.f;  // +inf / 0 for rows that contribute nothing (and padding)
+    if (idx >= 0) {
+      v = q_item_of(p, idx);
+      if (v.n_kv > 0) {
+        lse2 = p.lse2[stat_index(v)];
+        delta = p.delta[stat_index(v)];
+      }
+    }
+    for (int k = 0; idx >= 0 && ok; ++k) {
+      const int n_kv = v.n_kv;
+      const int row = v.q0 + r;
+      const int shift = v.Sk - v.Sq;
+      const int key_limit = p.causal ? min(v.Sk - 1, row + shift) : v.Sk - 1;
+      const int warp_limit = p.causal ? min(v.Sk - 1, v.q0 + quad * 32 + shift) : v.Sk - 1;
+      for (int j = 0; j < n_kv; ++j) {
+        const uint32_t gi = g + j;
+        const uint32_t s = gi & 1;
+        const int key0 = j * BKV + wg * 64;
+        const bool need_mask = key0 + 63 > warp_limit;  // warp-uniform
+        if (!mbar_wait(&bars->s_full[s], (gi >> 1) & 1, abort_word, 331)) { ok = false; break; }
+        tc_fence_after();
+        float pr[64];
+        {
+          uint32_t sr[2][32];
+          tmem_ld32(tmem_base + lane_addr + Q_COL_S + s * 128 + wg * 64, sr[0]);
+          tmem_ld32(tmem_base + lane_addr + Q_COL_S + s * 128 + wg * 64 + 32, sr[1]);
+          tmem_wait_ld();
+          float x[64];
+          const uint64_t scale2 = pk2(p.scale_log2, p.scale_log2), neg_lse2 = pk2(-lse2, -lse2);
+#pragma unroll
+          for (int c = 0; c < 64; c += 2)
+            upk2(fma_x2(pk2(__uint_as_float(sr[c >> 5][c & 31]), __uint_as_float(sr[c >> 5][(c & 31) + 1])), scale2, neg_lse2),
+                 x[c], x[c + 1]);
+          exp2_row64(x, pr);
+          if (need_mask) {  // warp-uniform
+#pragma unroll
+            for (int c = 0; c < 64; ++c)
+              if (key0 + c > key_limit) pr[c] = 0.f;
+          }
+        }
+        if (!mbar_wait(&bars->dp_full, gi & 1, abort_word, 332)) { ok = false; break; }
+        tc_fence_after();
+        uint32_t pk[32];
+        {
+          uint32_t dr[2][32];
+          tmem_ld32(tmem_base + lane_addr + Q_COL_DP + wg * 64, dr[0]);
+          tmem_ld32(tmem_base + lane_addr + Q_COL_DP + wg * 64 + 32, dr[1]);
+          tmem_wait_ld();
+          const uint64_t delta2 = pk2(delta, delta);
+#pragma unroll
+          for (int c = 0; c < 32; ++c) {
+            // without the softmax scale: it is applied once, when dQ leaves tensor memory
+            float d0, d1;
+            upk2(mul_x2(pk2(pr[2 * c], pr[2 * c + 1]),
+                        sub_x2(pk2(__uint_as_float(dr[(2 * c) >> 5][(2 * c) & 31]),
+                                   __uint_as_float(dr[(2 * c) >> 5][((2 * c) & 31) + 1])),
+                               delta2)),
+                 d0, d1);
+            pk[c] = pack_bf16x2(d0, d1);
+          }
+        }
+        // dS (bf16 pairs) of this thread's 64 keys goes over the first 32 of the 64 S columns it has read
+        tmem_st32(tmem_base + lane_addr + Q_COL_S + s * 128 + wg * 64, pk);
+        tmem_wait_st();
+        tc_fence_before();
+        __syncwarp();
+        if (lane == 0) mbar_arrive(&bars->ds_ready);
+      }
+      if (!ok) break;
+
+      // The next item and its row statistics: fetched before the stores so that they have landed
+      // when the epilogue is through.
+      const int idx_next = read_item(k + 1);
+      QItem vn = v;
+      float lse2_next = 0.f, delta_next = 0.f;
+      if (idx_next >= 0) {
+        vn = q_item_of(p, idx_next);
+        if (vn.n_kv > 0) {
+          lse2_next = p.lse2[stat_index(vn)];
+          delta_next = p.delta[stat_index(vn)];
+        }
+      }
+
+      __nv_bfloat16* dst = p.dq + v.bt * p.dq_sb + static_cast<long long>(v.q_base + row) * p.dq_ss + v.h * p.dq_sh + wg * 64;
+      if (n_kv == 0) {
+        // Query rows without any visible key: their gradient is zero.
+        if (row < v.Sq) {
+#pragma unroll
+          for (int c = 0; c < 8; ++c) *reinterpret_cast<uint4*>(dst + c * 8) = make_uint4(0u, 0u, 0u, 0u);
+        }
+      } else {
+        // ---- epilogue: this thread's 64 columns of its dQ row, through the K stage of the item's
+        // last key block and TMA stores (a partial block of a packed sequence stores directly)
+        if (!mbar_wait(&bars->dq_done, qn & 1, abort_word, 333)) { ok = false; break; }
+        tc_fence_after();
+        const uint32_t sk_last = (g + n_kv - 1) % QK_STAGES;
+        uint8_t* stage = s_k + sk_last * TILE_BYTES;
+        const bool staged = p.cu_q == nullptr || v.q0 + BQ <= v.Sq;
+        uint8_t* stage_row = stage + wg * PANEL_BYTES + r * 128;
+        const bool rotate = p.rope != nullptr;
+#pragma unroll
+        for (int half = 0; half < 2; ++half) {
+          uint32_t a[32];
+          tmem_ld32(tmem_base + lane_addr + Q_COL_DQ + wg * 64 + half * 32, a);
+          tmem_wait_ld();
+          const float sc = p.scale;
+#pragma unroll
+          for (int gq = 0; gq < 4; ++gq) {
+            uint4 q;
+            q.x = pack_bf16x2(__uint_as_float(a[gq * 8 + 0]) * sc, __uint_as_float(a[gq * 8 + 1]) * sc);
+            q.y = pack_bf16x2(__uint_as_float(a[gq * 8 + 2]) * sc, __uint_as_float(a[gq * 8 + 3]) * sc);
+            q.z = pack_bf16x2(__uint_as_float(a[gq * 8 + 4]) * sc, __uint_as_float(a[gq * 8 + 5]) * sc);
+            q.w = pack_bf16x2(__uint_as_float(a[gq * 8 + 6]) * sc, __uint_as_float(a[gq * 8 + 7]) * sc);
+            if (staged || rotate)
+              *reinterpret_cast<uint4*>(stage_row + (((half * 4 + gq) ^ (r & 7)) << 4)) = q;
+            else if (row < v.Sq)
+              *reinterpret_cast<uint4*>(dst + half * 32 + gq * 8) = q;
+          }
+        }
+        if (rotate) {
+          // dQ of the queries before the rotary rotation (see rope_inverse_row)
+          uint4 rot[8];
+          compute_bar_sync();
+          rope_inverse_row(stage, wg, r, p.rope + static_cast<long long>(min(row, p.rope_rows - 1)) * 128, rot);
+          compute_bar_sync();
+#pragma unroll
+          for (int c = 0; c < 8; ++c) {
+            if (staged)
+              *reinterpret_cast<uint4*>(stage_row + ((c ^ (r & 7)) << 4)) = rot[c];
+            else if (row < v.Sq)
+              *reinterpret_cast<uint4*>(dst + c * 8) = rot[c];
+          }
+        }
+        if (staged) fence_proxy_async_smem();
+        compute_bar_sync();  // every thread is through with the stage (and with the accumulator)
+        if (ct == 0) {
+          if (staged) {
+            tma_store_4d(&tmap_dq, stage, 0, v.q_base + v.q0, v.h, v.bt);
+            tma_store_4d(&tmap_dq, stage + PANEL_BYTES, 64, v.q_base + v.q0, v.h, v.bt);
+            tma_store_commit();
+            tma_store_wait_read<0>();
+          }
+          mbar_arrive(&bars->k_empty[sk_last]);  // the stage goes back to the producer
+        }
+        tc_fence_before();
+        g += n_kv;
+        ++qn;
+      }
+      v = vn;
+      idx = idx_next;
+      lse2 = lse2_next;
+      delta = delta_next;
+    }
+  }
+
+  // ------------------------------------------------------------ tear-down
+  __syncwarp();
+  if (*abort_word != 0) {
+    const unsigned long long t0 = globaltimer_ns();
+    while (globaltimer_ns() - t0 < 200000ull) __nanosleep(1000);
+  }
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 1) {
+    tc_fence_after();
+    tmem_dealloc(tmem_base, TMEM_COLS);
+  }
+  if (threadIdx.x == 0 && *abort_word != 0) atomicExch(p.status, *abort_word);
+}
+
 static long long pad128(long long v) { return (v + 127) / 128 * 128; }
 
 }  // namespace attn_bwd
@@ -1738,6 +2212,9 @@ static int32_t bwd_run(const attn_bwd::Params& p_const, const cdl_tensor* q, con
     if (attr_err == cudaSuccess)
       attr_err = cudaFuncSetAttribute(attn_bwd_dq_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                       static_cast<int>(Q_SMEM_BYTES));
+    if (attr_err == cudaSuccess)
+      attr_err = cudaFuncSetAttribute(attn_bwd_dq_persistent_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                      static_cast<int>(QP_SMEM_BYTES));
   });
   if (attr_err != cudaSuccess)
     return fail(CDL_ERR_CUDA, "cudaFuncSetAttribute failed: %s", cudaGetErrorString(attr_err));
@@ -1807,8 +2284,18 @@ static int32_t bwd_run(const attn_bwd::Params& p_const, const cdl_tensor* q, con
     CDL_CUDA(cudaGetLastError());
   }
   if (have_q) {
-    dim3 grid(static_cast<unsigned>(static_cast<long long>(p.q_blocks) * p.q_heads_total));
-    CDL_CUDA(launch_pdl(attn_bwd_dq_kernel, grid, dim3(THREADS), Q_SMEM_BYTES, stream, tq, tk, tv, tdo, tdq, p));
+    const long long items = static_cast<long long>(p.q_blocks) * p.q_heads_total;
+    const bool persistent = p.variant == CDL_ATTN_PERSISTENT ||
+                            (p.variant == CDL_ATTN_AUTO && CDL_ATTN_BWD_PERSISTENT && items > sm_count());
+    if (persistent && items < (1ll << 30)) {
+      const long long ctas = items < sm_count() ? items : sm_count();
+      unsigned int* counter = items > ctas ? sched_counter_for(3, dev, stream) : nullptr;
+      CDL_CUDA(launch_pdl(attn_bwd_dq_persistent_kernel, dim3(static_cast<unsigned>(ctas)), dim3(THREADS),
+                          QP_SMEM_BYTES, stream, tq, tk, tv, tdo, tdq, p, counter));
+    } else {
+      dim3 grid(static_cast<unsigned>(items));
+      CDL_CUDA(launch_pdl(attn_bwd_dq_kernel, grid, dim3(THREADS), Q_SMEM_BYTES, stream, tq, tk, tv, tdo, tdq, p));
+    }
     CDL_CUDA(cudaGetLastError());
   }
   return CDL_OK;

@@ -172,7 +172,7 @@ def test_bwd_cases(cdl, gpu_ok, b, sq, sk, hq, hk, causal, variant):
 @pytest.mark.parametrize("b,s,hq,hk,causal", [(6, 1024, 8, 4, True), (3, 1100, 8, 8, False),
                                               (20, 300, 8, 8, True)])
 def test_bwd_persistent_equals_one_shot(cdl, gpu_ok, b, s, hq, hk, causal):
-    """More key blocks than SMs, so every CTA of the persistent dK/dV kernel takes several items
+    """More key blocks than SMs, so every CTA of the persistent dK/dV and dQ kernels takes several items
     (among them one-block items, whose hand-over to the next item is the shortest): the two forms
     run the same arithmetic in the same order and must agree bit for bit; one (batch, head)
     against the oracle."""
@@ -191,6 +191,7 @@ def test_bwd_persistent_equals_one_shot(cdl, gpu_ok, b, s, hq, hk, causal):
                          to_f32(do[sl][:, :, :g]), causal=causal)
     for name, got in (("dk", res[2][1]), ("dv", res[2][2])):
         assert_all_close(name, to_f32(got[sl][:, :, :1]), r[name], oracle.attention_tolerance(r[name], 2e-2, 2e-2))
+    assert_all_close("dq", to_f32(res[2][0][sl][:, :, :g]), r["dq"], oracle.attention_tolerance(r["dq"], 2e-2, 2e-2))
 
 
 def test_bwd_on_several_streams_at_once(cdl, gpu_ok):
