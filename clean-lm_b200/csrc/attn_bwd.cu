@@ -23,6 +23,10 @@
 //        S  = Q K^T   (SS) -> TMEM S[j & 1]      dS (bf16) overwrites it in place
 //        dP = dO V^T  (SS) -> TMEM [256,384)
 //        dQ += dS K   (A = dS from TMEM)          -> TMEM [384,512)
+// Kernels 2 and 3 exist in two forms: one short-lived CTA per block, and (the default when there
+// are more blocks than SMs) one CTA per SM that walks many blocks handed out at run time, so
+// that launch, allocation, first loads and first products of a block run under the previous
+// block's last products and stores.  Both forms execute the same arithmetic in the same order.
 // Scratch: LSE2 and delta, f32 [B, H, Sq_pad] each.
 #include "host.h"
 #include "ptx.cuh"
