@@ -239,41 +239,72 @@ __device__ __forceinline__ void compute_bar_sync() {
   asm volatile("bar.sync 1, 256;" ::: "memory");
 }
 
-// Inverse rotary rotation of one staged dQ / dK row, in place of the transposed-rotation kernel
-// that would otherwise re-read the tensor: thread (wg, r) holds columns [64 wg, 64 wg + 64) of row
-// r, staged as bf16 in two 128-byte-swizzled panels of [128 rows][64 columns]; the rotation pairs
-// column i with column i + 64, i.e. with the same chunk of the other panel.  With x the staged
-// (bf16-rounded) values, out_lo = x_lo cos + x_hi sin and out_hi = x_hi cos - x_lo sin, evaluated
-// in f32 exactly as the stand-alone kernel does on the stored bf16 tensor.  The caller has
-// synchronised the compute threads after staging and synchronises again before the rows are
-// overwritten (this function only reads).
-__device__ __forceinline__ void rope_inverse_row(const uint8_t* stage, int wg, int r, const float* cs,
-                                                 uint4 (&out)[8]) {
-  const uint8_t* own = stage + wg * PANEL_BYTES + r * 128;
-  const uint8_t* other = stage + (1 - wg) * PANEL_BYTES + r * 128;
-  const float sign = wg == 0 ? 1.0f : -1.0f;
+// Inverse rotary rotation of the staged dQ / dK rows, in place of the transposed-rotation kernel
+// that would otherwise re-read the tensor.  Thread (wg, r) has staged columns [64 wg, 64 wg + 64) of
+// row r as bf16 in two 128-byte-swizzled panels of [128 rows][64 columns]; the rotation pairs column
+// i with column i + 64, i.e. 16-byte chunk c of a row in the first panel with chunk c of that row
+// in the second.  The rotation itself is dealt out anew: the 128 x 8 (row, chunk) units go to the
+// 256 compute threads in order, unit i * 256 + ct to thread ct, so that eight neighbouring threads
+// read one row's cosines and sines side by side (the table rows of a tile are contiguous) and one
+// row of each panel without bank conflicts; a thread's 16 table loads are issued together by
+// rope_units_load, early enough to land under the last product, and a thread overwrites exactly
+// what it has read, so no barrier separates reading from writing.  With x the staged
+// (bf16-rounded) values, out_lo = x_lo cos + x_hi sin and out_hi = x_hi cos - x_lo sin, in f32 as
+// the stand-alone kernel computes them from the stored bf16 tensor.  The caller synchronises the
+// compute threads between staging and apply.  (Two earlier forms kept a thread on its own row:
+// all 128 table values of the row loaded chunk by chunk behind the barrier, then half of them
+// loaded ahead.  A warp's load then touches 32 table rows, 32 cache lines per instruction, and
+// the rotation cost 0.2 ms, then 0.1 ms per backward call at B 8, S 2048 -- more than the
+// stand-alone rotation kernels it replaced.)
+struct RopeUnits {
+  float4 t[16];  // per unit: cos[0..4), cos[4..8), sin[0..4), sin[4..8) of its chunk
+};
+__device__ __forceinline__ void rope_units_load(const float* table, int pos0, int rope_rows, int ct, RopeUnits& ru) {
 #pragma unroll
-  for (int c = 0; c < 8; ++c) {
-    const int off = (c ^ (r & 7)) << 4;
-    const uint4 a = *reinterpret_cast<const uint4*>(own + off);
-    const uint4 b = *reinterpret_cast<const uint4*>(other + off);
-    const float4 c0 = __ldg(reinterpret_cast<const float4*>(cs + c * 8));
-    const float4 c1 = __ldg(reinterpret_cast<const float4*>(cs + c * 8 + 4));
-    const float4 s0 = __ldg(reinterpret_cast<const float4*>(cs + 64 + c * 8));
-    const float4 s1 = __ldg(reinterpret_cast<const float4*>(cs + 64 + c * 8 + 4));
+  for (int i = 0; i < 4; ++i) {
+    const int id = i * 256 + ct;
+    const int row = id >> 3, c = id & 7;
+    const float* cs = table + static_cast<long long>(min(pos0 + row, rope_rows - 1)) * 128;
+    ru.t[i * 4 + 0] = __ldg(reinterpret_cast<const float4*>(cs + c * 8));
+    ru.t[i * 4 + 1] = __ldg(reinterpret_cast<const float4*>(cs + c * 8 + 4));
+    ru.t[i * 4 + 2] = __ldg(reinterpret_cast<const float4*>(cs + 64 + c * 8));
+    ru.t[i * 4 + 3] = __ldg(reinterpret_cast<const float4*>(cs + 64 + c * 8 + 4));
+  }
+}
+// to_stage: the rotated chunks go back to the staging tile (a TMA store follows); otherwise to
+// global memory: `dst_tile` is column 0 of the tile's first row, rows at `row_stride` elements,
+// the first `rows_ok` of them inside the sequence.
+__device__ __forceinline__ void rope_inverse_apply(uint8_t* stage, int ct, const RopeUnits& ru, bool to_stage,
+                                                   __nv_bfloat16* dst_tile, long long row_stride, int rows_ok) {
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {
+    const int id = i * 256 + ct;
+    const int row = id >> 3, c = id & 7;
+    uint8_t* lo_row = stage + row * 128;
+    uint8_t* hi_row = stage + PANEL_BYTES + row * 128;
+    const int off = (c ^ (row & 7)) << 4;
+    const uint4 a = *reinterpret_cast<const uint4*>(lo_row + off);
+    const uint4 b = *reinterpret_cast<const uint4*>(hi_row + off);
+    const float4 c0 = ru.t[i * 4 + 0], c1 = ru.t[i * 4 + 1], s0 = ru.t[i * 4 + 2], s1 = ru.t[i * 4 + 3];
     const float cv[8] = {c0.x, c0.y, c0.z, c0.w, c1.x, c1.y, c1.z, c1.w};
     const float sv[8] = {s0.x, s0.y, s0.z, s0.w, s1.x, s1.y, s1.z, s1.w};
     const uint32_t aw[4] = {a.x, a.y, a.z, a.w}, bw[4] = {b.x, b.y, b.z, b.w};
-    uint32_t ow[4];
+    uint32_t lw[4], hw[4];
 #pragma unroll
     for (int e = 0; e < 4; ++e) {
       const float x0 = __uint_as_float(aw[e] << 16), x1 = __uint_as_float(aw[e] & 0xffff0000u);
       const float y0 = __uint_as_float(bw[e] << 16), y1 = __uint_as_float(bw[e] & 0xffff0000u);
-      const float r0 = x0 * cv[2 * e] + y0 * (sv[2 * e] * sign);
-      const float r1 = x1 * cv[2 * e + 1] + y1 * (sv[2 * e + 1] * sign);
-      ow[e] = pack_bf16x2(r0, r1);
+      lw[e] = pack_bf16x2(x0 * cv[2 * e] + y0 * sv[2 * e], x1 * cv[2 * e + 1] + y1 * sv[2 * e + 1]);
+      hw[e] = pack_bf16x2(y0 * cv[2 * e] - x0 * sv[2 * e], y1 * cv[2 * e + 1] - x1 * sv[2 * e + 1]);
     }
-    out[c] = make_uint4(ow[0], ow[1], ow[2], ow[3]);
+    const uint4 ol = make_uint4(lw[0], lw[1], lw[2], lw[3]), oh = make_uint4(hw[0], hw[1], hw[2], hw[3]);
+    if (to_stage) {
+      *reinterpret_cast<uint4*>(lo_row + off) = ol;
+      *reinterpret_cast<uint4*>(hi_row + off) = oh;
+    } else if (row < rows_ok) {
+      *reinterpret_cast<uint4*>(dst_tile + row * row_stride + c * 8) = ol;
+      *reinterpret_cast<uint4*>(dst_tile + row * row_stride + 64 + c * 8) = oh;
+    }
   }
 }
 
@@ -752,6 +783,8 @@ __global__ void __launch_bounds__(THREADS, 1)
     }
 
     // ---- epilogue: dV and dK rows of this key block
+    RopeUnits rope_units;  // the table values of the inverse rotation: on their way while dV is staged
+    if (p.rope != nullptr) rope_units_load(p.rope, key0, p.rope_rows, ct, rope_units);
     if (ok && iters > 0) {
       ok = mbar_wait(&bars->dv_done, 0, abort_word, 325);
       tc_fence_after();
@@ -805,17 +838,8 @@ __global__ void __launch_bounds__(THREADS, 1)
         }
         if (rotate) {
           // dK of the keys before the rotary rotation: the staged rows are rotated back in place
-          uint4 rot[8];
           compute_bar_sync();
-          rope_inverse_row(stage, wg, r, p.rope + static_cast<long long>(min(key, p.rope_rows - 1)) * 128, rot);
-          compute_bar_sync();
-#pragma unroll
-          for (int c = 0; c < 8; ++c) {
-            if (staged)
-              *reinterpret_cast<uint4*>(stage_row + ((c ^ (r & 7)) << 4)) = rot[c];
-            else if (row_ok)
-              *reinterpret_cast<uint4*>(dst + c * 8) = rot[c];
-          }
+          rope_inverse_apply(stage, ct, rope_units, staged, dst - wg * 64 - r * p.dk_ss, p.dk_ss, p.Sk - key0);
         }
         if (staged) {
           fence_proxy_async_smem();
@@ -1337,6 +1361,8 @@ __global__ void __launch_bounds__(THREADS, 1)
         const uint32_t s_last = (g + iters - 1) & 1;
         const bool staged = p.cu_k == nullptr || v.key0 + BKV <= v.Sk;
         const bool row_ok = key < v.Sk;
+        RopeUnits rope_units;  // the table values of the inverse rotation: on their way while dV is staged
+        if (p.rope != nullptr) rope_units_load(p.rope, v.key0, p.rope_rows, ct, rope_units);
 #pragma unroll
         for (int which = 0; which < 2; ++which) {
           __nv_bfloat16* dst = which == 0 ? dv_row : dk_row;
@@ -1371,17 +1397,8 @@ __global__ void __launch_bounds__(THREADS, 1)
           }
           if (rotate) {
             // dK of the keys before the rotary rotation: the staged rows are rotated back in place
-            uint4 rot[8];
             compute_bar_sync();
-            rope_inverse_row(stage, wg, r, p.rope + static_cast<long long>(min(key, p.rope_rows - 1)) * 128, rot);
-            compute_bar_sync();
-#pragma unroll
-            for (int c = 0; c < 8; ++c) {
-              if (staged)
-                *reinterpret_cast<uint4*>(stage_row + ((c ^ (r & 7)) << 4)) = rot[c];
-              else if (row_ok)
-                *reinterpret_cast<uint4*>(dst + c * 8) = rot[c];
-            }
+            rope_inverse_apply(stage, ct, rope_units, staged, dst - wg * 64 - r * p.dk_ss, p.dk_ss, v.Sk - v.key0);
           }
           if (staged) fence_proxy_async_smem();
           compute_bar_sync();  // every thread is through with the stage (and with the accumulator)
@@ -1685,6 +1702,8 @@ __global__ void __launch_bounds__(THREADS, 1)
     }
 
     // ---- epilogue: this thread's 64 columns of its dQ row
+    RopeUnits rope_units;  // the table values of the inverse rotation: on their way under the last product
+    if (p.rope != nullptr) rope_units_load(p.rope, q0, p.rope_rows, threadIdx.x - 128, rope_units);
     if (ok && n_kv > 0) {
       ok = mbar_wait(&bars->dq_done, 0, abort_word, 333);
       tc_fence_after();
@@ -1720,18 +1739,9 @@ __global__ void __launch_bounds__(THREADS, 1)
         }
       }
       if (rotate) {
-        // dQ of the queries before the rotary rotation (see rope_inverse_row)
-        uint4 rot[8];
+        // dQ of the queries before the rotary rotation (see rope_inverse_apply)
         compute_bar_sync();
-        rope_inverse_row(s_k, wg, r, p.rope + static_cast<long long>(min(row, p.rope_rows - 1)) * 128, rot);
-        compute_bar_sync();
-#pragma unroll
-        for (int c = 0; c < 8; ++c) {
-          if (staged)
-            *reinterpret_cast<uint4*>(stage_row + ((c ^ (r & 7)) << 4)) = rot[c];
-          else if (row < p.Sq)
-            *reinterpret_cast<uint4*>(dst + c * 8) = rot[c];
-        }
+        rope_inverse_apply(s_k, threadIdx.x - 128, rope_units, staged, dst - wg * 64 - r * p.dq_ss, p.dq_ss, p.Sq - q0);
       }
       if (staged) {
         fence_proxy_async_smem();
@@ -2158,6 +2168,8 @@ __global__ void __launch_bounds__(THREADS, 1)
       } else {
         // ---- epilogue: this thread's 64 columns of its dQ row, through the K stage of the item's
         // last key block and TMA stores (a partial block of a packed sequence stores directly)
+        RopeUnits rope_units;  // the table values of the inverse rotation: on their way under the last product
+        if (p.rope != nullptr) rope_units_load(p.rope, v.q0, p.rope_rows, ct, rope_units);
         if (!mbar_wait(&bars->dq_done, qn & 1, abort_word, 333)) { ok = false; break; }
         tc_fence_after();
         const uint32_t sk_last = (g + n_kv - 1) % QK_STAGES;
@@ -2185,18 +2197,9 @@ __global__ void __launch_bounds__(THREADS, 1)
           }
         }
         if (rotate) {
-          // dQ of the queries before the rotary rotation (see rope_inverse_row)
-          uint4 rot[8];
+          // dQ of the queries before the rotary rotation (see rope_inverse_apply)
           compute_bar_sync();
-          rope_inverse_row(stage, wg, r, p.rope + static_cast<long long>(min(row, p.rope_rows - 1)) * 128, rot);
-          compute_bar_sync();
-#pragma unroll
-          for (int c = 0; c < 8; ++c) {
-            if (staged)
-              *reinterpret_cast<uint4*>(stage_row + ((c ^ (r & 7)) << 4)) = rot[c];
-            else if (row < v.Sq)
-              *reinterpret_cast<uint4*>(dst + c * 8) = rot[c];
-          }
+          rope_inverse_apply(stage, ct, rope_units, staged, dst - wg * 64 - r * p.dq_ss, p.dq_ss, v.Sq - v.q0);
         }
         if (staged) fence_proxy_async_smem();
         compute_bar_sync();  // every thread is through with the stage (and with the accumulator)
