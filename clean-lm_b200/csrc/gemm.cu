@@ -410,12 +410,24 @@ __device__ __forceinline__ void store_tile_rows_rope(const Params& p, uint32_t t
       ohi[g * 2] = pack_bf16x2(rh[0], rh[1]);
       ohi[g * 2 + 1] = pack_bf16x2(rh[2], rh[3]);
     }
+    if (p.wide) {  // whole 32-byte sectors per access, as in store_chunk_wide
 #pragma unroll
-    for (int g = 0; g < 4; ++g) {
-      *reinterpret_cast<uint4*>(dp + pr * 32 + g * 8) =
-          make_uint4(olo[g * 4], olo[g * 4 + 1], olo[g * 4 + 2], olo[g * 4 + 3]);
-      *reinterpret_cast<uint4*>(dp + (pr + 2) * 32 + g * 8) =
-          make_uint4(ohi[g * 4], ohi[g * 4 + 1], ohi[g * 4 + 2], ohi[g * 4 + 3]);
+      for (int g = 0; g < 2; ++g) {
+        const uint32_t wl[8] = {olo[g * 8], olo[g * 8 + 1], olo[g * 8 + 2], olo[g * 8 + 3],
+                                olo[g * 8 + 4], olo[g * 8 + 5], olo[g * 8 + 6], olo[g * 8 + 7]};
+        const uint32_t wh[8] = {ohi[g * 8], ohi[g * 8 + 1], ohi[g * 8 + 2], ohi[g * 8 + 3],
+                                ohi[g * 8 + 4], ohi[g * 8 + 5], ohi[g * 8 + 6], ohi[g * 8 + 7]};
+        st_global_v8(dp + pr * 32 + g * 16, wl);
+        st_global_v8(dp + (pr + 2) * 32 + g * 16, wh);
+      }
+    } else {
+#pragma unroll
+      for (int g = 0; g < 4; ++g) {
+        *reinterpret_cast<uint4*>(dp + pr * 32 + g * 8) =
+            make_uint4(olo[g * 4], olo[g * 4 + 1], olo[g * 4 + 2], olo[g * 4 + 3]);
+        *reinterpret_cast<uint4*>(dp + (pr + 2) * 32 + g * 8) =
+            make_uint4(ohi[g * 4], ohi[g * 4 + 1], ohi[g * 4 + 2], ohi[g * 4 + 3]);
+      }
     }
   }
 }
