@@ -208,16 +208,15 @@ __device__ __forceinline__ int kv_blocks_for_tile(int Sq, int Sk, int causal, in
   return max_key < 0 ? 0 : max_key / BKV + 1;
 }
 
-// Work items are ordered longest first (last query block first).  A CTA's first item is its
-// index; every further one is drawn from a counter at run time by the producer lane, which
-// publishes the k-th item of the CTA in slot k % ITEM_SLOTS of a ring in shared memory (-1: no
-// further item).  The MMA lane (once per tile) and the softmax warps read the slot after its
+// Work items are ordered longest first (last query block first).  Every item is drawn from a
+// counter at run time by the producer lane, which publishes the k-th item of the CTA in slot
+// k % ITEM_SLOTS of a ring in shared memory (-1: no further item).  The MMA lane (once per tile) and the softmax warps read the slot after its
 // barrier and report that on item_read; the producer refills a slot only when all ten readers
 // have (items without key blocks pass through no other barrier, so nothing else would bound how
 // far the producer runs ahead).  Handing items out at run
 // time is the longest-first schedule itself, and a CTA that finds its SM late (another kernel
-// holds it, e.g. a collective of a data-parallel step) takes fewer items instead of keeping a
-// fixed share back to the end.  Without a counter (fixed assignment): a boustrophedon deal.
+// holds it, e.g. a collective of a data-parallel step) takes fewer items, or none, instead of
+// keeping a fixed share back to the end.  Without a counter (fixed assignment): a boustrophedon deal.
 __device__ __forceinline__ int fixed_item_of(int k, int cid, int nc, int total) {
   if (static_cast<long long>(k) * nc >= total) return -1;
   const int idx = k * nc + ((k & 1) ? nc - 1 - cid : cid);
@@ -323,20 +322,20 @@ __global__ void __launch_bounds__(THREADS, 1)
     if (elect_one()) {
       uint32_t kv_cnt = 0, q_cnt[2] = {0, 0};
       bool ok = true;
-      // Every CTA draws after each item it takes, until a draw runs past the last item; the
-      // launch's last draw puts the counter back to zero.
+      // Every item is drawn, a CTA's first one too: a CTA that finds its SM late then finds
+      // nothing left instead of running one of the longest items after everybody else has
+      // finished.  A CTA draws until a draw runs past the last item; the launch's last draw puts
+      // the counter back to zero.
       const int total = p_in.total_items;
-      const unsigned total_draws = static_cast<unsigned>((total > nc ? total - nc : 0) + (nc < total ? nc : total));
-      int idx = cid < total ? cid : -1;
-      unsigned drawn = 0;  // the draw for the next item
+      const unsigned total_draws = static_cast<unsigned>(total) + static_cast<unsigned>(nc);
+      int idx = -1;
+      unsigned drawn = p_in.item_counter != nullptr ? atomicAdd(p_in.item_counter, 1u) : 0u;  // the draw for the next item
       for (int k = 0; ok; ++k) {
-        if (k > 0) {
-          if (p_in.item_counter != nullptr) {
-            idx = static_cast<unsigned>(nc) + drawn < static_cast<unsigned>(total) ? static_cast<int>(nc + drawn) : -1;
-            if (drawn + 1 == total_draws) atomicExch(p_in.item_counter, 0u);
-          } else {
-            idx = fixed_item_of(k, cid, nc, total);
-          }
+        if (p_in.item_counter != nullptr) {
+          idx = drawn < static_cast<unsigned>(total) ? static_cast<int>(drawn) : -1;
+          if (drawn + 1 == total_draws) atomicExch(p_in.item_counter, 0u);
+        } else {
+          idx = fixed_item_of(k, cid, nc, total);
         }
         if (k >= ITEM_SLOTS &&
             !mbar_wait(&bars->item_read[k % ITEM_SLOTS], ((k / ITEM_SLOTS) - 1) & 1, abort_word, 124)) {
