@@ -772,7 +772,14 @@ def run_kernel(args) -> None:
             " + colwise" if args.colwise else "")
     else:
         bsz, s_, h = args.batch, args.seq, args.heads
-        q, kx, v, do = (rnd(bsz, s_, h, 128) for _ in range(4))
+        if args.fused_qkv:  # q, k, v (and their gradients) as views of one [B, S, 3H, 128] buffer, the block's layout
+            qkv, dqkv = rnd(bsz, s_, 3 * h, 128), rnd(bsz, s_, 3 * h, 128)
+            q, kx, v = qkv[:, :, :h], qkv[:, :, h:2 * h], qkv[:, :, 2 * h:]
+            dq, dk, dv = dqkv[:, :, :h], dqkv[:, :, h:2 * h], dqkv[:, :, 2 * h:]
+            do = rnd(bsz, s_, h, 128)
+        else:
+            q, kx, v, do = (rnd(bsz, s_, h, 128) for _ in range(4))
+            dq, dk, dv = (torch.empty_like(q) for _ in range(3))
         aopts = cdl.ops.AttentionOpts(variant=args.variant)
         fwd = cdl.ops.attention_fwd(q, kx, v, aopts)
         if k == "attn_fwd":
@@ -780,12 +787,17 @@ def run_kernel(args) -> None:
             work = 4.0 * bsz * h * s_ * s_ * 128 / 2
         else:
             scr = torch.empty(cdl.ops.attention_bwd_scratch_bytes(q, kx), dtype=torch.uint8, device=dev)
-            dq, dk, dv = (torch.empty_like(q) for _ in range(3))
-            fns = [lambda: cdl.ops.attention_bwd(q, kx, v, fwd.out, do, fwd.lse, scratch=scr,
-                                                 dq=dq, dk=dk, dv=dv)]
+            table = None
+            if args.rope:  # the inverse rotary rotation of dQ / dK inside the store epilogues
+                inv = 1.0 / (10000.0 ** (torch.arange(0, 64, dtype=torch.float64) / 64))
+                ang = torch.arange(s_, dtype=torch.float64)[:, None] * inv[None]
+                table = torch.cat([ang.cos(), ang.sin()], 1).float().to(dev).contiguous()
+            fns = [lambda: cdl.ops.attention_bwd(q, kx, v, fwd.out, do, fwd.lse, aopts, scratch=scr,
+                                                 dq=dq, dk=dk, dv=dv, rope_table=table)]
             work = 10.0 * bsz * h * s_ * s_ * 128 / 2
         unit, peak = "TFLOP/s", peaks["bf16_burst"]
-        desc = f"{k} causal B={bsz} H={h} S={s_} D=128" + (f" variant {args.variant}" if args.variant else "")
+        desc = (f"{k} causal B={bsz} H={h} S={s_} D=128" + (f" variant {args.variant}" if args.variant else "")
+                + (" fused-qkv views" if args.fused_qkv else "") + (" + inverse RoPE" if args.rope and k == "attn_bwd" else ""))
     for i in range(args.warmup):
         fns[i % len(fns)]()
     torch.cuda.synchronize()
@@ -973,7 +985,12 @@ def main() -> None:
     ap.add_argument("--colwise", action="store_true",
                     help="norm_fwd_mx: also produce the colwise (transposed-block) output")
     ap.add_argument("--variant", type=int, default=0,
-                    help="attn_fwd: cdl_attn_desc.variant (0 default, 1 one-shot kernel, 2 persistent kernel)")
+                    help="attn_fwd / attn_bwd: cdl_attn_desc.variant (0 default, 1 one-shot kernels, 2 persistent kernels); "
+                         "norm_fwd / norm_bwd: cdl_norm_options.variant")
+    ap.add_argument("--rope", action="store_true",
+                    help="attn_bwd: with the inverse rotary rotation in the store epilogues (cdl_b200_attn_bwd_rope)")
+    ap.add_argument("--fused-qkv", action="store_true",
+                    help="attn_fwd / attn_bwd: q, k, v and dq, dk, dv are views of one [B, S, 3H, 128] buffer")
     ap.add_argument("--rows", type=int, default=16384)
     ap.add_argument("--cols", type=int, default=2048)
     ap.add_argument("--batch", type=int, default=8)
