@@ -345,7 +345,8 @@ def test_packed_equals_dense_for_equal_lengths(cdl, gpu_ok):
     assert torch.equal(pdv.view(b, s, h, 128), ddv)
 
 
-def test_packed_sequence_longer_than_the_bound_is_cut_and_reported(cdl, gpu_ok):
+@pytest.mark.parametrize("variant", [1, 2], ids=["one_shot", "persistent"])
+def test_packed_sequence_longer_than_the_bound_is_cut_and_reported(cdl, gpu_ok, variant):
     """max_seqlen_q / max_seqlen_k size the grids and the backward's statistics scratch.  A
     sequence longer than the bound must not make the backward read or write beyond that scratch:
     it is cut at the bound and the device status word reports code 921.  The sequences within the
@@ -353,12 +354,12 @@ def test_packed_sequence_longer_than_the_bound_is_cut_and_reported(cdl, gpu_ok):
     sq = [128, 300]
     q, k, v, do, cu_q, cu_k = make_packed(sq, sq, 2, 2)
     qd, kd, vd, dod = q.cuda(), k.cuda(), v.cuda(), do.cuda()
-    ok = cdl.ops.AttentionOpts(causal=True, cu_seqlens_q=cu_q.cuda(), cu_seqlens_k=cu_k.cuda(),
+    ok = cdl.ops.AttentionOpts(causal=True, variant=variant, cu_seqlens_q=cu_q.cuda(), cu_seqlens_k=cu_k.cuda(),
                                max_seqlen_q=300, max_seqlen_k=300)
     fwd = cdl.ops.attention_fwd(qd, kd, vd, ok)
     ref_dq, ref_dk, ref_dv = cdl.ops.attention_bwd(qd, kd, vd, fwd.out, dod, fwd.lse, ok)
     assert cdl._lib.device_status() == 0
-    low = cdl.ops.AttentionOpts(causal=True, cu_seqlens_q=cu_q.cuda(), cu_seqlens_k=cu_k.cuda(),
+    low = cdl.ops.AttentionOpts(causal=True, variant=variant, cu_seqlens_q=cu_q.cuda(), cu_seqlens_k=cu_k.cuda(),
                                 max_seqlen_q=128, max_seqlen_k=128)
     # scratch sized exactly by the (too small) bound, followed by a guard region
     n = ctypes.c_size_t(0)
