@@ -21,6 +21,12 @@ backward at B 8, H 16, S 2048 -- next to the library stand-ins for the reference
 (torch.matmul = cuBLASLt, torch SDPA), and under `lm_step` a short run of the 24-layer training
 step (configuration 5).  `--impl reference` times only the CPU path (the reference has no other
 host implementation of these operators and cannot be built here).
+
+`--kernel NAME` times one kernel alone (a CUDA graph of `--steps` back-to-back calls, best of three
+replays): gemm (`--m --n --k --layout --accumulate`), norm_fwd / norm_bwd (`--rows --cols --residual
+--variant`), attn_fwd / attn_bwd (`--batch --seq --heads`, `--variant` 1 = one short-lived CTA per
+block, 2 = one CTA per SM; `--fused-qkv` = operands as views of one [B, S, 3H, 128] buffer; attn_bwd
+`--rope` = with the inverse rotary rotation in the store epilogues), gemm_mx, norm_fwd_mx.
 """
 from __future__ import annotations
 
