@@ -31,7 +31,7 @@ pub struct CdlTensor {
 pub struct CdlAttnDesc {
     pub softmax_scale: f32, // <= 0: 1 / sqrt(head_dim)
     pub causal: i32,        // 0 = AttentionMask::None, 1 = AttentionMask::Causal
-    pub variant: i32,       // cdl_attn_variant: 0 auto, 1 one-shot forward, 2 persistent forward
+    pub variant: i32,       // cdl_attn_variant: 0 auto, 1 one short-lived CTA per block, 2 one CTA per SM (forward and backward)
 }
 
 /// `cdl_matmul_options`: what a tuner candidate of the matmul executor carries.
@@ -157,6 +157,21 @@ extern "C" {
     ) -> i32;
     pub fn cdl_b200_attn_bwd_packed_scratch_bytes(
         batch: i64, max_seqlen_q: i64, heads: i64, bytes_out: *mut usize,
+    ) -> i32;
+    // The backward with the inverse rotary rotation of dQ / dK in its store epilogues (q and k are
+    // the rotated tensors): for a graph pass that fuses the RoPE node behind AttentionBwd.
+    pub fn cdl_b200_attn_bwd_rope(
+        desc: *const CdlAttnDesc, q: *const CdlTensor, k: *const CdlTensor, v: *const CdlTensor,
+        o: *const CdlTensor, d_out: *const CdlTensor, lse: *const CdlTensor,
+        cos_sin: *const CdlTensor, dq: *const CdlTensor, dk: *const CdlTensor,
+        dv: *const CdlTensor, scratch: *mut c_void, scratch_bytes: usize, stream: *mut c_void,
+    ) -> i32;
+    pub fn cdl_b200_attn_bwd_packed_rope(
+        desc: *const CdlAttnDesc, q: *const CdlTensor, k: *const CdlTensor, v: *const CdlTensor,
+        o: *const CdlTensor, d_out: *const CdlTensor, lse: *const CdlTensor,
+        cu_seqlens_q: *const CdlTensor, cu_seqlens_k: *const CdlTensor, max_seqlen_q: i64,
+        max_seqlen_k: i64, cos_sin: *const CdlTensor, dq: *const CdlTensor, dk: *const CdlTensor,
+        dv: *const CdlTensor, scratch: *mut c_void, scratch_bytes: usize, stream: *mut c_void,
     ) -> i32;
 
     // ---- block-scaled tensors (MxTensor, crates/cleandl/src/mx_tensor.rs:11-30)
